@@ -1,0 +1,133 @@
+"""In-tree native build for tnn_b200.
+
+Two shared objects are produced next to this file, under ``_lib/``:
+
+* ``libtnnb_kernels.so`` - every CUDA kernel, compiled by ``nvcc`` for
+  ``sm_100a`` only and exported through ``extern "C"`` entry points (loaded
+  with ``ctypes``; it does not link against libtorch so it compiles in seconds).
+* ``_host.*.so`` - the host-side C++ runtime (typed config, archiver wire
+  format, TNNG checkpoints, graph IR, partitioner, CPU oracle engine, profiler,
+  data loaders, allocators) as a pybind11 module.
+
+Both are rebuilt only when a source is newer than the output.
+"""
+from __future__ import annotations
+
+import glob
+import os
+import subprocess
+import sys
+import sysconfig
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(ROOT, "csrc")
+LIB = os.path.join(ROOT, "_lib")
+
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+CXX = os.environ.get("CXX", "g++")
+
+CUDA_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
+    "--expt-relaxed-constexpr",
+]
+
+
+def _newer(srcs, out):
+    if not os.path.exists(out):
+        return True
+    t = os.path.getmtime(out)
+    return any(os.path.getmtime(s) > t for s in srcs)
+
+
+def _run(cmd, verbose):
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("build step failed: " + " ".join(cmd[:6]) + " ...")
+    if verbose and (r.stdout or r.stderr):
+        print(r.stdout + r.stderr)
+
+
+def kernels_path():
+    return os.path.join(LIB, "libtnnb_kernels.so")
+
+
+def host_path():
+    ext = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    return os.path.join(LIB, "_host" + ext)
+
+
+def build_kernels(verbose=False, force=False, ptxas_info=False):
+    os.makedirs(LIB, exist_ok=True)
+    kdir = os.path.join(CSRC, "kernels")
+    srcs = sorted(glob.glob(os.path.join(kdir, "*.cu")))
+    hdrs = glob.glob(os.path.join(kdir, "*.cuh")) + glob.glob(os.path.join(kdir, "*.h"))
+    objs = []
+    jobs = []
+    for s in srcs:
+        o = os.path.join(LIB, os.path.basename(s)[:-3] + ".o")
+        objs.append(o)
+        if force or _newer([s] + hdrs, o):
+            cmd = [NVCC] + CUDA_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + ["-I", kdir, "-c", s, "-o", o]
+            jobs.append(cmd)
+    if jobs:
+        procs = []
+        for cmd in jobs:
+            if verbose:
+                print(" ".join(cmd), flush=True)
+            procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        for cmd, pr in procs:
+            out, _ = pr.communicate()
+            if pr.returncode != 0:
+                sys.stderr.write(out)
+                raise RuntimeError("nvcc failed for " + cmd[-3])
+            if (verbose or ptxas_info) and out:
+                print(out)
+    out = kernels_path()
+    if force or jobs or _newer(objs, out):
+        _run([NVCC, "-shared", "-o", out] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"], verbose)
+    return out
+
+
+def build_host(verbose=False, force=False):
+    import pybind11
+
+    os.makedirs(LIB, exist_ok=True)
+    hdir = os.path.join(CSRC, "host")
+    srcs = sorted(glob.glob(os.path.join(hdir, "*.cc")))
+    hdrs = glob.glob(os.path.join(hdir, "*.h"))
+    out = host_path()
+    site = os.path.dirname(os.path.dirname(pybind11.__file__))
+    json_inc = os.path.join(site, "include", "cudnn_frontend", "thirdparty")
+    objs = []
+    procs = []
+    for s in srcs:
+        o = os.path.join(LIB, "host_" + os.path.basename(s)[:-3] + ".o")
+        objs.append(o)
+        if force or _newer([s] + hdrs, o):
+            cmd = [CXX, "-O2", "-std=c++17", "-fPIC", "-fopenmp", "-fvisibility=hidden", "-I", hdir,
+                   "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
+                   "-I", json_inc, "-c", s, "-o", o]
+            if verbose:
+                print(" ".join(cmd), flush=True)
+            procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    for s, pr in procs:
+        o, _ = pr.communicate()
+        if pr.returncode != 0:
+            sys.stderr.write(o)
+            raise RuntimeError("g++ failed for " + s)
+    if force or procs or _newer(objs, out):
+        _run([CXX, "-shared", "-fopenmp", "-o", out] + objs, verbose)
+    return out
+
+
+def build_all(verbose=False, force=False):
+    return build_kernels(verbose, force), build_host(verbose, force)
+
+
+if __name__ == "__main__":
+    build_all(verbose=True, force="--force" in sys.argv)
+    print("built:", kernels_path(), host_path())

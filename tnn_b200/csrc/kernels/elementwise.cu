@@ -1,0 +1,312 @@
+// Bandwidth-bound element-wise kernels (bf16 I/O, fp32 math, 16-byte vectors):
+// activations, binary ops, dropout with a regenerable counter-based mask,
+// token+position embedding and its scatter-add gradient, bias-gradient column
+// sums. They replace the reference's one-element-per-thread kernels
+// (src/nn/activations_impl/cuda/*.cu, src/nn/engines/cudnn_engine.cu:31-50,
+// 1077-1233, src/ops/cuda/kernels.cu:30-591).
+#include "ptx.cuh"
+
+namespace tnnb {
+
+typedef __nv_bfloat16 bf16;
+
+struct alignas(16) Bf8 {
+  bf16 v[8];
+};
+
+__device__ __forceinline__ void load8(const bf16* p, float (&f)[8]) {
+  Bf8 r = *reinterpret_cast<const Bf8*>(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(r.v[i]);
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
+  Bf8 r;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) r.v[i] = __float2bfloat16(f[i]);
+  *reinterpret_cast<Bf8*>(p) = r;
+}
+
+enum ActKind { ACT_RELU = 0, ACT_GELU = 1, ACT_ELU = 2, ACT_LEAKY = 3, ACT_SIGMOID = 4, ACT_TANH = 5, ACT_LINEAR = 6 };
+
+__device__ __forceinline__ float act_fwd(int kind, float x, float alpha) {
+  switch (kind) {
+    case ACT_RELU: return fmaxf(x, 0.f);
+    case ACT_GELU: return gelu_tanh(x);
+    case ACT_ELU: return x > 0.f ? x : alpha * (__expf(x) - 1.f);
+    case ACT_LEAKY: return x > 0.f ? x : alpha * x;
+    case ACT_SIGMOID: return 1.f / (1.f + __expf(-x));
+    case ACT_TANH: return tanhf(x);
+    default: return x;
+  }
+}
+// Derivative with respect to the input x (the saved tensor is the input).
+__device__ __forceinline__ float act_bwd(int kind, float x, float alpha) {
+  switch (kind) {
+    case ACT_RELU: return x > 0.f ? 1.f : 0.f;
+    case ACT_GELU: return gelu_tanh_grad(x);
+    case ACT_ELU: return x > 0.f ? 1.f : alpha * __expf(x);
+    case ACT_LEAKY: return x > 0.f ? 1.f : alpha;
+    case ACT_SIGMOID: {
+      float s = 1.f / (1.f + __expf(-x));
+      return s * (1.f - s);
+    }
+    case ACT_TANH: {
+      float t = tanhf(x);
+      return 1.f - t * t;
+    }
+    default: return 1.f;
+  }
+}
+
+__global__ void act_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long n, int kind,
+                               float alpha) {
+  long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  for (; i + 8 <= n; i += stride) {
+    float f[8];
+    load8(x + i, f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = act_fwd(kind, f[k], alpha);
+    store8(y + i, f);
+  }
+  if (i < n && i + 8 > n)
+    for (long long j = i; j < n; ++j) y[j] = __float2bfloat16(act_fwd(kind, __bfloat162float(x[j]), alpha));
+}
+
+__global__ void act_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy,
+                               bf16* __restrict__ dx, long long n, int kind, float alpha) {
+  long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  for (; i + 8 <= n; i += stride) {
+    float f[8], g[8];
+    load8(x + i, f);
+    load8(dy + i, g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) g[k] *= act_bwd(kind, f[k], alpha);
+    store8(dx + i, g);
+  }
+  if (i < n && i + 8 > n)
+    for (long long j = i; j < n; ++j)
+      dx[j] = __float2bfloat16(__bfloat162float(dy[j]) * act_bwd(kind, __bfloat162float(x[j]), alpha));
+}
+
+// out = a (op) b, op: 0 add, 1 sub, 2 mul, 3 div.  relu!=0 applies max(.,0).
+__global__ void binary_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b,
+                              bf16* __restrict__ o, long long n, int op, int relu) {
+  long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  for (; i + 8 <= n; i += stride) {
+    float f[8], g[8];
+    load8(a + i, f);
+    load8(b + i, g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float r = op == 0 ? f[k] + g[k] : op == 1 ? f[k] - g[k] : op == 2 ? f[k] * g[k] : f[k] / g[k];
+      f[k] = relu ? fmaxf(r, 0.f) : r;
+    }
+    store8(o + i, f);
+  }
+  if (i < n && i + 8 > n)
+    for (long long j = i; j < n; ++j) {
+      float x = __bfloat162float(a[j]), y = __bfloat162float(b[j]);
+      float r = op == 0 ? x + y : op == 1 ? x - y : op == 2 ? x * y : x / y;
+      o[j] = __float2bfloat16(relu ? fmaxf(r, 0.f) : r);
+    }
+}
+
+// y = keep ? x / (1-p) : 0, keep regenerated from (seed, element index).
+__global__ void dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long n, float p,
+                               unsigned long long seed) {
+  const float inv = 1.f / (1.f - p);
+  long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  for (; i + 8 <= n; i += stride) {
+    float f[8];
+    load8(x + i, f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = hash_uniform(seed, i + k) >= p ? f[k] * inv : 0.f;
+    store8(y + i, f);
+  }
+  if (i < n && i + 8 > n)
+    for (long long j = i; j < n; ++j)
+      y[j] = __float2bfloat16(hash_uniform(seed, j) >= p ? __bfloat162float(x[j]) * inv : 0.f);
+}
+
+// out[r, :] = wte[clamp(id[r])] (+ wpe[r % S]) then optional dropout.
+__global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ wte,
+                                     const bf16* __restrict__ wpe, bf16* __restrict__ out,
+                                     long long rows, int E, int S, long long vocab,
+                                     long long padding_idx, float p, unsigned long long seed) {
+  const int chunks = E / 8;
+  const float inv = 1.f / (1.f - p);
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    long long id = ids[r];
+    const bool pad = (id == padding_idx);
+    if (id < 0 || id >= vocab) id = 0;
+    const bf16* trow = wte + id * E;
+    const bf16* prow = wpe ? wpe + (long long)(r % S) * E : nullptr;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+      float f[8], g[8];
+      load8(trow + c * 8, f);
+      if (pad)
+        for (int k = 0; k < 8; ++k) f[k] = 0.f;
+      if (prow) {
+        load8(prow + c * 8, g);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] += g[k];
+      }
+      if (p > 0.f) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          f[k] = hash_uniform(seed, r * E + c * 8 + k) >= p ? f[k] * inv : 0.f;
+      }
+      store8(out + r * E + c * 8, f);
+    }
+  }
+}
+
+// dwte[id[r]] += dropout'(dy[r]);  dwpe[r % S] += dropout'(dy[r])  (fp32 atomics)
+__global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ dy,
+                                     float* __restrict__ dwte, float* __restrict__ dwpe,
+                                     long long rows, int E, int S, long long vocab,
+                                     long long padding_idx, float p, unsigned long long seed) {
+  const int chunks = E / 8;
+  const float inv = 1.f / (1.f - p);
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    long long id = ids[r];
+    const bool pad = (id == padding_idx);
+    if (id < 0 || id >= vocab) id = 0;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+      float g[8];
+      load8(dy + r * E + c * 8, g);
+      if (p > 0.f) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          g[k] = hash_uniform(seed, r * E + c * 8 + k) >= p ? g[k] * inv : 0.f;
+      }
+      if (!pad && dwte) {
+        float* d = dwte + id * E + c * 8;
+        asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(d), "f"(g[0]), "f"(g[1]), "f"(g[2]), "f"(g[3]) : "memory");
+        asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(d + 4), "f"(g[4]), "f"(g[5]), "f"(g[6]), "f"(g[7]) : "memory");
+      }
+      if (dwpe) {
+        float* d = dwpe + (long long)(r % S) * E + c * 8;
+        asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(d), "f"(g[0]), "f"(g[1]), "f"(g[2]), "f"(g[3]) : "memory");
+        asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(d + 4), "f"(g[4]), "f"(g[5]), "f"(g[6]), "f"(g[7]) : "memory");
+      }
+    }
+  }
+}
+
+// db[n] += sum_m dy[m, n].  Block = 32 column-chunks (256 columns) x 8 row lanes.
+__global__ void colsum_kernel(const bf16* __restrict__ dy, long long ld, float* __restrict__ db,
+                              long long M, int N, int rows_per_block) {
+  __shared__ float red[8][32][9];
+  const int cx = threadIdx.x, ry = threadIdx.y;
+  const int col = (blockIdx.x * 32 + cx) * 8;
+  const long long r0 = (long long)blockIdx.y * rows_per_block;
+  const long long r1 = min(M, r0 + rows_per_block);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (col + 8 <= N && (ld % 8 == 0)) {
+    for (long long r = r0 + ry; r < r1; r += 8) {
+      float f[8];
+      load8(dy + r * ld + col, f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += f[k];
+    }
+  } else if (col < N) {
+    for (long long r = r0 + ry; r < r1; r += 8)
+      for (int k = 0; k < 8 && col + k < N; ++k) acc[k] += __bfloat162float(dy[r * ld + col + k]);
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) red[ry][cx][k] = acc[k];
+  __syncthreads();
+  if (ry == 0 && col < N) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += red[j][cx][k];
+      if (col + k < N) atomicAdd(db + col + k, s);
+    }
+  }
+}
+
+// dst(bf16) = src(fp32) and back; used for parameter casts of flat buffers.
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ s, bf16* __restrict__ d, long long n) {
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) d[i] = __float2bfloat16(s[i]);
+}
+
+static inline int grid_for(long long n, int per_thread, int block) {
+  long long g = (n + (long long)per_thread * block - 1) / ((long long)per_thread * block);
+  long long cap = 148ll * 16;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace tnnb
+
+using namespace tnnb;
+
+#define LAUNCH_RC()                                         \
+  do {                                                      \
+    cudaError_t e__ = cudaGetLastError();                   \
+    return e__ == cudaSuccess ? 0 : -(int)e__ - 1000;       \
+  } while (0)
+
+extern "C" {
+
+int tnnb_act_fwd(const void* x, void* y, long long n, int kind, float alpha, void* stream) {
+  if (((uintptr_t)x | (uintptr_t)y) & 15) return -4;
+  act_fwd_kernel<<<grid_for(n, 8, 256), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, n, kind, alpha);
+  LAUNCH_RC();
+}
+int tnnb_act_bwd(const void* x, const void* dy, void* dx, long long n, int kind, float alpha, void* stream) {
+  if (((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dx) & 15) return -4;
+  act_bwd_kernel<<<grid_for(n, 8, 256), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)dy, (bf16*)dx, n, kind, alpha);
+  LAUNCH_RC();
+}
+int tnnb_binary(const void* a, const void* b, void* o, long long n, int op, int relu, void* stream) {
+  if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)o) & 15) return -4;
+  binary_kernel<<<grid_for(n, 8, 256), 256, 0, (cudaStream_t)stream>>>((const bf16*)a, (const bf16*)b, (bf16*)o, n, op, relu);
+  LAUNCH_RC();
+}
+int tnnb_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, void* stream) {
+  if (((uintptr_t)x | (uintptr_t)y) & 15) return -4;
+  if (p < 0.f || p >= 1.f) return -2;
+  dropout_kernel<<<grid_for(n, 8, 256), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, n, p, seed);
+  LAUNCH_RC();
+}
+int tnnb_embedding_fwd(const void* ids, const void* wte, const void* wpe, void* out, long long rows, int E,
+                       int S, long long vocab, long long padding_idx, float p, unsigned long long seed,
+                       void* stream) {
+  if (E % 8) return -3;
+  int grid = (int)(rows < 148 * 8 ? rows : 148 * 8);
+  embedding_fwd_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((const long long*)ids, (const bf16*)wte, (const bf16*)wpe,
+                                                              (bf16*)out, rows, E, S, vocab, padding_idx, p, seed);
+  LAUNCH_RC();
+}
+int tnnb_embedding_bwd(const void* ids, const void* dy, void* dwte, void* dwpe, long long rows, int E, int S,
+                       long long vocab, long long padding_idx, float p, unsigned long long seed, void* stream) {
+  if (E % 8) return -3;
+  int grid = (int)(rows < 148 * 8 ? rows : 148 * 8);
+  embedding_bwd_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((const long long*)ids, (const bf16*)dy, (float*)dwte,
+                                                              (float*)dwpe, rows, E, S, vocab, padding_idx, p, seed);
+  LAUNCH_RC();
+}
+int tnnb_colsum_accum(const void* dy, long long ld, void* db, long long M, int N, void* stream) {
+  int gx = (N + 255) / 256;
+  int want_y = (2 * 148 + gx - 1) / gx;
+  long long rpb = (M + want_y - 1) / want_y;
+  if (rpb < 64) rpb = 64;
+  int gy = (int)((M + rpb - 1) / rpb);
+  colsum_kernel<<<dim3(gx, gy), dim3(32, 8), 0, (cudaStream_t)stream>>>((const bf16*)dy, ld, (float*)db, M, N, (int)rpb);
+  LAUNCH_RC();
+}
+int tnnb_cast_f32_bf16(const void* s, void* d, long long n, void* stream) {
+  cast_f32_bf16_kernel<<<grid_for(n, 4, 256), 256, 0, (cudaStream_t)stream>>>((const float*)s, (bf16*)d, n);
+  LAUNCH_RC();
+}
+
+}  // extern "C"

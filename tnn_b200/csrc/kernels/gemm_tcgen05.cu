@@ -1,0 +1,550 @@
+// bf16 GEMM for sm_100a: TMA -> 128B-swizzled shared memory -> tcgen05.mma
+// with the fp32 accumulator in TMEM -> tcgen05.ld epilogue.
+//
+//   D[M,N] (+)= op(A)[M,K] * op(B)[N,K]^T   (+ bias, GELU, dGELU, ReLU, residual)
+//
+// Either operand may be "K-major" (stored [rows, K], K contiguous) or
+// "MN-major" (stored [K, rows], rows contiguous), which is what lets one
+// kernel serve the three products of a dense layer without a transpose pass:
+//   forward  Y  = X  * W^T      A K-major,  B K-major
+//   dgrad    dX = dY * W        A K-major,  B MN-major
+//   wgrad    dW += dY^T * X     A MN-major, B MN-major, fp32 atomic split-K
+// The reference obtains these from cublasGemmEx / cuDNN matmul graphs
+// (src/math/cuda/gemm.cu:72-112, src/nn/engines/cudnn_engine.cu:113-326).
+//
+// Structure: persistent CTAs (one per SM), 6 warps.
+//   warp 0      TMA producer (one lane), STAGES-deep ring of (A,B) k-blocks
+//   warp 1      TMEM owner + MMA issuer (one lane), two accumulators so the
+//               epilogue of tile i overlaps the main loop of tile i+1
+//   warps 2-5   epilogue: TMEM -> registers -> fused math -> global memory
+// Every barrier wait is bounded; on expiry the kernel records a status code,
+// raises a CTA-wide abort flag and unwinds (TMEM is always released).
+#include "gemm_tcgen05.h"
+
+#include <mutex>
+
+#include "ptx.cuh"
+
+namespace tnnb {
+
+struct GemmParams {
+  int M, N, K;
+  int num_m_blocks, num_n_blocks, num_k_blocks;
+  int split_k, kb_per_split;
+  void* D;
+  long long ldd;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* aux_in;
+  __nv_bfloat16* aux_out;
+  long long ld_aux;
+  const __nv_bfloat16* resid;
+  long long ld_res;
+  int flags;
+  int* status;
+};
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Wait on an mbarrier phase for at most ~2 s, giving up early when another
+// role of this CTA has already raised the abort flag.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity,
+                                              volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 127u) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > 2000000000ull) return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void raise_abort(const GemmParams& p, volatile uint32_t* abort_flag,
+                                            int code) {
+  *abort_flag = 1;
+  if (p.status) atomicCAS(p.status, 0, code);
+}
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int BM = 128;
+  static constexpr int BK = 64;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+template <int BN>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, uint32_t (&r)[32], int row,
+                                               int col0) {
+  if (row >= p.M || col0 >= p.N) return;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  const int flags = p.flags;
+  const bool full = (col0 + 32 <= p.N);
+
+  if (flags & EPI_BIAS) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (full || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+  }
+  if (flags & EPI_GELU) {
+    if (p.aux_out) {
+      __nv_bfloat16* z = p.aux_out + (long long)row * p.ld_aux + col0;
+      if (full && (p.ld_aux % 8 == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          __align__(16) __nv_bfloat16 t[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) t[k] = __float2bfloat16(v[j + k]);
+          *reinterpret_cast<uint4*>(z + j) = *reinterpret_cast<uint4*>(t);
+        }
+      } else {
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) z[j] = __float2bfloat16(v[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+  }
+  if (flags & EPI_DGELU) {
+    const __nv_bfloat16* z = p.aux_in + (long long)row * p.ld_aux + col0;
+    if (full && (p.ld_aux % 8 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 raw = *reinterpret_cast<const uint4*>(z + j);
+        const __nv_bfloat16* t = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[j + k] *= gelu_tanh_grad(__bfloat162float(t[k]));
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) v[j] *= gelu_tanh_grad(__bfloat162float(z[j]));
+    }
+  }
+  if (flags & EPI_RELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+  }
+  if (flags & EPI_RESID) {
+    const __nv_bfloat16* rs = p.resid + (long long)row * p.ld_res + col0;
+    if (full && (p.ld_res % 8 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 raw = *reinterpret_cast<const uint4*>(rs + j);
+        const __nv_bfloat16* t = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[j + k] += __bfloat162float(t[k]);
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) v[j] += __bfloat162float(rs[j]);
+    }
+  }
+
+  if (flags & EPI_ATOMIC) {
+    float* d = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col0;
+    if (full && (p.ldd % 4 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d + j), "f"(v[j]),
+                     "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3])
+                     : "memory");
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) atomicAdd(d + j, v[j]);
+    }
+  } else if (flags & EPI_OUT_F32) {
+    float* d = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col0;
+    if (full && (p.ldd % 4 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (flags & EPI_ACCUM) {
+          float4 old = *reinterpret_cast<float4*>(d + j);
+          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+        }
+        *reinterpret_cast<float4*>(d + j) = o;
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) d[j] = (flags & EPI_ACCUM) ? d[j] + v[j] : v[j];
+    }
+  } else {
+    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + col0;
+    if (full && (p.ldd % 8 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        __align__(16) __nv_bfloat16 t[8];
+        if (flags & EPI_ACCUM) {
+          uint4 raw = *reinterpret_cast<const uint4*>(d + j);
+          const __nv_bfloat16* o = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) t[k] = __float2bfloat16(v[j + k] + __bfloat162float(o[k]));
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) t[k] = __float2bfloat16(v[j + k]);
+        }
+        *reinterpret_cast<uint4*>(d + j) = *reinterpret_cast<uint4*>(t);
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N)
+          d[j] = __float2bfloat16((flags & EPI_ACCUM) ? v[j] + __bfloat162float(d[j]) : v[j]);
+    }
+  }
+}
+
+template <int BN, int A_MN, int B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                         const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles = p.num_m_blocks * p.num_n_blocks;
+  const int total_work = tiles * p.split_k;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int last_stage = -1;
+      uint32_t last_phase = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
+        const int ks = work / tiles;
+        const int t = work - ks * tiles;
+        const int nb = t / p.num_m_blocks;
+        const int mb = t - nb * p.num_m_blocks;
+        const int kb0 = ks * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!wait_or_abort(&empty[stage], phase ^ 1, abort_flag)) {
+            raise_abort(p, abort_flag, ST_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          uint8_t* a_dst = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + Cfg::A_BYTES;
+          if (A_MN == 0) {
+            tma_load_2d(a_dst, &tmA, &full[stage], kb * 64, mb * 128);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              tma_load_2d(a_dst + i * 8192, &tmA, &full[stage], mb * 128 + i * 64, kb * 64);
+          }
+          if (B_MN == 0) {
+            tma_load_2d(b_dst, &tmB, &full[stage], kb * 64, nb * BN);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_2d(b_dst + i * 8192, &tmB, &full[stage], nb * BN + i * 64, kb * 64);
+          }
+          last_stage = stage;
+          last_phase = phase;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      // On an abort, let the newest copy land before the CTA retires.
+      if (!ok && last_stage >= 0) {
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(&full[last_stage], last_phase)) {
+          if (globaltimer_ns() - t0 > 200000000ull) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
+        const int ks = work / tiles;
+        const int kb0 = ks * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
+        if (!wait_or_abort(&tempty[acc], acc_phase ^ 1, abort_flag)) {
+          raise_abort(p, abort_flag, ST_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!wait_or_abort(&full[stage], phase, abort_flag)) {
+            raise_abort(p, abort_flag, ST_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t ad = A_MN ? make_smem_desc(a_addr + k * 2048, 8192, 1024)
+                                     : make_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024)
+                                     : make_smem_desc(b_addr + k * 32, 16, 1024);
+            tc_mma_ss(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        tc_commit(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
+      const int ks = work / tiles;
+      const int t = work - ks * tiles;
+      const int nb = t / p.num_m_blocks;
+      const int mb = t - nb * p.num_m_blocks;
+      if (!wait_or_abort(&tfull[acc], acc_phase, abort_flag)) {
+        if (lane == 0) raise_abort(p, abort_flag, ST_TIMEOUT_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      const int row = mb * 128 + q * 32 + lane;
+      const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        epilogue_chunk<BN>(p, r, row, nb * BN + c * 32);
+      }
+      tc_fence_before();
+      mbar_arrive(&tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+int encode_tmap_bf16(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
+                     const uint64_t* strides_bytes, const uint32_t* box,
+                     const uint32_t* elem_strides) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[5];
+  cuuint32_t bx[5];
+  cuuint32_t es[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = elem_strides ? elem_strides[i] : 1;
+    if (i > 0) gstr[i - 1] = strides_bytes[i - 1];
+  }
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdim, gstr,
+                  bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 100;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int BN, int A_MN, int B_MN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+                       cudaStream_t stream) {
+  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmCfg<BN>::SMEM_BYTES);
+    if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
+    attr_set = true;
+  }
+  kern<<<grid, 192, GemmCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
+}  // namespace tnnb
+
+using namespace tnnb;
+
+extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int a_mn,
+                              int b_mn, long long lda, long long ldb, long long ldd,
+                              const void* bias, const void* aux_in, void* aux_out,
+                              long long ld_aux, const void* resid, long long ld_res, int flags,
+                              int split_k, int force_bn, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return -2;
+  if ((lda % 8) || (ldb % 8)) return -3;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -4;
+  if ((flags & EPI_BIAS) && !bias) return -5;
+  if ((flags & EPI_DGELU) && !aux_in) return -5;
+  if ((flags & EPI_RESID) && !resid) return -5;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.num_m_blocks = (M + 127) / 128;
+  p.num_k_blocks = (K + 63) / 64;
+  int bn = force_bn;
+  if (bn != 128 && bn != 256) {
+    const int t256 = p.num_m_blocks * ((N + 255) / 256);
+    bn = (N > 128 && t256 * (split_k > 0 ? split_k : 1) >= sm_count()) ? 256 : 128;
+    if (N > 128 && (flags & EPI_ATOMIC)) bn = 256;
+  }
+  p.num_n_blocks = (N + bn - 1) / bn;
+  const int tiles = p.num_m_blocks * p.num_n_blocks;
+  if (split_k <= 0) {
+    split_k = 1;
+    if (flags & EPI_ATOMIC) {
+      // Enough (tile, k-range) work items to fill the machine about twice.
+      const int want = (2 * sm_count() + tiles - 1) / tiles;
+      split_k = max(1, min(want, p.num_k_blocks / 4 > 0 ? p.num_k_blocks / 4 : 1));
+    }
+  }
+  if (split_k > 1 && !(flags & EPI_ATOMIC)) return -6;
+  split_k = min(split_k, p.num_k_blocks);
+  p.kb_per_split = (p.num_k_blocks + split_k - 1) / split_k;
+  p.split_k = (p.num_k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+  p.D = D; p.ldd = ldd;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.aux_in = static_cast<const __nv_bfloat16*>(aux_in);
+  p.aux_out = static_cast<__nv_bfloat16*>(aux_out);
+  p.ld_aux = ld_aux;
+  p.resid = static_cast<const __nv_bfloat16*>(resid);
+  p.ld_res = ld_res;
+  p.flags = flags;
+  p.status = status;
+
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn) {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {64, 128};
+    rc = encode_tmap_bf16(&ta, A, 2, dims, str, box, nullptr);
+  } else {
+    uint64_t dims[2] = {(uint64_t)M, (uint64_t)K};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {64, 64};
+    rc = encode_tmap_bf16(&ta, A, 2, dims, str, box, nullptr);
+  }
+  if (rc) return rc;
+  if (!b_mn) {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {64, (uint32_t)bn};
+    rc = encode_tmap_bf16(&tb, B, 2, dims, str, box, nullptr);
+  } else {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {64, 64};
+    rc = encode_tmap_bf16(&tb, B, 2, dims, str, box, nullptr);
+  }
+  if (rc) return rc;
+
+  const int grid = min(tiles * p.split_k, sm_count());
+#define TNNB_LAUNCH(BN_, AM, BM_) return launch_gemm<BN_, AM, BM_>(ta, tb, p, grid, stream)
+  if (bn == 256) {
+    if (!a_mn && !b_mn) TNNB_LAUNCH(256, 0, 0);
+    if (!a_mn && b_mn) TNNB_LAUNCH(256, 0, 1);
+    if (a_mn && !b_mn) TNNB_LAUNCH(256, 1, 0);
+    TNNB_LAUNCH(256, 1, 1);
+  } else {
+    if (!a_mn && !b_mn) TNNB_LAUNCH(128, 0, 0);
+    if (!a_mn && b_mn) TNNB_LAUNCH(128, 0, 1);
+    if (a_mn && !b_mn) TNNB_LAUNCH(128, 1, 0);
+    TNNB_LAUNCH(128, 1, 1);
+  }
+#undef TNNB_LAUNCH
+}
