@@ -1,0 +1,77 @@
+"""The fp32 torch restatements in ops.raw (used as references for the kernels) against autograd."""
+import torch
+
+from tnn_b200.ops import raw
+from tnn_b200.ops.gemm import gemm, gelu_tanh_grad
+
+
+def test_hash_uniform_range_and_rate():
+    u = raw.hash_uniform(42, torch.arange(100000))
+    assert 0 <= u.min() and u.max() < 1
+    assert abs(u.mean().item() - 0.5) < 0.01
+    assert abs((u >= 0.3).float().mean().item() - 0.7) < 0.01
+
+
+def test_layernorm_matches_autograd():
+    torch.manual_seed(0)
+    x = torch.randn(17, 64, requires_grad=True)
+    g = torch.randn(64, requires_grad=True)
+    b = torch.randn(64, requires_grad=True)
+    ref = torch.nn.functional.layer_norm(x, (64,), g, b, 1e-5)
+    _, h, mean, rstd = raw.layernorm_fwd(x.detach(), None, g.detach(), b.detach(), 1e-5)
+    assert torch.allclose(h, ref, atol=1e-5)
+    dh = torch.randn(17, 64)
+    ref.backward(dh)
+    dg, db = torch.zeros(64), torch.zeros(64)
+    dx, _ = raw.layernorm_bwd(dh, x.detach(), mean, rstd, g.detach(), None, False, 0.0, 0, dg, db)
+    assert torch.allclose(dx, x.grad, atol=1e-4)
+    assert torch.allclose(dg, g.grad, atol=1e-4) and torch.allclose(db, b.grad, atol=1e-4)
+
+
+def test_attention_matches_autograd():
+    torch.manual_seed(1)
+    B, S, H, D = 2, 24, 2, 8
+    qkv = torch.randn(B * S, 3 * H * D, requires_grad=True)
+    q, k, v = (t.reshape(B, S, H, D).transpose(1, 2) for t in qkv.reshape(B * S, 3, H * D).unbind(1))
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, scale=0.3)
+    ref = ref.transpose(1, 2).reshape(B * S, H * D)
+    out, lse = raw.attn_fwd(qkv.detach(), B, S, H, D, True, 0.3)
+    assert torch.allclose(out, ref, atol=1e-5)
+    do = torch.randn_like(ref)
+    ref.backward(do)
+    d = raw.attn_bwd(qkv.detach(), out, do, lse, B, S, H, D, True, 0.3)
+    assert torch.allclose(d, qkv.grad, atol=1e-4)
+
+
+def test_softmax_ce_matches_autograd():
+    torch.manual_seed(2)
+    z = torch.randn(9, 13, requires_grad=True)
+    y = torch.randint(0, 13, (9,))
+    ref = torch.nn.functional.cross_entropy(z, y)
+    ref.backward()
+    loss, corr, grad = raw.softmax_ce(z.detach(), y, 13, 1.0 / 9, 1.0 / 9)
+    assert torch.allclose(loss[0], ref, atol=1e-5)
+    assert torch.allclose(grad, z.grad, atol=1e-5)
+    assert int(corr) == int((z.argmax(1) == y).sum())
+
+
+def test_gelu_grad_and_cpu_gemm_epilogues():
+    x = torch.linspace(-4, 4, 101, requires_grad=True)
+    torch.nn.functional.gelu(x, approximate="tanh").sum().backward()
+    assert torch.allclose(gelu_tanh_grad(x.detach()), x.grad, atol=1e-5)
+    a, b = torch.randn(5, 7), torch.randn(3, 7)
+    out = gemm(a, b, bias=torch.ones(3), relu=True, out_dtype=torch.float32)
+    assert torch.allclose(out, torch.relu(a @ b.t() + 1), atol=1e-5)
+    acc = torch.ones(3, 7)
+    gemm(torch.randn(11, 3), torch.randn(11, 7), a_t=True, b_t=True, out=acc, atomic=True)
+    assert acc.shape == (3, 7)
+
+
+def test_adam_matches_reference_formula():
+    w = torch.tensor([1.0, -2.0])
+    g = torch.tensor([0.5, 0.25])
+    m, v = torch.zeros(2), torch.zeros(2)
+    raw.adam_step(w, None, g, m, v, 0.1, 0.9, 0.999, 1e-8, 0.01, 1)
+    mh, vh = g, g * g
+    exp = torch.tensor([1.0, -2.0]) - 0.1 * mh / (vh.sqrt() + 1e-8) - 0.01 * 0.1 * torch.tensor([1.0, -2.0])
+    assert torch.allclose(w, exp, atol=1e-6)

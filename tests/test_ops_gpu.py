@@ -1,0 +1,165 @@
+"""Each sm_100a kernel against the fp32 torch restatement of the same op (ops.raw CPU path)."""
+import pytest
+import torch
+
+from tnn_b200.ops import _lib, raw
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def rnd(*shape, scale=1.0):
+    return (torch.randn(*shape) * scale).to(BF)
+
+
+def close(got, ref, tol=2e-2, what=""):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    err = (got - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < tol, f"{what} rel err {err / scale:.4g} (abs {err:.4g})"
+
+
+@pytest.mark.parametrize("kind,alpha", [("relu", 0), ("gelu", 0), ("elu", 1.0), ("leaky_relu", 0.01),
+                                        ("sigmoid", 0), ("tanh", 0), ("linear", 0)])
+def test_activations(kind, alpha):
+    torch.manual_seed(0)
+    x, dy = rnd(1000, 37), rnd(1000, 37)
+    close(raw.act_fwd(x.cuda(), kind, alpha), raw.act_fwd(x, kind, alpha), what=kind)
+    close(raw.act_bwd(x.cuda(), dy.cuda(), kind, alpha), raw.act_bwd(x, dy, kind, alpha), what=kind + " bwd")
+
+
+@pytest.mark.parametrize("op", ["add", "sub", "mul", "div"])
+def test_binary(op):
+    a, b = rnd(333, 65), rnd(333, 65).abs() + 1
+    close(raw.binary(a.cuda(), b.cuda(), op), raw.binary(a, b, op))
+    close(raw.binary(a.cuda(), b.cuda(), op, relu=True), raw.binary(a, b, op, relu=True))
+
+
+def test_dropout_mask_matches_host_hash():
+    x = rnd(257, 129)
+    y = raw.dropout(x.cuda(), 0.3, 1234567)
+    ref = raw.dropout(x, 0.3, 1234567)
+    close(y, ref)
+    keep = (y != 0).float().mean().item()
+    assert 0.6 < keep < 0.8
+
+
+def test_embedding():
+    torch.manual_seed(1)
+    V, E, S, B = 1000, 64, 16, 3
+    ids = torch.randint(0, V, (B, S))
+    ids[0, 0] = V + 5  # out of range -> row 0
+    wte, wpe = rnd(V, E), rnd(S, E)
+    for p in (0.0, 0.1):
+        o = raw.embedding_fwd(ids.cuda(), wte.cuda(), wpe.cuda(), S, V, p, 77)
+        close(o, raw.embedding_fwd(ids, wte, wpe, S, V, p, 77))
+        dy = rnd(B * S, E)
+        g1, g2 = torch.zeros(V, E), torch.zeros(S, E)
+        raw.embedding_bwd(ids, dy, g1, g2, S, V, p, 77)
+        c1, c2 = torch.zeros(V, E, device="cuda"), torch.zeros(S, E, device="cuda")
+        raw.embedding_bwd(ids.cuda(), dy.cuda(), c1, c2, S, V, p, 77)
+        close(c1, g1, tol=1e-3)
+        close(c2, g2, tol=1e-3)
+
+
+@pytest.mark.parametrize("M,N", [(4096, 768), (1000, 50), (77, 3072)])
+def test_colsum(M, N):
+    dy = rnd(M, N)
+    db = torch.ones(N, device="cuda")
+    raw.colsum_accum(dy.cuda(), db)
+    close(db, dy.float().sum(0) + 1, tol=1e-3)
+
+
+@pytest.mark.parametrize("rows,C", [(513, 768), (64, 1024), (100, 1280), (33, 256), (10, 2048)])
+@pytest.mark.parametrize("fused,p", [(False, 0.0), (True, 0.0), (True, 0.1)])
+def test_layernorm(rows, C, fused, p):
+    torch.manual_seed(2)
+    x, d, g, b = rnd(rows, C), rnd(rows, C), rnd(C) + 1, rnd(C)
+    delta = d if fused else None
+    xo, h, mean, rstd = raw.layernorm_fwd(x.cuda(), None if delta is None else delta.cuda(), g.cuda(), b.cuda(), 1e-5, p, 99)
+    rxo, rh, rmean, rrstd = raw.layernorm_fwd(x, delta, g, b, 1e-5, p, 99)
+    close(xo, rxo, what="x_out")
+    close(h, rh, what="h")
+    close(mean, rmean, tol=1e-3)
+    close(rstd, rrstd, tol=1e-3)
+    dh, dres = rnd(rows, C), rnd(rows, C)
+    dg, dbt = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+    dx, dd = raw.layernorm_bwd(dh.cuda(), xo, mean, rstd, g.cuda(), dres.cuda(), fused, p, 99, dg, dbt)
+    rdg, rdb = torch.zeros(C), torch.zeros(C)
+    rdx, rdd = raw.layernorm_bwd(dh, rxo, rmean, rrstd, g, dres, fused, p, 99, rdg, rdb)
+    close(dx, rdx, what="dx")
+    if fused:
+        close(dd, rdd, what="ddelta")
+    close(dg, rdg, what="dgamma")
+    close(dbt, rdb, what="dbeta")
+
+
+@pytest.mark.parametrize("rows,V,ld", [(64, 1000, 1000), (33, 100, 104), (16, 50257, 50304), (8, 10, 10), (5, 3000, 3000)])
+def test_softmax_ce(rows, V, ld):
+    torch.manual_seed(3)
+    buf = torch.zeros(rows, ld, dtype=BF)
+    buf[:, :V] = rnd(rows, V, scale=3.0)
+    labels = torch.randint(0, V, (rows,))
+    logits = buf.cuda()[:, :V]
+    loss, corr, grad = raw.softmax_ce(logits, labels.cuda(), V, 1.0 / rows, 1.0 / rows)
+    rloss, rcorr, rgrad = raw.softmax_ce(buf[:, :V], labels, V, 1.0 / rows, 1.0 / rows)
+    close(loss, rloss, tol=1e-3)
+    assert int(corr.item()) == int(rcorr.item())
+    close(grad, rgrad, tol=2e-2)
+
+
+@pytest.mark.parametrize("B,S,H,causal", [(1, 128, 1, True), (2, 256, 3, True), (1, 384, 2, False),
+                                           (2, 200, 2, True), (1, 257, 4, False), (1, 1024, 2, True)])
+def test_attention_fwd_bwd(B, S, H, causal):
+    torch.manual_seed(4)
+    D = 64
+    qkv = rnd(B * S, 3 * H * D, scale=0.7)
+    scale = 0.125
+    out, lse = raw.attn_fwd(qkv.cuda(), B, S, H, D, causal, scale)
+    _lib.check_status()
+    rout, rlse = raw.attn_fwd(qkv, B, S, H, D, causal, scale)
+    close(out, rout, what="out")
+    close(lse, rlse, tol=1e-2, what="lse")
+    dout = rnd(B * S, H * D)
+    dqkv = raw.attn_bwd(qkv.cuda(), out, dout.cuda(), lse, B, S, H, D, causal, scale)
+    _lib.check_status()
+    rd = raw.attn_bwd(qkv, rout, dout, rlse, B, S, H, D, causal, scale)
+    E = H * D
+    for i, name in enumerate("qkv"):
+        close(dqkv[:, i * E:(i + 1) * E], rd[:, i * E:(i + 1) * E], tol=3e-2, what="d" + name)
+
+
+def test_attention_scale_one_like_reference_block():
+    torch.manual_seed(5)
+    B, S, H, D = 1, 256, 2, 64
+    qkv = rnd(B * S, 3 * H * D, scale=0.2)
+    out, _ = raw.attn_fwd(qkv.cuda(), B, S, H, D, True, 1.0)
+    _lib.check_status()
+    close(out, raw.attn_fwd(qkv, B, S, H, D, True, 1.0)[0])
+
+
+def test_optimizers():
+    torch.manual_seed(6)
+    n = 100003
+    w = torch.randn(n)
+    g = torch.randn(n)
+    for step in (1, 2):
+        pass
+    mw, m, v = w.clone().cuda(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    lp = torch.empty(n, dtype=BF, device="cuda")
+    rw, rm, rv = w.clone(), torch.zeros(n), torch.zeros(n)
+    for step in (1, 2, 3):
+        raw.adam_step(mw, lp, g.cuda(), m, v, 1e-2, 0.9, 0.99, 1e-8, 0.01, step)
+        raw.adam_step(rw, None, g, rm, rv, 1e-2, 0.9, 0.99, 1e-8, 0.01, step)
+    close(mw, rw, tol=1e-4)
+    close(lp, rw, tol=1e-2)
+    mw, vel = w.clone().cuda(), torch.zeros(n, device="cuda")
+    rw, rvel = w.clone(), torch.zeros(n)
+    for _ in range(3):
+        raw.sgd_step(mw, lp, g.cuda(), vel, 0.1, 0.9)
+        raw.sgd_step(rw, None, g, rvel, 0.1, 0.9)
+    close(mw, rw, tol=1e-4)
+    hyper = torch.tensor([0.5, 1.0, 1.0, 2.0], device="cuda")
+    mw2 = w.clone().cuda()
+    raw.sgd_step(mw2, None, g.cuda(), None, 0.0, 0.0, 1.0, hyper)
+    close(mw2, w - 0.5 * 2.0 * g, tol=1e-4)

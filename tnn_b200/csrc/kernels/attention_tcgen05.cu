@@ -1,0 +1,830 @@
+// Flash attention for sm_100a (head dim 64, bf16, causal or full), forward and
+// backward, on tcgen05 tensor cores with TMEM accumulators and TMA-fed tiles.
+//
+// Q, K, V are read straight out of the packed projection output
+// qkv[B, S, 3, H, 64] and O / dO use [B, S, H, 64], so none of the
+// [B,S,H,D] <-> [B,H,S,D] transposes of the reference block exist here
+// (src/nn/blocks_impl/flash_attention_block.cpp:109-132,193-250 launches 4 in
+// forward and 8 in backward around cuDNN's sdpa / sdpa_backward graphs,
+// src/nn/engines/cudnn_engine.cu:1479-1621).
+//
+// Forward, one CTA per (128-row Q tile, head, batch), two CTAs per SM:
+//   warp 0   TMA: Q once, then (K_j, V_j) into a two-stage ring
+//   warp 1   MMA: S = Q K_j^T -> TMEM; after the softmax warps have published
+//            P_j (bf16, 128B-swizzled shared memory) O_j = P_j V_j -> TMEM
+//   warps 2-5  one thread per Q row (TMEM lane == row): online softmax with no
+//            shuffles, running O kept in registers, O_j folded in from TMEM
+// Memory is O(S): only the log-sum-exp per row is kept for the backward.
+//
+// Backward = a row-wise preprocess (delta = sum O*dO) and two tile kernels that
+// recompute P from Q, K and the saved log-sum-exp:
+//   dK/dV  one CTA per K/V tile, loops over Q tiles, transposed products so
+//          that every shared-memory operand it writes is K-major:
+//          S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q
+//   dQ     one CTA per Q tile, loops over K/V tiles: dQ += dS K
+// K, V, Q, dO tiles double as MN-major operands (their rows become the
+// reduction index), so no transposed copy is ever made.
+// All barrier waits are bounded (status word + CTA abort flag).
+#include "gemm_tcgen05.h"
+#include "ptx.cuh"
+
+namespace tnnb {
+
+typedef __nv_bfloat16 bf16;
+
+struct AttnParams {
+  int B, S, H;
+  int causal;
+  float scale_log2;  // softmax scale * log2(e)
+  float scale;
+  bf16* O;           // [B,S,H,64]
+  float* LSE;        // [B,H,S] in scaled log2 units
+  const float* delta;  // [B,H,S]
+  bf16* dQ;          // dqkv + 0        row pitch 3*H*64
+  bf16* dK;          // dqkv + H*64
+  bf16* dV;          // dqkv + 2*H*64
+  int* status;
+};
+
+static constexpr int TILE_BYTES = 128 * 64 * 2;  // one [128 x 64] bf16 tile
+
+__device__ __forceinline__ void tmem_ld_32x32f(uint32_t taddr, float (&f)[32]) {
+  uint32_t r[32];
+  tmem_ld_32x32(taddr, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+}
+
+// Write 32 fp32 values of row `row` as bf16 into columns [c0, c0+32) of a
+// K-major 128B-swizzled [128 x 128] tile made of two [128 x 64] blocks.
+__device__ __forceinline__ void store_row_chunk_sw128(uint8_t* tile, int row, int c0, const float (&f)[32]) {
+  uint8_t* blk = tile + (c0 >> 6) * TILE_BYTES;
+  const int chunk0 = (c0 & 63) >> 3;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    __align__(16) bf16 t[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t[k] = __float2bfloat16(f[c * 8 + k]);
+    *reinterpret_cast<uint4*>(blk + sw128_offset(row, chunk0 + c)) = *reinterpret_cast<uint4*>(t);
+  }
+}
+
+// ------------------------------------------------------------------ forward
+struct FwdSmem {
+  static constexpr int Q = 0;
+  static constexpr int K0 = Q + TILE_BYTES;          // stage s: K at K0 + s*2*TILE, V right after
+  static constexpr int P = K0 + 4 * TILE_BYTES;      // [128 x 128] bf16
+  static constexpr int BARS = P + 2 * TILE_BYTES;
+  static constexpr int TOTAL = BARS + 256;
+};
+
+__global__ void __launch_bounds__(192, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_ARG);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FwdSmem::BARS);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_ready = bars + 6;
+  uint64_t* o_full = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qt * 128;
+  const int n_kv_all = (p.S + 127) / 128;
+  const int n_kv = p.causal ? min(qt + 1, n_kv_all) : n_kv_all;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_S = tmem_base;        // 128 columns
+  const uint32_t tm_O = tmem_base + 128;  // 64 columns
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, TILE_BYTES);
+      tma_load_4d(smem + FwdSmem::Q, &tmQ, q_full, 0, h, q0, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        if (!wait_or_abort(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_PRODUCER);
+          break;
+        }
+        mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+        uint8_t* kdst = smem + FwdSmem::K0 + s * 2 * TILE_BYTES;
+        tma_load_4d(kdst, &tmK, &kv_full[s], 0, h, j * 128, b);
+        tma_load_4d(kdst + TILE_BYTES, &tmV, &kv_full[s], 0, h, j * 128, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, 0, 1);
+      const uint32_t q_addr = smem_u32(smem + FwdSmem::Q);
+      const uint32_t p_addr = smem_u32(smem + FwdSmem::P);
+      bool ok = wait_or_abort(q_full, 0, abort_flag);
+      if (!ok) raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t k_addr = smem_u32(smem + FwdSmem::K0 + s * 2 * TILE_BYTES);
+        const uint32_t v_addr = k_addr + TILE_BYTES;
+        if (!wait_or_abort(&kv_full[s], (j >> 1) & 1, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+        // S_j may overwrite S_{j-1}: the softmax warps published P_{j-1}
+        // (p_ready) only after they had finished reading S_{j-1}.
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_ss(tm_S, make_smem_desc(q_addr + k * 32, 16, 1024),
+                    make_smem_desc(k_addr + k * 32, 16, 1024), idesc_s, k > 0);
+        tc_commit(s_full);
+        if (!wait_or_abort(p_ready, j & 1, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          tc_mma_ss(tm_O, make_smem_desc(p_addr + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(v_addr + k * 2048, 8192, 1024), idesc_o, k > 0);
+        tc_commit(o_full);
+        tc_commit(&kv_empty[s]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // row inside the Q tile == TMEM lane
+    const int q_idx = q0 + row;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    float o_acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o_acc[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!wait_or_abort(s_full, j & 1, abort_flag)) {
+        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int kv0 = j * 128;
+      const bool need_mask = (p.causal && j == qt) || (kv0 + 128 > p.S);
+      // pass 1: row maximum
+      float m_tile = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float f[32];
+        tmem_ld_32x32f(tm_S + lane_off + c * 32, f);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kv = kv0 + c * 32 + i;
+          const bool dead = need_mask && ((p.causal && kv > q_idx) || kv >= p.S);
+          m_tile = fmaxf(m_tile, dead ? -INFINITY : f[i] * p.scale_log2);
+        }
+      }
+      const float m_new = fmaxf(m_run, m_tile);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_use);
+      // fold in O_{j-1} (it was computed against m_run), then rescale
+      if (j > 0) {
+        if (!wait_or_abort(o_full, (j - 1) & 1, abort_flag)) {
+          if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          float f[32];
+          tmem_ld_32x32f(tm_O + lane_off + c * 32, f);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += f[i];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 64; ++i) o_acc[i] *= alpha;
+      // pass 2: P = exp2(S*scale - m), row sum, publish P
+      float l_tile = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float f[32];
+        tmem_ld_32x32f(tm_S + lane_off + c * 32, f);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kv = kv0 + c * 32 + i;
+          const bool dead = need_mask && ((p.causal && kv > q_idx) || kv >= p.S);
+          const float e = dead ? 0.f : exp2f(f[i] * p.scale_log2 - m_use);
+          // accumulate what the tensor core will actually see (bf16 P)
+          f[i] = __bfloat162float(__float2bfloat16(e));
+          l_tile += f[i];
+        }
+        store_row_chunk_sw128(smem + FwdSmem::P, row, c * 32, f);
+      }
+      l_run = l_run * alpha + l_tile;
+      m_run = m_new;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+    if (ok && n_kv > 0) {
+      if (wait_or_abort(o_full, (n_kv - 1) & 1, abort_flag)) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          float f[32];
+          tmem_ld_32x32f(tm_O + lane_off + c * 32, f);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += f[i];
+        }
+      } else {
+        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+        ok = false;
+      }
+    }
+    if (ok && q_idx < p.S) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      bf16* orow = p.O + (((long long)b * p.S + q_idx) * p.H + h) * 64;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        __align__(16) bf16 t[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t[k] = __float2bfloat16(o_acc[c * 8 + k] * inv);
+        *reinterpret_cast<uint4*>(orow + c * 8) = *reinterpret_cast<uint4*>(t);
+      }
+      if (p.LSE) p.LSE[((long long)b * p.H + h) * p.S + q_idx] = (l_run > 0.f) ? m_run + log2f(l_run) : INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// --------------------------------------------------------------- preprocess
+// delta[b,h,s] = sum_d O[b,s,h,d] * dO[b,s,h,d]; one warp per (b,s,h) row.
+__global__ void attn_delta_kernel(const bf16* __restrict__ O, const bf16* __restrict__ dO,
+                                  float* __restrict__ delta, int B, int S, int H) {
+  const long long total = (long long)B * S * H;
+  const int lane = threadIdx.x & 31;
+  for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < total;
+       r += (long long)gridDim.x * (blockDim.x >> 5)) {
+    const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(O + r * 64)[lane];
+    const __nv_bfloat162 d = reinterpret_cast<const __nv_bfloat162*>(dO + r * 64)[lane];
+    float v = __bfloat162float(a.x) * __bfloat162float(d.x) + __bfloat162float(a.y) * __bfloat162float(d.y);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) {
+      const long long hh = r % H;
+      const long long bs = r / H;
+      const long long s = bs % S, bb = bs / S;
+      delta[(bb * H + hh) * S + s] = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------ backward dK/dV
+struct BwdKvSmem {
+  static constexpr int K = 0;
+  static constexpr int V = K + TILE_BYTES;
+  static constexpr int Q0 = V + TILE_BYTES;            // stage s: Q at Q0 + s*2*TILE, dO right after
+  static constexpr int PT = Q0 + 4 * TILE_BYTES;       // P^T  [128 kv x 128 q]
+  static constexpr int DST = PT + 2 * TILE_BYTES;      // dS^T [128 kv x 128 q]
+  static constexpr int STATS = DST + 2 * TILE_BYTES;   // [2 stages][2][128] fp32: LSE, delta
+  static constexpr int BARS = STATS + 2 * 2 * 128 * 4;
+  static constexpr int TOTAL = BARS + 256;
+};
+
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                   const AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_ARG);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdKvSmem::BARS);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;   // [2]
+  uint64_t* q_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;   // S^T and dP^T ready
+  uint64_t* p_ready = bars + 6;  // P^T and dS^T published
+  uint64_t* acc_done = bars + 7; // dV/dK MMAs of the step finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  float* stats = reinterpret_cast<float*>(smem + BwdKvSmem::STATS);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int kv0 = kt * 128;
+  const int n_q_all = (p.S + 127) / 128;
+  const int qt_begin = p.causal ? kt : 0;
+  const int n_steps = n_q_all - qt_begin;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1 + 128);  // TMA tx + the 128 threads that stage LSE/delta
+      mbar_init(&q_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_ST = tmem_base, tm_DPT = tmem_base + 128, tm_dV = tmem_base + 256, tm_dK = tmem_base + 320;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+      tma_load_4d(smem + BwdKvSmem::K, &tmK, kv_full, 0, h, kv0, b);
+      tma_load_4d(smem + BwdKvSmem::V, &tmV, kv_full, 0, h, kv0, b);
+      for (int it = 0; it < n_steps; ++it) {
+        const int s = it & 1;
+        if (!wait_or_abort(&q_empty[s], ((it >> 1) & 1) ^ 1, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_PRODUCER);
+          break;
+        }
+        mbar_expect_tx(&q_full[s], 2 * TILE_BYTES);
+        uint8_t* qdst = smem + BwdKvSmem::Q0 + s * 2 * TILE_BYTES;
+        const int qrow0 = (qt_begin + it) * 128;
+        tma_load_4d(qdst, &tmQ, &q_full[s], 0, h, qrow0, b);
+        tma_load_4d(qdst + TILE_BYTES, &tmdO, &q_full[s], 0, h, qrow0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_g = make_idesc_bf16(128, 64, 0, 1);
+      const uint32_t k_addr = smem_u32(smem + BwdKvSmem::K), v_addr = smem_u32(smem + BwdKvSmem::V);
+      const uint32_t pt_addr = smem_u32(smem + BwdKvSmem::PT), dst_addr = smem_u32(smem + BwdKvSmem::DST);
+      bool ok = wait_or_abort(kv_full, 0, abort_flag);
+      if (!ok) raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+      for (int it = 0; ok && it < n_steps; ++it) {
+        const int s = it & 1;
+        const uint32_t q_addr = smem_u32(smem + BwdKvSmem::Q0 + s * 2 * TILE_BYTES);
+        const uint32_t do_addr = q_addr + TILE_BYTES;
+        if (!wait_or_abort(&q_full[s], (it >> 1) & 1, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_ss(tm_ST, make_smem_desc(k_addr + k * 32, 16, 1024),
+                    make_smem_desc(q_addr + k * 32, 16, 1024), idesc_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_ss(tm_DPT, make_smem_desc(v_addr + k * 32, 16, 1024),
+                    make_smem_desc(do_addr + k * 32, 16, 1024), idesc_s, k > 0);
+        tc_commit(s_full);
+        if (!wait_or_abort(p_ready, it & 1, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          tc_mma_ss(tm_dV, make_smem_desc(pt_addr + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(do_addr + k * 2048, 8192, 1024), idesc_g, (it > 0 || k > 0));
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          tc_mma_ss(tm_dK, make_smem_desc(dst_addr + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(q_addr + k * 2048, 8192, 1024), idesc_g, (it > 0 || k > 0));
+        tc_commit(&q_empty[s]);
+        tc_commit(acc_done);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // kv row inside the tile == TMEM lane
+    const int kv_idx = kv0 + row;
+    const int tid = threadIdx.x - 64;     // 0..127
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < n_steps; ++it) {
+      const int s = it & 1;
+      const int qrow0 = (qt_begin + it) * 128;
+      // stage LSE / delta of this Q tile (thread tid owns q row tid); the slot was last
+      // read two steps ago, and p_ready of that step has been passed by every thread.
+      {
+        const int qi = qrow0 + tid;
+        const long long off = ((long long)b * p.H + h) * p.S + qi;
+        float* st = stats + s * 256;
+        st[tid] = qi < p.S ? p.LSE[off] : INFINITY;
+        st[128 + tid] = qi < p.S ? p.delta[off] : 0.f;
+        mbar_arrive(&q_full[s]);
+      }
+      if (!wait_or_abort(&q_full[s], (it >> 1) & 1, abort_flag) || !wait_or_abort(s_full, it & 1, abort_flag)) {
+        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      // P^T/dS^T buffers are free once the previous step's dV/dK MMAs are done.
+      if (it > 0 && !wait_or_abort(acc_done, (it - 1) & 1, abort_flag)) {
+        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+        ok = false;
+        break;
+      }
+      const float* lse = stats + s * 256;
+      const float* dlt = lse + 128;
+      const bool diag = p.causal && (qt_begin + it == kt);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float st_[32], dp[32];
+        tmem_ld_32x32f(tm_ST + lane_off + c * 32, st_);
+        tmem_ld_32x32f(tm_DPT + lane_off + c * 32, dp);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int qc = c * 32 + i;
+          const int qi = qrow0 + qc;
+          const bool dead = (diag && qi < kv_idx) || kv_idx >= p.S;
+          const float pv = dead ? 0.f : exp2f(st_[i] * p.scale_log2 - lse[qc]);
+          st_[i] = pv;
+          dp[i] = pv * (dp[i] - dlt[qc]);
+        }
+        store_row_chunk_sw128(smem + BwdKvSmem::PT, row, c * 32, st_);
+        store_row_chunk_sw128(smem + BwdKvSmem::DST, row, c * 32, dp);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+    if (ok && n_steps > 0) {
+      if (wait_or_abort(acc_done, (n_steps - 1) & 1, abort_flag)) {
+        tc_fence_after();
+        // tcgen05.ld is warp-collective: every lane loads, only in-range rows store.
+        const bool live = kv_idx < p.S;
+        const long long roff = (((long long)b * p.S + (live ? kv_idx : 0)) * 3 * p.H + h) * 64;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          float f[32];
+          tmem_ld_32x32f(tm_dV + lane_off + c * 32, f);
+          if (live) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              __align__(16) bf16 t[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) t[k] = __float2bfloat16(f[g * 8 + k]);
+              *reinterpret_cast<uint4*>(p.dV + roff + c * 32 + g * 8) = *reinterpret_cast<uint4*>(t);
+            }
+          }
+          tmem_ld_32x32f(tm_dK + lane_off + c * 32, f);
+          if (live) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              __align__(16) bf16 t[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) t[k] = __float2bfloat16(f[g * 8 + k] * p.scale);
+              *reinterpret_cast<uint4*>(p.dK + roff + c * 32 + g * 8) = *reinterpret_cast<uint4*>(t);
+            }
+          }
+        }
+      } else if (lane == 0) {
+        raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+      }
+    } else if (ok && kv_idx < p.S) {
+      // no Q tile attends to this K/V tile: gradients are zero
+      const long long roff = (((long long)b * p.S + kv_idx) * 3 * p.H + h) * 64;
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int c = 0; c < 8; ++c) {
+        *reinterpret_cast<uint4*>(p.dV + roff + c * 8) = z;
+        *reinterpret_cast<uint4*>(p.dK + roff + c * 8) = z;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// --------------------------------------------------------------- backward dQ
+struct BwdQSmem {
+  static constexpr int Q = 0;
+  static constexpr int DO = Q + TILE_BYTES;
+  static constexpr int K0 = DO + TILE_BYTES;           // stage s: K at K0 + s*2*TILE, V right after
+  static constexpr int DS = K0 + 4 * TILE_BYTES;       // dS [128 q x 128 kv]
+  static constexpr int BARS = DS + 2 * TILE_BYTES;
+  static constexpr int TOTAL = BARS + 256;
+};
+
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                  const AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_ARG);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdQSmem::BARS);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_ready = bars + 6;
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qt * 128;
+  const int n_kv_all = (p.S + 127) / 128;
+  const int n_kv = p.causal ? min(qt + 1, n_kv_all) : n_kv_all;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_S = tmem_base, tm_DP = tmem_base + 128, tm_dQ = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * TILE_BYTES);
+      tma_load_4d(smem + BwdQSmem::Q, &tmQ, q_full, 0, h, q0, b);
+      tma_load_4d(smem + BwdQSmem::DO, &tmdO, q_full, 0, h, q0, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        if (!wait_or_abort(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_PRODUCER);
+          break;
+        }
+        mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+        uint8_t* kdst = smem + BwdQSmem::K0 + s * 2 * TILE_BYTES;
+        tma_load_4d(kdst, &tmK, &kv_full[s], 0, h, j * 128, b);
+        tma_load_4d(kdst + TILE_BYTES, &tmV, &kv_full[s], 0, h, j * 128, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_g = make_idesc_bf16(128, 64, 0, 1);
+      const uint32_t q_addr = smem_u32(smem + BwdQSmem::Q), do_addr = smem_u32(smem + BwdQSmem::DO);
+      const uint32_t ds_addr = smem_u32(smem + BwdQSmem::DS);
+      bool ok = wait_or_abort(q_full, 0, abort_flag);
+      if (!ok) raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t k_addr = smem_u32(smem + BwdQSmem::K0 + s * 2 * TILE_BYTES);
+        const uint32_t v_addr = k_addr + TILE_BYTES;
+        if (!wait_or_abort(&kv_full[s], (j >> 1) & 1, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_ss(tm_S, make_smem_desc(q_addr + k * 32, 16, 1024),
+                    make_smem_desc(k_addr + k * 32, 16, 1024), idesc_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_ss(tm_DP, make_smem_desc(do_addr + k * 32, 16, 1024),
+                    make_smem_desc(v_addr + k * 32, 16, 1024), idesc_s, k > 0);
+        tc_commit(s_full);
+        if (!wait_or_abort(p_ready, j & 1, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          tc_mma_ss(tm_dQ, make_smem_desc(ds_addr + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(k_addr + k * 2048, 8192, 1024), idesc_g, (j > 0 || k > 0));
+        tc_commit(&kv_empty[s]);
+        tc_commit(acc_done);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int q_idx = q0 + row;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const long long soff = ((long long)b * p.H + h) * p.S + q_idx;
+    const float lse = q_idx < p.S ? p.LSE[soff] : INFINITY;
+    const float dlt = q_idx < p.S ? p.delta[soff] : 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!wait_or_abort(s_full, j & 1, abort_flag)) {
+        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      if (j > 0 && !wait_or_abort(acc_done, (j - 1) & 1, abort_flag)) {
+        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+        ok = false;
+        break;
+      }
+      const int kv0 = j * 128;
+      const bool need_mask = (p.causal && j == qt) || (kv0 + 128 > p.S);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float sv[32], dp[32];
+        tmem_ld_32x32f(tm_S + lane_off + c * 32, sv);
+        tmem_ld_32x32f(tm_DP + lane_off + c * 32, dp);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kv = kv0 + c * 32 + i;
+          const bool dead = need_mask && ((p.causal && kv > q_idx) || kv >= p.S);
+          const float pv = dead ? 0.f : exp2f(sv[i] * p.scale_log2 - lse);
+          dp[i] = pv * (dp[i] - dlt);
+        }
+        store_row_chunk_sw128(smem + BwdQSmem::DS, row, c * 32, dp);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+    if (ok && n_kv > 0) {
+      if (wait_or_abort(acc_done, (n_kv - 1) & 1, abort_flag)) {
+        tc_fence_after();
+        const bool live = q_idx < p.S;
+        const long long roff = (((long long)b * p.S + (live ? q_idx : 0)) * 3 * p.H + h) * 64;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          float f[32];
+          tmem_ld_32x32f(tm_dQ + lane_off + c * 32, f);
+          if (live) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              __align__(16) bf16 t[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) t[k] = __float2bfloat16(f[g * 8 + k] * p.scale);
+              *reinterpret_cast<uint4*>(p.dQ + roff + c * 32 + g * 8) = *reinterpret_cast<uint4*>(t);
+            }
+          }
+        }
+      } else if (lane == 0) {
+        raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// --------------------------------------------------------------------- host
+// 4-D map over x[B, S, pitch...] selecting head h: dims {64, H, S, B}.
+static int make_head_map(CUtensorMap* m, const void* base, int B, int S, int H, long long row_pitch_elems) {
+  uint64_t dims[4] = {64, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+  uint64_t str[3] = {64 * 2, (uint64_t)row_pitch_elems * 2, (uint64_t)row_pitch_elems * 2 * (uint64_t)S};
+  uint32_t box[4] = {64, 1, 128, 1};
+  return encode_tmap_bf16(m, base, 4, dims, str, box, nullptr);
+}
+
+template <typename K>
+static int set_smem(K kern, int bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  return e == cudaSuccess ? 0 : -(int)e - 1000;
+}
+
+}  // namespace tnnb
+
+using namespace tnnb;
+
+extern "C" {
+
+// qkv: [B,S,3,H,64] bf16; out: [B,S,H,64] bf16; lse: [B,H,S] fp32 (scaled log2 units).
+int tnnb_attn_fwd(const void* qkv, void* out, void* lse, int B, int S, int H, int D, int causal, float scale,
+                  int* status, void* stream) {
+  if (D != 64) return -7;
+  if ((uintptr_t)qkv & 15 || (uintptr_t)out & 15) return -4;
+  const long long E = (long long)H * 64;
+  const bf16* base = (const bf16*)qkv;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_head_map(&tq, base, B, S, H, 3 * E))) return rc;
+  if ((rc = make_head_map(&tk, base + E, B, S, H, 3 * E))) return rc;
+  if ((rc = make_head_map(&tv, base + 2 * E, B, S, H, 3 * E))) return rc;
+  AttnParams p{};
+  p.B = B; p.S = S; p.H = H; p.causal = causal;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.O = (bf16*)out;
+  p.LSE = (float*)lse;
+  p.status = status;
+  static bool once = false;
+  if (!once) {
+    if ((rc = set_smem(attn_fwd_kernel, FwdSmem::TOTAL))) return rc;
+    once = true;
+  }
+  dim3 grid((S + 127) / 128, H, B);
+  attn_fwd_kernel<<<grid, 192, FwdSmem::TOTAL, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e - 1000;
+}
+
+// dqkv: [B,S,3,H,64] bf16 (fully overwritten); delta: [B,H,S] fp32 scratch owned by the caller.
+int tnnb_attn_bwd(const void* qkv, const void* out, const void* dout, const void* lse, void* delta, void* dqkv,
+                  int B, int S, int H, int D, int causal, float scale, int* status, void* stream) {
+  if (D != 64) return -7;
+  if (((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)dout | (uintptr_t)dqkv) & 15) return -4;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long E = (long long)H * 64;
+  const bf16* base = (const bf16*)qkv;
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = make_head_map(&tq, base, B, S, H, 3 * E))) return rc;
+  if ((rc = make_head_map(&tk, base + E, B, S, H, 3 * E))) return rc;
+  if ((rc = make_head_map(&tv, base + 2 * E, B, S, H, 3 * E))) return rc;
+  if ((rc = make_head_map(&tdo, dout, B, S, H, E))) return rc;
+  AttnParams p{};
+  p.B = B; p.S = S; p.H = H; p.causal = causal;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.LSE = (float*)lse;
+  p.delta = (const float*)delta;
+  p.dQ = (bf16*)dqkv;
+  p.dK = (bf16*)dqkv + E;
+  p.dV = (bf16*)dqkv + 2 * E;
+  p.status = status;
+  static bool once = false;
+  if (!once) {
+    if ((rc = set_smem(attn_bwd_kv_kernel, BwdKvSmem::TOTAL))) return rc;
+    if ((rc = set_smem(attn_bwd_q_kernel, BwdQSmem::TOTAL))) return rc;
+    once = true;
+  }
+  const long long rows = (long long)B * S * H;
+  int g = (int)((rows + 7) / 8 > 148 * 8 ? 148 * 8 : (rows + 7) / 8);
+  attn_delta_kernel<<<g, 256, 0, st>>>((const bf16*)out, (const bf16*)dout, (float*)delta, B, S, H);
+  dim3 grid((S + 127) / 128, H, B);
+  attn_bwd_kv_kernel<<<grid, 192, BwdKvSmem::TOTAL, st>>>(tq, tk, tv, tdo, p);
+  attn_bwd_q_kernel<<<grid, 192, BwdQSmem::TOTAL, st>>>(tq, tk, tv, tdo, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e - 1000;
+}
+
+}  // extern "C"

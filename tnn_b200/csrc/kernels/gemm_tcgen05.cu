@@ -43,33 +43,6 @@ struct GemmParams {
   int* status;
 };
 
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Wait on an mbarrier phase for at most ~2 s, giving up early when another
-// role of this CTA has already raised the abort flag.
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity,
-                                              volatile uint32_t* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  for (uint32_t i = 1;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 127u) == 0) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > 2000000000ull) return false;
-    }
-  }
-}
-
-__device__ __forceinline__ void raise_abort(const GemmParams& p, volatile uint32_t* abort_flag,
-                                            int code) {
-  *abort_flag = 1;
-  if (p.status) atomicCAS(p.status, 0, code);
-}
-
 template <int BN>
 struct GemmCfg {
   static constexpr int BM = 128;
@@ -265,7 +238,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         const int kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_or_abort(&empty[stage], phase ^ 1, abort_flag)) {
-            raise_abort(p, abort_flag, ST_TIMEOUT_PRODUCER);
+            raise_abort(p.status, abort_flag, ST_TIMEOUT_PRODUCER);
             ok = false;
             break;
           }
@@ -315,14 +288,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         const int kb0 = ks * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
         if (!wait_or_abort(&tempty[acc], acc_phase ^ 1, abort_flag)) {
-          raise_abort(p, abort_flag, ST_TIMEOUT_MMA);
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_or_abort(&full[stage], phase, abort_flag)) {
-            raise_abort(p, abort_flag, ST_TIMEOUT_MMA);
+            raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
             ok = false;
             break;
           }
@@ -359,7 +332,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const int nb = t / p.num_m_blocks;
       const int mb = t - nb * p.num_m_blocks;
       if (!wait_or_abort(&tfull[acc], acc_phase, abort_flag)) {
-        if (lane == 0) raise_abort(p, abort_flag, ST_TIMEOUT_EPILOGUE);
+        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
         break;
       }
       tc_fence_after();

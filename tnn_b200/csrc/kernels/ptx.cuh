@@ -189,6 +189,41 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, int a_mn_ma
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+
+// ------------------------------------------------------------ bounded waits
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Wait on an mbarrier phase for at most ~2 s, giving up early when another
+// role of this CTA has already raised the abort flag.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity,
+                                              volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 127u) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > 2000000000ull) return false;
+    }
+  }
+}
+
+// Record the first failure of a launch and tell the other roles of the CTA.
+__device__ __forceinline__ void raise_abort(int* status, volatile uint32_t* abort_flag, int code) {
+  *abort_flag = 1;
+  if (status) atomicCAS(status, 0, code);
+}
+
+// 16-byte chunk address inside a 128B-swizzled [rows][128 B] tile (the layout
+// TMA SWIZZLE_128B produces and the K-major UMMA descriptor expects).
+__device__ __forceinline__ uint32_t sw128_offset(int row, int chunk) {
+  return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
 // ---------------------------------------------------------------- numerics
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;

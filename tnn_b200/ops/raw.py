@@ -1,0 +1,411 @@
+"""Raw (non-autograd) operator entry points.
+
+Each function runs the sm_100a kernel when its tensors are on a CUDA device and an
+equivalent fp32 torch computation otherwise (the CPU path doubles as the numerical
+reference in the tests). Nothing here falls back to torch for CUDA tensors.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .gemm import LAUNCHES, gelu_tanh, gelu_tanh_grad
+
+ACT_KINDS = {"relu": 0, "gelu": 1, "elu": 2, "leaky_relu": 3, "sigmoid": 4, "tanh": 5, "linear": 6}
+_M64 = (1 << 64) - 1
+
+
+def _count(n=1):
+    LAUNCHES["count"] += n
+
+
+# ----------------------------------------------------------------------------- RNG
+def hash_uniform(seed: int, idx: torch.Tensor) -> torch.Tensor:
+    """Counter-based uniform in [0,1) identical to the device function of the same name."""
+    def lsr(x, k):
+        return (x >> k) & ((1 << (64 - k)) - 1)
+
+    def c(v):  # python int -> wrapped int64 constant
+        v &= _M64
+        return v - (1 << 64) if v >= (1 << 63) else v
+
+    z = idx.to(torch.int64) * c(0x9E3779B97F4A7C15) + c(seed)
+    z = (z ^ lsr(z, 30)) * c(0xBF58476D1CE4E5B9)
+    z = (z ^ lsr(z, 27)) * c(0x94D049BB133111EB)
+    z = z ^ lsr(z, 31)
+    return lsr(z, 40).to(torch.float32) * (1.0 / 16777216.0)
+
+
+def dropout_mask(shape, p: float, seed: int, device="cpu") -> torch.Tensor:
+    n = int(math.prod(shape))
+    idx = torch.arange(n, device=device, dtype=torch.int64)
+    return (hash_uniform(seed, idx) >= p).reshape(shape)
+
+
+# ---------------------------------------------------------------------- element-wise
+def act_fwd(x: torch.Tensor, kind: str, alpha: float = 0.0) -> torch.Tensor:
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        rc = _lib.load().tnnb_act_fwd(_lib.ptr(x), _lib.ptr(y), x.numel(), ACT_KINDS[kind], alpha, _lib.stream())
+        _lib.check_rc(rc, "act_fwd")
+        _count()
+        return y
+    xf = x.float()
+    if kind == "relu":
+        r = torch.relu(xf)
+    elif kind == "gelu":
+        r = gelu_tanh(xf)
+    elif kind == "elu":
+        r = torch.where(xf > 0, xf, alpha * (torch.exp(xf) - 1))
+    elif kind == "leaky_relu":
+        r = torch.where(xf > 0, xf, alpha * xf)
+    elif kind == "sigmoid":
+        r = torch.sigmoid(xf)
+    elif kind == "tanh":
+        r = torch.tanh(xf)
+    else:
+        r = xf
+    return r.to(x.dtype)
+
+
+def act_bwd(x: torch.Tensor, dy: torch.Tensor, kind: str, alpha: float = 0.0) -> torch.Tensor:
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        x, dy = x.contiguous(), dy.contiguous()
+        dx = torch.empty_like(x)
+        rc = _lib.load().tnnb_act_bwd(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dx), x.numel(), ACT_KINDS[kind], alpha,
+                                      _lib.stream())
+        _lib.check_rc(rc, "act_bwd")
+        _count()
+        return dx
+    xf = x.float()
+    if kind == "relu":
+        g = (xf > 0).float()
+    elif kind == "gelu":
+        g = gelu_tanh_grad(xf)
+    elif kind == "elu":
+        g = torch.where(xf > 0, torch.ones_like(xf), alpha * torch.exp(xf))
+    elif kind == "leaky_relu":
+        g = torch.where(xf > 0, torch.ones_like(xf), torch.full_like(xf, alpha))
+    elif kind == "sigmoid":
+        s = torch.sigmoid(xf)
+        g = s * (1 - s)
+    elif kind == "tanh":
+        g = 1 - torch.tanh(xf) ** 2
+    else:
+        g = torch.ones_like(xf)
+    return (dy.float() * g).to(x.dtype)
+
+
+_BIN = {"add": 0, "sub": 1, "mul": 2, "div": 3}
+
+
+def binary(a: torch.Tensor, b: torch.Tensor, op: str, relu: bool = False) -> torch.Tensor:
+    if a.is_cuda and a.dtype == torch.bfloat16 and a.shape == b.shape:
+        a, b = a.contiguous(), b.contiguous()
+        o = torch.empty_like(a)
+        rc = _lib.load().tnnb_binary(_lib.ptr(a), _lib.ptr(b), _lib.ptr(o), a.numel(), _BIN[op], int(relu),
+                                     _lib.stream())
+        _lib.check_rc(rc, "binary")
+        _count()
+        return o
+    af, bf = a.float(), b.float()
+    r = af + bf if op == "add" else af - bf if op == "sub" else af * bf if op == "mul" else af / bf
+    if relu:
+        r = torch.relu(r)
+    return r.to(a.dtype)
+
+
+def dropout(x: torch.Tensor, p: float, seed: int) -> torch.Tensor:
+    """``keep ? x/(1-p) : 0`` with the mask regenerated from ``seed`` (apply to dy for the backward)."""
+    if p <= 0.0:
+        return x
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        rc = _lib.load().tnnb_dropout(_lib.ptr(x), _lib.ptr(y), x.numel(), p, seed & _M64, _lib.stream())
+        _lib.check_rc(rc, "dropout")
+        _count()
+        return y
+    m = dropout_mask(x.shape, p, seed, x.device)
+    return torch.where(m, x.float() / (1 - p), torch.zeros((), device=x.device)).to(x.dtype)
+
+
+def embedding_fwd(ids: torch.Tensor, wte: torch.Tensor, wpe: Optional[torch.Tensor], seq_len: int,
+                  padding_idx: int, p: float, seed: int) -> torch.Tensor:
+    """``out[r] = dropout(wte[ids[r]] + wpe[r % seq_len])`` for flattened ids (int64)."""
+    rows, E = ids.numel(), wte.shape[1]
+    ids = ids.reshape(-1).to(torch.int64).contiguous()
+    if wte.is_cuda and wte.dtype == torch.bfloat16:
+        out = torch.empty(rows, E, dtype=wte.dtype, device=wte.device)
+        rc = _lib.load().tnnb_embedding_fwd(_lib.ptr(ids), _lib.ptr(wte), _lib.ptr(wpe), _lib.ptr(out), rows, E,
+                                            seq_len, wte.shape[0], padding_idx, p, seed & _M64, _lib.stream())
+        _lib.check_rc(rc, "embedding_fwd")
+        _count()
+        return out
+    safe = torch.where((ids < 0) | (ids >= wte.shape[0]), torch.zeros_like(ids), ids)
+    o = wte.float()[safe]
+    o = torch.where((ids == padding_idx)[:, None], torch.zeros_like(o), o)
+    if wpe is not None:
+        o = o + wpe.float()[torch.arange(rows, device=ids.device) % seq_len]
+    if p > 0:
+        o = torch.where(dropout_mask(o.shape, p, seed, o.device), o / (1 - p), torch.zeros_like(o))
+    return o.to(wte.dtype)
+
+
+def embedding_bwd(ids: torch.Tensor, dy: torch.Tensor, dwte: Optional[torch.Tensor], dwpe: Optional[torch.Tensor],
+                  seq_len: int, padding_idx: int, p: float, seed: int) -> None:
+    """Scatter-add ``dropout'(dy)`` into fp32 ``dwte`` / ``dwpe``."""
+    rows, E = dy.shape
+    ids = ids.reshape(-1).to(torch.int64).contiguous()
+    vocab = dwte.shape[0] if dwte is not None else 1 << 62
+    if dy.is_cuda and dy.dtype == torch.bfloat16:
+        dy = dy.contiguous()
+        rc = _lib.load().tnnb_embedding_bwd(_lib.ptr(ids), _lib.ptr(dy), _lib.ptr(dwte), _lib.ptr(dwpe), rows, E,
+                                            seq_len, vocab, padding_idx, p, seed & _M64, _lib.stream())
+        _lib.check_rc(rc, "embedding_bwd")
+        _count()
+        return
+    g = dy.float()
+    if p > 0:
+        g = torch.where(dropout_mask(g.shape, p, seed, g.device), g / (1 - p), torch.zeros_like(g))
+    if dwte is not None:
+        safe = torch.where((ids < 0) | (ids >= vocab), torch.zeros_like(ids), ids)
+        gg = torch.where((ids == padding_idx)[:, None], torch.zeros_like(g), g)
+        dwte.index_add_(0, safe, gg.to(dwte.dtype))
+    if dwpe is not None:
+        dwpe.index_add_(0, torch.arange(rows, device=ids.device) % seq_len, g.to(dwpe.dtype))
+
+
+def colsum_accum(dy: torch.Tensor, db: torch.Tensor) -> None:
+    """``db (fp32) += dy.sum(0)`` - the bias gradient of a dense layer."""
+    if dy.is_cuda and dy.dtype == torch.bfloat16:
+        assert db.dtype == torch.float32 and dy.stride(1) == 1
+        rc = _lib.load().tnnb_colsum_accum(_lib.ptr(dy), dy.stride(0), _lib.ptr(db), dy.shape[0], dy.shape[1],
+                                           _lib.stream())
+        _lib.check_rc(rc, "colsum_accum")
+        _count()
+        return
+    db.add_(dy.float().sum(0).to(db.dtype))
+
+
+# ------------------------------------------------------------------------- layernorm
+def layernorm_fwd(x: torch.Tensor, delta: Optional[torch.Tensor], gamma: Optional[torch.Tensor],
+                  beta: Optional[torch.Tensor], eps: float, p: float = 0.0, seed: int = 0
+                  ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``x_out = x + dropout(delta)``; ``h = LN(x_out)``. Returns (x_out, h, mean, rstd); x is 2-D [rows, C]."""
+    rows, C = x.shape
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        x = x.contiguous()
+        h = torch.empty_like(x)
+        x_out = torch.empty_like(x) if delta is not None else None
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty_like(mean)
+        if delta is not None:
+            delta = delta.contiguous()
+        rc = _lib.load().tnnb_layernorm_fwd(_lib.ptr(x), _lib.ptr(delta), _lib.ptr(x_out), _lib.ptr(h),
+                                            _lib.ptr(gamma), _lib.ptr(beta), _lib.ptr(mean), _lib.ptr(rstd), rows, C,
+                                            eps, p, seed & _M64, _lib.stream())
+        _lib.check_rc(rc, "layernorm_fwd")
+        _count()
+        return (x_out if delta is not None else x), h, mean, rstd
+    xf = x.float()
+    if delta is not None:
+        d = delta.float()
+        if p > 0:
+            d = torch.where(dropout_mask(d.shape, p, seed, d.device), d / (1 - p), torch.zeros_like(d))
+        xf = (xf + d).to(x.dtype).float()
+    mean = xf.mean(1)
+    var = xf.var(1, unbiased=False)
+    rstd = torch.rsqrt(var + eps)
+    hh = (xf - mean[:, None]) * rstd[:, None]
+    if gamma is not None:
+        hh = hh * gamma.float() + beta.float()
+    return xf.to(x.dtype), hh.to(x.dtype), mean, rstd
+
+
+def layernorm_bwd(dh: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: torch.Tensor,
+                  gamma: Optional[torch.Tensor], dres: Optional[torch.Tensor], want_ddelta: bool, p: float,
+                  seed: int, dgamma: Optional[torch.Tensor], dbeta: Optional[torch.Tensor]
+                  ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Returns (dx, ddelta); accumulates into fp32 dgamma/dbeta."""
+    rows, C = x.shape
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        dh = dh.contiguous()
+        dx = torch.empty_like(x)
+        dd = torch.empty_like(x) if want_ddelta else None
+        if dres is not None:
+            dres = dres.contiguous()
+        rc = _lib.load().tnnb_layernorm_bwd(_lib.ptr(dh), _lib.ptr(x), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma),
+                                            _lib.ptr(dres), _lib.ptr(dx), _lib.ptr(dd), _lib.ptr(dgamma),
+                                            _lib.ptr(dbeta), rows, C, p, seed & _M64, _lib.stream())
+        _lib.check_rc(rc, "layernorm_bwd")
+        _count()
+        return dx, dd
+    xh = (x.float() - mean[:, None]) * rstd[:, None]
+    g = dh.float()
+    if dgamma is not None:
+        dgamma.add_((g * xh).sum(0).to(dgamma.dtype))
+        dbeta.add_(g.sum(0).to(dbeta.dtype))
+    dy = g * gamma.float() if gamma is not None else g
+    s1 = dy.mean(1, keepdim=True)
+    s2 = (dy * xh).mean(1, keepdim=True)
+    dx = rstd[:, None] * (dy - s1 - xh * s2)
+    if dres is not None:
+        dx = dx + dres.float()
+    dx = dx.to(x.dtype)
+    dd = None
+    if want_ddelta:
+        dd = dx.float()
+        if p > 0:
+            dd = torch.where(dropout_mask(dd.shape, p, seed, dd.device), dd / (1 - p), torch.zeros_like(dd))
+        dd = dd.to(x.dtype)
+    return dx, dd
+
+
+# ------------------------------------------------------------------------------ loss
+def softmax_ce(logits: torch.Tensor, labels: torch.Tensor, vocab: int, grad_scale: Optional[float],
+               loss_scale: float, grad_out: Optional[torch.Tensor] = None
+               ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """Fused log-softmax + NLL over rows of ``logits[:, :vocab]``.
+
+    Returns (loss_sum (1,), corrects (1,) int32, grad or None). ``grad = (softmax-onehot)*grad_scale`` is
+    written to ``grad_out`` (may be ``logits`` itself) when ``grad_scale`` is not None.
+    """
+    rows = logits.shape[0]
+    labels = labels.reshape(-1).to(torch.int64)
+    if logits.is_cuda and logits.dtype == torch.bfloat16:
+        ld = logits.stride(0)
+        if ld % 8 or ld < (vocab + 7) // 8 * 8 or logits.data_ptr() % 16:
+            pad = (vocab + 7) // 8 * 8
+            buf = torch.zeros(rows, pad, dtype=logits.dtype, device=logits.device)
+            buf[:, :vocab] = logits[:, :vocab]
+            logits = buf
+            if grad_out is not None and (grad_out.stride(0) % 8 or grad_out.stride(0) < pad):
+                grad_out = None
+        grad = None
+        if grad_scale is not None:
+            if grad_out is not None:
+                grad = grad_out
+            else:
+                grad = torch.empty(rows, logits.stride(0), dtype=logits.dtype, device=logits.device)
+        loss = torch.zeros(1, dtype=torch.float32, device=logits.device)
+        corr = torch.zeros(1, dtype=torch.int32, device=logits.device)
+        rc = _lib.load().tnnb_softmax_ce(_lib.ptr(logits), logits.stride(0), _lib.ptr(labels.contiguous()),
+                                         _lib.ptr(grad), grad.stride(0) if grad is not None else 0, None,
+                                         _lib.ptr(loss), _lib.ptr(corr), rows, vocab,
+                                         grad_scale if grad_scale is not None else 0.0, loss_scale, _lib.stream())
+        _lib.check_rc(rc, "softmax_ce")
+        _count()
+        return loss, corr, (grad[:, :vocab] if grad is not None else None)
+    z = logits[:, :vocab].float()
+    lse = torch.logsumexp(z, 1)
+    loss = ((lse - z.gather(1, labels[:, None]).squeeze(1)).sum() * loss_scale).reshape(1)
+    corr = (z.argmax(1) == labels).sum().to(torch.int32).reshape(1)
+    grad = None
+    if grad_scale is not None:
+        g = torch.softmax(z, 1)
+        g[torch.arange(rows), labels] -= 1
+        grad = (g * grad_scale).to(logits.dtype)
+        if grad_out is not None:
+            grad_out[:, :vocab].copy_(grad)
+            grad = grad_out[:, :vocab]
+    return loss, corr, grad
+
+
+# ------------------------------------------------------------------------- attention
+def attn_fwd(qkv: torch.Tensor, B: int, S: int, H: int, D: int, causal: bool, scale: float
+             ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """qkv: [B*S, 3*H*D] (q | k | v, heads contiguous). Returns (out [B*S, H*D], lse [B,H,S] in log2 units)."""
+    E = H * D
+    if qkv.is_cuda and qkv.dtype == torch.bfloat16:
+        qkv = qkv.contiguous()
+        out = torch.empty(B * S, E, dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty(B, H, S, dtype=torch.float32, device=qkv.device)
+        rc = _lib.load().tnnb_attn_fwd(_lib.ptr(qkv), _lib.ptr(out), _lib.ptr(lse), B, S, H, D, int(causal), scale,
+                                       _lib.ptr(_lib.status_word(qkv.device)), _lib.stream())
+        _lib.check_rc(rc, "attn_fwd")
+        _count()
+        return out, lse
+    q, k, v = (t.reshape(B, S, H, D).permute(0, 2, 1, 3).float() for t in qkv.reshape(B * S, 3, E).unbind(1))
+    s = (q @ k.transpose(-1, -2)) * scale
+    if causal:
+        s = s.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool, device=s.device), 1), float("-inf"))
+    lse_n = torch.logsumexp(s, -1)
+    pm = torch.exp(s - lse_n[..., None])
+    o = (pm @ v).permute(0, 2, 1, 3).reshape(B * S, E)
+    return o.to(qkv.dtype), lse_n * 1.4426950408889634
+
+
+def attn_bwd(qkv: torch.Tensor, out: torch.Tensor, dout: torch.Tensor, lse: torch.Tensor, B: int, S: int, H: int,
+             D: int, causal: bool, scale: float) -> torch.Tensor:
+    """Gradient with respect to the packed qkv, same layout as the input."""
+    E = H * D
+    if qkv.is_cuda and qkv.dtype == torch.bfloat16:
+        dout = dout.contiguous()
+        dqkv = torch.empty_like(qkv)
+        delta = torch.empty(B, H, S, dtype=torch.float32, device=qkv.device)
+        rc = _lib.load().tnnb_attn_bwd(_lib.ptr(qkv), _lib.ptr(out), _lib.ptr(dout), _lib.ptr(lse), _lib.ptr(delta),
+                                       _lib.ptr(dqkv), B, S, H, D, int(causal), scale,
+                                       _lib.ptr(_lib.status_word(qkv.device)), _lib.stream())
+        _lib.check_rc(rc, "attn_bwd")
+        _count(3)
+        return dqkv
+    q, k, v = (t.reshape(B, S, H, D).permute(0, 2, 1, 3).float() for t in qkv.reshape(B * S, 3, E).unbind(1))
+    do = dout.reshape(B, S, H, D).permute(0, 2, 1, 3).float()
+    o = out.reshape(B, S, H, D).permute(0, 2, 1, 3).float()
+    s = (q @ k.transpose(-1, -2)) * scale
+    if causal:
+        s = s.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool, device=s.device), 1), float("-inf"))
+    pm = torch.exp2(s * 1.4426950408889634 - lse[..., None])
+    dv = pm.transpose(-1, -2) @ do
+    dp = do @ v.transpose(-1, -2)
+    ds = pm * (dp - (o * do).sum(-1, keepdim=True))
+    dq = ds @ k * scale
+    dk = ds.transpose(-1, -2) @ q * scale
+    pack = torch.stack([t.permute(0, 2, 1, 3).reshape(B * S, E) for t in (dq, dk, dv)], 1)
+    return pack.reshape(B * S, 3 * E).to(qkv.dtype)
+
+
+# ------------------------------------------------------------------------ optimizers
+def adam_step(master: torch.Tensor, p_lp: Optional[torch.Tensor], grad: torch.Tensor, m: torch.Tensor,
+              v: torch.Tensor, lr: float, b1: float, b2: float, eps: float, wd: float, step: int,
+              gscale: float = 1.0, hyper: Optional[torch.Tensor] = None) -> None:
+    """Flat-buffer Adam (reference semantics: p -= lr*m^/(sqrt(v^)+eps) + wd*lr*p)."""
+    bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
+    if master.is_cuda:
+        rc = _lib.load().tnnb_adam_step(_lib.ptr(master), _lib.ptr(p_lp), _lib.ptr(grad), _lib.ptr(m), _lib.ptr(v),
+                                        master.numel(), lr, b1, b2, eps, wd, bc1, bc2, gscale, _lib.ptr(hyper),
+                                        _lib.stream())
+        _lib.check_rc(rc, "adam_step")
+        _count()
+        return
+    g = grad.float() * gscale
+    m.mul_(b1).add_(g, alpha=1 - b1)
+    v.mul_(b2).addcmul_(g, g, value=1 - b2)
+    upd = lr * (m / bc1) / (torch.sqrt(v / bc2) + eps)
+    master.sub_(upd + wd * lr * master)
+    if p_lp is not None:
+        p_lp.copy_(master.to(p_lp.dtype))
+
+
+def sgd_step(master: torch.Tensor, p_lp: Optional[torch.Tensor], grad: torch.Tensor, vel: Optional[torch.Tensor],
+             lr: float, momentum: float, gscale: float = 1.0, hyper: Optional[torch.Tensor] = None) -> None:
+    """Flat-buffer SGD (reference semantics: v = mu*v - lr*g; p += v)."""
+    if master.is_cuda:
+        rc = _lib.load().tnnb_sgd_step(_lib.ptr(master), _lib.ptr(p_lp), _lib.ptr(grad), _lib.ptr(vel),
+                                       master.numel(), lr, momentum, gscale, _lib.ptr(hyper), _lib.stream())
+        _lib.check_rc(rc, "sgd_step")
+        _count()
+        return
+    g = grad.float() * gscale
+    if vel is not None:
+        vel.mul_(momentum).sub_(g, alpha=lr)
+        master.add_(vel)
+    else:
+        master.sub_(g, alpha=lr)
+    if p_lp is not None:
+        p_lp.copy_(master.to(p_lp.dtype))
