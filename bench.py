@@ -1,0 +1,234 @@
+#!/usr/bin/env python
+"""Headline benchmark: GPT-2 small pre-training throughput (tokens/s) on N B200 GPUs of one node.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+
+The step is the full training step of the flagship configuration: GPT-2 small (12 layers, d=768,
+12 heads, context 1024, vocabulary 50257, tanh-GELU, pre-LN, dropout 0.1, untied biased head),
+bf16 compute with fp32 master weights, AdamW, 8 sequences of 1024 tokens per GPU (global batch 64
+at 8 GPUs, weak scaling), synthetic uniform token ids, random-init weights. With more than one
+GPU the layout is TP=2 x DP=N/2. ``--model resnet50`` runs the ResNet-50 images/s configuration.
+
+Two numbers are reported in one JSON line: ``value`` times K steps on the device (CUDA events,
+max over ranks) with the batch already resident, ``e2e`` times the same K steps through
+``Trainer.train_step`` including the pinned host->device upload of every batch and a device->host
+read of every loss. ``--impl reference`` times the reference's own code instead (see
+baseline/README.md for what can be built offline).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="gpt2_small", choices=["gpt2_small", "gpt2_medium", "resnet50", "wrn16_8"])
+    ap.add_argument("--per-gpu-batch", type=int, default=0)
+    ap.add_argument("--parallelism", default="", help="override, e.g. dp8 or tp2dp4")
+    ap.add_argument("--no-graph", action="store_true", help="do not capture the step in a CUDA graph")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([x.strip() for x in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
+        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(s) > 2 + i and s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+BASELINE_PUBLISHED = None  # the reference publishes no throughput numbers
+
+
+def model_setup(args):
+    if args.model.startswith("gpt2"):
+        per_gpu = args.per_gpu_batch or 8
+        return {"zoo": args.model, "per_gpu_batch": per_gpu, "seq_len": 1024, "unit": "tokens/s", "metric": "tokens_per_sec",
+                "items_per_sample": 1024, "optimizer": {"type": "adamw", "learning_rate": 3e-4, "beta1": 0.9, "beta2": 0.95,
+                                                        "epsilon": 1e-8, "weight_decay": 0.1}}
+    if args.model == "resnet50":
+        per_gpu = args.per_gpu_batch or 256
+        return {"zoo": "imagenet_resnet50", "per_gpu_batch": per_gpu, "seq_len": None, "unit": "images/s",
+                "metric": "images_per_sec", "items_per_sample": 1, "optimizer": {"type": "sgd", "learning_rate": 0.1, "momentum": 0.9}}
+    per_gpu = args.per_gpu_batch or 128
+    return {"zoo": "cifar100_wrn16_8", "per_gpu_batch": per_gpu, "seq_len": None, "unit": "images/s", "metric": "images_per_sec",
+            "items_per_sample": 1, "optimizer": {"type": "sgd", "learning_rate": 0.1, "momentum": 0.9}}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from tnn_b200.data.loaders import SyntheticLoader
+    from tnn_b200.models import zoo
+    from tnn_b200.ops.gemm import LAUNCHES
+    from tnn_b200.utils.config import TrainingConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    ms = model_setup(args)
+    cfg = TrainingConfig.from_dict({"model_name": ms["zoo"], "batch_size": ms["per_gpu_batch"], "device_type": "CUDA",
+                                    "optimizer": ms["optimizer"], "scheduler": {"type": "no_op"},
+                                    "loss": {"type": "logsoftmax_crossentropy"}, "seed": 0})
+    if world > 1:
+        from tnn_b200.parallel.runtime import ParallelTrainer, default_layout
+        layout = args.parallelism or default_layout(world, ms["zoo"])
+        trainer = ParallelTrainer(cfg, layout=layout, log=False)
+    else:
+        from tnn_b200.trainer import Trainer
+        layout = "single"
+        trainer = Trainer(cfg, device=dev, log=False)
+
+    is_lm = ms["seq_len"] is not None
+    if is_lm:
+        loader = SyntheticLoader((ms["seq_len"],), 50257, trainer.local_batch if world > 1 else ms["per_gpu_batch"],
+                                 10 ** 9, tokens=True, seed=1234 + rank)
+    else:
+        shape = zoo.INPUT_SHAPES[ms["zoo"]]
+        classes = 1000 if ms["zoo"] == "imagenet_resnet50" else 100
+        loader = SyntheticLoader(shape, classes, trainer.local_batch if world > 1 else ms["per_gpu_batch"], 10 ** 9,
+                                 seed=1234 + rank)
+    batches = iter(loader)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up (also captures the CUDA graph) ----
+    data, labels = next(batches)
+    if not args.no_graph:
+        trainer.enable_cuda_graph(data, labels)
+    for _ in range(max(3, args.warmup)):
+        data, labels = next(batches)
+        loss = trainer.train_step(data, labels)
+    barrier()
+    first_loss = float(loss.item())
+
+    # ---- device-timed region: K steps, batch resident, no host sync in between ----
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    time.sleep(0.3)
+    n0 = LAUNCHES["count"]
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = trainer.step_resident()
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+    launches = (LAUNCHES["count"] - n0) if trainer.launches_per_step == 0 else trainer.launches_per_step * args.steps
+
+    # ---- end-to-end region: fresh pinned batch uploaded and loss read back every step ----
+    barrier()
+    t0 = time.perf_counter()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    last = 0.0
+    for _ in range(args.steps):
+        data, labels = next(batches)
+        loss = trainer.train_step(data, labels)
+        last = float(loss.item())
+    e3.record()
+    barrier()
+    e2e_ms = max(e2.elapsed_time(e3), (time.perf_counter() - t0) * 1e3)
+    clocks = sampler.stop() if rank == 0 else {}
+
+    if world > 1:
+        t = torch.tensor([dev_ms, e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms = float(t[0]), float(t[1])
+    from tnn_b200.ops import _lib
+    _lib.check_status(dev)
+
+    global_batch = (trainer.global_batch if world > 1 else ms["per_gpu_batch"])
+    items = global_batch * ms["items_per_sample"]
+    value = items * args.steps / (dev_ms / 1e3)
+    e2e = items * args.steps / (e2e_ms / 1e3)
+    h2d = int(data.numel() * data.element_size() + labels.numel() * labels.element_size())
+    out = {
+        "metric": ms["metric"], "value": round(value, 1), "unit": ms["unit"], "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": round(dev_ms / args.steps, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None, "dtype": "bf16",
+        "data": "synthetic (uniform random token ids / N(0,1) images, random-init weights)",
+        "config": {"model": args.model, "global_batch": global_batch, "seq_len": ms["seq_len"], "parallelism": layout,
+                   "per_gpu_batch": ms["per_gpu_batch"], "optimizer": ms["optimizer"]["type"], "cuda_graph": not args.no_graph,
+                   "l2": "working set (weights + activations, > 2 GB per step) far exceeds the 126 MB L2; no flush needed"},
+        "clocks": clocks,
+        "e2e": {"value": round(e2e, 1), "unit": ms["unit"], "ms_per_step": round(e2e_ms / args.steps, 3),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+        "gpu_launches": int(launches), "loss_first": round(first_loss, 4), "loss_last": round(last, 4), "impl": "ours",
+    }
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        from baseline.reference_arm import run_reference
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -24,7 +24,9 @@ CSRC = os.path.join(ROOT, "csrc")
 LIB = os.path.join(ROOT, "_lib")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-CXX = os.environ.get("CXX", "g++")
+# The system compiler is preferred over $CXX: toolchain wrappers found in some images
+# cannot link OpenMP.
+CXX = os.environ.get("TNNB_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
 
 CUDA_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -116,7 +116,8 @@ __global__ void binary_kernel(const bf16* __restrict__ a, const bf16* __restrict
 
 // y = keep ? x / (1-p) : 0, keep regenerated from (seed, element index).
 __global__ void dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long n, float p,
-                               unsigned long long seed) {
+                               unsigned long long seed, const unsigned long long* __restrict__ seed_off) {
+  seed = mix_seed(seed, seed_off);
   const float inv = 1.f / (1.f - p);
   long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
   const long long stride = (long long)gridDim.x * blockDim.x * 8;
@@ -136,7 +137,9 @@ __global__ void dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y,
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ wte,
                                      const bf16* __restrict__ wpe, bf16* __restrict__ out,
                                      long long rows, int E, int S, long long vocab,
-                                     long long padding_idx, float p, unsigned long long seed) {
+                                     long long padding_idx, float p, unsigned long long seed,
+                                     const unsigned long long* __restrict__ seed_off) {
+  seed = mix_seed(seed, seed_off);
   const int chunks = E / 8;
   const float inv = 1.f / (1.f - p);
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -169,7 +172,9 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const bf
 __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ dy,
                                      float* __restrict__ dwte, float* __restrict__ dwpe,
                                      long long rows, int E, int S, long long vocab,
-                                     long long padding_idx, float p, unsigned long long seed) {
+                                     long long padding_idx, float p, unsigned long long seed,
+                                     const unsigned long long* __restrict__ seed_off) {
+  seed = mix_seed(seed, seed_off);
   const int chunks = E / 8;
   const float inv = 1.f / (1.f - p);
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -272,27 +277,32 @@ int tnnb_binary(const void* a, const void* b, void* o, long long n, int op, int 
   binary_kernel<<<grid_for(n, 8, 256), 256, 0, (cudaStream_t)stream>>>((const bf16*)a, (const bf16*)b, (bf16*)o, n, op, relu);
   LAUNCH_RC();
 }
-int tnnb_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, void* stream) {
+int tnnb_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, const void* seed_off,
+                 void* stream) {
   if (((uintptr_t)x | (uintptr_t)y) & 15) return -4;
   if (p < 0.f || p >= 1.f) return -2;
-  dropout_kernel<<<grid_for(n, 8, 256), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, n, p, seed);
+  dropout_kernel<<<grid_for(n, 8, 256), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, n, p, seed,
+                                                                        (const unsigned long long*)seed_off);
   LAUNCH_RC();
 }
 int tnnb_embedding_fwd(const void* ids, const void* wte, const void* wpe, void* out, long long rows, int E,
                        int S, long long vocab, long long padding_idx, float p, unsigned long long seed,
-                       void* stream) {
+                       const void* seed_off, void* stream) {
   if (E % 8) return -3;
   int grid = (int)(rows < 148 * 8 ? rows : 148 * 8);
   embedding_fwd_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((const long long*)ids, (const bf16*)wte, (const bf16*)wpe,
-                                                              (bf16*)out, rows, E, S, vocab, padding_idx, p, seed);
+                                                              (bf16*)out, rows, E, S, vocab, padding_idx, p, seed,
+                                                              (const unsigned long long*)seed_off);
   LAUNCH_RC();
 }
 int tnnb_embedding_bwd(const void* ids, const void* dy, void* dwte, void* dwpe, long long rows, int E, int S,
-                       long long vocab, long long padding_idx, float p, unsigned long long seed, void* stream) {
+                       long long vocab, long long padding_idx, float p, unsigned long long seed, const void* seed_off,
+                       void* stream) {
   if (E % 8) return -3;
   int grid = (int)(rows < 148 * 8 ? rows : 148 * 8);
   embedding_bwd_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((const long long*)ids, (const bf16*)dy, (float*)dwte,
-                                                              (float*)dwpe, rows, E, S, vocab, padding_idx, p, seed);
+                                                              (float*)dwpe, rows, E, S, vocab, padding_idx, p, seed,
+                                                              (const unsigned long long*)seed_off);
   LAUNCH_RC();
 }
 int tnnb_colsum_accum(const void* dy, long long ld, void* db, long long M, int N, void* stream) {

@@ -32,7 +32,8 @@ __global__ void __launch_bounds__(256)
 ln_fwd_kernel(const bf16* __restrict__ x_in, const bf16* __restrict__ delta, bf16* __restrict__ x_out,
               bf16* __restrict__ h, const bf16* __restrict__ gamma, const bf16* __restrict__ beta,
               float* __restrict__ mean_o, float* __restrict__ rstd_o, long long rows, int C, float eps,
-              float p, unsigned long long seed) {
+              float p, unsigned long long seed, const unsigned long long* __restrict__ seed_off) {
+  seed = mix_seed(seed, seed_off);
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int chunks = C >> 3;
@@ -109,7 +110,9 @@ __global__ void __launch_bounds__(256)
 ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const float* __restrict__ mean_i,
               const float* __restrict__ rstd_i, const bf16* __restrict__ gamma, const bf16* __restrict__ dres,
               bf16* __restrict__ dx, bf16* __restrict__ ddelta, float* __restrict__ dgamma,
-              float* __restrict__ dbeta, long long rows, int C, float p, unsigned long long seed) {
+              float* __restrict__ dbeta, long long rows, int C, float p, unsigned long long seed,
+              const unsigned long long* __restrict__ seed_off) {
+  seed = mix_seed(seed, seed_off);
   extern __shared__ float sm[];  // [2][C]
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
@@ -224,7 +227,7 @@ extern "C" {
 // (plain layernorm of x_in); gamma/beta may be null together (no affine).
 int tnnb_layernorm_fwd(const void* x_in, const void* delta, void* x_out, void* h, const void* gamma,
                        const void* beta, void* mean, void* rstd, long long rows, int C, float eps, float p,
-                       unsigned long long seed, void* stream) {
+                       unsigned long long seed, const void* seed_off, void* stream) {
   if (C % 8 || rows <= 0) return -3;
   if ((delta == nullptr) != (x_out == nullptr)) return -5;
   const int mc = pick_maxch(C);
@@ -236,7 +239,7 @@ int tnnb_layernorm_fwd(const void* x_in, const void* delta, void* x_out, void* h
 #define LN_F(MC)                                                                                          \
   ln_fwd_kernel<MC><<<grid, block, 0, st>>>((const bf16*)x_in, (const bf16*)delta, (bf16*)x_out, (bf16*)h, \
                                             (const bf16*)gamma, (const bf16*)beta, (float*)mean,          \
-                                            (float*)rstd, rows, C, eps, p, seed)
+                                            (float*)rstd, rows, C, eps, p, seed, (const unsigned long long*)seed_off)
   if (mc == 3) LN_F(3); else if (mc == 5) LN_F(5); else LN_F(8);
 #undef LN_F
   cudaError_t e = cudaGetLastError();
@@ -246,7 +249,7 @@ int tnnb_layernorm_fwd(const void* x_in, const void* delta, void* x_out, void* h
 // dgamma/dbeta (fp32 [C]) are accumulated into; pass null to skip them.
 int tnnb_layernorm_bwd(const void* dh, const void* x, const void* mean, const void* rstd, const void* gamma,
                        const void* dres, void* dx, void* ddelta, void* dgamma, void* dbeta, long long rows,
-                       int C, float p, unsigned long long seed, void* stream) {
+                       int C, float p, unsigned long long seed, const void* seed_off, void* stream) {
   if (C % 8 || rows <= 0) return -3;
   const int mc = pick_maxch(C);
   if (!mc) return -7;
@@ -259,7 +262,7 @@ int tnnb_layernorm_bwd(const void* dh, const void* x, const void* mean, const vo
   ln_bwd_kernel<MC><<<grid, block, smem, st>>>((const bf16*)dh, (const bf16*)x, (const float*)mean,           \
                                                (const float*)rstd, (const bf16*)gamma, (const bf16*)dres,     \
                                                (bf16*)dx, (bf16*)ddelta, (float*)dgamma, (float*)dbeta, rows, \
-                                               C, p, seed)
+                                               C, p, seed, (const unsigned long long*)seed_off)
   if (mc == 3) LN_B(3); else if (mc == 5) LN_B(5); else LN_B(8);
 #undef LN_B
   cudaError_t e = cudaGetLastError();

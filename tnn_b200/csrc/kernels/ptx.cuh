@@ -249,4 +249,12 @@ __device__ __forceinline__ float hash_uniform(uint64_t seed, uint64_t idx) {
   return static_cast<float>(z >> 40) * (1.0f / 16777216.0f);
 }
 
+// Effective dropout seed: the host-side seed plus an optional step counter that
+// lives in device memory, so that a captured CUDA graph draws a fresh mask on
+// every replay (the counter is bumped once per training step).
+__device__ __forceinline__ unsigned long long mix_seed(unsigned long long seed,
+                                                       const unsigned long long* seed_off) {
+  return seed_off ? seed + (*seed_off) * 0xD1B54A32D192ED03ull : seed;
+}
+
 }  // namespace tnnb

@@ -64,17 +64,17 @@ def _declare(lib):
     sig("tnnb_act_fwd", [c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p])
     sig("tnnb_act_bwd", [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p])
     sig("tnnb_binary", [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p])
-    sig("tnnb_dropout", [c_void_p, c_void_p, c_ll, c_float, c_ull, c_void_p])
+    sig("tnnb_dropout", [c_void_p, c_void_p, c_ll, c_float, c_ull, c_void_p, c_void_p])
     sig("tnnb_embedding_fwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_ll, c_ll, c_float,
-                               c_ull, c_void_p])
+                               c_ull, c_void_p, c_void_p])
     sig("tnnb_embedding_bwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_ll, c_ll, c_float,
-                               c_ull, c_void_p])
+                               c_ull, c_void_p, c_void_p])
     sig("tnnb_colsum_accum", [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p])
     sig("tnnb_cast_f32_bf16", [c_void_p, c_void_p, c_ll, c_void_p])
     sig("tnnb_layernorm_fwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                               c_ll, c_int, c_float, c_float, c_ull, c_void_p])
+                               c_ll, c_int, c_float, c_float, c_ull, c_void_p, c_void_p])
     sig("tnnb_layernorm_bwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                               c_void_p, c_void_p, c_ll, c_int, c_float, c_ull, c_void_p])
+                               c_void_p, c_void_p, c_ll, c_int, c_float, c_ull, c_void_p, c_void_p])
     sig("tnnb_softmax_ce", [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int,
                             c_float, c_float, c_void_p])
     sig("tnnb_adam_step", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_float, c_float, c_float,

@@ -37,7 +37,7 @@ def _ld(t: torch.Tensor) -> int:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
          bias: Optional[torch.Tensor] = None, gelu: bool = False, save_preact: Optional[torch.Tensor] = None,
          dgelu_of: Optional[torch.Tensor] = None, relu: bool = False, residual: Optional[torch.Tensor] = None,
-         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, accumulate: bool = False,
          atomic: bool = False, split_k: int = 0, force_bn: int = 0) -> torch.Tensor:
     """``out = epilogue(op(a) @ op(b).T)``.
 
@@ -53,7 +53,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     if atomic:
         assert out is not None and out.dtype == torch.float32
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
     assert out.shape == (M, N)
 
     if not a.is_cuda:

@@ -39,6 +39,23 @@ def hash_uniform(seed: int, idx: torch.Tensor) -> torch.Tensor:
     return lsr(z, 40).to(torch.float32) * (1.0 / 16777216.0)
 
 
+# Optional device-resident step counter added to every dropout seed (see mix_seed in
+# csrc/kernels/ptx.cuh): set ``SEED_OFF["tensor"]`` to a 1-element int64 tensor that is
+# bumped once per training step so that a captured CUDA graph draws fresh masks per replay.
+SEED_OFF = {"tensor": None}
+
+
+def _seed_off_ptr():
+    return _lib.ptr(SEED_OFF["tensor"])
+
+
+def _eff_seed(seed: int) -> int:
+    t = SEED_OFF["tensor"]
+    if t is None:
+        return seed
+    return (seed + int(t.item()) * 0xD1B54A32D192ED03) & _M64
+
+
 def dropout_mask(shape, p: float, seed: int, device="cpu") -> torch.Tensor:
     n = int(math.prod(shape))
     idx = torch.arange(n, device=device, dtype=torch.int64)
@@ -126,11 +143,11 @@ def dropout(x: torch.Tensor, p: float, seed: int) -> torch.Tensor:
     if x.is_cuda and x.dtype == torch.bfloat16:
         x = x.contiguous()
         y = torch.empty_like(x)
-        rc = _lib.load().tnnb_dropout(_lib.ptr(x), _lib.ptr(y), x.numel(), p, seed & _M64, _lib.stream())
+        rc = _lib.load().tnnb_dropout(_lib.ptr(x), _lib.ptr(y), x.numel(), p, seed & _M64, _seed_off_ptr(), _lib.stream())
         _lib.check_rc(rc, "dropout")
         _count()
         return y
-    m = dropout_mask(x.shape, p, seed, x.device)
+    m = dropout_mask(x.shape, p, _eff_seed(seed),x.device)
     return torch.where(m, x.float() / (1 - p), torch.zeros((), device=x.device)).to(x.dtype)
 
 
@@ -142,7 +159,7 @@ def embedding_fwd(ids: torch.Tensor, wte: torch.Tensor, wpe: Optional[torch.Tens
     if wte.is_cuda and wte.dtype == torch.bfloat16:
         out = torch.empty(rows, E, dtype=wte.dtype, device=wte.device)
         rc = _lib.load().tnnb_embedding_fwd(_lib.ptr(ids), _lib.ptr(wte), _lib.ptr(wpe), _lib.ptr(out), rows, E,
-                                            seq_len, wte.shape[0], padding_idx, p, seed & _M64, _lib.stream())
+                                            seq_len, wte.shape[0], padding_idx, p, seed & _M64, _seed_off_ptr(), _lib.stream())
         _lib.check_rc(rc, "embedding_fwd")
         _count()
         return out
@@ -152,7 +169,7 @@ def embedding_fwd(ids: torch.Tensor, wte: torch.Tensor, wpe: Optional[torch.Tens
     if wpe is not None:
         o = o + wpe.float()[torch.arange(rows, device=ids.device) % seq_len]
     if p > 0:
-        o = torch.where(dropout_mask(o.shape, p, seed, o.device), o / (1 - p), torch.zeros_like(o))
+        o = torch.where(dropout_mask(o.shape, p, _eff_seed(seed),o.device), o / (1 - p), torch.zeros_like(o))
     return o.to(wte.dtype)
 
 
@@ -165,13 +182,13 @@ def embedding_bwd(ids: torch.Tensor, dy: torch.Tensor, dwte: Optional[torch.Tens
     if dy.is_cuda and dy.dtype == torch.bfloat16:
         dy = dy.contiguous()
         rc = _lib.load().tnnb_embedding_bwd(_lib.ptr(ids), _lib.ptr(dy), _lib.ptr(dwte), _lib.ptr(dwpe), rows, E,
-                                            seq_len, vocab, padding_idx, p, seed & _M64, _lib.stream())
+                                            seq_len, vocab, padding_idx, p, seed & _M64, _seed_off_ptr(), _lib.stream())
         _lib.check_rc(rc, "embedding_bwd")
         _count()
         return
     g = dy.float()
     if p > 0:
-        g = torch.where(dropout_mask(g.shape, p, seed, g.device), g / (1 - p), torch.zeros_like(g))
+        g = torch.where(dropout_mask(g.shape, p, _eff_seed(seed),g.device), g / (1 - p), torch.zeros_like(g))
     if dwte is not None:
         safe = torch.where((ids < 0) | (ids >= vocab), torch.zeros_like(ids), ids)
         gg = torch.where((ids == padding_idx)[:, None], torch.zeros_like(g), g)
@@ -208,7 +225,7 @@ def layernorm_fwd(x: torch.Tensor, delta: Optional[torch.Tensor], gamma: Optiona
             delta = delta.contiguous()
         rc = _lib.load().tnnb_layernorm_fwd(_lib.ptr(x), _lib.ptr(delta), _lib.ptr(x_out), _lib.ptr(h),
                                             _lib.ptr(gamma), _lib.ptr(beta), _lib.ptr(mean), _lib.ptr(rstd), rows, C,
-                                            eps, p, seed & _M64, _lib.stream())
+                                            eps, p, seed & _M64, _seed_off_ptr(), _lib.stream())
         _lib.check_rc(rc, "layernorm_fwd")
         _count()
         return (x_out if delta is not None else x), h, mean, rstd
@@ -216,7 +233,7 @@ def layernorm_fwd(x: torch.Tensor, delta: Optional[torch.Tensor], gamma: Optiona
     if delta is not None:
         d = delta.float()
         if p > 0:
-            d = torch.where(dropout_mask(d.shape, p, seed, d.device), d / (1 - p), torch.zeros_like(d))
+            d = torch.where(dropout_mask(d.shape, p, _eff_seed(seed),d.device), d / (1 - p), torch.zeros_like(d))
         xf = (xf + d).to(x.dtype).float()
     mean = xf.mean(1)
     var = xf.var(1, unbiased=False)
@@ -241,7 +258,7 @@ def layernorm_bwd(dh: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: t
             dres = dres.contiguous()
         rc = _lib.load().tnnb_layernorm_bwd(_lib.ptr(dh), _lib.ptr(x), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma),
                                             _lib.ptr(dres), _lib.ptr(dx), _lib.ptr(dd), _lib.ptr(dgamma),
-                                            _lib.ptr(dbeta), rows, C, p, seed & _M64, _lib.stream())
+                                            _lib.ptr(dbeta), rows, C, p, seed & _M64, _seed_off_ptr(), _lib.stream())
         _lib.check_rc(rc, "layernorm_bwd")
         _count()
         return dx, dd
@@ -261,7 +278,7 @@ def layernorm_bwd(dh: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: t
     if want_ddelta:
         dd = dx.float()
         if p > 0:
-            dd = torch.where(dropout_mask(dd.shape, p, seed, dd.device), dd / (1 - p), torch.zeros_like(dd))
+            dd = torch.where(dropout_mask(dd.shape, p, _eff_seed(seed),dd.device), dd / (1 - p), torch.zeros_like(dd))
         dd = dd.to(x.dtype)
     return dx, dd
 
@@ -409,3 +426,147 @@ def sgd_step(master: torch.Tensor, p_lp: Optional[torch.Tensor], grad: torch.Ten
         master.sub_(g, alpha=lr)
     if p_lp is not None:
         p_lp.copy_(master.to(p_lp.dtype))
+
+
+# ------------------------------------------------------------------------------ conv
+def _to_nchw(x):
+    return x.permute(0, 3, 1, 2)
+
+
+def conv2d_fwd(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], stride, pad,
+               relu: bool = False) -> torch.Tensor:
+    """NHWC x [N,H,W,C] * OHWI w [O,KH,KW,C] -> [N,OH,OW,O] (zero padding, no dilation)."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        from . import conv
+        return conv.conv2d_fwd(x, w, bias, stride, pad, relu)
+    y = torch.nn.functional.conv2d(_to_nchw(x).float(), w.permute(0, 3, 1, 2).float(),
+                                   None if bias is None else bias.float(), stride, pad)
+    if relu:
+        y = torch.relu(y)
+    return y.permute(0, 2, 3, 1).contiguous().to(x.dtype)
+
+
+def conv2d_dgrad(dy: torch.Tensor, w: torch.Tensor, x_shape, stride, pad) -> torch.Tensor:
+    if dy.is_cuda and dy.dtype == torch.bfloat16:
+        from . import conv
+        return conv.conv2d_dgrad(dy, w, x_shape, stride, pad)
+    n, h, wd, c = x_shape
+    dx = torch.nn.grad.conv2d_input((n, c, h, wd), w.permute(0, 3, 1, 2).float(), _to_nchw(dy).float(), stride, pad)
+    return dx.permute(0, 2, 3, 1).contiguous().to(dy.dtype)
+
+
+def conv2d_wgrad(x: torch.Tensor, dy: torch.Tensor, dw: torch.Tensor, stride, pad) -> None:
+    """dw (fp32, [O,KH,KW,C]) += correlation of x with dy."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        from . import conv
+        return conv.conv2d_wgrad(x, dy, dw, stride, pad)
+    o, kh, kw, c = dw.shape
+    g = torch.nn.grad.conv2d_weight(_to_nchw(x).float(), (o, c, kh, kw), _to_nchw(dy).float(), stride, pad)
+    dw.add_(g.permute(0, 2, 3, 1).to(dw.dtype))
+
+
+# ------------------------------------------------------------------------- batchnorm
+def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps: float, momentum: float, relu: bool):
+    """Training-mode batch norm over all dims but the last; updates the running stats in place.
+    Returns (y, mean, rstd) with fp32 statistics."""
+    C = x.shape[-1]
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        from . import norm
+        return norm.batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps, momentum, relu)
+    x2 = x.reshape(-1, C).float()
+    M = x2.shape[0]
+    mean = x2.mean(0)
+    var = x2.var(0, unbiased=False)
+    rstd = torch.rsqrt(var + eps)
+    y = (x2 - mean) * rstd
+    if gamma is not None:
+        y = y * gamma.float() + beta.float()
+    if relu:
+        y = torch.relu(y)
+    unb = var * (M / max(M - 1, 1))
+    run_mean.copy_(((1 - momentum) * run_mean.float() + momentum * mean).to(run_mean.dtype))
+    run_var.copy_(((1 - momentum) * run_var.float() + momentum * unb).to(run_var.dtype))
+    return y.reshape(x.shape).to(x.dtype), mean, rstd
+
+
+def batchnorm_infer(x, gamma, beta, run_mean, run_var, eps: float, relu: bool):
+    C = x.shape[-1]
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        from . import norm
+        return norm.batchnorm_infer(x, gamma, beta, run_mean, run_var, eps, relu)
+    scale = torch.rsqrt(run_var.float() + eps)
+    shift = -run_mean.float() * scale
+    if gamma is not None:
+        scale = scale * gamma.float()
+        shift = beta.float() - run_mean.float() * scale
+    y = x.reshape(-1, C).float() * scale + shift
+    if relu:
+        y = torch.relu(y)
+    return y.reshape(x.shape).to(x.dtype)
+
+
+def batchnorm_bwd(dy, x, y, mean, rstd, gamma, dgamma, dbeta, relu: bool):
+    """dx; dgamma/dbeta (fp32) accumulate. ``y`` is the saved post-ReLU output when relu is fused."""
+    C = x.shape[-1]
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        from . import norm
+        return norm.batchnorm_bwd(dy, x, y, mean, rstd, gamma, dgamma, dbeta, relu)
+    x2, g = x.reshape(-1, C).float(), dy.reshape(-1, C).float()
+    M = x2.shape[0]
+    if relu:
+        g = g * (y.reshape(-1, C) > 0)
+    xh = (x2 - mean) * rstd
+    sg, sgx = g.sum(0), (g * xh).sum(0)
+    if dgamma is not None:
+        dgamma.add_(sgx.to(dgamma.dtype))
+        dbeta.add_(sg.to(dbeta.dtype))
+    gam = gamma.float() if gamma is not None else 1.0
+    dx = gam * rstd / M * (M * g - sg - xh * sgx)
+    return dx.reshape(x.shape).to(x.dtype)
+
+
+# ------------------------------------------------------------------------------ pools
+def _pool_windows(x, pool, stride, pad, fill):
+    """[N,OH,OW,KH*KW,C] view of the windows plus a validity mask [1,OH,OW,KH*KW,1]."""
+    n, h, w, c = x.shape
+    xp = torch.nn.functional.pad(x.float(), (0, 0, pad[1], pad[1], pad[0], pad[0]), value=fill)
+    valid = torch.nn.functional.pad(torch.ones(1, h, w, 1, device=x.device), (0, 0, pad[1], pad[1], pad[0], pad[0]))
+    win = xp.unfold(1, pool[0], stride[0]).unfold(2, pool[1], stride[1])       # N,OH,OW,C,KH,KW
+    vwin = valid.unfold(1, pool[0], stride[0]).unfold(2, pool[1], stride[1])
+    oh, ow = win.shape[1], win.shape[2]
+    win = win.permute(0, 1, 2, 4, 5, 3).reshape(n, oh, ow, pool[0] * pool[1], c)
+    vwin = vwin.permute(0, 1, 2, 4, 5, 3).reshape(1, oh, ow, pool[0] * pool[1], 1)
+    return win, vwin
+
+
+def pool2d_fwd(x, mode: str, pool, stride, pad, need_index: bool = True):
+    """Returns (y, idx). For max pooling idx is the window-relative argmax (int32, kh*pool_w+kw)."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        from . import pool as pool_ops
+        return pool_ops.pool2d_fwd(x, mode, pool, stride, pad, need_index)
+    if mode == "max":
+        win, vwin = _pool_windows(x, pool, stride, pad, float("-inf"))
+        win = torch.where(vwin > 0, win, torch.full_like(win, float("-inf")))
+        y, idx = win.max(3)
+        return y.to(x.dtype), idx.to(torch.int32)
+    win, vwin = _pool_windows(x, pool, stride, pad, 0.0)
+    cnt = vwin.sum(3).clamp(min=1)
+    return (win.sum(3) / cnt).to(x.dtype), None
+
+
+def pool2d_bwd(dy, idx, x_shape, mode: str, pool, stride, pad):
+    if dy.is_cuda and dy.dtype == torch.bfloat16:
+        from . import pool as pool_ops
+        return pool_ops.pool2d_bwd(dy, idx, x_shape, mode, pool, stride, pad)
+    n, h, w, c = x_shape
+    oh, ow = dy.shape[1], dy.shape[2]
+    dxp = torch.zeros(n, h + 2 * pad[0], w + 2 * pad[1], c)
+    g = dy.float()
+    if mode == "avg":
+        _, vwin = _pool_windows(torch.zeros(1, h, w, 1), pool, stride, pad, 0.0)
+        g = g / vwin.sum(3).clamp(min=1)
+    for kh in range(pool[0]):
+        for kw in range(pool[1]):
+            sel = g if mode == "avg" else g * (idx == kh * pool[1] + kw)
+            dxp[:, kh:kh + oh * stride[0]:stride[0], kw:kw + ow * stride[1]:stride[1], :] += sel
+    return dxp[:, pad[0]:pad[0] + h, pad[1]:pad[1] + w, :].contiguous().to(dy.dtype)
