@@ -1,0 +1,165 @@
+#!/usr/bin/env python
+"""Operator micro-benchmarks (the counterpart of the reference's benchmarks/*.cpp: gemm, dense,
+attention block, batchnorm, conv2d ...). Each sub-command times one kernel with CUDA events after
+warm-up, on inputs larger than the 126 MB L2 or with an L2 flush between iterations, and prints
+achieved bandwidth / FLOP rate. Also the programs the ncu summaries under profiles/ were made with.
+
+    python benchmarks/microbench.py gemm --m 8192 --n 3072 --k 768
+    python benchmarks/microbench.py attention --batch 8 --heads 12 --seq 1024
+    python benchmarks/microbench.py layernorm --rows 65536 --cols 768
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from tnn_b200.ops import _lib, raw  # noqa: E402
+from tnn_b200.ops.gemm import gemm  # noqa: E402
+
+_FLUSH = None
+
+
+def flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _FLUSH.zero_()
+
+
+def timeit(fn, iters, warmup=3, flush=True):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters
+
+
+def bf(*shape, scale=0.5):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def cmd_gemm(a):
+    M, N, K = a.m, a.n, a.k
+    res = {}
+    x, w = bf(M, K), bf(N, K)
+    res["fwd_ms"] = timeit(lambda: gemm(x, w, force_bn=a.bn), a.iters)
+    if a.all:
+        dy = bf(M, N)
+        dw = torch.zeros(N, K, device="cuda")
+        res["dgrad_ms"] = timeit(lambda: gemm(dy, w, b_t=True), a.iters)
+        res["wgrad_ms"] = timeit(lambda: gemm(dy, x, a_t=True, b_t=True, out=dw, atomic=True), a.iters)
+        res["torch_fwd_ms"] = timeit(lambda: x @ w.t(), a.iters)
+    fl = 2.0 * M * N * K
+    for k in list(res):
+        res[k.replace("_ms", "_tflops")] = round(fl / res[k] / 1e9, 1)
+    return res
+
+
+def cmd_attention(a):
+    B, S, H, D = a.batch, a.seq, a.heads, 64
+    qkv = bf(B * S, 3 * H * D)
+    out, lse = raw.attn_fwd(qkv, B, S, H, D, True, 0.125)
+    do = bf(B * S, H * D)
+    fl = 4.0 * B * H * S * S * D / 2
+    f = timeit(lambda: raw.attn_fwd(qkv, B, S, H, D, True, 0.125), a.iters)
+    b = timeit(lambda: raw.attn_bwd(qkv, out, do, lse, B, S, H, D, True, 0.125), a.iters)
+    return {"fwd_ms": f, "fwd_tflops": round(fl / f / 1e9, 1), "bwd_ms": b, "bwd_tflops": round(2.5 * fl / b / 1e9, 1)}
+
+
+def cmd_layernorm(a):
+    R, C = a.rows, a.cols
+    x, d, g, b = bf(R, C), bf(R, C), bf(C) + 1, bf(C)
+    f = timeit(lambda: raw.layernorm_fwd(x, d, g, b, 1e-5, 0.1, 1), a.iters)
+    xo, h, mean, rstd = raw.layernorm_fwd(x, d, g, b, 1e-5, 0.1, 1)
+    dg, db = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+    bw = timeit(lambda: raw.layernorm_bwd(h, xo, mean, rstd, g, x, True, 0.1, 1, dg, db), a.iters)
+    byt = R * C * 2
+    return {"fwd_ms": f, "fwd_gbs": round(4 * byt / f / 1e6), "bwd_ms": bw, "bwd_gbs": round(5 * byt / bw / 1e6)}
+
+
+def cmd_softmax_ce(a):
+    R, V = a.rows, a.vocab
+    ld = (V + 63) // 64 * 64
+    lg = bf(R, ld, scale=2.0)
+    lab = torch.randint(0, V, (R,), device="cuda")
+    t = timeit(lambda: raw.softmax_ce(lg[:, :V], lab, V, 1.0 / R, 1.0 / R, grad_out=lg[:, :V]), a.iters)
+    return {"ms": t, "gbs": round(2 * R * ld * 2 / t / 1e6)}
+
+
+def cmd_adam(a):
+    n = a.n
+    w, g, m, v = (torch.zeros(n, device="cuda") for _ in range(4))
+    lp = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    t = timeit(lambda: raw.adam_step(w, lp, g, m, v, 1e-3, 0.9, 0.99, 1e-8, 0.0, 1), a.iters, flush=False)
+    return {"ms": t, "gbs": round(n * 30 / t / 1e6)}
+
+
+def cmd_conv2d(a):
+    x = bf(a.batch, a.size, a.size, a.cin)
+    w = bf(a.cout, a.ksize, a.ksize, a.cin, scale=0.05)
+    st, pd = (a.stride, a.stride), (a.ksize // 2, a.ksize // 2)
+    y = raw.conv2d_fwd(x, w, None, st, pd)
+    dy = torch.randn_like(y)
+    dw = torch.zeros(w.shape, device="cuda")
+    fl = 2.0 * y.numel() * a.ksize * a.ksize * a.cin
+    f = timeit(lambda: raw.conv2d_fwd(x, w, None, st, pd), a.iters)
+    d = timeit(lambda: raw.conv2d_dgrad(dy, w, x.shape, st, pd), a.iters)
+    g = timeit(lambda: raw.conv2d_wgrad(x, dy, dw, st, pd), a.iters)
+    return {"fwd_ms": f, "fwd_tflops": round(fl / f / 1e9, 1), "dgrad_ms": d, "dgrad_tflops": round(fl / d / 1e9, 1),
+            "wgrad_ms": g, "wgrad_tflops": round(fl / g / 1e9, 1)}
+
+
+def cmd_batchnorm(a):
+    x = bf(a.batch, a.size, a.size, a.channels)
+    C = a.channels
+    g, b = bf(C) + 1, bf(C)
+    rm, rv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+    f = timeit(lambda: raw.batchnorm_fwd_train(x, g, b, rm, rv, 1e-5, 0.1, True), a.iters)
+    y, mean, rstd = raw.batchnorm_fwd_train(x, g, b, rm, rv, 1e-5, 0.1, True)
+    dg, db = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+    bw = timeit(lambda: raw.batchnorm_bwd(y, x, y, mean, rstd, g, dg, db, True), a.iters)
+    byt = x.numel() * 2
+    return {"fwd_ms": f, "fwd_gbs": round(3 * byt / f / 1e6), "bwd_ms": bw, "bwd_gbs": round(5 * byt / bw / 1e6)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("gemm"); p.add_argument("--m", type=int, default=8192); p.add_argument("--n", type=int, default=3072)
+    p.add_argument("--k", type=int, default=768); p.add_argument("--bn", type=int, default=0); p.add_argument("--all", action="store_true")
+    p = sub.add_parser("attention"); p.add_argument("--batch", type=int, default=8); p.add_argument("--heads", type=int, default=12)
+    p.add_argument("--seq", type=int, default=1024)
+    p = sub.add_parser("layernorm"); p.add_argument("--rows", type=int, default=65536); p.add_argument("--cols", type=int, default=768)
+    p = sub.add_parser("softmax_ce"); p.add_argument("--rows", type=int, default=8192); p.add_argument("--vocab", type=int, default=50257)
+    p = sub.add_parser("adam"); p.add_argument("--n", type=int, default=163_000_000)
+    p = sub.add_parser("conv2d"); p.add_argument("--batch", type=int, default=128); p.add_argument("--size", type=int, default=56)
+    p.add_argument("--cin", type=int, default=64); p.add_argument("--cout", type=int, default=64); p.add_argument("--ksize", type=int, default=3)
+    p.add_argument("--stride", type=int, default=1)
+    p = sub.add_parser("batchnorm"); p.add_argument("--batch", type=int, default=128); p.add_argument("--size", type=int, default=56)
+    p.add_argument("--channels", type=int, default=256)
+    for sp in sub.choices.values():
+        sp.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    res = globals()["cmd_" + a.cmd](a)
+    _lib.check_status()
+    print(json.dumps({"bench": a.cmd, "args": {k: v for k, v in vars(a).items() if k != "cmd"},
+                      **{k: (round(v, 4) if isinstance(v, float) else v) for k, v in res.items()}}))
+
+
+if __name__ == "__main__":
+    main()

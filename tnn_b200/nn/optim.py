@@ -29,6 +29,14 @@ class Optimizer:
     def attach(self, graph) -> "Optimizer":
         self.graph = graph
         self._alloc_state(graph.master_flat)
+        # indices of non-trainable entries, found once here so that update() never synchronises
+        idx = (~graph.trainable_mask).nonzero().squeeze(1)
+        used = torch.zeros_like(graph.trainable_mask)
+        for sl in graph.layer_slices.values():
+            for (o, n, _, _) in sl:
+                used[o:o + n] = True
+        idx = (used & ~graph.trainable_mask).nonzero().squeeze(1)
+        self._frozen_idx = idx if idx.numel() else None
         return self
 
     def _alloc_state(self, like: torch.Tensor) -> None:
@@ -134,15 +142,16 @@ class Adam(Optimizer):
             self.prepare_step()
         g = self.graph
         frozen = None
-        if self.weight_decay != 0.0 and g is not None and not bool(g.trainable_mask.all()) and sl is None:
-            frozen = g.master_flat[~g.trainable_mask].clone()
+        if self.weight_decay != 0.0 and self._frozen_idx is not None and sl is None:
+            frozen = g.master_flat.index_select(0, self._frozen_idx)
         m, lp, gr = self._views(sl)
         mm, vv = (self.m, self.v) if sl is None else (self.m[sl], self.v[sl])
         raw.adam_step(m, lp, gr, mm, vv, self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, self.step_count,
                       self.grad_scale, self.hyper)
-        if frozen is not None:
-            g.master_flat[~g.trainable_mask] = frozen
-            g.sync_params_from_master()
+        if frozen is not None:  # weight decay must not touch batch-norm running statistics
+            g.master_flat.index_copy_(0, self._frozen_idx, frozen)
+            if g.master_flat is not g.params_flat:
+                g.params_flat.index_copy_(0, self._frozen_idx, frozen.to(g.params_flat.dtype))
 
     def state_dict(self):
         d = super().state_dict()
