@@ -136,12 +136,12 @@ def run_ours(args):
     is_lm = ms["seq_len"] is not None
     if is_lm:
         loader = SyntheticLoader((ms["seq_len"],), 50257, trainer.local_batch if world > 1 else ms["per_gpu_batch"],
-                                 10 ** 9, tokens=True, seed=1234 + rank)
+                                 10 ** 9, tokens=True, seed=1234 + getattr(trainer, 'data_rank', rank))
     else:
         shape = zoo.INPUT_SHAPES[ms["zoo"]]
         classes = 1000 if ms["zoo"] == "imagenet_resnet50" else 100
         loader = SyntheticLoader(shape, classes, trainer.local_batch if world > 1 else ms["per_gpu_batch"], 10 ** 9,
-                                 seed=1234 + rank)
+                                 seed=1234 + getattr(trainer, 'data_rank', rank))
     batches = iter(loader)
 
     def barrier():

@@ -1,0 +1,42 @@
+"""gloo worker for the CPU multi-process tests: data / tensor parallel steps vs one process."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from tnn_b200.models import zoo  # noqa: E402
+from tnn_b200.utils.config import TrainingConfig  # noqa: E402
+
+
+def main():
+    mode, out = sys.argv[1], sys.argv[2]
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    zoo.register_model("tiny_gpt", lambda: zoo.gpt2(128, 2, 2, "t", seq_len=128, vocab=97, drop=0.0))
+    from tnn_b200.parallel.runtime import ParallelTrainer
+    from tnn_b200.parallel.tp import copy_full_to_shards
+    cfg = TrainingConfig.from_dict({"model_name": "tiny_gpt", "batch_size": 1 if mode == "tp" else 2, "device_type": "CPU",
+                                    "seed": 5, "optimizer": {"type": "sgd", "learning_rate": 0.1, "momentum": 0.9}})
+    t = ParallelTrainer(cfg, layout="tp2" if mode == "tp" else f"dp{world}", fused=False, log=False)
+    if mode == "tp":
+        full = zoo.create("tiny_gpt").compile(seed=5)
+        copy_full_to_shards(t.graph, full, t.topo)
+    gen = torch.Generator().manual_seed(100 + t.data_rank)
+    losses = []
+    for _ in range(3):
+        seq = torch.randint(0, 97, (t.local_batch, 129), generator=gen)
+        losses.append(float(t.train_step(seq[:, :-1].contiguous(), seq[:, 1:].contiguous()).item()))
+    allm = [None] * world
+    dist.all_gather_object(allm, (losses, t.graph.master_flat.clone()))
+    if rank == 0:
+        torch.save({"losses": [a[0] for a in allm], "masters": [a[1] for a in allm],
+                    "layout": {l.name: t.graph.layer_slices[id(l)] for l in t.graph.layers()}}, out)
+    t.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,50 @@
+"""Worker launched by the multi-GPU tests through ``torch.distributed.run`` (one rank per GPU)."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from tnn_b200.models import zoo  # noqa: E402
+from tnn_b200.ops import _lib  # noqa: E402
+from tnn_b200.utils.config import TrainingConfig  # noqa: E402
+
+
+def main():
+    mode = sys.argv[1]
+    fused = sys.argv[2] == "fused"
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    zoo.register_model("tiny_gpt", lambda: zoo.gpt2(128, 2, 2, "t", seq_len=128, vocab=203, drop=0.0))
+    from tnn_b200.parallel.runtime import ParallelTrainer
+    cfg = TrainingConfig.from_dict({"model_name": "tiny_gpt", "batch_size": 2, "device_type": "CUDA", "seed": 5,
+                                    "optimizer": {"type": "adamw", "learning_rate": 1e-2, "weight_decay": 0.01}})
+    layout = {"dp": f"dp{world}", "tp": f"tp2dp{world // 2}" if world > 2 else "tp2"}[mode]
+    t = ParallelTrainer(cfg, layout=layout, fused=fused, log=False, heap_bytes=256 << 20)
+    gen = torch.Generator().manual_seed(100 + t.data_rank)
+    losses = []
+    for step in range(4):
+        seq = torch.randint(0, 203, (t.local_batch, 129), generator=gen)
+        loss = t.train_step(seq[:, :-1].contiguous(), seq[:, 1:].contiguous())
+        losses.append(float(loss.item()))
+    _lib.check_status()
+    master = t.graph.params_flat.float().clone()
+    gathered = [torch.zeros_like(master) for _ in range(world)]
+    dist.all_gather(gathered, master)
+    if rank == 0:
+        out = {"losses": losses, "param_sum": float(t.graph.params_flat.float().sum()), "n": t.graph.num_parameters()}
+        if mode == "dp":
+            out["max_rank_diff"] = max(float((g - gathered[0]).abs().max()) for g in gathered)
+        torch.save({"params": t.graph.params_flat.float().cpu(), "losses": losses}, sys.argv[3])
+        print("RESULT " + json.dumps(out), flush=True)
+    t.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

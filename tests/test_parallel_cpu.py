@@ -1,0 +1,67 @@
+"""Multi-process (gloo, CPU) checks of the parallel runtime's host logic and math: data parallel and
+tensor parallel training steps must reproduce the single-process run on the combined batch."""
+import os
+import subprocess
+import sys
+
+import torch
+
+from tnn_b200.models import zoo
+from tnn_b200.parallel.runtime import default_layout, parse_layout
+from tnn_b200.trainer import Trainer
+from tnn_b200.utils.config import TrainingConfig
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def launch(n, mode, out, port):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "_cpu_parallel_worker.py"), mode, out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    return torch.load(out, weights_only=False)
+
+
+def reference(batches):
+    zoo.register_model("tiny_gpt", lambda: zoo.gpt2(128, 2, 2, "t", seq_len=128, vocab=97, drop=0.0))
+    cfg = TrainingConfig.from_dict({"model_name": "tiny_gpt", "batch_size": 2, "device_type": "CPU", "seed": 5,
+                                    "optimizer": {"type": "sgd", "learning_rate": 0.1, "momentum": 0.9}})
+    t = Trainer(cfg, log=False)
+    losses = [float(t.train_step(s[:, :-1].contiguous(), s[:, 1:].contiguous()).item()) for s in batches]
+    g = t.graph
+    t.close()
+    return losses, g
+
+
+def test_layout_strings():
+    assert parse_layout("pp4tp2") == {"dp": 1, "tp": 2, "pp": 4}
+    assert default_layout(8, "gpt2_small") == "tp2dp4" and default_layout(2, "gpt2_small") == "tp2"
+    assert default_layout(4, "imagenet_resnet50") == "dp4"
+
+
+def test_dp2_equals_single_process(tmp_path):
+    res = launch(2, "dp", str(tmp_path / "dp.pt"), 29621)
+    gens = [torch.Generator().manual_seed(100 + r) for r in range(2)]
+    batches = [torch.cat([torch.randint(0, 97, (2, 129), generator=g) for g in gens]) for _ in range(3)]
+    ref_losses, g = reference(batches)
+    assert torch.allclose(res["masters"][0], res["masters"][1])
+    assert torch.allclose(res["masters"][0], g.master_flat, atol=2e-4), float((res["masters"][0] - g.master_flat).abs().max())
+    mean_loss = [(a + b) / 2 for a, b in zip(*res["losses"])]
+    assert all(abs(a - b) < 1e-3 for a, b in zip(mean_loss, ref_losses))
+
+
+def test_tp2_equals_single_process(tmp_path):
+    res = launch(2, "tp", str(tmp_path / "tp.pt"), 29622)
+    gen = torch.Generator().manual_seed(100)
+    batches = [torch.randint(0, 97, (2, 129), generator=gen) for _ in range(3)]
+    ref_losses, g = reference(batches)
+    mean_loss = [(a + b) / 2 for a, b in zip(*res["losses"])]
+    assert all(abs(a - b) < 2e-3 for a, b in zip(mean_loss, ref_losses)), (mean_loss, ref_losses)
+    # a replicated parameter (final layernorm gamma) and a sharded one (fc1 weight rows) after 3 steps
+    full = {l.name: l for l in g.layers()}
+    lay = res["layout"]
+    o, n, shape, _ = lay["ln_f"][0]
+    assert torch.allclose(res["masters"][0][o:o + n], full["ln_f"].params[0].reshape(-1), atol=2e-3)
+    o, n, shape, _ = lay["t_block_0_mlp_fc1"][0]
+    got = torch.cat([m[o:o + n].view(shape) for m in res["masters"]], 0)
+    assert torch.allclose(got, full["t_block_0_mlp_fc1"].params[0], atol=2e-3), float((got - full["t_block_0_mlp_fc1"].params[0]).abs().max())

@@ -1,0 +1,61 @@
+"""Multi-GPU tests (need >= 2 GPUs): fused NVLink kernels vs the NCCL baseline vs one process."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from tnn_b200.models import zoo
+from tnn_b200.trainer import Trainer
+from tnn_b200.utils.config import TrainingConfig
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def launch(n, mode, kind, out):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29611", os.path.join(HERE, "_parallel_worker.py"), mode, kind, out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    return json.loads(line[7:])
+
+
+def single_process_reference(global_batch_sets, tmp):
+    zoo.register_model("tiny_gpt", lambda: zoo.gpt2(128, 2, 2, "t", seq_len=128, vocab=203, drop=0.0))
+    cfg = TrainingConfig.from_dict({"model_name": "tiny_gpt", "batch_size": 4, "device_type": "CUDA", "seed": 5,
+                                    "optimizer": {"type": "adamw", "learning_rate": 1e-2, "weight_decay": 0.01}})
+    t = Trainer(cfg, log=False)
+    losses = []
+    for seq in global_batch_sets:
+        losses.append(float(t.train_step(seq[:, :-1].contiguous(), seq[:, 1:].contiguous()).item()))
+    p = t.graph.params_flat.float().cpu()
+    t.close()
+    return losses, p
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("kind", ["fused", "nccl"])
+def test_dp2_matches_single_process(kind, tmp_path):
+    out = str(tmp_path / "dp.pt")
+    res = launch(2, "dp", kind, out)
+    assert res["max_rank_diff"] == 0.0
+    gens = [torch.Generator().manual_seed(100 + r) for r in range(2)]
+    sets = [torch.cat([torch.randint(0, 203, (2, 129), generator=g) for g in gens]) for _ in range(4)]
+    ref_losses, ref_params = single_process_reference(sets, tmp_path)
+    got = torch.load(out)
+    # rank 0 reports the loss of its half of the batch; parameters must agree with the full-batch run
+    rel = (got["params"] - ref_params).norm() / ref_params.norm()
+    assert rel < 2e-2, float(rel)
+    assert abs(res["losses"][-1] - ref_losses[-1]) < 0.3
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("kind", ["fused", "nccl"])
+def test_tp2_trains(kind, tmp_path):
+    res = launch(2, "tp", kind, str(tmp_path / "tp.pt"))
+    assert res["losses"][-1] < res["losses"][0]

@@ -93,7 +93,8 @@ struct CommGemmParams {
   int M, N, K;
   int num_m_blocks, num_n_blocks, num_k_blocks;
   int tp, rank, rows_per_rank, blocks_per_rank;
-  uint32_t epoch;
+  uint32_t epoch;             // call counter: host value ...
+  const uint32_t* epoch_ptr;  // ... plus an optional device-resident counter (CUDA-graph replays)
   int* status;
   const bf16* bias;
   PeerFlags peers;
@@ -111,6 +112,9 @@ struct CommGemmParams {
   uint32_t* tile_flag_remote[MAX_PEERS];
   const uint32_t* tile_flag_local[MAX_PEERS];
   long long ldi;
+  // --- extra epilogue of the all-gather GEMM: 1 = GELU (pre-activation saved to aux), 2 = times GELU'(aux) ---
+  int epi;
+  bf16* aux;  // [M, N], row pitch ldd
 };
 
 template <int BN>
@@ -148,6 +152,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t EPOCH = p.epoch + (p.epoch_ptr ? *p.epoch_ptr : 0u);
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -180,7 +185,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         decode_tile<MODE>(p, t, mb, nb);
         if (MODE == MODE_AG && mb / p.blocks_per_rank != p.rank) {
           // rows of a peer: wait until a copy warp (of any CTA) has landed them locally
-          if (!spin_until<false>(p.chunk_flags + mb, p.epoch)) {
+          if (!spin_until<false>(p.chunk_flags + mb, EPOCH)) {
             raise_abort(p.status, abort_flag, ST_TIMEOUT_PEER);
             break;
           }
@@ -269,9 +274,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int ltile = (mb - owner * p.blocks_per_rank) * p.num_n_blocks + nb;
       bool peers_ok = true;
       if (MODE == MODE_RS && owner == p.rank) {
-        // all sources must have delivered this tile (4 epilogue warps each add 1 per call)
+        // every source must have delivered this warp's row quarter of the tile for this call
         for (int s = 0; s < p.tp; ++s)
-          if (s != p.rank) peers_ok = spin_until<true>(p.tile_flag_local[s] + ltile, 4u * p.epoch) && peers_ok;
+          if (s != p.rank) peers_ok = spin_until<true>(p.tile_flag_local[s] + ltile * 4 + q, EPOCH) && peers_ok;
         peers_ok = __all_sync(0xffffffffu, peers_ok);
         if (!peers_ok && lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_PEER);
       }
@@ -320,6 +325,18 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               if (fullc || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
           }
           const long long orow = (MODE == MODE_RS) ? lrow : row;
+          if (MODE == MODE_AG && p.epi) {
+            bf16* ax = p.aux + orow * p.ldd + col0;
+            for (int j = 0; j < 32; ++j) {
+              if (!(fullc || col0 + j < p.N)) continue;
+              if (p.epi == 1) {
+                ax[j] = __float2bfloat16(v[j]);
+                v[j] = gelu_tanh(__bfloat162float(ax[j]));
+              } else {
+                v[j] *= gelu_tanh_grad(__bfloat162float(ax[j]));
+              }
+            }
+          }
           dst = p.D + orow * p.ldd + col0;
           ld = p.ldd;
         }
@@ -337,10 +354,11 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       if (MODE == MODE_RS && owner != p.rank) {
-        // make this warp's partial-sum stores visible at the owner, then count the warp in
+        // make this warp's 32 rows of partial sums visible at the owner, then publish the call
+        // number in the flag of (tile, row quarter): the owner's warp q needs exactly these rows
         __threadfence_system();
         __syncwarp();
-        if (lane == 0) red_release_sys_add(p.tile_flag_remote[owner] + ltile, 1u);
+        if (lane == 0) st_release_sys(p.tile_flag_remote[owner] + ltile * 4 + q, EPOCH);
       }
       tc_fence_before();
       mbar_arrive(&tempty[acc]);
@@ -352,13 +370,13 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int cw = threadIdx.x - 192;  // 0..63
     if (blockIdx.x == 0 && warp == 6) {
       // every rank's own rows are written once all ranks have reached this kernel
-      const bool ok = peer_barrier_warp(p.peers, p.epoch, lane);
+      const bool ok = peer_barrier_warp(p.peers, EPOCH, lane);
       if (lane == 0) {
         if (!ok && p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
-        st_release_gpu(p.go_flag, p.epoch);  // released even on a timeout so that nothing waits twice
+        st_release_gpu(p.go_flag, EPOCH);  // released even on a timeout so that nothing waits twice
       }
     }
-    if (cw == 0 && !spin_until<false>(p.go_flag, p.epoch) && p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
+    if (cw == 0 && !spin_until<false>(p.go_flag, EPOCH) && p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
     asm volatile("bar.sync 1, 64;" ::: "memory");  // the two copy warps only
     const int remote_blocks = p.num_m_blocks - p.blocks_per_rank;
     const int chunks_per_row = p.K / 8;
@@ -392,7 +410,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __threadfence();
       fence_proxy_async_all();
       asm volatile("bar.sync 1, 64;" ::: "memory");
-      if (cw == 0) st_release_gpu(p.chunk_flags + mb, p.epoch);
+      if (cw == 0) st_release_gpu(p.chunk_flags + mb, EPOCH);
     }
   }
 
@@ -418,7 +436,8 @@ struct DpParams {
   int opt;                        // 0 AdamW, 1 SGD(momentum)
   float lr, b1, b2, eps, wd, bc1, bc2, gscale, momentum;
   const float* hyper;             // optional device {lr, bc1, bc2, gscale}
-  uint32_t epoch;
+  uint32_t epoch;             // call counter: host value ...
+  const uint32_t* epoch_ptr;  // ... plus an optional device-resident counter (CUDA-graph replays)
   uint32_t* go_flag;              // local
   uint32_t* done_count;           // local
   int* status;
@@ -428,15 +447,16 @@ __global__ void __launch_bounds__(512)
 dp_step_kernel(const DpParams p) {
   __shared__ int s_ok;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t EPOCH = p.epoch + (p.epoch_ptr ? *p.epoch_ptr : 0u);
   // ---- barrier 1: every peer has finished writing its gradients ----
   if (blockIdx.x == 0 && warp == 0) {
-    const bool ok = peer_barrier_warp(p.peers, 2 * p.epoch - 1, lane);
+    const bool ok = peer_barrier_warp(p.peers, 2 * EPOCH - 1, lane);
     if (lane == 0) {
       if (!ok && p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
-      st_release_gpu(p.go_flag, p.epoch);
+      st_release_gpu(p.go_flag, EPOCH);
     }
   }
-  if (threadIdx.x == 0) s_ok = spin_until<false>(p.go_flag, p.epoch) ? 1 : 0;
+  if (threadIdx.x == 0) s_ok = spin_until<false>(p.go_flag, EPOCH) ? 1 : 0;
   __syncthreads();
   if (!s_ok) {
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
@@ -496,11 +516,11 @@ dp_step_kernel(const DpParams p) {
   __syncthreads();
   if (threadIdx.x == 0) {
     const uint32_t prev = atomicAdd(p.done_count, 1u);
-    s_ok = (prev + 1 == gridDim.x * p.epoch) ? 1 : 0;  // counter is cumulative over calls
+    s_ok = (prev + 1 == gridDim.x * EPOCH) ? 1 : 0;  // counter is cumulative over calls
   }
   __syncthreads();
   if (s_ok && warp == 0) {
-    const bool ok = peer_barrier_warp(p.peers, 2 * p.epoch, lane);
+    const bool ok = peer_barrier_warp(p.peers, 2 * EPOCH, lane);
     if (!ok && lane == 0 && p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
   }
 }
@@ -565,9 +585,10 @@ int tnnb_ipc_close(void* p) {
 // where they are not needed. mode: 1 = all-gather->GEMM, 2 = GEMM->reduce-scatter.
 int tnnb_gemm_comm(int mode, int M, int N, int K, int b_mn, const void* A, long long lda, const void* B,
                    long long ldb, void* D, long long ldd, const void* bias, int tp, int rank, int rows_per_rank,
-                   unsigned int epoch, void** barrier_flags, void** ag_src, void* chunk_flags, void* go_flag,
+                   unsigned int epoch, const void* epoch_ptr, void** barrier_flags, void** ag_src, void* chunk_flags,
+                   void* go_flag,
                    void** inbox_remote, void** inbox_local, void** tile_flag_remote, void** tile_flag_local,
-                   long long ldi, int* status, void* stream) {
+                   long long ldi, int epi, void* aux, int* status, void* stream) {
   if (tp < 1 || tp > MAX_PEERS || rank < 0 || rank >= tp) return -2;
   if (rows_per_rank % 128 || rows_per_rank * tp != M) return -8;
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -3;
@@ -578,7 +599,7 @@ int tnnb_gemm_comm(int mode, int M, int N, int K, int b_mn, const void* A, long 
   const int bn = (N > 128) ? 256 : 128;
   p.num_n_blocks = (N + bn - 1) / bn;
   p.tp = tp; p.rank = rank; p.rows_per_rank = rows_per_rank; p.blocks_per_rank = rows_per_rank / 128;
-  p.epoch = epoch; p.status = status; p.bias = (const bf16*)bias;
+  p.epoch = epoch; p.epoch_ptr = (const uint32_t*)epoch_ptr; p.status = status; p.bias = (const bf16*)bias;
   p.peers.rank = rank; p.peers.world = tp;
   for (int r = 0; r < tp; ++r) {
     p.peers.flags[r] = barrier_flags ? (uint32_t*)barrier_flags[r] : nullptr;
@@ -591,6 +612,8 @@ int tnnb_gemm_comm(int mode, int M, int N, int K, int b_mn, const void* A, long 
   p.ag_dst = (bf16*)A; p.lda = lda;
   p.chunk_flags = (uint32_t*)chunk_flags; p.go_flag = (uint32_t*)go_flag;
   p.D = (bf16*)D; p.ldd = ldd; p.ldi = ldi;
+  p.epi = epi; p.aux = (bf16*)aux;
+  if (epi && !aux) return -5;
   if (mode == MODE_AG && (K % 8)) return -3;
 
   CUtensorMap ta, tb;
@@ -630,7 +653,7 @@ int tnnb_gemm_comm(int mode, int M, int N, int K, int b_mn, const void* A, long 
 int tnnb_dp_step(int dp, int dp_rank, void** barrier_flags, void** grads, void** params_lp, void** params_f32,
                  void* master, void* m, void* v, long long lo, long long hi, int opt, float lr, float b1, float b2,
                  float eps, float wd, float bc1, float bc2, float gscale, float momentum, const void* hyper,
-                 unsigned int epoch, void* go_flag, void* done_count, int* status, void* stream) {
+                 unsigned int epoch, const void* epoch_ptr, void* go_flag, void* done_count, int* status, void* stream) {
   if (dp < 1 || dp > MAX_PEERS || dp_rank < 0 || dp_rank >= dp) return -2;
   if ((lo % 8) || (hi % 8) || hi < lo) return -3;
   DpParams p{};
@@ -645,7 +668,7 @@ int tnnb_dp_step(int dp, int dp_rank, void** barrier_flags, void** grads, void**
   p.master = (float*)master; p.m = (float*)m; p.v = (float*)v;
   p.lo = lo; p.hi = hi; p.opt = opt;
   p.lr = lr; p.b1 = b1; p.b2 = b2; p.eps = eps; p.wd = wd; p.bc1 = bc1; p.bc2 = bc2; p.gscale = gscale; p.momentum = momentum;
-  p.hyper = (const float*)hyper; p.epoch = epoch;
+  p.hyper = (const float*)hyper; p.epoch = epoch; p.epoch_ptr = (const uint32_t*)epoch_ptr;
   p.go_flag = (uint32_t*)go_flag; p.done_count = (uint32_t*)done_count; p.status = status;
   const int grid = sm_count();  // one resident CTA per SM: block 0 must be able to run for the others to proceed
   dp_step_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(p);

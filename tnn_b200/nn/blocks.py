@@ -172,11 +172,15 @@ class FlashAttentionBlock(Layer):
     def param_specs(self):
         E = self.embed_dim
         std = 1.0 / math.sqrt(E)
-        return [ParamSpec("qkv_weight", (3 * E, E), True, ("normal", std)), ParamSpec("qkv_bias", (3 * E,), True, ("normal", std)),
-                ParamSpec("out_weight", (E, E), True, ("normal", std)), ParamSpec("out_bias", (E,), True, ("normal", std))]
+        tp = getattr(self, "tp", 1)  # tensor parallelism: heads are split, q|k|v each [E/tp, E], out [E, E/tp]
+        sh = tp > 1
+        return [ParamSpec("qkv_weight", (3 * E // tp, E), True, ("normal", std), sharded=sh),
+                ParamSpec("qkv_bias", (3 * E // tp,), True, ("normal", std), sharded=sh),
+                ParamSpec("out_weight", (E, E // tp), True, ("normal", std), sharded=sh),
+                ParamSpec("out_bias", (E,), True, ("normal", std))]
 
     def param_descriptors(self):
-        E = self.embed_dim
+        E = self.embed_dim // getattr(self, "tp", 1)
         w, b, wo, bo = self.params
         return [w[0:E], b[0:E], w[E:2 * E], b[E:2 * E], w[2 * E:3 * E], b[2 * E:3 * E], wo, bo]
 

@@ -193,7 +193,7 @@ class Graph:
 
     # -------------------------------------------------------------------- compiling
     def compile(self, device="cpu", param_dtype: Optional[torch.dtype] = None, io_dtype: Optional[torch.dtype] = None,
-                seed: Optional[int] = 0, init: bool = True, fuse: bool = True):
+                seed: Optional[int] = 0, init: bool = True, fuse: bool = True, alloc=None):
         """Sort, allocate the flat parameter / gradient buffers, bind and initialise every layer."""
         self.device = torch.device(device)
         on_gpu = self.device.type == "cuda"
@@ -209,19 +209,34 @@ class Graph:
         elem = torch.tensor([], dtype=self.param_dtype).element_size()
         align = max(1, ALIGN_BYTES // min(elem, 4))  # in elements; same element offsets in all three buffers
         off = 0
-        self.layer_slices = {}
-        for l in layers:
-            sl = []
-            for spec in l.param_specs():
-                n = 1
-                for d in spec.shape:
-                    n *= d
-                sl.append((off, n, spec.shape, spec.trainable))
-                off = (off + n + align - 1) // align * align
-            self.layer_slices[id(l)] = sl
+        self.layer_slices = {id(l): [None] * len(l.param_specs()) for l in layers}
+        self.shard_boundary = None
+        # Two passes: parameters replicated on every tensor-parallel rank first, then the ones a
+        # tensor-parallel layer marks as sharded, so that each kind forms one contiguous range.
+        for want_sharded in (False, True):
+            if want_sharded:
+                off = (off + 1023) // 1024 * 1024
+                self.shard_boundary = off
+            for l in layers:
+                for k, spec in enumerate(l.param_specs()):
+                    if bool(getattr(spec, "sharded", False)) != want_sharded:
+                        continue
+                    n = 1
+                    for d in spec.shape:
+                        n *= d
+                    self.layer_slices[id(l)][k] = (off, n, spec.shape, spec.trainable)
+                    off = (off + n + align - 1) // align * align
         total = max(off, align)
-        self.params_flat = torch.zeros(total, dtype=self.param_dtype, device=self.device)
-        self.grads_flat = torch.zeros(total, dtype=torch.float32, device=self.device)
+        # ``alloc(numel, dtype)`` lets the parameter and gradient slabs live in a symmetric heap so that
+        # peer GPUs can read gradients and write parameters directly (tnn_b200.parallel).
+        total = (total + 1023) // 1024 * 1024
+        self.total_elems = total
+        if alloc is not None:
+            self.params_flat = alloc(total, self.param_dtype).zero_()
+            self.grads_flat = alloc(total, torch.float32).zero_()
+        else:
+            self.params_flat = torch.zeros(total, dtype=self.param_dtype, device=self.device)
+            self.grads_flat = torch.zeros(total, dtype=torch.float32, device=self.device)
         self.master_flat = self.params_flat if self.param_dtype == torch.float32 else torch.zeros(
             total, dtype=torch.float32, device=self.device)
         self.trainable_mask = torch.zeros(total, dtype=torch.bool, device=self.device)

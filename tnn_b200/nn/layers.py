@@ -43,10 +43,12 @@ def f32(x: float) -> float:
 
 
 class ParamSpec:
-    __slots__ = ("name", "shape", "trainable", "init")
+    __slots__ = ("name", "shape", "trainable", "init", "sharded")
 
-    def __init__(self, name: str, shape: Sequence[int], trainable: bool = True, init: Tuple[str, float] = ("zeros", 0.0)):
+    def __init__(self, name: str, shape: Sequence[int], trainable: bool = True, init: Tuple[str, float] = ("zeros", 0.0),
+                 sharded: bool = False):
         self.name, self.shape, self.trainable, self.init = name, tuple(int(s) for s in shape), trainable, init
+        self.sharded = sharded  # True: this rank holds one tensor-parallel shard of the full parameter
 
 
 class Layer:
@@ -133,9 +135,14 @@ class Dense(Layer):
 
     def param_specs(self):
         std = 1.0 / math.sqrt(self.input_features)
-        specs = [ParamSpec("weight", (self.output_features, self.input_features), True, ("normal", std))]
+        # tensor parallelism (set by tnn_b200.parallel.tp): "col" splits the output features (weight
+        # rows and bias), "row" splits the input features (weight columns; the bias stays replicated)
+        tp, mode = getattr(self, "tp", 1), getattr(self, "tp_mode", None)
+        out_f = self.output_features // tp if mode == "col" else self.output_features
+        in_f = self.input_features // tp if mode == "row" else self.input_features
+        specs = [ParamSpec("weight", (out_f, in_f), True, ("normal", std), sharded=mode is not None)]
         if self.use_bias:
-            specs.append(ParamSpec("bias", (self.output_features,), True, ("normal", std)))
+            specs.append(ParamSpec("bias", (out_f,), True, ("normal", std), sharded=mode == "col"))
         return specs
 
     def output_shape(self, in_shapes):

@@ -211,13 +211,15 @@ def colsum_accum(dy: torch.Tensor, db: torch.Tensor) -> None:
 
 # ------------------------------------------------------------------------- layernorm
 def layernorm_fwd(x: torch.Tensor, delta: Optional[torch.Tensor], gamma: Optional[torch.Tensor],
-                  beta: Optional[torch.Tensor], eps: float, p: float = 0.0, seed: int = 0
+                  beta: Optional[torch.Tensor], eps: float, p: float = 0.0, seed: int = 0,
+                  h_out: Optional[torch.Tensor] = None
                   ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-    """``x_out = x + dropout(delta)``; ``h = LN(x_out)``. Returns (x_out, h, mean, rstd); x is 2-D [rows, C]."""
+    """``x_out = x + dropout(delta)``; ``h = LN(x_out)``. Returns (x_out, h, mean, rstd); x is 2-D [rows, C].
+    ``h_out`` (contiguous, same shape) receives ``h`` in place, e.g. rows of a symmetric gather buffer."""
     rows, C = x.shape
     if x.is_cuda and x.dtype == torch.bfloat16:
         x = x.contiguous()
-        h = torch.empty_like(x)
+        h = h_out if h_out is not None else torch.empty_like(x)
         x_out = torch.empty_like(x) if delta is not None else None
         mean = torch.empty(rows, dtype=torch.float32, device=x.device)
         rstd = torch.empty_like(mean)
@@ -246,14 +248,15 @@ def layernorm_fwd(x: torch.Tensor, delta: Optional[torch.Tensor], gamma: Optiona
 
 def layernorm_bwd(dh: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: torch.Tensor,
                   gamma: Optional[torch.Tensor], dres: Optional[torch.Tensor], want_ddelta: bool, p: float,
-                  seed: int, dgamma: Optional[torch.Tensor], dbeta: Optional[torch.Tensor]
+                  seed: int, dgamma: Optional[torch.Tensor], dbeta: Optional[torch.Tensor],
+                  ddelta_out: Optional[torch.Tensor] = None
                   ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-    """Returns (dx, ddelta); accumulates into fp32 dgamma/dbeta."""
+    """Returns (dx, ddelta); accumulates into fp32 dgamma/dbeta. ``ddelta_out`` receives ddelta in place."""
     rows, C = x.shape
     if x.is_cuda and x.dtype == torch.bfloat16:
         dh = dh.contiguous()
         dx = torch.empty_like(x)
-        dd = torch.empty_like(x) if want_ddelta else None
+        dd = (ddelta_out if ddelta_out is not None else torch.empty_like(x)) if want_ddelta else None
         if dres is not None:
             dres = dres.contiguous()
         rc = _lib.load().tnnb_layernorm_bwd(_lib.ptr(dh), _lib.ptr(x), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma),

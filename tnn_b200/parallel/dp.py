@@ -1,0 +1,171 @@
+"""Data-parallel optimizer step.
+
+``FusedDPOptimizer`` runs the hand-written kernel ``tnnb_dp_step`` (csrc/kernels/comm_fused.cu):
+gradient reduce-scatter over NVLink peer loads, 1/N scale, AdamW / SGD-momentum on the rank's
+fp32 master slice (optimizer state is sharded, ZeRO-1 style) and parameter all-gather by peer
+stores, all in one launch per region. ``NcclDPOptimizer`` does the same with
+``reduce_scatter_tensor`` / ``all_gather_into_tensor`` around the local update kernel - the
+"only calls NCCL" baseline - and also serves gloo/CPU tests with an all-reduce.
+
+A *region* is a range of the flat buffers together with the ranks that hold a replica of it: with
+tensor parallelism the replicated parameters (embeddings, layernorms, head) are reduced over
+every rank of the job and the sharded ones only over the data-parallel group. The reference has
+no data parallelism to compare with (include/distributed/coordinator.hpp:618-620 is a stub).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..nn.optim import SGD, Adam, Optimizer
+from ..ops import _lib
+from ..ops.gemm import LAUNCHES
+from .symm import SymmetricHeap, ptr_array
+
+
+@dataclass
+class Region:
+    lo: int
+    hi: int
+    ranks: List[int]          # global ranks that replicate this range (this rank included)
+    group: Optional[object] = None  # matching torch.distributed group (NCCL baseline)
+
+
+def _declare(lib):
+    vp, ll, f, i, u = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_float, ctypes.c_int, ctypes.c_uint
+    lib.tnnb_dp_step.argtypes = [i, i, vp, vp, vp, vp, vp, vp, vp, ll, ll, i, f, f, f, f, f, f, f, f, f, vp, u, vp, vp, vp, vp, vp]
+    lib.tnnb_dp_step.restype = i
+
+
+class FusedDPOptimizer:
+    """Drives ``tnnb_dp_step`` for every region of a graph whose flat buffers live in ``heap``."""
+
+    def __init__(self, opt: Optimizer, graph, heap: SymmetricHeap, regions: Sequence[Region], grad_scale: float):
+        self.opt, self.graph, self.heap, self.regions = opt, graph, heap, list(regions)
+        self.lib = _lib.load()
+        _declare(self.lib)
+        opt.graph = graph
+        opt.grad_scale = grad_scale
+        self.me = dist.get_rank() if dist.is_initialized() else 0
+        dev = graph.master_flat.device
+        self.is_adam = isinstance(opt, Adam)
+        # number of updates so far, kept on the device so that a captured CUDA graph advances it on replay
+        self.tick = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.sites = []
+        for reg in self.regions:
+            n = len(reg.ranks)
+            idx = reg.ranks.index(self.me)
+            span = reg.hi - reg.lo
+            per = (span // n) // 8 * 8
+            lo = reg.lo + idx * per
+            hi = reg.hi if idx == n - 1 else lo + per
+            flags = heap.alloc((16,), torch.int32).zero_()
+            site = {
+                "n": n, "idx": idx, "lo": lo, "hi": hi, "epoch": 0,
+                "flags": ptr_array(heap.peer_ptrs(flags, reg.ranks)),
+                "grads": ptr_array(heap.peer_ptrs(graph.grads_flat, reg.ranks)),
+                "lp": ptr_array(heap.peer_ptrs(graph.params_flat, reg.ranks)) if graph.master_flat is not graph.params_flat else None,
+                "f32": ptr_array(heap.peer_ptrs(graph.params_flat, reg.ranks)) if graph.master_flat is graph.params_flat else None,
+                "m": torch.zeros(max(hi - lo, 8), dtype=torch.float32, device=dev),
+                "v": torch.zeros(max(hi - lo, 8), dtype=torch.float32, device=dev) if self.is_adam else None,
+                "go": torch.zeros(1, dtype=torch.int32, device=dev), "done": torch.zeros(1, dtype=torch.int32, device=dev),
+            }
+            self.sites.append(site)
+        # a parameter written by a peer lands in params_flat; when params are fp32 the master *is* params_flat
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier()
+
+    # Optimizer-compatible surface used by the trainer
+    def get_learning_rate(self):
+        return self.opt.get_learning_rate()
+
+    def set_learning_rate(self, lr):
+        self.opt.set_learning_rate(lr)
+
+    def enable_device_hyper(self):
+        self.opt.enable_device_hyper()
+
+    def prepare_step(self):
+        self.opt.prepare_step()
+
+    @property
+    def hyper(self):
+        return self.opt.hyper
+
+    @property
+    def step_count(self):
+        return self.opt.step_count
+
+    @step_count.setter
+    def step_count(self, v):
+        self.opt.step_count = v
+
+    def update(self, prepared: bool = False):
+        o = self.opt
+        if not prepared:
+            o.prepare_step()
+        g = self.graph
+        st = _lib.stream()
+        status = _lib.ptr(_lib.status_word(g.master_flat.device))
+        if self.is_adam:
+            bc1, bc2 = 1 - o.beta1 ** o.step_count, 1 - o.beta2 ** o.step_count
+            args = (0, o.lr, o.beta1, o.beta2, o.eps, o.weight_decay, bc1, bc2, o.grad_scale, 0.0)
+        else:
+            args = (1, o.lr, 0.0, 0.0, 0.0, 0.0, 1.0, 1.0, o.grad_scale, o.momentum)
+        self.tick.add_(1)
+        for s in self.sites:
+            rc = self.lib.tnnb_dp_step(
+                s["n"], s["idx"], s["flags"], s["grads"], s["lp"], s["f32"], _lib.ptr(g.master_flat), _lib.ptr(s["m"]),
+                _lib.ptr(s["v"]), s["lo"], s["hi"], args[0], args[1], args[2], args[3], args[4], args[5], args[6], args[7],
+                args[8], args[9], _lib.ptr(o.hyper), 0, _lib.ptr(self.tick), _lib.ptr(s["go"]), _lib.ptr(s["done"]), status, st)
+            _lib.check_rc(rc, "tnnb_dp_step")
+            LAUNCHES["count"] += 1
+
+    def state_dict(self):
+        d = self.opt.state_dict()
+        for k, s in enumerate(self.sites):
+            d[f"m{k}"] = s["m"]
+            if s["v"] is not None:
+                d[f"v{k}"] = s["v"]
+        return d
+
+    def load_state_dict(self, d):
+        self.opt.step_count = int(d["step"])
+        self.opt.lr = float(d["lr"])
+        for k, s in enumerate(self.sites):
+            s["m"].copy_(d[f"m{k}"])
+            if s["v"] is not None:
+                s["v"].copy_(d[f"v{k}"])
+
+
+class NcclDPOptimizer:
+    """Library-collective version: all-reduce (gloo/CPU) or reduce-scatter + all-gather (NCCL) around
+    the local update kernels. Used as the baseline of the fused path and on CPU."""
+
+    def __init__(self, opt: Optimizer, graph, regions: Sequence[Region], grad_scale: float):
+        self.opt, self.graph, self.regions = opt, graph, list(regions)
+        opt.attach(graph)
+        opt.grad_scale = grad_scale
+
+    def __getattr__(self, name):
+        return getattr(self.__dict__["opt"], name)
+
+    @property
+    def step_count(self):
+        return self.opt.step_count
+
+    @step_count.setter
+    def step_count(self, v):
+        self.opt.step_count = v
+
+    def update(self, prepared: bool = False):
+        g = self.graph
+        for reg in self.regions:
+            if len(reg.ranks) > 1:
+                dist.all_reduce(g.grads_flat[reg.lo:reg.hi], group=reg.group)
+        self.opt.update(prepared=prepared)

@@ -1,0 +1,167 @@
+"""Tensor-parallel execution of a run of transformer blocks (see :mod:`tnn_b200.parallel.tp`).
+
+Rows of the residual stream are split over the tensor-parallel ranks (sequence parallelism): the
+layernorm / residual / dropout kernels work on ``M/tp`` rows, the attention and MLP GEMMs on all
+``M`` rows but ``1/tp`` of the heads / hidden width. Per block and direction there are two
+all-gather->GEMM and two GEMM->reduce-scatter launches; no stand-alone collective is issued.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..nn.graph import Graph, _EmbedSegment, _GPTChain, _Segment, _accum, _flat2d
+from ..ops import raw
+from ..ops.gemm import gemm
+from .tp import CommContext, GatherSite, ScatterSite, _reinit_shards
+
+
+class _TPGPTChain(_Segment):
+    def __init__(self, chain: _GPTChain, cc: CommContext):
+        self.start, self.end = chain.start, chain.end
+        self.blocks, self.final = chain.blocks, chain.final
+        self.in_node, self.out_node = chain.in_node, chain.out_node
+        self.cc = cc
+        self.sites = None
+
+    def _make_sites(self, M: int, E: int):
+        cc = self.cc
+        sites = []
+        for es in self.blocks:
+            fc1 = es[5].layer
+            F = fc1.output_features // cc.tp
+            sites.append({
+                "g1": GatherSite(cc, M, E), "g2": GatherSite(cc, M, E),          # forward: LN1 / LN2 outputs
+                "gb1": GatherSite(cc, M, E), "gb2": GatherSite(cc, M, E),        # backward: dY of out-proj / fc2
+                "s_out": ScatterSite(cc, M, E), "s_fc2": ScatterSite(cc, M, E),  # forward reduce-scatters
+                "s_qkv": ScatterSite(cc, M, E), "s_fc1": ScatterSite(cc, M, E),  # backward reduce-scatters
+                "F": F,
+            })
+        self.sites, self.M = sites, M
+
+    def _ln_into(self, site: GatherSite, x, pending, ln, p, seed):
+        tgt = site.mine()
+        xo, h, mean, rstd = raw.layernorm_fwd(x, pending, ln.params[0], ln.params[1], ln.epsilon, p, seed, h_out=tgt)
+        if h.data_ptr() != tgt.data_ptr():
+            tgt.copy_(h)
+        return xo, mean, rstd
+
+    def forward(self, vals, ctx):
+        cc = self.cc
+        x3 = vals[id(self.in_node)]
+        B, S, E = x3.shape
+        M = B * S
+        if M % (128 * cc.tp):
+            raise ValueError(f"tensor parallelism needs batch*seq ({M}) to be a multiple of {128 * cc.tp}")
+        if self.sites is None or self.M != M:
+            self._make_sites(M, E)
+        Ms = M // cc.tp
+        cc.tick.add_(1)  # new call number for every fused GEMM of this pass
+        x = _flat2d(x3)[cc.idx * Ms:(cc.idx + 1) * Ms].contiguous()
+        pending, p_pend, seed_pend = None, 0.0, 0
+        saved = []
+        for es, st in zip(self.blocks, self.sites):
+            ln1, attn, drop1, _, ln2, fc1, _, fc2, drop2, _ = (e.layer for e in es)
+            s = {}
+            x, s["mean1"], s["rstd1"] = self._ln_into(st["g1"], x, pending, ln1, p_pend, seed_pend)
+            s["x"], s["p_in"], s["seed_in"], s["had_pending"] = x, p_pend, seed_pend, pending is not None
+            wqkv, bqkv, wo, bo = attn.params
+            qkv = st["g1"].gemm(wqkv, bias=bqkv)                                  # [M, 3E/tp]
+            heads = attn.num_heads // cc.tp
+            a, lse = raw.attn_fwd(qkv, B, S, heads, attn.head_dim, attn.is_causal, attn.attn_scale)
+            y1 = st["s_out"].gemm(a, wo, bias=bo)                                 # [Ms, E]
+            p1 = drop1.dropout_rate if drop1.training else 0.0
+            seed1 = drop1.step_seed(ctx)
+            x1, s["mean2"], s["rstd2"] = self._ln_into(st["g2"], x, y1, ln2, p1, seed1)
+            z = torch.empty(M, st["F"], dtype=x.dtype, device=x.device)
+            gact = st["g2"].gemm(fc1.params[0], bias=fc1.params[1], gelu_preact=z)  # [M, 4E/tp]
+            y2 = st["s_fc2"].gemm(gact, fc2.params[0], bias=fc2.params[1])        # [Ms, E]
+            s.update(qkv=qkv, a=a, lse=lse, x1=x1, z=z, g=gact, p1=p1, seed1=seed1, heads=heads)
+            saved.append(s)
+            x, pending = x1, y2
+            p_pend = drop2.dropout_rate if drop2.training else 0.0
+            seed_pend = drop2.step_seed(ctx)
+        ctx["saved"], ctx["dims"], ctx["tail"] = saved, (B, S, E), (p_pend, seed_pend)
+        if self.final is not None:
+            ln = self.final.layer
+            xf, hf, mean, rstd = raw.layernorm_fwd(x, pending, ln.params[0], ln.params[1], ln.epsilon, p_pend, seed_pend)
+            ctx["final"] = (xf, mean, rstd)
+            out = hf
+        else:
+            out = raw.binary(x, raw.dropout(pending, p_pend, seed_pend), "add")
+        # downstream layers (the vocabulary head) see only this rank's rows
+        vals[id(self.out_node)] = out.reshape(1, Ms, E)
+
+    def backward(self, gvals, ctx, no_grad_nodes):
+        g = gvals.pop(id(self.out_node), None)
+        if g is None:
+            return
+        cc = self.cc
+        B, S, E = ctx["dims"]
+        M = B * S
+        Ms = M // cc.tp
+        g = _flat2d(g).contiguous()
+        cc.tick.add_(1)
+        p_pend, seed_pend = ctx["tail"]
+        last = self.sites[-1]
+        if self.final is not None:
+            ln = self.final.layer
+            xf, mean, rstd = ctx["final"]
+            dres, dpend = raw.layernorm_bwd(g, xf, mean, rstd, ln.params[0], None, True, p_pend, seed_pend, ln.grads[0],
+                                            ln.grads[1], ddelta_out=last["gb2"].mine() if g.is_cuda else None)
+        else:
+            dres, dpend = g, raw.dropout(g, p_pend, seed_pend)
+        for bi in reversed(range(len(self.blocks))):
+            es, s, st = self.blocks[bi], ctx["saved"][bi], self.sites[bi]
+            ln1, attn, _, _, ln2, fc1, _, fc2, _, _ = (e.layer for e in es)
+            wqkv, bqkv, wo, bo = attn.params
+            # ---- fc2 (row parallel): gather dY, dgrad with GELU' ----
+            tgt = st["gb2"].mine()
+            if dpend.data_ptr() != tgt.data_ptr():
+                tgt.copy_(dpend)
+            raw.colsum_accum(tgt, fc2.grads[1])
+            dz = st["gb2"].gemm(fc2.params[0], b_t=True, dgelu_of=s["z"])          # [M, 4E/tp]
+            gemm(st["gb2"].buf, s["g"], a_t=True, b_t=True, out=fc2.grads[0], atomic=True)
+            # ---- fc1 (column parallel) ----
+            gemm(dz, st["g2"].buf, a_t=True, b_t=True, out=fc1.grads[0], atomic=True)
+            raw.colsum_accum(dz, fc1.grads[1])
+            dh2 = st["s_fc1"].gemm(dz, fc1.params[0], b_t=True)                    # [Ms, E]
+            # ---- LN2 + residual + dropout ----
+            dx1, dy1 = raw.layernorm_bwd(dh2, s["x1"], s["mean2"], s["rstd2"], ln2.params[0], dres, True, s["p1"], s["seed1"],
+                                         ln2.grads[0], ln2.grads[1], ddelta_out=st["gb1"].mine() if dh2.is_cuda else None)
+            tgt = st["gb1"].mine()
+            if dy1.data_ptr() != tgt.data_ptr():
+                tgt.copy_(dy1)
+            # ---- attention output projection (row parallel) ----
+            raw.colsum_accum(tgt, attn.grads[3])
+            da = st["gb1"].gemm(wo, b_t=True)                                      # [M, E/tp]
+            gemm(st["gb1"].buf, s["a"], a_t=True, b_t=True, out=attn.grads[2], atomic=True)
+            dqkv = raw.attn_bwd(s["qkv"], s["a"], da, s["lse"], B, S, s["heads"], attn.head_dim, attn.is_causal, attn.attn_scale)
+            # ---- QKV projection (column parallel) ----
+            gemm(dqkv, st["g1"].buf, a_t=True, b_t=True, out=attn.grads[0], atomic=True)
+            raw.colsum_accum(dqkv, attn.grads[1])
+            dh1 = st["s_qkv"].gemm(dqkv, wqkv, b_t=True)                           # [Ms, E]
+            # ---- LN1 (+ the previous block's trailing residual add + dropout) ----
+            prev_tgt = self.sites[bi - 1]["gb2"].mine() if (bi > 0 and dh1.is_cuda) else None
+            dres, dpend = raw.layernorm_bwd(dh1, s["x"], s["mean1"], s["rstd1"], ln1.params[0], dx1, s["had_pending"],
+                                            s["p_in"], s["seed_in"], ln1.grads[0], ln1.grads[1], ddelta_out=prev_tgt)
+        if id(self.in_node) not in no_grad_nodes:
+            full = torch.zeros(M, E, dtype=dres.dtype, device=dres.device)
+            full[cc.idx * Ms:(cc.idx + 1) * Ms] = dres
+            _accum(gvals, self.in_node, full.reshape(B, S, E))
+
+
+def install_tp_segments(graph: Graph, topo, heap, fused: bool = True) -> None:
+    """Swap every fused GPT chain of a compiled graph for its tensor-parallel version and give the
+    shards of each tensor-parallel rank their own random initialisation."""
+    cc = CommContext(topo, heap, fused, graph.device)
+    n = 0
+    for k, seg in enumerate(graph.segments):
+        if isinstance(seg, _GPTChain):
+            graph.segments[k] = _TPGPTChain(seg, cc)
+            n += 1
+    if n == 0:
+        raise ValueError("no transformer block chain found for tensor parallelism")
+    _reinit_shards(graph, topo)
+    graph.tp_context = cc
