@@ -1,0 +1,105 @@
+"""Convolution / batch-norm / pooling kernels and a CNN training step against the fp32 CPU path."""
+import pytest
+import torch
+
+from tnn_b200.models import zoo
+from tnn_b200.nn.loss import CrossEntropyLoss
+from tnn_b200.ops import _lib, raw
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def rnd(*shape, scale=1.0):
+    return (torch.randn(*shape) * scale).to(BF)
+
+
+def close(got, ref, tol=2e-2, what=""):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    err = (got - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < tol, f"{what} rel err {err / scale:.4g}"
+
+
+@pytest.mark.parametrize("n,h,c,o,k,s,p", [(2, 16, 64, 64, 3, 1, 1), (2, 15, 32, 48, 3, 2, 1), (3, 14, 64, 128, 1, 1, 0),
+                                           (2, 14, 64, 128, 1, 2, 0), (2, 20, 3, 16, 7, 2, 3), (1, 9, 8, 24, 5, 1, 0),
+                                           (2, 8, 16, 16, 3, 1, 1)])
+def test_conv2d(n, h, c, o, k, s, p):
+    torch.manual_seed(0)
+    x, w, b = rnd(n, h, h, c), rnd(o, k, k, c, scale=0.2), rnd(o)
+    y = raw.conv2d_fwd(x.cuda(), w.cuda(), b.cuda(), (s, s), (p, p))
+    ry = raw.conv2d_fwd(x, w, b, (s, s), (p, p))
+    close(y, ry, what="fwd")
+    dy = rnd(*ry.shape)
+    close(raw.conv2d_dgrad(dy.cuda(), w.cuda(), x.shape, (s, s), (p, p)), raw.conv2d_dgrad(dy, w, x.shape, (s, s), (p, p)),
+          what="dgrad")
+    dw, rdw = torch.ones(w.shape, device="cuda"), torch.ones(w.shape)
+    raw.conv2d_wgrad(x.cuda(), dy.cuda(), dw, (s, s), (p, p))
+    raw.conv2d_wgrad(x, dy, rdw, (s, s), (p, p))
+    close(dw, rdw, what="wgrad")
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("shape", [(4, 8, 8, 64), (2, 7, 7, 256), (3, 5, 5, 8), (64, 512)])
+@pytest.mark.parametrize("relu,affine", [(True, True), (False, True), (False, False)])
+def test_batchnorm(shape, relu, affine):
+    torch.manual_seed(1)
+    C = shape[-1]
+    x = rnd(*shape) + 0.5
+    g, b = (rnd(C) + 1, rnd(C)) if affine else (None, None)
+    rm, rv = torch.zeros(C), torch.ones(C)
+    crm, crv = rm.cuda(), rv.cuda()
+    y, mean, rstd = raw.batchnorm_fwd_train(x.cuda(), None if g is None else g.cuda(), None if b is None else b.cuda(), crm, crv,
+                                            1e-5, 0.1, relu)
+    ry, rmean, rrstd = raw.batchnorm_fwd_train(x, g, b, rm, rv, 1e-5, 0.1, relu)
+    close(y, ry, what="y")
+    close(mean, rmean, tol=1e-3)
+    close(rstd, rrstd, tol=1e-2)
+    close(crm, rm, tol=1e-3)
+    close(crv, rv, tol=1e-2)
+    dy = rnd(*shape)
+    dg, db = (torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")) if affine else (None, None)
+    rdg, rdb = (torch.zeros(C), torch.zeros(C)) if affine else (None, None)
+    dx = raw.batchnorm_bwd(dy.cuda(), x.cuda(), y, mean, rstd, None if g is None else g.cuda(), dg, db, relu)
+    rdx = raw.batchnorm_bwd(dy, x, ry, rmean, rrstd, g, rdg, rdb, relu)
+    close(dx, rdx, tol=4e-2, what="dx")
+    if affine:
+        close(dg, rdg, tol=3e-2)
+        close(db, rdb, tol=3e-2)
+    yi = raw.batchnorm_infer(x.cuda(), None if g is None else g.cuda(), None if b is None else b.cuda(), crm, crv, 1e-5, relu)
+    close(yi, raw.batchnorm_infer(x, g, b, rm, rv, 1e-5, relu), what="infer")
+
+
+@pytest.mark.parametrize("mode", ["max", "avg"])
+@pytest.mark.parametrize("h,k,s,p", [(8, 2, 2, 0), (9, 3, 2, 1), (7, 7, 1, 0), (6, 3, 3, 0)])
+def test_pool(mode, h, k, s, p):
+    torch.manual_seed(2)
+    x = rnd(2, h, h, 16)
+    y, idx = raw.pool2d_fwd(x.cuda(), mode, (k, k), (s, s), (p, p))
+    ry, ridx = raw.pool2d_fwd(x, mode, (k, k), (s, s), (p, p))
+    close(y, ry, tol=1e-2)
+    dy = rnd(*ry.shape)
+    dx = raw.pool2d_bwd(dy.cuda(), idx, x.shape, mode, (k, k), (s, s), (p, p))
+    rdx = raw.pool2d_bwd(dy, ridx, x.shape, mode, (k, k), (s, s), (p, p))
+    close(dx, rdx, tol=2e-2)
+
+
+def test_resnet9_step_matches_cpu():
+    torch.manual_seed(3)
+    x = torch.randn(4, 32, 32, 3)
+    labels = torch.randint(0, 10, (4,))
+    gc = zoo.create("cifar10_resnet9").compile(device="cpu", seed=9)
+    gg = zoo.create("cifar10_resnet9").compile(device="cuda", seed=9)
+    gc.params_flat.copy_(gg.params_flat.float().cpu())
+    oc = gc.forward({"input": x})["output"]
+    og = gg.forward({"input": x.cuda()})["output"]
+    _lib.check_status()
+    assert (og.float().cpu() - oc).abs().max() < 0.2 * oc.abs().max() + 0.05
+    lc, gradc = CrossEntropyLoss().compute(oc, labels)
+    lg, gradg = CrossEntropyLoss().compute(og, labels.cuda())
+    gc.backward({"output": gradc})
+    gg.backward({"output": gradg})
+    _lib.check_status()
+    a, b = gc.grads_flat, gg.grads_flat.cpu()
+    cos = torch.nn.functional.cosine_similarity(a, b, dim=0)
+    assert cos > 0.97, float(cos)

@@ -1,0 +1,226 @@
+// Batch normalisation over [M, C] (M = N*H*W, channels last), bf16 I/O, fp32 statistics.
+//
+//   training forward   two passes: per-channel sum / sum of squares (block partials in fp32,
+//                      combined with double atomics) then normalise + affine (+ReLU); the
+//                      second kernel also updates the running statistics (unbiased variance)
+//                      and stores mean / inv_std for the backward
+//   backward           two passes: sum(dy), sum(dy * xhat) with the ReLU mask taken from the
+//                      saved output, then dx = gamma*inv_std/M * (M*dy - sum(dy) - xhat*sum(dy*xhat))
+//   inference          one pass with the running statistics
+//
+// Semantics follow src/nn/engines/cpu_engine.cpp:378-511 (biased variance for normalisation,
+// unbiased for the running estimate, ReLU mask applied to dy first). The reference runs cuDNN
+// batchnorm graphs (cudnn_engine.cu:580-865) or block-per-channel NCHW kernels
+// (cuda_engine.cu:295-672). Each pass moves 16-byte vectors and reads x exactly once.
+#include "ptx.cuh"
+
+namespace tnnb {
+
+typedef __nv_bfloat16 bf16;
+
+// Block = 32 channel groups of 8 (256 channels) x 8 row lanes. grid = (ceil(C/256), row splits).
+// ws: double[2*C] (sum, sum of squares) - or (sum dy, sum dy*xhat) for the backward.
+template <bool BWD>
+__global__ void __launch_bounds__(256)
+bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
+                 const float* __restrict__ mean, const float* __restrict__ rstd, double* __restrict__ ws, long long M,
+                 int C, long long rows_per_block, int relu) {
+  __shared__ float red[2][8][32][9];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c0 = (blockIdx.x * 32 + cx) * 8;
+  const long long r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
+  float a[8], b[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) a[k] = 0.f, b[k] = 0.f;
+  if (c0 < C) {
+    float mu[8], rs[8];
+    if (BWD) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) mu[k] = mean[c0 + k], rs[k] = rstd[c0 + k];
+    }
+    for (long long r = r0 + ry; r < r1; r += 8) {
+      uint4 raw = *reinterpret_cast<const uint4*>(x + r * C + c0);
+      const bf16* xv = reinterpret_cast<const bf16*>(&raw);
+      if (!BWD) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float v = __bfloat162float(xv[k]);
+          a[k] += v;
+          b[k] += v * v;
+        }
+      } else {
+        uint4 graw = *reinterpret_cast<const uint4*>(dy + r * C + c0);
+        const bf16* gv = reinterpret_cast<const bf16*>(&graw);
+        uint4 yraw = make_uint4(0, 0, 0, 0);
+        if (relu) yraw = *reinterpret_cast<const uint4*>(y + r * C + c0);
+        const bf16* yv = reinterpret_cast<const bf16*>(&yraw);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          float g = __bfloat162float(gv[k]);
+          if (relu && !(__bfloat162float(yv[k]) > 0.f)) g = 0.f;
+          a[k] += g;
+          b[k] += g * (__bfloat162float(xv[k]) - mu[k]) * rs[k];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) red[0][ry][cx][k] = a[k], red[1][ry][cx][k] = b[k];
+  __syncthreads();
+  if (ry < 2 && c0 < C) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += red[ry][j][cx][k];
+      atomicAdd(ws + (long long)ry * C + c0 + k, (double)s);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+bn_fwd_apply_kernel(const bf16* __restrict__ x, bf16* __restrict__ yout, const bf16* __restrict__ gamma,
+                    const bf16* __restrict__ beta, const double* __restrict__ ws, float* __restrict__ mean_o,
+                    float* __restrict__ rstd_o, float* __restrict__ run_mean, float* __restrict__ run_var, long long M, int C,
+                    long long rows_per_block, float eps, float momentum, int relu, int training) {
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c0 = (blockIdx.x * 32 + cx) * 8;
+  if (c0 >= C) return;
+  float sc[8], sh[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    float mu, var;
+    if (training) {
+      const double m = ws[c0 + k] / (double)M;
+      double v = ws[C + c0 + k] / (double)M - m * m;
+      if (v < 0) v = 0;
+      mu = (float)m;
+      var = (float)v;
+    } else {
+      mu = run_mean[c0 + k];
+      var = run_var[c0 + k];
+    }
+    const float rs = rsqrtf(var + eps);
+    if (training && blockIdx.y == 0 && ry == 0) {
+      mean_o[c0 + k] = mu;
+      rstd_o[c0 + k] = rs;
+      const float unb = M > 1 ? var * (float)((double)M / (double)(M - 1)) : var;
+      run_mean[c0 + k] = (1.f - momentum) * run_mean[c0 + k] + momentum * mu;
+      run_var[c0 + k] = (1.f - momentum) * run_var[c0 + k] + momentum * unb;
+    }
+    const float g = gamma ? __bfloat162float(gamma[c0 + k]) : 1.f;
+    const float b = beta ? __bfloat162float(beta[c0 + k]) : 0.f;
+    sc[k] = g * rs;
+    sh[k] = b - mu * sc[k];
+  }
+  const long long r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
+  for (long long r = r0 + ry; r < r1; r += 8) {
+    uint4 raw = *reinterpret_cast<const uint4*>(x + r * C + c0);
+    const bf16* xv = reinterpret_cast<const bf16*>(&raw);
+    __align__(16) bf16 o[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float v = __bfloat162float(xv[k]) * sc[k] + sh[k];
+      o[k] = __float2bfloat16(relu ? fmaxf(v, 0.f) : v);
+    }
+    *reinterpret_cast<uint4*>(yout + r * C + c0) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
+                    const bf16* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ rstd,
+                    const double* __restrict__ ws, bf16* __restrict__ dx, float* __restrict__ dgamma,
+                    float* __restrict__ dbeta, long long M, int C, long long rows_per_block, int relu) {
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c0 = (blockIdx.x * 32 + cx) * 8;
+  if (c0 >= C) return;
+  float mu[8], rs[8], k1[8], sg[8], sgx[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    mu[k] = mean[c0 + k];
+    rs[k] = rstd[c0 + k];
+    sg[k] = (float)ws[c0 + k];
+    sgx[k] = (float)ws[C + c0 + k];
+    k1[k] = (gamma ? __bfloat162float(gamma[c0 + k]) : 1.f) * rs[k] / (float)M;
+    if (blockIdx.y == 0 && ry == 0 && dgamma) {
+      dgamma[c0 + k] += sgx[k];
+      dbeta[c0 + k] += sg[k];
+    }
+  }
+  const long long r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
+  for (long long r = r0 + ry; r < r1; r += 8) {
+    uint4 raw = *reinterpret_cast<const uint4*>(x + r * C + c0);
+    const bf16* xv = reinterpret_cast<const bf16*>(&raw);
+    uint4 graw = *reinterpret_cast<const uint4*>(dy + r * C + c0);
+    const bf16* gv = reinterpret_cast<const bf16*>(&graw);
+    uint4 yraw = make_uint4(0, 0, 0, 0);
+    if (relu) yraw = *reinterpret_cast<const uint4*>(y + r * C + c0);
+    const bf16* yv = reinterpret_cast<const bf16*>(&yraw);
+    __align__(16) bf16 o[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float g = __bfloat162float(gv[k]);
+      if (relu && !(__bfloat162float(yv[k]) > 0.f)) g = 0.f;
+      const float xh = (__bfloat162float(xv[k]) - mu[k]) * rs[k];
+      o[k] = __float2bfloat16(k1[k] * ((float)M * g - sg[k] - xh * sgx[k]));
+    }
+    *reinterpret_cast<uint4*>(dx + r * C + c0) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+static void bn_grid(long long M, int C, dim3& grid, long long& rpb) {
+  const int gx = (C + 255) / 256;
+  int gy = (4 * 148 + gx - 1) / gx;
+  rpb = (M + gy - 1) / gy;
+  if (rpb < 32) rpb = 32;
+  gy = (int)((M + rpb - 1) / rpb);
+  grid = dim3(gx, gy);
+}
+
+}  // namespace tnnb
+
+using namespace tnnb;
+
+extern "C" {
+
+// ws: double[2*C] scratch owned by the caller (zeroed here). gamma/beta may be null.
+int tnnb_batchnorm_fwd(const void* x, void* y, const void* gamma, const void* beta, void* ws, void* mean, void* rstd,
+                       void* run_mean, void* run_var, long long M, int C, float eps, float momentum, int relu, int training,
+                       void* stream) {
+  if (C % 8 || ((uintptr_t)x & 15) || ((uintptr_t)y & 15)) return -3;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid;
+  long long rpb;
+  bn_grid(M, C, grid, rpb);
+  if (training) {
+    cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st);
+    bn_reduce_kernel<false><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, (double*)ws, M, C, rpb, 0);
+  }
+  bn_fwd_apply_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)y, (const bf16*)gamma, (const bf16*)beta, (const double*)ws,
+                                            (float*)mean, (float*)rstd, (float*)run_mean, (float*)run_var, M, C, rpb, eps,
+                                            momentum, relu, training);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e - 1000;
+}
+
+// y: saved forward output (needed only when relu != 0). dgamma/dbeta (fp32) accumulate; may be null.
+int tnnb_batchnorm_bwd(const void* x, const void* dy, const void* y, const void* gamma, const void* mean, const void* rstd,
+                       void* ws, void* dx, void* dgamma, void* dbeta, long long M, int C, int relu, void* stream) {
+  if (C % 8 || ((uintptr_t)x & 15) || ((uintptr_t)dy & 15) || ((uintptr_t)dx & 15)) return -3;
+  if (relu && !y) return -5;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid;
+  long long rpb;
+  bn_grid(M, C, grid, rpb);
+  cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st);
+  bn_reduce_kernel<true><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y, (const float*)mean,
+                                               (const float*)rstd, (double*)ws, M, C, rpb, relu);
+  bn_bwd_apply_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y, (const bf16*)gamma,
+                                            (const float*)mean, (const float*)rstd, (const double*)ws, (bf16*)dx,
+                                            (float*)dgamma, (float*)dbeta, M, C, rpb, relu);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e - 1000;
+}
+
+}  // extern "C"

@@ -327,6 +327,24 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const long long orow = (MODE == MODE_RS) ? lrow : row;
           if (MODE == MODE_AG && p.epi) {
             bf16* ax = p.aux + orow * p.ldd + col0;
+            if (fullc && (p.ldd % 8 == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                __align__(16) bf16 tt[8];
+                if (p.epi == 1) {
+#pragma unroll
+                  for (int k = 0; k < 8; ++k) {
+                    tt[k] = __float2bfloat16(v[j + k]);
+                    v[j + k] = gelu_tanh(__bfloat162float(tt[k]));
+                  }
+                  *reinterpret_cast<uint4*>(ax + j) = *reinterpret_cast<uint4*>(tt);
+                } else {
+                  *reinterpret_cast<uint4*>(tt) = *reinterpret_cast<const uint4*>(ax + j);
+#pragma unroll
+                  for (int k = 0; k < 8; ++k) v[j + k] *= gelu_tanh_grad(__bfloat162float(tt[k]));
+                }
+              }
+            } else
             for (int j = 0; j < 32; ++j) {
               if (!(fullc || col0 + j < p.N)) continue;
               if (p.epi == 1) {

@@ -12,11 +12,12 @@
 // The reference obtains these from cublasGemmEx / cuDNN matmul graphs
 // (src/math/cuda/gemm.cu:72-112, src/nn/engines/cudnn_engine.cu:113-326).
 //
-// Structure: persistent CTAs (one per SM), 6 warps.
+// Structure: persistent CTAs (one per SM), 10 warps.
 //   warp 0      TMA producer (one lane), STAGES-deep ring of (A,B) k-blocks
 //   warp 1      TMEM owner + MMA issuer (one lane), two accumulators so the
 //               epilogue of tile i overlaps the main loop of tile i+1
-//   warps 2-5   epilogue: TMEM -> registers -> fused math -> global memory
+//   warps 2-9   epilogue: TMEM -> registers -> fused math -> global memory
+//               (two warps per 32-lane TMEM quarter, each owning half of the columns)
 // Every barrier wait is bounded; on expiry the kernel records a status code,
 // raises a CTA-wide abort flag and unwinds (TMEM is always released).
 #include "gemm_tcgen05.h"
@@ -178,7 +179,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, uint32_t (&r
 }
 
 template <int BN, int A_MN, int B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   using Cfg = GemmCfg<BN>;
@@ -203,7 +204,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 128);
+      mbar_init(&tempty[a], 256);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -323,7 +324,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       }
     }
   } else {
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int q = warp & 3;            // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;  // eight epilogue warps: two per quarter, each takes half of the columns
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
@@ -339,7 +341,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const int row = mb * 128 + q * 32 + lane;
       const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
         uint32_t r[32];
         tmem_ld_32x32(t_addr + c * 32, r);
         tmem_ld_wait();
@@ -423,7 +425,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
     attr_set = true;
   }
-  kern<<<grid, 192, GemmCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, p);
+  kern<<<grid, 320, GemmCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }

@@ -42,6 +42,14 @@ class _Composite(Layer):
             c.bind(params[i:i + n], grads[i:i + n])
             i += n
 
+    def bind_masters(self, masters):
+        self.masters = masters
+        i = 0
+        for c in self.children():
+            n = len(c.param_specs())
+            c.bind_masters(masters[i:i + n])
+            i += n
+
     def param_descriptors(self):
         out = []
         for c in self.children():

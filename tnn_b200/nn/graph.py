@@ -261,6 +261,8 @@ class Graph:
                     else:
                         m.zero_()
             l.bind(ps, gs)
+            # fp32 views of the same parameters (batch-norm running statistics are kept in these)
+            l.bind_masters([self.master_flat[o:o + n].view(shape) for (o, n, shape, _) in self.layer_slices[id(l)]])
             l.set_io_dtype(self.io_dtype)
         self.sync_params_from_master()
         self._build_segments()

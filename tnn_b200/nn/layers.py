@@ -85,6 +85,9 @@ class Layer:
     def bind(self, params: List[torch.Tensor], grads: List[Optional[torch.Tensor]]):
         self.params, self.grads = params, grads
 
+    def bind_masters(self, masters: List[torch.Tensor]):
+        self.masters = masters
+
     def sublayers(self) -> List["Layer"]:
         return []
 
@@ -621,9 +624,11 @@ class BatchNorm(Layer):
         return specs
 
     def _split(self):
+        # gamma / beta in the compute dtype, running statistics always from the fp32 master views
+        stats = getattr(self, "masters", None) or self.params
         if self.affine:
-            return self.params[0], self.params[1], self.params[2], self.params[3]
-        return None, None, self.params[0], self.params[1]
+            return self.params[0], self.params[1], stats[2], stats[3]
+        return None, None, stats[0], stats[1]
 
     def forward(self, inputs, ctx):
         x = inputs[0].contiguous()

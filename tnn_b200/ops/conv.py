@@ -1,0 +1,108 @@
+"""NHWC convolution on CUDA: tcgen05 GEMM over the activations (1x1, stride 1) or over patch
+matrices built by the im2col / col2im kernels (every other geometry). Reference semantics:
+src/nn/engines/cpu_engine.cpp:617-734; the reference itself calls cuDNN conv graphs."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .gemm import LAUNCHES, gemm
+
+_DECL = False
+
+
+def _lib_conv():
+    global _DECL
+    lib = _lib.load()
+    if not _DECL:
+        vp, i = ctypes.c_void_p, ctypes.c_int
+        for name in ("tnnb_im2col", "tnnb_col2im"):
+            getattr(lib, name).argtypes = [vp, vp] + [i] * 11 + [vp]
+            getattr(lib, name).restype = i
+        _DECL = True
+    return lib
+
+
+def _geom(x_shape, w_shape, stride, pad):
+    n, h, w, c = x_shape
+    o, kh, kw, _ = w_shape
+    oh = (h + 2 * pad[0] - kh) // stride[0] + 1
+    ow = (w + 2 * pad[1] - kw) // stride[1] + 1
+    return n, h, w, c, o, kh, kw, oh, ow
+
+
+def _is_pointwise(kh, kw, stride, pad):
+    return kh == 1 and kw == 1 and stride == (1, 1) and pad == (0, 0)
+
+
+def im2col(x: torch.Tensor, kh, kw, stride, pad, oh, ow) -> Tuple[torch.Tensor, int]:
+    n, h, w, c = x.shape
+    K = kh * kw * c
+    kld = (K + 7) // 8 * 8
+    cols = torch.empty(n * oh * ow, kld, dtype=x.dtype, device=x.device)
+    rc = _lib_conv().tnnb_im2col(_lib.ptr(x), _lib.ptr(cols), n, h, w, c, kh, kw, stride[0], stride[1], pad[0], pad[1], kld,
+                                 _lib.stream())
+    _lib.check_rc(rc, "im2col")
+    LAUNCHES["count"] += 1
+    return cols, K
+
+
+def _w2d(w: torch.Tensor, K: int) -> torch.Tensor:
+    """[O, KH*KW*C] view of the weights; padded to a multiple of 8 columns when TMA needs it."""
+    w2 = w.reshape(w.shape[0], K)
+    if K % 8 == 0:
+        return w2
+    pad = torch.zeros(w.shape[0], (K + 7) // 8 * 8, dtype=w.dtype, device=w.device)
+    pad[:, :K] = w2
+    return pad[:, :K]
+
+
+def conv2d_fwd(x, w, bias, stride, pad, relu=False):
+    stride, pad = tuple(stride), tuple(pad)
+    n, h, wd, c, o, kh, kw, oh, ow = _geom(x.shape, w.shape, stride, pad)
+    if _is_pointwise(kh, kw, stride, pad) and c % 8 == 0:
+        a, K = x.reshape(-1, c), c
+    else:
+        cols, K = im2col(x, kh, kw, stride, pad, oh, ow)
+        a = cols[:, :K]
+    y = gemm(a, _w2d(w, K), bias=bias, relu=relu)
+    return y.view(n, oh, ow, o)
+
+
+def conv2d_dgrad(dy, w, x_shape, stride, pad):
+    stride, pad = tuple(stride), tuple(pad)
+    n, h, wd, c, o, kh, kw, oh, ow = _geom(x_shape, w.shape, stride, pad)
+    dy2 = dy.reshape(-1, o)
+    K = kh * kw * c
+    if _is_pointwise(kh, kw, stride, pad) and c % 8 == 0:
+        return gemm(dy2, w.reshape(o, K), b_t=True).view(n, h, wd, c)
+    kld = (K + 7) // 8 * 8
+    dcols = torch.empty(dy2.shape[0], kld, dtype=dy.dtype, device=dy.device)
+    gemm(dy2, _w2d(w, K), b_t=True, out=dcols[:, :K])
+    dx = torch.empty(n, h, wd, c, dtype=dy.dtype, device=dy.device)
+    rc = _lib_conv().tnnb_col2im(_lib.ptr(dcols), _lib.ptr(dx), n, h, wd, c, kh, kw, stride[0], stride[1], pad[0], pad[1], kld,
+                                 _lib.stream())
+    _lib.check_rc(rc, "col2im")
+    LAUNCHES["count"] += 1
+    return dx
+
+
+def conv2d_wgrad(x, dy, dw, stride, pad):
+    stride, pad = tuple(stride), tuple(pad)
+    n, h, wd, c, o, kh, kw, oh, ow = _geom(x.shape, dw.shape, stride, pad)
+    dy2 = dy.reshape(-1, o)
+    K = kh * kw * c
+    if _is_pointwise(kh, kw, stride, pad) and c % 8 == 0:
+        a = x.reshape(-1, c)
+    else:
+        cols, _ = im2col(x, kh, kw, stride, pad, oh, ow)
+        a = cols[:, :K]
+    if K % 4 == 0:
+        gemm(dy2, a, a_t=True, b_t=True, out=dw.view(o, K), atomic=True)
+    else:
+        tmp = torch.zeros(o, (K + 7) // 8 * 8, dtype=torch.float32, device=dw.device)
+        gemm(dy2, a, a_t=True, b_t=True, out=tmp[:, :K], atomic=True)
+        dw.view(o, K).add_(tmp[:, :K])
