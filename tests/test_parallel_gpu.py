@@ -59,3 +59,27 @@ def test_dp2_matches_single_process(kind, tmp_path):
 def test_tp2_trains(kind, tmp_path):
     res = launch(2, "tp", kind, str(tmp_path / "tp.pt"))
     assert res["losses"][-1] < res["losses"][0]
+
+
+def launch_pp(n, layout, kind, out):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29613", os.path.join(HERE, "_pp_gpu_worker.py"), layout, kind, out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_pp2_1f1b_trains_and_saves_stage(tmp_path):
+    from tnn_b200.nn.graph import Graph
+    res = launch_pp(2, "pp2", "nccl", str(tmp_path / "ckpt"))
+    assert res["losses"][-1] < res["losses"][0] - 0.5
+    g = Graph.load_state(res["stage_file"])  # stage 0 file written by rank 0: a TNNG graph of its own
+    assert g.input_nodes[0].uid() == "input" and len(g.edges) > 10
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_pp2_tp2_fused_trains(tmp_path):
+    res = launch_pp(4, "pp2tp2", "fused", str(tmp_path / "ckpt"))
+    assert res["losses"][-1] < res["losses"][0] - 0.5

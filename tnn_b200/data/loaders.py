@@ -61,6 +61,19 @@ class SyntheticLoader(BaseLoader):
                 l = torch.empty((self.batch,), dtype=torch.int64)
             self.ring.append((d.pin_memory() if pin else d, l.pin_memory() if pin else l))
         self.i = 0
+        # the ring is filled once: generating tens of millions of random numbers per step on the host
+        # would time the random generator, not the input pipeline
+        for d, l in self.ring:
+            self._fill(d, l)
+
+    def _fill(self, d, l):
+        if self.tokens:
+            seq = torch.randint(0, self.num_classes, (self.batch, self.shape[0] + 1), generator=self.gen)
+            d.copy_(seq[:, :-1])
+            l.copy_(seq[:, 1:])
+        else:
+            d.copy_(torch.rand(d.shape, generator=self.gen) if self.uniform else torch.randn(d.shape, generator=self.gen))
+            l.copy_(torch.randint(0, self.num_classes, (self.batch,), generator=self.gen))
 
     def __len__(self):
         return self.steps * self.batch
@@ -75,16 +88,6 @@ class SyntheticLoader(BaseLoader):
         if self.i >= self.steps:
             return None
         d, l = self.ring[self.i % len(self.ring)]
-        if self.tokens:
-            seq = torch.randint(0, self.num_classes, (self.batch, self.shape[0] + 1), generator=self.gen)
-            d.copy_(seq[:, :-1])
-            l.copy_(seq[:, 1:])
-        else:
-            if self.uniform:
-                d.copy_(torch.rand(d.shape, generator=self.gen))
-            else:
-                d.copy_(torch.randn(d.shape, generator=self.gen))
-            l.copy_(torch.randint(0, self.num_classes, (self.batch,), generator=self.gen))
         self.i += 1
         return d, l
 

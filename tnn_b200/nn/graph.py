@@ -449,6 +449,42 @@ class Graph:
         return cls.from_state(tnng.read_file(path), device=device, **compile_kw)
 
 
+def infer_shapes(graph: "Graph", input_shapes: Dict[str, Tuple[int, ...]]) -> Dict[str, Tuple[int, ...]]:
+    """Static shape of every node, from the layers' ``output_shape`` rules (no tensors involved)."""
+    graph.sort()
+    shapes = dict(input_shapes)
+    for e in graph.edges:
+        ins = [tuple(shapes[p.uid()]) for p in e.producers]
+        shapes[e.consumers[0].uid()] = tuple(e.layer.output_shape(ins))
+    return shapes
+
+
+def partition_graph(graph: "Graph", ratios: Sequence[float]) -> List["Graph"]:
+    """Cut the sorted edge list into contiguous pipeline stages by ``ratios`` with the C++
+    partitioner (same algorithm and boundaries as src/partitioner/graph_partitioner.cpp:101-260:
+    a stage's inputs are the nodes it consumes but does not produce, its outputs the nodes it
+    produces that a later stage consumes or that nothing consumes). Stage graphs share the layer
+    objects of ``graph`` and are returned uncompiled; ``stage.start_layer`` / ``stage.layer_count``
+    give the position in the full edge list."""
+    from ..host import H
+    graph.sort()
+    parts = H.partition(graph.ir(), [float(r) for r in ratios])
+    stages = []
+    for p in parts:
+        g = Graph()
+        nodes = [g.make_node(uid) for uid in p["nodes"]]
+        for i in p["inputs"]:
+            g.set_input(nodes[i])
+        for i in p["outputs"]:
+            g.set_output(nodes[i])
+        for eid, (_, prod, cons) in zip(p["edge_ids"], p["edges"]):
+            g.add_edge(graph.edges[eid].layer, [nodes[i] for i in prod], [nodes[i] for i in cons])
+        g.start_layer, g.layer_count = int(p["start_layer"]), int(p["layer_count"])
+        g.input_uids, g.output_uids = list(p["input_uids"]), list(p["output_uids"])
+        stages.append(g)
+    return stages
+
+
 def _sorted(o):
     if isinstance(o, dict):
         return {k: _sorted(o[k]) for k in sorted(o)}

@@ -101,6 +101,7 @@ class CommContext:
         # call number of the current pass, read by the kernels from device memory so that a captured
         # CUDA graph sees a new value on every replay
         self.tick = torch.zeros(1, dtype=torch.int32, device=device)
+        self.seq_len = 0  # set by the pipeline runtime: stages after the first cannot read it off their input
         if self.fused:
             _declare(self.lib)
 

@@ -18,12 +18,17 @@ from .tp import CommContext, GatherSite, ScatterSite, _reinit_shards
 
 
 class _TPGPTChain(_Segment):
-    def __init__(self, chain: _GPTChain, cc: CommContext):
+    def __init__(self, chain: _GPTChain, cc: CommContext, ring: int = 1, in_is_shard: bool = False):
         self.start, self.end = chain.start, chain.end
         self.blocks, self.final = chain.blocks, chain.final
         self.in_node, self.out_node = chain.in_node, chain.out_node
         self.cc = cc
-        self.sites = None
+        # One set of symmetric buffers per micro-batch that can be in flight (pipeline stages keep the
+        # gathered activations of a micro-batch until its backward pass).
+        self.ring = max(1, ring)
+        self.site_ring = {}
+        # True when the chain starts at a pipeline-stage boundary: the input is already this rank's rows
+        self.in_is_shard = in_is_shard
 
     def _make_sites(self, M: int, E: int):
         cc = self.cc
@@ -38,7 +43,7 @@ class _TPGPTChain(_Segment):
                 "s_qkv": ScatterSite(cc, M, E), "s_fc1": ScatterSite(cc, M, E),  # backward reduce-scatters
                 "F": F,
             })
-        self.sites, self.M = sites, M
+        return sites
 
     def _ln_into(self, site: GatherSite, x, pending, ln, p, seed):
         tgt = site.mine()
@@ -50,18 +55,23 @@ class _TPGPTChain(_Segment):
     def forward(self, vals, ctx):
         cc = self.cc
         x3 = vals[id(self.in_node)]
-        B, S, E = x3.shape
-        M = B * S
+        E = x3.shape[-1]
+        rows_in = x3.numel() // E
+        M = rows_in * cc.tp if self.in_is_shard else rows_in
+        S = cc.seq_len or x3.shape[1]
+        B = M // S
         if M % (128 * cc.tp):
             raise ValueError(f"tensor parallelism needs batch*seq ({M}) to be a multiple of {128 * cc.tp}")
-        if self.sites is None or self.M != M:
-            self._make_sites(M, E)
+        slot = int(ctx.get("_pid", 0)) % self.ring
+        if slot not in self.site_ring or self.site_ring[slot][0] != M:
+            self.site_ring[slot] = (M, self._make_sites(M, E))
+        sites = ctx["sites"] = self.site_ring[slot][1]
         Ms = M // cc.tp
         cc.tick.add_(1)  # new call number for every fused GEMM of this pass
-        x = _flat2d(x3)[cc.idx * Ms:(cc.idx + 1) * Ms].contiguous()
+        x = _flat2d(x3).contiguous() if self.in_is_shard else _flat2d(x3)[cc.idx * Ms:(cc.idx + 1) * Ms].contiguous()
         pending, p_pend, seed_pend = None, 0.0, 0
         saved = []
-        for es, st in zip(self.blocks, self.sites):
+        for es, st in zip(self.blocks, sites):
             ln1, attn, drop1, _, ln2, fc1, _, fc2, drop2, _ = (e.layer for e in es)
             s = {}
             x, s["mean1"], s["rstd1"] = self._ln_into(st["g1"], x, pending, ln1, p_pend, seed_pend)
@@ -104,7 +114,8 @@ class _TPGPTChain(_Segment):
         g = _flat2d(g).contiguous()
         cc.tick.add_(1)
         p_pend, seed_pend = ctx["tail"]
-        last = self.sites[-1]
+        sites = ctx["sites"]
+        last = sites[-1]
         if self.final is not None:
             ln = self.final.layer
             xf, mean, rstd = ctx["final"]
@@ -113,7 +124,7 @@ class _TPGPTChain(_Segment):
         else:
             dres, dpend = g, raw.dropout(g, p_pend, seed_pend)
         for bi in reversed(range(len(self.blocks))):
-            es, s, st = self.blocks[bi], ctx["saved"][bi], self.sites[bi]
+            es, s, st = self.blocks[bi], ctx["saved"][bi], sites[bi]
             ln1, attn, _, _, ln2, fc1, _, fc2, _, _ = (e.layer for e in es)
             wqkv, bqkv, wo, bo = attn.params
             # ---- fc2 (row parallel): gather dY, dgrad with GELU' ----
@@ -143,23 +154,26 @@ class _TPGPTChain(_Segment):
             raw.colsum_accum(dqkv, attn.grads[1])
             dh1 = st["s_qkv"].gemm(dqkv, wqkv, b_t=True)                           # [Ms, E]
             # ---- LN1 (+ the previous block's trailing residual add + dropout) ----
-            prev_tgt = self.sites[bi - 1]["gb2"].mine() if (bi > 0 and dh1.is_cuda) else None
+            prev_tgt = sites[bi - 1]["gb2"].mine() if (bi > 0 and dh1.is_cuda) else None
             dres, dpend = raw.layernorm_bwd(dh1, s["x"], s["mean1"], s["rstd1"], ln1.params[0], dx1, s["had_pending"],
                                             s["p_in"], s["seed_in"], ln1.grads[0], ln1.grads[1], ddelta_out=prev_tgt)
-        if id(self.in_node) not in no_grad_nodes:
+        if self.in_is_shard:
+            if id(self.in_node) not in no_grad_nodes:
+                _accum(gvals, self.in_node, dres.reshape(1, Ms, E))
+        elif id(self.in_node) not in no_grad_nodes:
             full = torch.zeros(M, E, dtype=dres.dtype, device=dres.device)
             full[cc.idx * Ms:(cc.idx + 1) * Ms] = dres
             _accum(gvals, self.in_node, full.reshape(B, S, E))
 
 
-def install_tp_segments(graph: Graph, topo, heap, fused: bool = True) -> None:
+def install_tp_segments(graph: Graph, topo, heap, fused: bool = True, ring: int = 1) -> None:
     """Swap every fused GPT chain of a compiled graph for its tensor-parallel version and give the
     shards of each tensor-parallel rank their own random initialisation."""
     cc = CommContext(topo, heap, fused, graph.device)
     n = 0
     for k, seg in enumerate(graph.segments):
         if isinstance(seg, _GPTChain):
-            graph.segments[k] = _TPGPTChain(seg, cc)
+            graph.segments[k] = _TPGPTChain(seg, cc, ring, id(seg.in_node) in {id(n) for n in graph.input_nodes})
             n += 1
     if n == 0:
         raise ValueError("no transformer block chain found for tensor parallelism")
