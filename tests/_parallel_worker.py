@@ -47,4 +47,10 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:
+        import traceback
+
+        print("WORKER-ERROR rank", os.environ.get("RANK"), traceback.format_exc()[-1500:].replace("\n", " | "), flush=True)
+        os._exit(1)

@@ -20,7 +20,7 @@ def launch(n, mode, kind, out):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", "29611", os.path.join(HERE, "_parallel_worker.py"), mode, kind, out]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, "\n".join(l for l in r.stdout.splitlines() if "WORKER-ERROR" in l or "Error" in l)[:3000] + r.stdout[-2500:] + r.stderr[-500:]
     line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
     return json.loads(line[7:])
 
@@ -66,7 +66,7 @@ def launch_pp(n, layout, kind, out):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", "29613", os.path.join(HERE, "_pp_gpu_worker.py"), layout, kind, out]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, "\n".join(l for l in r.stdout.splitlines() if "WORKER-ERROR" in l or "Error" in l)[:3000] + r.stdout[-2500:] + r.stderr[-500:]
     return json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
 
 
