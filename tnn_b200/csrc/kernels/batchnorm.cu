@@ -224,3 +224,64 @@ int tnnb_batchnorm_bwd(const void* x, const void* dy, const void* y, const void*
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free training-mode forward (declared in batchnorm_noalloc.h; no counterpart in the
+// reference). Same kernels and launch shapes as tnnb_batchnorm_fwd; the only difference is where
+// the per-channel partial sums live: in the fixed array below instead of a caller-supplied buffer.
+// ---------------------------------------------------------------------------------------------
+#include "batchnorm_noalloc.h"
+
+static __device__ __align__(256) double g_bn_noalloc_scratch[2 * TNNB_BN_NOALLOC_MAX_CHANNELS];  // 64 KiB per device
+
+namespace {
+constexpr int kMaxDevices = 64;
+double* g_bn_noalloc_ptr[kMaxDevices] = {};  // device address of the array above, per device ordinal
+}
+
+extern "C" {
+
+int tnnb_batchnorm_fwd_noalloc(const void* x, void* y, const void* gamma, const void* beta, void* mean, void* rstd,
+                               void* run_mean, void* run_var, long long M, int C, float eps, float momentum, int relu,
+                               void* stream) {
+  if (M <= 0 || C <= 0 || !x || !y || !mean || !rstd || !run_mean || !run_var) return TNNB_NOALLOC_BAD_ARG;
+  if (C > TNNB_BN_NOALLOC_MAX_CHANNELS) return TNNB_NOALLOC_TOO_LARGE;
+  if (C % 8 || ((uintptr_t)x & 15) || ((uintptr_t)y & 15)) return TNNB_NOALLOC_MISALIGNED;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TNNB_NOALLOC_SETUP_FAILED;
+  if (!g_bn_noalloc_ptr[dev]) {  // first call on this device: look the array up once
+    double* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_bn_noalloc_scratch) != cudaSuccess || !p) {
+      (void)cudaGetLastError();
+      return TNNB_NOALLOC_SETUP_FAILED;
+    }
+    g_bn_noalloc_ptr[dev] = p;
+  }
+  double* ws = g_bn_noalloc_ptr[dev];
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid;
+  long long rpb;
+  bn_grid(M, C, grid, rpb);
+  // The reduce kernel accumulates with atomics, so the 2*C sums it uses must start at zero.
+  if (cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st) != cudaSuccess) return TNNB_NOALLOC_LAUNCH_FAILED;
+  bn_reduce_kernel<false><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, ws, M, C, rpb, 0);
+  bn_fwd_apply_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)y, (const bf16*)gamma, (const bf16*)beta, ws, (float*)mean,
+                                            (float*)rstd, (float*)run_mean, (float*)run_var, M, C, rpb, eps, momentum, relu, 1);
+  return cudaGetLastError() == cudaSuccess ? TNNB_NOALLOC_OK : TNNB_NOALLOC_LAUNCH_FAILED;
+}
+
+int tnnb_batchnorm_noalloc_max_channels(void) { return TNNB_BN_NOALLOC_MAX_CHANNELS; }
+
+const char* tnnb_noalloc_strerror(int rc) {
+  switch (rc) {
+    case TNNB_NOALLOC_OK: return "ok";
+    case TNNB_NOALLOC_BAD_ARG: return "null pointer or non-positive size";
+    case TNNB_NOALLOC_TOO_LARGE: return "channel count exceeds TNNB_BN_NOALLOC_MAX_CHANNELS (4096): use tnnb_batchnorm_fwd with a caller-owned workspace";
+    case TNNB_NOALLOC_MISALIGNED: return "channels must be a multiple of 8 and x/y 16-byte aligned";
+    case TNNB_NOALLOC_SETUP_FAILED: return "could not obtain the address of the built-in scratch array on the current device";
+    case TNNB_NOALLOC_LAUNCH_FAILED: return "memset or kernel launch failed";
+    default: return "unknown code";
+  }
+}
+
+}  // extern "C"
