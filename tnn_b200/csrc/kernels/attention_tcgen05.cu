@@ -71,15 +71,23 @@ __device__ __forceinline__ void store_row_chunk_sw128(uint8_t* tile, int row, in
 }
 
 // ------------------------------------------------------------------ forward
+// One CTA per PAIR of 128-row Q tiles (A = rows [q0, q0+128), B = the next 128), one CTA per SM:
+//   warp 0      TMA: both Q tiles once, then (K_j, V_j) into a two-stage ring shared by A and B
+//   warp 1      MMA: S_X = Q_X K_j^T -> TMEM (128 columns each), O_X += P_X V_j accumulated IN TMEM
+//   warps 2-5   softmax of tile A, warps 6-9 softmax of tile B: one thread per Q row (TMEM lane)
+// While one tile's threads are busy with exponentials the tensor core runs the other tile's products
+// and the next S of the same tile (S is consumed into registers in one tcgen05.ld, which frees its
+// TMEM columns at once). The running maximum is only raised when a row's new maximum exceeds it by
+// more than 2^8 ("lazy rescale"): then, and only then, O is corrected in TMEM (ld, scale, st).
 struct FwdSmem {
-  static constexpr int Q = 0;
-  static constexpr int K0 = Q + TILE_BYTES;          // stage s: K at K0 + s*2*TILE, V right after
-  static constexpr int P = K0 + 4 * TILE_BYTES;      // [128 x 128] bf16
-  static constexpr int BARS = P + 2 * TILE_BYTES;
+  static constexpr int Q = 0;                          // two [128 x 64] tiles
+  static constexpr int K0 = Q + 2 * TILE_BYTES;        // stage s: K at K0 + s*2*TILE, V right after
+  static constexpr int P = K0 + 4 * TILE_BYTES;        // P_A then P_B, [128 x 128] bf16 each
+  static constexpr int BARS = P + 4 * TILE_BYTES;
   static constexpr int TOTAL = BARS + 256;
 };
 
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(320, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -92,46 +100,51 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;   // [2]
   uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_ready = bars + 6;
-  uint64_t* o_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* s_full = bars + 5;    // [2]  per Q tile
+  uint64_t* s_free = bars + 7;    // [2]
+  uint64_t* p_ready = bars + 9;   // [2]
+  uint64_t* o_full = bars + 11;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
+  const int pair = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
   const int h = blockIdx.y, b = blockIdx.z;
-  const int q0 = qt * 128;
+  const int q0 = pair * 256;
   const int n_kv_all = (p.S + 127) / 128;
-  const int n_kv = p.causal ? min(qt + 1, n_kv_all) : n_kv_all;
+  // number of K/V tiles each Q tile needs (causal: up to and including its diagonal tile)
+  const int n_a = p.causal ? min(2 * pair + 1, n_kv_all) : n_kv_all;
+  const int n_b = p.causal ? min(2 * pair + 2, n_kv_all) : n_kv_all;
+  const int n_kv = n_b;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_free[s], 4);
+      mbar_init(&p_ready[s], 128);
+      mbar_init(&o_full[s], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, 128);
-    mbar_init(o_full, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 256);
+    tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tm_S = tmem_base;        // 128 columns
-  const uint32_t tm_O = tmem_base + 128;  // 64 columns
+  // columns: S_A 0..127, S_B 128..255, O_A 256..319, O_B 320..383
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, TILE_BYTES);
+      mbar_expect_tx(q_full, 2 * TILE_BYTES);
       tma_load_4d(smem + FwdSmem::Q, &tmQ, q_full, 0, h, q0, b);
+      tma_load_4d(smem + FwdSmem::Q + TILE_BYTES, &tmQ, q_full, 0, h, q0 + 128, b);
       for (int j = 0; j < n_kv; ++j) {
         const int s = j & 1;
         if (!wait_or_abort(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) {
@@ -150,139 +163,189 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, 0, 1);
       const uint32_t q_addr = smem_u32(smem + FwdSmem::Q);
       const uint32_t p_addr = smem_u32(smem + FwdSmem::P);
-      bool ok = wait_or_abort(q_full, 0, abort_flag);
-      if (!ok) raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
-      for (int j = 0; ok && j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t k_addr = smem_u32(smem + FwdSmem::K0 + s * 2 * TILE_BYTES);
-        const uint32_t v_addr = k_addr + TILE_BYTES;
-        if (!wait_or_abort(&kv_full[s], (j >> 1) & 1, abort_flag)) {
-          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
-          break;
-        }
-        tc_fence_after();
-        // S_j may overwrite S_{j-1}: the softmax warps published P_{j-1}
-        // (p_ready) only after they had finished reading S_{j-1}.
+      auto issue_qk = [&](int x, int j) {
+        const uint32_t k_addr = smem_u32(smem + FwdSmem::K0 + (j & 1) * 2 * TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          tc_mma_ss(tm_S, make_smem_desc(q_addr + k * 32, 16, 1024),
+          tc_mma_ss(tmem_base + x * 128, make_smem_desc(q_addr + x * TILE_BYTES + k * 32, 16, 1024),
                     make_smem_desc(k_addr + k * 32, 16, 1024), idesc_s, k > 0);
-        tc_commit(s_full);
-        if (!wait_or_abort(p_ready, j & 1, abort_flag)) {
-          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
-          break;
-        }
-        tc_fence_after();
+        tc_commit(&s_full[x]);
+      };
+      auto issue_pv = [&](int x, int j) {
+        const uint32_t v_addr = smem_u32(smem + FwdSmem::K0 + (j & 1) * 2 * TILE_BYTES + TILE_BYTES);
+        const uint32_t pa = p_addr + x * 2 * TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          tc_mma_ss(tm_O, make_smem_desc(p_addr + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
-                    make_smem_desc(v_addr + k * 2048, 8192, 1024), idesc_o, k > 0);
-        tc_commit(o_full);
-        tc_commit(&kv_empty[s]);
+          tc_mma_ss(tmem_base + 256 + x * 64, make_smem_desc(pa + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(v_addr + k * 2048, 8192, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&o_full[x]);
+      };
+      bool ok = wait_or_abort(q_full, 0, abort_flag) && wait_or_abort(&kv_full[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0, 0);
+        issue_qk(1, 0);
       }
+      for (int j = 0; ok && j < n_kv; ++j) {
+        if (j + 1 < n_kv) {  // next scores first: they overlap with this step's softmax
+          ok = wait_or_abort(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
+          if (ok && j + 1 < n_a) {
+            ok = wait_or_abort(&s_free[0], j & 1, abort_flag);
+            if (ok) {
+              tc_fence_after();
+              issue_qk(0, j + 1);
+            }
+          }
+          if (ok) ok = wait_or_abort(&s_free[1], j & 1, abort_flag);
+          if (ok) {
+            tc_fence_after();
+            issue_qk(1, j + 1);
+          }
+        }
+        if (ok && j < n_a) {
+          ok = wait_or_abort(&p_ready[0], j & 1, abort_flag);
+          if (ok) {
+            tc_fence_after();
+            issue_pv(0, j);
+          }
+        }
+        if (ok) ok = wait_or_abort(&p_ready[1], j & 1, abort_flag);
+        if (ok) {
+          tc_fence_after();
+          issue_pv(1, j);
+          tc_commit(&kv_empty[j & 1]);
+        }
+      }
+      if (!ok) raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
     }
   } else {
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;  // row inside the Q tile == TMEM lane
-    const int q_idx = q0 + row;
+    const int x = (warp - 2) >> 2;  // 0: tile A, 1: tile B
+    const int quarter = warp & 3;   // TMEM lane quarter this warp may touch
+    const int row = quarter * 32 + lane;
+    const int q_idx = q0 + x * 128 + row;
+    const int n_x = x ? n_b : n_a;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    float o_acc[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) o_acc[i] = 0.f;
+    const uint32_t tm_S = tmem_base + x * 128 + lane_off;
+    const uint32_t tm_O = tmem_base + 256 + x * 64 + lane_off;
+    uint8_t* p_tile = smem + FwdSmem::P + x * 2 * TILE_BYTES;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      if (!wait_or_abort(s_full, j & 1, abort_flag)) {
-        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+    for (int j = 0; j < n_x; ++j) {
+      if (!wait_or_abort(&s_full[x], j & 1, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after();
+      uint32_t sr[128];
+      tmem_ld_32x128_wait(tm_S, sr);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[x]);  // S_X may be overwritten by the next product
       const int kv0 = j * 128;
-      const bool need_mask = (p.causal && j == qt) || (kv0 + 128 > p.S);
-      // pass 1: row maximum
-      float m_tile = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float f[32];
-        tmem_ld_32x32f(tm_S + lane_off + c * 32, f);
+      const bool need_mask = (p.causal && kv0 + 127 > q0 + x * 128) || (kv0 + 128 > p.S);
+      if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv = kv0 + c * 32 + i;
-          const bool dead = need_mask && ((p.causal && kv > q_idx) || kv >= p.S);
-          m_tile = fmaxf(m_tile, dead ? -INFINITY : f[i] * p.scale_log2);
+        for (int i = 0; i < 128; ++i) {
+          const int kv = kv0 + i;
+          if ((p.causal && kv > q_idx) || kv >= p.S) sr[i] = 0xff800000u;  // -inf
         }
       }
-      const float m_new = fmaxf(m_run, m_tile);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);
-      // fold in O_{j-1} (it was computed against m_run), then rescale
-      if (j > 0) {
-        if (!wait_or_abort(o_full, (j - 1) & 1, abort_flag)) {
-          if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
+      float mx0 = __uint_as_float(sr[0]), mx1 = __uint_as_float(sr[1]), mx2 = __uint_as_float(sr[2]),
+            mx3 = __uint_as_float(sr[3]);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          float f[32];
-          tmem_ld_32x32f(tm_O + lane_off + c * 32, f);
+      for (int i = 4; i < 128; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
+      }
+      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      bool waited_o = false;
+      if (j == 0) {
+        m_run = (m_tile == -INFINITY) ? 0.f : m_tile;
+      } else {
+        const bool raise = m_tile > m_run + 8.f;
+        if (__any_sync(0xffffffffu, raise)) {  // warp-uniform: tcgen05.ld/st are warp-collective
+          float alpha = 1.f;
+          if (raise) {
+            alpha = exp2f(m_run - m_tile);
+            m_run = m_tile;
+            l_run *= alpha;
+          }
+          if (!wait_or_abort(&o_full[x], (j - 1) & 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          waited_o = true;
+          tc_fence_after();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += f[i];
+          for (int c = 0; c < 2; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tm_O + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(tm_O + c * 32, r);
+          }
+          tmem_st_wait();
         }
       }
-#pragma unroll
-      for (int i = 0; i < 64; ++i) o_acc[i] *= alpha;
-      // pass 2: P = exp2(S*scale - m), row sum, publish P
-      float l_tile = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float f[32];
-        tmem_ld_32x32f(tm_S + lane_off + c * 32, f);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv = kv0 + c * 32 + i;
-          const bool dead = need_mask && ((p.causal && kv > q_idx) || kv >= p.S);
-          const float e = dead ? 0.f : exp2f(f[i] * p.scale_log2 - m_use);
-          // accumulate what the tensor core will actually see (bf16 P)
-          f[i] = __bfloat162float(__float2bfloat16(e));
-          l_tile += f[i];
-        }
-        store_row_chunk_sw128(smem + FwdSmem::P, row, c * 32, f);
+      // P_X(j-1) must have been consumed before its shared-memory tile is overwritten
+      if (j > 0 && !waited_o && !wait_or_abort(&o_full[x], (j - 1) & 1, abort_flag)) {
+        ok = false;
+        break;
       }
-      l_run = l_run * alpha + l_tile;
-      m_run = m_new;
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float e0 = exp2f(fmaf(__uint_as_float(sr[c * 8 + 2 * k]), p.scale_log2, -m_run));
+          const float e1 = exp2f(fmaf(__uint_as_float(sr[c * 8 + 2 * k + 1]), p.scale_log2, -m_run));
+          l0 += e0;
+          l1 += e1;
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(e0, e1);
+          pk[k] = *reinterpret_cast<uint32_t*>(&h2);
+        }
+        *reinterpret_cast<uint4*>(p_tile + (c >> 3) * TILE_BYTES + sw128_offset(row, c & 7)) =
+            make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      l_run += l0 + l1;
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_ready);
+      mbar_arrive(&p_ready[x]);
     }
-    if (ok && n_kv > 0) {
-      if (wait_or_abort(o_full, (n_kv - 1) & 1, abort_flag)) {
+    if (!ok && lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+    if (ok && n_x > 0) {
+      if (wait_or_abort(&o_full[x], (n_x - 1) & 1, abort_flag)) {
         tc_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        bf16* orow = p.O + (((long long)b * p.S + q_idx) * p.H + h) * 64;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          float f[32];
-          tmem_ld_32x32f(tm_O + lane_off + c * 32, f);
+          uint32_t r[32];
+          tmem_ld_32x32(tm_O + c * 32, r);
+          tmem_ld_wait();
+          if (q_idx < p.S) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += f[i];
+            for (int g = 0; g < 4; ++g) {
+              uint32_t pk[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * k]) * inv,
+                                                           __uint_as_float(r[g * 8 + 2 * k + 1]) * inv);
+                pk[k] = *reinterpret_cast<uint32_t*>(&h2);
+              }
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+          }
         }
-      } else {
-        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
-        ok = false;
+        if (q_idx < p.S && p.LSE)
+          p.LSE[((long long)b * p.H + h) * p.S + q_idx] = (l_run > 0.f) ? m_run + log2f(l_run) : INFINITY;
+      } else if (lane == 0) {
+        raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
       }
-    }
-    if (ok && q_idx < p.S) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      bf16* orow = p.O + (((long long)b * p.S + q_idx) * p.H + h) * 64;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        __align__(16) bf16 t[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) t[k] = __float2bfloat16(o_acc[c * 8 + k] * inv);
-        *reinterpret_cast<uint4*>(orow + c * 8) = *reinterpret_cast<uint4*>(t);
-      }
-      if (p.LSE) p.LSE[((long long)b * p.H + h) * p.S + q_idx] = (l_run > 0.f) ? m_run + log2f(l_run) : INFINITY;
     }
   }
 
@@ -290,7 +353,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -781,8 +844,8 @@ int tnnb_attn_fwd(const void* qkv, void* out, void* lse, int B, int S, int H, in
     if ((rc = set_smem(attn_fwd_kernel, FwdSmem::TOTAL))) return rc;
     once = true;
   }
-  dim3 grid((S + 127) / 128, H, B);
-  attn_fwd_kernel<<<grid, 192, FwdSmem::TOTAL, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  dim3 grid((S + 255) / 256, H, B);
+  attn_fwd_kernel<<<grid, 320, FwdSmem::TOTAL, (cudaStream_t)stream>>>(tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
 }
