@@ -40,6 +40,7 @@ struct AttnParams {
   bf16* O;           // [B,S,H,64]
   float* LSE;        // [B,H,S] in scaled log2 units
   const float* delta;  // [B,H,S]
+  float* dq_acc;       // [B,S,H,64] fp32, zeroed before the backward kernel
   bf16* dQ;          // dqkv + 0        row pitch 3*H*64
   bf16* dK;          // dqkv + H*64
   bf16* dV;          // dqkv + 2*H*64
@@ -379,8 +380,19 @@ __global__ void attn_delta_kernel(const bf16* __restrict__ O, const bf16* __rest
   }
 }
 
-// ------------------------------------------------------------ backward dK/dV
-struct BwdKvSmem {
+// ----------------------------------------------------------------- backward
+// One kernel for dK, dV and dQ. One CTA per 128-row K/V tile (resident in shared memory), looping
+// over the Q tiles that attend to it. Per step, with everything transposed so that each operand the
+// CTA writes to shared memory is usable as stored:
+//     S^T  = K Q_i^T            dP^T = V dO_i^T                          (TMEM, 128 columns each)
+//     P^T  = exp2(S^T * c - LSE_q)      dS^T = P^T o (dP^T - delta_q)     (8 compute warps)
+//     dV  += P^T dO_i           dK  += dS^T Q_i                          (TMEM accumulators)
+//     dQ_i = (dS^T)^T K         (the dS^T tile read as an MN-major A operand; fresh accumulator)
+// dQ_i partial sums of the different K/V tiles are added into an fp32 buffer with vector reductions
+// and converted to bf16 afterwards. The scores of step i+1 are issued as soon as the compute warps
+// have pulled step i's S^T / dP^T into registers, so the tensor core works during the exponentials.
+// Compute warp w handles TMEM lane quarter (w & 3) and the column half ((w - 2) >> 2).
+struct BwdSmem {
   static constexpr int K = 0;
   static constexpr int V = K + TILE_BYTES;
   static constexpr int Q0 = V + TILE_BYTES;            // stage s: Q at Q0 + s*2*TILE, dO right after
@@ -391,26 +403,28 @@ struct BwdKvSmem {
   static constexpr int TOTAL = BARS + 256;
 };
 
-__global__ void __launch_bounds__(192, 1)
-attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                   const AttnParams p) {
+__global__ void __launch_bounds__(320, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned base
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_ARG);
     return;
   }
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdKvSmem::BARS);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdSmem::BARS);
   uint64_t* kv_full = bars;
-  uint64_t* q_full = bars + 1;   // [2]
-  uint64_t* q_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;   // S^T and dP^T ready
-  uint64_t* p_ready = bars + 6;  // P^T and dS^T published
-  uint64_t* acc_done = bars + 7; // dV/dK MMAs of the step finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* q_full = bars + 1;    // [2]  TMA bytes + the 256 threads that stage LSE / delta
+  uint64_t* q_empty = bars + 3;   // [2]
+  uint64_t* s_full = bars + 5;    // S^T and dP^T ready
+  uint64_t* s_free = bars + 6;    // ... and pulled into registers (8 warps)
+  uint64_t* p_ready = bars + 7;   // P^T and dS^T published
+  uint64_t* acc_done = bars + 8;  // dV / dK / dQ products of the step finished
+  uint64_t* dq_free = bars + 9;   // dQ accumulator drained (8 warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  float* stats = reinterpret_cast<float*>(smem + BwdKvSmem::STATS);
+  float* stats = reinterpret_cast<float*>(smem + BwdSmem::STATS);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -422,12 +436,14 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&q_full[s], 1 + 128);  // TMA tx + the 128 threads that stage LSE/delta
+      mbar_init(&q_full[s], 1 + 256);
       mbar_init(&q_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_ready, 128);
+    mbar_init(s_free, 8);
+    mbar_init(p_ready, 256);
     mbar_init(acc_done, 1);
+    mbar_init(dq_free, 8);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -439,13 +455,14 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tm_ST = tmem_base, tm_DPT = tmem_base + 128, tm_dV = tmem_base + 256, tm_dK = tmem_base + 320;
+  const uint32_t tm_ST = tmem_base, tm_DPT = tmem_base + 128, tm_dV = tmem_base + 256, tm_dK = tmem_base + 320,
+                 tm_dQ = tmem_base + 384;
 
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * TILE_BYTES);
-      tma_load_4d(smem + BwdKvSmem::K, &tmK, kv_full, 0, h, kv0, b);
-      tma_load_4d(smem + BwdKvSmem::V, &tmV, kv_full, 0, h, kv0, b);
+      tma_load_4d(smem + BwdSmem::K, &tmK, kv_full, 0, h, kv0, b);
+      tma_load_4d(smem + BwdSmem::V, &tmV, kv_full, 0, h, kv0, b);
       for (int it = 0; it < n_steps; ++it) {
         const int s = it & 1;
         if (!wait_or_abort(&q_empty[s], ((it >> 1) & 1) ^ 1, abort_flag)) {
@@ -453,7 +470,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           break;
         }
         mbar_expect_tx(&q_full[s], 2 * TILE_BYTES);
-        uint8_t* qdst = smem + BwdKvSmem::Q0 + s * 2 * TILE_BYTES;
+        uint8_t* qdst = smem + BwdSmem::Q0 + s * 2 * TILE_BYTES;
         const int qrow0 = (qt_begin + it) * 128;
         tma_load_4d(qdst, &tmQ, &q_full[s], 0, h, qrow0, b);
         tma_load_4d(qdst + TILE_BYTES, &tmdO, &q_full[s], 0, h, qrow0, b);
@@ -463,33 +480,41 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_g = make_idesc_bf16(128, 64, 0, 1);
-      const uint32_t k_addr = smem_u32(smem + BwdKvSmem::K), v_addr = smem_u32(smem + BwdKvSmem::V);
-      const uint32_t pt_addr = smem_u32(smem + BwdKvSmem::PT), dst_addr = smem_u32(smem + BwdKvSmem::DST);
-      bool ok = wait_or_abort(kv_full, 0, abort_flag);
-      if (!ok) raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+      constexpr uint32_t idesc_q = make_idesc_bf16(128, 64, 1, 1);
+      const uint32_t k_addr = smem_u32(smem + BwdSmem::K), v_addr = smem_u32(smem + BwdSmem::V);
+      const uint32_t pt_addr = smem_u32(smem + BwdSmem::PT), dst_addr = smem_u32(smem + BwdSmem::DST);
+      auto issue_scores = [&](int it) {
+        const uint32_t q_addr = smem_u32(smem + BwdSmem::Q0 + (it & 1) * 2 * TILE_BYTES);
+        const uint32_t do_addr = q_addr + TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_ss(tm_ST, make_smem_desc(k_addr + k * 32, 16, 1024), make_smem_desc(q_addr + k * 32, 16, 1024),
+                    idesc_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_ss(tm_DPT, make_smem_desc(v_addr + k * 32, 16, 1024), make_smem_desc(do_addr + k * 32, 16, 1024),
+                    idesc_s, k > 0);
+        tc_commit(s_full);
+      };
+      bool ok = n_steps > 0 && wait_or_abort(kv_full, 0, abort_flag) && wait_or_abort(&q_full[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0);
+      }
       for (int it = 0; ok && it < n_steps; ++it) {
         const int s = it & 1;
-        const uint32_t q_addr = smem_u32(smem + BwdKvSmem::Q0 + s * 2 * TILE_BYTES);
+        if (it + 1 < n_steps) {
+          ok = wait_or_abort(&q_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag) &&
+               wait_or_abort(s_free, it & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_scores(it + 1);
+        }
+        ok = wait_or_abort(p_ready, it & 1, abort_flag) && (it == 0 || wait_or_abort(dq_free, (it - 1) & 1, abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(smem + BwdSmem::Q0 + s * 2 * TILE_BYTES);
         const uint32_t do_addr = q_addr + TILE_BYTES;
-        if (!wait_or_abort(&q_full[s], (it >> 1) & 1, abort_flag)) {
-          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
-          break;
-        }
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ss(tm_ST, make_smem_desc(k_addr + k * 32, 16, 1024),
-                    make_smem_desc(q_addr + k * 32, 16, 1024), idesc_s, k > 0);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ss(tm_DPT, make_smem_desc(v_addr + k * 32, 16, 1024),
-                    make_smem_desc(do_addr + k * 32, 16, 1024), idesc_s, k > 0);
-        tc_commit(s_full);
-        if (!wait_or_abort(p_ready, it & 1, abort_flag)) {
-          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
-          break;
-        }
-        tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           tc_mma_ss(tm_dV, make_smem_desc(pt_addr + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
@@ -499,93 +524,149 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tc_mma_ss(tm_dK, make_smem_desc(dst_addr + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
                     make_smem_desc(q_addr + k * 2048, 8192, 1024), idesc_g, (it > 0 || k > 0));
         tc_commit(&q_empty[s]);
+        // dQ_i[q, d] = sum_kv dS^T[kv, q] K[kv, d]: both operands MN-major, 16 kv rows per instruction
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          tc_mma_ss(tm_dQ, make_smem_desc(dst_addr + k * 2048, TILE_BYTES, 1024),
+                    make_smem_desc(k_addr + k * 2048, 8192, 1024), idesc_q, k > 0);
         tc_commit(acc_done);
       }
+      if (!ok && n_steps > 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
     }
   } else {
     const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;  // kv row inside the tile == TMEM lane
+    const int half = (warp - 2) >> 2;
+    const int row = quarter * 32 + lane;  // TMEM lane: kv row for S^T/dP^T/dV/dK, q row for dQ
     const int kv_idx = kv0 + row;
-    const int tid = threadIdx.x - 64;     // 0..127
+    const int tid = threadIdx.x - 64;     // 0..255
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const long long bh = (long long)b * p.H + h;
     bool ok = true;
+
+    // add this warp's [32 q rows x 32 columns] of the finished dQ accumulator of Q tile `qt` to dq_acc
+    auto drain_dq = [&](int qt) {
+      uint32_t r[32];
+      tmem_ld_32x32(tm_dQ + lane_off + half * 32, r);
+      tmem_ld_wait();
+      tc_fence_before();
+      const int qi = qt * 128 + row;
+      if (qi < p.S) {
+        float* dst = p.dq_acc + (((long long)b * p.S + qi) * p.H + h) * 64 + half * 32;
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + g * 4),
+                       "f"(__uint_as_float(r[g * 4]) * p.scale), "f"(__uint_as_float(r[g * 4 + 1]) * p.scale),
+                       "f"(__uint_as_float(r[g * 4 + 2]) * p.scale), "f"(__uint_as_float(r[g * 4 + 3]) * p.scale)
+                       : "memory");
+      }
+    };
+
     for (int it = 0; it < n_steps; ++it) {
       const int s = it & 1;
       const int qrow0 = (qt_begin + it) * 128;
-      // stage LSE / delta of this Q tile (thread tid owns q row tid); the slot was last
-      // read two steps ago, and p_ready of that step has been passed by every thread.
-      {
-        const int qi = qrow0 + tid;
-        const long long off = ((long long)b * p.H + h) * p.S + qi;
+      {  // stage LSE (threads 0-127) / delta (128-255) of this Q tile
+        const int qi = qrow0 + (tid & 127);
         float* st = stats + s * 256;
-        st[tid] = qi < p.S ? p.LSE[off] : INFINITY;
-        st[128 + tid] = qi < p.S ? p.delta[off] : 0.f;
+        if (tid < 128) st[tid] = qi < p.S ? p.LSE[bh * p.S + qi] : INFINITY;
+        else st[tid] = qi < p.S ? p.delta[bh * p.S + qi] : 0.f;
         mbar_arrive(&q_full[s]);
       }
       if (!wait_or_abort(&q_full[s], (it >> 1) & 1, abort_flag) || !wait_or_abort(s_full, it & 1, abort_flag)) {
-        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
         ok = false;
         break;
       }
       tc_fence_after();
-      // P^T/dS^T buffers are free once the previous step's dV/dK MMAs are done.
-      if (it > 0 && !wait_or_abort(acc_done, (it - 1) & 1, abort_flag)) {
-        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
-        ok = false;
-        break;
-      }
-      const float* lse = stats + s * 256;
-      const float* dlt = lse + 128;
-      const bool diag = p.causal && (qt_begin + it == kt);
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float st_[32], dp[32];
-        tmem_ld_32x32f(tm_ST + lane_off + c * 32, st_);
-        tmem_ld_32x32f(tm_DPT + lane_off + c * 32, dp);
+      uint32_t sr[64], dr[64];
+      tmem_ld2_32x64_wait(tm_ST + lane_off + half * 64, tm_DPT + lane_off + half * 64, sr, dr);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);
+      const float4* lse4 = reinterpret_cast<const float4*>(stats + s * 256 + half * 64);
+      const float4* dlt4 = reinterpret_cast<const float4*>(stats + s * 256 + 128 + half * 64);
+      const bool need_mask = (p.causal && qt_begin + it == kt) || (kv0 + 128 > p.S);
+      uint32_t pp[32], dd[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qc = c * 32 + i;
-          const int qi = qrow0 + qc;
-          const bool dead = (diag && qi < kv_idx) || kv_idx >= p.S;
-          const float pv = dead ? 0.f : exp2f(st_[i] * p.scale_log2 - lse[qc]);
-          st_[i] = pv;
-          dp[i] = pv * (dp[i] - dlt[qc]);
+      for (int g = 0; g < 16; ++g) {
+        const float4 l4 = lse4[g], d4 = dlt4[g];
+        const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+        float pv[4], ds[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = g * 4 + k;
+          float e = exp2f(fmaf(__uint_as_float(sr[c]), p.scale_log2, -lv[k]));
+          if (need_mask) {
+            const int qi = qrow0 + half * 64 + c;
+            if ((p.causal && qi < kv_idx) || kv_idx >= p.S) e = 0.f;
+          }
+          pv[k] = e;
+          ds[k] = e * (__uint_as_float(dr[c]) - dv[k]);
         }
-        store_row_chunk_sw128(smem + BwdKvSmem::PT, row, c * 32, st_);
-        store_row_chunk_sw128(smem + BwdKvSmem::DST, row, c * 32, dp);
+        __nv_bfloat162 a0 = __floats2bfloat162_rn(pv[0], pv[1]), a1 = __floats2bfloat162_rn(pv[2], pv[3]);
+        __nv_bfloat162 b0 = __floats2bfloat162_rn(ds[0], ds[1]), b1 = __floats2bfloat162_rn(ds[2], ds[3]);
+        pp[g * 2] = *reinterpret_cast<uint32_t*>(&a0);
+        pp[g * 2 + 1] = *reinterpret_cast<uint32_t*>(&a1);
+        dd[g * 2] = *reinterpret_cast<uint32_t*>(&b0);
+        dd[g * 2 + 1] = *reinterpret_cast<uint32_t*>(&b1);
+      }
+      if (it > 0) {
+        // the previous step's products are done: its dQ can be drained and P^T / dS^T overwritten
+        if (!wait_or_abort(acc_done, (it - 1) & 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        drain_dq(qt_begin + it - 1);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_free);
+      }
+      uint8_t* pt = smem + BwdSmem::PT + half * TILE_BYTES;
+      uint8_t* dt = smem + BwdSmem::DST + half * TILE_BYTES;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint32_t off = sw128_offset(row, c);
+        *reinterpret_cast<uint4*>(pt + off) = make_uint4(pp[c * 4], pp[c * 4 + 1], pp[c * 4 + 2], pp[c * 4 + 3]);
+        *reinterpret_cast<uint4*>(dt + off) = make_uint4(dd[c * 4], dd[c * 4 + 1], dd[c * 4 + 2], dd[c * 4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_ready);
     }
+    if (!ok && lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
     if (ok && n_steps > 0) {
       if (wait_or_abort(acc_done, (n_steps - 1) & 1, abort_flag)) {
         tc_fence_after();
+        drain_dq(qt_begin + n_steps - 1);
         // tcgen05.ld is warp-collective: every lane loads, only in-range rows store.
         const bool live = kv_idx < p.S;
-        const long long roff = (((long long)b * p.S + (live ? kv_idx : 0)) * 3 * p.H + h) * 64;
+        const long long roff = (((long long)b * p.S + (live ? kv_idx : 0)) * 3 * p.H + h) * 64 + half * 32;
+        uint32_t r[32];
+        tmem_ld_32x32(tm_dV + lane_off + half * 32, r);
+        tmem_ld_wait();
+        if (live) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          float f[32];
-          tmem_ld_32x32f(tm_dV + lane_off + c * 32, f);
-          if (live) {
+          for (int g = 0; g < 4; ++g) {
+            uint32_t pk[4];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              __align__(16) bf16 t[8];
-#pragma unroll
-              for (int k = 0; k < 8; ++k) t[k] = __float2bfloat16(f[g * 8 + k]);
-              *reinterpret_cast<uint4*>(p.dV + roff + c * 32 + g * 8) = *reinterpret_cast<uint4*>(t);
+            for (int k = 0; k < 4; ++k) {
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * k]), __uint_as_float(r[g * 8 + 2 * k + 1]));
+              pk[k] = *reinterpret_cast<uint32_t*>(&h2);
             }
+            *reinterpret_cast<uint4*>(p.dV + roff + g * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
           }
-          tmem_ld_32x32f(tm_dK + lane_off + c * 32, f);
-          if (live) {
+        }
+        tmem_ld_32x32(tm_dK + lane_off + half * 32, r);
+        tmem_ld_wait();
+        if (live) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              __align__(16) bf16 t[8];
+          for (int g = 0; g < 4; ++g) {
+            uint32_t pk[4];
 #pragma unroll
-              for (int k = 0; k < 8; ++k) t[k] = __float2bfloat16(f[g * 8 + k] * p.scale);
-              *reinterpret_cast<uint4*>(p.dK + roff + c * 32 + g * 8) = *reinterpret_cast<uint4*>(t);
+            for (int k = 0; k < 4; ++k) {
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * k]) * p.scale,
+                                                         __uint_as_float(r[g * 8 + 2 * k + 1]) * p.scale);
+              pk[k] = *reinterpret_cast<uint32_t*>(&h2);
             }
+            *reinterpret_cast<uint4*>(p.dK + roff + g * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
           }
         }
       } else if (lane == 0) {
@@ -593,9 +674,9 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     } else if (ok && kv_idx < p.S) {
       // no Q tile attends to this K/V tile: gradients are zero
-      const long long roff = (((long long)b * p.S + kv_idx) * 3 * p.H + h) * 64;
+      const long long roff = (((long long)b * p.S + kv_idx) * 3 * p.H + h) * 64 + half * 32;
       const uint4 z = make_uint4(0, 0, 0, 0);
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         *reinterpret_cast<uint4*>(p.dV + roff + c * 8) = z;
         *reinterpret_cast<uint4*>(p.dK + roff + c * 8) = z;
       }
@@ -610,192 +691,19 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
-// --------------------------------------------------------------- backward dQ
-struct BwdQSmem {
-  static constexpr int Q = 0;
-  static constexpr int DO = Q + TILE_BYTES;
-  static constexpr int K0 = DO + TILE_BYTES;           // stage s: K at K0 + s*2*TILE, V right after
-  static constexpr int DS = K0 + 4 * TILE_BYTES;       // dS [128 q x 128 kv]
-  static constexpr int BARS = DS + 2 * TILE_BYTES;
-  static constexpr int TOTAL = BARS + 256;
-};
-
-__global__ void __launch_bounds__(192, 1)
-attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                  const AttnParams p) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = smem_raw;
-  if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned base
-    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_ARG);
-    return;
-  }
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdQSmem::BARS);
-  uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_ready = bars + 6;
-  uint64_t* acc_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
-  volatile uint32_t* abort_flag = tmem_slot + 1;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int q0 = qt * 128;
-  const int n_kv_all = (p.S + 127) / 128;
-  const int n_kv = p.causal ? min(qt + 1, n_kv_all) : n_kv_all;
-
-  if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
-    }
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, 128);
-    mbar_init(acc_done, 1);
-    *abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tm_S = tmem_base, tm_DP = tmem_base + 128, tm_dQ = tmem_base + 256;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(q_full, 2 * TILE_BYTES);
-      tma_load_4d(smem + BwdQSmem::Q, &tmQ, q_full, 0, h, q0, b);
-      tma_load_4d(smem + BwdQSmem::DO, &tmdO, q_full, 0, h, q0, b);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        if (!wait_or_abort(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) {
-          raise_abort(p.status, abort_flag, ST_TIMEOUT_PRODUCER);
-          break;
-        }
-        mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
-        uint8_t* kdst = smem + BwdQSmem::K0 + s * 2 * TILE_BYTES;
-        tma_load_4d(kdst, &tmK, &kv_full[s], 0, h, j * 128, b);
-        tma_load_4d(kdst + TILE_BYTES, &tmV, &kv_full[s], 0, h, j * 128, b);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_g = make_idesc_bf16(128, 64, 0, 1);
-      const uint32_t q_addr = smem_u32(smem + BwdQSmem::Q), do_addr = smem_u32(smem + BwdQSmem::DO);
-      const uint32_t ds_addr = smem_u32(smem + BwdQSmem::DS);
-      bool ok = wait_or_abort(q_full, 0, abort_flag);
-      if (!ok) raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
-      for (int j = 0; ok && j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t k_addr = smem_u32(smem + BwdQSmem::K0 + s * 2 * TILE_BYTES);
-        const uint32_t v_addr = k_addr + TILE_BYTES;
-        if (!wait_or_abort(&kv_full[s], (j >> 1) & 1, abort_flag)) {
-          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
-          break;
-        }
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ss(tm_S, make_smem_desc(q_addr + k * 32, 16, 1024),
-                    make_smem_desc(k_addr + k * 32, 16, 1024), idesc_s, k > 0);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ss(tm_DP, make_smem_desc(do_addr + k * 32, 16, 1024),
-                    make_smem_desc(v_addr + k * 32, 16, 1024), idesc_s, k > 0);
-        tc_commit(s_full);
-        if (!wait_or_abort(p_ready, j & 1, abort_flag)) {
-          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
-          break;
-        }
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          tc_mma_ss(tm_dQ, make_smem_desc(ds_addr + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
-                    make_smem_desc(k_addr + k * 2048, 8192, 1024), idesc_g, (j > 0 || k > 0));
-        tc_commit(&kv_empty[s]);
-        tc_commit(acc_done);
-      }
-    }
-  } else {
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const int q_idx = q0 + row;
-    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    const long long soff = ((long long)b * p.H + h) * p.S + q_idx;
-    const float lse = q_idx < p.S ? p.LSE[soff] : INFINITY;
-    const float dlt = q_idx < p.S ? p.delta[soff] : 0.f;
-    bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      if (!wait_or_abort(s_full, j & 1, abort_flag)) {
-        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      if (j > 0 && !wait_or_abort(acc_done, (j - 1) & 1, abort_flag)) {
-        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
-        ok = false;
-        break;
-      }
-      const int kv0 = j * 128;
-      const bool need_mask = (p.causal && j == qt) || (kv0 + 128 > p.S);
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float sv[32], dp[32];
-        tmem_ld_32x32f(tm_S + lane_off + c * 32, sv);
-        tmem_ld_32x32f(tm_DP + lane_off + c * 32, dp);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv = kv0 + c * 32 + i;
-          const bool dead = need_mask && ((p.causal && kv > q_idx) || kv >= p.S);
-          const float pv = dead ? 0.f : exp2f(sv[i] * p.scale_log2 - lse);
-          dp[i] = pv * (dp[i] - dlt);
-        }
-        store_row_chunk_sw128(smem + BwdQSmem::DS, row, c * 32, dp);
-      }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(p_ready);
-    }
-    if (ok && n_kv > 0) {
-      if (wait_or_abort(acc_done, (n_kv - 1) & 1, abort_flag)) {
-        tc_fence_after();
-        const bool live = q_idx < p.S;
-        const long long roff = (((long long)b * p.S + (live ? q_idx : 0)) * 3 * p.H + h) * 64;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          float f[32];
-          tmem_ld_32x32f(tm_dQ + lane_off + c * 32, f);
-          if (live) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              __align__(16) bf16 t[8];
-#pragma unroll
-              for (int k = 0; k < 8; ++k) t[k] = __float2bfloat16(f[g * 8 + k] * p.scale);
-              *reinterpret_cast<uint4*>(p.dQ + roff + c * 32 + g * 8) = *reinterpret_cast<uint4*>(t);
-            }
-          }
-        }
-      } else if (lane == 0) {
-        raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
-      }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+// dQ: fp32 accumulator [B*S, E] -> bf16 rows of pitch 3E inside dqkv. Eight elements per thread.
+__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, long long rows, int E) {
+  const long long per_row = E / 8;
+  const long long total = rows * per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / per_row, c = (i - r * per_row) * 8;
+    const float4 a = *reinterpret_cast<const float4*>(acc + r * E + c);
+    const float4 b2 = *reinterpret_cast<const float4*>(acc + r * E + c + 4);
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(a.x, a.y), h1 = __floats2bfloat162_rn(a.z, a.w);
+    __nv_bfloat162 h2 = __floats2bfloat162_rn(b2.x, b2.y), h3 = __floats2bfloat162_rn(b2.z, b2.w);
+    *reinterpret_cast<uint4*>(dq + r * 3 * E + c) =
+        make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1), *reinterpret_cast<uint32_t*>(&h2),
+                   *reinterpret_cast<uint32_t*>(&h3));
   }
 }
 
@@ -850,11 +758,12 @@ int tnnb_attn_fwd(const void* qkv, void* out, void* lse, int B, int S, int H, in
   return e == cudaSuccess ? 0 : -(int)e - 1000;
 }
 
-// dqkv: [B,S,3,H,64] bf16 (fully overwritten); delta: [B,H,S] fp32 scratch owned by the caller.
-int tnnb_attn_bwd(const void* qkv, const void* out, const void* dout, const void* lse, void* delta, void* dqkv,
-                  int B, int S, int H, int D, int causal, float scale, int* status, void* stream) {
+// dqkv: [B,S,3,H,64] bf16 (fully overwritten); delta: [B,H,S] fp32 and dq_acc: [B,S,H,64] fp32 are
+// scratch owned by the caller (dq_acc is zeroed here).
+int tnnb_attn_bwd(const void* qkv, const void* out, const void* dout, const void* lse, void* delta, void* dq_acc,
+                  void* dqkv, int B, int S, int H, int D, int causal, float scale, int* status, void* stream) {
   if (D != 64) return -7;
-  if (((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)dout | (uintptr_t)dqkv) & 15) return -4;
+  if (((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)dout | (uintptr_t)dqkv | (uintptr_t)dq_acc) & 15) return -4;
   cudaStream_t st = (cudaStream_t)stream;
   const long long E = (long long)H * 64;
   const bf16* base = (const bf16*)qkv;
@@ -870,22 +779,23 @@ int tnnb_attn_bwd(const void* qkv, const void* out, const void* dout, const void
   p.scale_log2 = scale * 1.4426950408889634f;
   p.LSE = (float*)lse;
   p.delta = (const float*)delta;
+  p.dq_acc = (float*)dq_acc;
   p.dQ = (bf16*)dqkv;
   p.dK = (bf16*)dqkv + E;
   p.dV = (bf16*)dqkv + 2 * E;
   p.status = status;
   static bool once = false;
   if (!once) {
-    if ((rc = set_smem(attn_bwd_kv_kernel, BwdKvSmem::TOTAL))) return rc;
-    if ((rc = set_smem(attn_bwd_q_kernel, BwdQSmem::TOTAL))) return rc;
+    if ((rc = set_smem(attn_bwd_kernel, BwdSmem::TOTAL))) return rc;
     once = true;
   }
   const long long rows = (long long)B * S * H;
+  cudaMemsetAsync(dq_acc, 0, sizeof(float) * (size_t)B * S * E, st);
   int g = (int)((rows + 7) / 8 > 148 * 8 ? 148 * 8 : (rows + 7) / 8);
   attn_delta_kernel<<<g, 256, 0, st>>>((const bf16*)out, (const bf16*)dout, (float*)delta, B, S, H);
   dim3 grid((S + 127) / 128, H, B);
-  attn_bwd_kv_kernel<<<grid, 192, BwdKvSmem::TOTAL, st>>>(tq, tk, tv, tdo, p);
-  attn_bwd_q_kernel<<<grid, 192, BwdQSmem::TOTAL, st>>>(tq, tk, tv, tdo, p);
+  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, st>>>(tq, tk, tv, tdo, p);
+  attn_dq_convert_kernel<<<148 * 4, 256, 0, st>>>((const float*)dq_acc, (bf16*)dqkv, (long long)B * S, (int)E);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
 }

@@ -83,7 +83,7 @@ def _declare(lib):
                           c_void_p])
     sig("tnnb_attn_fwd", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                           c_void_p])
-    sig("tnnb_attn_bwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+    sig("tnnb_attn_bwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                           c_int, c_float, c_void_p, c_void_p])
 
 

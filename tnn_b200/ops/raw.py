@@ -368,11 +368,12 @@ def attn_bwd(qkv: torch.Tensor, out: torch.Tensor, dout: torch.Tensor, lse: torc
         dout = dout.contiguous()
         dqkv = torch.empty_like(qkv)
         delta = torch.empty(B, H, S, dtype=torch.float32, device=qkv.device)
+        dq_acc = torch.empty(B * S, E, dtype=torch.float32, device=qkv.device)  # zeroed by the entry point
         rc = _lib.load().tnnb_attn_bwd(_lib.ptr(qkv), _lib.ptr(out), _lib.ptr(dout), _lib.ptr(lse), _lib.ptr(delta),
-                                       _lib.ptr(dqkv), B, S, H, D, int(causal), scale,
+                                       _lib.ptr(dq_acc), _lib.ptr(dqkv), B, S, H, D, int(causal), scale,
                                        _lib.ptr(_lib.status_word(qkv.device)), _lib.stream())
         _lib.check_rc(rc, "attn_bwd")
-        _count(3)
+        _count(3)  # delta, fused dK/dV/dQ, dQ conversion (plus one memset node)
         return dqkv
     q, k, v = (t.reshape(B, S, H, D).permute(0, 2, 1, 3).float() for t in qkv.reshape(B * S, 3, E).unbind(1))
     do = dout.reshape(B, S, H, D).permute(0, 2, 1, 3).float()
