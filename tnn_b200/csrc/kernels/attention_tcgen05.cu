@@ -49,6 +49,14 @@ struct AttnParams {
 
 static constexpr int TILE_BYTES = 128 * 64 * 2;  // one [128 x 64] bf16 tile
 
+#ifdef TNNB_TRACE
+// Debug builds only: per-phase clock64 stamps of CTA (0,0,0), compute warp 2 lane 0 and the MMA thread.
+__device__ long long g_trace[2][512];
+#define TRACE(who, idx) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 512) g_trace[who][idx] = clock64(); } while (0)
+#else
+#define TRACE(who, idx) do { } while (0)
+#endif
+
 __device__ __forceinline__ void tmem_ld_32x32f(uint32_t taddr, float (&f)[32]) {
   uint32_t r[32];
   tmem_ld_32x32(taddr, r);
@@ -395,18 +403,21 @@ __global__ void attn_delta_kernel(const bf16* __restrict__ O, const bf16* __rest
 struct BwdSmem {
   static constexpr int K = 0;
   static constexpr int V = K + TILE_BYTES;
-  static constexpr int Q0 = V + TILE_BYTES;            // stage s: Q at Q0 + s*2*TILE, dO right after
-  static constexpr int PT = Q0 + 4 * TILE_BYTES;       // P^T  [128 kv x 128 q]
-  static constexpr int DST = PT + 2 * TILE_BYTES;      // dS^T [128 kv x 128 q]
-  static constexpr int STATS = DST + 2 * TILE_BYTES;   // [2 stages][2][128] fp32: LSE, delta
+  static constexpr int QSTAGES = 3;
+  static constexpr int Q0 = V + TILE_BYTES;                  // stage s: Q at Q0 + s*2*TILE, dO right after
+  static constexpr int PT = Q0 + QSTAGES * 2 * TILE_BYTES;   // P^T  [128 kv x 128 q]
+  static constexpr int DST = PT + 2 * TILE_BYTES;            // dS^T [128 kv x 128 q]
+  static constexpr int DQS = DST + 2 * TILE_BYTES;           // per compute warp: [32 rows x 32 fp32] dQ staging tile
+  static constexpr int STATS = DQS + 8 * 4096;               // [2 slots][2][128] fp32: LSE, delta (slot = step parity)
   static constexpr int BARS = STATS + 2 * 2 * 128 * 4;
   static constexpr int TOTAL = BARS + 256;
+  static_assert(TOTAL <= 232448, "exceeds the 227 KB of dynamic shared memory a CTA may use");
 };
 
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                const AttnParams p) {
+                const __grid_constant__ CUtensorMap tmDQ, const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned base
@@ -415,14 +426,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdSmem::BARS);
   uint64_t* kv_full = bars;
-  uint64_t* q_full = bars + 1;    // [2]  TMA bytes + the 256 threads that stage LSE / delta
-  uint64_t* q_empty = bars + 3;   // [2]
-  uint64_t* s_full = bars + 5;    // S^T and dP^T ready
-  uint64_t* s_free = bars + 6;    // ... and pulled into registers (8 warps)
-  uint64_t* p_ready = bars + 7;   // P^T and dS^T published
-  uint64_t* acc_done = bars + 8;  // dV / dK / dQ products of the step finished
-  uint64_t* dq_free = bars + 9;   // dQ accumulator drained (8 warps)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  constexpr int QS = BwdSmem::QSTAGES;
+  uint64_t* q_full = bars + 1;    // [QS]  TMA bytes of Q_i and dO_i
+  uint64_t* q_empty = bars + 4;   // [QS]
+  uint64_t* s_full = bars + 7;    // S^T and dP^T ready
+  uint64_t* s_free = bars + 8;    // ... and pulled into registers (8 warps)
+  uint64_t* p_ready = bars + 9;   // P^T and dS^T published
+  uint64_t* acc_done = bars + 10; // dV / dK / dQ products of the step finished
+  uint64_t* dq_free = bars + 11;  // dQ accumulator drained (8 warps)
+  uint64_t* st_full = bars + 12;  // [2]  LSE / delta of the step staged by the 256 compute threads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   float* stats = reinterpret_cast<float*>(smem + BwdSmem::STATS);
 
@@ -435,8 +448,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&q_full[s], 1 + 256);
+    for (int s = 0; s < QS; ++s) {
+      mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
     }
     mbar_init(s_full, 1);
@@ -444,6 +457,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(p_ready, 256);
     mbar_init(acc_done, 1);
     mbar_init(dq_free, 8);
+    mbar_init(&st_full[0], 256);
+    mbar_init(&st_full[1], 256);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -464,8 +479,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tma_load_4d(smem + BwdSmem::K, &tmK, kv_full, 0, h, kv0, b);
       tma_load_4d(smem + BwdSmem::V, &tmV, kv_full, 0, h, kv0, b);
       for (int it = 0; it < n_steps; ++it) {
-        const int s = it & 1;
-        if (!wait_or_abort(&q_empty[s], ((it >> 1) & 1) ^ 1, abort_flag)) {
+        const int s = it % QS;
+        if (!wait_or_abort(&q_empty[s], ((it / QS) & 1) ^ 1, abort_flag)) {
           raise_abort(p.status, abort_flag, ST_TIMEOUT_PRODUCER);
           break;
         }
@@ -484,7 +499,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t k_addr = smem_u32(smem + BwdSmem::K), v_addr = smem_u32(smem + BwdSmem::V);
       const uint32_t pt_addr = smem_u32(smem + BwdSmem::PT), dst_addr = smem_u32(smem + BwdSmem::DST);
       auto issue_scores = [&](int it) {
-        const uint32_t q_addr = smem_u32(smem + BwdSmem::Q0 + (it & 1) * 2 * TILE_BYTES);
+        const uint32_t q_addr = smem_u32(smem + BwdSmem::Q0 + (it % QS) * 2 * TILE_BYTES);
         const uint32_t do_addr = q_addr + TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
@@ -502,17 +517,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         issue_scores(0);
       }
       for (int it = 0; ok && it < n_steps; ++it) {
-        const int s = it & 1;
+        const int s = it % QS;
         if (it + 1 < n_steps) {
-          ok = wait_or_abort(&q_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag) &&
+          ok = wait_or_abort(&q_full[(it + 1) % QS], ((it + 1) / QS) & 1, abort_flag) &&
                wait_or_abort(s_free, it & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
+          TRACE(1, it * 8 + 0);
           issue_scores(it + 1);
         }
+        TRACE(1, it * 8 + 1);
         ok = wait_or_abort(p_ready, it & 1, abort_flag) && (it == 0 || wait_or_abort(dq_free, (it - 1) & 1, abort_flag));
         if (!ok) break;
         tc_fence_after();
+        TRACE(1, it * 8 + 2);
         const uint32_t q_addr = smem_u32(smem + BwdSmem::Q0 + s * 2 * TILE_BYTES);
         const uint32_t do_addr = q_addr + TILE_BYTES;
 #pragma unroll
@@ -530,6 +548,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tc_mma_ss(tm_dQ, make_smem_desc(dst_addr + k * 2048, TILE_BYTES, 1024),
                     make_smem_desc(k_addr + k * 2048, 8192, 1024), idesc_q, k > 0);
         tc_commit(acc_done);
+        TRACE(1, it * 8 + 3);
       }
       if (!ok && n_steps > 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
     }
@@ -543,71 +562,93 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const long long bh = (long long)b * p.H + h;
     bool ok = true;
 
-    // add this warp's [32 q rows x 32 columns] of the finished dQ accumulator of Q tile `qt` to dq_acc
-    auto drain_dq = [&](int qt) {
+    // Add this warp's [32 q rows x 32 columns] of the finished dQ accumulator of Q tile `qt` into the fp32
+    // buffer: registers -> swizzled staging tile of the warp -> one TMA reduce (rows past S are clipped).
+    uint8_t* dq_stage = smem + BwdSmem::DQS + (warp - 2) * 4096;
+    auto drain_stage = [&]() {  // TMEM -> registers -> staging tile (no fence yet)
+      if (lane == 0) bulk_wait_group_read0();  // the warp's previous reduce has consumed the staging tile
+      __syncwarp();
       uint32_t r[32];
       tmem_ld_32x32(tm_dQ + lane_off + half * 32, r);
       tmem_ld_wait();
       tc_fence_before();
-      const int qi = qt * 128 + row;
-      if (qi < p.S) {
-        float* dst = p.dq_acc + (((long long)b * p.S + qi) * p.H + h) * 64 + half * 32;
 #pragma unroll
-        for (int g = 0; g < 8; ++g)
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + g * 4),
-                       "f"(__uint_as_float(r[g * 4]) * p.scale), "f"(__uint_as_float(r[g * 4 + 1]) * p.scale),
-                       "f"(__uint_as_float(r[g * 4 + 2]) * p.scale), "f"(__uint_as_float(r[g * 4 + 3]) * p.scale)
-                       : "memory");
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<float4*>(dq_stage + sw128_offset(lane, c)) =
+            make_float4(__uint_as_float(r[c * 4]) * p.scale, __uint_as_float(r[c * 4 + 1]) * p.scale,
+                        __uint_as_float(r[c * 4 + 2]) * p.scale, __uint_as_float(r[c * 4 + 3]) * p.scale);
+    };
+    auto drain_issue = [&](int qt) {  // after every lane's fence.proxy.async
+      __syncwarp();
+      if (lane == 0) {
+        tma_reduce_add_4d(&tmDQ, dq_stage, half * 32, h, qt * 128 + quarter * 32, b);
+        bulk_commit_group();
       }
     };
 
+    // LSE (threads 0-127) / delta (128-255) of a Q tile, fetched one step ahead
+    auto load_stat = [&](int it) -> float {
+      const int qi = (qt_begin + it) * 128 + (tid & 127);
+      if (tid < 128) return qi < p.S ? p.LSE[bh * p.S + qi] : INFINITY;
+      return qi < p.S ? p.delta[bh * p.S + qi] : 0.f;
+    };
+    float stat_next = n_steps > 0 ? load_stat(0) : 0.f;
+
     for (int it = 0; it < n_steps; ++it) {
-      const int s = it & 1;
       const int qrow0 = (qt_begin + it) * 128;
-      {  // stage LSE (threads 0-127) / delta (128-255) of this Q tile
-        const int qi = qrow0 + (tid & 127);
-        float* st = stats + s * 256;
-        if (tid < 128) st[tid] = qi < p.S ? p.LSE[bh * p.S + qi] : INFINITY;
-        else st[tid] = qi < p.S ? p.delta[bh * p.S + qi] : 0.f;
-        mbar_arrive(&q_full[s]);
-      }
-      if (!wait_or_abort(&q_full[s], (it >> 1) & 1, abort_flag) || !wait_or_abort(s_full, it & 1, abort_flag)) {
+      if (warp == 2 && lane == 0) TRACE(0, it * 8 + 0);
+      stats[(it & 1) * 256 + tid] = stat_next;
+      mbar_arrive(&st_full[it & 1]);
+      if (it + 1 < n_steps) stat_next = load_stat(it + 1);
+      if (!wait_or_abort(&st_full[it & 1], (it >> 1) & 1, abort_flag) || !wait_or_abort(s_full, it & 1, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after();
+      if (warp == 2 && lane == 0) TRACE(0, it * 8 + 1);
       uint32_t sr[64], dr[64];
       tmem_ld2_32x64_wait(tm_ST + lane_off + half * 64, tm_DPT + lane_off + half * 64, sr, dr);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
-      const float4* lse4 = reinterpret_cast<const float4*>(stats + s * 256 + half * 64);
-      const float4* dlt4 = reinterpret_cast<const float4*>(stats + s * 256 + 128 + half * 64);
+      if (warp == 2 && lane == 0) TRACE(0, it * 8 + 2);
+      const float4* lse4 = reinterpret_cast<const float4*>(stats + (it & 1) * 256 + half * 64);
+      const float4* dlt4 = reinterpret_cast<const float4*>(stats + (it & 1) * 256 + 128 + half * 64);
       const bool need_mask = (p.causal && qt_begin + it == kt) || (kv0 + 128 > p.S);
+      // phase 1: exponent arguments (in place), phase 2: 64 independent exponentials, phase 3: dS and packing.
+      // Keeping the phases apart gives the scheduler long runs of independent instructions per pipe.
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {
+        const float4 l4 = lse4[g];
+        sr[g * 4 + 0] = __float_as_uint(fmaf(__uint_as_float(sr[g * 4 + 0]), p.scale_log2, -l4.x));
+        sr[g * 4 + 1] = __float_as_uint(fmaf(__uint_as_float(sr[g * 4 + 1]), p.scale_log2, -l4.y));
+        sr[g * 4 + 2] = __float_as_uint(fmaf(__uint_as_float(sr[g * 4 + 2]), p.scale_log2, -l4.z));
+        sr[g * 4 + 3] = __float_as_uint(fmaf(__uint_as_float(sr[g * 4 + 3]), p.scale_log2, -l4.w));
+      }
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int qi = qrow0 + half * 64 + c;
+          if ((p.causal && qi < kv_idx) || kv_idx >= p.S) sr[c] = 0xff800000u;  // exp2(-inf) = 0
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 64; ++c) sr[c] = __float_as_uint(exp2f(__uint_as_float(sr[c])));
       uint32_t pp[32], dd[32];
 #pragma unroll
       for (int g = 0; g < 16; ++g) {
-        const float4 l4 = lse4[g], d4 = dlt4[g];
-        const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
-        float pv[4], ds[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int c = g * 4 + k;
-          float e = exp2f(fmaf(__uint_as_float(sr[c]), p.scale_log2, -lv[k]));
-          if (need_mask) {
-            const int qi = qrow0 + half * 64 + c;
-            if ((p.causal && qi < kv_idx) || kv_idx >= p.S) e = 0.f;
-          }
-          pv[k] = e;
-          ds[k] = e * (__uint_as_float(dr[c]) - dv[k]);
-        }
-        __nv_bfloat162 a0 = __floats2bfloat162_rn(pv[0], pv[1]), a1 = __floats2bfloat162_rn(pv[2], pv[3]);
-        __nv_bfloat162 b0 = __floats2bfloat162_rn(ds[0], ds[1]), b1 = __floats2bfloat162_rn(ds[2], ds[3]);
+        const float4 d4 = dlt4[g];
+        const float e0 = __uint_as_float(sr[g * 4]), e1 = __uint_as_float(sr[g * 4 + 1]), e2 = __uint_as_float(sr[g * 4 + 2]),
+                    e3 = __uint_as_float(sr[g * 4 + 3]);
+        __nv_bfloat162 a0 = __floats2bfloat162_rn(e0, e1), a1 = __floats2bfloat162_rn(e2, e3);
+        __nv_bfloat162 b0 = __floats2bfloat162_rn(e0 * (__uint_as_float(dr[g * 4]) - d4.x), e1 * (__uint_as_float(dr[g * 4 + 1]) - d4.y));
+        __nv_bfloat162 b1 = __floats2bfloat162_rn(e2 * (__uint_as_float(dr[g * 4 + 2]) - d4.z), e3 * (__uint_as_float(dr[g * 4 + 3]) - d4.w));
         pp[g * 2] = *reinterpret_cast<uint32_t*>(&a0);
         pp[g * 2 + 1] = *reinterpret_cast<uint32_t*>(&a1);
         dd[g * 2] = *reinterpret_cast<uint32_t*>(&b0);
         dd[g * 2 + 1] = *reinterpret_cast<uint32_t*>(&b1);
       }
+      if (warp == 2 && lane == 0) TRACE(0, it * 8 + 3);
       if (it > 0) {
         // the previous step's products are done: its dQ can be drained and P^T / dS^T overwritten
         if (!wait_or_abort(acc_done, (it - 1) & 1, abort_flag)) {
@@ -615,10 +656,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           break;
         }
         tc_fence_after();
-        drain_dq(qt_begin + it - 1);
+        if (warp == 2 && lane == 0) TRACE(0, it * 8 + 4);
+        drain_stage();
         __syncwarp();
         if (lane == 0) mbar_arrive(dq_free);
       }
+      if (warp == 2 && lane == 0) TRACE(0, it * 8 + 5);
       uint8_t* pt = smem + BwdSmem::PT + half * TILE_BYTES;
       uint8_t* dt = smem + BwdSmem::DST + half * TILE_BYTES;
 #pragma unroll
@@ -627,15 +670,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         *reinterpret_cast<uint4*>(pt + off) = make_uint4(pp[c * 4], pp[c * 4 + 1], pp[c * 4 + 2], pp[c * 4 + 3]);
         *reinterpret_cast<uint4*>(dt + off) = make_uint4(dd[c * 4], dd[c * 4 + 1], dd[c * 4 + 2], dd[c * 4 + 3]);
       }
-      fence_proxy_async_smem();
+      fence_proxy_async_smem();  // covers the dQ staging tile as well as P^T / dS^T
       tc_fence_before();
       mbar_arrive(p_ready);
+      if (it > 0) drain_issue(qt_begin + it - 1);
+      if (warp == 2 && lane == 0) TRACE(0, it * 8 + 6);
     }
-    if (!ok && lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+    if (!ok && lane == 0) {
+      raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+      bulk_wait_group0();
+    }
     if (ok && n_steps > 0) {
       if (wait_or_abort(acc_done, (n_steps - 1) & 1, abort_flag)) {
         tc_fence_after();
-        drain_dq(qt_begin + n_steps - 1);
+        drain_stage();
+        fence_proxy_async_smem();
+        drain_issue(qt_begin + n_steps - 1);
         // tcgen05.ld is warp-collective: every lane loads, only in-range rows store.
         const bool live = kv_idx < p.S;
         const long long roff = (((long long)b * p.S + (live ? kv_idx : 0)) * 3 * p.H + h) * 64 + half * 32;
@@ -672,6 +722,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       } else if (lane == 0) {
         raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
       }
+      if (lane == 0) bulk_wait_group0();  // the staging tile must outlive the last reduce
     } else if (ok && kv_idx < p.S) {
       // no Q tile attends to this K/V tile: gradients are zero
       const long long roff = (((long long)b * p.S + kv_idx) * 3 * p.H + h) * 64 + half * 32;
@@ -773,6 +824,13 @@ int tnnb_attn_bwd(const void* qkv, const void* out, const void* dout, const void
   if ((rc = make_head_map(&tk, base + E, B, S, H, 3 * E))) return rc;
   if ((rc = make_head_map(&tv, base + 2 * E, B, S, H, 3 * E))) return rc;
   if ((rc = make_head_map(&tdo, dout, B, S, H, E))) return rc;
+  CUtensorMap tdq;
+  {
+    uint64_t dims[4] = {64, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+    uint64_t str[3] = {64 * 4, (uint64_t)E * 4, (uint64_t)E * 4 * (uint64_t)S};
+    uint32_t box[4] = {32, 1, 32, 1};
+    if ((rc = encode_tmap_f32(&tdq, dq_acc, 4, dims, str, box))) return rc;
+  }
   AttnParams p{};
   p.B = B; p.S = S; p.H = H; p.causal = causal;
   p.scale = scale;
@@ -794,10 +852,17 @@ int tnnb_attn_bwd(const void* qkv, const void* out, const void* dout, const void
   int g = (int)((rows + 7) / 8 > 148 * 8 ? 148 * 8 : (rows + 7) / 8);
   attn_delta_kernel<<<g, 256, 0, st>>>((const bf16*)out, (const bf16*)dout, (float*)delta, B, S, H);
   dim3 grid((S + 127) / 128, H, B);
-  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, st>>>(tq, tk, tv, tdo, p);
+  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, st>>>(tq, tk, tv, tdo, tdq, p);
   attn_dq_convert_kernel<<<148 * 4, 256, 0, st>>>((const float*)dq_acc, (bf16*)dqkv, (long long)B * S, (int)E);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
 }
+
+#ifdef TNNB_TRACE
+int tnnb_attn_trace_dump(void* host_out) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(g_trace));
+}
+#endif
 
 }  // extern "C"

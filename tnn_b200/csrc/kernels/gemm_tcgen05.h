@@ -23,6 +23,8 @@ enum GemmEpilogue : int {
 int encode_tmap_bf16(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
                      const uint64_t* strides_bytes, const uint32_t* box,
                      const uint32_t* elem_strides);
+int encode_tmap_f32(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                    const uint32_t* box);
 int sm_count();
 
 }  // namespace tnnb
