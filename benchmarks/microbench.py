@@ -101,6 +101,14 @@ def cmd_softmax_ce(a):
     return {"ms": t, "gbs": round(2 * R * ld * 2 / t / 1e6)}
 
 
+def cmd_colsum(a):
+    R, C = a.rows, a.cols
+    dy = bf(R, C)
+    db = torch.zeros(C, device="cuda")
+    t = timeit(lambda: raw.colsum_accum(dy, db), a.iters)
+    return {"ms": t, "gbs": round(R * C * 2 / t / 1e6)}
+
+
 def cmd_adam(a):
     n = a.n
     w, g, m, v = (torch.zeros(n, device="cuda") for _ in range(4))
@@ -146,6 +154,7 @@ def main():
     p.add_argument("--seq", type=int, default=1024)
     p = sub.add_parser("layernorm"); p.add_argument("--rows", type=int, default=65536); p.add_argument("--cols", type=int, default=768)
     p = sub.add_parser("softmax_ce"); p.add_argument("--rows", type=int, default=8192); p.add_argument("--vocab", type=int, default=50257)
+    p = sub.add_parser("colsum"); p.add_argument("--rows", type=int, default=8192); p.add_argument("--cols", type=int, default=3072)
     p = sub.add_parser("adam"); p.add_argument("--n", type=int, default=163_000_000)
     p = sub.add_parser("conv2d"); p.add_argument("--batch", type=int, default=128); p.add_argument("--size", type=int, default=56)
     p.add_argument("--cin", type=int, default=64); p.add_argument("--cout", type=int, default=64); p.add_argument("--ksize", type=int, default=3)

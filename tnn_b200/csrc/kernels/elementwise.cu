@@ -203,37 +203,49 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const bf
   }
 }
 
-// db[n] += sum_m dy[m, n].  Block = 32 column-chunks (256 columns) x 8 row lanes.
-__global__ void colsum_kernel(const bf16* __restrict__ dy, long long ld, float* __restrict__ db,
-                              long long M, int N, int rows_per_block) {
-  __shared__ float red[8][32][9];
+// db[n] += sum_m dy[m, n].  Block = 8 column-chunks (64 columns, one 128-byte line per row) x 32 row
+// lanes, four independent 16-byte loads in flight per thread; narrow column tiles give enough blocks
+// to fill the GPU while keeping the number of atomic adds per output element small.
+__global__ void __launch_bounds__(256)
+colsum_kernel(const bf16* __restrict__ dy, long long ld, float* __restrict__ db, long long M, int N, int rows_per_block) {
+  __shared__ float red[32][8][9];
   const int cx = threadIdx.x, ry = threadIdx.y;
-  const int col = (blockIdx.x * 32 + cx) * 8;
+  const int col = (blockIdx.x * 8 + cx) * 8;
   const long long r0 = (long long)blockIdx.y * rows_per_block;
   const long long r1 = min(M, r0 + rows_per_block);
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (col + 8 <= N && (ld % 8 == 0)) {
-    for (long long r = r0 + ry; r < r1; r += 8) {
+    long long r = r0 + ry;
+    for (; r + 96 < r1; r += 128) {
+      float f0[8], f1[8], f2[8], f3[8];
+      load8(dy + r * ld + col, f0);
+      load8(dy + (r + 32) * ld + col, f1);
+      load8(dy + (r + 64) * ld + col, f2);
+      load8(dy + (r + 96) * ld + col, f3);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += (f0[k] + f1[k]) + (f2[k] + f3[k]);
+    }
+    for (; r < r1; r += 32) {
       float f[8];
       load8(dy + r * ld + col, f);
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] += f[k];
     }
   } else if (col < N) {
-    for (long long r = r0 + ry; r < r1; r += 8)
+    for (long long r = r0 + ry; r < r1; r += 32)
       for (int k = 0; k < 8 && col + k < N; ++k) acc[k] += __bfloat162float(dy[r * ld + col + k]);
   }
 #pragma unroll
   for (int k = 0; k < 8; ++k) red[ry][cx][k] = acc[k];
   __syncthreads();
-  if (ry == 0 && col < N) {
+  const int t = ry * 8 + cx;
+  if (t < 64) {  // one thread per column of the tile
+    const int c = t >> 3, k = t & 7;
+    float s = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      float s = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) s += red[j][cx][k];
-      if (col + k < N) atomicAdd(db + col + k, s);
-    }
+    for (int j = 0; j < 32; ++j) s += red[j][c][k];
+    const int oc = (blockIdx.x * 8 + c) * 8 + k;
+    if (oc < N) atomicAdd(db + oc, s);
   }
 }
 
@@ -306,12 +318,13 @@ int tnnb_embedding_bwd(const void* ids, const void* dy, void* dwte, void* dwpe, 
   LAUNCH_RC();
 }
 int tnnb_colsum_accum(const void* dy, long long ld, void* db, long long M, int N, void* stream) {
-  int gx = (N + 255) / 256;
-  int want_y = (2 * 148 + gx - 1) / gx;
+  const int gx = (N + 63) / 64;
+  int want_y = (4 * 148 + gx - 1) / gx;
+  if (want_y > 64) want_y = 64;  // at most 64 atomic adds per output element
   long long rpb = (M + want_y - 1) / want_y;
-  if (rpb < 64) rpb = 64;
-  int gy = (int)((M + rpb - 1) / rpb);
-  colsum_kernel<<<dim3(gx, gy), dim3(32, 8), 0, (cudaStream_t)stream>>>((const bf16*)dy, ld, (float*)db, M, N, (int)rpb);
+  rpb = (rpb + 127) / 128 * 128;
+  const int gy = (int)((M + rpb - 1) / rpb);
+  colsum_kernel<<<dim3(gx, gy), dim3(8, 32), 0, (cudaStream_t)stream>>>((const bf16*)dy, ld, (float*)db, M, N, (int)rpb);
   LAUNCH_RC();
 }
 int tnnb_cast_f32_bf16(const void* s, void* d, long long n, void* stream) {

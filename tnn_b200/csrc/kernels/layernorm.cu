@@ -105,60 +105,81 @@ ln_fwd_kernel(const bf16* __restrict__ x_in, const bf16* __restrict__ delta, bf1
   }
 }
 
+// Backward. One warp per row with the row held in registers as packed bf16; the dgamma / dbeta partial
+// sums of a warp live in its private slice of shared memory (plain read-modify-write, no atomics), which
+// keeps the register count low enough for several 256-thread blocks per SM - the kernel is bandwidth bound
+// and needs that many loads in flight (three blocks at C <= 768).
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
 template <int MAXCH>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, (MAXCH <= 3) ? 3 : 2)
 ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const float* __restrict__ mean_i,
               const float* __restrict__ rstd_i, const bf16* __restrict__ gamma, const bf16* __restrict__ dres,
               bf16* __restrict__ dx, bf16* __restrict__ ddelta, float* __restrict__ dgamma,
               float* __restrict__ dbeta, long long rows, int C, float p, unsigned long long seed,
               const unsigned long long* __restrict__ seed_off) {
   seed = mix_seed(seed, seed_off);
-  extern __shared__ float sm[];  // [2][C]
+  extern __shared__ float sm[];  // [warps][2][C]
   const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
   const int wpb = blockDim.x >> 5;
   const int chunks = C >> 3;
   const float inv_keep = 1.f / (1.f - p);
-  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) sm[i] = 0.f;
-  __syncthreads();
+  float* acc_g = sm + (size_t)warp * 2 * C;
+  float* acc_b = acc_g + C;
+  for (int i = lane; i < 2 * C; i += 32) acc_g[i] = 0.f;
+  __syncwarp();
+  const uint4 ones = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);  // bf16 1.0 x 8
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
-  float gw[MAXCH][8];
-  float ag[MAXCH][8], ab[MAXCH][8];
+  for (long long r = (long long)blockIdx.x * wpb + warp; r < rows; r += (long long)gridDim.x * wpb) {
+    uint4 xa[MAXCH], da[MAXCH], ra[MAXCH];
 #pragma unroll
-  for (int i = 0; i < MAXCH; ++i) {
-    const int c = lane + i * 32;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      ag[i][k] = 0.f;
-      ab[i][k] = 0.f;
-      gw[i][k] = 1.f;
+    for (int i = 0; i < MAXCH; ++i) {
+      const int c = lane + i * 32;
+      const bool in = c < chunks;
+      xa[i] = in ? *reinterpret_cast<const uint4*>(x + r * C + c * 8) : zero4;
+      da[i] = in ? *reinterpret_cast<const uint4*>(dh + r * C + c * 8) : zero4;
+      ra[i] = (in && dres) ? *reinterpret_cast<const uint4*>(dres + r * C + c * 8) : zero4;
     }
-    if (gamma && c < chunks) {
-      LBf8 g = *reinterpret_cast<const LBf8*>(gamma + c * 8);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) gw[i][k] = __bfloat162float(g.v[k]);
-    }
-  }
-
-  for (long long r = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += (long long)gridDim.x * wpb) {
     const float mean = mean_i[r], rstd = rstd_i[r];
-    float xh[MAXCH][8], dy[MAXCH][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < MAXCH; ++i) {
       const int c = lane + i * 32;
       if (c < chunks) {
-        LBf8 a = *reinterpret_cast<const LBf8*>(x + r * C + c * 8);
-        LBf8 d = *reinterpret_cast<const LBf8*>(dh + r * C + c * 8);
+        float xv[8], gv[8], gm[8];
+        unpack8(xa[i], xv);
+        unpack8(da[i], gv);
+        unpack8(gamma ? *reinterpret_cast<const uint4*>(gamma + c * 8) : ones, gm);
+        const float4 t0 = *reinterpret_cast<float4*>(acc_g + c * 8), t1 = *reinterpret_cast<float4*>(acc_g + c * 8 + 4);
+        const float4 u0 = *reinterpret_cast<float4*>(acc_b + c * 8), u1 = *reinterpret_cast<float4*>(acc_b + c * 8 + 4);
+        float ag[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+        float ab[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          xh[i][k] = (__bfloat162float(a.v[k]) - mean) * rstd;
-          const float g = __bfloat162float(d.v[k]);
-          ag[i][k] += g * xh[i][k];
-          ab[i][k] += g;
-          dy[i][k] = g * gw[i][k];
-          s1 += dy[i][k];
-          s2 += dy[i][k] * xh[i][k];
+          const float xh = (xv[k] - mean) * rstd;
+          ag[k] += gv[k] * xh;
+          ab[k] += gv[k];
+          const float dy = gv[k] * gm[k];
+          s1 += dy;
+          s2 += dy * xh;
         }
+        *reinterpret_cast<float4*>(acc_g + c * 8) = make_float4(ag[0], ag[1], ag[2], ag[3]);
+        *reinterpret_cast<float4*>(acc_g + c * 8 + 4) = make_float4(ag[4], ag[5], ag[6], ag[7]);
+        *reinterpret_cast<float4*>(acc_b + c * 8) = make_float4(ab[0], ab[1], ab[2], ab[3]);
+        *reinterpret_cast<float4*>(acc_b + c * 8 + 4) = make_float4(ab[4], ab[5], ab[6], ab[7]);
       }
     }
     s1 = warp_sum(s1) / C;
@@ -167,46 +188,41 @@ ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const flo
     for (int i = 0; i < MAXCH; ++i) {
       const int c = lane + i * 32;
       if (c < chunks) {
-        float o[8];
+        float xv[8], gv[8], gm[8], rv[8], o[8];
+        unpack8(xa[i], xv);
+        unpack8(da[i], gv);
+        unpack8(ra[i], rv);
+        unpack8(gamma ? *reinterpret_cast<const uint4*>(gamma + c * 8) : ones, gm);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) o[k] = rstd * (dy[i][k] - s1 - xh[i][k] * s2);
-        if (dres) {
-          LBf8 rr = *reinterpret_cast<const LBf8*>(dres + r * C + c * 8);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) o[k] += __bfloat162float(rr.v[k]);
+        for (int k = 0; k < 8; ++k) {
+          const float xh = (xv[k] - mean) * rstd;
+          o[k] = rstd * (gv[k] * gm[k] - s1 - xh * s2) + rv[k];
         }
-        LBf8 w;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) w.v[k] = __float2bfloat16(o[k]);
-        *reinterpret_cast<LBf8*>(dx + r * C + c * 8) = w;
+        const uint4 w = make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
+        *reinterpret_cast<uint4*>(dx + r * C + c * 8) = w;
         if (ddelta) {
+          float t[8];
+          unpack8(w, t);  // dropout acts on the rounded dx, like a separate pass would
+          if (p > 0.f) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            float t = __bfloat162float(w.v[k]);
-            if (p > 0.f) t = hash_uniform(seed, r * C + c * 8 + k) >= p ? t * inv_keep : 0.f;
-            w.v[k] = __float2bfloat16(t);
+            for (int k = 0; k < 8; ++k) t[k] = hash_uniform(seed, r * C + c * 8 + k) >= p ? t[k] * inv_keep : 0.f;
           }
-          *reinterpret_cast<LBf8*>(ddelta + r * C + c * 8) = w;
+          *reinterpret_cast<uint4*>(ddelta + r * C + c * 8) =
+              make_uint4(pack2(t[0], t[1]), pack2(t[2], t[3]), pack2(t[4], t[5]), pack2(t[6], t[7]));
         }
       }
     }
   }
   if (dgamma) {
-#pragma unroll
-    for (int i = 0; i < MAXCH; ++i) {
-      const int c = lane + i * 32;
-      if (c < chunks) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          atomicAdd(&sm[c * 8 + k], ag[i][k]);
-          atomicAdd(&sm[C + c * 8 + k], ab[i][k]);
-        }
-      }
-    }
     __syncthreads();
     for (int i = threadIdx.x; i < C; i += blockDim.x) {
-      atomicAdd(dgamma + i, sm[i]);
-      atomicAdd(dbeta + i, sm[C + i]);
+      float g = 0.f, bb = 0.f;
+      for (int w = 0; w < wpb; ++w) {
+        g += sm[(size_t)w * 2 * C + i];
+        bb += sm[(size_t)w * 2 * C + C + i];
+      }
+      atomicAdd(dgamma + i, g);
+      atomicAdd(dbeta + i, bb);
     }
   }
 }
@@ -255,8 +271,16 @@ int tnnb_layernorm_bwd(const void* dh, const void* x, const void* mean, const vo
   if (!mc) return -7;
   const int block = 256, wpb = 8;
   long long g = (rows + wpb - 1) / wpb;
-  int grid = (int)(g > 148 * 2 ? 148 * 2 : g);
-  size_t smem = 2 * (size_t)C * sizeof(float);
+  const int per_sm = (mc == 3) ? 3 : (mc == 5) ? 2 : 1;
+  int grid = (int)(g > 148 * per_sm ? 148 * per_sm : g);
+  size_t smem = (size_t)wpb * 2 * C * sizeof(float);  // <= 128 KB at C = 2048
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(ln_bwd_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 768 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 1280 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 2048 * 4);
+    attr_done = true;
+  }
   cudaStream_t st = (cudaStream_t)stream;
 #define LN_B(MC)                                                                                              \
   ln_bwd_kernel<MC><<<grid, block, smem, st>>>((const bf16*)dh, (const bf16*)x, (const float*)mean,           \
