@@ -16,8 +16,11 @@
 //   warp 0      TMA producer (one lane), STAGES-deep ring of (A,B) k-blocks
 //   warp 1      TMEM owner + MMA issuer (one lane), two accumulators so the
 //               epilogue of tile i overlaps the main loop of tile i+1
-//   warps 2-9   epilogue: TMEM -> registers -> fused math -> global memory
+//   warps 2-9   epilogue: TMEM -> registers -> fused math -> per-warp staging tile in shared
+//               memory -> global memory in whole 128-byte lines
 //               (two warps per 32-lane TMEM quarter, each owning half of the columns)
+// Two kernels share this structure: a single-CTA one (128 x 256 or 128 x 128 tiles) and a CTA-pair
+// one (`cta_group::2`, 256 x 256 tiles over two SMs), which is the default for large problems.
 // Every barrier wait is bounded; on expiry the kernel records a status code,
 // raises a CTA-wide abort flag and unwinds (TMEM is always released).
 #include "gemm_tcgen05.h"
@@ -52,16 +55,11 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 8 * 4096;  // + per-warp epilogue staging
 };
 
-template <int BN>
-__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, uint32_t (&r)[32], int row,
-                                               int col0) {
-  if (row >= p.M || col0 >= p.N) return;
-  float v[32];
-#pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+// Fused element-wise part of the epilogue for 32 accumulator columns of one row (row < M, col0 < N).
+__device__ __forceinline__ void epilogue_math(const GemmParams& p, float (&v)[32], int row, int col0) {
   const int flags = p.flags;
   const bool full = (col0 + 32 <= p.N);
 
@@ -124,6 +122,13 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, uint32_t (&r
     }
   }
 
+}
+
+// Row-per-lane store of 32 columns (each lane writes its own row): used for ragged edges and for the
+// output forms the coalescing path below does not cover.
+__device__ __forceinline__ void epilogue_store_rowwise(const GemmParams& p, const float (&v)[32], int row, int col0) {
+  const int flags = p.flags;
+  const bool full = (col0 + 32 <= p.N);
   if (flags & EPI_ATOMIC) {
     float* d = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col0;
     if (full && (p.ldd % 4 == 0)) {
@@ -174,6 +179,102 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, uint32_t (&r
       for (int j = 0; j < 32; ++j)
         if (col0 + j < p.N)
           d[j] = __float2bfloat16((flags & EPI_ACCUM) ? v[j] + __bfloat162float(d[j]) : v[j]);
+    }
+  }
+}
+
+
+// ---- coalescing epilogue ------------------------------------------------------------------------
+// tcgen05.ld hands every lane one ROW of the accumulator, so a direct store touches 32 different
+// 128-byte lines per instruction. Each epilogue warp therefore owns a 4 KB staging tile in shared
+// memory ([32 rows][128 B], 16-byte chunks XOR-swizzled by row): lanes write their row into it, and the
+// warp reads it back with 8 lanes per row so that every global store / reduction instruction covers
+// four complete 128-byte lines.
+__device__ __forceinline__ uint32_t stage_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+// bf16 output, 64 columns [col0, col0+64) of rows [row_base, row_base+32): lane = row has written its
+// 64 values (as packed bf16) to the staging tile. Requires ldd % 8 == 0 and col0 + 64 <= N.
+__device__ __forceinline__ void stage_flush_bf16(const GemmParams& p, const uint8_t* stage, int lane, int row_base, int col0) {
+  __syncwarp();
+  __nv_bfloat16* D = reinterpret_cast<__nv_bfloat16*>(p.D);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3), c = lane & 7;
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + stage_off(r, c));
+    if (row_base + r < p.M) *reinterpret_cast<uint4*>(D + (long long)(row_base + r) * p.ldd + col0 + c * 8) = v;
+  }
+  __syncwarp();
+}
+// fp32 output (store, accumulate or atomic add), 32 columns. Requires ldd % 4 == 0 and col0 + 32 <= N.
+__device__ __forceinline__ void stage_flush_f32(const GemmParams& p, const uint8_t* stage, int lane, int row_base, int col0) {
+  __syncwarp();
+  float* D = reinterpret_cast<float*>(p.D);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3), c = lane & 7;
+    float4 v = *reinterpret_cast<const float4*>(stage + stage_off(r, c));
+    if (row_base + r < p.M) {
+      float* d = D + (long long)(row_base + r) * p.ldd + col0 + c * 4;
+      if (p.flags & EPI_ATOMIC) {
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+      } else {
+        if (p.flags & EPI_ACCUM) {
+          const float4 o = *reinterpret_cast<const float4*>(d);
+          v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+        }
+        *reinterpret_cast<float4*>(d) = v;
+      }
+    }
+  }
+  __syncwarp();
+}
+
+// One warp's share of a tile: `nchunks` groups of 32 accumulator columns starting at TMEM address t_addr /
+// global column col_base, rows row_base + lane. Chooses the coalescing path where its conditions hold.
+__device__ __forceinline__ void epilogue_warp(const GemmParams& p, uint32_t t_addr, int nchunks, int row_base, int col_base,
+                                              int lane, uint8_t* stage) {
+  const int row = row_base + lane;
+  const bool f32 = (p.flags & (EPI_ATOMIC | EPI_OUT_F32)) != 0;
+  const bool staged_ok = f32 ? (p.ldd % 4 == 0) : (p.ldd % 8 == 0 && !(p.flags & EPI_ACCUM));
+#pragma unroll 1
+  for (int c = 0; c < nchunks; c += 2) {
+    const int col0 = col_base + c * 32;
+    if (col0 >= p.N) {  // whole pair of chunks is outside the matrix (tcgen05.ld is not needed)
+      continue;
+    }
+    const bool pair_staged = staged_ok && (col0 + 64 <= p.N) && (c + 1 < nchunks);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (c + h >= nchunks) break;
+      uint32_t r[32];
+      tmem_ld_32x32(t_addr + (c + h) * 32, r);  // warp-collective: never under a per-lane condition
+      tmem_ld_wait();
+      const int cc = col0 + h * 32;
+      if (cc >= p.N) continue;
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      if (row < p.M) epilogue_math(p, v, row, cc);
+      if (!pair_staged) {
+        if (row < p.M) epilogue_store_rowwise(p, v, row, cc);
+      } else if (f32) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          *reinterpret_cast<float4*>(stage + stage_off(lane, k)) = make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+        stage_flush_f32(p, stage, lane, row_base, cc);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * k + 2 * j], v[8 * k + 2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t*>(&h2);
+          }
+          *reinterpret_cast<uint4*>(stage + stage_off(lane, h * 4 + k)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        if (h == 1) stage_flush_bf16(p, stage, lane, row_base, col0);
+      }
     }
   }
 }
@@ -338,15 +439,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         break;
       }
       tc_fence_after();
-      const int row = mb * 128 + q * 32 + lane;
-      const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-#pragma unroll 1
-      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_addr + c * 32, r);
-        tmem_ld_wait();
-        epilogue_chunk<BN>(p, r, row, nb * BN + c * 32);
-      }
+      const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + half * (BN / 2);
+      epilogue_warp(p, t_addr, BN / 64, mb * 128 + q * 32, nb * BN + half * (BN / 2), lane,
+                    smem + STAGES * Cfg::STAGE_BYTES + 256 + (warp - 2) * 4096);
       tc_fence_before();
       mbar_arrive(&tempty[acc]);
       acc ^= 1;
@@ -359,6 +454,197 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ------------------------------------------------------------- CTA-pair kernel
+// The same product on 256 x 256 tiles computed by a CTA PAIR (cluster of two, `cta_group::2`): each CTA
+// stages its own 128 rows of A and HALF of the B tile (128 of the 256 N rows) per k-block, the even CTA's
+// MMA thread issues one 256 x 256 x 16 instruction that reads both CTAs' shared memory and writes 128
+// accumulator rows into each CTA's TMEM. Per SM this halves the B traffic through shared memory, which is
+// what limits the single-CTA kernel (12 KB per instruction read by the tensor core plus the same written
+// by TMA), and leaves room for six stages.
+//   full[s]   lives in the even CTA; both CTAs' TMA loads count their bytes on it (no multicast of data)
+//   empty[s]  one per CTA, signalled by a multicast tcgen05.commit
+//   tfull[a]  one per CTA (multicast commit); tempty[a] in the even CTA, 8 local + 8 remote warp arrivals
+struct Gemm2Cfg {
+  static constexpr int A_BYTES = 128 * 64 * 2;
+  static constexpr int B_BYTES = 128 * 64 * 2;  // this CTA's half of the 256-row B tile
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 8 * 4096;  // + per-warp epilogue staging
+};
+
+template <int A_MN, int B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                              const GemmParams p) {
+  using Cfg = Gemm2Cfg;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int BN = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0: issues the MMAs, 1: partner
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 16);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers and tensor memory exist before anything refers to them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles = p.num_m_blocks * p.num_n_blocks;  // in units of 256 x 256
+  const int total_work = tiles * p.split_k;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int work = pair; ok && work < total_work; work += num_pairs) {
+        const int ks = work / tiles;
+        const int t = work - ks * tiles;
+        const int nb = t / p.num_m_blocks;
+        const int mb = t - nb * p.num_m_blocks;
+        const int row0 = mb * 256 + (int)rank * 128;   // this CTA's rows of A
+        const int col0 = nb * 256 + (int)rank * 128;   // this CTA's rows of B (output columns)
+        const int kb0 = ks * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!wait_or_abort(&empty[stage], phase ^ 1, abort_flag)) {
+            raise_abort(p.status, abort_flag, ST_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * Cfg::STAGE_BYTES);
+          const uint32_t bar = mapa_shared(smem_u32(&full[stage]), 0);
+          uint8_t* a_dst = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + Cfg::A_BYTES;
+          if (A_MN == 0) {
+            tma_load_2d_pair(a_dst, &tmA, bar, kb * 64, row0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) tma_load_2d_pair(a_dst + i * 8192, &tmA, bar, row0 + i * 64, kb * 64);
+          }
+          if (B_MN == 0) {
+            tma_load_2d_pair(b_dst, &tmB, bar, kb * 64, col0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) tma_load_2d_pair(b_dst + i * 8192, &tmB, bar, col0 + i * 64, kb * 64);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(256, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int work = pair; ok && work < total_work; work += num_pairs) {
+        const int ks = work / tiles;
+        const int kb0 = ks * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
+        if (!wait_or_abort(&tempty[acc], acc_phase ^ 1, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!wait_or_abort(&full[stage], phase, abort_flag)) {
+            raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t ad = A_MN ? make_smem_desc(a_addr + k * 2048, 8192, 1024) : make_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024) : make_smem_desc(b_addr + k * 32, 16, 1024);
+            tc_mma_ss_pair(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit_pair(&empty[stage], 3);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        tc_commit_pair(&tfull[acc], 3);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const uint32_t tempty_remote[2] = {mapa_shared(smem_u32(&tempty[0]), 0), mapa_shared(smem_u32(&tempty[1]), 0)};
+    for (int work = pair; work < total_work; work += num_pairs) {
+      const int ks = work / tiles;
+      const int t = work - ks * tiles;
+      const int nb = t / p.num_m_blocks;
+      const int mb = t - nb * p.num_m_blocks;
+      if (!wait_or_abort(&tfull[acc], acc_phase, abort_flag)) {
+        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + half * 128;
+      epilogue_warp(p, t_addr, 4, mb * 256 + (int)rank * 128 + q * 32, nb * BN + half * 128, lane,
+                    smem + STAGES * Cfg::STAGE_BYTES + 256 + (warp - 2) * 4096);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_remote[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // no CTA frees tensor memory or exits while its partner may still touch it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
@@ -451,6 +737,20 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
 
+template <int A_MN, int B_MN>
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+  auto kern = gemm_bf16_tcgen05_pair_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
+    attr_set = true;
+  }
+  kern<<<grid, 320, Gemm2Cfg::SMEM_BYTES, stream>>>(ta, tb, p);  // cluster of two through __cluster_dims__
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
+}
+
 }  // namespace tnnb
 
 using namespace tnnb;
@@ -470,9 +770,12 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
 
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
-  p.num_m_blocks = (M + 127) / 128;
+  // 256 x 256 tiles on CTA pairs whenever the problem has at least one such tile's worth of rows and
+  // columns (force_bn: 512 forces the pair kernel, 128 / 256 force the single-CTA tile widths)
+  const bool pair = (force_bn == 512) || (force_bn == 0 && M > 128 && N > 128);
+  p.num_m_blocks = pair ? (M + 255) / 256 : (M + 127) / 128;
   p.num_k_blocks = (K + 63) / 64;
-  int bn = force_bn;
+  int bn = pair ? 256 : force_bn;
   if (bn != 128 && bn != 256) {
     const int t256 = p.num_m_blocks * ((N + 255) / 256);
     bn = (N > 128 && t256 * (split_k > 0 ? split_k : 1) >= sm_count()) ? 256 : 128;
@@ -484,7 +787,8 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
     split_k = 1;
     if (flags & EPI_ATOMIC) {
       // Enough (tile, k-range) work items to fill the machine about twice.
-      const int want = (2 * sm_count() + tiles - 1) / tiles;
+      const int units = pair ? sm_count() / 2 : sm_count();
+      const int want = (2 * units + tiles - 1) / tiles;
       split_k = max(1, min(want, p.num_k_blocks / 4 > 0 ? p.num_k_blocks / 4 : 1));
     }
   }
@@ -519,7 +823,7 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
   if (!b_mn) {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
     uint64_t str[1] = {(uint64_t)ldb * 2};
-    uint32_t box[2] = {64, (uint32_t)bn};
+    uint32_t box[2] = {64, pair ? 128u : (uint32_t)bn};
     rc = encode_tmap_bf16(&tb, B, 2, dims, str, box, nullptr);
   } else {
     uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
@@ -529,6 +833,13 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
   }
   if (rc) return rc;
 
+  if (pair) {
+    const int grid2 = 2 * min(tiles * p.split_k, sm_count() / 2);
+    if (!a_mn && !b_mn) return launch_gemm_pair<0, 0>(ta, tb, p, grid2, stream);
+    if (!a_mn && b_mn) return launch_gemm_pair<0, 1>(ta, tb, p, grid2, stream);
+    if (a_mn && !b_mn) return launch_gemm_pair<1, 0>(ta, tb, p, grid2, stream);
+    return launch_gemm_pair<1, 1>(ta, tb, p, grid2, stream);
+  }
   const int grid = min(tiles * p.split_k, sm_count());
 #define TNNB_LAUNCH(BN_, AM, BM_) return launch_gemm<BN_, AM, BM_>(ta, tb, p, grid, stream)
   if (bn == 256) {
