@@ -31,6 +31,21 @@ def test_layouts(M, N, K, a_t, b_t):
     _close(out, ref)
 
 
+@pytest.mark.parametrize("M,N,K", [(8192, 768, 256), (4096, 704, 192), (2048, 768, 128), (1024, 1000, 64)])
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, True)])
+def test_pair_kernel_tile_widths(M, N, K, a_t, b_t):
+    """CTA-pair kernel: shapes where the wave heuristic picks 384-wide single-accumulator tiles (N = 768 / 704 with
+    many rows) and shapes that stay on 256-wide ones, plus the forced 256-wide form, with bias + residual fused."""
+    torch.manual_seed(2)
+    a = _rand(K, M) if a_t else _rand(M, K)
+    b = _rand(K, N) if b_t else _rand(N, K)
+    bias, res = _rand(N), _rand(M, N)
+    ref = (a.t() if a_t else a).float() @ (b if b_t else b.t()).float() + bias.float() + res.float()
+    _close(gemm(a, b, a_t=a_t, b_t=b_t, bias=bias, residual=res), ref)
+    _close(gemm(a, b, a_t=a_t, b_t=b_t, bias=bias, residual=res, force_bn=512), ref)
+    _lib.check_status()
+
+
 @pytest.mark.parametrize("bn", [128, 256])
 def test_tile_variants(bn):
     a, b = _rand(512, 256), _rand(512, 256)

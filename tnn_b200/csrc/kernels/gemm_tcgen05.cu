@@ -467,21 +467,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 //   full[s]   lives in the even CTA; both CTAs' TMA loads count their bytes on it (no multicast of data)
 //   empty[s]  one per CTA, signalled by a multicast tcgen05.commit
 //   tfull[a]  one per CTA (multicast commit); tempty[a] in the even CTA, 8 local + 8 remote warp arrivals
+template <int BN>
 struct Gemm2Cfg {
   static constexpr int A_BYTES = 128 * 64 * 2;
-  static constexpr int B_BYTES = 128 * 64 * 2;  // this CTA's half of the 256-row B tile
+  static constexpr int B_BYTES = (BN / 2) * 64 * 2;  // this CTA's half of the BN-row B tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = 6;
+  static constexpr int STAGES = (BN == 384) ? 4 : (BN == 256) ? 6 : 8;
+  static constexpr int ACCS = (BN == 384) ? 1 : 2;  // 384 columns leave no room for a second accumulator
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 8 * 4096;  // + per-warp epilogue staging
 };
 
-template <int A_MN, int B_MN>
+template <int BN, int A_MN, int B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                               const GemmParams p) {
-  using Cfg = Gemm2Cfg;
+  using Cfg = Gemm2Cfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
-  constexpr int BN = 256;
+  constexpr int HALF = BN / 2;  // B rows (output columns) staged by each CTA
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
@@ -521,7 +523,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles = p.num_m_blocks * p.num_n_blocks;  // in units of 256 x 256
+  const int tiles = p.num_m_blocks * p.num_n_blocks;  // in units of 256 x BN
   const int total_work = tiles * p.split_k;
 
   if (warp == 0) {
@@ -535,7 +537,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
         const int nb = t / p.num_m_blocks;
         const int mb = t - nb * p.num_m_blocks;
         const int row0 = mb * 256 + (int)rank * 128;   // this CTA's rows of A
-        const int col0 = nb * 256 + (int)rank * 128;   // this CTA's rows of B (output columns)
+        const int col0 = nb * BN + (int)rank * HALF;   // this CTA's rows of B (output columns)
         const int kb0 = ks * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -558,7 +560,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
             tma_load_2d_pair(b_dst, &tmB, bar, kb * 64, col0);
           } else {
 #pragma unroll
-            for (int i = 0; i < 2; ++i) tma_load_2d_pair(b_dst + i * 8192, &tmB, bar, col0 + i * 64, kb * 64);
+            for (int i = 0; i < HALF / 64; ++i) tma_load_2d_pair(b_dst + i * 8192, &tmB, bar, col0 + i * 64, kb * 64);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -569,7 +571,8 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(256, BN, A_MN, B_MN);
+      constexpr uint32_t idesc = make_idesc_bf16(256, BN == 384 ? 256 : BN, A_MN, B_MN);
+      constexpr uint32_t idesc_tail = make_idesc_bf16(256, 128, A_MN, B_MN);  // BN == 384 only
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -584,7 +587,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * (BN == 384 ? 0 : BN);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_or_abort(&full[stage], phase, abort_flag)) {
             raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
@@ -599,6 +602,11 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
             const uint64_t ad = A_MN ? make_smem_desc(a_addr + k * 2048, 8192, 1024) : make_smem_desc(a_addr + k * 32, 16, 1024);
             const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024) : make_smem_desc(b_addr + k * 32, 16, 1024);
             tc_mma_ss_pair(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (BN == 384) {  // this CTA's B rows 128..191 (two 64-row boxes further when MN-major)
+              const uint64_t bt = B_MN ? make_smem_desc(b_addr + 2 * 8192 + k * 2048, 8192, 1024)
+                                       : make_smem_desc(b_addr + 128 * 128 + k * 32, 16, 1024);
+              tc_mma_ss_pair(d_tmem + 256, ad, bt, idesc_tail, (kb > kb0 || k > 0) ? 1u : 0u);
+            }
           }
           tc_commit_pair(&empty[stage], 3);
           if (++stage == STAGES) {
@@ -608,7 +616,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
         }
         if (!ok) break;
         tc_commit_pair(&tfull[acc], 3);
-        acc ^= 1;
+        if (Cfg::ACCS == 2) acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
     }
@@ -628,13 +636,21 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
         break;
       }
       tc_fence_after();
-      const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + half * 128;
-      epilogue_warp(p, t_addr, 4, mb * 256 + (int)rank * 128 + q * 32, nb * BN + half * 128, lane,
-                    smem + STAGES * Cfg::STAGE_BYTES + 256 + (warp - 2) * 4096);
+      uint8_t* stage_tile = smem + STAGES * Cfg::STAGE_BYTES + 256 + (warp - 2) * 4096;
+      const int row_base = mb * 256 + (int)rank * 128 + q * 32;
+      if (BN == 384) {
+        // warp half h owns output columns [h*192, h*192+192): 128 from the first product, 64 from the second
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        epilogue_warp(p, t_lane + half * 128, 4, row_base, nb * BN + half * 192, lane, stage_tile);
+        epilogue_warp(p, t_lane + 256 + half * 64, 2, row_base, nb * BN + half * 192 + 128, lane, stage_tile);
+      } else {
+        const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + half * HALF;
+        epilogue_warp(p, t_addr, HALF / 32, row_base, nb * BN + half * HALF, lane, stage_tile);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty_remote[acc]);
-      acc ^= 1;
+      if (Cfg::ACCS == 2) acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
   }
@@ -737,16 +753,16 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
 
-template <int A_MN, int B_MN>
+template <int BN, int A_MN, int B_MN>
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
-  auto kern = gemm_bf16_tcgen05_pair_kernel<A_MN, B_MN>;
+  auto kern = gemm_bf16_tcgen05_pair_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg<BN>::SMEM_BYTES);
     if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
     attr_set = true;
   }
-  kern<<<grid, 320, Gemm2Cfg::SMEM_BYTES, stream>>>(ta, tb, p);  // cluster of two through __cluster_dims__
+  kern<<<grid, 320, Gemm2Cfg<BN>::SMEM_BYTES, stream>>>(ta, tb, p);  // cluster of two through __cluster_dims__
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
@@ -775,8 +791,17 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
   const bool pair = (force_bn == 512) || (force_bn == 0 && M > 128 && N > 128);
   p.num_m_blocks = pair ? (M + 255) / 256 : (M + 127) / 128;
   p.num_k_blocks = (K + 63) / 64;
-  int bn = pair ? 256 : force_bn;
-  if (bn != 128 && bn != 256) {
+  int bn = force_bn;
+  if (pair) {
+    // 256-wide tiles (narrower pair tiles are limited by shared-memory bandwidth: A is re-read per 128
+    // columns), or 384-wide ones with a single accumulator when they need clearly fewer waves of CTA pairs
+    // (N = 768 with 8192 rows: 64 tiles on 74 pairs instead of 96).
+    const int units = sm_count() / 2;
+    const long long sk = split_k > 0 ? split_k : 1;
+    const long long w256 = ((long long)p.num_m_blocks * ((N + 255) / 256) * sk + units - 1) / units * 256;
+    const long long w384 = ((long long)p.num_m_blocks * ((N + 383) / 384) * sk + units - 1) / units * 384;
+    bn = (force_bn == 0 && !(flags & EPI_ATOMIC) && w384 * 10 <= w256 * 8) ? 384 : 256;
+  } else if (bn != 128 && bn != 256) {
     const int t256 = p.num_m_blocks * ((N + 255) / 256);
     bn = (N > 128 && t256 * (split_k > 0 ? split_k : 1) >= sm_count()) ? 256 : 128;
     if (N > 128 && (flags & EPI_ATOMIC)) bn = 256;
@@ -823,7 +848,7 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
   if (!b_mn) {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
     uint64_t str[1] = {(uint64_t)ldb * 2};
-    uint32_t box[2] = {64, pair ? 128u : (uint32_t)bn};
+    uint32_t box[2] = {64, pair ? (uint32_t)bn / 2 : (uint32_t)bn};
     rc = encode_tmap_bf16(&tb, B, 2, dims, str, box, nullptr);
   } else {
     uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
@@ -835,10 +860,18 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
 
   if (pair) {
     const int grid2 = 2 * min(tiles * p.split_k, sm_count() / 2);
-    if (!a_mn && !b_mn) return launch_gemm_pair<0, 0>(ta, tb, p, grid2, stream);
-    if (!a_mn && b_mn) return launch_gemm_pair<0, 1>(ta, tb, p, grid2, stream);
-    if (a_mn && !b_mn) return launch_gemm_pair<1, 0>(ta, tb, p, grid2, stream);
-    return launch_gemm_pair<1, 1>(ta, tb, p, grid2, stream);
+#define TNNB_PAIR(BN_, AM, BM_) return launch_gemm_pair<BN_, AM, BM_>(ta, tb, p, grid2, stream)
+    if (bn == 256) {
+      if (!a_mn && !b_mn) TNNB_PAIR(256, 0, 0);
+      if (!a_mn && b_mn) TNNB_PAIR(256, 0, 1);
+      if (a_mn && !b_mn) TNNB_PAIR(256, 1, 0);
+      TNNB_PAIR(256, 1, 1);
+    }
+    if (!a_mn && !b_mn) TNNB_PAIR(384, 0, 0);
+    if (!a_mn && b_mn) TNNB_PAIR(384, 0, 1);
+    if (a_mn && !b_mn) TNNB_PAIR(384, 1, 0);
+    TNNB_PAIR(384, 1, 1);
+#undef TNNB_PAIR
   }
   const int grid = min(tiles * p.split_k, sm_count());
 #define TNNB_LAUNCH(BN_, AM, BM_) return launch_gemm<BN_, AM, BM_>(ta, tb, p, grid, stream)

@@ -35,12 +35,11 @@ def parse_layout(layout: str) -> Dict[str, int]:
 
 
 def default_layout(world: int, model_name: str) -> str:
-    """GPT-2 models use TP=2 combined with data parallelism (the flagship configuration); CNNs are
-    purely data parallel."""
+    """Pure data parallelism: every zoo model (GPT-2 medium included) fits one 180 GB GPU many times over, so
+    sharding the model only adds communication. Tensor / pipeline layouts are chosen explicitly
+    (``tp2dp4``, ``pp2tp2`` ...)."""
     if world <= 1:
         return "single"
-    if "gpt2" in model_name and world % 2 == 0:
-        return f"tp2dp{world // 2}" if world > 2 else "tp2"
     return f"dp{world}"
 
 
