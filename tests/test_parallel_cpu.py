@@ -35,7 +35,7 @@ def reference(batches):
 
 def test_layout_strings():
     assert parse_layout("pp4tp2") == {"dp": 1, "tp": 2, "pp": 4}
-    assert default_layout(8, "gpt2_small") == "tp2dp4" and default_layout(2, "gpt2_small") == "tp2"
+    assert default_layout(8, "gpt2_small") == "dp8" and default_layout(1, "gpt2_small") == "single"
     assert default_layout(4, "imagenet_resnet50") == "dp4"
 
 
