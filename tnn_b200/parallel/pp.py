@@ -256,6 +256,30 @@ class PipelineTrainer:
             return torch.stack([l.reshape(()) for l in losses]).mean().reshape(1)
         return None
 
+    def fit(self, train_loader=None, max_steps: Optional[int] = None, log_every: int = 10) -> Dict[str, float]:
+        """Step-mode training loop: every rank draws the same batches (same loader seed per data-parallel
+        replica), the last stage owns the loss. Returns ``{"steps", "loss"}`` (loss is NaN on other stages)."""
+        from ..data.loaders import create_loaders
+        cfg = self.cfg
+        if train_loader is None:
+            train_loader, _ = create_loaders(cfg.dataset_name, cfg.dataset_path, self.local_batch, seed=cfg.seed + self.data_rank,
+                                             model_name=cfg.model_name, steps_per_epoch=max(1, cfg.max_steps if cfg.max_steps > 0 else 100))
+        steps = max_steps if max_steps is not None else (cfg.max_steps if cfg.max_steps > 0 else None)
+        last = float("nan")
+        epoch = 0
+        while True:
+            for data, labels in train_loader:
+                loss = self.train_step(data, labels)
+                if loss is not None:
+                    last = float(loss.item())
+                    if log_every and self.global_step % log_every == 0 and self.topo.dp_idx == 0 and self.topo.tp_idx == 0:
+                        print(f"step {self.global_step} loss {last:.4f}", flush=True)
+                if steps is not None and self.global_step >= steps:
+                    return {"steps": self.global_step, "loss": last}
+            epoch += 1
+            if steps is None and epoch >= cfg.epochs:
+                return {"steps": self.global_step, "loss": last}
+
     def save_stage(self, path: str) -> str:
         """Write this stage's graph state (the counterpart of the reference's SAVE_TO_FILE command:
         every worker saves its own stage, include/distributed/worker.hpp:279-296)."""

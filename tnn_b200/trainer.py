@@ -192,7 +192,9 @@ class Trainer:
     @torch.no_grad()
     def validate(self, loader: Optional[BaseLoader] = None, max_batches: Optional[int] = None) -> Dict[str, float]:
         """Mean loss / accuracy over a loader in eval mode (src/nn/train.cpp:596-660)."""
-        loader = loader or self.val_loader
+        if loader is None:
+            self._ensure_loaders()
+            loader = self.val_loader
         g = self.graph
         g.set_training(False)
         tot_loss, tot_corr, tot_rows, n = 0.0, 0, 0, 0
@@ -214,12 +216,17 @@ class Trainer:
                 "batches": n}
 
     # ------------------------------------------------------------------------ fit
-    def fit(self) -> Dict[str, float]:
+    def _ensure_loaders(self) -> None:
         cfg = self.cfg
-        if self.train_loader is None:
-            self.train_loader, self.val_loader = create_loaders(cfg.dataset_name, cfg.dataset_path, cfg.batch_size, cfg.seed,
-                                                                cfg.prefetch_depth if cfg.prefetch_data else 0, cfg.model_name)
-        return self._fit_steps() if cfg.step_mode else self._fit_epochs()
+        if self.train_loader is None or self.val_loader is None:
+            tr, va = create_loaders(cfg.dataset_name, cfg.dataset_path, cfg.batch_size, cfg.seed,
+                                    cfg.prefetch_depth if cfg.prefetch_data else 0, cfg.model_name)
+            self.train_loader = self.train_loader or tr
+            self.val_loader = self.val_loader or va
+
+    def fit(self) -> Dict[str, float]:
+        self._ensure_loaders()
+        return self._fit_steps() if self.cfg.step_mode else self._fit_epochs()
 
     def _log_step(self, epoch, loss_t, t_ms, avg):
         loss = float(loss_t.item())
