@@ -4,18 +4,20 @@
 //
 //   tnnb_gemm_ag   all-gather -> GEMM   Y[M, N] = AllGather_rows(X)[M, K] * op(W)^T
 //       Every rank owns rows [r*M/tp, (r+1)*M/tp) of a symmetric [M, K] buffer.
-//       Copy warps of the persistent GEMM pull the peers' row blocks into the
-//       local buffer (each block crosses NVLink exactly once) and publish a
-//       per-block flag; the TMA producer starts with the locally owned rows and
-//       waits on the flag only when it reaches a remote block, so the transfer
-//       hides behind the first wave of tiles. Operands reach the tensor core by
-//       TMA from LOCAL memory only.
+//       Four copy warps per CTA of the persistent GEMM pull pieces (about 32 KB) of
+//       the peers' row blocks into the local buffer with plain 16-byte loads,
+//       sixteen in flight per thread (each byte crosses NVLink exactly once), and
+//       set the piece's flag; the TMA producer runs every tile of the locally
+//       owned rows first and checks the flags only when it reaches a peer's block,
+//       so the transfer hides behind the local tiles. Operands reach the tensor
+//       core by TMA from LOCAL memory only.
 //   tnnb_gemm_rs   GEMM -> reduce-scatter   Y_r[M/tp, N] = sum_s (A_s * op(W_s)^T)[rows of r]
 //       Tiles whose rows belong to a peer are computed first and their bf16
-//       partial sums are stored straight from the epilogue into that peer's
-//       inbox, followed by a release increment of the tile's flag; tiles of the
-//       rank's own rows come last and add the peers' partials (acquire on the
-//       flag) before bias and the final store.
+//       partial sums are stored from the epilogue (through a per-warp staging tile,
+//       in whole 128-byte lines) into that peer's inbox, followed by a release
+//       store of the call number into the flag of (tile, row quarter, column
+//       half); tiles of the rank's own rows come last and add the peers' partials
+//       (acquire on the flags) and the bias before the final store.
 //   tnnb_dp_step   data-parallel gradient reduce-scatter + optimizer + parameter
 //       all-gather in ONE kernel: each rank pulls its slice of every peer's fp32
 //       gradient buffer, sums, applies AdamW / SGD-momentum to its fp32 master
@@ -102,7 +104,7 @@ struct CommGemmParams {
   const bf16* ag_src[MAX_PEERS];  // peer r's [M, lda] buffer
   bf16* ag_dst;                   // this rank's [M, lda] buffer
   long long lda;
-  uint32_t* chunk_flags;          // local, one per m-block
+  uint32_t* chunk_flags[MAX_PEERS];  // rank r's piece flags (128 per row block); [rank] is local
   uint32_t* go_flag;              // local
   bf16* D;                        // MODE_AG: [M, N] output ; MODE_RS: [rows_per_rank, N] output
   long long ldd;
@@ -117,38 +119,58 @@ struct CommGemmParams {
   bf16* aux;  // [M, N], row pitch ldd
 };
 
-template <int BN>
+template <int BN, int MODE>
 struct CommCfg {
   static constexpr int A_BYTES = 128 * 64 * 2;
   static constexpr int B_BYTES = BN * 64 * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  // all-gather: 4 epilogue warps + 4 copy warps; reduce-scatter: 8 epilogue warps
+  static constexpr int EPI_WARPS = (MODE == MODE_AG) ? 4 : 8;
+  static constexpr int THREADS = 320;
+  static constexpr int COPY_THREADS = 128;  // all-gather: warps 6-9
+  static constexpr int COPY_BYTES = 0;
+  static constexpr int BARS = STAGES * STAGE_BYTES;          // 256 bytes of barriers
+  static constexpr int STAGING = BARS + 256;                 // per epilogue warp 4 KB
+  static constexpr int COPY = STAGING + EPI_WARPS * 4096;
+  static constexpr int SMEM_BYTES = COPY + COPY_BYTES + 1024;
 };
 
-// Tile order: MODE_AG starts with the locally owned row blocks, MODE_RS ends with them.
+// Tile order. MODE_AG: every tile of the locally owned row blocks first (their operands are already
+// here), then the peers' row blocks in the order the copy warps bring them in. MODE_RS: tiles whose rows
+// belong to a peer first (their partial sums have the longest way to go), own rows last. Within the
+// peers' part the order is row block by row block (all column tiles of a block before the next block),
+// which is the order the data arrives in: the first remote tile needs one block, not all of them.
 template <int MODE>
 __device__ __forceinline__ void decode_tile(const CommGemmParams& p, int t, int& mb, int& nb) {
-  nb = t / p.num_m_blocks;
-  const int i = t - nb * p.num_m_blocks;
-  const int first_local = p.rank * p.blocks_per_rank;
-  const int start = (MODE == MODE_AG) ? first_local : first_local + p.blocks_per_rank;
-  mb = (start + i) % p.num_m_blocks;
+  const int bpr = p.blocks_per_rank;
+  const int first_local = p.rank * bpr;
+  const int remote_blocks = p.num_m_blocks - bpr;
+  const int first_tiles = (MODE == MODE_AG ? bpr : remote_blocks) * p.num_n_blocks;
+  const bool local = (MODE == MODE_AG) ? (t < first_tiles) : (t >= first_tiles);
+  const int u = (t < first_tiles) ? t : t - first_tiles;
+  const int j = u / p.num_n_blocks;  // row block inside its group
+  nb = u - j * p.num_n_blocks;
+  mb = local ? first_local + j : (first_local + bpr + j) % p.num_m_blocks;
 }
 
+__device__ __forceinline__ uint32_t cstage_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
 template <int BN, int B_MN, int MODE>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(CommCfg<BN, MODE>::THREADS, 1)
 gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const CommGemmParams p) {
-  using Cfg = CommCfg<BN>;
+  using Cfg = CommCfg<BN, MODE>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int EW = Cfg::EPI_WARPS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::BARS);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* cbar = tempty + 2;  // [2] bounce buffers of the copy warp
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cbar + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -160,7 +182,8 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 128);
+      mbar_init(&tempty[a], EW);
+      mbar_init(&cbar[a], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -174,23 +197,31 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int tiles = p.num_m_blocks * p.num_n_blocks;
+  // all-gather: a peer's 128-row block arrives as `cpb` pieces of `piece_rows` rows (about 32 KB each)
+  const int piece_rows = max(1, min(128, 32768 / (p.K * 2)));
+  const int cpb = (128 + piece_rows - 1) / piece_rows;
 
   if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
-        int mb, nb;
-        decode_tile<MODE>(p, t, mb, nb);
-        if (MODE == MODE_AG && mb / p.blocks_per_rank != p.rank) {
-          // rows of a peer: wait until a copy warp (of any CTA) has landed them locally
-          if (!spin_until<false>(p.chunk_flags + mb, EPOCH)) {
-            raise_abort(p.status, abort_flag, ST_TIMEOUT_PEER);
-            break;
-          }
-          fence_proxy_async_all();
+    // lane 0 issues the TMA loads; the whole warp checks the piece flags of a peer's row block
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      int mb, nb;
+      decode_tile<MODE>(p, t, mb, nb);
+      if (MODE == MODE_AG && mb / p.blocks_per_rank != p.rank) {
+        bool landed = true;
+        for (int i = lane; i < cpb; i += 32) landed = spin_until<false>(p.chunk_flags[p.rank] + mb * 128 + i, EPOCH) && landed;
+        landed = __all_sync(0xffffffffu, landed);
+        if (!landed) {
+          if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_PEER);
+          break;
         }
+        fence_proxy_async_all();
+      }
+      if (lane == 0) {
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!wait_or_abort(&empty[stage], phase ^ 1, abort_flag)) {
             raise_abort(p.status, abort_flag, ST_TIMEOUT_PRODUCER);
@@ -214,6 +245,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -255,8 +287,12 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (acc == 0) acc_phase ^= 1;
       }
     }
-  } else if (warp < 6) {
-    const int q = warp & 3;
+  } else if (warp < 2 + EW) {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;                               // TMEM lane quarter
+    const int half = (EW == 8) ? ((warp - 2) >> 2) : 0;   // column half when eight warps share a tile
+    constexpr int COLS = BN / (EW / 4);                   // accumulator columns of this warp
+    uint8_t* stage_tile = smem + Cfg::STAGING + (warp - 2) * 4096;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
@@ -267,127 +303,212 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         break;
       }
       tc_fence_after();
-      const int row = mb * 128 + q * 32 + lane;  // global row
-      const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      const int row_base = mb * 128 + q * 32;             // global row of lane 0
+      const int row = row_base + lane;
+      const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + half * COLS;
+      const int col_base = nb * BN + half * COLS;
       const int owner = (MODE == MODE_RS) ? mb / p.blocks_per_rank : p.rank;
-      const int lrow = row - owner * p.rows_per_rank;      // row inside the owner's block (MODE_RS)
-      const int ltile = (mb - owner * p.blocks_per_rank) * p.num_n_blocks + nb;
-      bool peers_ok = true;
-      if (MODE == MODE_RS && owner == p.rank) {
-        // every source must have delivered this warp's row quarter of the tile for this call
+      const int lrow_base = row_base - owner * p.rows_per_rank;   // row inside the owner's block (MODE_RS)
+      const int fidx = ((mb - owner * p.blocks_per_rank) * p.num_n_blocks + nb) * 8 + q * 2 + half;
+      const bool remote = (MODE == MODE_RS) && owner != p.rank;
+      if (MODE == MODE_RS && !remote) {
+        // every source must have delivered this warp's part of the tile for this call
+        bool peers_ok = true;
         for (int s = 0; s < p.tp; ++s)
-          if (s != p.rank) peers_ok = spin_until<true>(p.tile_flag_local[s] + ltile * 4 + q, EPOCH) && peers_ok;
+          if (s != p.rank) peers_ok = spin_until<true>(p.tile_flag_local[s] + fidx, EPOCH) && peers_ok;
         peers_ok = __all_sync(0xffffffffu, peers_ok);
         if (!peers_ok && lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_PEER);
       }
+      // destination of bf16 rows for the coalesced flush: the output, or the owner's inbox
+      bf16* dst = remote ? p.inbox_remote[owner] : p.D;
+      const long long dld = remote ? p.ldi : p.ldd;
+      const int drow_base = (MODE == MODE_RS) ? lrow_base : row_base;
+      const int drows = (MODE == MODE_RS) ? p.rows_per_rank : p.M;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_addr + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = nb * BN + c * 32;
-        if (row >= p.M || col0 >= p.N) continue;
-        float v[32];
+      for (int c = 0; c < COLS / 32; c += 2) {
+        const int col0 = col_base + c * 32;
+        if (col0 >= p.N) continue;
+        const bool vec_ok = (col0 + 64 <= p.N) && (dld % 8 == 0) && (p.ldi % 8 == 0);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        const bool fullc = col0 + 32 <= p.N;
-        bf16* dst;
-        long long ld;
-        if (MODE == MODE_RS && owner != p.rank) {
-          dst = p.inbox_remote[owner] + (long long)lrow * p.ldi + col0;
-          ld = p.ldi;
-        } else {
-          if (MODE == MODE_RS) {
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_addr + (c + h) * 32, r);
+          tmem_ld_wait();
+          const int cc = col0 + h * 32;
+          if (cc >= p.N) continue;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (MODE == MODE_RS && !remote && vec_ok) {
+            // own rows: fp32 partial through the staging tile, the peers' partials and the bias are added
+            // in the coalesced phase (8 lanes per row, 4 columns each)
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              *reinterpret_cast<float4*>(stage_tile + cstage_off(lane, k)) = make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+            __syncwarp();
+            float4 a[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[i] = *reinterpret_cast<const float4*>(stage_tile + cstage_off(i * 4 + (lane >> 3), lane & 7));
+            const int c4 = lane & 7;
             for (int s = 0; s < p.tp; ++s) {
               if (s == p.rank) continue;
-              const bf16* in = p.inbox_local[s] + (long long)lrow * p.ldi + col0;
-              if (fullc && (p.ldi % 8 == 0)) {
+              uint2 raw[8];
 #pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  uint4 raw;
-                  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                               : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
-                               : "l"(in + j)
-                               : "memory");
-                  const bf16* tt = reinterpret_cast<const bf16*>(&raw);
+              for (int i = 0; i < 8; ++i) {  // eight independent loads in flight before any is used
+                const int lr = lrow_base + i * 4 + (lane >> 3);
+                raw[i] = make_uint2(0, 0);
+                if (lr < drows)
+                  asm volatile("ld.relaxed.gpu.global.v2.u32 {%0,%1}, [%2];" : "=r"(raw[i].x), "=r"(raw[i].y)
+                               : "l"(p.inbox_local[s] + (long long)lr * p.ldi + cc + c4 * 4));
+              }
 #pragma unroll
-                  for (int k = 0; k < 8; ++k) v[j + k] += __bfloat162float(tt[k]);
-                }
-              } else {
-                for (int j = 0; j < 32; ++j)
-                  if (col0 + j < p.N) v[j] += __bfloat162float(in[j]);
+              for (int i = 0; i < 8; ++i) {
+                a[i].x += __uint_as_float(raw[i].x << 16); a[i].y += __uint_as_float(raw[i].x & 0xffff0000u);
+                a[i].z += __uint_as_float(raw[i].y << 16); a[i].w += __uint_as_float(raw[i].y & 0xffff0000u);
               }
             }
+            float4 bb = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p.bias) {
+              const uint2 braw = *reinterpret_cast<const uint2*>(p.bias + cc + c4 * 4);
+              bb = make_float4(__uint_as_float(braw.x << 16), __uint_as_float(braw.x & 0xffff0000u), __uint_as_float(braw.y << 16),
+                               __uint_as_float(braw.y & 0xffff0000u));
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int lr = lrow_base + i * 4 + (lane >> 3);
+              if (lr < drows) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a[i].x + bb.x, a[i].y + bb.y), hi = __floats2bfloat162_rn(a[i].z + bb.z, a[i].w + bb.w);
+                *reinterpret_cast<uint2*>(p.D + (long long)lr * p.ldd + cc + c4 * 4) =
+                    make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+              }
+            }
+            __syncwarp();
+            continue;
           }
-          if (p.bias) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (fullc || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+          if (MODE == MODE_RS && !remote) {  // ragged edge of an own tile: row-per-lane
+            const int lr = lrow_base + lane;
+            if (lr < drows) {
+              for (int j = 0; j < 32 && cc + j < p.N; ++j) {
+                float a = v[j];
+                for (int s = 0; s < p.tp; ++s)
+                  if (s != p.rank) a += __bfloat162float(p.inbox_local[s][(long long)lr * p.ldi + cc + j]);
+                if (p.bias) a += __bfloat162float(p.bias[cc + j]);
+                p.D[(long long)lr * p.ldd + cc + j] = __float2bfloat16(a);
+              }
+            }
+            continue;
           }
-          const long long orow = (MODE == MODE_RS) ? lrow : row;
-          if (MODE == MODE_AG && p.epi) {
-            bf16* ax = p.aux + orow * p.ldd + col0;
-            if (fullc && (p.ldd % 8 == 0)) {
+          // all-gather GEMM: bias and the optional GELU pair, row-per-lane
+          bool store_aux = false;
+          if (MODE == MODE_AG) {
+            const bool fullc = cc + 32 <= p.N;
+            if (p.bias) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                __align__(16) bf16 tt[8];
-                if (p.epi == 1) {
+              for (int j = 0; j < 32; ++j)
+                if (fullc || cc + j < p.N) v[j] += __bfloat162float(p.bias[cc + j]);
+            }
+            if (p.epi == 2 && row < p.M) {
+              const bf16* ax = p.aux + (long long)row * p.ldd + cc;
+              if (fullc && (p.ldd % 8 == 0)) {
 #pragma unroll
-                  for (int k = 0; k < 8; ++k) {
-                    tt[k] = __float2bfloat16(v[j + k]);
-                    v[j + k] = gelu_tanh(__bfloat162float(tt[k]));
-                  }
-                  *reinterpret_cast<uint4*>(ax + j) = *reinterpret_cast<uint4*>(tt);
-                } else {
-                  *reinterpret_cast<uint4*>(tt) = *reinterpret_cast<const uint4*>(ax + j);
+                for (int j = 0; j < 32; j += 8) {
+                  const uint4 raw = *reinterpret_cast<const uint4*>(ax + j);
+                  const bf16* tt = reinterpret_cast<const bf16*>(&raw);
 #pragma unroll
                   for (int k = 0; k < 8; ++k) v[j + k] *= gelu_tanh_grad(__bfloat162float(tt[k]));
                 }
-              }
-            } else
-            for (int j = 0; j < 32; ++j) {
-              if (!(fullc || col0 + j < p.N)) continue;
-              if (p.epi == 1) {
-                ax[j] = __float2bfloat16(v[j]);
-                v[j] = gelu_tanh(__bfloat162float(ax[j]));
               } else {
-                v[j] *= gelu_tanh_grad(__bfloat162float(ax[j]));
+                for (int j = 0; j < 32 && cc + j < p.N; ++j) v[j] *= gelu_tanh_grad(__bfloat162float(ax[j]));
               }
             }
+            store_aux = (p.epi == 1);
           }
-          dst = p.D + orow * p.ldd + col0;
-          ld = p.ldd;
-        }
-        if (fullc && (ld % 8 == 0)) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            __align__(16) bf16 tt[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) tt[k] = __float2bfloat16(v[j + k]);
-            *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<uint4*>(tt);
+          if (!vec_ok) {  // ragged edge: row-per-lane stores
+            const int dr = drow_base + lane;
+            if (dr < drows) {
+              for (int j = 0; j < 32 && cc + j < p.N; ++j) {
+                float a = v[j];
+                if (store_aux) {
+                  const bf16 z = __float2bfloat16(a);
+                  p.aux[(long long)row * p.ldd + cc + j] = z;
+                  a = gelu_tanh(__bfloat162float(z));
+                }
+                dst[(long long)dr * dld + cc + j] = __float2bfloat16(a);
+              }
+            }
+            continue;
           }
-        } else {
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) dst[j] = __float2bfloat16(v[j]);
+          // coalesced path: 64 columns of bf16 per flush (this chunk fills half of the staging rows)
+          if (store_aux) {
+            // pre-activation first (it is what the backward pass needs), through its own flush
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * k + 2 * j], v[8 * k + 2 * j + 1]);
+                w[j] = *reinterpret_cast<uint32_t*>(&h2);
+                v[8 * k + 2 * j] = gelu_tanh(__low2float(h2));
+                v[8 * k + 2 * j + 1] = gelu_tanh(__high2float(h2));
+              }
+              *reinterpret_cast<uint4*>(stage_tile + cstage_off(lane, k)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {  // 32 columns = 64 bytes per row: 4 lanes per row
+              const int rr = i * 8 + (lane >> 2), c16 = lane & 3;
+              if (i < 4 && row_base + rr < p.M)
+                *reinterpret_cast<uint4*>(p.aux + (long long)(row_base + rr) * p.ldd + cc + c16 * 8) =
+                    *reinterpret_cast<const uint4*>(stage_tile + cstage_off(rr, c16));
+            }
+            __syncwarp();
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * k + 2 * j], v[8 * k + 2 * j + 1]);
+              w[j] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            *reinterpret_cast<uint4*>(stage_tile + cstage_off(lane, h * 4 + k)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          if (h == 1) {
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3), c16 = lane & 7;
+              if (drow_base + rr < drows)
+                *reinterpret_cast<uint4*>(dst + (long long)(drow_base + rr) * dld + col0 + c16 * 8) =
+                    *reinterpret_cast<const uint4*>(stage_tile + cstage_off(rr, c16));
+            }
+            __syncwarp();
+          }
         }
       }
-      if (MODE == MODE_RS && owner != p.rank) {
-        // make this warp's 32 rows of partial sums visible at the owner, then publish the call
-        // number in the flag of (tile, row quarter): the owner's warp q needs exactly these rows
+      if (remote) {
+        // make this warp's rows of partial sums visible at the owner, then publish the call number in the
+        // flag of (tile, row quarter, column half): the owner's warp with the same (q, half) needs exactly these
         __threadfence_system();
         __syncwarp();
-        if (lane == 0) st_release_sys(p.tile_flag_remote[owner] + ltile * 4 + q, EPOCH);
+        if (lane == 0) st_release_sys(p.tile_flag_remote[owner] + fidx, EPOCH);
       }
       tc_fence_before();
-      mbar_arrive(&tempty[acc]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
   } else if (MODE == MODE_AG) {
-    // warps 6-7: pull the peers' row blocks into the local buffer, one 128-row block at a time
-    const int cw = threadIdx.x - 192;  // 0..63
+    // ---------------------------------------------------------------- all-gather copy (warps 6 to 9)
+    // PULL with plain 16-byte loads: the 128 copy threads of every CTA bring pieces (about 32 KB, whole rows) of
+    // the peers' row blocks into the local buffer, sixteen loads in flight per thread, in the order the tiles
+    // need them, and set the piece's flag. (Bulk async copies were measured slower here in both directions:
+    // a remote bulk load has a long latency and few can be in flight per SM, a remote bulk store completes late.)
+    constexpr int CT = Cfg::COPY_THREADS;
+    const int cw = threadIdx.x - 192;  // 0..CT-1
     if (blockIdx.x == 0 && warp == 6) {
-      // every rank's own rows are written once all ranks have reached this kernel
+      // a peer's rows may be read once every rank has reached this kernel
       const bool ok = peer_barrier_warp(p.peers, EPOCH, lane);
       if (lane == 0) {
         if (!ok && p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
@@ -395,40 +516,41 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     if (cw == 0 && !spin_until<false>(p.go_flag, EPOCH) && p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
-    asm volatile("bar.sync 1, 64;" ::: "memory");  // the two copy warps only
+    asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");  // the copy warps only
     const int remote_blocks = p.num_m_blocks - p.blocks_per_rank;
+    const int total = remote_blocks * cpb;
     const int chunks_per_row = p.K / 8;
-    for (int j = blockIdx.x; j < remote_blocks; j += gridDim.x) {
-      // j-th remote block in the order the tiles will need them
+    for (int c = blockIdx.x; c < total; c += gridDim.x) {
+      const int j = c / cpb, part = c - j * cpb;
       const int mb = (p.rank * p.blocks_per_rank + p.blocks_per_rank + j) % p.num_m_blocks;
-      const int owner = mb / p.blocks_per_rank;
-      const bf16* src = p.ag_src[owner] + (long long)mb * 128 * p.lda;
-      bf16* dst = p.ag_dst + (long long)mb * 128 * p.lda;
-      const int rows = min(128, p.M - mb * 128);
-      const int total = rows * chunks_per_row;
-      for (int e = cw; e < total; e += 64 * 4) {
-        uint4 v[4];
+      const int r0 = part * piece_rows;
+      const int nrows = min(piece_rows, 128 - r0);
+      const bf16* src = p.ag_src[mb / p.blocks_per_rank] + ((long long)mb * 128 + r0) * p.lda;
+      bf16* dst = p.ag_dst + ((long long)mb * 128 + r0) * p.lda;
+      const int n16 = nrows * chunks_per_row;
+      for (int e0 = 0; e0 < n16; e0 += CT * 16) {
+        uint4 v[16];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int ee = e + u * 64;
-          if (ee < total) {
-            const int rr = ee / chunks_per_row, cc = ee - rr * chunks_per_row;
+        for (int u = 0; u < 16; ++u) {
+          const int e = e0 + u * CT + cw;
+          if (e < n16) {
+            const int rr = e / chunks_per_row, cc = e - rr * chunks_per_row;
             v[u] = *reinterpret_cast<const uint4*>(src + (long long)rr * p.lda + cc * 8);
           }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int ee = e + u * 64;
-          if (ee < total) {
-            const int rr = ee / chunks_per_row, cc = ee - rr * chunks_per_row;
+        for (int u = 0; u < 16; ++u) {
+          const int e = e0 + u * CT + cw;
+          if (e < n16) {
+            const int rr = e / chunks_per_row, cc = e - rr * chunks_per_row;
             *reinterpret_cast<uint4*>(dst + (long long)rr * p.lda + cc * 8) = v[u];
           }
         }
       }
       __threadfence();
       fence_proxy_async_all();
-      asm volatile("bar.sync 1, 64;" ::: "memory");
-      if (cw == 0) st_release_gpu(p.chunk_flags + mb, EPOCH);
+      asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
+      if (cw == 0) st_release_gpu(p.chunk_flags[p.rank] + mb * 128 + part, EPOCH);
     }
   }
 
@@ -554,11 +676,11 @@ static int launch_comm(const CUtensorMap& ta, const CUtensorMap& tb, const CommG
   auto kern = gemm_comm_kernel<BN, B_MN, MODE>;
   static bool once = false;
   if (!once) {
-    int rc = set_dyn_smem(kern, CommCfg<BN>::SMEM_BYTES);
+    int rc = set_dyn_smem(kern, CommCfg<BN, MODE>::SMEM_BYTES);
     if (rc) return rc;
     once = true;
   }
-  kern<<<grid, 256, CommCfg<BN>::SMEM_BYTES, st>>>(ta, tb, p);
+  kern<<<grid, CommCfg<BN, MODE>::THREADS, CommCfg<BN, MODE>::SMEM_BYTES, st>>>(ta, tb, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
 }
@@ -603,7 +725,7 @@ int tnnb_ipc_close(void* p) {
 // where they are not needed. mode: 1 = all-gather->GEMM, 2 = GEMM->reduce-scatter.
 int tnnb_gemm_comm(int mode, int M, int N, int K, int b_mn, const void* A, long long lda, const void* B,
                    long long ldb, void* D, long long ldd, const void* bias, int tp, int rank, int rows_per_rank,
-                   unsigned int epoch, const void* epoch_ptr, void** barrier_flags, void** ag_src, void* chunk_flags,
+                   unsigned int epoch, const void* epoch_ptr, void** barrier_flags, void** ag_src, void** chunk_flags,
                    void* go_flag,
                    void** inbox_remote, void** inbox_local, void** tile_flag_remote, void** tile_flag_local,
                    long long ldi, int epi, void* aux, int* status, void* stream) {
@@ -628,7 +750,8 @@ int tnnb_gemm_comm(int mode, int M, int N, int K, int b_mn, const void* A, long 
     p.tile_flag_local[r] = tile_flag_local ? (const uint32_t*)tile_flag_local[r] : nullptr;
   }
   p.ag_dst = (bf16*)A; p.lda = lda;
-  p.chunk_flags = (uint32_t*)chunk_flags; p.go_flag = (uint32_t*)go_flag;
+  for (int r = 0; r < tp; ++r) p.chunk_flags[r] = chunk_flags ? (uint32_t*)((void**)chunk_flags)[r] : nullptr;
+  p.go_flag = (uint32_t*)go_flag;
   p.D = (bf16*)D; p.ldd = ldd; p.ldi = ldi;
   p.epi = epi; p.aux = (bf16*)aux;
   if (epi && !aux) return -5;

@@ -157,6 +157,20 @@ class PipelineTrainer:
                     a, b = (p * topo.dp + d_) * topo.tp + t, ((p + 1) * topo.dp + d_) * topo.tp + t
                     self.fwd_group[(a, b)] = dist.new_group([a, b])
                     self.bwd_group[(a, b)] = dist.new_group([a, b])
+        # NCCL builds a communicator on first use, which can take seconds; do it now, on every rank, so that no
+        # rank sits in that set-up while its tensor-parallel partner is already inside a fused kernel whose
+        # cross-rank waits are bounded.
+        if on_gpu:
+            tok = torch.zeros(1, device=self.device)
+            for (a, b), grp in sorted(self.fwd_group.items()):
+                if topo.rank in (a, b):
+                    for g in (grp, self.bwd_group[(a, b)]):
+                        if topo.rank == a:
+                            dist.send(tok, b, group=g)
+                        else:
+                            dist.recv(tok, a, group=g)
+            torch.cuda.synchronize()
+        dist.barrier()
 
     # ------------------------------------------------------------------ shapes of the boundaries
     def _boundary_shapes(self, mb_input_shape: Tuple[int, ...]) -> Dict[str, Tuple[int, ...]]:

@@ -119,7 +119,9 @@ class GatherSite:
             self.barrier = cc.heap.alloc((16,), torch.int32).zero_()
             self.src = ptr_array(cc.heap.peer_ptrs(self.buf, cc.ranks))
             self.bar = ptr_array(cc.heap.peer_ptrs(self.barrier, cc.ranks))
-            self.chunk_flags = torch.zeros(M // 128 + 1, dtype=torch.int32, device=cc.device)
+            # 128 piece flags per row block, written by the ranks that push their rows into this rank's buffer
+            self.piece_flags = cc.heap.alloc(((M // 128 + 1) * 128,), torch.int32).zero_()
+            self.chunk_flags = ptr_array(cc.heap.peer_ptrs(self.piece_flags, cc.ranks))
             self.go = torch.zeros(1, dtype=torch.int32, device=cc.device)
         else:
             self.buf = torch.empty(M, K, dtype=torch.bfloat16 if cc.device.type == "cuda" else torch.float32, device=cc.device)
@@ -143,7 +145,7 @@ class GatherSite:
         epi, aux = (1, gelu_preact) if gelu_preact is not None else (2, dgelu_of) if dgelu_of is not None else (0, None)
         rc = cc.lib.tnnb_gemm_comm(1, self.M, N, self.K, int(b_t), _lib.ptr(self.buf), self.K, _lib.ptr(w), w.stride(0),
                                    _lib.ptr(out), N, _lib.ptr(bias), cc.tp, cc.idx, self.rows, 0, _lib.ptr(cc.tick), self.bar, self.src,
-                                   _lib.ptr(self.chunk_flags), _lib.ptr(self.go), None, None, None, None, 0, epi,
+                                   self.chunk_flags, _lib.ptr(self.go), None, None, None, None, 0, epi,
                                    _lib.ptr(aux), _lib.ptr(_lib.status_word(cc.device)), _lib.stream())
         _lib.check_rc(rc, "tnnb_gemm_comm(all-gather)")
         LAUNCHES["count"] += 1
@@ -157,7 +159,7 @@ class ScatterSite:
         self.cc, self.M, self.N, self.epoch = cc, M, N, 0
         self.rows = M // cc.tp
         if cc.fused:
-            tiles = 4 * (self.rows // 128) * ((N + 127) // 128)  # one flag per (tile, 32-row quarter)
+            tiles = 8 * (self.rows // 128) * ((N + 127) // 128)  # one flag per (tile, 32-row quarter, column half)
             self.inbox = cc.heap.alloc((cc.tp, self.rows, N), torch.bfloat16)
             self.flags = cc.heap.alloc((cc.tp, tiles), torch.int32).zero_()
             ib, fl = cc.heap.peer_ptrs(self.inbox, cc.ranks), cc.heap.peer_ptrs(self.flags, cc.ranks)
