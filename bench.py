@@ -124,101 +124,121 @@ def run_ours(args):
     cfg = TrainingConfig.from_dict({"model_name": ms["zoo"], "batch_size": ms["per_gpu_batch"], "device_type": "CUDA",
                                     "optimizer": ms["optimizer"], "scheduler": {"type": "no_op"},
                                     "loss": {"type": "logsoftmax_crossentropy"}, "seed": 0})
-    if world > 1:
-        from tnn_b200.parallel.runtime import ParallelTrainer, default_layout
-        layout = args.parallelism or default_layout(world, ms["zoo"])
-        trainer = ParallelTrainer(cfg, layout=layout, log=False)
-    else:
-        from tnn_b200.trainer import Trainer
-        layout = "single"
-        trainer = Trainer(cfg, device=dev, log=False)
-
     is_lm = ms["seq_len"] is not None
-    if is_lm:
-        loader = SyntheticLoader((ms["seq_len"],), 50257, trainer.local_batch if world > 1 else ms["per_gpu_batch"],
-                                 10 ** 9, tokens=True, seed=1234 + getattr(trainer, 'data_rank', rank))
-    else:
-        shape = zoo.INPUT_SHAPES[ms["zoo"]]
-        classes = 1000 if ms["zoo"] == "imagenet_resnet50" else 100
-        loader = SyntheticLoader(shape, classes, trainer.local_batch if world > 1 else ms["per_gpu_batch"], 10 ** 9,
-                                 seed=1234 + getattr(trainer, 'data_rank', rank))
-    batches = iter(loader)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- warm-up (also captures the CUDA graph) ----
-    data, labels = next(batches)
-    if not args.no_graph:
-        trainer.enable_cuda_graph(data, labels)
-    for _ in range(max(3, args.warmup)):
+    def measure(layout, sample_clocks):
+        """Build the trainer for one layout, warm up, time K resident steps on the device and K end-to-end steps."""
+        if world > 1:
+            from tnn_b200.parallel.runtime import ParallelTrainer
+            trainer = ParallelTrainer(cfg, layout=layout, log=False)
+        else:
+            from tnn_b200.trainer import Trainer
+            trainer = Trainer(cfg, device=dev, log=False)
+        lb = trainer.local_batch if world > 1 else ms["per_gpu_batch"]
+        seed = 1234 + getattr(trainer, "data_rank", rank)
+        if is_lm:
+            loader = SyntheticLoader((ms["seq_len"],), 50257, lb, 10 ** 9, tokens=True, seed=seed)
+        else:
+            classes = 1000 if ms["zoo"] == "imagenet_resnet50" else 100
+            loader = SyntheticLoader(zoo.INPUT_SHAPES[ms["zoo"]], classes, lb, 10 ** 9, seed=seed)
+        batches = iter(loader)
+        # ---- warm-up (also captures the CUDA graph) ----
         data, labels = next(batches)
-        loss = trainer.train_step(data, labels)
-    barrier()
-    first_loss = float(loss.item())
+        if not args.no_graph:
+            trainer.enable_cuda_graph(data, labels)
+        for _ in range(max(3, args.warmup)):
+            data, labels = next(batches)
+            loss = trainer.train_step(data, labels)
+        barrier()
+        first_loss = float(loss.item())
+        # ---- device-timed region: K steps, batch resident, no host sync in between ----
+        sampler = ClockSampler(local) if (sample_clocks and rank == 0) else None
+        if sampler:
+            sampler.start()
+        time.sleep(0.3)
+        n0 = LAUNCHES["count"]
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            loss = trainer.step_resident()
+        e1.record()
+        barrier()
+        dev_ms = e0.elapsed_time(e1)
+        launches = (LAUNCHES["count"] - n0) if trainer.launches_per_step == 0 else trainer.launches_per_step * args.steps
+        # ---- end-to-end region: fresh pinned batch uploaded and loss read back every step ----
+        barrier()
+        t0 = time.perf_counter()
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record()
+        last = 0.0
+        for _ in range(args.steps):
+            data, labels = next(batches)
+            loss = trainer.train_step(data, labels)
+            last = float(loss.item())
+        e3.record()
+        barrier()
+        e2e_ms = max(e2.elapsed_time(e3), (time.perf_counter() - t0) * 1e3)
+        clocks = sampler.stop() if sampler else {}
+        if world > 1:
+            t = torch.tensor([dev_ms, e2e_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dev_ms, e2e_ms = float(t[0]), float(t[1])
+        from tnn_b200.ops import _lib
+        _lib.check_status(dev)
+        global_batch = trainer.global_batch if world > 1 else ms["per_gpu_batch"]
+        items = global_batch * ms["items_per_sample"]
+        res = {"layout": layout, "global_batch": global_batch, "dev_ms": dev_ms, "e2e_ms": e2e_ms,
+               "value": items * args.steps / (dev_ms / 1e3), "e2e": items * args.steps / (e2e_ms / 1e3),
+               "h2d": int(data.numel() * data.element_size() + labels.numel() * labels.element_size()), "launches": int(launches),
+               "first_loss": first_loss, "last_loss": last, "clocks": clocks}
+        trainer.close()
+        del trainer
+        torch.cuda.empty_cache()
+        barrier()
+        return res
 
-    # ---- device-timed region: K steps, batch resident, no host sync in between ----
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    time.sleep(0.3)
-    n0 = LAUNCHES["count"]
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        loss = trainer.step_resident()
-    e1.record()
-    barrier()
-    dev_ms = e0.elapsed_time(e1)
-    launches = (LAUNCHES["count"] - n0) if trainer.launches_per_step == 0 else trainer.launches_per_step * args.steps
+    from tnn_b200.parallel.runtime import default_layout
+    layout = args.parallelism or (named_layout(world, ms["zoo"]) if world > 1 else "single")
+    r = measure(layout, True)
+    alt = None
+    dp_layout = default_layout(world, ms["zoo"])
+    if world > 1 and not args.parallelism and layout != dp_layout:
+        alt = measure(dp_layout, False)  # the same job as pure data parallelism, for comparison
 
-    # ---- end-to-end region: fresh pinned batch uploaded and loss read back every step ----
-    barrier()
-    t0 = time.perf_counter()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    last = 0.0
-    for _ in range(args.steps):
-        data, labels = next(batches)
-        loss = trainer.train_step(data, labels)
-        last = float(loss.item())
-    e3.record()
-    barrier()
-    e2e_ms = max(e2.elapsed_time(e3), (time.perf_counter() - t0) * 1e3)
-    clocks = sampler.stop() if rank == 0 else {}
-
-    if world > 1:
-        t = torch.tensor([dev_ms, e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = float(t[0]), float(t[1])
-    from tnn_b200.ops import _lib
-    _lib.check_status(dev)
-
-    global_batch = (trainer.global_batch if world > 1 else ms["per_gpu_batch"])
-    items = global_batch * ms["items_per_sample"]
-    value = items * args.steps / (dev_ms / 1e3)
-    e2e = items * args.steps / (e2e_ms / 1e3)
-    h2d = int(data.numel() * data.element_size() + labels.numel() * labels.element_size())
     out = {
-        "metric": ms["metric"], "value": round(value, 1), "unit": ms["unit"], "n_gpus": world, "steps": args.steps,
-        "warmup": max(3, args.warmup), "ms_per_step": round(dev_ms / args.steps, 3), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None, "dtype": "bf16",
+        "metric": ms["metric"], "value": round(r["value"], 1), "unit": ms["unit"], "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": round(r["dev_ms"] / args.steps, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": (r["value"] / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None, "dtype": "bf16",
         "data": "synthetic (uniform random token ids / N(0,1) images, random-init weights)",
-        "config": {"model": args.model, "global_batch": global_batch, "seq_len": ms["seq_len"], "parallelism": layout,
+        "config": {"model": args.model, "global_batch": r["global_batch"], "seq_len": ms["seq_len"], "parallelism": layout,
                    "per_gpu_batch": ms["per_gpu_batch"], "optimizer": ms["optimizer"]["type"], "cuda_graph": not args.no_graph,
                    "l2": "working set (weights + activations, > 2 GB per step) far exceeds the 126 MB L2; no flush needed"},
-        "clocks": clocks,
-        "e2e": {"value": round(e2e, 1), "unit": ms["unit"], "ms_per_step": round(e2e_ms / args.steps, 3),
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
-        "gpu_launches": int(launches), "loss_first": round(first_loss, 4), "loss_last": round(last, 4), "impl": "ours",
+        "clocks": r["clocks"],
+        "e2e": {"value": round(r["e2e"], 1), "unit": ms["unit"], "ms_per_step": round(r["e2e_ms"] / args.steps, 3),
+                "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": 4},
+        "gpu_launches": r["launches"], "loss_first": round(r["first_loss"], 4), "loss_last": round(r["last_loss"], 4), "impl": "ours",
     }
+    if alt is not None:
+        out["alt"] = {"parallelism": alt["layout"], "value": round(alt["value"], 1), "ms_per_step": round(alt["dev_ms"] / args.steps, 3),
+                      "e2e_value": round(alt["e2e"], 1), "note": "same model, batch and steps as pure data parallelism (fused reduce + AdamW + broadcast kernel)"}
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def named_layout(world: int, zoo_name: str) -> str:
+    """The layout the benchmark configuration names: GPT-2 runs tensor-parallel pairs (fused all-gather->GEMM and
+    GEMM->reduce-scatter) combined with data parallelism; the CNNs are data parallel."""
+    if "gpt2" in zoo_name and world % 2 == 0:
+        return "tp2" if world == 2 else f"tp2dp{world // 2}"
+    return f"dp{world}"
 
 
 def main():
