@@ -665,6 +665,27 @@ dp_step_kernel(const DpParams p) {
   }
 }
 
+// ===================================================== stream-ordered flag wait / set
+// A one-thread kernel that makes the stream wait until a 32-bit flag (local or peer memory) has reached
+// `want`, for at most `timeout_ns`; on expiry it records ST_TIMEOUT_PEER in the status word and returns,
+// so the stream and the context stay usable. With tnnb_flag_set it gives ranks a way to order their
+// streams against each other without a collective call.
+__global__ void flag_wait_kernel(const uint32_t* flag, uint32_t want, unsigned long long timeout_ns, int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 0;; ++i) {
+    if (static_cast<int32_t>(ld_acquire_sys(flag) - want) >= 0) return;
+    if ((i & 15u) == 15u && globaltimer_ns() - t0 > timeout_ns) {
+      if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER);
+      return;
+    }
+    __nanosleep(100);
+  }
+}
+__global__ void flag_set_kernel(uint32_t* flag, uint32_t value) {
+  __threadfence_system();
+  st_release_sys(flag, value);
+}
+
 template <typename K>
 static int set_dyn_smem(K kern, int bytes) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
@@ -789,6 +810,21 @@ int tnnb_gemm_comm(int mode, int M, int N, int K, int b_mn, const void* A, long 
   }
 #undef CL
   return -2;
+}
+
+// Stream-ordered bounded wait on / release store to a flag; see flag_wait_kernel. timeout_ns is capped at 10 s.
+int tnnb_flag_wait(const void* flag, unsigned int want, unsigned long long timeout_ns, int* status, void* stream) {
+  if (!flag || ((uintptr_t)flag & 3)) return -3;
+  if (timeout_ns > 10000000000ull) timeout_ns = 10000000000ull;
+  flag_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((const uint32_t*)flag, want, timeout_ns, status);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e - 1000;
+}
+int tnnb_flag_set(void* flag, unsigned int value, void* stream) {
+  if (!flag || ((uintptr_t)flag & 3)) return -3;
+  flag_set_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((uint32_t*)flag, value);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e - 1000;
 }
 
 int tnnb_dp_step(int dp, int dp_rank, void** barrier_flags, void** grads, void** params_lp, void** params_f32,
