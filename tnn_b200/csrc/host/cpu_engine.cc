@@ -6,6 +6,7 @@
 // :66-210, batchnorm :378-511, layernorm :513-614, conv :617-734) and its loss /
 // optimizer kernels (src/nn/loss_impl/cpu/loss_ops.cpp, optimizers_impl/cpu).
 #include <pybind11/numpy.h>
+#include <pybind11/stl.h>
 #include <pybind11/pybind11.h>
 
 #include <algorithm>
