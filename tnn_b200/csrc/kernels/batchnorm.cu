@@ -18,16 +18,38 @@ namespace tnnb {
 
 typedef __nv_bfloat16 bf16;
 
-// Block = 32 channel groups of 8 (256 channels) x 8 row lanes. grid = (ceil(C/256), row splits).
+// Thread layout of all kernels here: a block of 256 threads is `cl` channel groups of 8 channels x `256 / cl` row
+// lanes, with cl = the largest power of two <= min(32, C / 8), so that narrow tensors (C = 64: 8 groups x 32 row
+// lanes) keep every thread busy. grid = (ceil(C / 8 / cl), row splits).
+struct BnLane {
+  int cl, cx, ry, nry, c0;
+};
+__device__ __forceinline__ BnLane bn_lane(int C) {
+  BnLane l;
+  const int groups = C >> 3;
+  l.cl = 32;
+  while (l.cl > groups) l.cl >>= 1;
+  l.cx = threadIdx.x & (l.cl - 1);
+  l.ry = threadIdx.x / l.cl;
+  l.nry = 256 / l.cl;
+  l.c0 = (blockIdx.x * l.cl + l.cx) * 8;
+  return l;
+}
+static int bn_cl(int C) {
+  int cl = 32;
+  while (cl > (C >> 3)) cl >>= 1;
+  return cl < 1 ? 1 : cl;
+}
+
 // ws: double[2*C] (sum, sum of squares) - or (sum dy, sum dy*xhat) for the backward.
 template <bool BWD>
 __global__ void __launch_bounds__(256)
 bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
                  const float* __restrict__ mean, const float* __restrict__ rstd, double* __restrict__ ws, long long M,
                  int C, long long rows_per_block, int relu) {
-  __shared__ float red[2][8][32][9];
-  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
-  const int c0 = (blockIdx.x * 32 + cx) * 8;
+  __shared__ float red[2][256][9];
+  const BnLane ln = bn_lane(C);
+  const int cx = ln.cx, ry = ln.ry, c0 = ln.c0, nry = ln.nry;
   const long long r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
   float a[8], b[8];
 #pragma unroll
@@ -38,7 +60,7 @@ bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const 
 #pragma unroll
       for (int k = 0; k < 8; ++k) mu[k] = mean[c0 + k], rs[k] = rstd[c0 + k];
     }
-    for (long long r = r0 + ry; r < r1; r += 8) {
+    for (long long r = r0 + ry; r < r1; r += nry) {
       uint4 raw = *reinterpret_cast<const uint4*>(x + r * C + c0);
       const bf16* xv = reinterpret_cast<const bf16*>(&raw);
       if (!BWD) {
@@ -65,14 +87,13 @@ bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const 
     }
   }
 #pragma unroll
-  for (int k = 0; k < 8; ++k) red[0][ry][cx][k] = a[k], red[1][ry][cx][k] = b[k];
+  for (int k = 0; k < 8; ++k) red[0][threadIdx.x][k] = a[k], red[1][threadIdx.x][k] = b[k];
   __syncthreads();
-  if (ry < 2 && c0 < C) {
+  if (ry < 2 && c0 < C) {  // row lane 0 sums the `sum` partials, row lane 1 the second moment's
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       float s = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) s += red[ry][j][cx][k];
+      for (int j = 0; j < nry; ++j) s += red[ry][j * ln.cl + cx][k];
       atomicAdd(ws + (long long)ry * C + c0 + k, (double)s);
     }
   }
@@ -83,8 +104,8 @@ bn_fwd_apply_kernel(const bf16* __restrict__ x, bf16* __restrict__ yout, const b
                     const bf16* __restrict__ beta, const double* __restrict__ ws, float* __restrict__ mean_o,
                     float* __restrict__ rstd_o, float* __restrict__ run_mean, float* __restrict__ run_var, long long M, int C,
                     long long rows_per_block, float eps, float momentum, int relu, int training) {
-  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
-  const int c0 = (blockIdx.x * 32 + cx) * 8;
+  const BnLane ln = bn_lane(C);
+  const int ry = ln.ry, c0 = ln.c0, nry = ln.nry;
   if (c0 >= C) return;
   float sc[8], sh[8];
 #pragma unroll
@@ -114,7 +135,7 @@ bn_fwd_apply_kernel(const bf16* __restrict__ x, bf16* __restrict__ yout, const b
     sh[k] = b - mu * sc[k];
   }
   const long long r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
-  for (long long r = r0 + ry; r < r1; r += 8) {
+  for (long long r = r0 + ry; r < r1; r += nry) {
     uint4 raw = *reinterpret_cast<const uint4*>(x + r * C + c0);
     const bf16* xv = reinterpret_cast<const bf16*>(&raw);
     __align__(16) bf16 o[8];
@@ -132,8 +153,8 @@ bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, con
                     const bf16* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ rstd,
                     const double* __restrict__ ws, bf16* __restrict__ dx, float* __restrict__ dgamma,
                     float* __restrict__ dbeta, long long M, int C, long long rows_per_block, int relu) {
-  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
-  const int c0 = (blockIdx.x * 32 + cx) * 8;
+  const BnLane ln = bn_lane(C);
+  const int ry = ln.ry, c0 = ln.c0, nry = ln.nry;
   if (c0 >= C) return;
   float mu[8], rs[8], k1[8], sg[8], sgx[8];
 #pragma unroll
@@ -149,7 +170,7 @@ bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, con
     }
   }
   const long long r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
-  for (long long r = r0 + ry; r < r1; r += 8) {
+  for (long long r = r0 + ry; r < r1; r += nry) {
     uint4 raw = *reinterpret_cast<const uint4*>(x + r * C + c0);
     const bf16* xv = reinterpret_cast<const bf16*>(&raw);
     uint4 graw = *reinterpret_cast<const uint4*>(dy + r * C + c0);
@@ -170,10 +191,12 @@ bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, con
 }
 
 static void bn_grid(long long M, int C, dim3& grid, long long& rpb) {
-  const int gx = (C + 255) / 256;
-  int gy = (4 * 148 + gx - 1) / gx;
+  const int cl = bn_cl(C);
+  const int gx = ((C >> 3) + cl - 1) / cl;
+  int gy = (6 * 148 + gx - 1) / gx;
   rpb = (M + gy - 1) / gy;
-  if (rpb < 32) rpb = 32;
+  const int nry = 256 / cl;
+  if (rpb < 4 * nry) rpb = 4 * nry;
   gy = (int)((M + rpb - 1) / rpb);
   grid = dim3(gx, gy);
 }

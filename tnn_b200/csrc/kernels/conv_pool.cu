@@ -22,30 +22,56 @@ struct ConvGeo {
   int Kld;  // row pitch of the patch matrix in elements (>= KH*KW*C, multiple of 8)
 };
 
-// VEC = 8 (C % 8 == 0, 16-byte moves) or 1.
+// VEC = 8: C % 8 == 0, one 16-byte move per thread. VEC = 1 (any C, e.g. the 3-channel stem): each thread still
+// writes one 16-byte group of eight consecutive columns of the row (Kld % 8 == 0), gathering its eight elements
+// with scalar loads - the write side, which is the larger one, stays coalesced.
 template <int VEC>
 __global__ void im2col_kernel(const bf16* __restrict__ x, bf16* __restrict__ cols, ConvGeo g) {
-  const int cv = g.C / VEC;
-  const long long per_row = (long long)g.KH * g.KW * cv;
-  const long long total = (long long)g.N * g.OH * g.OW * per_row;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)(i % cv);
-    long long r = i / cv;
-    const int kw = (int)(r % g.KW); r /= g.KW;
-    const int kh = (int)(r % g.KH); r /= g.KH;
-    const long long pix = r;  // (n, oh, ow)
-    const int ow = (int)(pix % g.OW);
-    const int oh = (int)((pix / g.OW) % g.OH);
-    const int n = (int)(pix / ((long long)g.OW * g.OH));
-    const int ih = oh * g.SH + kh - g.PH, iw = ow * g.SW + kw - g.PW;
-    bf16* dst = cols + pix * g.Kld + ((long long)(kh * g.KW + kw) * g.C) + c * VEC;
-    const bool in = ih >= 0 && ih < g.H && iw >= 0 && iw < g.W;
-    if (VEC == 8) {
+  if (VEC == 8) {
+    const int cv = g.C / 8;
+    const long long per_row = (long long)g.KH * g.KW * cv;
+    const long long total = (long long)g.N * g.OH * g.OW * per_row;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+      const int c = (int)(i % cv);
+      long long r = i / cv;
+      const int kw = (int)(r % g.KW); r /= g.KW;
+      const int kh = (int)(r % g.KH); r /= g.KH;
+      const long long pix = r;  // (n, oh, ow)
+      const int ow = (int)(pix % g.OW);
+      const int oh = (int)((pix / g.OW) % g.OH);
+      const int n = (int)(pix / ((long long)g.OW * g.OH));
+      const int ih = oh * g.SH + kh - g.PH, iw = ow * g.SW + kw - g.PW;
+      bf16* dst = cols + pix * g.Kld + ((long long)(kh * g.KW + kw) * g.C) + c * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (in) v = *reinterpret_cast<const uint4*>(x + (((long long)n * g.H + ih) * g.W + iw) * g.C + c * 8);
+      if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) v = *reinterpret_cast<const uint4*>(x + (((long long)n * g.H + ih) * g.W + iw) * g.C + c * 8);
       *reinterpret_cast<uint4*>(dst) = v;
-    } else {
-      *dst = in ? x[(((long long)n * g.H + ih) * g.W + iw) * g.C + c] : __float2bfloat16(0.f);
+    }
+  } else {
+    const int K = g.KH * g.KW * g.C;
+    const int groups = g.Kld / 8;  // 16-byte groups per row, padding columns included (written as zeros)
+    const long long total = (long long)g.N * g.OH * g.OW * groups;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+      const int gi = (int)(i % groups);
+      const long long pix = i / groups;
+      const int ow = (int)(pix % g.OW);
+      const int oh = (int)((pix / g.OW) % g.OH);
+      const int n = (int)(pix / ((long long)g.OW * g.OH));
+      const bf16* img = x + (long long)n * g.H * g.W * g.C;
+      __align__(16) bf16 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = gi * 8 + j;
+        bf16 e = __float2bfloat16(0.f);
+        if (k < K) {
+          const int c = k % g.C;
+          const int kw = (k / g.C) % g.KW;
+          const int kh = k / (g.C * g.KW);
+          const int ih = oh * g.SH + kh - g.PH, iw = ow * g.SW + kw - g.PW;
+          if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) e = img[((long long)ih * g.W + iw) * g.C + c];
+        }
+        v[j] = e;
+      }
+      *reinterpret_cast<uint4*>(cols + pix * g.Kld + gi * 8) = *reinterpret_cast<const uint4*>(v);
     }
   }
 }
@@ -216,8 +242,9 @@ int tnnb_im2col(const void* x, void* cols, int N, int H, int W, int C, int KH, i
                 int Kld, void* stream) {
   ConvGeo g = make_geo(N, H, W, C, KH, KW, SH, SW, PH, PW, Kld);
   if (g.OH <= 0 || g.OW <= 0 || Kld < KH * KW * C) return -2;
-  const bool vec = (C % 8 == 0) && (Kld % 8 == 0) && !(((uintptr_t)x | (uintptr_t)cols) & 15);
-  const long long total = (long long)N * g.OH * g.OW * KH * KW * (vec ? C / 8 : C);
+  if (Kld % 8 || ((uintptr_t)cols & 15)) return -3;
+  const bool vec = (C % 8 == 0) && !((uintptr_t)x & 15);
+  const long long total = (long long)N * g.OH * g.OW * (vec ? (long long)KH * KW * (C / 8) : Kld / 8);
   if (vec) im2col_kernel<8><<<grid1d(total, 256), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)cols, g);
   else im2col_kernel<1><<<grid1d(total, 256), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)cols, g);
   RC_LAST();

@@ -575,14 +575,17 @@ class Conv2D(Layer):
     def forward(self, inputs, ctx):
         x = inputs[0].contiguous()
         ctx["x"] = x
+        # in training the patch matrix of the forward pass is kept for the weight gradient
+        keep = ctx if (self.training and self.grads[0] is not None) else None
         return raw.conv2d_fwd(x, self.params[0], self.params[1] if self.use_bias else None,
-                              (self.stride_h, self.stride_w), (self.pad_h, self.pad_w))
+                              (self.stride_h, self.stride_w), (self.pad_h, self.pad_w), keep=keep)
 
     def backward(self, grad, ctx):
         x = ctx["x"]
         grad = grad.contiguous()
         if self.grads[0] is not None:
-            raw.conv2d_wgrad(x, grad, self.grads[0], (self.stride_h, self.stride_w), (self.pad_h, self.pad_w))
+            raw.conv2d_wgrad(x, grad, self.grads[0], (self.stride_h, self.stride_w), (self.pad_h, self.pad_w),
+                             cols=ctx.pop("cols", None))
             if self.use_bias:
                 raw.colsum_accum(_flat2d(grad), self.grads[1])
         if ctx.get("_skip_dgrad"):

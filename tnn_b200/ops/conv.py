@@ -60,7 +60,9 @@ def _w2d(w: torch.Tensor, K: int) -> torch.Tensor:
     return pad[:, :K]
 
 
-def conv2d_fwd(x, w, bias, stride, pad, relu=False):
+def conv2d_fwd(x, w, bias, stride, pad, relu=False, keep=None):
+    """``keep`` (a dict) receives the patch matrix under ``"cols"`` so that the weight-gradient pass can reuse
+    it instead of gathering the patches a second time (it costs memory, not bandwidth)."""
     stride, pad = tuple(stride), tuple(pad)
     n, h, wd, c, o, kh, kw, oh, ow = _geom(x.shape, w.shape, stride, pad)
     if _is_pointwise(kh, kw, stride, pad) and c % 8 == 0:
@@ -68,6 +70,8 @@ def conv2d_fwd(x, w, bias, stride, pad, relu=False):
     else:
         cols, K = im2col(x, kh, kw, stride, pad, oh, ow)
         a = cols[:, :K]
+        if keep is not None:
+            keep["cols"] = cols
     y = gemm(a, _w2d(w, K), bias=bias, relu=relu)
     return y.view(n, oh, ow, o)
 
@@ -90,7 +94,7 @@ def conv2d_dgrad(dy, w, x_shape, stride, pad):
     return dx
 
 
-def conv2d_wgrad(x, dy, dw, stride, pad):
+def conv2d_wgrad(x, dy, dw, stride, pad, cols=None):
     stride, pad = tuple(stride), tuple(pad)
     n, h, wd, c, o, kh, kw, oh, ow = _geom(x.shape, dw.shape, stride, pad)
     dy2 = dy.reshape(-1, o)
@@ -98,7 +102,8 @@ def conv2d_wgrad(x, dy, dw, stride, pad):
     if _is_pointwise(kh, kw, stride, pad) and c % 8 == 0:
         a = x.reshape(-1, c)
     else:
-        cols, _ = im2col(x, kh, kw, stride, pad, oh, ow)
+        if cols is None:
+            cols, _ = im2col(x, kh, kw, stride, pad, oh, ow)
         a = cols[:, :K]
     if K % 4 == 0:
         gemm(dy2, a, a_t=True, b_t=True, out=dw.view(o, K), atomic=True)

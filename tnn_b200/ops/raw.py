@@ -438,11 +438,12 @@ def _to_nchw(x):
 
 
 def conv2d_fwd(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], stride, pad,
-               relu: bool = False) -> torch.Tensor:
-    """NHWC x [N,H,W,C] * OHWI w [O,KH,KW,C] -> [N,OH,OW,O] (zero padding, no dilation)."""
+               relu: bool = False, keep: Optional[dict] = None) -> torch.Tensor:
+    """NHWC x [N,H,W,C] * OHWI w [O,KH,KW,C] -> [N,OH,OW,O] (zero padding, no dilation). On CUDA ``keep`` receives
+    the patch matrix (``keep["cols"]``) for :func:`conv2d_wgrad`."""
     if x.is_cuda and x.dtype == torch.bfloat16:
         from . import conv
-        return conv.conv2d_fwd(x, w, bias, stride, pad, relu)
+        return conv.conv2d_fwd(x, w, bias, stride, pad, relu, keep)
     y = torch.nn.functional.conv2d(_to_nchw(x).float(), w.permute(0, 3, 1, 2).float(),
                                    None if bias is None else bias.float(), stride, pad)
     if relu:
@@ -459,11 +460,11 @@ def conv2d_dgrad(dy: torch.Tensor, w: torch.Tensor, x_shape, stride, pad) -> tor
     return dx.permute(0, 2, 3, 1).contiguous().to(dy.dtype)
 
 
-def conv2d_wgrad(x: torch.Tensor, dy: torch.Tensor, dw: torch.Tensor, stride, pad) -> None:
+def conv2d_wgrad(x: torch.Tensor, dy: torch.Tensor, dw: torch.Tensor, stride, pad, cols: Optional[torch.Tensor] = None) -> None:
     """dw (fp32, [O,KH,KW,C]) += correlation of x with dy."""
     if x.is_cuda and x.dtype == torch.bfloat16:
         from . import conv
-        return conv.conv2d_wgrad(x, dy, dw, stride, pad)
+        return conv.conv2d_wgrad(x, dy, dw, stride, pad, cols)
     o, kh, kw, c = dw.shape
     g = torch.nn.grad.conv2d_weight(_to_nchw(x).float(), (o, c, kh, kw), _to_nchw(dy).float(), stride, pad)
     dw.add_(g.permute(0, 2, 3, 1).to(dw.dtype))
