@@ -29,6 +29,8 @@ def main():
     for _ in range(3):
         seq = torch.randint(0, 97, (t.local_batch, 129), generator=gen)
         losses.append(float(t.train_step(seq[:, :-1].contiguous(), seq[:, 1:].contiguous()).item()))
+    if mode == "tp":
+        t.save_snapshot(out + ".tnng")  # gathers the shards: one file that an unsharded job can load
     allm = [None] * world
     dist.all_gather_object(allm, (losses, t.graph.master_flat.clone()))
     if rank == 0:

@@ -65,3 +65,13 @@ def test_tp2_equals_single_process(tmp_path):
     o, n, shape, _ = lay["t_block_0_mlp_fc1"][0]
     got = torch.cat([m[o:o + n].view(shape) for m in res["masters"]], 0)
     assert torch.allclose(got, full["t_block_0_mlp_fc1"].params[0], atol=2e-3), float((got - full["t_block_0_mlp_fc1"].params[0]).abs().max())
+    # the gathered checkpoint is an ordinary TNNG file of the unsharded model: every parameter matches the reference run
+    from tnn_b200.nn.graph import Graph
+    loaded = Graph.load_state(str(tmp_path / "tp.pt") + ".tnng", device="cpu")
+    ref_layers = {l.name: l for l in g.layers()}
+    n_checked = 0
+    for l in loaded.layers():
+        for a, b in zip(l.params, ref_layers[l.name].params):
+            assert a.shape == b.shape and torch.allclose(a.float(), b.float(), atol=3e-3), l.name
+            n_checked += 1
+    assert n_checked > 20

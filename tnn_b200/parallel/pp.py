@@ -294,16 +294,29 @@ class PipelineTrainer:
             if steps is None and epoch >= cfg.epochs:
                 return {"steps": self.global_step, "loss": last}
 
-    def save_stage(self, path: str) -> str:
-        """Write this stage's graph state (the counterpart of the reference's SAVE_TO_FILE command:
-        every worker saves its own stage, include/distributed/worker.hpp:279-296)."""
+    def save_stage(self, path: str, gather_tp: bool = True) -> str:
+        """Write this stage's graph state to ``<path>.stage<i>`` (the counterpart of the reference's SAVE_TO_FILE
+        command: every worker saves its own stage, include/distributed/worker.hpp:279-296). Tensor-parallel
+        shards are gathered to full tensors first, so a stage file is the same whatever the tensor-parallel width."""
         g = self.stage
         if g.master_flat is not g.params_flat and isinstance(self.optimizer, FusedDPOptimizer):
             mine = torch.zeros_like(g.trainable_mask)
             for s in self.optimizer.sites:
                 mine[s["lo"]:s["hi"]] = True
             g.master_flat.copy_(torch.where(mine, g.master_flat, g.params_flat.float()))
-        name = f"{path}.stage{self.topo.pp_idx}" + (f".tp{self.topo.tp_idx}" if self.topo.tp > 1 else "")
+        name = f"{path}.stage{self.topo.pp_idx}"
+        if self.topo.tp > 1 and gather_tp:
+            from .tp import gather_full_state
+            ratios = list(self.cfg.parallel.partition_ratios) or block_aligned_ratios(zoo.create(self.cfg.model_name), self.topo.pp)
+            full_stage = partition_graph(zoo.create(self.cfg.model_name), ratios)[self.topo.pp_idx]
+            full_stage.compile(device="cpu", seed=self.cfg.seed)
+            gather_full_state(g, full_stage, self.topo)
+            if self.topo.dp_idx == 0 and self.topo.tp_idx == 0:
+                os.makedirs(os.path.dirname(name) or ".", exist_ok=True)
+                full_stage.save_state(name)
+            return name
+        if self.topo.tp > 1:
+            name += f".tp{self.topo.tp_idx}"
         if self.topo.dp_idx == 0:
             os.makedirs(os.path.dirname(name) or ".", exist_ok=True)
             g.save_state(name)

@@ -148,17 +148,31 @@ class ParallelTrainer(Trainer):
             l = flat[topo.tp_idx * rows:(topo.tp_idx + 1) * rows]
         return super()._fwd_bwd(d, l, scale)
 
-    def save_snapshot(self, path=None, with_optimizer: bool = False) -> str:
-        """Rank 0 of the stage writes the TNNG file. With the sharded optimizer every rank holds
-        fp32 master values only for its own slice, so the other slices are refreshed from the
-        (broadcast) compute copy first. Tensor-parallel shards are written as held by this rank."""
+    def _refresh_master(self) -> None:
+        """With the sharded optimizer every rank holds fp32 master values only for its own slice: refresh the
+        other slices from the (broadcast) compute copy."""
         g = self.graph
         if g.master_flat is not g.params_flat:
             mine = torch.zeros_like(g.trainable_mask)
             for s in getattr(self.optimizer, "sites", []):
                 mine[s["lo"]:s["hi"]] = True
             g.master_flat.copy_(torch.where(mine, g.master_flat, g.params_flat.float()))
+
+    def save_snapshot(self, path=None, with_optimizer: bool = False, gather_tp: bool = True) -> str:
+        """Writes ONE TNNG file that any layout (or the reference) can read: tensor-parallel shards are gathered
+        to full tensors first (collective over the tensor-parallel group), then the first rank writes.
+        ``gather_tp=False`` writes each shard as held, to ``<path>.tp<i>``."""
+        self._refresh_master()
         path = path or self.snapshot_path()
+        if self.topo.tp > 1 and gather_tp:
+            from ..models import zoo
+            from .tp import gather_full_state
+            full = zoo.create(self.cfg.model_name).compile(device="cpu", seed=self.cfg.seed)
+            gather_full_state(self.graph, full, self.topo)
+            if self.topo.dp_idx == 0 and self.topo.tp_idx == 0:
+                os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+                full.save_state(path)
+            return path
         if self.topo.tp > 1:
             path = f"{path}.tp{self.topo.tp_idx}"
         if self.topo.dp_idx == 0:

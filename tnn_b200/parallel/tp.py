@@ -222,6 +222,47 @@ def _shard_of(layer, spec_name: str, full: torch.Tensor, tp: int, t: int) -> tor
     return full
 
 
+def _unshard(layer, spec_name: str, parts: List[torch.Tensor], tp: int) -> torch.Tensor:
+    """Inverse of :func:`_shard_of`: the full parameter from the ``tp`` shards (in rank order)."""
+    from ..nn.blocks import FlashAttentionBlock
+    if isinstance(layer, FlashAttentionBlock):
+        if spec_name in ("qkv_weight", "qkv_bias"):
+            Es = parts[0].shape[0] // 3
+            return torch.cat([p[k * Es:(k + 1) * Es] for k in range(3) for p in parts], 0)  # q of every rank, then k, then v
+        if spec_name == "out_weight":
+            return torch.cat(parts, 1)
+        return parts[0]
+    mode = getattr(layer, "tp_mode", None)
+    if mode == "col":
+        return torch.cat(parts, 0)
+    if mode == "row" and spec_name == "weight":
+        return torch.cat(parts, 1)
+    return parts[0]
+
+
+def gather_full_state(tp_graph: Graph, full_graph: Graph, topo, group=None) -> None:
+    """Fill ``full_graph`` (the same model without tensor parallelism, same layer names) from the shards the ranks
+    of a tensor-parallel group hold - what a checkpoint that other layouts can read needs. Collective over the
+    group; every rank ends up with the full parameters in ``full_graph``."""
+    group = group if group is not None else topo.tp_group
+    full = {l.name: l for l in full_graph.layers()}
+    for l in tp_graph.layers():
+        dst = full[l.name]
+        for (o, n, shape, _), spec, (fo, fn, fshape, _) in zip(tp_graph.layer_slices[id(l)], l.param_specs(),
+                                                              full_graph.layer_slices[id(dst)]):
+            mine = tp_graph.master_flat[o:o + n].view(shape).contiguous()
+            if spec.sharded and topo.tp > 1:
+                parts = [torch.empty_like(mine) for _ in range(topo.tp)]
+                dist.all_gather(parts, mine, group=group)
+                whole = _unshard(l, spec.name, parts, topo.tp)
+            else:
+                whole = mine
+            if tuple(whole.shape) != tuple(fshape):
+                raise ValueError(f"{l.name}.{spec.name}: gathered shape {tuple(whole.shape)} != {tuple(fshape)}")
+            full_graph.master_flat[fo:fo + fn].copy_(whole.reshape(-1).to(full_graph.master_flat.device))
+    full_graph.sync_params_from_master()
+
+
 def copy_full_to_shards(tp_graph: Graph, full_graph: Graph, topo) -> None:
     """Initialise a tensor-parallel graph from an unsharded one with the same layer names (used to
     load a full checkpoint into a tensor-parallel job and by the equivalence tests)."""
