@@ -69,3 +69,29 @@ def test_every_config_file_parses():
         if name.endswith(".json"):
             cfg = TrainingConfig.load_from_json(os.path.join(ROOT, "configs", name))
             assert cfg.batch_size > 0 and cfg.model_name
+
+
+def test_layer_profiler_records_compute_events_and_log_lines(tmp_path):
+    from tnn_b200.models import zoo
+    from tnn_b200.trainer import Trainer
+    from tnn_b200.utils.config import TrainingConfig
+
+    zoo.register_model("tiny_prof", lambda: zoo.gpt2(64, 1, 2, "t", seq_len=16, vocab=37, drop=0.0))
+    cfg = TrainingConfig.from_dict({"model_name": "tiny_prof", "batch_size": 2, "device_type": "CPU", "profiler_type": "CUMULATIVE",
+                                    "optimizer": {"type": "sgd", "learning_rate": 0.01}})
+    t = Trainer(cfg, log=False)
+    seq = torch.randint(0, 37, (2, 17))
+    for _ in range(2):
+        t.train_step(seq[:, :-1].contiguous(), seq[:, 1:].contiguous())
+    lp = t.layer_profiler
+    names = {n for (n, _ph) in lp.totals}
+    assert any("block_0" in n for n in names) and all(calls == 2 for _, calls in lp.totals.values())   # cumulative over 2 steps
+    assert {ph for (_n, ph) in lp.totals} == {"forward", "backward"}
+    table = lp.table()
+    assert "fwd ms" in table and "total" in table
+    log = lp.write_log(str(tmp_path / "profiler.log"))
+    first = open(log).readline()
+    assert first.startswith("Event: ") and "Type: COMPUTE" in first and "Duration:" in first
+    from tnn_b200.utils.profiling import merge_across_ranks
+    assert len(merge_across_ranks(lp)) == len(lp.profiler)      # single process: nothing to merge
+    t.close()

@@ -75,3 +75,21 @@ def test_adam_matches_reference_formula():
     mh, vh = g, g * g
     exp = torch.tensor([1.0, -2.0]) - 0.1 * mh / (vh.sqrt() + 1e-8) - 0.01 * 0.1 * torch.tensor([1.0, -2.0])
     assert torch.allclose(w, exp, atol=1e-6)
+
+
+def test_named_ops_api():
+    from tnn_b200.ops import tensor_ops as T
+
+    a, b, c = torch.tensor([1.0, -2.0, 3.0]), torch.tensor([4.0, 5.0, -6.0]), torch.tensor([0.5, 0.5, 0.5])
+    assert torch.equal(T.fmadd(a, b, c), a * b + c) and torch.equal(T.fnmadd(a, b, c), c - a * b) and torch.equal(T.fmsub(a, b, c), a * b - c)
+    assert torch.equal(T.sub_mul_scalar(a, b, 2.0), (a - b) * 2) and torch.equal(T.mul_add_scalar(a, 2.0, 1.0), a * 2 + 1)
+    y = c.clone()
+    assert torch.equal(T.axpy(2.0, a, y), c + 2 * a) and y is not c
+    assert float(T.dot_product(a, b)) == -24.0 and float(T.norm_squared(a)) == 14.0 and float(T.sum_squared_diff(a, 1.0)) == 13.0
+    assert torch.equal(T.scalar_max(a, 0.0), torch.tensor([1.0, 0.0, 3.0])) and torch.equal(T.greater(a, b), torch.tensor([0.0, 0.0, 1.0]))
+    x = torch.tensor([1, 256, 0x01020304], dtype=torch.int32)
+    assert T.bswap(x).tolist() == [0x01000000, 0x00010000, 0x04030201] and torch.equal(T.bswap(T.bswap(x)), x)
+    u = T.fill_random_uniform(torch.empty(1000), -1.0, 1.0, seed=3)
+    assert -1.0 <= float(u.min()) and float(u.max()) <= 1.0 and torch.equal(u, T.fill_random_uniform(torch.empty(1000), -1.0, 1.0, seed=3))
+    assert T.check_equals(a, a + 1e-4, tol=1e-3) and not T.check_equals(a, a + 1e-2, tol=1e-3)
+    assert T.cast(a, torch.bfloat16).dtype == torch.bfloat16

@@ -106,6 +106,7 @@ class Graph:
         self.trainable_mask: Optional[torch.Tensor] = None
         self.layer_slices: Dict[int, List[Tuple[int, int, Tuple[int, ...], bool]]] = {}
         self.training = True
+        self.profiler = None  # utils.profiling.LayerProfiler, set by the trainer when profiler_type != NONE
         self.step = 0
         self.input_requires_grad = False
         self._ctx: Dict[int, dict] = {}
@@ -342,9 +343,14 @@ class Graph:
             if t.is_floating_point() and t.dtype != self.io_dtype:
                 t = t.to(self.io_dtype)
             vals[id(by_uid[uid])] = t
+        prof = self.profiler
         for k, seg in enumerate(self.segments):
             sctx = st["seg"][k] = {"_step": self.step, "_pid": pid}
-            seg.forward(vals, sctx)
+            if prof is None:
+                seg.forward(vals, sctx)
+            else:
+                with prof.span(self.segment_name(k), "forward"):
+                    seg.forward(vals, sctx)
         out = {n._uid: vals[id(n)] for n in self.output_nodes}
         if not self.training:
             self._ctx.pop(pid, None)
@@ -361,9 +367,20 @@ class Graph:
         for uid, g in grads.items():
             gvals[id(by_uid[uid])] = g.to(self.io_dtype) if g.dtype != self.io_dtype else g
         need_in = {id(n) for n in self.input_nodes} if not self.input_requires_grad else set()
+        prof = self.profiler
         for k in reversed(range(len(self.segments))):
-            self.segments[k].backward(gvals, st["seg"][k], need_in)
+            if prof is None:
+                self.segments[k].backward(gvals, st["seg"][k], need_in)
+            else:
+                with prof.span(self.segment_name(k), "backward"):
+                    self.segments[k].backward(gvals, st["seg"][k], need_in)
         return {n._uid: gvals[id(n)] for n in self.input_nodes if id(n) in gvals and gvals[id(n)] is not None}
+
+    def segment_name(self, k: int) -> str:
+        """Name of executor segment ``k``: the layer's name, or first..last layer of a fused chain."""
+        seg = self.segments[k]
+        names = [self.edges[i].layer.name for i in range(seg.start, seg.end)]
+        return names[0] if len(names) == 1 else f"{names[0]}..{names[-1]}[{type(seg).__name__.lstrip('_')}]"
 
     def __call__(self, x: torch.Tensor, pid: int = 0) -> torch.Tensor:
         """Single-input single-output convenience wrapper."""

@@ -78,6 +78,13 @@ class Trainer:
             raw.SEED_OFF["tensor"] = self.step_counter
         self._graphed = None
         self.launches_per_step = 0
+        # per-layer timing (profiler_type NORMAL: last step, CUMULATIVE: summed over steps)
+        self.layer_profiler = None
+        if str(cfg.profiler_type).upper() in ("NORMAL", "CUMULATIVE"):
+            from .utils.profiling import LayerProfiler
+            self.layer_profiler = LayerProfiler(self.device, source=f"rank{os.environ.get('RANK', '0')}",
+                                                cumulative=str(cfg.profiler_type).upper() == "CUMULATIVE")
+            self.graph.profiler = self.layer_profiler
 
     def _is_language_model(self) -> bool:
         from .nn.layers import Embedding
@@ -127,7 +134,14 @@ class Trainer:
         g = self.graph
         g.set_training(True)
         g.set_step(self.global_step)
+        lp = self.layer_profiler
+        if lp is not None:
+            lp.begin_step()
         loss = self._fwd_bwd(d, l, 1.0 / self.accum)
+        if lp is not None:
+            lp.end_step()
+            if self.cfg.print_layer_profiling and self.global_step % max(1, self.cfg.progress_print_interval) == 0:
+                print(lp.table(top=20), flush=True)
         self.micro_step += 1
         if self.micro_step % self.accum == 0:
             self.optimizer.update()
@@ -138,9 +152,12 @@ class Trainer:
         return loss
 
     # ------------------------------------------------------------ CUDA graph mode
+    def _profiling(self) -> bool:
+        return self.layer_profiler is not None
+
     def enable_cuda_graph(self, data: torch.Tensor, labels: torch.Tensor, warmup: int = 2) -> None:
         """Capture one full step (including the pinned-host upload) and replay it afterwards."""
-        if self.device.type != "cuda":
+        if self.device.type != "cuda" or self._profiling():  # events inside a captured graph carry no timing
             return
         if self.accum != 1:
             raise ValueError("cuda_graph needs gradient_accumulation_steps == 1")
