@@ -23,7 +23,11 @@ def close(got, ref, tol=2e-2, what=""):
 
 @pytest.mark.parametrize("n,h,c,o,k,s,p", [(2, 16, 64, 64, 3, 1, 1), (2, 15, 32, 48, 3, 2, 1), (3, 14, 64, 128, 1, 1, 0),
                                            (2, 14, 64, 128, 1, 2, 0), (2, 20, 3, 16, 7, 2, 3), (1, 9, 8, 24, 5, 1, 0),
-                                           (2, 8, 16, 16, 3, 1, 1)])
+                                           (2, 8, 16, 16, 3, 1, 1),
+                                           # implicit-GEMM routes (channel counts multiple of 64): odd batch and spatial sizes,
+                                           # strided 3x3, 7x7 maps, more than one column block
+                                           (3, 28, 64, 64, 3, 1, 1), (4, 14, 128, 256, 3, 2, 1), (3, 7, 256, 64, 3, 1, 1),
+                                           (5, 9, 64, 320, 3, 1, 1), (2, 12, 192, 128, 5, 1, 2)])
 def test_conv2d(n, h, c, o, k, s, p):
     torch.manual_seed(0)
     x, w, b = rnd(n, h, h, c), rnd(o, k, k, c, scale=0.2), rnd(o)

@@ -1,6 +1,12 @@
-"""NHWC convolution on CUDA: tcgen05 GEMM over the activations (1x1, stride 1) or over patch
-matrices built by the im2col / col2im kernels (every other geometry). Reference semantics:
-src/nn/engines/cpu_engine.cpp:617-734; the reference itself calls cuDNN conv graphs."""
+"""NHWC convolution on CUDA. Three routes, all ending on the tcgen05 tensor cores:
+
+* 1x1, stride 1: a plain GEMM over the activations;
+* channel counts that are multiples of 64: the implicit-GEMM kernels of ``csrc/kernels/conv_implicit.cu`` - TMA fetches
+  shifted spatial boxes of the input straight into operand tiles, no patch matrix exists (forward, weight gradient,
+  and the data gradient of stride-1 layers, which is the forward kernel run on ``dy`` with the rotated filter);
+* everything else (the 3-channel stem, data gradients of strided layers): im2col / col2im kernels around the GEMM.
+
+Reference semantics: src/nn/engines/cpu_engine.cpp:617-734; the reference itself calls cuDNN conv graphs."""
 from __future__ import annotations
 
 import ctypes
@@ -22,8 +28,29 @@ def _lib_conv():
         for name in ("tnnb_im2col", "tnnb_col2im"):
             getattr(lib, name).argtypes = [vp, vp] + [i] * 11 + [vp]
             getattr(lib, name).restype = i
+        lib.tnnb_conv2d_fwd_implicit.argtypes = [vp, vp, vp, vp] + [i] * 12 + [vp, vp]
+        lib.tnnb_conv2d_fwd_implicit.restype = i
+        lib.tnnb_conv2d_wgrad_implicit.argtypes = [vp, vp, vp] + [i] * 11 + [vp, vp]
+        lib.tnnb_conv2d_wgrad_implicit.restype = i
         _DECL = True
     return lib
+
+
+def _implicit_ok(c_in: int, c_out: int) -> bool:
+    return c_in % 64 == 0 and c_out % 64 == 0
+
+
+def _fwd_implicit(x, w, bias, stride, pad, relu):
+    n, h, wd, c = x.shape
+    o, kh, kw, _ = w.shape
+    oh = (h + 2 * pad[0] - kh) // stride[0] + 1
+    ow = (wd + 2 * pad[1] - kw) // stride[1] + 1
+    y = torch.empty(n, oh, ow, o, dtype=x.dtype, device=x.device)
+    rc = _lib_conv().tnnb_conv2d_fwd_implicit(_lib.ptr(x), _lib.ptr(w), _lib.ptr(bias), _lib.ptr(y), n, h, wd, c, o, kh, kw, stride[0],
+                                              stride[1], pad[0], pad[1], int(relu), _lib.ptr(_lib.status_word(x.device)), _lib.stream())
+    _lib.check_rc(rc, "conv2d_fwd_implicit")
+    LAUNCHES["count"] += 1
+    return y
 
 
 def _geom(x_shape, w_shape, stride, pad):
@@ -67,6 +94,8 @@ def conv2d_fwd(x, w, bias, stride, pad, relu=False, keep=None):
     n, h, wd, c, o, kh, kw, oh, ow = _geom(x.shape, w.shape, stride, pad)
     if _is_pointwise(kh, kw, stride, pad) and c % 8 == 0:
         a, K = x.reshape(-1, c), c
+    elif _implicit_ok(c, o) and x.is_contiguous() and w.is_contiguous():
+        return _fwd_implicit(x, w, bias, stride, pad, relu)
     else:
         cols, K = im2col(x, kh, kw, stride, pad, oh, ow)
         a = cols[:, :K]
@@ -83,6 +112,10 @@ def conv2d_dgrad(dy, w, x_shape, stride, pad):
     K = kh * kw * c
     if _is_pointwise(kh, kw, stride, pad) and c % 8 == 0:
         return gemm(dy2, w.reshape(o, K), b_t=True).view(n, h, wd, c)
+    if stride == (1, 1) and _implicit_ok(o, c) and dy.is_contiguous() and kh - 1 - pad[0] >= 0 and kw - 1 - pad[1] >= 0:
+        # dx = conv(dy, filter rotated by 180 degrees with its channel axes swapped), padding k - 1 - p
+        w_rot = w.flip(1, 2).permute(3, 1, 2, 0).contiguous()
+        return _fwd_implicit(dy, w_rot, None, (1, 1), (kh - 1 - pad[0], kw - 1 - pad[1]), False)
     kld = (K + 7) // 8 * 8
     dcols = torch.empty(dy2.shape[0], kld, dtype=dy.dtype, device=dy.device)
     gemm(dy2, _w2d(w, K), b_t=True, out=dcols[:, :K])
@@ -101,6 +134,13 @@ def conv2d_wgrad(x, dy, dw, stride, pad, cols=None):
     K = kh * kw * c
     if _is_pointwise(kh, kw, stride, pad) and c % 8 == 0:
         a = x.reshape(-1, c)
+    elif cols is None and _implicit_ok(c, o) and dw.dtype == torch.float32 and dw.is_contiguous() and x.is_contiguous() \
+            and dy.is_contiguous():
+        rc = _lib_conv().tnnb_conv2d_wgrad_implicit(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), n, h, wd, c, o, kh, kw, stride[0], stride[1],
+                                                    pad[0], pad[1], _lib.ptr(_lib.status_word(x.device)), _lib.stream())
+        _lib.check_rc(rc, "conv2d_wgrad_implicit")
+        LAUNCHES["count"] += 1
+        return
     else:
         if cols is None:
             cols, _ = im2col(x, kh, kw, stride, pad, oh, ow)
