@@ -1,0 +1,84 @@
+"""Image-folder loaders on synthetic JPEG trees and the augmentation pipeline."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+
+def _write_jpeg(path, color, side=80):
+    from PIL import Image
+
+    arr = np.zeros((side, side + 16, 3), dtype=np.uint8)
+    arr[..., :] = color
+    Image.fromarray(arr).save(path, quality=95)
+
+
+def test_tiny_imagenet_and_imagenet100_trees(tmp_path):
+    pytest.importorskip("PIL")
+    from tnn_b200.data.image_folder import create_image_folder_loaders
+
+    # TinyImageNet layout: wnids.txt, train/<wnid>/images/*.JPEG, val/val_annotations.txt + val/images
+    root = tmp_path / "tiny"
+    wnids = ["n01", "n02", "n03"]
+    colors = {"n01": (250, 10, 10), "n02": (10, 250, 10), "n03": (10, 10, 250)}
+    (root / "val" / "images").mkdir(parents=True)
+    (root / "wnids.txt").write_text("\n".join(wnids) + "\n")
+    ann = []
+    for w in wnids:
+        d = root / "train" / w / "images"
+        d.mkdir(parents=True)
+        for i in range(4):
+            _write_jpeg(str(d / f"{w}_{i}.JPEG"), colors[w], side=64)
+        _write_jpeg(str(root / "val" / "images" / f"val_{w}.JPEG"), colors[w], side=64)
+        ann.append(f"val_{w}.JPEG\t{w}\t0\t0\t10\t10")
+    (root / "val" / "val_annotations.txt").write_text("\n".join(ann) + "\n")
+    tr, va = create_image_folder_loaders("tiny_imagenet", str(root), 3, 0, None)  # partial batches are dropped
+    assert len(tr) == 12 and len(va) == 3
+    x, y = next(iter(va))
+    assert x.shape == (3, 64, 64, 3) and x.dtype == torch.float32 and sorted(y.tolist()) == [0, 1, 2]
+    for img, lab in zip(x, y):           # NHWC floats in [0,1]; the dominant channel identifies the class
+        assert int(img.mean((0, 1)).argmax()) == int(lab)
+    # ImageNet-100 layout: Labels.json + <split>/<wnid>/*.JPEG, 224x224 after resize / crop, mean/std normalised
+    root = tmp_path / "in100"
+    (root).mkdir()
+    (root / "Labels.json").write_text(json.dumps({w: f"class {w}" for w in wnids}))
+    for split in ("train.X1", "val.X"):
+        for w in wnids:
+            d = root / split / w
+            d.mkdir(parents=True)
+            for i in range(2):
+                _write_jpeg(str(d / f"{i}.JPEG"), colors[w], side=260)
+    tr, va = create_image_folder_loaders("imagenet100", str(root), 2, 0, None)
+    assert len(tr) == 6 and len(va) == 6
+    x, y = next(iter(tr))
+    assert x.shape == (2, 224, 224, 3)
+    xv, yv = next(iter(va))
+    assert xv.shape == (2, 224, 224, 3) and abs(float(xv.mean())) < 3.0   # normalised, not raw 0..255
+
+
+def test_augmentation_ops_and_builder():
+    from tnn_b200.data.augmentation import AugmentationBuilder
+
+    x = torch.arange(2 * 8 * 8 * 3, dtype=torch.float32).reshape(2, 8, 8, 3) / 400.0
+    flip = AugmentationBuilder(seed=1).horizontal_flip(1.0).build()
+    assert torch.equal(flip(x), x.flip(2))
+    vflip = AugmentationBuilder(seed=1).vertical_flip(1.0).build()
+    assert torch.equal(vflip(x), x.flip(1))
+    norm = AugmentationBuilder().normalize([0.5, 0.5, 0.5], [0.25, 0.25, 0.25]).build()
+    assert torch.allclose(norm(x), (x - 0.5) / 0.25)
+    crop = AugmentationBuilder(seed=3).random_crop(1.0, 2).build()
+    assert crop(x).shape == x.shape
+    rrc = AugmentationBuilder(seed=3).random_resized_crop(1.0).build()
+    assert rrc(x).shape == x.shape
+    cut = AugmentationBuilder(seed=5).cutout(1.0, 4).build()
+    out = cut(x + 1.0)
+    assert (out == 0).any() and out.shape == x.shape
+    full = (AugmentationBuilder(seed=7).horizontal_flip(0.5).rotation(0.5, 10.0).brightness(0.5, 0.2).contrast(0.5, 0.2)
+            .saturation(0.5, 0.2).gaussian_noise(0.5, 0.01).random_crop(1.0, 2).normalize([0.4] * 3, [0.2] * 3).build())
+    a, b = full(x.clone()), (AugmentationBuilder(seed=7).horizontal_flip(0.5).rotation(0.5, 10.0).brightness(0.5, 0.2).contrast(0.5, 0.2)
+                             .saturation(0.5, 0.2).gaussian_noise(0.5, 0.01).random_crop(1.0, 2).normalize([0.4] * 3, [0.2] * 3).build())(x.clone())
+    assert a.shape == x.shape and torch.equal(a, b)                      # same seed, same stream of decisions
+    rc = AugmentationBuilder().resize_center_crop(16, 8).build()
+    assert rc(x).shape == (2, 8, 8, 3)
