@@ -5,6 +5,7 @@ so this test must hold both when it runs alone and after every other GPU test ha
 The exported C symbol is called directly through ctypes, the way a host without PyTorch would.
 """
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -57,10 +58,11 @@ def test_noalloc_matches_regular_twice(shape, relu, affine):
         y = torch.empty_like(x)
         mean = torch.empty(C, dtype=torch.float32, device=dev)
         rstd = torch.empty_like(mean)
+        gc.collect()  # garbage of earlier tests must not be freed between the two readings
         before = torch.cuda.memory_allocated()
         rc = _call(lib, x, y, gamma, beta, mean, rstd, rm_b, rv_b, eps, mom, relu)
         assert rc == 0, lib.tnnb_noalloc_strerror(rc).decode()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_allocated() <= before  # the call took nothing from the tensor allocator
         torch.cuda.synchronize()
         # plain fp32 reference of the same op
         x2 = x.float().reshape(-1, C)
