@@ -82,3 +82,44 @@ def test_augmentation_ops_and_builder():
     assert a.shape == x.shape and torch.equal(a, b)                      # same seed, same stream of decisions
     rc = AugmentationBuilder().resize_center_crop(16, 8).build()
     assert rc(x).shape == (2, 8, 8, 3)
+
+
+def test_wifi_regression_loader(tmp_path):
+    """Wi-Fi fingerprint CSV rules: no-signal cells, default target columns, population-std normalisation."""
+    from tnn_b200.data.regression import WiFiLoader
+
+    rows = ["ap0,ap1,ap2,x,y", "-60,100,-70,1.0,10.0", "-50,0,bad,3.0,30.0", "-40,-80,-90,5.0,50.0", "-30,-85,-95,7.0,oops"]
+    p = tmp_path / "train.csv"
+    p.write_text("\n".join(rows) + "\n")
+    ld = WiFiLoader(batch_size=3, is_regression=True, shuffle=False)
+    assert ld.load_data(str(p))
+    assert (ld.num_features, ld.num_outputs, len(ld)) == (3, 2, 4)
+    assert ld.data_shape() == (3, 1, 1)
+    assert ld.features[0].tolist() == [-60.0, -100.0, -70.0]  # 100 means "not heard"
+    assert ld.features[1].tolist() == [-50.0, -100.0, -100.0]  # 0 and unparsable cells too
+    assert ld.targets[3].tolist() == [7.0, 0.0]  # unparsable target -> 0
+    assert ld.coordinate_ranges()[0] == (1.0, 7.0)
+    raw_f, raw_t = ld.features.copy(), ld.targets.copy()
+    ld.normalize_data()
+    assert ld.is_normalized()
+    assert np.allclose(ld.feature_means, raw_f.mean(0)) and np.allclose(ld.feature_stds, raw_f.std(0))
+    assert np.allclose(ld.features.mean(0), 0, atol=1e-6) and np.allclose(ld.features.std(0), 1, atol=1e-5)
+    assert np.allclose(ld.denormalize_targets(ld.targets), raw_t, atol=1e-4)
+    batches = list(ld)
+    assert [tuple(b[0].shape) for b in batches] == [(3, 3, 1, 1), (1, 3, 1, 1)]
+    assert batches[0][1].shape == (3, 2) and batches[0][1].dtype == torch.float32
+    # validation data scaled with the training statistics
+    val = WiFiLoader(batch_size=2, shuffle=False)
+    assert val.load_data(str(p))
+    val.apply_normalization(ld.feature_means, ld.feature_stds, ld.target_means, ld.target_stds)
+    assert np.allclose(val.features, ld.features, atol=1e-6)
+    # classification mode: the last column is the class id; a constant column gets std 1
+    q = tmp_path / "cls.csv"
+    q.write_text("a,b,label\n-10,-20,2\n-10,-30,0\n")
+    c = WiFiLoader(batch_size=2, is_regression=False, shuffle=False)
+    assert c.load_data(str(q))
+    c.normalize_data()
+    assert c.feature_stds[0] == 1.0 and c.target_means is None
+    x, y = c.next_batch()
+    assert y.dtype == torch.int64 and y.tolist() == [2, 0]
+    assert not WiFiLoader().load_data(str(tmp_path / "missing.csv"))
