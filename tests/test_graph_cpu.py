@@ -123,3 +123,18 @@ def test_attention_block_checkpoint_has_eight_tensors():
     ids = torch.randint(0, 50, (1, 16))
     g.eval(); g2.eval()
     assert torch.allclose(g(ids), g2(ids), atol=1e-5)
+
+
+def test_memory_report_counts_params_and_saved_tensors():
+    from tnn_b200.models import zoo
+
+    g = zoo.create("cifar10_resnet9").compile(device="cpu", seed=1)
+    g.train()
+    g(torch.randn(2, 32, 32, 3))
+    rows = g.memory_report()
+    assert len(rows) == len(g.segments)
+    assert sum(r[1] for r in rows) == g.params_flat.numel() * g.params_flat.element_size() or \
+        sum(r[1] for r in rows) <= g.params_flat.numel() * g.params_flat.element_size()  # slab has alignment padding
+    assert sum(r[1] for r in rows) >= g.num_parameters() * g.params_flat.element_size()
+    assert sum(r[2] for r in rows) > 0
+    assert "total" in g.format_memory_report()

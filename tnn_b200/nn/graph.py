@@ -382,6 +382,49 @@ class Graph:
         names = [self.edges[i].layer.name for i in range(seg.start, seg.end)]
         return names[0] if len(names) == 1 else f"{names[0]}..{names[-1]}[{type(seg).__name__.lstrip('_')}]"
 
+    def memory_report(self, pid: int = 0) -> List[Tuple[str, int, int]]:
+        """``(segment name, parameter bytes, bytes saved for backward)`` per executor segment.
+
+        Call between a training ``forward`` and its ``backward``: the saved bytes are the tensors that the
+        segment keeps for its backward pass for micro-batch ``pid``; a storage shared by several segments
+        is counted once, for the first that holds it. This is what the trainer option
+        ``print_layer_memory_usage`` prints (the reference parses that option, src/nn/train.cpp:159, but
+        prints nothing for it)."""
+        st = self._ctx.get(pid, {"seg": {}})
+        seen: set = set()
+
+        def walk(o) -> int:
+            if isinstance(o, torch.Tensor):
+                key = o.untyped_storage().data_ptr()
+                if key in seen or key == 0:
+                    return 0
+                seen.add(key)
+                return o.untyped_storage().nbytes()
+            if isinstance(o, dict):
+                return sum(walk(v) for v in o.values())
+            if isinstance(o, (list, tuple)):
+                return sum(walk(v) for v in o)
+            return 0
+
+        rows = []
+        for k, seg in enumerate(self.segments):
+            pbytes, counted = 0, set()
+            for i in range(seg.start, seg.end):
+                lay = self.edges[i].layer
+                if id(lay) not in counted:  # a layer used by several edges owns its parameters once
+                    counted.add(id(lay))
+                    pbytes += sum(sl[1] for sl in self.layer_slices.get(id(lay), []) if sl) * self.params_flat.element_size()
+            rows.append((self.segment_name(k), pbytes, walk(st["seg"].get(k, {}))))
+        return rows
+
+    def format_memory_report(self, pid: int = 0) -> str:
+        rows = self.memory_report(pid)
+        w = max([len(r[0]) for r in rows] + [5])
+        lines = [f"{'layer':<{w}}  {'params MiB':>11}  {'saved MiB':>10}"]
+        lines += [f"{n:<{w}}  {p / 2**20:>11.2f}  {a / 2**20:>10.2f}" for n, p, a in rows]
+        lines.append(f"{'total':<{w}}  {sum(r[1] for r in rows) / 2**20:>11.2f}  {sum(r[2] for r in rows) / 2**20:>10.2f}")
+        return "\n".join(lines)
+
     def __call__(self, x: torch.Tensor, pid: int = 0) -> torch.Tensor:
         """Single-input single-output convenience wrapper."""
         out = self.forward({self.input_nodes[0]._uid: x}, pid)

@@ -77,6 +77,7 @@ class Trainer:
         if self.device.type == "cuda":
             raw.SEED_OFF["tensor"] = self.step_counter
         self._graphed = None
+        self._print_memory_once = bool(getattr(cfg, "print_layer_memory_usage", False))
         self.launches_per_step = 0
         # per-layer timing (profiler_type NORMAL: last step, CUMULATIVE: summed over steps)
         self.layer_profiler = None
@@ -102,6 +103,9 @@ class Trainer:
         g = self.graph
         in_uid, out_uid = g.input_nodes[0].uid(), g.output_nodes[0].uid()
         out = g.forward({in_uid: d})[out_uid]
+        if self._print_memory_once:
+            self._print_memory_once = False
+            print("per-layer memory after the first forward pass:\n" + g.format_memory_report(), flush=True)
         in_place = isinstance(self.loss, CrossEntropyLoss) and out.is_cuda
         if in_place:
             loss, grad = self.loss.compute(out, l, scale, True, in_place=True)
