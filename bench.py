@@ -203,12 +203,116 @@ def run_ours(args):
         barrier()
         return res
 
+    def measure_pipeline(layout, sample_clocks):
+        """Pipeline layouts (``pp4tp2`` ...): 1F1B over the partitioner's stages, 8 micro-batches per step, stage
+        send / recv on NCCL point-to-point; after the timed steps every stage writes its TNNG file and reads it back."""
+        import tempfile
+
+        from tnn_b200.nn.graph import Graph
+        from tnn_b200.parallel.pp import PipelineTrainer
+        from tnn_b200.parallel.runtime import parse_layout
+
+        n_stages = parse_layout(layout)["pp"]
+        micro = 8
+        pcfg = TrainingConfig.from_dict({"model_name": ms["zoo"], "batch_size": ms["per_gpu_batch"] * n_stages, "device_type": "CUDA",
+                                         "optimizer": ms["optimizer"], "scheduler": {"type": "no_op"},
+                                         "loss": {"type": "logsoftmax_crossentropy"}, "seed": 0,
+                                         "parallel": {"microbatches": micro}})
+        trainer = PipelineTrainer(pcfg, layout)
+        lb = trainer.local_batch
+        loader = SyntheticLoader((ms["seq_len"],), 50257, lb, 10 ** 9, tokens=True, seed=1234 + trainer.data_rank)
+        batches = iter(loader)
+        loss = None
+        for _ in range(max(3, args.warmup)):
+            data, labels = next(batches)
+            loss = trainer.train_step(data, labels)
+        barrier()
+        first_loss = float(loss.item()) if loss is not None else None
+        sampler = ClockSampler(local) if (sample_clocks and rank == 0) else None
+        if sampler:
+            sampler.start()
+        time.sleep(0.3)
+        d_res, l_res = data.to(dev), labels.to(dev)
+        n0 = LAUNCHES["count"]
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            loss = trainer.train_step(d_res, l_res)
+        e1.record()
+        barrier()
+        dev_ms = e0.elapsed_time(e1)
+        launches = LAUNCHES["count"] - n0
+        barrier()
+        t0 = time.perf_counter()
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record()
+        last = None
+        for _ in range(args.steps):
+            data, labels = next(batches)
+            loss = trainer.train_step(data, labels)
+            if loss is not None:
+                last = float(loss.item())
+        e3.record()
+        barrier()
+        e2e_ms = max(e2.elapsed_time(e3), (time.perf_counter() - t0) * 1e3)
+        clocks = sampler.stop() if sampler else {}
+        t = torch.tensor([dev_ms, e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms = float(t[0]), float(t[1])
+        from tnn_b200.ops import _lib
+        _lib.check_status(dev)
+        # ---- checkpoint round trip: one TNNG file per stage (tensor-parallel shards gathered), read back ----
+        folder = [tempfile.mkdtemp(prefix="tnnb_bench_ckpt_") if rank == 0 else None]
+        dist.broadcast_object_list(folder, src=0)
+        t1 = time.perf_counter()
+        name = trainer.save_stage(os.path.join(folder[0], "gpt2"))
+        barrier()
+        save_s = time.perf_counter() - t1
+        ck = {"stage": trainer.topo.pp_idx, "ok": None}
+        if trainer.topo.dp_idx == 0 and trainer.topo.tp_idx == 0:
+            t2 = time.perf_counter()
+            g2 = Graph.load_state(name, device="cpu")
+            n_loaded = g2.num_parameters()
+            n_stage = trainer.stage.num_parameters()
+            # replicated parameters count once, sharded ones tp times
+            ck = {"stage": trainer.topo.pp_idx, "bytes": os.path.getsize(name), "params": n_loaded, "load_s": round(time.perf_counter() - t2, 2),
+                  "ok": bool(torch.isfinite(g2.params_flat).all()) and n_stage <= n_loaded <= n_stage * trainer.topo.tp}
+            os.remove(name)
+        allck, alll = [None] * world, [None] * world
+        dist.all_gather_object(allck, ck)
+        dist.all_gather_object(alll, (first_loss, last))
+        stages = sorted((c for c in allck if c.get("ok") is not None), key=lambda c: c["stage"])
+        losses = [x for x in alll if x[0] is not None][0]
+        if rank == 0:
+            try:
+                os.rmdir(folder[0])
+            except OSError:
+                pass
+        items = trainer.global_batch * ms["items_per_sample"]
+        res = {"layout": layout, "global_batch": trainer.global_batch, "dev_ms": dev_ms, "e2e_ms": e2e_ms,
+               "value": items * args.steps / (dev_ms / 1e3), "e2e": items * args.steps / (e2e_ms / 1e3),
+               "h2d": int(data.numel() * data.element_size() + labels.numel() * labels.element_size()), "launches": int(launches),
+               "first_loss": losses[0], "last_loss": losses[1], "clocks": clocks,
+               "checkpoint": {"format": "TNNG, one file per stage", "save_s": round(save_s, 2), "stages": stages,
+                              "round_trip_ok": all(c["ok"] for c in stages) and len(stages) == trainer.topo.pp},
+               "microbatches": micro}
+        trainer.close()
+        del trainer
+        torch.cuda.empty_cache()
+        barrier()
+        return res
+
     from tnn_b200.parallel.runtime import default_layout
     layout = args.parallelism or (named_layout(world, ms["zoo"]) if world > 1 else "single")
-    r = measure(layout, True)
+    if layout.startswith("pp"):
+        r = measure_pipeline(layout, True)
+        args.no_graph = True
+    else:
+        r = measure(layout, True)
     alt = None
     dp_layout = default_layout(world, ms["zoo"])
-    if world > 1 and not args.parallelism and layout != dp_layout:
+    if world > 1 and not args.parallelism and layout != dp_layout and not layout.startswith("pp"):
         alt = measure(dp_layout, False)  # the same job as pure data parallelism, for comparison
 
     out = {
@@ -224,6 +328,10 @@ def run_ours(args):
                 "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": 4},
         "gpu_launches": r["launches"], "loss_first": round(r["first_loss"], 4), "loss_last": round(r["last_loss"], 4), "impl": "ours",
     }
+    if "checkpoint" in r:
+        out["checkpoint"] = r["checkpoint"]
+        out["config"]["microbatches"] = r["microbatches"]
+        out["config"]["schedule"] = "1F1B"
     if alt is not None:
         out["alt"] = {"parallelism": alt["layout"], "value": round(alt["value"], 1), "ms_per_step": round(alt["dev_ms"] / args.steps, 3),
                       "e2e_value": round(alt["e2e"], 1), "note": "same model, batch and steps as pure data parallelism (fused reduce + AdamW + broadcast kernel)"}
@@ -236,6 +344,8 @@ def run_ours(args):
 def named_layout(world: int, zoo_name: str) -> str:
     """The layout the benchmark configuration names: GPT-2 runs tensor-parallel pairs (fused all-gather->GEMM and
     GEMM->reduce-scatter) combined with data parallelism; the CNNs are data parallel."""
+    if zoo_name == "gpt2_medium" and world == 8:
+        return "pp4tp2"  # 1F1B over four partitioner stages, each a tensor-parallel pair
     if "gpt2" in zoo_name and world % 2 == 0:
         return "tp2" if world == 2 else f"tp2dp{world // 2}"
     return f"dp{world}"

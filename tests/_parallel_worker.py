@@ -24,6 +24,30 @@ def main():
     from tnn_b200.parallel.runtime import ParallelTrainer
     cfg = TrainingConfig.from_dict({"model_name": "tiny_gpt", "batch_size": 2, "device_type": "CUDA", "seed": 5,
                                     "optimizer": {"type": "adamw", "learning_rate": 1e-2, "weight_decay": 0.01}})
+    if mode == "dpbn":  # batch-norm model under a strongly decaying AdamW: running statistics must not be decayed
+        def tiny_bn_cnn():
+            b = zoo._start((1, 16, 16, 3))
+            b.conv(32, 3, 1, 1, True, "c1").bn(True, "bn1").maxpool(2, 2, 0, "p1")
+            b.conv(64, 3, 1, 1, False, "c2").bn(True, "bn2").avgpool(8, 1, 0, "gap")
+            return zoo._finish(b.flatten().dense(10, True, "fc"))
+        zoo.register_model("tiny_bn_cnn", tiny_bn_cnn)
+        cfg = TrainingConfig.from_dict({"model_name": "tiny_bn_cnn", "batch_size": 8, "device_type": "CUDA", "seed": 5,
+                                        "optimizer": {"type": "adamw", "learning_rate": 1e-2, "weight_decay": 5.0}})
+        t = ParallelTrainer(cfg, layout=f"dp{world}", fused=fused, log=False, heap_bytes=256 << 20)
+        gen = torch.Generator().manual_seed(100 + t.data_rank)
+        losses = []
+        for step in range(4):
+            x = torch.randn(t.local_batch, 16, 16, 3, generator=gen) * 2.0 + 0.5
+            y = torch.randint(0, 10, (t.local_batch,), generator=gen)
+            losses.append(float(t.train_step(x, y).item()))
+        _lib.check_status()
+        if rank == 0:
+            torch.save({"params": t.graph.master_flat.float().cpu(), "trainable": t.graph.trainable_mask.cpu(), "losses": losses},
+                       sys.argv[3])
+            print("RESULT " + json.dumps({"losses": losses}), flush=True)
+        t.close()
+        dist.destroy_process_group()
+        return
     layout = {"dp": f"dp{world}", "tp": f"tp2dp{world // 2}" if world > 2 else "tp2"}[mode]
     t = ParallelTrainer(cfg, layout=layout, fused=fused, log=False, heap_bytes=256 << 20)
     gen = torch.Generator().manual_seed(100 + t.data_rank)

@@ -55,6 +55,24 @@ def test_dp2_matches_single_process(kind, tmp_path):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_dp2_weight_decay_spares_running_statistics(tmp_path):
+    """AdamW with a large decay on a batch-norm model: the fused reduce + update kernel and the NCCL path must
+    agree, and the running statistics (stored as parameters, never trained) must come out undecayed."""
+    outs = {}
+    for kind in ("fused", "nccl"):
+        out = str(tmp_path / f"{kind}.pt")
+        launch(2, "dpbn", kind, out)
+        outs[kind] = torch.load(out)
+    frozen = ~outs["nccl"]["trainable"]
+    a, b = outs["fused"]["params"][frozen], outs["nccl"]["params"][frozen]  # running statistics and slab padding
+    assert int((b != 0).sum()) >= 2 * 64
+    assert torch.allclose(a, b, rtol=2e-2, atol=2e-2), float((a - b).abs().max())
+    # a decayed running variance would have lost 1 - 0.95^4 = 19 % of its value
+    rel = (outs["fused"]["params"] - outs["nccl"]["params"]).norm() / outs["nccl"]["params"].norm()
+    assert rel < 3e-2, float(rel)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("kind", ["fused", "nccl"])
 def test_tp2_trains(kind, tmp_path):
     res = launch(2, "tp", kind, str(tmp_path / "tp.pt"))

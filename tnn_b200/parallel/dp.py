@@ -75,6 +75,15 @@ class FusedDPOptimizer:
                 "go": torch.zeros(1, dtype=torch.int32, device=dev), "done": torch.zeros(1, dtype=torch.int32, device=dev),
             }
             self.sites.append(site)
+        # Entries that are stored as parameters but never trained (batch-norm running statistics): weight decay
+        # must not shrink them, so their values are put back after a decaying update (indices found once here).
+        used = torch.zeros_like(graph.trainable_mask)
+        for sl in graph.layer_slices.values():
+            for ent in sl:
+                if ent:
+                    used[ent[0]:ent[0] + ent[1]] = True
+        idx = (used & ~graph.trainable_mask).nonzero().squeeze(1)
+        self._frozen_idx = idx if idx.numel() else None
         # a parameter written by a peer lands in params_flat; when params are fp32 the master *is* params_flat
         torch.cuda.synchronize()
         if dist.is_initialized():
@@ -117,6 +126,9 @@ class FusedDPOptimizer:
             args = (0, o.lr, o.beta1, o.beta2, o.eps, o.weight_decay, bc1, bc2, o.grad_scale, 0.0)
         else:
             args = (1, o.lr, 0.0, 0.0, 0.0, 0.0, 1.0, 1.0, o.grad_scale, o.momentum)
+        frozen = None
+        if self.is_adam and o.weight_decay != 0.0 and self._frozen_idx is not None:
+            frozen = g.master_flat.index_select(0, self._frozen_idx)
         self.tick.add_(1)
         for s in self.sites:
             rc = self.lib.tnnb_dp_step(
@@ -125,6 +137,10 @@ class FusedDPOptimizer:
                 args[8], args[9], _lib.ptr(o.hyper), 0, _lib.ptr(self.tick), _lib.ptr(s["go"]), _lib.ptr(s["done"]), status, st)
             _lib.check_rc(rc, "tnnb_dp_step")
             LAUNCHES["count"] += 1
+        if frozen is not None:  # the kernel returns only after every peer's writes into this rank have landed
+            g.master_flat.index_copy_(0, self._frozen_idx, frozen)
+            if g.params_flat is not g.master_flat:
+                g.params_flat.index_copy_(0, self._frozen_idx, frozen.to(g.params_flat.dtype))
 
     def state_dict(self):
         d = self.opt.state_dict()
