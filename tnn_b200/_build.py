@@ -57,9 +57,30 @@ def kernels_path():
     return os.path.join(LIB, "libtnnb_kernels.so")
 
 
-def host_path():
+def host_path(sanitize=False):
     ext = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
-    return os.path.join(LIB, "_host" + ext)
+    return os.path.join(LIB, "san", "_host" + ext) if sanitize else os.path.join(LIB, "_host" + ext)
+
+
+# AddressSanitizer + UndefinedBehaviorSanitizer build of the host runtime (the reference's ENABLE_DEBUG build uses
+# -fsanitize=address,undefined for its CPU-only configuration, cmake/CompilerFlags.cmake:28-33). The interpreter is not
+# instrumented, so a process that imports this variant must start with the ASan runtime preloaded: sanitizer_env().
+SAN_FLAGS = ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"]
+
+
+def sanitizer_env(base=None):
+    """Environment for a child process that loads the sanitized host runtime (TNNB_HOST_SANITIZE=1)."""
+    env = dict(os.environ if base is None else base)
+    asan = subprocess.run([CXX, "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+    # libstdc++ is preloaded too: ASan looks up the real __cxa_throw when it starts, and the interpreter itself does not
+    # link the C++ runtime, so without it the first C++ exception aborts inside the interceptor
+    cxxrt = subprocess.run([CXX, "-print-file-name=libstdc++.so.6"], capture_output=True, text=True).stdout.strip()
+    env["LD_PRELOAD"] = " ".join(x for x in (asan, cxxrt if os.path.isabs(cxxrt) else "libstdc++.so.6", env.get("LD_PRELOAD", "")) if x)
+    # the interpreter's own arenas are not leaks of the runtime; an error must end the process with a non-zero code
+    env["ASAN_OPTIONS"] = "detect_leaks=0:abort_on_error=0:exitcode=97:allocator_may_return_null=1"
+    env["UBSAN_OPTIONS"] = "print_stacktrace=1:halt_on_error=1:exitcode=98"
+    env["TNNB_HOST_SANITIZE"] = "1"
+    return env
 
 
 def build_kernels(verbose=False, force=False, ptxas_info=False):
@@ -94,23 +115,25 @@ def build_kernels(verbose=False, force=False, ptxas_info=False):
     return out
 
 
-def build_host(verbose=False, force=False):
+def build_host(verbose=False, force=False, sanitize=False):
     import pybind11
 
-    os.makedirs(LIB, exist_ok=True)
+    os.makedirs(os.path.join(LIB, "san") if sanitize else LIB, exist_ok=True)
     hdir = os.path.join(CSRC, "host")
     srcs = sorted(glob.glob(os.path.join(hdir, "*.cc")))
     hdrs = glob.glob(os.path.join(hdir, "*.h"))
-    out = host_path()
+    out = host_path(sanitize)
+    opt = SAN_FLAGS if sanitize else ["-O2"]
+    tag = "host_san_" if sanitize else "host_"
     site = os.path.dirname(os.path.dirname(pybind11.__file__))
     json_inc = os.path.join(site, "include", "cudnn_frontend", "thirdparty")
     objs = []
     procs = []
     for s in srcs:
-        o = os.path.join(LIB, "host_" + os.path.basename(s)[:-3] + ".o")
+        o = os.path.join(LIB, tag + os.path.basename(s)[:-3] + ".o")
         objs.append(o)
         if force or _newer([s] + hdrs, o):
-            cmd = [CXX, "-O2", "-std=c++17", "-fPIC", "-fopenmp", "-fvisibility=hidden", "-I", hdir,
+            cmd = [CXX] + opt + ["-std=c++17", "-fPIC", "-fopenmp", "-fvisibility=hidden", "-I", hdir,
                    "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
                    "-I", json_inc, "-c", s, "-o", o]
             if verbose:
@@ -122,7 +145,7 @@ def build_host(verbose=False, force=False):
             sys.stderr.write(o)
             raise RuntimeError("g++ failed for " + s)
     if force or procs or _newer(objs, out):
-        _run([CXX, "-shared", "-fopenmp", "-o", out] + objs, verbose)
+        _run([CXX, "-shared", "-fopenmp"] + (["-fsanitize=address,undefined"] if sanitize else []) + ["-o", out] + objs, verbose)
     return out
 
 

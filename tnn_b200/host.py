@@ -13,9 +13,11 @@ from . import _build
 
 
 def _load():
-    path = _build.host_path()
+    # TNNB_HOST_SANITIZE=1 selects the AddressSanitizer / UBSan build (start the process with _build.sanitizer_env())
+    sanitize = os.environ.get("TNNB_HOST_SANITIZE", "") == "1"
+    path = _build.host_path(sanitize)
     if not os.path.exists(path):
-        _build.build_host()
+        _build.build_host(sanitize=sanitize)
     spec = importlib.util.spec_from_file_location("_host", path)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
