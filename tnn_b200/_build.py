@@ -53,8 +53,8 @@ def _run(cmd, verbose):
         print(r.stdout + r.stderr)
 
 
-def kernels_path():
-    return os.path.join(LIB, "libtnnb_kernels.so")
+def kernels_path(bounds_check=False):
+    return os.path.join(LIB, "dbg", "libtnnb_kernels.so") if bounds_check else os.path.join(LIB, "libtnnb_kernels.so")
 
 
 def host_path(sanitize=False):
@@ -83,18 +83,22 @@ def sanitizer_env(base=None):
     return env
 
 
-def build_kernels(verbose=False, force=False, ptxas_info=False):
-    os.makedirs(LIB, exist_ok=True)
+def build_kernels(verbose=False, force=False, ptxas_info=False, bounds_check=False):
+    """``bounds_check=True`` builds the checked variant (``-DTNNB_BOUNDS_CHECK``, see ptx.cuh) into ``_lib/dbg``; a process
+    loads it instead of the regular library when ``TNNB_BOUNDS_CHECK=1`` is set."""
+    odir = os.path.join(LIB, "dbg") if bounds_check else LIB
+    os.makedirs(odir, exist_ok=True)
     kdir = os.path.join(CSRC, "kernels")
     srcs = sorted(glob.glob(os.path.join(kdir, "*.cu")))
     hdrs = glob.glob(os.path.join(kdir, "*.cuh")) + glob.glob(os.path.join(kdir, "*.h"))
     objs = []
     jobs = []
     for s in srcs:
-        o = os.path.join(LIB, os.path.basename(s)[:-3] + ".o")
+        o = os.path.join(odir, os.path.basename(s)[:-3] + ".o")
         objs.append(o)
         if force or _newer([s] + hdrs, o):
-            cmd = [NVCC] + CUDA_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + ["-I", kdir, "-c", s, "-o", o]
+            cmd = ([NVCC] + CUDA_FLAGS + (["-DTNNB_BOUNDS_CHECK"] if bounds_check else []) + (["-Xptxas", "-v"] if ptxas_info else [])
+                   + ["-I", kdir, "-c", s, "-o", o])
             jobs.append(cmd)
     if jobs:
         procs = []
@@ -109,7 +113,7 @@ def build_kernels(verbose=False, force=False, ptxas_info=False):
                 raise RuntimeError("nvcc failed for " + cmd[-3])
             if (verbose or ptxas_info) and out:
                 print(out)
-    out = kernels_path()
+    out = kernels_path(bounds_check)
     if force or jobs or _newer(objs, out):
         _run([NVCC, "-shared", "-o", out] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"], verbose)
     return out
@@ -150,7 +154,10 @@ def build_host(verbose=False, force=False, sanitize=False):
 
 
 def build_all(verbose=False, force=False):
-    return build_kernels(verbose, force), build_host(verbose, force)
+    """Every native piece: the kernel library, its bounds-checked variant, and the host runtime."""
+    k = build_kernels(verbose, force)
+    build_kernels(verbose, force, bounds_check=True)
+    return k, build_host(verbose, force)
 
 
 if __name__ == "__main__":

@@ -14,6 +14,8 @@
 // (cuda_engine.cu:295-672). Each pass moves 16-byte vectors and reads x exactly once.
 #include "ptx.cuh"
 
+TNNB_BOUNDS_TU(batchnorm)
+
 namespace tnnb {
 
 typedef __nv_bfloat16 bf16;
@@ -61,6 +63,7 @@ bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const 
       for (int k = 0; k < 8; ++k) mu[k] = mean[c0 + k], rs[k] = rstd[c0 + k];
     }
     for (long long r = r0 + ry; r < r1; r += nry) {
+      if (!TNNB_CHECK(r * C + c0 + 7, M * (long long)C)) break;  // lane layout vs. tensor extent
       uint4 raw = *reinterpret_cast<const uint4*>(x + r * C + c0);
       const bf16* xv = reinterpret_cast<const bf16*>(&raw);
       if (!BWD) {
@@ -136,6 +139,7 @@ bn_fwd_apply_kernel(const bf16* __restrict__ x, bf16* __restrict__ yout, const b
   }
   const long long r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
   for (long long r = r0 + ry; r < r1; r += nry) {
+    if (!TNNB_CHECK(r * C + c0 + 7, M * (long long)C)) break;  // lane layout vs. tensor extent
     uint4 raw = *reinterpret_cast<const uint4*>(x + r * C + c0);
     const bf16* xv = reinterpret_cast<const bf16*>(&raw);
     __align__(16) bf16 o[8];
@@ -171,6 +175,7 @@ bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, con
   }
   const long long r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
   for (long long r = r0 + ry; r < r1; r += nry) {
+    if (!TNNB_CHECK(r * C + c0 + 7, M * (long long)C)) break;  // lane layout vs. tensor extent
     uint4 raw = *reinterpret_cast<const uint4*>(x + r * C + c0);
     const bf16* xv = reinterpret_cast<const bf16*>(&raw);
     uint4 graw = *reinterpret_cast<const uint4*>(dy + r * C + c0);

@@ -13,6 +13,8 @@
 // (cudnn_engine.cu:328-578) and scatter kernels with atomics for the pool backward.
 #include "ptx.cuh"
 
+TNNB_BOUNDS_TU(conv_pool)
+
 namespace tnnb {
 
 typedef __nv_bfloat16 bf16;
@@ -41,9 +43,14 @@ __global__ void im2col_kernel(const bf16* __restrict__ x, bf16* __restrict__ col
       const int oh = (int)((pix / g.OW) % g.OH);
       const int n = (int)(pix / ((long long)g.OW * g.OH));
       const int ih = oh * g.SH + kh - g.PH, iw = ow * g.SW + kw - g.PW;
-      bf16* dst = cols + pix * g.Kld + ((long long)(kh * g.KW + kw) * g.C) + c * 8;
+      const long long doff = pix * g.Kld + ((long long)(kh * g.KW + kw) * g.C) + c * 8;
+      if (!TNNB_CHECK(doff + 7, (long long)g.N * g.OH * g.OW * g.Kld)) continue;
+      bf16* dst = cols + doff;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) v = *reinterpret_cast<const uint4*>(x + (((long long)n * g.H + ih) * g.W + iw) * g.C + c * 8);
+      if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) {
+        const long long soff = (((long long)n * g.H + ih) * g.W + iw) * g.C + c * 8;
+        if (TNNB_CHECK(soff + 7, (long long)g.N * g.H * g.W * g.C)) v = *reinterpret_cast<const uint4*>(x + soff);
+      }
       *reinterpret_cast<uint4*>(dst) = v;
     }
   } else {
@@ -67,7 +74,8 @@ __global__ void im2col_kernel(const bf16* __restrict__ x, bf16* __restrict__ col
           const int kw = (k / g.C) % g.KW;
           const int kh = k / (g.C * g.KW);
           const int ih = oh * g.SH + kh - g.PH, iw = ow * g.SW + kw - g.PW;
-          if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) e = img[((long long)ih * g.W + iw) * g.C + c];
+          if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W && TNNB_CHECK(((long long)ih * g.W + iw) * g.C + c, (long long)g.H * g.W * g.C))
+            e = img[((long long)ih * g.W + iw) * g.C + c];
         }
         v[j] = e;
       }
@@ -99,7 +107,9 @@ __global__ void col2im_kernel(const bf16* __restrict__ dcols, bf16* __restrict__
         if (u < 0 || u % g.SW) continue;
         const int ow = u / g.SW;
         if (ow >= g.OW) continue;
-        const bf16* src = dcols + (((long long)n * g.OH + oh) * g.OW + ow) * g.Kld + (long long)(kh * g.KW + kw) * g.C + c * VEC;
+        const long long soff = (((long long)n * g.OH + oh) * g.OW + ow) * g.Kld + (long long)(kh * g.KW + kw) * g.C + c * VEC;
+        if (!TNNB_CHECK(soff + VEC - 1, (long long)g.N * g.OH * g.OW * g.Kld)) continue;
+        const bf16* src = dcols + soff;
         if (VEC == 8) {
           uint4 raw = *reinterpret_cast<const uint4*>(src);
           const bf16* t8 = reinterpret_cast<const bf16*>(&raw);
@@ -189,6 +199,7 @@ __global__ void pool_bwd_kernel(const bf16* __restrict__ dy, const unsigned char
         const int ow = u / g.SW;
         if (ow >= g.OW) continue;
         const long long o = ((((long long)n * g.OH + oh) * g.OW + ow) * cv + c) * 8;
+        if (!TNNB_CHECK(o + 7, (long long)g.N * g.OH * g.OW * g.C)) continue;
         uint4 raw = *reinterpret_cast<const uint4*>(dy + o);
         const bf16* t8 = reinterpret_cast<const bf16*>(&raw);
         if (mode == 0) {
@@ -196,8 +207,10 @@ __global__ void pool_bwd_kernel(const bf16* __restrict__ dy, const unsigned char
           const unsigned char* b8 = reinterpret_cast<const unsigned char*>(&ir);
           const unsigned char me = (unsigned char)(kh * g.KW + kw);
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
+          for (int k = 0; k < 8; ++k) {
+            if (b8[k] != 255) (void)TNNB_CHECK(b8[k], g.KH * g.KW);  // a saved position outside the window (255 = empty window)
             if (b8[k] == me) acc[k] += __bfloat162float(t8[k]);
+          }
         } else {
           const int h0 = max(oh * g.SH - g.PH, 0), h1 = min(oh * g.SH - g.PH + g.KH, g.H);
           const int w0 = max(ow * g.SW - g.PW, 0), w1 = min(ow * g.SW - g.PW + g.KW, g.W);

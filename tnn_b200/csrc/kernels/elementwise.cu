@@ -6,6 +6,8 @@
 // 1077-1233, src/ops/cuda/kernels.cu:30-591).
 #include "ptx.cuh"
 
+TNNB_BOUNDS_TU(elementwise)
+
 namespace tnnb {
 
 typedef __nv_bfloat16 bf16;
@@ -145,6 +147,7 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const bf
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
     long long id = ids[r];
     const bool pad = (id == padding_idx);
+    if (!pad) (void)TNNB_CHECK(id, vocab);  // checked build: report the id; both builds read row 0 instead
     if (id < 0 || id >= vocab) id = 0;
     const bf16* trow = wte + id * E;
     const bf16* prow = wpe ? wpe + (long long)(r % S) * E : nullptr;
@@ -180,6 +183,7 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const bf
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
     long long id = ids[r];
     const bool pad = (id == padding_idx);
+    if (!pad) (void)TNNB_CHECK(id, vocab);
     if (id < 0 || id >= vocab) id = 0;
     for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
       float g[8];

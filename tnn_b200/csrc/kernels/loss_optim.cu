@@ -13,6 +13,8 @@
 // master weights and writes the bf16 compute copy in the same pass.
 #include "ptx.cuh"
 
+TNNB_BOUNDS_TU(loss_optim)
+
 namespace tnnb {
 
 typedef __nv_bfloat16 bf16;
@@ -85,6 +87,7 @@ softmax_ce_stream_kernel(const bf16* __restrict__ logits, long long ld, const lo
     uint4* row = reinterpret_cast<uint4*>(ce_smem);
     bf16* row_e = reinterpret_cast<bf16*>(ce_smem);
     const long long lab = labels[r];
+    if (threadIdx.x == 0) (void)TNNB_CHECK(lab, V);  // checked build: report the label; both builds leave it out of the loss
     // Columns V .. 8*chunks-1 of the last chunk hold whatever the row pitch contains: make them -inf once
     // (exp gives 0, the gradient 0) so that the passes below need no per-element bounds checks.
     if (threadIdx.x < 8 && (chunks - 1) * 8 + (int)threadIdx.x >= V)
@@ -268,6 +271,7 @@ softmax_ce_kernel(const bf16* __restrict__ logits, long long ld, const long long
     const long long lab = labels[r];
     const float inv = 1.f / s;
     if (threadIdx.x == 0) {
+      (void)TNNB_CHECK(lab, V);
       float zl = (lab >= 0 && lab < V) ? __bfloat162float(z[lab]) : rmax;
       float loss = __logf(s) + rmax - zl;
       if (row_loss) row_loss[r] = loss;

@@ -28,6 +28,50 @@ enum KernelStatus : int {
   ST_BAD_ARG = 5,
 };
 
+// ---------------------------------------------------------------- bounds-checked debug build
+// Compiled with -DTNNB_BOUNDS_CHECK (tnn_b200/_build.py: build_kernels(bounds_check=True)), the kernels test the
+// global-memory indices they compute from data or from hand-written geometry (token and label ids, saved pool
+// positions, patch-matrix offsets, flat optimizer offsets) with TNNB_CHECK(index, limit). A violation is recorded -
+// first one wins: source line, index, limit - in a per-file device record and the access is skipped, so the
+// context stays usable; nothing traps. The host reads and clears the record through tnnb_bounds_fetch_<file>().
+// In the regular build TNNB_CHECK is the constant true and costs nothing.
+struct BoundsRecord {
+  int hit;
+  int line;
+  long long index;
+  long long limit;
+};
+#ifdef TNNB_BOUNDS_CHECK
+__device__ __forceinline__ bool bounds_ok(BoundsRecord* rec, long long idx, long long limit, int line) {
+  if (idx >= 0 && idx < limit) return true;
+  if (atomicCAS(&rec->hit, 0, 1) == 0) {
+    rec->line = line;
+    rec->index = idx;
+    rec->limit = limit;
+  }
+  return false;
+}
+#define TNNB_BOUNDS_TU(tu)                                                                             \
+  namespace tnnb {                                                                                     \
+  static __device__ BoundsRecord g_bounds = {0, 0, 0, 0};                                              \
+  }                                                                                                    \
+  extern "C" int tnnb_bounds_fetch_##tu(int* hit_line, long long* index_limit) {                       \
+    tnnb::BoundsRecord r;                                                                              \
+    if (cudaMemcpyFromSymbol(&r, tnnb::g_bounds, sizeof(r)) != cudaSuccess) return -2;                 \
+    hit_line[0] = r.hit, hit_line[1] = r.line, index_limit[0] = r.index, index_limit[1] = r.limit;     \
+    if (r.hit) {                                                                                       \
+      const tnnb::BoundsRecord z = {0, 0, 0, 0};                                                       \
+      if (cudaMemcpyToSymbol(tnnb::g_bounds, &z, sizeof(z)) != cudaSuccess) return -2;                 \
+    }                                                                                                  \
+    return 0;                                                                                          \
+  }
+#define TNNB_CHECK(idx, limit) tnnb::bounds_ok(&tnnb::g_bounds, (long long)(idx), (long long)(limit), __LINE__)
+#else
+#define TNNB_BOUNDS_TU(tu) \
+  extern "C" int tnnb_bounds_fetch_##tu(int*, long long*) { return -1; /* not a checked build */ }
+#define TNNB_CHECK(idx, limit) (true)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -23,10 +23,15 @@ c_float = ctypes.c_float
 c_ull = ctypes.c_ulonglong
 
 
+def bounds_checked() -> bool:
+    """True when this process runs the bounds-checked build of the kernels (``TNNB_BOUNDS_CHECK=1``)."""
+    return os.environ.get("TNNB_BOUNDS_CHECK", "") == "1"
+
+
 def lib_path() -> str:
     from .. import _build
 
-    return _build.kernels_path()
+    return _build.kernels_path(bounds_checked())
 
 
 def load(build_if_missing: bool = True):
@@ -43,7 +48,7 @@ def load(build_if_missing: bool = True):
                 raise RuntimeError(f"tnn_b200 kernel library missing: {path}")
             from .. import _build
 
-            _build.build_kernels()
+            _build.build_kernels(bounds_check=bounds_checked())
         lib = ctypes.CDLL(path)
         _declare(lib)
         _LIB = lib
@@ -122,6 +127,37 @@ def check_status(device=None):
     if code != 0:
         w.zero_()
         raise RuntimeError(f"tnn_b200 kernel reported status {code}: {_STATUS_NAMES.get(code, '?')}")
+
+
+_BOUNDS_FILES = ("elementwise", "loss_optim", "conv_pool", "batchnorm")
+
+
+def fetch_bounds_violations():
+    """Read and clear the bounds records of the checked build: a list of ``{"file", "line", "index", "limit"}`` (first
+    violation per kernel source file). Synchronises the device. Raises if the loaded library is the regular build."""
+    lib = load()
+    out = []
+    for name in _BOUNDS_FILES:
+        fn = getattr(lib, "tnnb_bounds_fetch_" + name)
+        fn.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_longlong)]
+        fn.restype = ctypes.c_int
+        hl = (ctypes.c_int * 2)()
+        il = (ctypes.c_longlong * 2)()
+        rc = fn(hl, il)
+        if rc == -1:
+            raise RuntimeError("the loaded kernel library is not the bounds-checked build (set TNNB_BOUNDS_CHECK=1 before importing)")
+        if rc != 0:
+            raise RuntimeError(f"reading the bounds record of {name} failed ({rc})")
+        if hl[0]:
+            out.append({"file": name + ".cu", "line": int(hl[1]), "index": int(il[0]), "limit": int(il[1])})
+    return out
+
+
+def check_bounds():
+    """Raise ``IndexError`` if a kernel of the checked build recorded an out-of-range index since the last call."""
+    v = fetch_bounds_violations()
+    if v:
+        raise IndexError("; ".join(f"{r['file']}:{r['line']} index {r['index']} outside [0, {r['limit']})" for r in v))
 
 
 def check_rc(rc: int, what: str):
