@@ -28,9 +28,12 @@ COMPUTE, COMMUNICATION, OTHER = 0, 1, 2
 
 
 class LayerProfiler:
-    def __init__(self, device: torch.device, source: str = "rank0", cumulative: bool = False):
+    def __init__(self, device: torch.device, source: str = "rank0", cumulative: bool = False, nvtx: Optional[bool] = None):
         self.device, self.source, self.cumulative = device, source, cumulative
         self.cuda = device.type == "cuda"
+        # NVTX ranges ("layer:phase") around every span, so that a timeline tool shows the same names as the event
+        # log; on by default on a GPU, TNNB_NVTX=0 turns them off
+        self.nvtx = (self.cuda and os.environ.get("TNNB_NVTX", "1") != "0") if nvtx is None else (bool(nvtx) and self.cuda)
         self._pending: List[Tuple[str, str, object, object]] = []
         self.totals: "OrderedDict[Tuple[str, str], List[float]]" = OrderedDict()  # (name, phase) -> [ms, calls]
         self.profiler = H.Profiler()
@@ -45,9 +48,15 @@ class LayerProfiler:
     def span(self, name: str, phase: str):
         if self.cuda:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if self.nvtx:
+                torch.cuda.nvtx.range_push(f"{name}:{phase}")
             a.record()
-            yield
-            b.record()
+            try:
+                yield
+            finally:
+                b.record()
+                if self.nvtx:
+                    torch.cuda.nvtx.range_pop()
             self._pending.append((name, phase, a, b))
         else:
             t0 = time.perf_counter_ns()
