@@ -140,7 +140,7 @@ def cmd_batchnorm(a):
     f = timeit(lambda: raw.batchnorm_fwd_train(x, g, b, rm, rv, 1e-5, 0.1, True), a.iters)
     y, mean, rstd = raw.batchnorm_fwd_train(x, g, b, rm, rv, 1e-5, 0.1, True)
     dg, db = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
-    bw = timeit(lambda: raw.batchnorm_bwd(y, x, y, mean, rstd, g, dg, db, True), a.iters)
+    bw = timeit(lambda: raw.batchnorm_bwd(y, x, y, mean, rstd, g, dg, db, True, beta=b), a.iters)
     byt = x.numel() * 2
     return {"fwd_ms": f, "fwd_gbs": round(3 * byt / f / 1e6), "bwd_ms": bw, "bwd_gbs": round(5 * byt / bw / 1e6)}
 

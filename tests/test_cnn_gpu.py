@@ -70,6 +70,13 @@ def test_batchnorm(shape, relu, affine):
     if affine:
         close(dg, rdg, tol=3e-2)
         close(db, rdb, tol=3e-2)
+    if relu:
+        # the same backward with the ReLU mask recomputed from x (beta given, y never read) must agree (up to the order of the atomic partial sums)
+        dg2, db2 = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+        dx2 = raw.batchnorm_bwd(dy.cuda(), x.cuda(), None, mean, rstd, g.cuda(), dg2, db2, relu, beta=b.cuda())
+        close(dx2, dx, tol=1e-3, what="dx with recomputed mask")  # one flipped mask element would be an O(1) difference
+        close(dg2, dg, tol=1e-4)
+        close(db2, db, tol=1e-4)
     yi = raw.batchnorm_infer(x.cuda(), None if g is None else g.cuda(), None if b is None else b.cuda(), crm, crv, 1e-5, relu)
     close(yi, raw.batchnorm_infer(x, g, b, rm, rv, 1e-5, relu), what="infer")
 

@@ -47,6 +47,7 @@ static int bn_cl(int C) {
 template <bool BWD>
 __global__ void __launch_bounds__(256)
 bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
+                 const bf16* __restrict__ gamma, const bf16* __restrict__ beta,
                  const float* __restrict__ mean, const float* __restrict__ rstd, double* __restrict__ ws, long long M,
                  int C, long long rows_per_block, int relu) {
   __shared__ float red[2][256][9];
@@ -57,10 +58,17 @@ bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const 
 #pragma unroll
   for (int k = 0; k < 8; ++k) a[k] = 0.f, b[k] = 0.f;
   if (c0 < C) {
-    float mu[8], rs[8];
+    float mu[8], rs[8], sc[8], sh[8];
+    // Fused ReLU without the saved output: the mask y > 0 is recomputed from x with the forward's own expression
+    // (same fp32 scale and shift), which saves one of the three tensor reads of this pass.
+    const bool remask = BWD && relu && !y;
     if (BWD) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) mu[k] = mean[c0 + k], rs[k] = rstd[c0 + k];
+      for (int k = 0; k < 8; ++k) {
+        mu[k] = mean[c0 + k], rs[k] = rstd[c0 + k];
+        sc[k] = (gamma ? __bfloat162float(gamma[c0 + k]) : 1.f) * rs[k];
+        sh[k] = (beta ? __bfloat162float(beta[c0 + k]) : 0.f) - mu[k] * sc[k];
+      }
     }
     for (long long r = r0 + ry; r < r1; r += nry) {
       if (!TNNB_CHECK(r * C + c0 + 7, M * (long long)C)) break;  // lane layout vs. tensor extent
@@ -77,14 +85,19 @@ bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const 
         uint4 graw = *reinterpret_cast<const uint4*>(dy + r * C + c0);
         const bf16* gv = reinterpret_cast<const bf16*>(&graw);
         uint4 yraw = make_uint4(0, 0, 0, 0);
-        if (relu) yraw = *reinterpret_cast<const uint4*>(y + r * C + c0);
+        if (relu && !remask) yraw = *reinterpret_cast<const uint4*>(y + r * C + c0);
         const bf16* yv = reinterpret_cast<const bf16*>(&yraw);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           float g = __bfloat162float(gv[k]);
-          if (relu && !(__bfloat162float(yv[k]) > 0.f)) g = 0.f;
+          const float xf = __bfloat162float(xv[k]);
+          if (remask) {
+            if (!(__bfloat162float(__float2bfloat16(xf * sc[k] + sh[k])) > 0.f)) g = 0.f;
+          } else if (relu && !(__bfloat162float(yv[k]) > 0.f)) {
+            g = 0.f;
+          }
           a[k] += g;
-          b[k] += g * (__bfloat162float(xv[k]) - mu[k]) * rs[k];
+          b[k] += g * (xf - mu[k]) * rs[k];
         }
       }
     }
@@ -154,17 +167,21 @@ bn_fwd_apply_kernel(const bf16* __restrict__ x, bf16* __restrict__ yout, const b
 
 __global__ void __launch_bounds__(256)
 bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
-                    const bf16* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ rstd,
+                    const bf16* __restrict__ gamma, const bf16* __restrict__ beta, const float* __restrict__ mean,
+                    const float* __restrict__ rstd,
                     const double* __restrict__ ws, bf16* __restrict__ dx, float* __restrict__ dgamma,
                     float* __restrict__ dbeta, long long M, int C, long long rows_per_block, int relu) {
   const BnLane ln = bn_lane(C);
   const int ry = ln.ry, c0 = ln.c0, nry = ln.nry;
   if (c0 >= C) return;
-  float mu[8], rs[8], k1[8], sg[8], sgx[8];
+  float mu[8], rs[8], k1[8], sg[8], sgx[8], sc[8], sh[8];
+  const bool remask = relu && !y;  // see bn_reduce_kernel
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     mu[k] = mean[c0 + k];
     rs[k] = rstd[c0 + k];
+    sc[k] = (gamma ? __bfloat162float(gamma[c0 + k]) : 1.f) * rs[k];
+    sh[k] = (beta ? __bfloat162float(beta[c0 + k]) : 0.f) - mu[k] * sc[k];
     sg[k] = (float)ws[c0 + k];
     sgx[k] = (float)ws[C + c0 + k];
     k1[k] = (gamma ? __bfloat162float(gamma[c0 + k]) : 1.f) * rs[k] / (float)M;
@@ -181,14 +198,19 @@ bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, con
     uint4 graw = *reinterpret_cast<const uint4*>(dy + r * C + c0);
     const bf16* gv = reinterpret_cast<const bf16*>(&graw);
     uint4 yraw = make_uint4(0, 0, 0, 0);
-    if (relu) yraw = *reinterpret_cast<const uint4*>(y + r * C + c0);
+    if (relu && !remask) yraw = *reinterpret_cast<const uint4*>(y + r * C + c0);
     const bf16* yv = reinterpret_cast<const bf16*>(&yraw);
     __align__(16) bf16 o[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       float g = __bfloat162float(gv[k]);
-      if (relu && !(__bfloat162float(yv[k]) > 0.f)) g = 0.f;
-      const float xh = (__bfloat162float(xv[k]) - mu[k]) * rs[k];
+      const float xf = __bfloat162float(xv[k]);
+      if (remask) {
+        if (!(__bfloat162float(__float2bfloat16(xf * sc[k] + sh[k])) > 0.f)) g = 0.f;
+      } else if (relu && !(__bfloat162float(yv[k]) > 0.f)) {
+        g = 0.f;
+      }
+      const float xh = (xf - mu[k]) * rs[k];
       o[k] = __float2bfloat16(k1[k] * ((float)M * g - sg[k] - xh * sgx[k]));
     }
     *reinterpret_cast<uint4*>(dx + r * C + c0) = *reinterpret_cast<uint4*>(o);
@@ -223,7 +245,7 @@ int tnnb_batchnorm_fwd(const void* x, void* y, const void* gamma, const void* be
   bn_grid(M, C, grid, rpb);
   if (training) {
     cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st);
-    bn_reduce_kernel<false><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, (double*)ws, M, C, rpb, 0);
+    bn_reduce_kernel<false><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (double*)ws, M, C, rpb, 0);
   }
   bn_fwd_apply_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)y, (const bf16*)gamma, (const bf16*)beta, (const double*)ws,
                                             (float*)mean, (float*)rstd, (float*)run_mean, (float*)run_var, M, C, rpb, eps,
@@ -232,20 +254,23 @@ int tnnb_batchnorm_fwd(const void* x, void* y, const void* gamma, const void* be
   return e == cudaSuccess ? 0 : -(int)e - 1000;
 }
 
-// y: saved forward output (needed only when relu != 0). dgamma/dbeta (fp32) accumulate; may be null.
-int tnnb_batchnorm_bwd(const void* x, const void* dy, const void* y, const void* gamma, const void* mean, const void* rstd,
-                       void* ws, void* dx, void* dgamma, void* dbeta, long long M, int C, int relu, void* stream) {
+// Fused ReLU (relu != 0): with y == null the mask is recomputed from x, gamma, beta, mean and rstd (beta is read only
+// then); with the saved forward output y it is y > 0. dgamma/dbeta (fp32) accumulate; may be null.
+int tnnb_batchnorm_bwd(const void* x, const void* dy, const void* y, const void* gamma, const void* beta, const void* mean,
+                       const void* rstd, void* ws, void* dx, void* dgamma, void* dbeta, long long M, int C, int relu,
+                       void* stream) {
   if (C % 8 || ((uintptr_t)x & 15) || ((uintptr_t)dy & 15) || ((uintptr_t)dx & 15)) return -3;
-  if (relu && !y) return -5;
+  if (relu && !y && gamma && !beta) return -5;  // an affine layer's mask needs its shift
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid;
   long long rpb;
   bn_grid(M, C, grid, rpb);
   cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st);
-  bn_reduce_kernel<true><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y, (const float*)mean,
-                                               (const float*)rstd, (double*)ws, M, C, rpb, relu);
+  bn_reduce_kernel<true><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y, (const bf16*)gamma,
+                                               (const bf16*)beta, (const float*)mean, (const float*)rstd, (double*)ws, M, C,
+                                               rpb, relu);
   bn_bwd_apply_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y, (const bf16*)gamma,
-                                            (const float*)mean, (const float*)rstd, (const double*)ws, (bf16*)dx,
+                                            (const bf16*)beta, (const float*)mean, (const float*)rstd, (const double*)ws, (bf16*)dx,
                                             (float*)dgamma, (float*)dbeta, M, C, rpb, relu);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
@@ -292,7 +317,7 @@ int tnnb_batchnorm_fwd_noalloc(const void* x, void* y, const void* gamma, const 
   bn_grid(M, C, grid, rpb);
   // The reduce kernel accumulates with atomics, so the 2*C sums it uses must start at zero.
   if (cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st) != cudaSuccess) return TNNB_NOALLOC_LAUNCH_FAILED;
-  bn_reduce_kernel<false><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, ws, M, C, rpb, 0);
+  bn_reduce_kernel<false><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, ws, M, C, rpb, 0);
   bn_fwd_apply_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)y, (const bf16*)gamma, (const bf16*)beta, ws, (float*)mean,
                                             (float*)rstd, (float*)run_mean, (float*)run_var, M, C, rpb, eps, momentum, relu, 1);
   return cudaGetLastError() == cudaSuccess ? TNNB_NOALLOC_OK : TNNB_NOALLOC_LAUNCH_FAILED;

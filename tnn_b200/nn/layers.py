@@ -643,9 +643,9 @@ class BatchNorm(Layer):
         return raw.batchnorm_infer(x, g, b, rm, rv, self.epsilon, self.use_relu)
 
     def backward(self, grad, ctx):
-        g, _, _, _ = self._split()
+        g, b, _, _ = self._split()
         dg, db = (self.grads[0], self.grads[1]) if self.affine and self.grads[0] is not None else (None, None)
-        dx = raw.batchnorm_bwd(grad.contiguous(), ctx["x"], ctx["y"], ctx["mean"], ctx["rstd"], g, dg, db, self.use_relu)
+        dx = raw.batchnorm_bwd(grad.contiguous(), ctx["x"], ctx["y"], ctx["mean"], ctx["rstd"], g, dg, db, self.use_relu, beta=b)
         return [dx]
 
 

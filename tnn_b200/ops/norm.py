@@ -17,7 +17,7 @@ def _l():
     if not _DECL:
         vp, i, ll, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
         lib.tnnb_batchnorm_fwd.argtypes = [vp] * 9 + [ll, i, f, f, i, i, vp]
-        lib.tnnb_batchnorm_bwd.argtypes = [vp] * 10 + [ll, i, i, vp]
+        lib.tnnb_batchnorm_bwd.argtypes = [vp] * 11 + [ll, i, i, vp]
         lib.tnnb_batchnorm_fwd.restype = lib.tnnb_batchnorm_bwd.restype = i
         _DECL = True
     return lib
@@ -55,14 +55,17 @@ def batchnorm_infer(x, gamma, beta, run_mean, run_var, eps, relu):
     return y
 
 
-def batchnorm_bwd(dy, x, y, mean, rstd, gamma, dgamma, dbeta, relu):
+def batchnorm_bwd(dy, x, y, mean, rstd, gamma, dgamma, dbeta, relu, beta=None):
+    """With a fused ReLU the kernels recompute the mask ``y > 0`` from ``x`` (same scale / shift arithmetic as the
+    forward) when they know the layer's shift - ``beta`` given, or a non-affine layer - and then never read ``y``."""
     C = x.shape[-1]
     M = x.numel() // C
     dx = torch.empty_like(x)
     ws = torch.empty(2 * C, dtype=torch.float64, device=x.device)
-    rc = _l().tnnb_batchnorm_bwd(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(y if relu else None), _lib.ptr(gamma), _lib.ptr(mean),
-                                 _lib.ptr(rstd), _lib.ptr(ws), _lib.ptr(dx), _lib.ptr(dgamma), _lib.ptr(dbeta), M, C, int(relu),
-                                 _lib.stream())
+    remask = relu and (beta is not None or gamma is None)
+    rc = _l().tnnb_batchnorm_bwd(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(y if (relu and not remask) else None), _lib.ptr(gamma),
+                                 _lib.ptr(beta if remask else None), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(ws), _lib.ptr(dx),
+                                 _lib.ptr(dgamma), _lib.ptr(dbeta), M, C, int(relu), _lib.stream())
     _lib.check_rc(rc, "batchnorm_bwd")
     LAUNCHES["count"] += 2
     return dx

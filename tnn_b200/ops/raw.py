@@ -510,12 +510,13 @@ def batchnorm_infer(x, gamma, beta, run_mean, run_var, eps: float, relu: bool):
     return y.reshape(x.shape).to(x.dtype)
 
 
-def batchnorm_bwd(dy, x, y, mean, rstd, gamma, dgamma, dbeta, relu: bool):
-    """dx; dgamma/dbeta (fp32) accumulate. ``y`` is the saved post-ReLU output when relu is fused."""
+def batchnorm_bwd(dy, x, y, mean, rstd, gamma, dgamma, dbeta, relu: bool, beta=None):
+    """dx; dgamma/dbeta (fp32) accumulate. ``y`` is the saved post-ReLU output when relu is fused; the GPU kernels do
+    not read it when ``beta`` is passed (they recompute the mask from ``x``)."""
     C = x.shape[-1]
     if x.is_cuda and x.dtype == torch.bfloat16:
         from . import norm
-        return norm.batchnorm_bwd(dy, x, y, mean, rstd, gamma, dgamma, dbeta, relu)
+        return norm.batchnorm_bwd(dy, x, y, mean, rstd, gamma, dgamma, dbeta, relu, beta)
     x2, g = x.reshape(-1, C).float(), dy.reshape(-1, C).float()
     M = x2.shape[0]
     if relu:
