@@ -37,6 +37,7 @@ __device__ __forceinline__ BnLane bn_lane(int C) {
   l.c0 = (blockIdx.x * l.cl + l.cx) * 8;
   return l;
 }
+static constexpr int BN_U = 4;  // rows in flight per thread and trip of the row loops
 static int bn_cl(int C) {
   int cl = 32;
   while (cl > (C >> 3)) cl >>= 1;
@@ -44,12 +45,13 @@ static int bn_cl(int C) {
 }
 
 // ws: double[2*C] (sum, sum of squares) - or (sum dy, sum dy*xhat) for the backward.
-template <bool BWD>
-__global__ void __launch_bounds__(256)
+// MASK (backward with a fused ReLU): 0 = none, 1 = y > 0 read from the saved output, 2 = recomputed from x.
+template <bool BWD, int MASK>
+__global__ void __launch_bounds__(256, 2)
 bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
                  const bf16* __restrict__ gamma, const bf16* __restrict__ beta,
                  const float* __restrict__ mean, const float* __restrict__ rstd, double* __restrict__ ws, long long M,
-                 int C, long long rows_per_block, int relu) {
+                 int C, long long rows_per_block) {
   __shared__ float red[2][256][9];
   const BnLane ln = bn_lane(C);
   const int cx = ln.cx, ry = ln.ry, c0 = ln.c0, nry = ln.nry;
@@ -61,7 +63,8 @@ bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const 
     float mu[8], rs[8], sc[8], sh[8];
     // Fused ReLU without the saved output: the mask y > 0 is recomputed from x with the forward's own expression
     // (same fp32 scale and shift), which saves one of the three tensor reads of this pass.
-    const bool remask = BWD && relu && !y;
+    constexpr bool remask = BWD && MASK == 2;
+    constexpr bool relu = BWD && MASK != 0;
     if (BWD) {
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
@@ -70,34 +73,48 @@ bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const 
         sh[k] = (beta ? __bfloat162float(beta[c0 + k]) : 0.f) - mu[k] * sc[k];
       }
     }
-    for (long long r = r0 + ry; r < r1; r += nry) {
-      if (!TNNB_CHECK(r * C + c0 + 7, M * (long long)C)) break;  // lane layout vs. tensor extent
-      uint4 raw = *reinterpret_cast<const uint4*>(x + r * C + c0);
-      const bf16* xv = reinterpret_cast<const bf16*>(&raw);
-      if (!BWD) {
+    // BN_U rows per trip: all loads of a trip are issued before the first use, which keeps enough bytes in flight
+    // per SM to cover the DRAM latency. Rows past the end load nothing and contribute zeros.
+    for (long long r = r0 + ry; r < r1; r += BN_U * nry) {
+      uint4 xr[BN_U], gr[BWD ? BN_U : 1], yr[MASK == 1 ? BN_U : 1];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float v = __bfloat162float(xv[k]);
-          a[k] += v;
-          b[k] += v * v;
+      for (int u = 0; u < BN_U; ++u) {
+        const long long rr = r + (long long)u * nry;
+        const bool ok = rr < r1 && TNNB_CHECK(rr * C + c0 + 7, M * (long long)C);  // lane layout vs. tensor extent
+        xr[u] = make_uint4(0, 0, 0, 0);
+        if (BWD) gr[BWD ? u : 0] = make_uint4(0, 0, 0, 0);
+        if (MASK == 1) yr[MASK == 1 ? u : 0] = make_uint4(0, 0, 0, 0);
+        if (ok) {
+          xr[u] = *reinterpret_cast<const uint4*>(x + rr * C + c0);
+          if (BWD) gr[BWD ? u : 0] = *reinterpret_cast<const uint4*>(dy + rr * C + c0);
+          if (MASK == 1) yr[MASK == 1 ? u : 0] = *reinterpret_cast<const uint4*>(y + rr * C + c0);
         }
-      } else {
-        uint4 graw = *reinterpret_cast<const uint4*>(dy + r * C + c0);
-        const bf16* gv = reinterpret_cast<const bf16*>(&graw);
-        uint4 yraw = make_uint4(0, 0, 0, 0);
-        if (relu && !remask) yraw = *reinterpret_cast<const uint4*>(y + r * C + c0);
-        const bf16* yv = reinterpret_cast<const bf16*>(&yraw);
+      }
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          float g = __bfloat162float(gv[k]);
-          const float xf = __bfloat162float(xv[k]);
-          if (remask) {
-            if (!(__bfloat162float(__float2bfloat16(xf * sc[k] + sh[k])) > 0.f)) g = 0.f;
-          } else if (relu && !(__bfloat162float(yv[k]) > 0.f)) {
-            g = 0.f;
+      for (int u = 0; u < BN_U; ++u) {
+        const bf16* xv = reinterpret_cast<const bf16*>(&xr[u]);
+        if (!BWD) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float v = __bfloat162float(xv[k]);
+            a[k] += v;
+            b[k] += v * v;
           }
-          a[k] += g;
-          b[k] += g * (xf - mu[k]) * rs[k];
+        } else {
+          const bf16* gv = reinterpret_cast<const bf16*>(&gr[BWD ? u : 0]);
+          const bf16* yv = reinterpret_cast<const bf16*>(&yr[MASK == 1 ? u : 0]);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            float g = __bfloat162float(gv[k]);
+            const float xf = __bfloat162float(xv[k]);
+            if (remask) {
+              if (!(__bfloat162float(__float2bfloat16(xf * sc[k] + sh[k])) > 0.f)) g = 0.f;
+            } else if (relu && !(__bfloat162float(yv[k]) > 0.f)) {
+              g = 0.f;
+            }
+            a[k] += g;
+            b[k] += g * (xf - mu[k]) * rs[k];
+          }
         }
       }
     }
@@ -151,31 +168,42 @@ bn_fwd_apply_kernel(const bf16* __restrict__ x, bf16* __restrict__ yout, const b
     sh[k] = b - mu * sc[k];
   }
   const long long r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
-  for (long long r = r0 + ry; r < r1; r += nry) {
-    if (!TNNB_CHECK(r * C + c0 + 7, M * (long long)C)) break;  // lane layout vs. tensor extent
-    uint4 raw = *reinterpret_cast<const uint4*>(x + r * C + c0);
-    const bf16* xv = reinterpret_cast<const bf16*>(&raw);
-    __align__(16) bf16 o[8];
+  for (long long r = r0 + ry; r < r1; r += BN_U * nry) {
+    uint4 xr[BN_U];
+    bool ok[BN_U];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      float v = __bfloat162float(xv[k]) * sc[k] + sh[k];
-      o[k] = __float2bfloat16(relu ? fmaxf(v, 0.f) : v);
+    for (int u = 0; u < BN_U; ++u) {
+      const long long rr = r + (long long)u * nry;
+      ok[u] = rr < r1 && TNNB_CHECK(rr * C + c0 + 7, M * (long long)C);  // lane layout vs. tensor extent
+      xr[u] = make_uint4(0, 0, 0, 0);
+      if (ok[u]) xr[u] = *reinterpret_cast<const uint4*>(x + rr * C + c0);
     }
-    *reinterpret_cast<uint4*>(yout + r * C + c0) = *reinterpret_cast<uint4*>(o);
+#pragma unroll
+    for (int u = 0; u < BN_U; ++u) {
+      const bf16* xv = reinterpret_cast<const bf16*>(&xr[u]);
+      __align__(16) bf16 o[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float v = __bfloat162float(xv[k]) * sc[k] + sh[k];
+        o[k] = __float2bfloat16(relu ? fmaxf(v, 0.f) : v);
+      }
+      if (ok[u]) *reinterpret_cast<uint4*>(yout + (r + (long long)u * nry) * C + c0) = *reinterpret_cast<uint4*>(o);
+    }
   }
 }
 
-__global__ void __launch_bounds__(256)
+template <int MASK>
+__global__ void __launch_bounds__(256, 2)
 bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
                     const bf16* __restrict__ gamma, const bf16* __restrict__ beta, const float* __restrict__ mean,
                     const float* __restrict__ rstd,
                     const double* __restrict__ ws, bf16* __restrict__ dx, float* __restrict__ dgamma,
-                    float* __restrict__ dbeta, long long M, int C, long long rows_per_block, int relu) {
+                    float* __restrict__ dbeta, long long M, int C, long long rows_per_block) {
   const BnLane ln = bn_lane(C);
   const int ry = ln.ry, c0 = ln.c0, nry = ln.nry;
   if (c0 >= C) return;
   float mu[8], rs[8], k1[8], sg[8], sgx[8], sc[8], sh[8];
-  const bool remask = relu && !y;  // see bn_reduce_kernel
+  constexpr bool remask = MASK == 2, relu = MASK != 0;  // see bn_reduce_kernel
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     mu[k] = mean[c0 + k];
@@ -191,29 +219,41 @@ bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, con
     }
   }
   const long long r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
-  for (long long r = r0 + ry; r < r1; r += nry) {
-    if (!TNNB_CHECK(r * C + c0 + 7, M * (long long)C)) break;  // lane layout vs. tensor extent
-    uint4 raw = *reinterpret_cast<const uint4*>(x + r * C + c0);
-    const bf16* xv = reinterpret_cast<const bf16*>(&raw);
-    uint4 graw = *reinterpret_cast<const uint4*>(dy + r * C + c0);
-    const bf16* gv = reinterpret_cast<const bf16*>(&graw);
-    uint4 yraw = make_uint4(0, 0, 0, 0);
-    if (relu && !remask) yraw = *reinterpret_cast<const uint4*>(y + r * C + c0);
-    const bf16* yv = reinterpret_cast<const bf16*>(&yraw);
-    __align__(16) bf16 o[8];
+  for (long long r = r0 + ry; r < r1; r += BN_U * nry) {
+    uint4 xr[BN_U], gr[BN_U], yr[MASK == 1 ? BN_U : 1];
+    bool ok[BN_U];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      float g = __bfloat162float(gv[k]);
-      const float xf = __bfloat162float(xv[k]);
-      if (remask) {
-        if (!(__bfloat162float(__float2bfloat16(xf * sc[k] + sh[k])) > 0.f)) g = 0.f;
-      } else if (relu && !(__bfloat162float(yv[k]) > 0.f)) {
-        g = 0.f;
+    for (int u = 0; u < BN_U; ++u) {
+      const long long rr = r + (long long)u * nry;
+      ok[u] = rr < r1 && TNNB_CHECK(rr * C + c0 + 7, M * (long long)C);  // lane layout vs. tensor extent
+      xr[u] = gr[u] = make_uint4(0, 0, 0, 0);
+      if (MASK == 1) yr[MASK == 1 ? u : 0] = make_uint4(0, 0, 0, 0);
+      if (ok[u]) {
+        xr[u] = *reinterpret_cast<const uint4*>(x + rr * C + c0);
+        gr[u] = *reinterpret_cast<const uint4*>(dy + rr * C + c0);
+        if (MASK == 1) yr[MASK == 1 ? u : 0] = *reinterpret_cast<const uint4*>(y + rr * C + c0);
       }
-      const float xh = (xf - mu[k]) * rs[k];
-      o[k] = __float2bfloat16(k1[k] * ((float)M * g - sg[k] - xh * sgx[k]));
     }
-    *reinterpret_cast<uint4*>(dx + r * C + c0) = *reinterpret_cast<uint4*>(o);
+#pragma unroll
+    for (int u = 0; u < BN_U; ++u) {
+      const bf16* xv = reinterpret_cast<const bf16*>(&xr[u]);
+      const bf16* gv = reinterpret_cast<const bf16*>(&gr[u]);
+      const bf16* yv = reinterpret_cast<const bf16*>(&yr[MASK == 1 ? u : 0]);
+      __align__(16) bf16 o[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float g = __bfloat162float(gv[k]);
+        const float xf = __bfloat162float(xv[k]);
+        if (remask) {
+          if (!(__bfloat162float(__float2bfloat16(xf * sc[k] + sh[k])) > 0.f)) g = 0.f;
+        } else if (relu && !(__bfloat162float(yv[k]) > 0.f)) {
+          g = 0.f;
+        }
+        const float xh = (xf - mu[k]) * rs[k];
+        o[k] = __float2bfloat16(k1[k] * ((float)M * g - sg[k] - xh * sgx[k]));
+      }
+      if (ok[u]) *reinterpret_cast<uint4*>(dx + (r + (long long)u * nry) * C + c0) = *reinterpret_cast<uint4*>(o);
+    }
   }
 }
 
@@ -245,7 +285,7 @@ int tnnb_batchnorm_fwd(const void* x, void* y, const void* gamma, const void* be
   bn_grid(M, C, grid, rpb);
   if (training) {
     cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st);
-    bn_reduce_kernel<false><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (double*)ws, M, C, rpb, 0);
+    bn_reduce_kernel<false, 0><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (double*)ws, M, C, rpb);
   }
   bn_fwd_apply_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)y, (const bf16*)gamma, (const bf16*)beta, (const double*)ws,
                                             (float*)mean, (float*)rstd, (float*)run_mean, (float*)run_var, M, C, rpb, eps,
@@ -266,12 +306,20 @@ int tnnb_batchnorm_bwd(const void* x, const void* dy, const void* y, const void*
   long long rpb;
   bn_grid(M, C, grid, rpb);
   cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st);
-  bn_reduce_kernel<true><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y, (const bf16*)gamma,
-                                               (const bf16*)beta, (const float*)mean, (const float*)rstd, (double*)ws, M, C,
-                                               rpb, relu);
-  bn_bwd_apply_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y, (const bf16*)gamma,
-                                            (const bf16*)beta, (const float*)mean, (const float*)rstd, (const double*)ws, (bf16*)dx,
-                                            (float*)dgamma, (float*)dbeta, M, C, rpb, relu);
+#define TNNB_BN_BWD(MASK)                                                                                              \
+  do {                                                                                                                 \
+    bn_reduce_kernel<true, MASK><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y, (const bf16*)gamma, \
+                                                       (const bf16*)beta, (const float*)mean, (const float*)rstd,       \
+                                                       (double*)ws, M, C, rpb);                                         \
+    bn_bwd_apply_kernel<MASK><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y, (const bf16*)gamma,  \
+                                                    (const bf16*)beta, (const float*)mean, (const float*)rstd,          \
+                                                    (const double*)ws, (bf16*)dx, (float*)dgamma, (float*)dbeta, M, C,  \
+                                                    rpb);                                                               \
+  } while (0)
+  if (!relu) TNNB_BN_BWD(0);
+  else if (y) TNNB_BN_BWD(1);
+  else TNNB_BN_BWD(2);
+#undef TNNB_BN_BWD
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
 }
@@ -317,7 +365,7 @@ int tnnb_batchnorm_fwd_noalloc(const void* x, void* y, const void* gamma, const 
   bn_grid(M, C, grid, rpb);
   // The reduce kernel accumulates with atomics, so the 2*C sums it uses must start at zero.
   if (cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st) != cudaSuccess) return TNNB_NOALLOC_LAUNCH_FAILED;
-  bn_reduce_kernel<false><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, ws, M, C, rpb, 0);
+  bn_reduce_kernel<false, 0><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, ws, M, C, rpb);
   bn_fwd_apply_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)y, (const bf16*)gamma, (const bf16*)beta, ws, (float*)mean,
                                             (float*)rstd, (float*)run_mean, (float*)run_var, M, C, rpb, eps, momentum, relu, 1);
   return cudaGetLastError() == cudaSuccess ? TNNB_NOALLOC_OK : TNNB_NOALLOC_LAUNCH_FAILED;
