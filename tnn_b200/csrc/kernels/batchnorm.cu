@@ -75,10 +75,11 @@ bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const 
     }
     // BN_U rows per trip: all loads of a trip are issued before the first use, which keeps enough bytes in flight
     // per SM to cover the DRAM latency. Rows past the end load nothing and contribute zeros.
-    for (long long r = r0 + ry; r < r1; r += BN_U * nry) {
-      uint4 xr[BN_U], gr[BWD ? BN_U : 1], yr[MASK == 1 ? BN_U : 1];
+    constexpr int U = BWD ? BN_U : 2 * BN_U;  // the forward statistics pass reads one tensor: twice the rows
+    for (long long r = r0 + ry; r < r1; r += U * nry) {
+      uint4 xr[U], gr[BWD ? U : 1], yr[MASK == 1 ? U : 1];
 #pragma unroll
-      for (int u = 0; u < BN_U; ++u) {
+      for (int u = 0; u < U; ++u) {
         const long long rr = r + (long long)u * nry;
         const bool ok = rr < r1 && TNNB_CHECK(rr * C + c0 + 7, M * (long long)C);  // lane layout vs. tensor extent
         xr[u] = make_uint4(0, 0, 0, 0);
@@ -91,7 +92,7 @@ bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const 
         }
       }
 #pragma unroll
-      for (int u = 0; u < BN_U; ++u) {
+      for (int u = 0; u < U; ++u) {
         const bf16* xv = reinterpret_cast<const bf16*>(&xr[u]);
         if (!BWD) {
 #pragma unroll

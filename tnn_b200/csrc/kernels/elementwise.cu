@@ -121,18 +121,22 @@ __global__ void dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y,
                                unsigned long long seed, const unsigned long long* __restrict__ seed_off) {
   seed = mix_seed(seed, seed_off);
   const float inv = 1.f / (1.f - p);
+  const uint32_t thr = dropout_threshold(p);
   long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
   const long long stride = (long long)gridDim.x * blockDim.x * 8;
   for (; i + 8 <= n; i += stride) {
     float f[8];
     load8(x + i, f);
+    const uint32_t keep = dropout_keep8(seed, (uint64_t)(i >> 3), thr);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) f[k] = hash_uniform(seed, i + k) >= p ? f[k] * inv : 0.f;
+    for (int k = 0; k < 8; ++k) f[k] = (keep >> k) & 1u ? f[k] * inv : 0.f;
     store8(y + i, f);
   }
-  if (i < n && i + 8 > n)
+  if (i < n && i + 8 > n) {
+    const uint32_t keep = dropout_keep8(seed, (uint64_t)(i >> 3), thr);
     for (long long j = i; j < n; ++j)
-      y[j] = __float2bfloat16(hash_uniform(seed, j) >= p ? __bfloat162float(x[j]) * inv : 0.f);
+      y[j] = __float2bfloat16((keep >> (int)(j - i)) & 1u ? __bfloat162float(x[j]) * inv : 0.f);
+  }
 }
 
 // out[r, :] = wte[clamp(id[r])] (+ wpe[r % S]) then optional dropout.
@@ -162,9 +166,9 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const bf
         for (int k = 0; k < 8; ++k) f[k] += g[k];
       }
       if (p > 0.f) {
+        const uint32_t keep = dropout_keep8(seed, (uint64_t)(r * chunks + c), dropout_threshold(p));
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          f[k] = hash_uniform(seed, r * E + c * 8 + k) >= p ? f[k] * inv : 0.f;
+        for (int k = 0; k < 8; ++k) f[k] = (keep >> k) & 1u ? f[k] * inv : 0.f;
       }
       store8(out + r * E + c * 8, f);
     }
@@ -189,9 +193,9 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const bf
       float g[8];
       load8(dy + r * E + c * 8, g);
       if (p > 0.f) {
+        const uint32_t keep = dropout_keep8(seed, (uint64_t)(r * chunks + c), dropout_threshold(p));
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          g[k] = hash_uniform(seed, r * E + c * 8 + k) >= p ? g[k] * inv : 0.f;
+        for (int k = 0; k < 8; ++k) g[k] = (keep >> k) & 1u ? g[k] * inv : 0.f;
       }
       if (!pad && dwte) {
         float* d = dwte + id * E + c * 8;
@@ -218,7 +222,7 @@ colsum_kernel(const bf16* __restrict__ dy, long long ld, float* __restrict__ db,
   const long long r0 = (long long)blockIdx.y * rows_per_block;
   const long long r1 = min(M, r0 + rows_per_block);
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  if (col + 8 <= N && (ld % 8 == 0)) {
+  if (col + 8 <= N && (ld % 8 == 0) && (reinterpret_cast<uintptr_t>(dy) & 15) == 0) {  // 16-byte row loads need both
     long long r = r0 + ry;
     for (; r + 96 < r1; r += 128) {
       float f0[8], f1[8], f2[8], f3[8];

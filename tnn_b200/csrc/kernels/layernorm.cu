@@ -38,6 +38,7 @@ ln_fwd_kernel(const bf16* __restrict__ x_in, const bf16* __restrict__ delta, bf1
   const int wpb = blockDim.x >> 5;
   const int chunks = C >> 3;
   const float inv_keep = 1.f / (1.f - p);
+  const uint32_t thr = dropout_threshold(p);
   for (long long r = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += (long long)gridDim.x * wpb) {
     float v[MAXCH][8];
     float s = 0.f;
@@ -50,10 +51,11 @@ ln_fwd_kernel(const bf16* __restrict__ x_in, const bf16* __restrict__ delta, bf1
         for (int k = 0; k < 8; ++k) v[i][k] = __bfloat162float(a.v[k]);
         if (delta) {
           LBf8 d = *reinterpret_cast<const LBf8*>(delta + r * C + c * 8);
+          const uint32_t keep = p > 0.f ? dropout_keep8(seed, (uint64_t)(r * chunks + c), thr) : 0xffu;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             float dv = __bfloat162float(d.v[k]);
-            if (p > 0.f) dv = hash_uniform(seed, r * C + c * 8 + k) >= p ? dv * inv_keep : 0.f;
+            if (p > 0.f) dv = (keep >> k) & 1u ? dv * inv_keep : 0.f;
             // Round the residual stream to bf16 first so that the saved x_out and
             // the statistics below describe exactly the same numbers.
             v[i][k] = __bfloat162float(__float2bfloat16(v[i][k] + dv));
@@ -136,6 +138,7 @@ ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const flo
   const int wpb = blockDim.x >> 5;
   const int chunks = C >> 3;
   const float inv_keep = 1.f / (1.f - p);
+  const uint32_t thr = dropout_threshold(p);
   float* acc_g = sm + (size_t)warp * 2 * C;
   float* acc_b = acc_g + C;
   for (int i = lane; i < 2 * C; i += 32) acc_g[i] = 0.f;
@@ -204,8 +207,9 @@ ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const flo
           float t[8];
           unpack8(w, t);  // dropout acts on the rounded dx, like a separate pass would
           if (p > 0.f) {
+            const uint32_t keep = dropout_keep8(seed, (uint64_t)(r * chunks + c), thr);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) t[k] = hash_uniform(seed, r * C + c * 8 + k) >= p ? t[k] * inv_keep : 0.f;
+            for (int k = 0; k < 8; ++k) t[k] = (keep >> k) & 1u ? t[k] * inv_keep : 0.f;
           }
           *reinterpret_cast<uint4*>(ddelta + r * C + c * 8) =
               make_uint4(pack2(t[0], t[1]), pack2(t[2], t[3]), pack2(t[4], t[5]), pack2(t[6], t[7]));

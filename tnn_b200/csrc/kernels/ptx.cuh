@@ -461,6 +461,31 @@ __device__ __forceinline__ float hash_uniform(uint64_t seed, uint64_t idx) {
   return static_cast<float>(z >> 40) * (1.0f / 16777216.0f);
 }
 
+// Dropout decisions for the eight elements 8*chunk .. 8*chunk+7 from ONE 64-bit mix (plus one cheap extra round for
+// the second 64 bits): bit k of the result is set when element k is kept, i.e. when its 16-bit uniform is >= thr,
+// thr = dropout_threshold(p) = round(p * 65536). An eighth of the 64-bit multiplies of a per-element hash - the
+// bandwidth-bound kernels that fuse dropout were instruction-bound on it. ops/raw.py dropout_mask is the same function.
+__device__ __forceinline__ uint32_t dropout_threshold(float p) { return (uint32_t)(p * 65536.f + 0.5f); }
+__device__ __forceinline__ uint32_t dropout_keep8(uint64_t seed, uint64_t chunk, uint32_t thr) {
+  uint64_t z = seed + chunk * 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z = z ^ (z >> 31);
+  uint64_t w = (z ^ (z >> 29)) * 0xD6E8FEB86659FD93ull;
+  w = w ^ (w >> 32);
+  const uint32_t z0 = (uint32_t)z, z1 = (uint32_t)(z >> 32), w0 = (uint32_t)w, w1 = (uint32_t)(w >> 32);
+  uint32_t m = 0;
+  m |= ((z0 & 0xffffu) >= thr) ? 1u : 0u;
+  m |= ((z0 >> 16) >= thr) ? 2u : 0u;
+  m |= ((z1 & 0xffffu) >= thr) ? 4u : 0u;
+  m |= ((z1 >> 16) >= thr) ? 8u : 0u;
+  m |= ((w0 & 0xffffu) >= thr) ? 16u : 0u;
+  m |= ((w0 >> 16) >= thr) ? 32u : 0u;
+  m |= ((w1 & 0xffffu) >= thr) ? 64u : 0u;
+  m |= ((w1 >> 16) >= thr) ? 128u : 0u;
+  return m;
+}
+
 // Effective dropout seed: the host-side seed plus an optional step counter that
 // lives in device memory, so that a captured CUDA graph draws a fresh mask on
 // every replay (the counter is bumped once per training step).

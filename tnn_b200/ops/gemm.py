@@ -34,6 +34,19 @@ def _ld(t: torch.Tensor) -> int:
     return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
 
 
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """An operand the TMA descriptors accept: unit inner stride, row pitch and base address multiples of 16 bytes.
+    Tensors produced by the layers already are (their buffers are allocated with padded pitches); anything else -
+    a gradient handed in by user code, an odd-width slice - is copied once into a padded buffer."""
+    per16 = 16 // t.element_size()
+    if t.dim() == 2 and t.stride(1) == 1 and t.data_ptr() % 16 == 0 and _ld(t) % per16 == 0:
+        return t
+    pitch = (t.shape[1] + per16 - 1) // per16 * per16
+    buf = torch.zeros((t.shape[0], pitch), dtype=t.dtype, device=t.device)
+    buf[:, :t.shape[1]].copy_(t)
+    return buf[:, :t.shape[1]]
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
          bias: Optional[torch.Tensor] = None, gelu: bool = False, save_preact: Optional[torch.Tensor] = None,
          dgelu_of: Optional[torch.Tensor] = None, relu: bool = False, residual: Optional[torch.Tensor] = None,
@@ -80,6 +93,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         return out
 
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    a, b = _tma_ready(a), _tma_ready(b)
     flags = 0
     if bias is not None:
         flags |= EPI_BIAS

@@ -57,9 +57,30 @@ def _eff_seed(seed: int) -> int:
 
 
 def dropout_mask(shape, p: float, seed: int, device="cpu") -> torch.Tensor:
+    """Keep mask of a flat tensor, identical to the device function ``dropout_keep8`` (csrc/kernels/ptx.cuh): the
+    eight elements of chunk ``i // 8`` take the eight 16-bit fields of two 64-bit words mixed from (seed, chunk) and
+    are kept when their field is ``>= round(p * 65536)``."""
+    import numpy as np
+
+    def lsr(x, k):
+        return (x >> k) & ((1 << (64 - k)) - 1)
+
+    def c(v):
+        v &= _M64
+        return v - (1 << 64) if v >= (1 << 63) else v
+
     n = int(math.prod(shape))
-    idx = torch.arange(n, device=device, dtype=torch.int64)
-    return (hash_uniform(seed, idx) >= p).reshape(shape)
+    thr = int(np.float32(p) * np.float32(65536.0) + np.float32(0.5))
+    chunk = torch.arange((n + 7) // 8, device=device, dtype=torch.int64)
+    z = chunk * c(0x9E3779B97F4A7C15) + c(seed)
+    z = (z ^ lsr(z, 30)) * c(0xBF58476D1CE4E5B9)
+    z = (z ^ lsr(z, 27)) * c(0x94D049BB133111EB)
+    z = z ^ lsr(z, 31)
+    w = (z ^ lsr(z, 29)) * c(0xD6E8FEB86659FD93)
+    w = w ^ lsr(w, 32)
+    fields = [lsr(z, 16 * k) & 0xFFFF for k in range(4)] + [lsr(w, 16 * k) & 0xFFFF for k in range(4)]
+    keep = torch.stack(fields, dim=1) >= thr          # [chunks, 8]
+    return keep.reshape(-1)[:n].reshape(shape)
 
 
 # ---------------------------------------------------------------------- element-wise
