@@ -20,6 +20,7 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     rank, world = dist.get_rank(), dist.get_world_size()
+    os.environ.setdefault("TNNB_DP_MIN_BUCKET", "4096")  # several buckets even for the tiny models: overlapped reduction
     zoo.register_model("tiny_gpt", lambda: zoo.gpt2(128, 2, 2, "t", seq_len=128, vocab=203, drop=0.0))
     from tnn_b200.parallel.runtime import ParallelTrainer
     cfg = TrainingConfig.from_dict({"model_name": "tiny_gpt", "batch_size": 2, "device_type": "CUDA", "seed": 5,
@@ -61,7 +62,8 @@ def main():
     gathered = [torch.zeros_like(master) for _ in range(world)]
     dist.all_gather(gathered, master)
     if rank == 0:
-        out = {"losses": losses, "param_sum": float(t.graph.params_flat.float().sum()), "n": t.graph.num_parameters()}
+        out = {"losses": losses, "param_sum": float(t.graph.params_flat.float().sum()), "n": t.graph.num_parameters(),
+               "dp_sites": len(getattr(t.optimizer, "sites", [])), "dp_overlap": bool(getattr(t.optimizer, "overlap", False))}
         if mode == "dp":
             out["max_rank_diff"] = max(float((g - gathered[0]).abs().max()) for g in gathered)
         torch.save({"params": t.graph.params_flat.float().cpu(), "losses": losses}, sys.argv[3])

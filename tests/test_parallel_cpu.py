@@ -75,3 +75,43 @@ def test_tp2_equals_single_process(tmp_path):
             assert a.shape == b.shape and torch.allclose(a.float(), b.float(), atol=3e-3), l.name
             n_checked += 1
     assert n_checked > 20
+
+
+def test_grad_hook_order_and_bucket_plan():
+    """Backward reports final gradient ranges from the end of the flat buffer; the bucket plan follows that order."""
+    import torch
+    from tnn_b200.models import zoo
+    from tnn_b200.parallel.dp import plan_buckets
+
+    g = zoo.gpt2(128, 2, 3, "t", seq_len=64, vocab=203, drop=0.0).compile(device="cpu", seed=1)
+    assert g.grad_hook_usable()
+    pts = g.grad_ready_points()
+    assert pts == sorted(pts, reverse=True) and pts[-1] == 0
+    fired = []
+    written = []
+
+    def hook(floor):
+        fired.append(floor)
+        # at the time of the call the gradients at offsets >= floor must already hold their final values
+        written.append(g.grads_flat[floor:].clone())
+
+    g.grad_hook = hook
+    g.train()
+    ids = torch.randint(0, 203, (2, 64))
+    out = g(ids)
+    g.backward({"output": torch.ones_like(out)})
+    assert fired == pts
+    for floor, snap in zip(fired, written):
+        assert torch.equal(snap, g.grads_flat[floor:])
+    total = g.total_elems
+    plan = plan_buckets(pts, 0, total, n_buckets=3, min_bucket=8)
+    assert plan[0][1] == total and plan[-1][0] == 0
+    assert all(a[0] == b[1] for a, b in zip(plan, plan[1:]))          # contiguous, descending
+    assert all(lo % 8 == 0 for lo, _ in plan) and len(plan) >= 2
+    assert all(lo in [p // 8 * 8 for p in pts] for lo, _ in plan)        # every boundary is a reported point
+    assert plan_buckets(pts, 0, total, n_buckets=1, min_bucket=8) == [(0, total)]
+    # a ResNet: many segments, floors still descend
+    r = zoo.create("cifar10_resnet9").compile(device="cpu", seed=1)
+    assert r.grad_hook_usable()
+    rp = r.grad_ready_points()
+    assert rp == sorted(rp, reverse=True)

@@ -44,6 +44,8 @@ def test_dp2_matches_single_process(kind, tmp_path):
     out = str(tmp_path / "dp.pt")
     res = launch(2, "dp", kind, out)
     assert res["max_rank_diff"] == 0.0
+    if kind == "fused":  # the fused path ran bucketed, overlapped with backward
+        assert res["dp_overlap"] and res["dp_sites"] > 1, res
     gens = [torch.Generator().manual_seed(100 + r) for r in range(2)]
     sets = [torch.cat([torch.randint(0, 203, (2, 129), generator=g) for g in gens]) for _ in range(4)]
     ref_losses, ref_params = single_process_reference(sets, tmp_path)

@@ -107,6 +107,9 @@ class Graph:
         self.layer_slices: Dict[int, List[Tuple[int, int, Tuple[int, ...], bool]]] = {}
         self.training = True
         self.profiler = None  # utils.profiling.LayerProfiler, set by the trainer when profiler_type != NONE
+        # Called during backward() as grad_hook(floor): every gradient at flat offset >= floor is final for this pass.
+        # The data-parallel optimizer uses it to start reducing finished buckets while backward is still running.
+        self.grad_hook = None
         self.step = 0
         self.input_requires_grad = False
         self._ctx: Dict[int, dict] = {}
@@ -325,6 +328,48 @@ class Graph:
             i = seg.end
         self.segments = segs
 
+    def _layer_floor(self, layer: Layer) -> Optional[int]:
+        offs = [sl[0] for sl in self.layer_slices.get(id(layer), []) if sl]
+        return min(offs) if offs else None
+
+    def segment_floors(self) -> List[Optional[int]]:
+        """Per executor segment, the lowest flat-buffer offset of its layers' parameters (None: no parameters).
+        Parameters are laid out in first-use order over the sorted edges, so once the backward of segment ``k`` has
+        run, every gradient at an offset >= ``segment_floors()[k]`` is final - provided no layer is shared between
+        segments (``grad_hook_usable``)."""
+        out = []
+        for seg in self.segments:
+            fl = [self._layer_floor(self.edges[i].layer) for i in range(seg.start, seg.end)]
+            fl = [f for f in fl if f is not None]
+            out.append(min(fl) if fl else None)
+        return out
+
+    def grad_hook_usable(self) -> bool:
+        """True when offsets grow with the segment index and every layer belongs to one edge only."""
+        seen = set()
+        for e in self.edges:
+            if id(e.layer) in seen:
+                return False
+            seen.add(id(e.layer))
+        last = -1
+        for f in self.segment_floors():
+            if f is None:
+                continue
+            if f < last:
+                return False
+            last = f
+        return True
+
+    def grad_ready_points(self) -> List[int]:
+        """The floors ``grad_hook`` will be called with during one backward pass, in firing order (descending)."""
+        pts: List[int] = []
+        floors = self.segment_floors()
+        for k in reversed(range(len(self.segments))):
+            pts += self.segments[k].inner_floors(self)
+            if floors[k] is not None:
+                pts.append(floors[k])
+        return pts
+
     # -------------------------------------------------------------------- execution
     def _pid_ctx(self, pid: int) -> dict:
         return self._ctx.setdefault(pid, {"values": {}, "seg": {}})
@@ -368,12 +413,16 @@ class Graph:
             gvals[id(by_uid[uid])] = g.to(self.io_dtype) if g.dtype != self.io_dtype else g
         need_in = {id(n) for n in self.input_nodes} if not self.input_requires_grad else set()
         prof = self.profiler
+        hook = self.grad_hook
+        floors = self.segment_floors() if hook is not None else None
         for k in reversed(range(len(self.segments))):
             if prof is None:
                 self.segments[k].backward(gvals, st["seg"][k], need_in)
             else:
                 with prof.span(self.segment_name(k), "backward"):
                     self.segments[k].backward(gvals, st["seg"][k], need_in)
+            if hook is not None and floors[k] is not None:
+                hook(floors[k])
         return {n._uid: gvals[id(n)] for n in self.input_nodes if id(n) in gvals and gvals[id(n)] is not None}
 
     def segment_name(self, k: int) -> str:
@@ -564,6 +613,10 @@ class _Segment:
     def backward(self, gvals: dict, ctx: dict, no_grad_nodes: set):
         raise NotImplementedError
 
+    def inner_floors(self, g: "Graph") -> List[int]:
+        """Floors a segment reports through ``g.grad_hook`` from inside its own backward (firing order)."""
+        return []
+
 
 def _accum(gvals: dict, node: Node, g: Optional[torch.Tensor]):
     """Fan-out gradient accumulation (include/nn/node.hpp:29-63)."""
@@ -659,6 +712,7 @@ class _GPTChain(_Segment):
     """
 
     def __init__(self, g: Graph, start: int, n_blocks: int, final_ln: bool):
+        self.g = g
         self.start = start
         self.end = start + 10 * n_blocks + (1 if final_ln else 0)
         self.blocks = [[g.edges[start + 10 * b + k] for k in range(10)] for b in range(n_blocks)]
@@ -713,6 +767,13 @@ class _GPTChain(_Segment):
                 and cons.get(id(last_out), []) == [j] and id(last_out) not in outs and g.edges[j].layer.affine):
             final_ln = True
         return _GPTChain(g, i, nb, final_ln)
+
+    @staticmethod
+    def _block_floor(g: Graph, es) -> int:
+        return min(f for f in (g._layer_floor(e.layer) for e in es) if f is not None)
+
+    def inner_floors(self, g: Graph) -> List[int]:
+        return [self._block_floor(g, es) for es in reversed(self.blocks)]
 
     # The residual stream is carried as (x, pending): the true value is x + dropout(pending).
     def forward(self, vals, ctx):
@@ -793,5 +854,7 @@ class _GPTChain(_Segment):
             # LN1 (+ the previous block's trailing residual add + dropout)
             dres, dpend = raw.layernorm_bwd(dh1, s["x"], s["mean1"], s["rstd1"], ln1.params[0], dx1, s["had_pending"],
                                             s["p_in"], s["seed_in"], ln1.grads[0], ln1.grads[1])
+            if self.g.grad_hook is not None:  # this block and everything after it in the flat buffer is final
+                self.g.grad_hook(self._block_floor(self.g, es))
         if id(self.in_node) not in no_grad_nodes:
             _accum(gvals, self.in_node, dres.reshape(B, S, E))

@@ -15,6 +15,7 @@ no data parallelism to compare with (include/distributed/coordinator.hpp:618-620
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
@@ -41,10 +42,34 @@ def _declare(lib):
     lib.tnnb_dp_step.restype = i
 
 
-class FusedDPOptimizer:
-    """Drives ``tnnb_dp_step`` for every region of a graph whose flat buffers live in ``heap``."""
+def plan_buckets(points: Sequence[int], lo: int, hi: int, n_buckets: int, min_bucket: int) -> List[tuple]:
+    """Cut ``[lo, hi)`` into buckets ``(lo_i, hi_i)`` in the order backward finishes them (highest offsets first).
+    ``points`` are the offsets ``Graph.grad_hook`` reports, in firing order; a bucket ends at such a point and holds
+    at least ``max(min_bucket, (hi - lo) / n_buckets)`` elements (the last one takes what is left)."""
+    target = max(min_bucket, (hi - lo) // max(1, n_buckets))
+    out, top = [], hi
+    for pt in points:
+        pt = pt // 8 * 8
+        if lo < pt < top and top - pt >= target:
+            out.append((pt, top))
+            top = pt
+    out.append((lo, top))
+    return out
 
-    def __init__(self, opt: Optimizer, graph, heap: SymmetricHeap, regions: Sequence[Region], grad_scale: float):
+
+class FusedDPOptimizer:
+    """Drives ``tnnb_dp_step`` for every region of a graph whose flat buffers live in ``heap``.
+
+    ``overlap=True`` (pure data parallelism, one region over the whole buffer, one backward pass per step) cuts the
+    region into buckets that follow the order in which backward finishes the gradients - the flat buffer is laid out
+    in first-use order, so backward completes it from the end - and starts a bucket's reduce + update + broadcast
+    kernel on a second stream as soon as ``Graph.grad_hook`` reports its gradients final, while backward keeps
+    running on the main stream. Only the last bucket (the embeddings, finished at the very end) is exposed."""
+
+    MIN_BUCKET = 4 << 20  # elements
+
+    def __init__(self, opt: Optimizer, graph, heap: SymmetricHeap, regions: Sequence[Region], grad_scale: float,
+                 overlap: bool = False, n_buckets: int = 6):
         self.opt, self.graph, self.heap, self.regions = opt, graph, heap, list(regions)
         self.lib = _lib.load()
         _declare(self.lib)
@@ -55,17 +80,27 @@ class FusedDPOptimizer:
         self.is_adam = isinstance(opt, Adam)
         # number of updates so far, kept on the device so that a captured CUDA graph advances it on replay
         self.tick = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.overlap = bool(overlap and len(self.regions) == 1 and len(self.regions[0].ranks) > 1
+                            and self.regions[0].lo == 0 and self.regions[0].hi == graph.total_elems and graph.grad_hook_usable())
+        spans = []  # (lo, hi, region) in launch order
+        if self.overlap:
+            reg = self.regions[0]
+            min_bucket = int(os.environ.get("TNNB_DP_MIN_BUCKET", str(self.MIN_BUCKET)))  # tests lower it for tiny models
+            spans = [(a, b, reg) for a, b in plan_buckets(graph.grad_ready_points(), reg.lo, reg.hi, n_buckets, min_bucket)]
+            self.overlap = len(spans) > 1
+        else:
+            spans = [(reg.lo, reg.hi, reg) for reg in self.regions]
         self.sites = []
-        for reg in self.regions:
+        for (blo, bhi, reg) in spans:
             n = len(reg.ranks)
             idx = reg.ranks.index(self.me)
-            span = reg.hi - reg.lo
+            span = bhi - blo
             per = (span // n) // 8 * 8
-            lo = reg.lo + idx * per
-            hi = reg.hi if idx == n - 1 else lo + per
+            lo = blo + idx * per
+            hi = bhi if idx == n - 1 else lo + per
             flags = heap.alloc((16,), torch.int32).zero_()
             site = {
-                "n": n, "idx": idx, "lo": lo, "hi": hi, "epoch": 0,
+                "n": n, "idx": idx, "lo": lo, "hi": hi, "epoch": 0, "bucket_lo": blo, "bucket_hi": bhi,
                 "flags": ptr_array(heap.peer_ptrs(flags, reg.ranks)),
                 "grads": ptr_array(heap.peer_ptrs(graph.grads_flat, reg.ranks)),
                 "lp": ptr_array(heap.peer_ptrs(graph.params_flat, reg.ranks)) if graph.master_flat is not graph.params_flat else None,
@@ -84,6 +119,15 @@ class FusedDPOptimizer:
                     used[ent[0]:ent[0] + ent[1]] = True
         idx = (used & ~graph.trainable_mask).nonzero().squeeze(1)
         self._frozen_idx = idx if idx.numel() else None
+        # per-step state of the overlapped launch sequence
+        self._prepared = False   # opt.prepare_step() done for the step in progress
+        self._begun = False      # tick advanced / arguments computed for the step in progress
+        self._next = 0           # next site to launch
+        self._args = None
+        self._frozen = None
+        self.comm = torch.cuda.Stream(device=dev, priority=-1) if self.overlap else None
+        if self.overlap:
+            graph.grad_hook = self._on_grads_ready
         # a parameter written by a peer lands in params_flat; when params are fp32 the master *is* params_flat
         torch.cuda.synchronize()
         if dist.is_initialized():
@@ -101,6 +145,7 @@ class FusedDPOptimizer:
 
     def prepare_step(self):
         self.opt.prepare_step()
+        self._prepared = True
 
     @property
     def hyper(self):
@@ -114,33 +159,81 @@ class FusedDPOptimizer:
     def step_count(self, v):
         self.opt.step_count = v
 
-    def update(self, prepared: bool = False):
-        o = self.opt
-        if not prepared:
-            o.prepare_step()
-        g = self.graph
-        st = _lib.stream()
-        status = _lib.ptr(_lib.status_word(g.master_flat.device))
+    # ------------------------------------------------------------------ one step = begin, launches, finish
+    def _begin(self):
+        """First launch of a step: advance the step count and the device tick, fix the kernel arguments."""
+        if self._begun:
+            return
+        o, g = self.opt, self.graph
+        if not self._prepared:
+            self.prepare_step()
         if self.is_adam:
             bc1, bc2 = 1 - o.beta1 ** o.step_count, 1 - o.beta2 ** o.step_count
-            args = (0, o.lr, o.beta1, o.beta2, o.eps, o.weight_decay, bc1, bc2, o.grad_scale, 0.0)
+            self._args = (0, o.lr, o.beta1, o.beta2, o.eps, o.weight_decay, bc1, bc2, o.grad_scale, 0.0)
         else:
-            args = (1, o.lr, 0.0, 0.0, 0.0, 0.0, 1.0, 1.0, o.grad_scale, o.momentum)
-        frozen = None
+            self._args = (1, o.lr, 0.0, 0.0, 0.0, 0.0, 1.0, 1.0, o.grad_scale, o.momentum)
+        self._frozen = None
         if self.is_adam and o.weight_decay != 0.0 and self._frozen_idx is not None:
-            frozen = g.master_flat.index_select(0, self._frozen_idx)
+            self._frozen = g.master_flat.index_select(0, self._frozen_idx)
         self.tick.add_(1)
-        for s in self.sites:
-            rc = self.lib.tnnb_dp_step(
-                s["n"], s["idx"], s["flags"], s["grads"], s["lp"], s["f32"], _lib.ptr(g.master_flat), _lib.ptr(s["m"]),
-                _lib.ptr(s["v"]), s["lo"], s["hi"], args[0], args[1], args[2], args[3], args[4], args[5], args[6], args[7],
-                args[8], args[9], _lib.ptr(o.hyper), 0, _lib.ptr(self.tick), _lib.ptr(s["go"]), _lib.ptr(s["done"]), status, st)
-            _lib.check_rc(rc, "tnnb_dp_step")
-            LAUNCHES["count"] += 1
-        if frozen is not None:  # the kernel returns only after every peer's writes into this rank have landed
-            g.master_flat.index_copy_(0, self._frozen_idx, frozen)
+        self._next = 0
+        self._begun = True
+
+    def _launch(self, s):
+        o, g, args = self.opt, self.graph, self._args
+        status = _lib.ptr(_lib.status_word(g.master_flat.device))
+        rc = self.lib.tnnb_dp_step(
+            s["n"], s["idx"], s["flags"], s["grads"], s["lp"], s["f32"], _lib.ptr(g.master_flat), _lib.ptr(s["m"]),
+            _lib.ptr(s["v"]), s["lo"], s["hi"], args[0], args[1], args[2], args[3], args[4], args[5], args[6], args[7],
+            args[8], args[9], _lib.ptr(o.hyper), 0, _lib.ptr(self.tick), _lib.ptr(s["go"]), _lib.ptr(s["done"]), status,
+            _lib.stream())
+        _lib.check_rc(rc, "tnnb_dp_step")
+        LAUNCHES["count"] += 1
+
+    def _launch_on_comm(self, upto: int):
+        """Launch sites ``[_next, upto)`` on the communication stream, ordered after everything queued so far."""
+        if upto <= self._next:
+            return
+        main = torch.cuda.current_stream()
+        ev = torch.cuda.Event()
+        ev.record(main)
+        self.comm.wait_event(ev)
+        with torch.cuda.stream(self.comm):
+            while self._next < upto:
+                self._launch(self.sites[self._next])
+                self._next += 1
+
+    def _on_grads_ready(self, floor: int):
+        """``Graph.grad_hook``: every gradient at a flat offset >= ``floor`` is final."""
+        if not self.overlap or not self.graph.training:
+            return
+        upto = self._next if self._begun else 0
+        while upto < len(self.sites) - 1 and self.sites[upto]["bucket_lo"] >= floor:  # the last bucket goes with update()
+            upto += 1
+        if upto > (self._next if self._begun else 0):
+            self._begin()
+            self._launch_on_comm(upto)
+
+    def update(self, prepared: bool = False):
+        if prepared:
+            self._prepared = True
+        self._begin()
+        g = self.graph
+        if self.overlap:
+            self._launch_on_comm(len(self.sites))
+            ev = torch.cuda.Event()
+            ev.record(self.comm)
+            torch.cuda.current_stream().wait_event(ev)
+        else:
+            while self._next < len(self.sites):
+                self._launch(self.sites[self._next])
+                self._next += 1
+        if self._frozen is not None:  # the kernel returns only after every peer's writes into this rank have landed
+            g.master_flat.index_copy_(0, self._frozen_idx, self._frozen)
             if g.params_flat is not g.master_flat:
-                g.params_flat.index_copy_(0, self._frozen_idx, frozen.to(g.params_flat.dtype))
+                g.params_flat.index_copy_(0, self._frozen_idx, self._frozen.to(g.params_flat.dtype))
+            self._frozen = None
+        self._prepared = self._begun = False
 
     def state_dict(self):
         d = self.opt.state_dict()

@@ -132,7 +132,10 @@ class ParallelTrainer(Trainer):
         else:
             regions = [Region(0, total, topo.dp_ranks, topo.dp_group)]
         if self.fused:
-            optimizer = FusedDPOptimizer(opt, graph, self.heap, regions, scale)
+            # gradient reduction overlapped with backward: pure data parallelism with one backward pass per step
+            overlap = (cfg.parallel.overlap_grad_reduce and topo.tp == 1 and topo.pp == 1 and topo.dp > 1
+                       and int(cfg.gradient_accumulation_steps) == 1 and os.environ.get("TNNB_DP_OVERLAP", "1") != "0")
+            optimizer = FusedDPOptimizer(opt, graph, self.heap, regions, scale, overlap=overlap)
             optimizer.attach = lambda g: optimizer  # already bound
         else:
             optimizer = NcclDPOptimizer(opt, graph, regions, scale)

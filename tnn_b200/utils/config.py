@@ -21,6 +21,7 @@ class ParallelConfig:
     partition_ratios: List[float] = field(default_factory=list)
     fused_collectives: bool = True   # hand-written NVLink kernels instead of NCCL calls
     zero: bool = True                # shard optimizer state across the data-parallel group
+    overlap_grad_reduce: bool = True  # start a bucket's fused reduce + update while backward is still running (pure DP)
     layout: str = ""                 # e.g. "dp8", "tp2dp4", "pp2tp2"; empty = data parallel over all ranks
 
 
