@@ -129,6 +129,24 @@ def test_attention_fwd_bwd(B, S, H, causal):
         close(dqkv[:, i * E:(i + 1) * E], rd[:, i * E:(i + 1) * E], tol=3e-2, what="d" + name)
 
 
+@pytest.mark.parametrize("B,S,H,D,causal", [(2, 128, 2, 96, True), (1, 200, 3, 32, False), (1, 256, 1, 128, True)])
+def test_attention_other_head_sizes(B, S, H, D, causal):
+    """Head sizes other than 64 run head by head on the GEMM kernel (the reference's attention benchmark uses 96)."""
+    torch.manual_seed(14)
+    qkv = rnd(B * S, 3 * H * D, scale=0.5)
+    scale = D ** -0.5
+    out, lse = raw.attn_fwd(qkv.cuda(), B, S, H, D, causal, scale)
+    _lib.check_status()
+    rout, rlse = raw.attn_fwd(qkv, B, S, H, D, causal, scale)
+    close(out, rout, what="out")
+    close(lse, rlse, tol=1e-2, what="lse")
+    dout = rnd(B * S, H * D)
+    dqkv = raw.attn_bwd(qkv.cuda(), out, dout.cuda(), lse, B, S, H, D, causal, scale)
+    _lib.check_status()
+    rd = raw.attn_bwd(qkv, rout, dout, rlse, B, S, H, D, causal, scale)
+    close(dqkv, rd, tol=3e-2, what="dqkv")
+
+
 def test_attention_scale_one_like_reference_block():
     torch.manual_seed(5)
     B, S, H, D = 1, 256, 2, 64

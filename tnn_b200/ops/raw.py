@@ -358,10 +358,69 @@ def softmax_ce(logits: torch.Tensor, labels: torch.Tensor, vocab: int, grad_scal
 
 
 # ------------------------------------------------------------------------- attention
+# Head sizes other than 64 on a GPU: the fused flash kernels are specialised for D = 64 (every zoo model); other sizes
+# (the reference's attention benchmark uses E 768 / 8 heads = 96, benchmarks/attention_benchmark.cpp:11-40) run head by
+# head on the tcgen05 GEMM - scores, probabilities and the five backward products - with the softmax as element-wise
+# tensor ops. Memory is one S x S tile at a time; D must be a multiple of 8 (16-byte rows for the TMA descriptors).
+def _head_views(qkv, b, h, S, D, E):
+    rows = qkv[b * S:(b + 1) * S]
+    return rows[:, h * D:(h + 1) * D], rows[:, E + h * D:E + (h + 1) * D], rows[:, 2 * E + h * D:2 * E + (h + 1) * D]
+
+
+def _scores(q, k, S, causal, scale):
+    from .gemm import gemm
+    s = gemm(q, k, out_dtype=torch.float32).mul_(scale)
+    if causal:
+        s.masked_fill_(torch.triu(torch.ones(S, S, dtype=torch.bool, device=s.device), 1), float("-inf"))
+    return s
+
+
+def _attn_fwd_generic(qkv, B, S, H, D, causal, scale):
+    from .gemm import gemm
+    if D % 8:
+        raise ValueError(f"attention on a GPU needs a head size that is a multiple of 8 (got {D})")
+    E = H * D
+    out = torch.empty(B * S, E, dtype=qkv.dtype, device=qkv.device)
+    lse = torch.empty(B, H, S, dtype=torch.float32, device=qkv.device)
+    for b in range(B):
+        for h in range(H):
+            q, k, v = _head_views(qkv, b, h, S, D, E)
+            s = _scores(q, k, S, causal, scale)
+            l = torch.logsumexp(s, -1)
+            p = torch.exp(s - l[:, None]).to(qkv.dtype)
+            gemm(p, v, b_t=True, out=out[b * S:(b + 1) * S, h * D:(h + 1) * D])
+            lse[b, h] = l * 1.4426950408889634
+    return out, lse
+
+
+def _attn_bwd_generic(qkv, out, dout, lse, B, S, H, D, causal, scale):
+    from .gemm import gemm
+    E = H * D
+    dqkv = torch.empty_like(qkv)
+    for b in range(B):
+        for h in range(H):
+            q, k, v = _head_views(qkv, b, h, S, D, E)
+            dq, dk, dv = _head_views(dqkv, b, h, S, D, E)
+            do = dout[b * S:(b + 1) * S, h * D:(h + 1) * D]
+            o = out[b * S:(b + 1) * S, h * D:(h + 1) * D]
+            s = _scores(q, k, S, causal, scale)
+            p = torch.exp2(s * 1.4426950408889634 - lse[b, h][:, None])
+            pb = p.to(qkv.dtype)
+            gemm(pb, do, a_t=True, b_t=True, out=dv)                      # dV = P^T dO
+            dp = gemm(do, v, out_dtype=torch.float32)                    # dP = dO V^T
+            delta = (do.float() * o.float()).sum(-1, keepdim=True)
+            ds = (p * (dp - delta) * scale).to(qkv.dtype)
+            gemm(ds, k, b_t=True, out=dq)                                # dQ = dS K
+            gemm(ds, q, a_t=True, b_t=True, out=dk)                      # dK = dS^T Q
+    return dqkv
+
+
 def attn_fwd(qkv: torch.Tensor, B: int, S: int, H: int, D: int, causal: bool, scale: float
              ) -> Tuple[torch.Tensor, torch.Tensor]:
     """qkv: [B*S, 3*H*D] (q | k | v, heads contiguous). Returns (out [B*S, H*D], lse [B,H,S] in log2 units)."""
     E = H * D
+    if qkv.is_cuda and qkv.dtype == torch.bfloat16 and D != 64:
+        return _attn_fwd_generic(qkv.contiguous(), B, S, H, D, causal, scale)
     if qkv.is_cuda and qkv.dtype == torch.bfloat16:
         qkv = qkv.contiguous()
         out = torch.empty(B * S, E, dtype=qkv.dtype, device=qkv.device)
@@ -385,6 +444,8 @@ def attn_bwd(qkv: torch.Tensor, out: torch.Tensor, dout: torch.Tensor, lse: torc
              D: int, causal: bool, scale: float) -> torch.Tensor:
     """Gradient with respect to the packed qkv, same layout as the input."""
     E = H * D
+    if qkv.is_cuda and qkv.dtype == torch.bfloat16 and D != 64:
+        return _attn_bwd_generic(qkv.contiguous(), out, dout.contiguous(), lse, B, S, H, D, causal, scale)
     if qkv.is_cuda and qkv.dtype == torch.bfloat16:
         dout = dout.contiguous()
         dqkv = torch.empty_like(qkv)
