@@ -42,6 +42,7 @@ def main():
             y = torch.randint(0, 10, (t.local_batch,), generator=gen)
             losses.append(float(t.train_step(x, y).item()))
         _lib.check_status()
+        t._refresh_master()  # with the sharded optimizer a rank holds fp32 master values for its own slices only
         if rank == 0:
             torch.save({"params": t.graph.master_flat.float().cpu(), "trainable": t.graph.trainable_mask.cpu(), "losses": losses},
                        sys.argv[3])

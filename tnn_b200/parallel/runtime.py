@@ -155,7 +155,7 @@ class ParallelTrainer(Trainer):
         """With the sharded optimizer every rank holds fp32 master values only for its own slice: refresh the
         other slices from the (broadcast) compute copy."""
         g = self.graph
-        if g.master_flat is not g.params_flat:
+        if g.master_flat is not g.params_flat and isinstance(self.optimizer, FusedDPOptimizer):
             mine = torch.zeros_like(g.trainable_mask)
             for s in getattr(self.optimizer, "sites", []):
                 mine[s["lo"]:s["hi"]] = True
