@@ -69,7 +69,7 @@ class FusedDPOptimizer:
     MIN_BUCKET = 4 << 20  # elements
 
     def __init__(self, opt: Optimizer, graph, heap: SymmetricHeap, regions: Sequence[Region], grad_scale: float,
-                 overlap: bool = False, n_buckets: int = 6):
+                 overlap: bool = False, n_buckets: int = 4):
         self.opt, self.graph, self.heap, self.regions = opt, graph, heap, list(regions)
         self.lib = _lib.load()
         _declare(self.lib)
