@@ -95,3 +95,23 @@ def test_layer_profiler_records_compute_events_and_log_lines(tmp_path):
     from tnn_b200.utils.profiling import merge_across_ranks
     assert len(merge_across_ranks(lp)) == len(lp.profiler)      # single process: nothing to merge
     t.close()
+
+
+def test_env_file_rules(tmp_path, monkeypatch):
+    from tnn_b200.utils.env import EnvLoader, augmentation_enabled, default_device_type, from_str
+
+    p = tmp_path / ".env"
+    p.write_text("# comment\n\nDEVICE_TYPE = CPU   # trailing comment\nNAME=\"quoted # kept\"\nN=0x10\nRATE='0.5'\n"
+                 "BAD KEY=1\nNOEQUALS\nAUGMENTATION=yes\n")
+    for k in ("DEVICE_TYPE", "NAME", "N", "RATE", "AUGMENTATION", "BAD KEY"):
+        monkeypatch.delenv(k, raising=False)
+    env = EnvLoader(str(p))
+    assert env.loaded and env.vars == {"DEVICE_TYPE": "CPU", "NAME": "quoted # kept", "N": "0x10", "RATE": "0.5", "AUGMENTATION": "yes"}
+    import os
+    assert os.environ["NAME"] == "quoted # kept"
+    assert env.get("N", 0) == 16 and env.get("RATE", 0.0) == 0.5 and env.get("MISSING", 7) == 7
+    assert default_device_type() == "CPU" and augmentation_enabled()
+    assert from_str("TRUE", bool) and not from_str("off", bool)
+    assert not EnvLoader(str(tmp_path / "nope.env")).loaded
+    for k in env.vars:
+        monkeypatch.delenv(k, raising=False)

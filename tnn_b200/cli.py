@@ -124,6 +124,8 @@ def cmd_info(a) -> int:
 
 
 def main(argv=None) -> int:
+    from .utils.env import EnvLoader, default_device_type
+    EnvLoader("./.env")  # optional KEY=value file in the working directory, exported to the environment
     ap = argparse.ArgumentParser(prog="tnn_b200")
     sub = ap.add_subparsers(dest="cmd", required=True)
     p = sub.add_parser("train", help="train from a JSON config (epoch or step mode)")
@@ -142,7 +144,7 @@ def main(argv=None) -> int:
     p.add_argument("--num-tokens", type=int, default=50)
     p.add_argument("--seq-len", type=int, default=0)
     p.add_argument("--eos", type=int, default=50256)
-    p.add_argument("--device", default="CUDA")
+    p.add_argument("--device", default=default_device_type(), help="CPU or CUDA (default: $DEVICE_TYPE, else CUDA when present)")
     p.add_argument("--seed", type=int, default=0)
     sub.add_parser("info", help="build and device information")
     a = ap.parse_args(argv)

@@ -103,6 +103,13 @@ def create_image_folder_loaders(name, path, batch, seed, augmentation):
                     val.append((os.path.join(path, "val", "images", parts[0]), cls[parts[1]]))
         return (ImageFolderLoader(train, batch, 64, True, seed, False, augmentation),
                 ImageFolderLoader(val, batch, 64, False, seed, False))
+    if augmentation is None:
+        # the reference switches its ImageNet-100 augmentation (flip, brightness, contrast, saturation) on with the
+        # AUGMENTATION / tunx_AUGMENTATION environment variable (src/data_loading/data_loading.cpp:93-124)
+        from ..utils.env import augmentation_enabled
+        if augmentation_enabled():
+            from .augmentation import AugmentationBuilder
+            augmentation = AugmentationBuilder(seed).horizontal_flip(0.5).brightness(0.5, 0.2).contrast(0.5, 0.2).saturation(0.5, 0.2).build()
     labels = json.load(open(os.path.join(path, "Labels.json")))
     cls = {w: i for i, w in enumerate(sorted(labels))}
     train, val = [], []
