@@ -23,7 +23,7 @@ class FakeReader:
 
 
 def test_monitor_writes_rows_and_rates(tmp_path):
-    from tnn_b200.tools import monitor
+    from tnn_b200.utils import monitor
 
     t = [100.0]
     path = str(tmp_path / "logs" / "telemetry.csv")
@@ -42,7 +42,7 @@ def test_monitor_writes_rows_and_rates(tmp_path):
 
 def test_profile_timeline_from_layer_profiler(tmp_path):
     from tnn_b200.models import zoo
-    from tnn_b200.tools import profile_timeline
+    from tnn_b200.utils import profile_timeline
     from tnn_b200.utils.profiling import LayerProfiler
 
     g = zoo.create("mnist_cnn").compile(device="cpu", seed=0)

@@ -1,6 +1,6 @@
 """GPU / NVLink / NIC telemetry sampler that appends one CSV row per interval.
 
-    python -m tnn_b200.tools.monitor --csv logs/telemetry.csv --gpu 0 --interval 1.0 [--iface eth0] [--duration 60]
+    python -m tnn_b200.utils.monitor --csv logs/telemetry.csv --gpu 0 --interval 1.0 [--iface eth0] [--duration 60]
 
 The B200 counterpart of the reference's ``torch/monitor_net_gpu.py`` (NIC and RDMA byte counters from sysfs plus
 ``nvidia-smi`` utilisation, written to CSV while a distributed run is going on). On one NVSwitch box the traffic that

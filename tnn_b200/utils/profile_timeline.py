@@ -1,6 +1,6 @@
 """Turn a profiler log into a timeline: a Chrome / Perfetto trace (JSON) and a text summary per source.
 
-    python -m tnn_b200.tools.profile_timeline logs/profiler.log --trace logs/profiler_trace.json
+    python -m tnn_b200.utils.profile_timeline logs/profiler.log --trace logs/profiler_trace.json
 
 Reads the lines the profiler writes - ``Event: <name>, Source: <src>, Type: COMPUTE|COMMUNICATION|OTHER, Start: <ms> ms,
 End: <ms> ms, Duration: <ms> ms`` - which is also the format of the reference's coordinator log, parsed there by
