@@ -123,3 +123,25 @@ def test_wifi_regression_loader(tmp_path):
     x, y = c.next_batch()
     assert y.dtype == torch.int64 and y.tolist() == [2, 0]
     assert not WiFiLoader().load_data(str(tmp_path / "missing.csv"))
+
+
+def test_prepare_text_corpus_and_token_loader(tmp_path):
+    """Text files -> train.bin / val.bin / vocab.bin (byte-level tokenizer), read back by the token loader and the tokenizer."""
+    from tnn_b200.data.loaders import create_loaders
+    from tnn_b200.data.prepare_text import prepare
+    from tnn_b200.data.tokenizer import Tokenizer
+
+    src = tmp_path / "a.txt"
+    src.write_text("\n\n".join(f"document number {i} says hello world, " * 12 for i in range(40)))
+    out = str(tmp_path / "owt")
+    info = prepare([str(src)], out, tokenizer="bytes", val_fraction=0.1, paragraph_docs=True)
+    assert info["vocab"] == 257 and info["eot"] == 256 and info["tokens"]["val"] > 0
+    train = np.fromfile(os.path.join(out, "train.bin"), dtype=np.uint16)
+    assert len(train) == info["tokens"]["train"] and int((train == 256).sum()) == 36 and train[-1] == 256
+    tok = Tokenizer(os.path.join(out, "vocab.bin"))
+    assert len(tok) == 257 and tok.decode(train[:15].tolist()).startswith("document number")
+    tr, va = create_loaders("open_webtext", out, 2, seed=1, model_name="gpt2_small", steps_per_epoch=3, seq_len=32) \
+        if "seq_len" in create_loaders.__code__.co_varnames else (None, None)
+    if tr is not None:
+        d, l = next(iter(tr))
+        assert d.shape == (2, 32) and torch.equal(d[:, 1:], l[:, :-1])
