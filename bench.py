@@ -145,7 +145,8 @@ def run_ours(args):
             loader = SyntheticLoader((ms["seq_len"],), 50257, lb, 10 ** 9, tokens=True, seed=seed)
         else:
             classes = 1000 if ms["zoo"] == "imagenet_resnet50" else 100
-            loader = SyntheticLoader(zoo.INPUT_SHAPES[ms["zoo"]], classes, lb, 10 ** 9, seed=seed)
+            # images are produced in the io dtype (bf16), as the reference's loaders emit `io_dtype` floats
+            loader = SyntheticLoader(zoo.INPUT_SHAPES[ms["zoo"]], classes, lb, 10 ** 9, seed=seed, dtype=torch.bfloat16)
         batches = iter(loader)
         # ---- warm-up (also captures the CUDA graph) ----
         data, labels = next(batches)
@@ -157,7 +158,7 @@ def run_ours(args):
         barrier()
         first_loss = float(loss.item())
         # ---- device-timed region: K steps, batch resident, no host sync in between ----
-        sampler = ClockSampler(local) if (sample_clocks and rank == 0) else None
+        sampler = ClockSampler(local) if sample_clocks else None
         if sampler:
             sampler.start()
         time.sleep(0.3)
@@ -189,6 +190,8 @@ def run_ours(args):
             t = torch.tensor([dev_ms, e2e_ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dev_ms, e2e_ms = float(t[0]), float(t[1])
+            if sampler:
+                clocks = merge_clocks(clocks, world)
         from tnn_b200.ops import _lib
         _lib.check_status(dev)
         global_batch = trainer.global_batch if world > 1 else ms["per_gpu_batch"]
@@ -228,7 +231,7 @@ def run_ours(args):
             loss = trainer.train_step(data, labels)
         barrier()
         first_loss = float(loss.item()) if loss is not None else None
-        sampler = ClockSampler(local) if (sample_clocks and rank == 0) else None
+        sampler = ClockSampler(local) if sample_clocks else None
         if sampler:
             sampler.start()
         time.sleep(0.3)
@@ -260,6 +263,8 @@ def run_ours(args):
         t = torch.tensor([dev_ms, e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_ms, e2e_ms = float(t[0]), float(t[1])
+        if sampler:
+            clocks = merge_clocks(clocks, world)
         from tnn_b200.ops import _lib
         _lib.check_status(dev)
         # ---- checkpoint round trip: one TNNG file per stage (tensor-parallel shards gathered), read back ----
@@ -339,6 +344,20 @@ def run_ours(args):
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def merge_clocks(mine: dict, world: int) -> dict:
+    """Every rank sampled its own GPU: report the slowest median SM clock, the union of the throttle reasons and the
+    per-rank medians (a step that ends in a cross-rank barrier runs at the pace of the slowest GPU)."""
+    import torch.distributed as dist
+
+    allc = [None] * world
+    dist.all_gather_object(allc, mine)
+    med = [c.get("sm_mhz") for c in allc]
+    known = [m for m in med if m is not None]
+    reasons = sorted({r for c in allc for r in c.get("reasons", [])})
+    return {"sm_mhz": min(known) if known else None, "sm_max_mhz": max((c.get("sm_max_mhz") or 0) for c in allc) or None,
+            "reasons": reasons, "samples": sum(c.get("samples", 0) for c in allc), "sm_mhz_per_rank": med}
 
 
 def named_layout(world: int, zoo_name: str) -> str:

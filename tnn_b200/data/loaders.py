@@ -46,7 +46,7 @@ class SyntheticLoader(BaseLoader):
     a small ring of pinned buffers so that the host-to-device copy is a true pinned transfer."""
 
     def __init__(self, sample_shape, num_classes: int, batch_size: int, steps_per_epoch: int = 100, tokens: bool = False,
-                 uniform: bool = False, seed: int = 0, pin: bool = True, ring: int = 4):
+                 uniform: bool = False, seed: int = 0, pin: bool = True, ring: int = 4, dtype: torch.dtype = torch.float32):
         self.shape, self.num_classes, self.batch = tuple(sample_shape), int(num_classes), int(batch_size)
         self.steps, self.tokens, self.uniform = int(steps_per_epoch), tokens, uniform
         self.gen = torch.Generator().manual_seed(seed)
@@ -57,7 +57,7 @@ class SyntheticLoader(BaseLoader):
                 d = torch.empty((self.batch,) + self.shape, dtype=torch.int64)
                 l = torch.empty((self.batch,) + self.shape, dtype=torch.int64)
             else:
-                d = torch.empty((self.batch,) + self.shape, dtype=torch.float32)
+                d = torch.empty((self.batch,) + self.shape, dtype=dtype)  # images in the model's io dtype, like the reference loaders
                 l = torch.empty((self.batch,), dtype=torch.int64)
             self.ring.append((d.pin_memory() if pin else d, l.pin_memory() if pin else l))
         self.i = 0

@@ -142,6 +142,7 @@ class PipelineTrainer:
         self.prev = topo.pp_ranks[topo.pp_idx - 1] if not self.first else None
         self.next = topo.pp_ranks[topo.pp_idx + 1] if not self.last else None
         self.global_step = 0
+        self._p2p_warm = False
         self._shapes: Optional[Dict[str, Tuple[int, ...]]] = None
         self.local_batch = cfg.batch_size * (topo.tp if topo.tp > 1 else 1)
         self.global_batch = self.local_batch * topo.dp
@@ -211,6 +212,32 @@ class PipelineTrainer:
             reqs.append(dist.isend(tensors[uid].contiguous(), dst=dst, group=grp))
         return reqs
 
+    def _warm_p2p(self, shapes) -> None:
+        """Exchange boundary-sized dummy tensors with both neighbours, in both directions, before the first real step.
+        NCCL opens the channels of a point-to-point connection when a message first needs them (a 4-byte token uses
+        one, an 8 MiB activation several), and each of those set-ups stalls the receiving rank for a while; if that
+        happens inside a step, the stalled rank's tensor-parallel partner is already spinning in a fused kernel whose
+        cross-rank waits are bounded, and the wait can run out. Done here, nothing is in flight yet."""
+        self._p2p_warm = True
+        if self.device.type != "cuda":
+            return
+        io = self.stage.io_dtype
+        for _ in range(2):
+            if self.prev is not None:
+                self._recv(self.recv_uids, self.prev, shapes)
+            if self.next is not None:
+                acts = {u: torch.zeros(shapes[u], dtype=io, device=self.device) for u in self.send_uids}
+                for r in self._send(acts, self.send_uids, self.next):
+                    r.wait()
+            if self.next is not None:
+                self._recv(self.send_uids, self.next, shapes)
+            if self.prev is not None:
+                grads = {u: torch.zeros(shapes[u], dtype=io, device=self.device) for u in self.recv_uids}
+                for r in self._send(grads, self.recv_uids, self.prev):
+                    r.wait()
+        torch.cuda.synchronize()
+        dist.barrier()
+
     # ------------------------------------------------------------------------------- one step
     def train_step(self, data: torch.Tensor, labels: torch.Tensor) -> Optional[torch.Tensor]:
         """Runs the schedule for this rank's batch; the last stage returns the mean loss."""
@@ -222,6 +249,8 @@ class PipelineTrainer:
             raise ValueError(f"batch of {data.shape[0]} cannot be split into {M} micro-batches")
         mb = data.shape[0] // M
         shapes = self._boundary_shapes((mb,) + tuple(data.shape[1:]))
+        if not self._p2p_warm:
+            self._warm_p2p(shapes)
         if topo.tp > 1:
             self.stage.tp_context.seq_len = int(data.shape[1])
         d_chunks = data.to(self.device, non_blocking=True).chunk(M) if self.first else None

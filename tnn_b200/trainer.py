@@ -160,7 +160,8 @@ class Trainer:
         return self.layer_profiler is not None
 
     def enable_cuda_graph(self, data: torch.Tensor, labels: torch.Tensor, warmup: int = 2) -> None:
-        """Capture one full step (including the pinned-host upload) and replay it afterwards."""
+        """Capture one full step and replay it afterwards; each replay is preceded by the upload of the batch into the
+        graph's input buffers."""
         if self.device.type != "cuda" or self._profiling():  # events inside a captured graph carry no timing
             return
         if self.accum != 1:
@@ -168,10 +169,12 @@ class Trainer:
         for _ in range(warmup):
             self.train_step(data, labels)
         self.optimizer.enable_device_hyper()
-        self._h_data = torch.empty_like(data).pin_memory()
-        self._h_labels = torch.empty_like(labels).pin_memory()
-        self._h_data.copy_(data)
-        self._h_labels.copy_(labels)
+        # Graph inputs: device buffers in the caller's dtypes. Every step copies the batch straight from the caller's
+        # (pinned) tensors into them - one DMA, no staging copy on the host - and the captured graph starts from there.
+        self._d_data = torch.empty(data.shape, dtype=data.dtype, device=self.device)
+        self._d_labels = torch.empty(labels.shape, dtype=labels.dtype, device=self.device)
+        self._d_data.copy_(data)
+        self._d_labels.copy_(labels)
         self.graph.set_training(True)
         torch.cuda.synchronize()
         side = torch.cuda.Stream()
@@ -193,7 +196,7 @@ class Trainer:
         self.scheduler.step()
 
     def _captured_body(self):
-        d, l = self._to_device(self._h_data, self._h_labels)
+        d, l = self._to_device(self._d_data, self._d_labels)
         loss = self._fwd_bwd(d, l, 1.0)
         self.optimizer.update(prepared=True)
         self.graph.zero_grads()
@@ -201,8 +204,8 @@ class Trainer:
         return loss
 
     def _graphed_step(self, data, labels):
-        self._h_data.copy_(data)
-        self._h_labels.copy_(labels)
+        self._d_data.copy_(data, non_blocking=True)
+        self._d_labels.copy_(labels, non_blocking=True)
         self.optimizer.prepare_step()
         self._graphed.replay()
         self.scheduler.step()
