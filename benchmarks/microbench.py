@@ -64,6 +64,11 @@ def cmd_gemm(a):
         res["dgrad_ms"] = timeit(lambda: gemm(dy, w, b_t=True), a.iters)
         res["wgrad_ms"] = timeit(lambda: gemm(dy, x, a_t=True, b_t=True, out=dw, atomic=True), a.iters)
         res["torch_fwd_ms"] = timeit(lambda: x @ w.t(), a.iters)
+        # the two GELU forms of the MLP: forward with bias + GELU and a saved pre-activation, data gradient times GELU'
+        bias, z, out = bf(N), torch.empty(M, N, device="cuda", dtype=torch.bfloat16), torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        res["fwd_bias_gelu_ms"] = timeit(lambda: gemm(x, w, bias=bias, gelu=True, save_preact=z, out=out), a.iters)
+        zk, dxo = bf(M, K), torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
+        res["dgrad_dgelu_ms"] = timeit(lambda: gemm(dy, w, b_t=True, dgelu_of=zk, out=dxo), a.iters)
     fl = 2.0 * M * N * K
     for k in list(res):
         res[k.replace("_ms", "_tflops")] = round(fl / res[k] / 1e9, 1)

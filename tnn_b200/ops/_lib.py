@@ -29,9 +29,10 @@ def bounds_checked() -> bool:
 
 
 def lib_path() -> str:
+    """``TNNB_KERNEL_LIB`` names another build of the kernel library to load (A/B comparisons of a kernel change)."""
     from .. import _build
 
-    return _build.kernels_path(bounds_checked())
+    return os.environ.get("TNNB_KERNEL_LIB") or _build.kernels_path(bounds_checked())
 
 
 def load(build_if_missing: bool = True):
