@@ -5,6 +5,7 @@
     python benchmarks/host_bench.py tnng [--model cifar10_resnet9]  # checkpoint write + read throughput
     python benchmarks/host_bench.py grad_clear [--model gpt2_small] # per-tensor fill vs one memset over the gradient slab
     python benchmarks/host_bench.py memcpy [--mib 256]           # pinned / pageable host<->device copies (needs a GPU)
+    python benchmarks/host_bench.py tcp [--mib 128] [--seconds 10] [--peer host:port]  # ping-pong over the TCP communicator
 
 Reference counterparts: benchmarks/serialization_benchmark.cpp, benchmarks/grad_clear_benchmark.cpp:7-54 (per-tensor
 fill against a slab memset on gpt2_small), benchmarks/memcpy_benchmark.cpp, and the 128 MiB message of
@@ -134,6 +135,36 @@ def cmd_memcpy(a):
     return out
 
 
+def cmd_tcp(a):
+    """Ping-pong of one large message with an echoing peer (reference: benchmarks/tcp_communicator_benchmark.cpp:132-223,
+    128 MiB messages for 10 s, MB/s). Without ``--peer`` the echo process is started on this host (loopback)."""
+    import subprocess
+
+    from tnn_b200.parallel.stage_worker import simple_message
+    from tnn_b200.parallel.tcp_transport import TcpTransport, ping_pong
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc, peer = None, a.peer
+    if not peer:
+        proc = subprocess.Popen([sys.executable, "-m", "tnn_b200.parallel.tcp_transport", "echo", "--sockets", str(a.sockets),
+                                 "--max-packet", str(a.packet_mib << 20)], stdout=subprocess.PIPE, text=True, cwd=root,
+                                env=dict(os.environ, PYTHONPATH=root))
+        peer = proc.stdout.readline().split()[1]
+    t = TcpTransport(a.host, 0, a.sockets, a.packet_mib << 20)
+    try:
+        ping_pong(t, peer, 1 << 20, 0.2)  # connect and warm up
+        r = ping_pong(t, peer, a.mib << 20, a.seconds)
+        small = ping_pong(t, peer, 6, min(a.seconds, 2.0))
+        t.send(peer, simple_message("SHUTDOWN"))
+    finally:
+        t.close()
+        if proc is not None:
+            proc.wait(timeout=30)
+    return {"bench": "tcp_ping_pong", "peer": peer, "message_mib": a.mib, "sockets": a.sockets, "packet_mib": a.packet_mib,
+            "round_trips": r["round_trips"], "mb_per_s_each_way": round(r["mb_per_s_each_way"], 1),
+            "small_message_round_trip_us": round(small["seconds"] / max(1, small["round_trips"]) * 1e6, 1)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -147,8 +178,15 @@ def main():
     s.add_argument("--cpu", action="store_true")
     s = sub.add_parser("memcpy")
     s.add_argument("--mib", type=int, default=256)
+    s = sub.add_parser("tcp")
+    s.add_argument("--mib", type=int, default=128)
+    s.add_argument("--seconds", type=float, default=10.0)
+    s.add_argument("--sockets", type=int, default=4)
+    s.add_argument("--packet-mib", type=int, default=4)
+    s.add_argument("--host", default="127.0.0.1")
+    s.add_argument("--peer", default="", help="host:port of a running `python -m tnn_b200.parallel.tcp_transport echo`")
     a = ap.parse_args()
-    print(json.dumps({"serialization": cmd_serialization, "tnng": cmd_tnng, "grad_clear": cmd_grad_clear, "memcpy": cmd_memcpy}[a.cmd](a)))
+    print(json.dumps({"tcp": cmd_tcp, "serialization": cmd_serialization, "tnng": cmd_tnng, "grad_clear": cmd_grad_clear, "memcpy": cmd_memcpy}[a.cmd](a)))
 
 
 if __name__ == "__main__":

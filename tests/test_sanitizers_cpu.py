@@ -86,3 +86,14 @@ def test_host_test_suite_under_asan_ubsan(sanitized_build):
     assert "ERROR: AddressSanitizer" not in r.stderr + r.stdout and "runtime error:" not in r.stderr + r.stdout, \
         (r.stdout[-2000:] + r.stderr[-3000:])
     assert r.returncode == 0, (r.stdout[-2000:] + r.stderr[-2000:])
+
+
+def test_tcp_communicator_under_asan_ubsan(sanitized_build):
+    """The socket reader / writer threads of the TCP communicator (loopback messages, reassembly, destruction with
+    packets still queued) on the sanitized build."""
+    cmd = [sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_tcp_cpu.py"), "-x", "-q", "-p", "no:cacheprovider",
+           "-k", "communicator or aggregator"]
+    r = subprocess.run(cmd, env=_env(), capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert "ERROR: AddressSanitizer" not in r.stderr + r.stdout and "runtime error:" not in r.stderr + r.stdout, \
+        (r.stdout[-2000:] + r.stderr[-3000:])
+    assert r.returncode == 0, (r.stdout[-2000:] + r.stderr[-2000:])

@@ -109,6 +109,72 @@ def cmd_generate(a) -> int:
     return 0
 
 
+def cmd_tcp_worker(a) -> int:
+    """One pipeline stage behind a TCP endpoint (reference: examples/tcp_worker.cpp:39-141)."""
+    from .parallel.tcp_transport import main as tcp_main
+
+    dev = "cuda" if (a.gpu and torch.cuda.is_available()) else "cpu"
+    return tcp_main(["worker", "--host", a.host, "--port", str(a.port), "--device", dev, "--sockets", str(a.sockets),
+                     "--max-packet", str(a.max_packet)])
+
+
+def cmd_tcp_coordinator(a) -> int:
+    """Pipeline training driven from this process over TCP (reference: examples/tcp_coordinator.cpp:27-128 with the keys
+    of configs/tcp_config.json): stage i goes to ``worker_endpoints[i]``; when ``local_worker_port`` is set, the last
+    stage runs on a thread of this process behind that port."""
+    import threading
+    import time
+
+    from .data.loaders import create_loaders
+    from .models import zoo
+    from .parallel.tcp_transport import TcpStageServer, tcp_coordinator
+
+    cfg = _load_cfg(a.config)
+    endpoints = [f"{w.get('host', '127.0.0.1')}:{int(w['port'])}" for w in cfg.worker_endpoints]
+    local = None
+    if cfg.local_worker_port:
+        dev = "cuda" if (cfg.device_type.upper() == "CUDA" and torch.cuda.is_available()) else "cpu"
+        srv = TcpStageServer(cfg.local_worker_host or cfg.host, cfg.local_worker_port, dev, cfg.skts_per_endpoint, cfg.max_packet_size)
+        local = threading.Thread(target=srv.serve, daemon=True)
+        local.start()
+        endpoints.append(srv.name)
+    ratios = list(cfg.partition_ratios or cfg.parallel.partition_ratios) or [1.0] * len(endpoints)
+    if len(ratios) != len(endpoints):
+        raise SystemExit(f"{len(ratios)} partition ratios for {len(endpoints)} workers")
+    graph = zoo.create(cfg.model_name)
+    co = tcp_coordinator(graph, ratios, endpoints, cfg.optimizer, cfg.scheduler, cfg.loss, cfg.num_microbatches,
+                         cfg.host, cfg.port, cfg.skts_per_endpoint, cfg.max_packet_size)
+    train, _ = create_loaders(cfg.dataset_name, cfg.dataset_path, cfg.batch_size, cfg.seed,
+                              cfg.prefetch_depth if cfg.prefetch_data else 0, cfg.model_name)
+    co.broadcast("TRAIN_MODE", expect="MODE_CHANGED")
+    steps = cfg.max_steps if cfg.max_steps and cfg.max_steps > 0 else cfg.epochs * train.batches_per_epoch()
+    it, done, loss = iter(train), 0, float("nan")
+    t0 = time.perf_counter()
+    while done < steps:
+        try:
+            data, labels = next(it)
+        except StopIteration:
+            it = iter(train)
+            continue
+        loss = co.train_batch(data, labels)
+        done += 1
+        if done % max(1, cfg.progress_print_interval) == 0 or done == steps:
+            print(f"step {done}/{steps} loss {loss:.4f} ({(time.perf_counter() - t0) / done * 1e3:.1f} ms/step)", flush=True)
+    if cfg.snapshot_dir:
+        os.makedirs(cfg.snapshot_dir, exist_ok=True)
+        from .parallel.stage_worker import simple_message
+        for i, name in enumerate(co.names):  # each worker writes its own stage, on its own host
+            co.post(name, simple_message("SAVE_TO_FILE", text=os.path.join(cfg.snapshot_dir, f"{cfg.model_name}_stage{i}.tnng")))
+        co.broadcast("PRINT_LR", expect="LR_PRINTED")  # answered after the save
+    co.shutdown()
+    stats = co.transport.stats()
+    co.transport.close()
+    if local is not None:
+        local.join(timeout=30)
+    print(json.dumps({"steps": done, "final_loss": loss, "seconds": round(time.perf_counter() - t0, 3), **stats}))
+    return 0
+
+
 def cmd_info(a) -> int:
     from . import _build
     from .host import H
@@ -146,9 +212,18 @@ def main(argv=None) -> int:
     p.add_argument("--eos", type=int, default=50256)
     p.add_argument("--device", default=default_device_type(), help="CPU or CUDA (default: $DEVICE_TYPE, else CUDA when present)")
     p.add_argument("--seed", type=int, default=0)
+    p = sub.add_parser("tcp-worker", help="serve one pipeline stage over TCP until the coordinator shuts it down")
+    p.add_argument("port", type=int, nargs="?", default=0)
+    p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--gpu", action="store_true")
+    p.add_argument("--sockets", type=int, default=4)
+    p.add_argument("--max-packet", type=int, default=4 << 20)
+    p = sub.add_parser("tcp-coordinator", help="partition a model and train it on TCP workers (keys of the reference's tcp_config.json)")
+    p.add_argument("--config", "-c", required=True)
     sub.add_parser("info", help="build and device information")
     a = ap.parse_args(argv)
-    return {"train": cmd_train, "infer": cmd_infer, "generate": cmd_generate, "info": cmd_info}[a.cmd](a)
+    return {"train": cmd_train, "infer": cmd_infer, "generate": cmd_generate, "info": cmd_info,
+            "tcp-worker": cmd_tcp_worker, "tcp-coordinator": cmd_tcp_coordinator}[a.cmd](a)
 
 
 if __name__ == "__main__":

@@ -6,6 +6,7 @@
 #include "profiler.h"
 #include "tconfig.h"
 #include "tnng.h"
+#include "tcp_comm.h"
 #include "wire.h"
 
 namespace py = pybind11;
@@ -259,6 +260,58 @@ PYBIND11_MODULE(_host, m) {
         return py::none();
       })
       .def("pending", &Aggregator::pending);
+
+  // ---- TCP transport (blocking calls release the interpreter lock) ----
+  // The destructor joins writer threads that may be waiting for the interpreter lock to release a bytes object,
+  // so the lock is dropped while the communicator is destroyed.
+  struct TcpDeleter {
+    void operator()(TcpCommunicator* p) const {
+      py::gil_scoped_release rel;
+      delete p;
+    }
+  };
+  py::class_<TcpCommunicator, std::unique_ptr<TcpCommunicator, TcpDeleter>>(m, "TcpCommunicator")
+      .def(py::init<std::string, int, int, uint64_t>(), py::arg("host") = "127.0.0.1", py::arg("port") = 0,
+           py::arg("sockets_per_endpoint") = 4, py::arg("max_packet_size") = 4ull << 20)
+      .def("start", &TcpCommunicator::start, py::call_guard<py::gil_scoped_release>())
+      .def("endpoint", &TcpCommunicator::endpoint)
+      .def("connect", &TcpCommunicator::connect, py::arg("host"), py::arg("port"), py::arg("timeout_s") = 10.0,
+           py::call_guard<py::gil_scoped_release>())
+      .def("connected", &TcpCommunicator::connected)
+      .def("peers", &TcpCommunicator::peers)
+      .def("send", [](TcpCommunicator& c, const std::string& ep, const py::bytes& data) {
+        // no copy: the packets point into the bytes object, which is released (under the interpreter lock, from a
+        // writer thread) after the last of them has been written
+        char* p = nullptr;
+        Py_ssize_t n = 0;
+        if (PyBytes_AsStringAndSize(data.ptr(), &p, &n) != 0) throw py::error_already_set();
+        PyObject* obj = data.ptr();
+        Py_INCREF(obj);
+        std::shared_ptr<const void> keep(static_cast<const void*>(obj), [](const void* o) {
+          py::gil_scoped_acquire g;
+          Py_DECREF(reinterpret_cast<PyObject*>(const_cast<void*>(o)));
+        });
+        py::gil_scoped_release rel;
+        c.send_view(ep, p, static_cast<size_t>(n), std::move(keep));
+      })
+      .def("recv", [](TcpCommunicator& c, double timeout_s) -> py::object {
+        std::string ep, msg;
+        bool ok;
+        {
+          py::gil_scoped_release rel;
+          ok = c.recv(timeout_s, &ep, &msg);
+        }
+        if (!ok) return py::none();
+        return py::make_tuple(ep, py::bytes(msg));
+      }, py::arg("timeout_s") = -1.0)
+      .def("flush", &TcpCommunicator::flush, py::arg("timeout_s") = 30.0, py::call_guard<py::gil_scoped_release>())
+      .def("stop", &TcpCommunicator::stop, py::call_guard<py::gil_scoped_release>())
+      .def("stats", [](const TcpCommunicator& c) {
+        py::dict d;
+        d["bytes_sent"] = c.bytes_sent(); d["bytes_received"] = c.bytes_received();
+        d["messages_sent"] = c.messages_sent(); d["messages_received"] = c.messages_received();
+        return d;
+      });
 
   // ---- profiler ----
   py::class_<Profiler>(m, "Profiler")

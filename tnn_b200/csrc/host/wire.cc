@@ -165,9 +165,7 @@ std::vector<std::string> slice_message(const std::string& msg, uint64_t msg_id, 
   return out;
 }
 
-bool Aggregator::feed(const char* packet, size_t n, std::string* out, uint64_t* msg_id) {
-  const PacketHeader h = read_packet_header(packet, n);
-  if (n != PacketHeader::kSize + h.packet_length) throw std::runtime_error("packet length does not match its header");
+char* Aggregator::reserve(const PacketHeader& h, bool* duplicate) {
   if (h.packet_offset >= h.total_packets) throw std::runtime_error("packet index out of range");
   Slot& s = slots_[h.msg_serial_id];
   if (s.seen.empty()) {
@@ -183,18 +181,34 @@ bool Aggregator::feed(const char* packet, size_t n, std::string* out, uint64_t* 
   else stride = (h.msg_length - h.packet_length) / (h.total_packets - 1);
   const uint64_t off = stride * h.packet_offset;
   if (off + h.packet_length > s.buf.size()) throw std::runtime_error("fragment exceeds message length");
+  if (duplicate) *duplicate = s.seen[h.packet_offset] != 0;
+  return s.buf.empty() ? nullptr : &s.buf[0] + off;
+}
+
+bool Aggregator::commit(const PacketHeader& h, std::string* out, uint64_t* msg_id) {
+  auto it = slots_.find(h.msg_serial_id);
+  if (it == slots_.end() || h.packet_offset >= it->second.seen.size()) throw std::runtime_error("commit of a packet that was not reserved");
+  Slot& s = it->second;
   if (!s.seen[h.packet_offset]) {
-    std::memcpy(&s.buf[off], packet + PacketHeader::kSize, h.packet_length);
     s.seen[h.packet_offset] = 1;
     ++s.received;
   }
   if (s.received == h.total_packets) {
     if (out) *out = std::move(s.buf);
     if (msg_id) *msg_id = h.msg_serial_id;
-    slots_.erase(h.msg_serial_id);
+    slots_.erase(it);
     return true;
   }
   return false;
+}
+
+bool Aggregator::feed(const char* packet, size_t n, std::string* out, uint64_t* msg_id) {
+  const PacketHeader h = read_packet_header(packet, n);
+  if (n != PacketHeader::kSize + h.packet_length) throw std::runtime_error("packet length does not match its header");
+  bool dup = false;
+  char* dst = reserve(h, &dup);
+  if (!dup && h.packet_length) std::memcpy(dst, packet + PacketHeader::kSize, h.packet_length);
+  return commit(h, out, msg_id);
 }
 
 }  // namespace tnnb

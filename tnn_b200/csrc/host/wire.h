@@ -94,6 +94,13 @@ std::vector<std::string> slice_message(const std::string& msg, uint64_t msg_id, 
 class Aggregator {
  public:
   bool feed(const char* packet, size_t n, std::string* out, uint64_t* msg_id = nullptr);
+  // The two halves of feed() for a receiver that reads a payload straight from a socket into the message:
+  // reserve() returns where the payload of the packet described by `h` belongs (`duplicate` tells whether that
+  // packet has arrived before, in which case the caller must not write there), commit() records its arrival.
+  // The message buffer does not move between the two calls, so several packets of one message may be filled at
+  // the same time as long as reserve() and commit() themselves are serialised by the caller.
+  char* reserve(const PacketHeader& h, bool* duplicate);
+  bool commit(const PacketHeader& h, std::string* out, uint64_t* msg_id = nullptr);
   size_t pending() const { return slots_.size(); }
 
  private:

@@ -65,19 +65,28 @@ __global__ void im2col_kernel(const bf16* __restrict__ x, bf16* __restrict__ col
       const int n = (int)(pix / ((long long)g.OW * g.OH));
       const bf16* img = x + (long long)n * g.H * g.W * g.C;
       __align__(16) bf16 v[8];
+      // In NHWC the (kw, c) run of one filter row is contiguous in the image, so a column index k = kh * KW*C + kp
+      // maps to img[(ih * W + iw0) * C + kp]; the horizontal bounds become a range of kp. One division per thread
+      // instead of six per element - with three channels this kernel is bound by integer arithmetic, not by memory.
+      const int kwc = g.KW * g.C;
+      const int ih0 = oh * g.SH - g.PH, iw0 = ow * g.SW - g.PW;
+      const int lo = (iw0 < 0 ? -iw0 : 0) * g.C;
+      const int hi = (g.W - iw0 < g.KW ? g.W - iw0 : g.KW) * g.C;
+      int kh = (gi * 8) / kwc;
+      int kp = gi * 8 - kh * kwc;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const int k = gi * 8 + j;
         bf16 e = __float2bfloat16(0.f);
-        if (k < K) {
-          const int c = k % g.C;
-          const int kw = (k / g.C) % g.KW;
-          const int kh = k / (g.C * g.KW);
-          const int ih = oh * g.SH + kh - g.PH, iw = ow * g.SW + kw - g.PW;
-          if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W && TNNB_CHECK(((long long)ih * g.W + iw) * g.C + c, (long long)g.H * g.W * g.C))
-            e = img[((long long)ih * g.W + iw) * g.C + c];
+        const int ih = ih0 + kh;
+        if (gi * 8 + j < K && ih >= 0 && ih < g.H && kp >= lo && kp < hi) {
+          const long long off = ((long long)ih * g.W + iw0) * g.C + kp;
+          if (TNNB_CHECK(off, (long long)g.H * g.W * g.C)) e = img[off];
         }
         v[j] = e;
+        if (++kp == kwc) {
+          kp = 0;
+          ++kh;
+        }
       }
       *reinterpret_cast<uint4*>(cols + pix * g.Kld + gi * 8) = *reinterpret_cast<const uint4*>(v);
     }

@@ -57,12 +57,13 @@ def simple_message(command: str, text: Optional[str] = None, flag: Optional[bool
     return H.serialize_message(m)
 
 
-def stage_config_message(stage: Graph, optimizer_cfg: dict, scheduler_cfg: dict, next_stage: str, prev_stage: str) -> bytes:
+def stage_config_message(stage: Graph, optimizer_cfg: dict, scheduler_cfg: dict, next_stage: str, prev_stage: str,
+                         coordinator: str = "coordinator") -> bytes:
     return H.serialize_message({"command": _cmd("CONFIG_TRANSFER"), "kind": STAGE_CONFIG, "stage": {
         "graph_state": tnng.serialize(stage.state()), "input_uids": [n.uid() for n in stage.input_nodes],
         "output_uids": [n.uid() for n in stage.output_nodes], "optimizer_config": json.dumps(optimizer_cfg),
         "scheduler_config": json.dumps(scheduler_cfg), "next_stage": next_stage, "prev_stage": prev_stage,
-        "coordinator": COORDINATOR}})
+        "coordinator": coordinator}})
 
 
 class StageWorker:
@@ -161,20 +162,31 @@ class StageWorker:
 
 
 class LocalCoordinator:
-    """Drives stage workers through the protocol. ``send(destination, bytes)`` delivers a message; the default
-    transport is an in-process queue that calls the destination worker's ``handle``."""
+    """Drives stage workers through the protocol. The default transport is an in-process queue that calls the
+    destination worker's ``handle``; with ``transport`` (an object with ``name``, ``send(endpoint, bytes)`` and
+    ``recv(timeout_s) -> (endpoint, bytes) | None``, see ``parallel/tcp_transport.py``) and ``endpoints`` (one per
+    stage, in pipeline order) the same coordinator drives worker processes on other hosts."""
+
+    reply_timeout_s = 60.0  # the reference's join() waits 60 s for the replies of a broadcast (coordinator.hpp:541-568)
 
     def __init__(self, graph: Graph, ratios: Sequence[float], optimizer_cfg: dict, scheduler_cfg: Optional[dict] = None,
                  loss_cfg: Optional[dict] = None, microbatches: int = 2, device: str = "cpu",
-                 workers: Optional[Dict[str, StageWorker]] = None):
+                 workers: Optional[Dict[str, StageWorker]] = None, transport=None, endpoints: Optional[Sequence[str]] = None):
         self.micro = max(1, int(microbatches))
         self.loss = create_loss(loss_cfg or {"type": "logsoftmax_crossentropy"})
         if not graph.compiled:
             graph.compile(device="cpu", seed=0)  # initial values of the whole model, as a single-process run would draw them
         # stage graphs share the layer objects (and so the parameter values) of `graph`; only their state is shipped
         stages = partition_graph(graph, ratios)
-        self.names = [f"stage{i}" for i in range(len(stages))]
-        self.workers = workers or {n: StageWorker(n, device) for n in self.names}
+        self.transport = transport
+        if transport is not None:
+            if endpoints is None or len(endpoints) != len(stages):
+                raise ValueError(f"{len(stages)} stages need {len(stages)} worker endpoints")
+            self.names = list(endpoints)
+            self.workers = {}
+        else:
+            self.names = [f"stage{i}" for i in range(len(stages))]
+            self.workers = workers or {n: StageWorker(n, device) for n in self.names}
         self.inbox: Deque[dict] = deque()
         self.queue: Deque[Tuple[str, bytes]] = deque()
         self.in_uid = stages[0].input_nodes[0].uid()
@@ -182,19 +194,35 @@ class LocalCoordinator:
         for i, (n, s) in enumerate(zip(self.names, stages)):
             nxt = self.names[i + 1] if i + 1 < len(stages) else ""
             prv = self.names[i - 1] if i > 0 else ""
-            self.post(n, stage_config_message(s, optimizer_cfg, scheduler_cfg or {"type": "no_op"}, nxt, prv))
-        replies = self.run()
+            self.post(n, stage_config_message(s, optimizer_cfg, scheduler_cfg or {"type": "no_op"}, nxt, prv,
+                                              transport.name if transport is not None else COORDINATOR))
+        replies = self.run(len(stages))
         bad = [r for r in replies if r["command_name"] != "CONFIG_RECEIVED" or not r.get("flag")]
         if bad or len(replies) != len(stages):
             raise RuntimeError(f"stage configuration failed: {bad}")
 
     # ------------------------------------------------------------------ transport
     def post(self, dst: str, data: bytes) -> None:
-        self.queue.append((dst, data))
+        if self.transport is not None:
+            self.transport.send(dst, data)
+        else:
+            self.queue.append((dst, data))
 
-    def run(self) -> List[dict]:
-        """Deliver queued messages until none is left; returns what reached the coordinator."""
+    def run(self, expect: int = 0) -> List[dict]:
+        """In process: deliver queued messages until none is left; returns what reached the coordinator. Over a
+        transport: wait for ``expect`` messages addressed to the coordinator."""
         got = []
+        if self.transport is not None:
+            deadline = time.monotonic() + self.reply_timeout_s
+            while len(got) < expect:
+                item = self.transport.recv(max(0.0, deadline - time.monotonic()))
+                if item is None:
+                    raise TimeoutError(f"{len(got)} of {expect} replies arrived within {self.reply_timeout_s:.0f} s")
+                m = H.parse_message(item[1])
+                if m["command_name"] == "ERROR_REPORT":
+                    raise RuntimeError(m.get("text", "worker error"))
+                got.append(m)
+            return got
         while self.queue:
             dst, data = self.queue.popleft()
             if dst == COORDINATOR:
@@ -210,7 +238,7 @@ class LocalCoordinator:
     def broadcast(self, command: str, expect: Optional[str] = None, **kw) -> List[dict]:
         for n in self.names:
             self.post(n, simple_message(command, **kw))
-        got = self.run()
+        got = self.run(len(self.names) if expect is not None else 0)
         if expect is not None and sorted(m["command_name"] for m in got) != [expect] * len(self.names):
             raise RuntimeError(f"{command}: expected {len(self.names)} x {expect}, got {[m['command_name'] for m in got]}")
         return got
@@ -222,14 +250,14 @@ class LocalCoordinator:
         mb_data, mb_labels = data.chunk(self.micro), labels.chunk(self.micro)
         for pid, d in enumerate(mb_data):
             self.post(self.names[0], job_message("FORWARD_JOB", pid, {self.in_uid: d}))
-        outs = {m["job"]["pid"]: m for m in self.run() if m["command_name"] == "FORWARD_JOB"}
+        outs = {m["job"]["pid"]: m for m in self.run(len(mb_data)) if m["command_name"] == "FORWARD_JOB"}
         total = 0.0
         for pid, lab in enumerate(mb_labels):
             logits = dict(outs[pid]["job"]["tensors"])[self.out_uid]
             loss, grad = self.loss.compute(tnng.record_to_tensor(logits), lab, 1.0 / len(mb_data), True)
             total += float(loss) / len(mb_data)
             self.post(self.names[-1], job_message("BACKWARD_JOB", pid, {self.out_uid: grad}))
-        done = [m for m in self.run() if m["command_name"] == "BACKWARD_COMPLETE"]
+        done = [m for m in self.run(len(mb_data)) if m["command_name"] == "BACKWARD_COMPLETE"]
         if len(done) != len(mb_data):
             raise RuntimeError("not every micro-batch completed its backward pass")
         self.broadcast("UPDATE_PARAMETERS", expect="PARAMETERS_UPDATED")
@@ -240,7 +268,7 @@ class LocalCoordinator:
         first = True
         for n in self.names:
             self.post(n, simple_message("REPORT_PROFILING"))
-        for m in self.run():
+        for m in self.run(len(self.names)):
             p = H.Profiler()
             p.set_start_time(m["profiler"]["start_time"])
             for (s, e, t, name, src) in m["profiler"]["events"]:

@@ -65,6 +65,9 @@ class TrainingConfig:
     worker_endpoints: List[Dict[str, Any]] = field(default_factory=list)
     partition_ratios: List[float] = field(default_factory=list)
     max_packet_size: int = 4 * 1024 * 1024
+    skts_per_endpoint: int = 4
+    local_worker_host: str = ""      # with a port: the last stage runs inside the coordinator process
+    local_worker_port: int = 0
 
     @property
     def step_mode(self) -> bool:
