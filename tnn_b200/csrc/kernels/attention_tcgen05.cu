@@ -367,23 +367,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 }
 
 // --------------------------------------------------------------- preprocess
-// delta[b,h,s] = sum_d O[b,s,h,d] * dO[b,s,h,d]; one warp per (b,s,h) row.
+// delta[b,h,s] = sum_d O[b,s,h,d] * dO[b,s,h,d]. Eight lanes per (b,s,h) row of 64 values, 16 bytes per lane and
+// tensor, so a warp covers four rows per trip with two 512-byte requests (both tensors are 16-byte aligned: the
+// entry point checks it).
 __global__ void attn_delta_kernel(const bf16* __restrict__ O, const bf16* __restrict__ dO,
                                   float* __restrict__ delta, int B, int S, int H) {
   const long long total = (long long)B * S * H;
   const int lane = threadIdx.x & 31;
-  for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < total;
-       r += (long long)gridDim.x * (blockDim.x >> 5)) {
-    const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(O + r * 64)[lane];
-    const __nv_bfloat162 d = reinterpret_cast<const __nv_bfloat162*>(dO + r * 64)[lane];
-    float v = __bfloat162float(a.x) * __bfloat162float(d.x) + __bfloat162float(a.y) * __bfloat162float(d.y);
+  const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  {
+    const int sub = lane >> 3, l8 = lane & 7;
+    for (long long g = warp0; g * 4 < total; g += nwarps) {
+      const long long r = g * 4 + sub;
+      float v = 0.f;
+      if (r < total) {
+        const uint4 a = reinterpret_cast<const uint4*>(O + r * 64)[l8];
+        const uint4 d = reinterpret_cast<const uint4*>(dO + r * 64)[l8];
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, dw[4] = {d.x, d.y, d.z, d.w};
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == 0) {
-      const long long hh = r % H;
-      const long long bs = r / H;
-      const long long s = bs % S, bb = bs / S;
-      delta[(bb * H + hh) * S + s] = v;
+        for (int i = 0; i < 4; ++i)
+          v += __uint_as_float(aw[i] << 16) * __uint_as_float(dw[i] << 16) +
+               __uint_as_float(aw[i] & 0xffff0000u) * __uint_as_float(dw[i] & 0xffff0000u);
+      }
+      v += __shfl_xor_sync(0xffffffffu, v, 4);
+      v += __shfl_xor_sync(0xffffffffu, v, 2);
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      if (l8 == 0 && r < total) {
+        const long long hh = r % H;
+        const long long bs = r / H;
+        const long long s = bs % S, bb = bs / S;
+        delta[(bb * H + hh) * S + s] = v;
+      }
     }
   }
 }
@@ -849,7 +864,8 @@ int tnnb_attn_bwd(const void* qkv, const void* out, const void* dout, const void
   }
   const long long rows = (long long)B * S * H;
   cudaMemsetAsync(dq_acc, 0, sizeof(float) * (size_t)B * S * E, st);
-  int g = (int)((rows + 7) / 8 > 148 * 8 ? 148 * 8 : (rows + 7) / 8);
+  const long long dw = (rows + 3) / 4;  // warps of work for the delta kernel, eight per block
+  int g = (int)((dw + 7) / 8 > 148 * 8 ? 148 * 8 : (dw + 7) / 8);
   attn_delta_kernel<<<g, 256, 0, st>>>((const bf16*)out, (const bf16*)dout, (float*)delta, B, S, H);
   dim3 grid((S + 127) / 128, H, B);
   attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, st>>>(tq, tk, tv, tdo, tdq, p);
