@@ -67,3 +67,41 @@ def test_profile_timeline_from_layer_profiler(tmp_path):
     tr = json.load(open(out))["traceEvents"]
     assert sum(1 for e in tr if e["ph"] == "X") == sum(len(v) for s in ev.values() for v in s.values())
     assert {e["args"]["name"] for e in tr if e["ph"] == "M" and e["name"] == "process_name"} == {"rank0", "worker1"}
+
+
+def test_compare_logs_throughput_and_loss(tmp_path):
+    """Two log dialects (this framework's batch CSV, the reference PyTorch trainer's phase-tagged log), the
+    reference's throughput and TFLOP/s arithmetic, rolling-mean loss, and the merged per-step series."""
+    import csv
+    import json as _json
+
+    from tnn_b200.utils import compare_logs as cl
+    from tnn_b200.utils.csv_logger import CsvLogger
+
+    lg = CsvLogger(str(tmp_path), "resnet50")
+    for i in range(10):
+        lg.log_train_step(epoch=0, step=i, batch_loss=2.0 - 0.1 * i, avg_loss=2.0, accuracy_pct=10.0 + i, time_ms=50.0 if i else 500.0)
+    lg.close()
+    ours = lg.paths["batch"]
+    theirs = tmp_path / "torch.csv"
+    with open(theirs, "w", newline="") as f:
+        w = csv.writer(f)
+        w.writerow(["phase", "epoch", "step", "batch_loss", "avg_loss", "accuracy_percent", "batch_total_time", "batch_size"])
+        for i in range(6):
+            w.writerow(["train_batch", 0, i, 3.0, 3.0, 5.0, 0.2, 64])
+        w.writerow(["validation", 0, 0, "", "", "", "", ""])
+        w.writerow(["train_batch", 0, 6, "broken", "", "", "", ""])
+    a = cl.summarize(ours, 256, gflop_per_sample=cl.GFLOP_PER_SAMPLE["resnet50"], skip=1, smooth=3)
+    assert a["steps"] == 10 and a["median_ms"] == 50.0 and a["throughput"] == 5120.0
+    assert abs(a["tflops"] - 256 * 12.3 / 0.05 / 1e3) < 0.01
+    assert abs(a["final_loss_smoothed"] - (1.3 + 1.2 + 1.1) / 3) < 1e-4 and a["first_loss"] == 2.0
+    b = cl.summarize(str(theirs), 128)  # the file's own batch_size column wins; seconds become milliseconds
+    assert b["steps"] == 6 and b["batch_size"] == 64 and b["median_ms"] == 200.0 and b["throughput"] == 320.0
+    assert cl.rolling_mean([1, 2, 3, 4], 2) == [1.0, 1.5, 2.5, 3.5]
+    out = tmp_path / "series.csv"
+    assert cl.main([ours, str(theirs), "--batch-size", "256", "--model", "resnet50", "--skip", "1", "--series-csv", str(out)]) == 0
+    rows = list(csv.reader(open(out)))
+    assert len(rows) == 11 and rows[0][0] == "global_step" and rows[7][3] == "" and float(rows[1][1]) == 2.0
+    # language-model form: tokens per second
+    c = cl.summarize(ours, 8, samples_per_item=1024, gflop_per_sample=cl.GFLOP_PER_SAMPLE["gpt2_small"], skip=1)
+    assert c["throughput"] == 8 * 1024 / 0.05 and _json.dumps(c)
