@@ -1,6 +1,9 @@
 """Partitioner and 1F1B pipeline on CPU: schedule order, stage boundaries (incl. skip connections),
 chained stages == full graph, stage checkpoints, and 2/4-rank gloo runs vs a single process."""
+import json
 import os
+
+import pytest
 import subprocess
 import sys
 
@@ -170,9 +173,37 @@ def test_coordinator_worker_protocol_equals_single_graph(tmp_path):
     assert all("lr 0.1" in t for t in lrs)
     prof = co.merged_profile()
     assert len(prof) > 10 and any("FORWARD_JOB" in line and "Source: stage1" in line for line in prof.log_lines())
+    # weights read back over the protocol equal the saved ones; pushed weights replace them; status and log commands answer
+    from tnn_b200.io import tnng as _tnng
+    from tnn_b200.parallel.stage_worker import job_message
+    per_stage, got = [], {}
+    for name in co.names:
+        co.post(name, simple_message("SEND_PARAMS"))
+        m, = co.run(1)
+        assert m["command_name"] == "PARAMS_TRANSFER"
+        per_stage.append(dict(m["job"]["tensors"]))
+        got.update(per_stage[-1])
+    for l in ref.layers():
+        for i, p in enumerate(l.params):
+            assert torch.allclose(_tnng.record_to_tensor(got[f"{l.name}:{i}"]), p, atol=1e-5), l.name
+    some = sorted(per_stage[0])[0]
+    co.post(co.names[0], job_message("LOAD_PARAMS", 0, {some: torch.zeros_like(_tnng.record_to_tensor(per_stage[0][some]))}))
+    m, = co.run(1)
+    assert m["command_name"] == "PARAMS_LOADED" and m["flag"]
+    co.post(co.names[0], simple_message("SEND_PARAMS"))
+    back = dict(co.run(1)[0]["job"]["tensors"])
+    assert float(_tnng.record_to_tensor(back[some]).abs().sum()) == 0.0
+    co.post(co.names[0], job_message("LOAD_PARAMS", 0, {sorted(per_stage[1])[0]: torch.zeros(1)}))  # another stage's tensor
+    with pytest.raises(RuntimeError, match="no such parameters"):
+        co.run(1)
+    st = [json.loads(m["text"]) for m in co.broadcast("STATUS_REQUEST", expect="STATUS_RESPONSE")]
+    assert all(s["configured"] and s["training"] and s["parameters"] > 0 for s in st) and abs(st[0]["learning_rate"] - 0.1) < 1e-7
+    co.broadcast("PRINT_LOGS", expect="LOGS_PRINTED")
+    co.broadcast("PRINT_PROFILING", expect="PROFILING_PRINTED")
+    co.broadcast("CLEAR_PROFILING", expect="PROFILING_CLEARED")
+    co.broadcast("HANDSHAKE")
     # a declared-but-unimplemented command comes back as ERROR_REPORT instead of raising inside the worker
     co.post("stage0", H.serialize_message({"command": H.command_code("HEALTH_CHECK"), "kind": 0}))
-    import pytest
     with pytest.raises(RuntimeError, match="not implemented"):
         co.run()
     co.shutdown()

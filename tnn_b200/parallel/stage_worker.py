@@ -12,8 +12,11 @@ stay meaningful and a stage can be driven by any transport that moves byte strin
   ``FORWARD_JOB -> FORWARD_JOB`` to the next stage, ``BACKWARD_JOB -> BACKWARD_JOB`` to the previous stage or
   ``BACKWARD_COMPLETE`` to the coordinator at stage 0, ``UPDATE_PARAMETERS -> PARAMETERS_UPDATED``,
   ``SAVE_TO_FILE`` (``ERROR_REPORT`` on failure), ``PRINT_LR -> LR_PRINTED``, ``START_PROFILING``,
-  ``REPORT_PROFILING -> PROFILING_REPORTED`` (profiler payload), ``SHUTDOWN``. Commands the reference declares but
-  never implements (``HEALTH_CHECK``, ``BARRIER_SYNC``, ...) answer ``ERROR_REPORT`` instead of throwing.
+  ``REPORT_PROFILING -> PROFILING_REPORTED`` (profiler payload), ``PRINT_PROFILING -> PROFILING_PRINTED``,
+  ``CLEAR_PROFILING -> PROFILING_CLEARED``, ``PRINT_LOGS -> LOGS_PRINTED``, ``HANDSHAKE`` / ``HANDSHAKE_ACK`` (ignored),
+  ``SHUTDOWN``. ``SEND_PARAMS -> PARAMS_TRANSFER``, ``LOAD_PARAMS -> PARAMS_LOADED`` and
+  ``STATUS_REQUEST -> STATUS_RESPONSE``, whose bodies the reference leaves empty or throwing, are implemented. Commands
+  the reference declares without a handler (``HEALTH_CHECK``, ``BARRIER_SYNC``, ...) answer ``ERROR_REPORT``.
 * :class:`LocalCoordinator` is the coordinator's side: it partitions a graph, configures the workers, splits a
   batch into micro-batches, computes loss and dL/dlogits (scaled by ``1 / micro-batches``,
   coordinator.hpp:225) and drives forward / backward / update - delivering messages through a ``send`` callable
@@ -154,7 +157,59 @@ class StageWorker:
 
     def _on_clear_profiling(self, msg):
         self.profiler.clear()
+        return [(COORDINATOR, simple_message("PROFILING_CLEARED"))]
+
+    def _on_print_profiling(self, msg):
+        for line in self.profiler.log_lines():
+            print(line, flush=True)
+        return [(COORDINATOR, simple_message("PROFILING_PRINTED"))]
+
+    def _on_print_logs(self, msg):
+        return [(COORDINATOR, simple_message("LOGS_PRINTED"))]
+
+    def _on_handshake(self, msg):
         return []
+
+    _on_handshake_ack = _on_handshake
+
+    def _on_error_report(self, msg):
+        print(f"{self.name} received error: {msg.get('text', '')}", flush=True)
+        return []
+
+    # The reference declares the next three commands and leaves their bodies empty or throwing
+    # (worker.hpp:192-195,246-261); here they work, so that a coordinator can read a stage's weights back, push new
+    # ones (a restart from another run's snapshot without touching the worker's disk) and ask what a worker holds.
+    def _param_items(self):
+        for layer in self.graph.layers():
+            for i, t in enumerate(layer.params):
+                yield f"{layer.name}:{i}", t
+
+    def _on_send_params(self, msg):
+        # master precision, like a checkpoint
+        return [(COORDINATOR, job_message("PARAMS_TRANSFER", 0, {k: self.graph._master_view(t) for k, t in self._param_items()}))]
+
+    def _on_load_params(self, msg):
+        mine = dict(self._param_items())
+        got = self._bundle(msg)
+        unknown = sorted(set(got) - set(mine))
+        if unknown:
+            raise KeyError(f"no such parameters on this stage: {unknown[:4]}")
+        for k, t in got.items():
+            if tuple(t.shape) != tuple(mine[k].shape):
+                raise ValueError(f"{k}: shape {tuple(t.shape)} does not match {tuple(mine[k].shape)}")
+        with torch.no_grad():
+            for k, t in got.items():
+                self.graph._load_param(mine[k], t)  # into the fp32 master where the stage keeps one
+            self.graph.sync_params_from_master()
+        return [(COORDINATOR, simple_message("PARAMS_LOADED", flag=True))]
+
+    def _on_status_request(self, msg):
+        st = {"name": self.name, "configured": self.graph is not None, "next_stage": self.next_stage, "prev_stage": self.prev_stage}
+        if self.graph is not None:
+            st.update(training=bool(self.graph.training), layers=len(self.graph.layers()),
+                      parameters=int(sum(t.numel() for _, t in self._param_items())),
+                      learning_rate=float(self.optimizer.get_learning_rate()), profiled_events=len(self.profiler))
+        return [(COORDINATOR, simple_message("STATUS_RESPONSE", text=json.dumps(st)))]
 
     def _on_shutdown(self, msg):
         self.alive = False
