@@ -126,3 +126,35 @@ def test_pipeline_over_tcp_matches_single_process(tmp_path):
         for p, _ in procs:
             if p.poll() is None:
                 p.kill()
+
+
+def test_coordinator_notices_a_dead_worker():
+    """Failure detection on the host: a worker process is killed between steps; the coordinator's next step ends
+    with ConnectionError within seconds instead of waiting out the reply timeout."""
+    import time
+
+    from tnn_b200.models import zoo
+    from tnn_b200.parallel.tcp_transport import tcp_coordinator
+
+    procs = [_spawn("worker", "--idle-timeout", "60") for _ in range(2)]
+    co = None
+    try:
+        co = tcp_coordinator(zoo.gpt2(32, 1, 2, "t", seq_len=16, vocab=29, drop=0.0), [1.0, 1.0], [e for _, e in procs],
+                             {"type": "sgd", "learning_rate": 0.1}, microbatches=2)
+        co.reply_timeout_s = 60.0
+        co.broadcast("TRAIN_MODE", expect="MODE_CHANGED")
+        seq = torch.randint(0, 29, (4, 17), generator=torch.Generator().manual_seed(1))
+        co.train_batch(seq[:, :-1].contiguous(), seq[:, 1:].contiguous())
+        procs[1][0].kill()
+        procs[1][0].wait(timeout=30)
+        t0 = time.monotonic()
+        with pytest.raises((ConnectionError, RuntimeError), match="lost the connection|cannot deliver"):
+            co.train_batch(seq[:, :-1].contiguous(), seq[:, 1:].contiguous())
+        assert time.monotonic() - t0 < 20.0
+        assert procs[0][0].poll() is None  # the surviving worker reported the failure and is still serving
+    finally:
+        if co is not None:
+            co.transport.close()
+        for p, _ in procs:
+            if p.poll() is None:
+                p.kill()

@@ -269,10 +269,18 @@ class LocalCoordinator:
         got = []
         if self.transport is not None:
             deadline = time.monotonic() + self.reply_timeout_s
+            lost_fn = getattr(self.transport, "lost", None)
             while len(got) < expect:
-                item = self.transport.recv(max(0.0, deadline - time.monotonic()))
+                # wait in short slices so that a worker whose connection dropped is noticed at once instead of after
+                # the whole reply timeout (the reference's coordinator blocks for ever on a lost worker)
+                item = self.transport.recv(min(0.5, max(0.0, deadline - time.monotonic())))
                 if item is None:
-                    raise TimeoutError(f"{len(got)} of {expect} replies arrived within {self.reply_timeout_s:.0f} s")
+                    gone = lost_fn(self.names) if lost_fn is not None else []
+                    if gone:
+                        raise ConnectionError(f"lost the connection to {gone} while waiting for {expect - len(got)} replies")
+                    if time.monotonic() >= deadline:
+                        raise TimeoutError(f"{len(got)} of {expect} replies arrived within {self.reply_timeout_s:.0f} s")
+                    continue
                 m = H.parse_message(item[1])
                 if m["command_name"] == "ERROR_REPORT":
                     raise RuntimeError(m.get("text", "worker error"))

@@ -47,6 +47,12 @@ class TcpTransport:
     def recv(self, timeout_s: float = -1.0):
         return self.comm.recv(timeout_s)
 
+    def lost(self, endpoints: Sequence[str]):
+        """Those of ``endpoints`` this side had a connection to, all of whose sockets have since closed (the peer
+        exited or the network dropped; reference: handle_channel_error, tcp_communicator.hpp:359-393)."""
+        known = set(self.comm.peers())
+        return [e for e in endpoints if e in known and not self.comm.connected(e)]
+
     def flush(self, timeout_s: float = 30.0) -> None:
         self.comm.flush(timeout_s)
 
@@ -85,7 +91,15 @@ class TcpStageServer:
                     target = self.coordinator if dst == COORDINATOR else dst
                     if target is None:
                         raise RuntimeError("a reply for the coordinator before any CONFIG_TRANSFER named one")
-                    self.transport.send(target, reply)
+                    try:
+                        self.transport.send(target, reply)
+                    except RuntimeError as e:
+                        if target == self.coordinator:
+                            raise  # nobody left to report to
+                        # a neighbour is gone: tell the coordinator instead of dying silently (the reference drops
+                        # the channel and keeps waiting, tcp_communicator.hpp:359-393)
+                        self.transport.send(self.coordinator, simple_message(
+                            "ERROR_REPORT", text=f"{self.name}: cannot deliver to {target}: {e}"))
                 n += 1
         finally:
             self.transport.close()
