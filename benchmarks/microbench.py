@@ -150,6 +150,59 @@ def cmd_batchnorm(a):
     return {"fwd_ms": f, "fwd_gbs": round(3 * byt / f / 1e6), "bwd_ms": bw, "bwd_gbs": round(5 * byt / bw / 1e6)}
 
 
+def _time_graph(g, x, iters):
+    """Forward + backward of a compiled graph through the executor (the calls a user makes), device-timed."""
+    out = g.forward({"input": x})["output"]
+    dy = torch.randn_like(out)
+    g.backward({"output": dy})
+    f = timeit(lambda: g.forward({"input": x}), iters)
+
+    def fb():
+        g.forward({"input": x})
+        g.backward({"output": dy})
+        g.zero_grads()
+
+    return f, timeit(fb, iters)
+
+
+def cmd_attention_block(a):
+    """The reference's attention-block benchmark (benchmarks/attention_benchmark.cpp:11-40: batch 16, sequence 512,
+    embedding 768, 8 heads, i.e. head size 96): QKV projection, causal attention and output projection as one layer."""
+    from tnn_b200.nn.blocks import FlashAttentionBlock
+    from tnn_b200.nn.graph import Graph
+
+    g = Graph()
+    out = FlashAttentionBlock(a.embed, a.heads, True, 1.0 / (a.embed // a.heads) ** 0.5, name="attn")(g.input("input"))
+    out.set_uid("output")
+    g.set_output(out)
+    g.input_requires_grad = True
+    g.compile(device="cuda", seed=0)
+    x = bf(a.batch, a.seq, a.embed)
+    f, fb = _time_graph(g, x, a.iters)
+    D = a.embed // a.heads
+    fl = 2.0 * a.batch * a.seq * a.embed * 4 * a.embed + 4.0 * a.batch * a.heads * a.seq * a.seq * D / 2
+    return {"head_dim": D, "fwd_ms": f, "fwd_tflops": round(fl / f / 1e9, 1), "fwd_bwd_ms": fb, "fwd_bwd_tflops": round(3 * fl / fb / 1e9, 1)}
+
+
+def cmd_conv_bn_pool(a):
+    """The reference's layer-pipeline benchmark (benchmarks/pipeline_benchmark.cpp:20-62): convolution -> batch norm
+    (+ ReLU) -> max pooling on a 128 x 224 x 224 x 3 batch."""
+    from tnn_b200.nn import layers as L
+    from tnn_b200.nn.graph import Graph
+
+    g = Graph()
+    h = L.Conv2D(3, a.cout, 3, 3, 1, 1, 1, 1, name="conv")(g.input("input"))
+    h = L.BatchNorm(a.cout, use_relu=True, name="bn")(h)
+    out = L.MaxPool2D(2, 2, 2, 2, name="pool")(h)
+    out.set_uid("output")
+    g.set_output(out)
+    g.compile(device="cuda", seed=0)
+    x = bf(a.batch, a.size, a.size, 3)
+    f, fb = _time_graph(g, x, a.iters)
+    act = a.batch * a.size * a.size * a.cout * 2  # bytes of the convolution output
+    return {"fwd_ms": f, "fwd_bwd_ms": fb, "conv_output_mb": round(act / 1e6, 1), "images_per_s_fwd_bwd": round(a.batch / fb * 1e3, 1)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -164,6 +217,10 @@ def main():
     p = sub.add_parser("conv2d"); p.add_argument("--batch", type=int, default=128); p.add_argument("--size", type=int, default=56)
     p.add_argument("--cin", type=int, default=64); p.add_argument("--cout", type=int, default=64); p.add_argument("--ksize", type=int, default=3)
     p.add_argument("--stride", type=int, default=1)
+    p = sub.add_parser("attention_block"); p.add_argument("--batch", type=int, default=16); p.add_argument("--seq", type=int, default=512)
+    p.add_argument("--embed", type=int, default=768); p.add_argument("--heads", type=int, default=8)
+    p = sub.add_parser("conv_bn_pool"); p.add_argument("--batch", type=int, default=128); p.add_argument("--size", type=int, default=224)
+    p.add_argument("--cout", type=int, default=64)
     p = sub.add_parser("batchnorm"); p.add_argument("--batch", type=int, default=128); p.add_argument("--size", type=int, default=56)
     p.add_argument("--channels", type=int, default=256)
     for sp in sub.choices.values():
