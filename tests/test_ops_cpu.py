@@ -93,3 +93,48 @@ def test_named_ops_api():
     assert -1.0 <= float(u.min()) and float(u.max()) <= 1.0 and torch.equal(u, T.fill_random_uniform(torch.empty(1000), -1.0, 1.0, seed=3))
     assert T.check_equals(a, a + 1e-4, tol=1e-3) and not T.check_equals(a, a + 1e-2, tol=1e-3)
     assert T.cast(a, torch.bfloat16).dtype == torch.bfloat16
+
+
+def test_functional_autograd_bridges_match_torch():
+    """ops/functional.py: the autograd Functions around the kernels (here their CPU references) against plain torch
+    autograd on the same expressions - a GPT-2 style block written as an ordinary module trains through them."""
+    import torch.nn.functional as TF
+
+    from tnn_b200.ops import functional as F
+
+    torch.manual_seed(0)
+    B, S, E, H, V = 2, 8, 16, 2, 11
+    x = torch.randn(B, S, E, requires_grad=True)
+    delta = torch.randn(B, S, E, requires_grad=True)
+    g1, b1 = torch.randn(E, requires_grad=True), torch.randn(E, requires_grad=True)
+    wqkv, bqkv = (torch.randn(3 * E, E) * 0.2).requires_grad_(), torch.randn(3 * E, requires_grad=True)
+    w1, bb1 = (torch.randn(4 * E, E) * 0.2).requires_grad_(), torch.randn(4 * E, requires_grad=True)
+    wh = (torch.randn(V, E) * 0.2).requires_grad_()
+    labels = torch.randint(0, V, (B, S))
+    params = [x, delta, g1, b1, wqkv, bqkv, w1, bb1, wh]
+
+    def ours():
+        h, s = F.add_layer_norm(x, delta, g1, b1, 1e-5)
+        a = F.causal_self_attention(F.linear(h, wqkv, bqkv), H)
+        m = F.linear(F.linear(a + s, w1, bb1, gelu=True)[..., :E].contiguous(), wh)
+        return F.cross_entropy(m, labels, return_corrects=True)
+
+    def theirs():
+        s = x + delta
+        h = TF.layer_norm(s, (E,), g1, b1, 1e-5)
+        q, k, v = TF.linear(h, wqkv, bqkv).split(E, dim=-1)
+        hd = lambda t: t.reshape(B, S, H, E // H).transpose(1, 2)
+        a = TF.scaled_dot_product_attention(hd(q), hd(k), hd(v), is_causal=True).transpose(1, 2).reshape(B, S, E)
+        m = TF.linear(TF.gelu(TF.linear(a + s, w1, bb1), approximate="tanh")[..., :E], wh)
+        return TF.cross_entropy(m.reshape(-1, V), labels.reshape(-1)), (m.argmax(-1) == labels).sum()
+
+    (l1, c1), (l2, c2) = ours(), theirs()
+    assert abs(float(l1) - float(l2)) < 1e-5 and int(c1) == int(c2)
+    ga = torch.autograd.grad(l1, params)
+    gb = torch.autograd.grad(l2, params)
+    for a, b, p in zip(ga, gb, params):
+        assert a.shape == p.shape and torch.allclose(a.float(), b, atol=2e-5, rtol=1e-4), (a - b).abs().max()
+    # a scaled loss scales the gradients (the saved gradient of the cross-entropy is multiplied by the incoming one)
+    l3, _ = ours()
+    g3, = torch.autograd.grad(3.0 * l3, [wh])
+    assert torch.allclose(g3, 3.0 * gb[-1], atol=1e-4)

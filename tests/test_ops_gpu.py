@@ -181,3 +181,42 @@ def test_optimizers():
     mw2 = w.clone().cuda()
     raw.sgd_step(mw2, None, g.cuda(), None, 0.0, 0.0, 1.0, hyper)
     close(mw2, w - 0.5 * 2.0 * g, tol=1e-4)
+
+
+def test_functional_autograd_bridges_on_gpu():
+    """ops/functional.py on bf16 CUDA tensors (tcgen05 GEMM, flash attention, layer norm and cross-entropy kernels
+    behind torch.autograd) against the same expressions in fp32 torch on the CPU."""
+    import torch.nn.functional as TF
+
+    from tnn_b200.ops import functional as F
+
+    torch.manual_seed(0)
+    B, S, E, H, V = 2, 128, 128, 2, 1000
+    mk = lambda *s, sc=1.0: (torch.randn(*s) * sc).to(BF).float()  # fp32 values that are exact in bf16
+    x, delta, g1, b1 = mk(B, S, E), mk(B, S, E), mk(E) + 1, mk(E, sc=0.1)
+    wqkv, bqkv, w1, bb1, wh = mk(3 * E, E, sc=0.08), mk(3 * E, sc=0.1), mk(4 * E, E, sc=0.08), mk(4 * E, sc=0.1), mk(V, 4 * E, sc=0.05)
+    labels = torch.randint(0, V, (B, S))
+    cpu = [t.clone().requires_grad_() for t in (x, delta, g1, b1, wqkv, bqkv, w1, bb1, wh)]
+    gpu = [t.cuda().to(BF).requires_grad_() for t in (x, delta, g1, b1, wqkv, bqkv, w1, bb1, wh)]
+
+    def ours(x, delta, g1, b1, wqkv, bqkv, w1, bb1, wh):
+        h, s = F.add_layer_norm(x, delta, g1, b1, 1e-5)
+        a = F.causal_self_attention(F.linear(h, wqkv, bqkv), H)
+        return F.cross_entropy(F.linear(F.linear(a + s, w1, bb1, gelu=True), wh), labels.cuda())
+
+    def theirs(x, delta, g1, b1, wqkv, bqkv, w1, bb1, wh):
+        s = x + delta
+        q, k, v = TF.linear(TF.layer_norm(s, (E,), g1, b1, 1e-5), wqkv, bqkv).split(E, dim=-1)
+        hd = lambda t: t.reshape(B, S, H, E // H).transpose(1, 2)
+        a = TF.scaled_dot_product_attention(hd(q), hd(k), hd(v), is_causal=True).transpose(1, 2).reshape(B, S, E)
+        m = TF.linear(TF.gelu(TF.linear(a + s, w1, bb1), approximate="tanh"), wh)
+        return TF.cross_entropy(m.reshape(-1, V), labels.reshape(-1))
+
+    l1, l2 = ours(*gpu), theirs(*cpu)
+    assert abs(l1.item() - l2.item()) < 3e-2 * abs(l2.item())
+    l1.backward()
+    l2.backward()
+    _lib.check_status()
+    for i, (a, b) in enumerate(zip(gpu, cpu)):
+        assert a.grad is not None and a.grad.dtype == BF
+        close(a.grad, b.grad, tol=6e-2, what=f"gradient {i}")

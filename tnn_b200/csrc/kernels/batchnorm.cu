@@ -258,10 +258,12 @@ bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, con
   }
 }
 
-static void bn_grid(long long M, int C, dim3& grid, long long& rpb) {
+// per_sm: blocks per SM the grid is sized for. The apply kernels run several short waves (6); the reduction kernels,
+// which end in a shared-memory reduction and atomics per block, run as a single wave of their resident block count.
+static void bn_grid(long long M, int C, dim3& grid, long long& rpb, int per_sm = 6) {
   const int cl = bn_cl(C);
   const int gx = ((C >> 3) + cl - 1) / cl;
-  int gy = (6 * 148 + gx - 1) / gx;
+  int gy = (per_sm * 148 + gx - 1) / gx;
   rpb = (M + gy - 1) / gy;
   const int nry = 256 / cl;
   if (rpb < 4 * nry) rpb = 4 * nry;
@@ -286,7 +288,10 @@ int tnnb_batchnorm_fwd(const void* x, void* y, const void* gamma, const void* be
   bn_grid(M, C, grid, rpb);
   if (training) {
     cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st);
-    bn_reduce_kernel<false, 0><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (double*)ws, M, C, rpb);
+    dim3 rgrid;
+    long long rrpb;
+    bn_grid(M, C, rgrid, rrpb, 3);
+    bn_reduce_kernel<false, 0><<<rgrid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (double*)ws, M, C, rrpb);
   }
   bn_fwd_apply_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)y, (const bf16*)gamma, (const bf16*)beta, (const double*)ws,
                                             (float*)mean, (float*)rstd, (float*)run_mean, (float*)run_var, M, C, rpb, eps,
@@ -307,11 +312,14 @@ int tnnb_batchnorm_bwd(const void* x, const void* dy, const void* y, const void*
   long long rpb;
   bn_grid(M, C, grid, rpb);
   cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st);
+  dim3 rgrid;
+  long long rrpb;
+  bn_grid(M, C, rgrid, rrpb, 2);
 #define TNNB_BN_BWD(MASK)                                                                                              \
   do {                                                                                                                 \
-    bn_reduce_kernel<true, MASK><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y, (const bf16*)gamma, \
+    bn_reduce_kernel<true, MASK><<<rgrid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y, (const bf16*)gamma, \
                                                        (const bf16*)beta, (const float*)mean, (const float*)rstd,       \
-                                                       (double*)ws, M, C, rpb);                                         \
+                                                       (double*)ws, M, C, rrpb);                                        \
     bn_bwd_apply_kernel<MASK><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y, (const bf16*)gamma,  \
                                                     (const bf16*)beta, (const float*)mean, (const float*)rstd,          \
                                                     (const double*)ws, (bf16*)dx, (float*)dgamma, (float*)dbeta, M, C,  \
