@@ -138,3 +138,15 @@ def test_functional_autograd_bridges_match_torch():
     l3, _ = ours()
     g3, = torch.autograd.grad(3.0 * l3, [wh])
     assert torch.allclose(g3, 3.0 * gb[-1], atol=1e-4)
+
+
+def test_example_torch_module_on_functional_ops_trains():
+    import importlib.util
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "torch_module_with_kernels.py")
+    spec = importlib.util.spec_from_file_location("torch_module_with_kernels", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    first, last = mod.main("cpu", 25)
+    assert last < 0.6 * first

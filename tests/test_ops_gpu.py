@@ -220,3 +220,16 @@ def test_functional_autograd_bridges_on_gpu():
     for i, (a, b) in enumerate(zip(gpu, cpu)):
         assert a.grad is not None and a.grad.dtype == BF
         close(a.grad, b.grad, tol=6e-2, what=f"gradient {i}")
+
+
+def test_example_torch_module_on_functional_ops_trains_on_gpu():
+    import importlib.util
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "torch_module_with_kernels.py")
+    spec = importlib.util.spec_from_file_location("torch_module_with_kernels", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    first, last = mod.main("cuda", 40)
+    _lib.check_status()
+    assert last == last and last < 0.8 * first  # finite and decreasing with bf16 parameters

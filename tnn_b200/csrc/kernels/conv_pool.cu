@@ -106,16 +106,15 @@ __global__ void col2im_kernel(const bf16* __restrict__ dcols, bf16* __restrict__
     float acc[VEC];
 #pragma unroll
     for (int k = 0; k < VEC; ++k) acc[k] = 0.f;
-    for (int kh = 0; kh < g.KH; ++kh) {
-      const int t = h + g.PH - kh;
-      if (t < 0 || t % g.SH) continue;
-      const int oh = t / g.SH;
-      if (oh >= g.OH) continue;
-      for (int kw = 0; kw < g.KW; ++kw) {
-        const int u = w + g.PW - kw;
-        if (u < 0 || u % g.SW) continue;
-        const int ow = u / g.SW;
-        if (ow >= g.OW) continue;
+    // the output pixels whose window covers (h, w), as index ranges (two divisions per axis, see pool_bwd_kernel)
+    const int th = h + g.PH, tw = w + g.PW;
+    const int oh_hi = min(th / g.SH, g.OH - 1), ow_hi = min(tw / g.SW, g.OW - 1);
+    const int oh_lo = th - g.KH + 1 > 0 ? (th - g.KH + g.SH) / g.SH : 0;
+    const int ow_lo = tw - g.KW + 1 > 0 ? (tw - g.KW + g.SW) / g.SW : 0;
+    for (int oh = oh_lo; oh <= oh_hi; ++oh) {
+      const int kh = th - oh * g.SH;
+      for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+        const int kw = tw - ow * g.SW;
         const long long soff = (((long long)n * g.OH + oh) * g.OW + ow) * g.Kld + (long long)(kh * g.KW + kw) * g.C + c * VEC;
         if (!TNNB_CHECK(soff + VEC - 1, (long long)g.N * g.OH * g.OW * g.Kld)) continue;
         const bf16* src = dcols + soff;
@@ -197,16 +196,17 @@ __global__ void pool_bwd_kernel(const bf16* __restrict__ dy, const unsigned char
     const int h = (int)(r % g.H);
     const int n = (int)(r / g.H);
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int kh = 0; kh < g.KH; ++kh) {
-      const int t = h + g.PH - kh;
-      if (t < 0 || t % g.SH) continue;
-      const int oh = t / g.SH;
-      if (oh >= g.OH) continue;
-      for (int kw = 0; kw < g.KW; ++kw) {
-        const int u = w + g.PW - kw;
-        if (u < 0 || u % g.SW) continue;
-        const int ow = u / g.SW;
-        if (ow >= g.OW) continue;
+    // Output rows whose window covers input row h: oh * SH - PH <= h < oh * SH - PH + KH. The range is computed with
+    // two divisions per axis instead of a divisibility test per filter tap (the kernel was bound by integer
+    // arithmetic, not by memory).
+    const int th = h + g.PH, tw = w + g.PW;
+    const int oh_hi = min(th / g.SH, g.OH - 1), ow_hi = min(tw / g.SW, g.OW - 1);
+    const int oh_lo = th - g.KH + 1 > 0 ? (th - g.KH + g.SH) / g.SH : 0;
+    const int ow_lo = tw - g.KW + 1 > 0 ? (tw - g.KW + g.SW) / g.SW : 0;
+    for (int oh = oh_lo; oh <= oh_hi; ++oh) {
+      const int kh = th - oh * g.SH;
+      for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+        const int kw = tw - ow * g.SW;
         const long long o = ((((long long)n * g.OH + oh) * g.OW + ow) * cv + c) * 8;
         if (!TNNB_CHECK(o + 7, (long long)g.N * g.OH * g.OW * g.C)) continue;
         uint4 raw = *reinterpret_cast<const uint4*>(dy + o);
