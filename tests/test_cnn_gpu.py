@@ -81,6 +81,61 @@ def test_batchnorm(shape, relu, affine):
     close(yi, raw.batchnorm_infer(x, g, b, rm, rv, 1e-5, relu), what="infer")
 
 
+@pytest.mark.parametrize("shape", [(4, 8, 8, 64), (3, 5, 5, 8), (37, 7, 7, 256)])
+def test_batchnorm_with_closing_residual_add(shape):
+    """y = relu(bn(x) + shortcut) in the batch norm's own pass, training and inference, and a bottleneck-style
+    residual block (main path ending in a batch norm without ReLU) through the layer API against the CPU path."""
+    torch.manual_seed(2)
+    C = shape[-1]
+    x, res = rnd(*shape) + 0.3, rnd(*shape)
+    g, b = rnd(C) + 1, rnd(C)
+    rm, rv = torch.zeros(C), torch.ones(C)
+    crm, crv = rm.cuda(), rv.cuda()
+    y, mean, rstd = raw.batchnorm_fwd_train(x.cuda(), g.cuda(), b.cuda(), crm, crv, 1e-5, 0.1, True, resid=res.cuda())
+    ry, rmean, rrstd = raw.batchnorm_fwd_train(x, g, b, rm, rv, 1e-5, 0.1, True, resid=res)
+    _lib.check_status()
+    close(y, ry, what="y")
+    assert float(y.min()) >= 0.0
+    close(mean, rmean, tol=1e-3)
+    close(crv, rv, tol=1e-2)
+    close(raw.batchnorm_infer(x.cuda(), g.cuda(), b.cuda(), crm, crv, 1e-5, False, resid=res.cuda()),
+          raw.batchnorm_infer(x, g, b, rm, rv, 1e-5, False, resid=res), what="infer")
+
+
+def test_residual_block_with_fused_closing_add_matches_cpu():
+    from tnn_b200.nn import layers as L
+    from tnn_b200.nn.blocks import ResidualBlock, Sequential
+    from tnn_b200.nn.graph import Graph
+
+    def build():
+        g = Graph()
+        main = Sequential([L.Conv2D(64, 64, 3, 3, 1, 1, 1, 1, name="c1"), L.BatchNorm(64, use_relu=True, name="b1"),
+                           L.Conv2D(64, 64, 1, 1, 1, 1, 0, 0, name="c2"), L.BatchNorm(64, name="b2")], name="main")
+        out = ResidualBlock(main, None, "relu", name="block")(g.input("input"))
+        out.set_uid("output")
+        g.set_output(out)
+        g.input_requires_grad = True
+        return g
+
+    torch.manual_seed(3)
+    cpu = build().compile(device="cpu", seed=0)
+    gpu = build().compile(device="cuda", seed=0)
+    for lc, lg in zip(cpu.layers(), gpu.layers()):  # bf16-rounded weights on both sides (slab layouts differ by dtype)
+        for pc, pg in zip(lc.params, lg.params):
+            pc.copy_(pg.float().cpu())
+    x, dy = rnd(4, 12, 12, 64), rnd(4, 12, 12, 64)
+    yc = cpu.forward({"input": x.float()})["output"]
+    yg = gpu.forward({"input": x.cuda()})["output"]
+    close(yg, yc, what="block output")
+    dc = cpu.backward({"output": dy.float()})["input"]
+    dg = gpu.backward({"output": dy.cuda()})["input"]
+    _lib.check_status()
+    close(dg, dc, tol=5e-2, what="block input gradient")
+    ga = torch.cat([g.reshape(-1).float() for l in cpu.layers() for g in l.grads if g is not None])
+    gb = torch.cat([g.reshape(-1).float().cpu() for l in gpu.layers() for g in l.grads if g is not None])
+    close(gb, ga, tol=5e-2, what="parameter gradients")
+
+
 @pytest.mark.parametrize("mode", ["max", "avg"])
 @pytest.mark.parametrize("h,k,s,p", [(8, 2, 2, 0), (9, 3, 2, 1), (7, 7, 1, 0), (6, 3, 3, 0)])
 def test_pool(mode, h, k, s, p):

@@ -133,8 +133,10 @@ bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const 
   }
 }
 
+// RES: y = relu?(bn(x) + resid) - the closing add (+ ReLU) of a residual block folded into the block's last batch norm.
+template <bool RES>
 __global__ void __launch_bounds__(256)
-bn_fwd_apply_kernel(const bf16* __restrict__ x, bf16* __restrict__ yout, const bf16* __restrict__ gamma,
+bn_fwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ resid, bf16* __restrict__ yout, const bf16* __restrict__ gamma,
                     const bf16* __restrict__ beta, const double* __restrict__ ws, float* __restrict__ mean_o,
                     float* __restrict__ rstd_o, float* __restrict__ run_mean, float* __restrict__ run_var, long long M, int C,
                     long long rows_per_block, float eps, float momentum, int relu, int training) {
@@ -170,22 +172,28 @@ bn_fwd_apply_kernel(const bf16* __restrict__ x, bf16* __restrict__ yout, const b
   }
   const long long r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
   for (long long r = r0 + ry; r < r1; r += BN_U * nry) {
-    uint4 xr[BN_U];
+    uint4 xr[BN_U], rr4[RES ? BN_U : 1];
     bool ok[BN_U];
 #pragma unroll
     for (int u = 0; u < BN_U; ++u) {
       const long long rr = r + (long long)u * nry;
       ok[u] = rr < r1 && TNNB_CHECK(rr * C + c0 + 7, M * (long long)C);  // lane layout vs. tensor extent
       xr[u] = make_uint4(0, 0, 0, 0);
-      if (ok[u]) xr[u] = *reinterpret_cast<const uint4*>(x + rr * C + c0);
+      if (RES) rr4[RES ? u : 0] = make_uint4(0, 0, 0, 0);
+      if (ok[u]) {
+        xr[u] = *reinterpret_cast<const uint4*>(x + rr * C + c0);
+        if (RES) rr4[RES ? u : 0] = *reinterpret_cast<const uint4*>(resid + rr * C + c0);
+      }
     }
 #pragma unroll
     for (int u = 0; u < BN_U; ++u) {
       const bf16* xv = reinterpret_cast<const bf16*>(&xr[u]);
+      const bf16* rv = reinterpret_cast<const bf16*>(&rr4[RES ? u : 0]);
       __align__(16) bf16 o[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         float v = __bfloat162float(xv[k]) * sc[k] + sh[k];
+        if (RES) v = __bfloat162float(__float2bfloat16(v)) + __bfloat162float(rv[k]);  // the sum of two bf16 tensors, as a separate add would see it
         o[k] = __float2bfloat16(relu ? fmaxf(v, 0.f) : v);
       }
       if (ok[u]) *reinterpret_cast<uint4*>(yout + (r + (long long)u * nry) * C + c0) = *reinterpret_cast<uint4*>(o);
@@ -258,8 +266,8 @@ bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, con
   }
 }
 
-// per_sm: blocks per SM the grid is sized for. The apply kernels run several short waves (6); the reduction kernels,
-// which end in a shared-memory reduction and atomics per block, run as a single wave of their resident block count.
+// per_sm: blocks per SM the grid is sized for. Every kernel here runs as a single wave of its resident block count
+// (set by its registers): measured faster than several short waves, each of which ramps up and drains.
 static void bn_grid(long long M, int C, dim3& grid, long long& rpb, int per_sm = 6) {
   const int cl = bn_cl(C);
   const int gx = ((C >> 3) + cl - 1) / cl;
@@ -278,14 +286,14 @@ using namespace tnnb;
 extern "C" {
 
 // ws: double[2*C] scratch owned by the caller (zeroed here). gamma/beta may be null.
-int tnnb_batchnorm_fwd(const void* x, void* y, const void* gamma, const void* beta, void* ws, void* mean, void* rstd,
+static int bn_fwd_impl(const void* x, const void* resid, void* y, const void* gamma, const void* beta, void* ws, void* mean, void* rstd,
                        void* run_mean, void* run_var, long long M, int C, float eps, float momentum, int relu, int training,
                        void* stream) {
-  if (C % 8 || ((uintptr_t)x & 15) || ((uintptr_t)y & 15)) return -3;
+  if (C % 8 || ((uintptr_t)x & 15) || ((uintptr_t)y & 15) || ((uintptr_t)resid & 15)) return -3;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid;
   long long rpb;
-  bn_grid(M, C, grid, rpb);
+  bn_grid(M, C, grid, rpb, resid ? 3 : 4);  // one wave of the apply kernel's resident blocks (64 / 80 registers)
   if (training) {
     cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st);
     dim3 rgrid;
@@ -293,11 +301,30 @@ int tnnb_batchnorm_fwd(const void* x, void* y, const void* gamma, const void* be
     bn_grid(M, C, rgrid, rrpb, 3);
     bn_reduce_kernel<false, 0><<<rgrid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (double*)ws, M, C, rrpb);
   }
-  bn_fwd_apply_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)y, (const bf16*)gamma, (const bf16*)beta, (const double*)ws,
-                                            (float*)mean, (float*)rstd, (float*)run_mean, (float*)run_var, M, C, rpb, eps,
-                                            momentum, relu, training);
+  if (resid)
+    bn_fwd_apply_kernel<true><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)resid, (bf16*)y, (const bf16*)gamma, (const bf16*)beta,
+                                                    (const double*)ws, (float*)mean, (float*)rstd, (float*)run_mean,
+                                                    (float*)run_var, M, C, rpb, eps, momentum, relu, training);
+  else
+    bn_fwd_apply_kernel<false><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, (bf16*)y, (const bf16*)gamma, (const bf16*)beta,
+                                                     (const double*)ws, (float*)mean, (float*)rstd, (float*)run_mean,
+                                                     (float*)run_var, M, C, rpb, eps, momentum, relu, training);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
+}
+
+int tnnb_batchnorm_fwd(const void* x, void* y, const void* gamma, const void* beta, void* ws, void* mean, void* rstd,
+                       void* run_mean, void* run_var, long long M, int C, float eps, float momentum, int relu, int training,
+                       void* stream) {
+  return bn_fwd_impl(x, nullptr, y, gamma, beta, ws, mean, rstd, run_mean, run_var, M, C, eps, momentum, relu, training, stream);
+}
+
+// y = relu?(bn(x) + resid): resid has the shape of x (bf16, 16-byte aligned).
+int tnnb_batchnorm_fwd_res(const void* x, const void* resid, void* y, const void* gamma, const void* beta, void* ws, void* mean,
+                           void* rstd, void* run_mean, void* run_var, long long M, int C, float eps, float momentum, int relu,
+                           int training, void* stream) {
+  if (!resid) return -5;
+  return bn_fwd_impl(x, resid, y, gamma, beta, ws, mean, rstd, run_mean, run_var, M, C, eps, momentum, relu, training, stream);
 }
 
 // Fused ReLU (relu != 0): with y == null the mask is recomputed from x, gamma, beta, mean and rstd (beta is read only
@@ -310,7 +337,7 @@ int tnnb_batchnorm_bwd(const void* x, const void* dy, const void* y, const void*
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid;
   long long rpb;
-  bn_grid(M, C, grid, rpb);
+  bn_grid(M, C, grid, rpb, 2);
   cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st);
   dim3 rgrid;
   long long rrpb;
@@ -375,7 +402,7 @@ int tnnb_batchnorm_fwd_noalloc(const void* x, void* y, const void* gamma, const 
   // The reduce kernel accumulates with atomics, so the 2*C sums it uses must start at zero.
   if (cudaMemsetAsync(ws, 0, sizeof(double) * 2 * C, st) != cudaSuccess) return TNNB_NOALLOC_LAUNCH_FAILED;
   bn_reduce_kernel<false, 0><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, ws, M, C, rpb);
-  bn_fwd_apply_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)y, (const bf16*)gamma, (const bf16*)beta, ws, (float*)mean,
+  bn_fwd_apply_kernel<false><<<grid, 256, 0, st>>>((const bf16*)x, nullptr, (bf16*)y, (const bf16*)gamma, (const bf16*)beta, ws, (float*)mean,
                                             (float*)rstd, (float*)run_mean, (float*)run_var, M, C, rpb, eps, momentum, relu, 1);
   return cudaGetLastError() == cudaSuccess ? TNNB_NOALLOC_OK : TNNB_NOALLOC_LAUNCH_FAILED;
 }

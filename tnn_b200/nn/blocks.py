@@ -130,6 +130,13 @@ class ResidualBlock(_Composite):
         x = inputs[0]
         base = {"_step": ctx.get("_step", 0), "_pid": ctx.get("_pid", 0)}
         ctx["m"], ctx["s"] = dict(base), dict(base)
+        if self._closing_add_in_batchnorm(x):
+            # shortcut first; the main path's last batch norm adds it and applies the ReLU in its own pass
+            s = self.shortcut.forward([x], ctx["s"]) if self.shortcut is not None else x
+            ctx["m"][len(self.main.layers) - 1] = dict(base, _add_relu=s.contiguous())
+            y = self.main.forward([x], ctx["m"])
+            ctx["y"] = y
+            return y
         m = self.main.forward([x], ctx["m"])
         s = self.shortcut.forward([x], ctx["s"]) if self.shortcut is not None else x
         if self.activation == "relu":
@@ -141,6 +148,13 @@ class ResidualBlock(_Composite):
             return z
         ctx["z"] = z
         return raw.act_fwd(z, self.activation, 1.0 if self.activation == "elu" else 0.01)
+
+    def _closing_add_in_batchnorm(self, x) -> bool:
+        from .layers import BatchNorm
+        if self.activation != "relu" or not self.main.layers:
+            return False
+        last = self.main.layers[-1]
+        return isinstance(last, BatchNorm) and not last.use_relu and x.dim() == 4
 
     def backward(self, grad, ctx):
         if self.activation == "relu":

@@ -636,11 +636,16 @@ class BatchNorm(Layer):
     def forward(self, inputs, ctx):
         x = inputs[0].contiguous()
         g, b, rm, rv = self._split()
+        # A residual block whose main path ends in this layer hands over its shortcut value: the block's closing
+        # add + ReLU then happens in this layer's normalisation pass (one read of the shortcut instead of a separate
+        # three-tensor kernel). The ReLU belongs to the block, whose backward masks the gradient before it gets here.
+        res = ctx.pop("_add_relu", None)
+        relu = self.use_relu or res is not None
         if self.training:
-            y, mean, rstd = raw.batchnorm_fwd_train(x, g, b, rm, rv, self.epsilon, self.momentum, self.use_relu)
+            y, mean, rstd = raw.batchnorm_fwd_train(x, g, b, rm, rv, self.epsilon, self.momentum, relu, resid=res)
             ctx["x"], ctx["y"], ctx["mean"], ctx["rstd"] = x, (y if self.use_relu else None), mean, rstd
             return y
-        return raw.batchnorm_infer(x, g, b, rm, rv, self.epsilon, self.use_relu)
+        return raw.batchnorm_infer(x, g, b, rm, rv, self.epsilon, relu, resid=res)
 
     def backward(self, grad, ctx):
         g, b, _, _ = self._split()

@@ -19,6 +19,8 @@ def _l():
         lib.tnnb_batchnorm_fwd.argtypes = [vp] * 9 + [ll, i, f, f, i, i, vp]
         lib.tnnb_batchnorm_bwd.argtypes = [vp] * 11 + [ll, i, i, vp]
         lib.tnnb_batchnorm_fwd.restype = lib.tnnb_batchnorm_bwd.restype = i
+        lib.tnnb_batchnorm_fwd_res.argtypes = [vp] * 10 + [ll, i, f, f, i, i, vp]
+        lib.tnnb_batchnorm_fwd_res.restype = i
         _DECL = True
     return lib
 
@@ -29,27 +31,36 @@ def _f32(t):
     return t
 
 
-def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps, momentum, relu):
+def _fwd(x, resid, *rest):
+    """``tnnb_batchnorm_fwd`` or, with a residual operand, ``tnnb_batchnorm_fwd_res`` (y = relu?(bn(x) + resid))."""
+    if resid is None:
+        return _l().tnnb_batchnorm_fwd(_lib.ptr(x), *rest)
+    if resid.shape != x.shape or resid.dtype != x.dtype:
+        raise ValueError("the residual operand must have the shape and dtype of the batch-norm input")
+    return _l().tnnb_batchnorm_fwd_res(_lib.ptr(x), _lib.ptr(resid.contiguous()), *rest)
+
+
+def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps, momentum, relu, resid=None):
     C = x.shape[-1]
     M = x.numel() // C
     y = torch.empty_like(x)
     mean = torch.empty(C, dtype=torch.float32, device=x.device)
     rstd = torch.empty_like(mean)
     ws = torch.empty(2 * C, dtype=torch.float64, device=x.device)
-    rc = _l().tnnb_batchnorm_fwd(_lib.ptr(x), _lib.ptr(y), _lib.ptr(gamma), _lib.ptr(beta), _lib.ptr(ws), _lib.ptr(mean),
-                                 _lib.ptr(rstd), _lib.ptr(_f32(run_mean)), _lib.ptr(_f32(run_var)), M, C, eps, momentum,
-                                 int(relu), 1, _lib.stream())
+    rc = _fwd(x, resid, _lib.ptr(y), _lib.ptr(gamma), _lib.ptr(beta), _lib.ptr(ws), _lib.ptr(mean),
+              _lib.ptr(rstd), _lib.ptr(_f32(run_mean)), _lib.ptr(_f32(run_var)), M, C, eps, momentum,
+              int(relu), 1, _lib.stream())
     _lib.check_rc(rc, "batchnorm_fwd")
     LAUNCHES["count"] += 2
     return y, mean, rstd
 
 
-def batchnorm_infer(x, gamma, beta, run_mean, run_var, eps, relu):
+def batchnorm_infer(x, gamma, beta, run_mean, run_var, eps, relu, resid=None):
     C = x.shape[-1]
     M = x.numel() // C
     y = torch.empty_like(x)
-    rc = _l().tnnb_batchnorm_fwd(_lib.ptr(x), _lib.ptr(y), _lib.ptr(gamma), _lib.ptr(beta), None, None, None,
-                                 _lib.ptr(_f32(run_mean)), _lib.ptr(_f32(run_var)), M, C, eps, 0.0, int(relu), 0, _lib.stream())
+    rc = _fwd(x, resid, _lib.ptr(y), _lib.ptr(gamma), _lib.ptr(beta), None, None, None,
+              _lib.ptr(_f32(run_mean)), _lib.ptr(_f32(run_var)), M, C, eps, 0.0, int(relu), 0, _lib.stream())
     _lib.check_rc(rc, "batchnorm_infer")
     LAUNCHES["count"] += 1
     return y

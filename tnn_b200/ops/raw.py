@@ -553,13 +553,14 @@ def conv2d_wgrad(x: torch.Tensor, dy: torch.Tensor, dw: torch.Tensor, stride, pa
 
 
 # ------------------------------------------------------------------------- batchnorm
-def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps: float, momentum: float, relu: bool):
+def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps: float, momentum: float, relu: bool, resid=None):
     """Training-mode batch norm over all dims but the last; updates the running stats in place.
-    Returns (y, mean, rstd) with fp32 statistics."""
+    Returns (y, mean, rstd) with fp32 statistics. With ``resid`` (shape of x) the result is ``relu?(bn(x) + resid)``:
+    the closing add of a residual block done in the same pass."""
     C = x.shape[-1]
     if x.is_cuda and x.dtype == torch.bfloat16:
         from . import norm
-        return norm.batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps, momentum, relu)
+        return norm.batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps, momentum, relu, resid)
     x2 = x.reshape(-1, C).float()
     M = x2.shape[0]
     mean = x2.mean(0)
@@ -568,6 +569,8 @@ def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps: float, momentum:
     y = (x2 - mean) * rstd
     if gamma is not None:
         y = y * gamma.float() + beta.float()
+    if resid is not None:
+        y = y.to(x.dtype).float() + resid.reshape(-1, C).float()
     if relu:
         y = torch.relu(y)
     unb = var * (M / max(M - 1, 1))
@@ -576,17 +579,19 @@ def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps: float, momentum:
     return y.reshape(x.shape).to(x.dtype), mean, rstd
 
 
-def batchnorm_infer(x, gamma, beta, run_mean, run_var, eps: float, relu: bool):
+def batchnorm_infer(x, gamma, beta, run_mean, run_var, eps: float, relu: bool, resid=None):
     C = x.shape[-1]
     if x.is_cuda and x.dtype == torch.bfloat16:
         from . import norm
-        return norm.batchnorm_infer(x, gamma, beta, run_mean, run_var, eps, relu)
+        return norm.batchnorm_infer(x, gamma, beta, run_mean, run_var, eps, relu, resid)
     scale = torch.rsqrt(run_var.float() + eps)
     shift = -run_mean.float() * scale
     if gamma is not None:
         scale = scale * gamma.float()
         shift = beta.float() - run_mean.float() * scale
     y = x.reshape(-1, C).float() * scale + shift
+    if resid is not None:
+        y = y.to(x.dtype).float() + resid.reshape(-1, C).float()
     if relu:
         y = torch.relu(y)
     return y.reshape(x.shape).to(x.dtype)
