@@ -9,7 +9,9 @@ gradient at zero *and* by restoring them after weight decay. State can be saved 
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+import os
+
+from typing import List, Sequence,  Dict, Optional
 
 import torch
 
@@ -170,6 +172,111 @@ class AdamW(Adam):
     def __init__(self, learning_rate: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, epsilon: float = 1e-8,
                  weight_decay: float = 0.01, **_):
         super().__init__(learning_rate, beta1, beta2, epsilon, weight_decay, True)
+
+
+def plan_buckets(points: Sequence[int], lo: int, hi: int, n_buckets: int, min_bucket: int) -> List[tuple]:
+    """Cut ``[lo, hi)`` into buckets ``(lo_i, hi_i)`` in the order backward finishes them (highest offsets first).
+    ``points`` are the offsets ``Graph.grad_hook`` reports, in firing order; a bucket ends at such a point and holds
+    at least ``max(min_bucket, (hi - lo) / n_buckets)`` elements (the last one takes what is left)."""
+    target = max(min_bucket, (hi - lo) // max(1, n_buckets))
+    out, top = [], hi
+    for pt in points:
+        pt = pt // 8 * 8
+        if lo < pt < top and top - pt >= target:
+            out.append((pt, top))
+            top = pt
+    out.append((lo, top))
+    return out
+
+
+class OverlappedUpdate:
+    """The optimizer step of a single-GPU job, spread under the backward pass.
+
+    The update is memory bound and small in registers; backward is a chain of tensor-core kernels. The flat parameter
+    buffer is laid out in first-use order, so backward finishes its gradients from the end: the buffer is cut into
+    buckets in that order (:func:`plan_buckets`) and a bucket's update (followed by the clearing of its gradients) is
+    launched on a second stream as soon as ``Graph.grad_hook`` reports its gradients final, while backward goes on in
+    the main stream. Only the last bucket (the embeddings) runs after backward. A bucket's parameters are no longer read
+    by the backward pass in progress, and ``update`` joins the second stream before the next forward pass.
+    The data-parallel optimizer does the same with its reduce + update + broadcast kernel (``parallel/dp.py``).
+
+    Wraps an :class:`Optimizer` and offers its surface; ``clears_grads`` tells the trainer that the gradient slab is
+    already zero after ``update``."""
+
+    clears_grads = True
+
+    def __init__(self, opt: Optimizer, graph, n_buckets: int = 4, min_bucket: int = 4 << 20):
+        self.opt, self.graph = opt, graph
+        min_bucket = int(os.environ.get("TNNB_UPDATE_MIN_BUCKET", str(min_bucket)))  # tests lower it for tiny models
+        self.spans = plan_buckets(graph.grad_ready_points(), 0, graph.total_elems, n_buckets, min_bucket)
+        self.side = torch.cuda.Stream(device=graph.master_flat.device, priority=-1)
+        self._next = 0
+        self._prepared = False
+        graph.grad_hook = self._on_grads_ready
+
+    @staticmethod
+    def usable(opt: Optimizer, graph) -> bool:
+        """Needs a CUDA graph whose gradients become final in buffer order, and no entries that a decaying update
+        must skip (the sliced update does not put batch-norm running statistics back)."""
+        if graph.master_flat is None or graph.master_flat.device.type != "cuda" or not graph.grad_hook_usable():
+            return False
+        if getattr(opt, "weight_decay", 0.0) != 0.0 and getattr(opt, "_frozen_idx", None) is not None:
+            return False
+        return graph.grad_hook is None
+
+    # ---- the optimizer's surface
+    def __getattr__(self, name):  # lr, hyper, state_dict, ... of the wrapped optimizer
+        return getattr(self.__dict__["opt"], name)
+
+    @property
+    def step_count(self):
+        return self.opt.step_count
+
+    @step_count.setter
+    def step_count(self, v):
+        self.opt.step_count = v
+
+    def prepare_step(self):
+        self.opt.prepare_step()
+        self._prepared = True
+
+    def _bucket(self, lo: int, hi: int):
+        self.opt.update(prepared=True, sl=slice(lo, hi))
+        self.graph.grads_flat[lo:hi].zero_()
+
+    def _on_grads_ready(self, floor: int):
+        """``Graph.grad_hook``: every gradient at a flat offset >= ``floor`` is final."""
+        if not self.graph.training:
+            return
+        upto = self._next
+        while upto < len(self.spans) - 1 and self.spans[upto][0] >= floor:  # the last bucket goes with update()
+            upto += 1
+        if upto == self._next:
+            return
+        if not self._prepared:
+            self.prepare_step()
+        main = torch.cuda.current_stream()
+        ev = torch.cuda.Event()
+        ev.record(main)
+        self.side.wait_event(ev)
+        with torch.cuda.stream(self.side):
+            while self._next < upto:
+                self._bucket(*self.spans[self._next])
+                self._next += 1
+
+    def update(self, prepared: bool = False):
+        if prepared:
+            self._prepared = True
+        if not self._prepared:
+            self.prepare_step()
+        while self._next < len(self.spans):  # what backward did not release early, at least the last bucket
+            self._bucket(*self.spans[self._next])
+            self._next += 1
+        ev = torch.cuda.Event()
+        ev.record(self.side)
+        torch.cuda.current_stream().wait_event(ev)
+        self._next = 0
+        self._prepared = False
 
 
 def create_optimizer(cfg: Optional[dict]) -> Optimizer:

@@ -22,7 +22,7 @@ from typing import List, Optional, Sequence
 import torch
 import torch.distributed as dist
 
-from ..nn.optim import SGD, Adam, Optimizer
+from ..nn.optim import SGD, Adam, Optimizer, plan_buckets  # noqa: F401 (re-exported: tests and callers import it from here)
 from ..ops import _lib
 from ..ops.gemm import LAUNCHES
 from .symm import SymmetricHeap, ptr_array
@@ -40,21 +40,6 @@ def _declare(lib):
     vp, ll, f, i, u = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_float, ctypes.c_int, ctypes.c_uint
     lib.tnnb_dp_step.argtypes = [i, i, vp, vp, vp, vp, vp, vp, vp, ll, ll, i, f, f, f, f, f, f, f, f, f, vp, u, vp, vp, vp, vp, vp]
     lib.tnnb_dp_step.restype = i
-
-
-def plan_buckets(points: Sequence[int], lo: int, hi: int, n_buckets: int, min_bucket: int) -> List[tuple]:
-    """Cut ``[lo, hi)`` into buckets ``(lo_i, hi_i)`` in the order backward finishes them (highest offsets first).
-    ``points`` are the offsets ``Graph.grad_hook`` reports, in firing order; a bucket ends at such a point and holds
-    at least ``max(min_bucket, (hi - lo) / n_buckets)`` elements (the last one takes what is left)."""
-    target = max(min_bucket, (hi - lo) // max(1, n_buckets))
-    out, top = [], hi
-    for pt in points:
-        pt = pt // 8 * 8
-        if lo < pt < top and top - pt >= target:
-            out.append((pt, top))
-            top = pt
-    out.append((lo, top))
-    return out
 
 
 class FusedDPOptimizer:

@@ -69,6 +69,17 @@ class Trainer:
             self.logger = CsvLogger(lm.get("log_dir", "logs"), cfg.model_name, lm.get("log_batch", True),
                                     lm.get("log_val", True), lm.get("log_epoch", True))
         self.accum = max(1, int(cfg.gradient_accumulation_steps))
+        # One GPU, one backward pass per step: run the update bucket by bucket on a second stream while backward is
+        # still going (nn/optim.py OverlappedUpdate). TNNB_OVERLAP_UPDATE=0 keeps the single update after backward.
+        if (optimizer is None and self.accum == 1 and getattr(cfg, "overlap_update", True)
+                and os.environ.get("TNNB_OVERLAP_UPDATE", "1") != "0" and isinstance(self.optimizer, Optimizer)):
+            from .nn.optim import OverlappedUpdate
+            if OverlappedUpdate.usable(self.optimizer, self.graph):
+                ov = OverlappedUpdate(self.optimizer, self.graph)
+                if len(ov.spans) > 1:
+                    self.optimizer = ov
+                else:
+                    self.graph.grad_hook = None
         self.global_step = 0
         self.micro_step = 0
         self.is_lm = self._is_language_model()
@@ -149,7 +160,8 @@ class Trainer:
         self.micro_step += 1
         if self.micro_step % self.accum == 0:
             self.optimizer.update()
-            g.zero_grads()
+            if not getattr(self.optimizer, "clears_grads", False):
+                g.zero_grads()
             self.scheduler.step()
             self.global_step += 1
             self.step_counter.add_(1)
@@ -199,7 +211,8 @@ class Trainer:
         d, l = self._to_device(self._d_data, self._d_labels)
         loss = self._fwd_bwd(d, l, 1.0)
         self.optimizer.update(prepared=True)
-        self.graph.zero_grads()
+        if not getattr(self.optimizer, "clears_grads", False):
+            self.graph.zero_grads()
         self.step_counter.add_(1)
         return loss
 
