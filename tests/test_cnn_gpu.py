@@ -102,38 +102,48 @@ def test_batchnorm_with_closing_residual_add(shape):
           raw.batchnorm_infer(x, g, b, rm, rv, 1e-5, False, resid=res), what="infer")
 
 
-def test_residual_block_with_fused_closing_add_matches_cpu():
+def test_residual_block_with_fused_closing_add():
+    """A bottleneck-style block (main path ending in a batch norm without ReLU): the closing add + ReLU done inside
+    that batch norm gives the same output, input gradient and parameter gradients as the separate add kernel (both in
+    bf16 on the GPU), and the output agrees with the fp32 CPU path."""
     from tnn_b200.nn import layers as L
     from tnn_b200.nn.blocks import ResidualBlock, Sequential
     from tnn_b200.nn.graph import Graph
 
-    def build():
+    def build(fused=True, shortcut=False):
         g = Graph()
         main = Sequential([L.Conv2D(64, 64, 3, 3, 1, 1, 1, 1, name="c1"), L.BatchNorm(64, use_relu=True, name="b1"),
-                           L.Conv2D(64, 64, 1, 1, 1, 1, 0, 0, name="c2"), L.BatchNorm(64, name="b2")], name="main")
-        out = ResidualBlock(main, None, "relu", name="block")(g.input("input"))
+                           L.Conv2D(64, 128 if shortcut else 64, 1, 1, 1, 1, 0, 0, name="c2"),
+                           L.BatchNorm(128 if shortcut else 64, name="b2")], name="main")
+        sc = Sequential([L.Conv2D(64, 128, 1, 1, 1, 1, 0, 0, name="sc"), L.BatchNorm(128, name="sb")], name="short") if shortcut else None
+        blk = ResidualBlock(main, sc, "relu", name="block")
+        if not fused:
+            blk._closing_add_in_batchnorm = lambda x: False
+        out = blk(g.input("input"))
         out.set_uid("output")
         g.set_output(out)
         g.input_requires_grad = True
         return g
 
     torch.manual_seed(3)
-    cpu = build().compile(device="cpu", seed=0)
-    gpu = build().compile(device="cuda", seed=0)
-    for lc, lg in zip(cpu.layers(), gpu.layers()):  # bf16-rounded weights on both sides (slab layouts differ by dtype)
-        for pc, pg in zip(lc.params, lg.params):
-            pc.copy_(pg.float().cpu())
-    x, dy = rnd(4, 12, 12, 64), rnd(4, 12, 12, 64)
-    yc = cpu.forward({"input": x.float()})["output"]
-    yg = gpu.forward({"input": x.cuda()})["output"]
-    close(yg, yc, what="block output")
-    dc = cpu.backward({"output": dy.float()})["input"]
-    dg = gpu.backward({"output": dy.cuda()})["input"]
-    _lib.check_status()
-    close(dg, dc, tol=5e-2, what="block input gradient")
-    ga = torch.cat([g.reshape(-1).float() for l in cpu.layers() for g in l.grads if g is not None])
-    gb = torch.cat([g.reshape(-1).float().cpu() for l in gpu.layers() for g in l.grads if g is not None])
-    close(gb, ga, tol=5e-2, what="parameter gradients")
+    x, dy = rnd(8, 12, 12, 64), rnd(8, 12, 12, 64)
+    for shortcut in (False, True):
+        dyy = torch.cat([dy, dy], -1) if shortcut else dy
+        a = build(True, shortcut).compile(device="cuda", seed=0)
+        b = build(False, shortcut).compile(device="cuda", seed=0)
+        assert torch.equal(a.master_flat, b.master_flat)
+        ya, yb = a.forward({"input": x.cuda()})["output"], b.forward({"input": x.cuda()})["output"]
+        close(ya, yb, tol=1e-3, what="output, fused vs separate add")
+        da, db = a.backward({"output": dyy.cuda()})["input"], b.backward({"output": dyy.cuda()})["input"]
+        _lib.check_status()
+        close(da, db, tol=5e-3, what="input gradient")
+        close(a.grads_flat, b.grads_flat, tol=5e-3, what="parameter gradients")
+        if not shortcut:
+            cpu = build(True).compile(device="cpu", seed=0)
+            for lc, lg in zip(cpu.layers(), a.layers()):  # bf16-rounded weights on both sides
+                for pc, pg in zip(lc.params, lg.params):
+                    pc.copy_(pg.float().cpu())
+            close(ya, cpu.forward({"input": x.float()})["output"], tol=4e-2, what="output vs fp32 CPU")
 
 
 @pytest.mark.parametrize("mode", ["max", "avg"])

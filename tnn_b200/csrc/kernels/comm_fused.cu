@@ -31,6 +31,8 @@
 // Every cross-rank wait is a bounded spin (about 2 s) that records
 // ST_TIMEOUT_PEER in the status word and lets the kernel finish.
 #include "gemm_tcgen05.h"
+#include <cstdlib>
+
 #include "ptx.cuh"
 
 namespace tnnb {
@@ -847,8 +849,19 @@ int tnnb_dp_step(int dp, int dp_rank, void** barrier_flags, void** grads, void**
   p.lr = lr; p.b1 = b1; p.b2 = b2; p.eps = eps; p.wd = wd; p.bc1 = bc1; p.bc2 = bc2; p.gscale = gscale; p.momentum = momentum;
   p.hyper = (const float*)hyper; p.epoch = epoch; p.epoch_ptr = (const uint32_t*)epoch_ptr;
   p.go_flag = (uint32_t*)go_flag; p.done_count = (uint32_t*)done_count; p.status = status;
-  const int grid = sm_count();  // one resident CTA per SM: block 0 must be able to run for the others to proceed
-  dp_step_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(p);
+  // Small blocks: 192 threads x 50 registers leave room beside a resident GEMM CTA (320 threads x 168 registers), so a
+  // bucket launched on the second stream really runs under the backward pass instead of waiting for a free SM between
+  // two GEMM kernels; with 512-thread blocks it could not. Four blocks per SM keep the standalone rate. Block 0 is
+  // dispatched first, and it is the one that releases the others, so blocks beyond the resident set cannot starve it.
+  // TNNB_DP_THREADS selects another block size for measurements.
+  static int threads = 0;
+  if (threads == 0) {
+    const char* e = getenv("TNNB_DP_THREADS");
+    const int t = e ? atoi(e) : 192;
+    threads = (t >= 64 && t <= 512 && t % 32 == 0) ? t : 192;
+  }
+  const int grid = sm_count() * (threads <= 256 ? 4 : 1);
+  dp_step_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>(p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
 }
