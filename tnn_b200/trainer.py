@@ -69,10 +69,11 @@ class Trainer:
             self.logger = CsvLogger(lm.get("log_dir", "logs"), cfg.model_name, lm.get("log_batch", True),
                                     lm.get("log_val", True), lm.get("log_epoch", True))
         self.accum = max(1, int(cfg.gradient_accumulation_steps))
-        # One GPU, one backward pass per step: run the update bucket by bucket on a second stream while backward is
-        # still going (nn/optim.py OverlappedUpdate). TNNB_OVERLAP_UPDATE=0 keeps the single update after backward.
-        if (optimizer is None and self.accum == 1 and getattr(cfg, "overlap_update", True)
-                and os.environ.get("TNNB_OVERLAP_UPDATE", "1") != "0" and isinstance(self.optimizer, Optimizer)):
+        # One GPU, one backward pass per step: optionally run the update bucket by bucket on a second stream while
+        # backward is still going (nn/optim.py OverlappedUpdate; `overlap_update` in the config or TNNB_OVERLAP_UPDATE=1).
+        # Off by default: on GPT-2 small it measured the same step time as one update after backward (11.93 ms both).
+        want = os.environ.get("TNNB_OVERLAP_UPDATE", "1" if getattr(cfg, "overlap_update", False) else "0") == "1"
+        if optimizer is None and self.accum == 1 and want and isinstance(self.optimizer, Optimizer):
             from .nn.optim import OverlappedUpdate
             if OverlappedUpdate.usable(self.optimizer, self.graph):
                 ov = OverlappedUpdate(self.optimizer, self.graph)

@@ -59,7 +59,7 @@ class TrainingConfig:
     snapshot_dir: str = "model_snapshots"
     seed: int = 0
     cuda_graph: bool = False
-    overlap_update: bool = True       # single GPU: optimizer buckets run on a second stream while backward continues
+    overlap_update: bool = False      # single GPU: optimizer buckets run on a second stream while backward continues
     # distributed (coordinator/worker) keys of configs/tcp_config.json; kept for compatibility
     host: str = "127.0.0.1"
     port: int = 9000
