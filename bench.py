@@ -178,9 +178,15 @@ def run_ours(args):
         e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e2.record()
         last = 0.0
-        for _ in range(args.steps):
-            data, labels = next(batches)
+        # every step's batch goes host -> device from pinned memory inside the timed region; the copy of step k+1 is
+        # started (Trainer.prefetch, copy stream) right after step k has been launched, so it overlaps step k's compute
+        nxt = next(batches)
+        for i in range(args.steps):
+            data, labels = nxt
             loss = trainer.train_step(data, labels)
+            if i + 1 < args.steps:
+                nxt = next(batches)
+                trainer.prefetch(*nxt)
             last = float(loss.item())
         e3.record()
         barrier()

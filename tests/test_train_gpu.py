@@ -101,3 +101,34 @@ def test_overlapped_update_equals_update_after_backward(graphed, monkeypatch):
     assert na == nb
     assert abs(la - lb) < 2e-2
     assert float((wa - wb).norm() / wb.norm()) < 2e-3
+
+
+@pytest.mark.parametrize("graphed", [False, True])
+def test_prefetched_batches_give_the_same_training(graphed):
+    """Trainer.prefetch uploads the next batch on a copy stream while the current step runs; the losses must be
+    those of plain train_step calls on the same batches, eagerly and under CUDA-graph replay."""
+    def run(prefetch):
+        torch.manual_seed(11)
+        g = tiny(0.0).compile(device="cuda", seed=3)
+        cfg = TrainingConfig.from_dict({"model_name": "t", "batch_size": 4, "optimizer": {"type": "adamw", "learning_rate": 1e-3}})
+        t = Trainer(cfg, graph=g, log=False)
+        gen = torch.Generator().manual_seed(2)
+        batches = []
+        for _ in range(8):
+            seq = torch.randint(0, 203, (4, 129), generator=gen)
+            batches.append((seq[:, :-1].contiguous().pin_memory(), seq[:, 1:].contiguous().pin_memory()))
+        if graphed:
+            t.enable_cuda_graph(*batches[0])
+        losses = []
+        for i, (d, l) in enumerate(batches):
+            loss = t.train_step(d, l)
+            if prefetch and i + 1 < len(batches):
+                t.prefetch(*batches[i + 1])
+            losses.append(float(loss.item()))
+        _lib.check_status()
+        t.close()
+        return losses
+
+    a, b = run(True), run(False)
+    assert len(a) == 8 and max(abs(x - y) for x, y in zip(a, b)) < 2e-2, (a, b)
+    assert abs(a[0] - a[-1]) > 1e-3  # different batches and updates: the losses move

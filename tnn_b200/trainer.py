@@ -89,6 +89,9 @@ class Trainer:
         if self.device.type == "cuda":
             raw.SEED_OFF["tensor"] = self.step_counter
         self._graphed = None
+        self._pf = None            # (data, labels, device copies, ready event) of a batch uploaded ahead of its step
+        self._pf_stream = None
+        self._pf_free = None       # recorded once the staging copies have been consumed
         self._print_memory_once = bool(getattr(cfg, "print_layer_memory_usage", False))
         self.launches_per_step = 0
         # per-layer timing (profiler_type NORMAL: last step, CUMULATIVE: summed over steps)
@@ -131,7 +134,12 @@ class Trainer:
         Returns the mean loss of the batch as a 1-element device tensor (no synchronisation)."""
         if self._graphed is not None:
             return self._graphed_step(data, labels)
-        d, l = self._to_device(data, labels)
+        src = self._take_prefetched(data, labels) if self.device.type == "cuda" else None
+        if src is not None:  # the step owns its inputs: the staging copies are overwritten by the next prefetch
+            d, l = self._to_device(src[0].clone(), src[1].clone())
+            self._release_prefetched()
+        else:
+            d, l = self._to_device(data, labels)
         self._resident = (d, l)
         return self._step_on_device(d, l)
 
@@ -217,9 +225,52 @@ class Trainer:
         self.step_counter.add_(1)
         return loss
 
+    def prefetch(self, data: torch.Tensor, labels: torch.Tensor) -> None:
+        """Start the host-to-device copy of the NEXT batch on a copy stream, to run while the current step computes;
+        ``train_step`` called later with the same two tensors then takes the device copies (one device-to-device copy
+        into the step's inputs) instead of waiting for PCIe. With 77 MB of bf16 images per ResNet-50 step the upload
+        is 1.4 ms that would otherwise sit in front of every step."""
+        if self.device.type != "cuda":
+            return
+        if self._pf_stream is None:
+            self._pf_stream = torch.cuda.Stream(device=self.device)
+        old = self._pf
+        if old is not None and old[2].shape == data.shape and old[2].dtype == data.dtype and old[3].shape == labels.shape \
+                and old[3].dtype == labels.dtype:
+            sd, sl = old[2], old[3]
+        else:
+            sd = torch.empty(data.shape, dtype=data.dtype, device=self.device)
+            sl = torch.empty(labels.shape, dtype=labels.dtype, device=self.device)
+        if self._pf_free is not None:
+            self._pf_stream.wait_event(self._pf_free)  # the previous contents have been read by their step
+        with torch.cuda.stream(self._pf_stream):
+            sd.copy_(data, non_blocking=True)
+            sl.copy_(labels, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        self._pf = (data, labels, sd, sl, ev)
+
+    def _take_prefetched(self, data, labels):
+        """Device copies of this batch if ``prefetch`` uploaded it, else None. Orders the current stream after the copy."""
+        pf = self._pf
+        if pf is None or pf[0] is not data or pf[1] is not labels:
+            return None
+        torch.cuda.current_stream().wait_event(pf[4])
+        return pf[2], pf[3]
+
+    def _release_prefetched(self):
+        self._pf_free = torch.cuda.Event()
+        self._pf_free.record()
+
     def _graphed_step(self, data, labels):
-        self._d_data.copy_(data, non_blocking=True)
-        self._d_labels.copy_(labels, non_blocking=True)
+        src = self._take_prefetched(data, labels)
+        if src is not None:
+            self._d_data.copy_(src[0], non_blocking=True)
+            self._d_labels.copy_(src[1], non_blocking=True)
+            self._release_prefetched()
+        else:
+            self._d_data.copy_(data, non_blocking=True)
+            self._d_labels.copy_(labels, non_blocking=True)
         self.optimizer.prepare_step()
         self._graphed.replay()
         self.scheduler.step()
@@ -290,16 +341,25 @@ class Trainer:
 
         last = {}
         it = iter(self.train_loader)
+
+        def fetch():
+            nonlocal it
+            while True:
+                try:
+                    return next(it)
+                except StopIteration:
+                    it = iter(self.train_loader)
+
+        nxt = fetch()
         while self.global_step < cfg.max_steps:
-            try:
-                data, labels = next(it)
-            except StopIteration:
-                it = iter(self.train_loader)
-                continue
+            data, labels = nxt
             t0 = time.perf_counter()
             if cfg.cuda_graph and self._graphed is None and self.device.type == "cuda" and self.accum == 1:
                 self.enable_cuda_graph(data, labels)
             loss_t = self.train_step(data, labels)
+            if self.global_step < cfg.max_steps:
+                nxt = fetch()
+                self.prefetch(*nxt)  # uploaded while the step just launched is computing
             self._last_rows = labels.numel()
             want = self.logger is not None or (self.global_step % max(1, cfg.progress_print_interval) == 0)
             if want:
