@@ -173,6 +173,16 @@ def test_coordinator_worker_protocol_equals_single_graph(tmp_path):
     assert all("lr 0.1" in t for t in lrs)
     prof = co.merged_profile()
     assert len(prof) > 10 and any("FORWARD_JOB" in line and "Source: stage1" in line for line in prof.log_lines())
+    # forward-only validation through the stages equals the unpartitioned graph in evaluation mode
+    vseq = torch.randint(0, 29, (4, 17), generator=gen)
+    vd, vl = vseq[:, :-1].contiguous(), vseq[:, 1:].contiguous()
+    ev = co.evaluate([(vd, vl)])
+    ref.set_training(False)
+    vout = ref.forward({"input": vd})["output"]
+    vloss, _ = loss_fn.compute(vout, vl, 1.0, False)
+    ref.set_training(True)
+    assert ev["batches"] == 1 and abs(ev["loss"] - float(vloss)) < 1e-4
+    assert abs(ev["accuracy_pct"] - 100.0 * float((vout.argmax(-1) == vl).sum()) / vl.numel()) < 1e-6
     # weights read back over the protocol equal the saved ones; pushed weights replace them; status and log commands answer
     from tnn_b200.io import tnng as _tnng
     from tnn_b200.parallel.stage_worker import job_message

@@ -144,7 +144,7 @@ def cmd_tcp_coordinator(a) -> int:
     graph = zoo.create(cfg.model_name)
     co = tcp_coordinator(graph, ratios, endpoints, cfg.optimizer, cfg.scheduler, cfg.loss, cfg.num_microbatches,
                          cfg.host, cfg.port, cfg.skts_per_endpoint, cfg.max_packet_size)
-    train, _ = create_loaders(cfg.dataset_name, cfg.dataset_path, cfg.batch_size, cfg.seed,
+    train, val = create_loaders(cfg.dataset_name, cfg.dataset_path, cfg.batch_size, cfg.seed,
                               cfg.prefetch_depth if cfg.prefetch_data else 0, cfg.model_name)
     co.broadcast("TRAIN_MODE", expect="MODE_CHANGED")
     steps = cfg.max_steps if cfg.max_steps and cfg.max_steps > 0 else cfg.epochs * train.batches_per_epoch()
@@ -160,6 +160,9 @@ def cmd_tcp_coordinator(a) -> int:
         done += 1
         if done % max(1, cfg.progress_print_interval) == 0 or done == steps:
             print(f"step {done}/{steps} loss {loss:.4f} ({(time.perf_counter() - t0) / done * 1e3:.1f} ms/step)", flush=True)
+    val_res = co.evaluate(val, max_batches=a.val_batches) if a.val_batches else {}
+    if val_res:
+        print(f"validation: loss {val_res['loss']:.4f} accuracy {val_res['accuracy_pct']:.2f} % over {val_res['batches']} batches", flush=True)
     if cfg.snapshot_dir:
         os.makedirs(cfg.snapshot_dir, exist_ok=True)
         from .parallel.stage_worker import simple_message
@@ -171,7 +174,8 @@ def cmd_tcp_coordinator(a) -> int:
     co.transport.close()
     if local is not None:
         local.join(timeout=30)
-    print(json.dumps({"steps": done, "final_loss": loss, "seconds": round(time.perf_counter() - t0, 3), **stats}))
+    print(json.dumps({"steps": done, "final_loss": loss, "seconds": round(time.perf_counter() - t0, 3),
+                      **{"val_" + k: v for k, v in val_res.items()}, **stats}))
     return 0
 
 
@@ -220,6 +224,7 @@ def main(argv=None) -> int:
     p.add_argument("--max-packet", type=int, default=4 << 20)
     p = sub.add_parser("tcp-coordinator", help="partition a model and train it on TCP workers (keys of the reference's tcp_config.json)")
     p.add_argument("--config", "-c", required=True)
+    p.add_argument("--val-batches", type=int, default=4, help="validation batches after training (0 = none)")
     sub.add_parser("info", help="build and device information")
     a = ap.parse_args(argv)
     return {"train": cmd_train, "infer": cmd_infer, "generate": cmd_generate, "info": cmd_info,

@@ -326,6 +326,38 @@ class LocalCoordinator:
         self.broadcast("UPDATE_PARAMETERS", expect="PARAMETERS_UPDATED")
         return total
 
+    def val_batch(self, data: torch.Tensor, labels: torch.Tensor) -> Tuple[float, int]:
+        """Forward-only pass of one batch through the stages, micro-batch by micro-batch; returns the mean loss and
+        the number of correct arg-max predictions (reference: coordinator async_val_batch / sync_val_batch,
+        distributed/train.hpp:153-199). The workers must be in evaluation mode (:meth:`evaluate` switches them)."""
+        mb_data, mb_labels = data.chunk(self.micro), labels.chunk(self.micro)
+        for pid, d in enumerate(mb_data):
+            self.post(self.names[0], job_message("FORWARD_JOB", pid, {self.in_uid: d}))
+        outs = {m["job"]["pid"]: m for m in self.run(len(mb_data)) if m["command_name"] == "FORWARD_JOB"}
+        total, correct = 0.0, 0
+        for pid, lab in enumerate(mb_labels):
+            logits = tnng.record_to_tensor(dict(outs[pid]["job"]["tensors"])[self.out_uid])
+            loss, _ = self.loss.compute(logits, lab, 1.0, False)
+            total += float(loss) / len(mb_data)
+            c = self.loss.corrects()
+            correct += int(c) if c is not None else 0
+        return total, correct
+
+    def evaluate(self, loader, max_batches: Optional[int] = None) -> Dict[str, float]:
+        """Validation over a loader: EVAL_MODE on every stage, forward-only batches, TRAIN_MODE again."""
+        self.broadcast("EVAL_MODE", expect="MODE_CHANGED")
+        tot, corr, rows, n = 0.0, 0, 0, 0
+        try:
+            for data, labels in loader:
+                l, c = self.val_batch(data, labels)
+                tot, corr, rows, n = tot + l, corr + c, rows + labels.numel(), n + 1
+                if max_batches and n >= max_batches:
+                    break
+        finally:
+            self.broadcast("TRAIN_MODE", expect="MODE_CHANGED")
+        mean = tot / max(1, n)
+        return {"loss": mean, "accuracy_pct": 100.0 * corr / max(1, rows), "batches": n}
+
     def merged_profile(self) -> H.Profiler:
         merged = H.Profiler()
         first = True
