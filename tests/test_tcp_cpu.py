@@ -76,7 +76,8 @@ def test_pipeline_over_tcp_matches_single_process(tmp_path):
     from tnn_b200.parallel.stage_worker import simple_message
     from tnn_b200.parallel.tcp_transport import tcp_coordinator
 
-    procs = [_spawn("worker", "--idle-timeout", "120") for _ in range(2)]
+    logs = [str(tmp_path / f"worker{i}.csv") for i in range(2)]
+    procs = [_spawn("worker", "--idle-timeout", "120", "--log", logs[i]) for i in range(2)]
     co = None
     try:
         mk = lambda: zoo.gpt2(32, 1, 2, "t", seq_len=16, vocab=29, drop=0.0)
@@ -120,6 +121,12 @@ def test_pipeline_over_tcp_matches_single_process(tmp_path):
         co = None
         for p, _ in procs:
             assert p.wait(timeout=60) == 0, p.stdout.read()
+        for f in logs:  # the worker's own event log: header, then one row per handled message
+            rows = open(f).read().strip().split("\n")
+            assert rows[0] == "step,event_type,time_ms,mem"
+            kinds = [r.split(",")[1] for r in rows[1:]]
+            assert kinds[0] == "CONFIG_TRANSFER" and kinds.count("FORWARD_JOB") == 6 and kinds.count("UPDATE_PARAMETERS") == 3
+            assert rows[-1].split(",")[0] == "3" and kinds[-1] == "SHUTDOWN"
     finally:
         if co is not None:
             co.transport.close()

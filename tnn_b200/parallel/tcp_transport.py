@@ -16,6 +16,7 @@ reader / writer threads that run while the interpreter computes).
 """
 from __future__ import annotations
 
+import time
 from typing import Optional, Sequence, Tuple
 
 from ..host import H
@@ -69,11 +70,18 @@ class TcpStageServer:
     sends ``CONFIG_TRANSFER``; the neighbours' endpoints arrive inside that message."""
 
     def __init__(self, host: str = "127.0.0.1", port: int = 0, device: str = "cpu", sockets_per_endpoint: int = 4,
-                 max_packet_size: int = 4 << 20):
+                 max_packet_size: int = 4 << 20, log_path: str = ""):
         self.transport = TcpTransport(host, port, sockets_per_endpoint, max_packet_size)
         self.name = self.transport.name
         self.worker = StageWorker(self.name, device)
         self.coordinator: Optional[str] = None
+        # per-event log of this worker: step (number of updates so far), command, handling time, device memory in use
+        # (the reference's worker CSV: step,event_type,time_ms,mem - include/nn/csv_logger.hpp:76-99)
+        self.log = None
+        if log_path:
+            from ..utils.csv_logger import WorkerCsvLogger
+            self.log = WorkerCsvLogger(log_path)
+        self._updates = 0
 
     def serve(self, idle_timeout_s: float = -1.0) -> int:
         """Handles messages until ``SHUTDOWN`` (or until nothing arrived for ``idle_timeout_s``); returns how many."""
@@ -87,7 +95,17 @@ class TcpStageServer:
                 sender, data = item
                 if int.from_bytes(data[:2], "little") == config_transfer:  # a message opens with its u16 command
                     self.coordinator = sender
-                for dst, reply in self.worker.handle(data):
+                t0 = time.perf_counter()
+                replies = self.worker.handle(data)
+                if self.log is not None:
+                    cmd = H.command_name(int.from_bytes(data[:2], "little"))
+                    self._updates += cmd == "UPDATE_PARAMETERS"
+                    mem = 0
+                    if self.worker.device != "cpu":
+                        import torch
+                        mem = int(torch.cuda.memory_allocated())
+                    self.log.log(self._updates, cmd, round((time.perf_counter() - t0) * 1e3, 3), mem)
+                for dst, reply in replies:
                     target = self.coordinator if dst == COORDINATOR else dst
                     if target is None:
                         raise RuntimeError("a reply for the coordinator before any CONFIG_TRANSFER named one")
@@ -103,6 +121,8 @@ class TcpStageServer:
                 n += 1
         finally:
             self.transport.close()
+            if self.log is not None:
+                self.log.close()
         return n
 
 
@@ -131,8 +151,6 @@ def _canonical(endpoint: str) -> str:
 def ping_pong(transport: TcpTransport, peer: str, message_bytes: int, seconds: float) -> dict:
     """Bandwidth of round trips of one ``message_bytes`` message with an echoing peer (the reference's
     benchmarks/tcp_communicator_benchmark.cpp:132-223 sends 128 MiB tensors for 10 s and prints MB/s)."""
-    import time
-
     payload = bytes(message_bytes)
     t0 = time.perf_counter()
     n = 0
@@ -171,9 +189,10 @@ def main(argv=None) -> int:
     ap.add_argument("--sockets", type=int, default=4)
     ap.add_argument("--max-packet", type=int, default=4 << 20)
     ap.add_argument("--idle-timeout", type=float, default=-1.0, help="worker: give up after this many idle seconds")
+    ap.add_argument("--log", default="", help="worker: CSV file for its per-message log (step,event_type,time_ms,mem)")
     a = ap.parse_args(argv)
     if a.role == "worker":
-        srv = TcpStageServer(a.host, a.port, a.device, a.sockets, a.max_packet)
+        srv = TcpStageServer(a.host, a.port, a.device, a.sockets, a.max_packet, a.log)
         print("listening", srv.name, flush=True)
         n = srv.serve(a.idle_timeout)
         print(f"{srv.name}: handled {n} messages", flush=True)
