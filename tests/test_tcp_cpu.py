@@ -165,3 +165,24 @@ def test_coordinator_notices_a_dead_worker():
         for p, _ in procs:
             if p.poll() is None:
                 p.kill()
+
+
+def test_workers_stop_when_the_coordinator_disappears():
+    """No SHUTDOWN is ever sent: the coordinator's sockets just close; workers that wait without an idle limit
+    notice it and exit instead of serving nobody for ever."""
+    from tnn_b200.models import zoo
+    from tnn_b200.parallel.tcp_transport import tcp_coordinator
+
+    procs = [_spawn("worker") for _ in range(2)]
+    try:
+        co = tcp_coordinator(zoo.gpt2(32, 1, 2, "t", seq_len=16, vocab=29, drop=0.0), [1.0, 1.0], [e for _, e in procs],
+                             {"type": "sgd", "learning_rate": 0.1}, microbatches=2)
+        co.broadcast("TRAIN_MODE", expect="MODE_CHANGED")
+        co.transport.close()
+        for p, _ in procs:
+            assert p.wait(timeout=30) == 0
+            assert "coordinator" in p.stdout.read()
+    finally:
+        for p, _ in procs:
+            if p.poll() is None:
+                p.kill()

@@ -89,9 +89,17 @@ class TcpStageServer:
         config_transfer = H.command_code("CONFIG_TRANSFER")
         try:
             while self.worker.alive:
-                item = self.transport.recv(idle_timeout_s)
-                if item is None:
-                    break
+                if idle_timeout_s >= 0:
+                    item = self.transport.recv(idle_timeout_s)
+                    if item is None:
+                        break
+                else:  # wait for ever, but not for a coordinator whose connection is gone
+                    item = self.transport.recv(1.0)
+                    if item is None:
+                        if self.coordinator is not None and self.transport.lost([self.coordinator]):
+                            print(f"{self.name}: the coordinator {self.coordinator} is gone, stopping", flush=True)
+                            break
+                        continue
                 sender, data = item
                 if int.from_bytes(data[:2], "little") == config_transfer:  # a message opens with its u16 command
                     self.coordinator = sender
