@@ -3,12 +3,15 @@
     train     --config x.json [--layout dp8|tp2dp4|pp2 ...]   single device, or one rank of a torchrun job
     infer     --config x.json                                  validation loss / accuracy of model_path or a fresh model
     generate  --model gpt2_small|--model-path f.tnng --vocab vocab.bin [--tokens train.bin]
+    tcp-worker      [port] [--host H] [--gpu]                  one pipeline stage served over TCP
+    tcp-coordinator --config x.json                            partition a model, deploy it to TCP workers, train
     info                                                       devices, build status, registered models and layers
 
 These are the counterparts of the reference's ``trainer``, ``inferencer`` and ``gpt2_inference`` binaries
-(examples/trainer.cpp:15-85, examples/inferencer.cpp:12-70, examples/gpt2_inference.cpp:16-114); its
-``tcp_coordinator`` / ``tcp_worker`` pair is replaced by launching ``train`` under ``torchrun`` with a
-``--layout`` (one process per GPU, no coordinator process).
+(examples/trainer.cpp:15-85, examples/inferencer.cpp:12-70, examples/gpt2_inference.cpp:16-114) and of its
+``tcp_coordinator`` / ``tcp_worker`` pair (examples/tcp_coordinator.cpp:27-128, examples/tcp_worker.cpp:39-141).
+Inside one NVSwitch box the parallel path is ``train`` under ``torchrun`` with a ``--layout`` (one process per GPU,
+no coordinator process); the TCP pair is for stages on other hosts.
 """
 from __future__ import annotations
 
