@@ -1,0 +1,3 @@
+// Stand-in for <tbb/blocked_range.h>: see tbb_min.h.
+#pragma once
+#include "tbb_min.h"

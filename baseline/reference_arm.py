@@ -1,22 +1,25 @@
 """``bench.py --impl reference``: time the reference's own code on the same metric and configuration.
 
-What "the reference" can mean on this machine (recorded in DESIGN.md):
+Two forms of "the reference" can run here, tried in this order:
 
-* Its C++/CUDA/cuDNN engine (``trainer --config``) cannot be built offline: CMake fetches asio,
-  nlohmann_json, googletest, stb, spdlog and cudnn-frontend from the network at configure time and
-  requires libibverbs and TBB, none of which exist here. ``pip install /root/reference`` installs
-  only the metadata of its documentation helper package (no importable code).
-* Its PyTorch trainer ``torch/torch_trainer.py`` is runnable. This arm imports that file
-  UNMODIFIED from ``baseline/_ref/tunx_torch`` and uses its own model class
-  (``GPT2Small`` / ``ResNet50ImageNet100``), its own model registry entry (batch size, optimizer type,
-  learning rate), the optimizer construction of its ``main`` and its own ``train_epoch`` loop, fed
-  by its own ``OpenWebTextDataset`` reading a synthetic ``train.bin`` of uniform random token ids
-  (or by a synthetic image iterable for ResNet-50). None of this repository's models, kernels or
-  engine are on that path. ``torch.compile(max-autotune)``, which the script's ``main`` also applies,
-  is off by default because its autotuning alone takes longer than the whole benchmark;
-  ``TNNB_REF_COMPILE=1`` turns it on.
+1. Its C++/CUDA/cuDNN engine through the stock ``trainer --config`` binary, built from the reference sources by
+   ``build_reference_engine.py`` (see ``reference_engine_arm.py``). The build of the UNMODIFIED sources starts,
+   builds the graph and then dies with SIGSEGV in the first forward pass of every model that contains a block
+   (``flash_gpt2_small``, the ResNets): ``Graph::compile`` gives the engine object to the top-level layers only
+   and ``Block`` does not forward it, so ``DenseLayerImpl::forward_impl`` inside ``FlashAttentionBlockImpl``
+   calls through a null engine. It is therefore not attempted by default; ``TNNB_REF_ARM=engine`` attempts it,
+   ``TNNB_REF_ARM=engine-fixed`` runs the build made with ``--fix-block-engine`` (two forwarding methods added
+   to one header at build time) and labels its line accordingly.
+2. (default) Its PyTorch trainer ``torch/torch_trainer.py``, imported UNMODIFIED from ``baseline/_ref/tunx_torch``: its
+   own model class (``GPT2Small`` / ``ResNet50ImageNet100``), model registry entry (batch size, optimizer
+   type, learning rate), the optimizer construction of its ``main``, ``torch.compile(mode="max-autotune")``
+   as its ``main`` applies it (compile time falls into the warm-up; eager only if compiling raises, or with
+   ``TNNB_REF_COMPILE=0``, and the line says which) and its own ``train_epoch`` loop, fed by its own
+   ``OpenWebTextDataset`` reading a synthetic ``train.bin`` of uniform random token ids (or by a synthetic
+   image iterable for ResNet-50).
 
-The reference trainer is single-GPU, so for N > 1 this arm reports ``unavailable``.
+None of this repository's models, kernels or engine are on either path. Both are single-GPU programs (the
+reference has no data- or tensor-parallel mode), so for N > 1 this arm reports ``unavailable``.
 """
 from __future__ import annotations
 
@@ -44,15 +47,45 @@ def run_reference(args):
             _unavailable("the reference trainer (C++ engine and torch/torch_trainer.py alike) is single-GPU; it has no data- or "
                          "tensor-parallel mode to run at N > 1")
         return
-    if not os.path.exists(os.path.join(REF_DIR, "torch_trainer.py")):
-        _unavailable("baseline/_ref/tunx_torch/torch_trainer.py is missing (copy /root/reference/torch there); the C++ engine "
-                     "cannot be built offline (network FetchContent, libibverbs, TBB)")
-        return
     import numpy as np
     import torch
 
     if not torch.cuda.is_available():
         _unavailable("no CUDA device")
+        return
+    engine_error = None
+    which = os.environ.get("TNNB_REF_ARM", "torch")
+    if args.model == "gpt2_small" and which in ("engine", "engine-fixed"):
+        from . import reference_engine_arm as eng
+
+        fixed = which == "engine-fixed"
+        if eng.available(fixed):
+            batch = args.per_gpu_batch or 8
+            warm, steps = max(3, args.warmup), args.steps
+            try:
+                r = eng.run_engine("gpt2_small", batch, warm, steps, dtype=os.environ.get("TNNB_REF_DTYPE", ""), fixed=fixed)
+                print(json.dumps({
+                    "impl": "reference", "metric": "tokens_per_sec", "value": r["value"], "unit": "tokens/s", "n_gpus": 1,
+                    "steps": steps, "warmup": warm, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+                    "vs_baseline": None, "dtype": r["dtype"], "data": "synthetic",
+                    "config": {"model": "gpt2_small", "global_batch": batch, "seq_len": 1024, "parallelism": "single", "path": r["path"]},
+                    "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": r["h2d_bytes_per_step"],
+                            "d2h_bytes_per_step": r["d2h_bytes_per_step"]},
+                    "loss_last": r["loss_last"], "run_ms": r["run_ms"],
+                    "note": "the timed loop is the reference trainer's own: it uploads each batch from host memory and reads the loss "
+                            "back every step, so value and e2e are the same measurement",
+                }), flush=True)
+                return
+            except Exception as e:  # fall through to the reference's PyTorch trainer, and say why
+                engine_error = f"{type(e).__name__}: {e}"[:500]
+        else:
+            engine_error = "the reference trainer binary is not present (python baseline/build_reference_engine.py --src <checkout>)"
+    elif args.model == "gpt2_small":
+        engine_error = ("not attempted: the build of the unmodified C++ engine dies with SIGSEGV in the first forward pass "
+                        "(null engine inside blocks, DenseLayerImpl::forward_impl); TNNB_REF_ARM=engine-fixed runs the patched build")
+    if not os.path.exists(os.path.join(REF_DIR, "torch_trainer.py")):
+        _unavailable("neither the built reference engine nor baseline/_ref/tunx_torch/torch_trainer.py (a copy of the reference's "
+                     "torch/ directory) is present" + (f"; engine: {engine_error}" if engine_error else ""))
         return
     sys.path.insert(0, REF_DIR)
     try:
@@ -101,8 +134,17 @@ def run_reference(args):
         items, metric, unit, name = 1, "images_per_sec", "images/s", "resnet50"
 
     model = cfg["model_cls"]().to(dev)
-    if os.environ.get("TNNB_REF_COMPILE") == "1":
-        model = torch.compile(model, mode="max-autotune")
+    compiled = "eager (TNNB_REF_COMPILE=0)"
+    if os.environ.get("TNNB_REF_COMPILE", "1") != "0":
+        eager_model = model
+        try:  # as the script's main() does; the first batches trigger the compilation, so check it here
+            model = torch.compile(model, mode="max-autotune")
+            xb = next(iter(torch.utils.data.DataLoader(ds, batch_size=batch)))[0].to(dev)
+            model(xb)
+            compiled = "torch.compile(mode='max-autotune')"
+        except Exception as e:
+            model = eager_model
+            compiled = f"eager (torch.compile raised {type(e).__name__})"
     criterion = cfg["criterion"]
     if cfg["optimizer_type"] == "adamw":
         optimizer = optim.AdamW(model.parameters(), lr=cfg["lr"], betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
@@ -130,10 +172,10 @@ def run_reference(args):
         "ms_per_step": round(ms / steps, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp32 (the reference trainer's stock precision; TF32 matmul via set_float32_matmul_precision('high'))",
         "data": "synthetic", "config": {"model": name, "global_batch": batch, "seq_len": 1024 if is_lm else None,
-                                        "parallelism": "single", "path": "reference torch/torch_trainer.py train_epoch, eager"},
+                                        "parallelism": "single", "path": "reference torch/torch_trainer.py train_epoch, " + compiled},
         "e2e": {"value": round(value, 1), "unit": unit,
                 "h2d_bytes_per_step": int(batch * (x0.numel() * x0.element_size() + (y0.numel() * y0.element_size() if hasattr(y0, 'numel') else 8))),
                 "d2h_bytes_per_step": 12},
-        "loss_last": round(float(loss), 4),
+        "loss_last": round(float(loss), 4), **({"engine_error": engine_error} if engine_error else {}),
         "note": "the timed loop is the reference's own train_epoch: it uploads each batch and reads loss/accuracy back every step",
     }), flush=True)

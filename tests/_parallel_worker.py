@@ -50,8 +50,13 @@ def main():
         t.close()
         dist.destroy_process_group()
         return
-    layout = {"dp": f"dp{world}", "tp": f"tp2dp{world // 2}" if world > 2 else "tp2"}[mode]
+    layout = {"dp": f"dp{world}", "tp": f"tp2dp{world // 2}" if world > 2 else "tp2",
+              "tpeq": f"tp2dp{world // 2}" if world > 2 else "tp2"}[mode]
     t = ParallelTrainer(cfg, layout=layout, fused=fused, log=False, heap_bytes=256 << 20)
+    if mode == "tpeq":  # start from the weights the single-process run starts from
+        from tnn_b200.parallel.tp import copy_full_to_shards
+        full = zoo.create(cfg.model_name).compile(device="cpu", seed=cfg.seed)
+        copy_full_to_shards(t.graph, full, t.topo)
     gen = torch.Generator().manual_seed(100 + t.data_rank)
     losses = []
     for step in range(4):
@@ -59,6 +64,17 @@ def main():
         loss = t.train_step(seq[:, :-1].contiguous(), seq[:, 1:].contiguous())
         losses.append(float(loss.item()))
     _lib.check_status()
+    if mode == "tpeq":  # gather the shards into an unsharded model and hand its parameters back
+        from tnn_b200.parallel.tp import gather_full_state
+        t._refresh_master()
+        full = zoo.create(cfg.model_name).compile(device="cpu", seed=cfg.seed)
+        gather_full_state(t.graph, full, t.topo)
+        if rank == 0:
+            torch.save({"params": full.params_flat.float().cpu(), "losses": losses}, sys.argv[3])
+            print("RESULT " + json.dumps({"losses": losses}), flush=True)
+        t.close()
+        dist.destroy_process_group()
+        return
     master = t.graph.params_flat.float().clone()
     gathered = [torch.zeros_like(master) for _ in range(world)]
     dist.all_gather(gathered, master)

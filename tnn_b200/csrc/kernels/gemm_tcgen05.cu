@@ -28,8 +28,31 @@
 #include <mutex>
 
 #include "ptx.cuh"
+#include "tp_flags.cuh"
 
 namespace tnnb {
+
+// Tensor-parallel extension of the CTA-pair kernel (tnnb_gemm_tp; protocol in tp_flags.cuh).
+//   mode 1  all-gather -> GEMM: rows of A that another rank owns are pushed into the local A buffer by
+//           that rank's producing kernel; the TMA producer polls the row block's counter before it loads
+//           a tile of such rows. Tiles of the locally owned rows run first.
+//   mode 2  GEMM -> reduce-scatter: the epilogue stores the bf16 partial sums of rows another rank owns
+//           straight into that rank's inbox (peer stores) and the rows this rank owns into the local
+//           output (with the bias); remote tiles run first and their counters are bumped as soon as the
+//           CTA has finished its last remote tile. The kernel itself never waits for a peer.
+struct TpExt {
+  int mode, tp, rank;
+  int rows_per_rank;   // rows of M owned by each rank (multiple of 128)
+  int pair_blocks_per_rank;  // rows_per_rank / 256, or 0 when that is not whole (tile order then stays plain)
+  const uint32_t* pass;      // device word: number of passes including the current one
+  int* status;
+  // mode 1
+  const uint32_t* a_ready;   // [M/128] cumulative rows landed per 128-row block of A (local memory)
+  // mode 2
+  void* out[TP_MAX];         // out[o]: [rows_per_rank, ldo] block that receives the rows owned by rank o
+  long long ldo;
+  uint32_t* arrived[TP_MAX]; // arrived[o]: rank o's counters, one per 128-row block of its rows
+};
 
 struct GemmParams {
   int M, N, K;
@@ -58,9 +81,17 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 8 * 4096;  // + per-warp epilogue staging
 };
 
+// Where a tile's result goes: the call's output, or (tensor-parallel reduce-scatter) the block of the rank
+// that owns the tile's rows, with the bias applied only by the owner.
+struct EpiOut {
+  void* D;
+  long long ldd;
+  int flags;
+};
+
 // Fused element-wise part of the epilogue for 32 accumulator columns of one row (row < M, col0 < N).
-__device__ __forceinline__ void epilogue_math(const GemmParams& p, float (&v)[32], int row, int col0) {
-  const int flags = p.flags;
+__device__ __forceinline__ void epilogue_math(const GemmParams& p, const EpiOut& eo, float (&v)[32], int row, int col0) {
+  const int flags = eo.flags;
   const bool full = (col0 + 32 <= p.N);
 
   if (flags & EPI_BIAS) {
@@ -126,12 +157,12 @@ __device__ __forceinline__ void epilogue_math(const GemmParams& p, float (&v)[32
 
 // Row-per-lane store of 32 columns (each lane writes its own row): used for ragged edges and for the
 // output forms the coalescing path below does not cover.
-__device__ __forceinline__ void epilogue_store_rowwise(const GemmParams& p, const float (&v)[32], int row, int col0) {
-  const int flags = p.flags;
+__device__ __forceinline__ void epilogue_store_rowwise(const GemmParams& p, const EpiOut& eo, const float (&v)[32], int row, int col0) {
+  const int flags = eo.flags;
   const bool full = (col0 + 32 <= p.N);
   if (flags & EPI_ATOMIC) {
-    float* d = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col0;
-    if (full && (p.ldd % 4 == 0)) {
+    float* d = reinterpret_cast<float*>(eo.D) + (long long)row * eo.ldd + col0;
+    if (full && (eo.ldd % 4 == 0)) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
         asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d + j), "f"(v[j]),
@@ -143,8 +174,8 @@ __device__ __forceinline__ void epilogue_store_rowwise(const GemmParams& p, cons
         if (col0 + j < p.N) atomicAdd(d + j, v[j]);
     }
   } else if (flags & EPI_OUT_F32) {
-    float* d = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col0;
-    if (full && (p.ldd % 4 == 0)) {
+    float* d = reinterpret_cast<float*>(eo.D) + (long long)row * eo.ldd + col0;
+    if (full && (eo.ldd % 4 == 0)) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
         float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -159,8 +190,8 @@ __device__ __forceinline__ void epilogue_store_rowwise(const GemmParams& p, cons
         if (col0 + j < p.N) d[j] = (flags & EPI_ACCUM) ? d[j] + v[j] : v[j];
     }
   } else {
-    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + col0;
-    if (full && (p.ldd % 8 == 0)) {
+    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(eo.D) + (long long)row * eo.ldd + col0;
+    if (full && (eo.ldd % 8 == 0)) {
 #pragma unroll
       for (int j = 0; j < 32; j += 8) {
         __align__(16) __nv_bfloat16 t[8];
@@ -194,31 +225,31 @@ __device__ __forceinline__ uint32_t stage_off(int row, int chunk) { return row *
 
 // bf16 output, 64 columns [col0, col0+64) of rows [row_base, row_base+32): lane = row has written its
 // 64 values (as packed bf16) to the staging tile. Requires ldd % 8 == 0 and col0 + 64 <= N.
-__device__ __forceinline__ void stage_flush_bf16(const GemmParams& p, const uint8_t* stage, int lane, int row_base, int col0) {
+__device__ __forceinline__ void stage_flush_bf16(const GemmParams& p, const EpiOut& eo, const uint8_t* stage, int lane, int row_base, int col0) {
   __syncwarp();
-  __nv_bfloat16* D = reinterpret_cast<__nv_bfloat16*>(p.D);
+  __nv_bfloat16* D = reinterpret_cast<__nv_bfloat16*>(eo.D);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int r = i * 4 + (lane >> 3), c = lane & 7;
     const uint4 v = *reinterpret_cast<const uint4*>(stage + stage_off(r, c));
-    if (row_base + r < p.M) *reinterpret_cast<uint4*>(D + (long long)(row_base + r) * p.ldd + col0 + c * 8) = v;
+    if (row_base + r < p.M) *reinterpret_cast<uint4*>(D + (long long)(row_base + r) * eo.ldd + col0 + c * 8) = v;
   }
   __syncwarp();
 }
 // fp32 output (store, accumulate or atomic add), 32 columns. Requires ldd % 4 == 0 and col0 + 32 <= N.
-__device__ __forceinline__ void stage_flush_f32(const GemmParams& p, const uint8_t* stage, int lane, int row_base, int col0) {
+__device__ __forceinline__ void stage_flush_f32(const GemmParams& p, const EpiOut& eo, const uint8_t* stage, int lane, int row_base, int col0) {
   __syncwarp();
-  float* D = reinterpret_cast<float*>(p.D);
+  float* D = reinterpret_cast<float*>(eo.D);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int r = i * 4 + (lane >> 3), c = lane & 7;
     float4 v = *reinterpret_cast<const float4*>(stage + stage_off(r, c));
     if (row_base + r < p.M) {
-      float* d = D + (long long)(row_base + r) * p.ldd + col0 + c * 4;
-      if (p.flags & EPI_ATOMIC) {
+      float* d = D + (long long)(row_base + r) * eo.ldd + col0 + c * 4;
+      if (eo.flags & EPI_ATOMIC) {
         asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
       } else {
-        if (p.flags & EPI_ACCUM) {
+        if (eo.flags & EPI_ACCUM) {
           const float4 o = *reinterpret_cast<const float4*>(d);
           v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
         }
@@ -231,11 +262,11 @@ __device__ __forceinline__ void stage_flush_f32(const GemmParams& p, const uint8
 
 // One warp's share of a tile: `nchunks` groups of 32 accumulator columns starting at TMEM address t_addr /
 // global column col_base, rows row_base + lane. Chooses the coalescing path where its conditions hold.
-__device__ __forceinline__ void epilogue_warp(const GemmParams& p, uint32_t t_addr, int nchunks, int row_base, int col_base,
-                                              int lane, uint8_t* stage) {
+__device__ __forceinline__ void epilogue_warp(const GemmParams& p, const EpiOut& eo, uint32_t t_addr, int nchunks, int row_base,
+                                              int col_base, int lane, uint8_t* stage) {
   const int row = row_base + lane;
-  const bool f32 = (p.flags & (EPI_ATOMIC | EPI_OUT_F32)) != 0;
-  const bool staged_ok = f32 ? (p.ldd % 4 == 0) : (p.ldd % 8 == 0 && !(p.flags & EPI_ACCUM));
+  const bool f32 = (eo.flags & (EPI_ATOMIC | EPI_OUT_F32)) != 0;
+  const bool staged_ok = f32 ? (eo.ldd % 4 == 0) : (eo.ldd % 8 == 0 && !(eo.flags & EPI_ACCUM));
 #pragma unroll 1
   for (int c = 0; c < nchunks; c += 2) {
     const int col0 = col_base + c * 32;
@@ -254,14 +285,14 @@ __device__ __forceinline__ void epilogue_warp(const GemmParams& p, uint32_t t_ad
       float v[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-      if (row < p.M) epilogue_math(p, v, row, cc);
+      if (row < p.M) epilogue_math(p, eo, v, row, cc);
       if (!pair_staged) {
-        if (row < p.M) epilogue_store_rowwise(p, v, row, cc);
+        if (row < p.M) epilogue_store_rowwise(p, eo, v, row, cc);
       } else if (f32) {
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           *reinterpret_cast<float4*>(stage + stage_off(lane, k)) = make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
-        stage_flush_f32(p, stage, lane, row_base, cc);
+        stage_flush_f32(p, eo, stage, lane, row_base, cc);
       } else {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -273,7 +304,7 @@ __device__ __forceinline__ void epilogue_warp(const GemmParams& p, uint32_t t_ad
           }
           *reinterpret_cast<uint4*>(stage + stage_off(lane, h * 4 + k)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        if (h == 1) stage_flush_bf16(p, stage, lane, row_base, col0);
+        if (h == 1) stage_flush_bf16(p, eo, stage, lane, row_base, col0);
       }
     }
   }
@@ -440,7 +471,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + half * (BN / 2);
-      epilogue_warp(p, t_addr, BN / 64, mb * 128 + q * 32, nb * BN + half * (BN / 2), lane,
+      const EpiOut eo = {p.D, p.ldd, p.flags};
+      epilogue_warp(p, eo, t_addr, BN / 64, mb * 128 + q * 32, nb * BN + half * (BN / 2), lane,
                     smem + STAGES * Cfg::STAGE_BYTES + 256 + (warp - 2) * 4096);
       tc_fence_before();
       mbar_arrive(&tempty[acc]);
@@ -477,10 +509,57 @@ struct Gemm2Cfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 8 * 4096;  // + per-warp epilogue staging
 };
 
-template <int BN, int A_MN, int B_MN>
+// Tile order of the tensor-parallel variants: the 256-row blocks are grouped by the rank that owns their rows;
+// mode 1 runs the group of this rank first (its operand rows are already here), mode 2 runs it last (the partial
+// sums for the peers have the longest way to go). Inside a group the row block index runs fastest, as in the
+// plain order, so that neighbouring CTA pairs share a B tile.
+template <int COMM>
+__device__ __forceinline__ void pair_decode_tile(const GemmParams& p, const TpExt& x, int t, int& mb, int& nb) {
+  if (COMM == 0 || x.pair_blocks_per_rank == 0) {
+    nb = t / p.num_m_blocks;
+    mb = t - nb * p.num_m_blocks;
+    return;
+  }
+  const int bpr = x.pair_blocks_per_rank;
+  const int per_group = bpr * p.num_n_blocks;
+  const int g = t / per_group;
+  const int u = t - g * per_group;
+  nb = u / bpr;
+  const int owner = (x.rank + g + (COMM == 2 ? 1 : 0)) % x.tp;
+  mb = owner * bpr + (u - nb * bpr);
+}
+
+// Reduce-scatter side: publish the partial sums this warp stored for its remote tiles. `upto` = first work item
+// that is NOT covered (the warp has finished every tile before it). One system-scope fence, then one counter add
+// per remote tile: the amount is the number of 32-column chunks the warp wrote, so the consumer's target,
+// 4 x ceil(N / 32) per 128-row block and pass, does not depend on the tile width.
+template <int BN>
+__device__ __forceinline__ void tp_signal_remote_tiles(const GemmParams& p, const TpExt& x, int pair, int num_pairs, int upto,
+                                                       uint32_t cta_rank, int half, int lane) {
+  __syncwarp();
+  if (lane == 0) {
+    __threadfence_system();
+    for (int work = pair; work < upto; work += num_pairs) {
+      int mb, nb;
+      pair_decode_tile<2>(p, x, work, mb, nb);
+      const int row0 = mb * 256 + (int)cta_rank * 128;
+      if (row0 >= p.M) continue;
+      const int owner = row0 / x.rows_per_rank;
+      if (owner == x.rank) continue;
+      const int ncols = (BN == 384) ? 192 : BN / 2;
+      const int c0 = nb * BN + half * ncols;
+      const int c1 = min(c0 + ncols, p.N);
+      if (c1 <= c0) continue;
+      red_add_sys(x.arrived[owner] + (row0 - owner * x.rows_per_rank) / 128, (uint32_t)((c1 - c0 + 31) / 32));
+    }
+  }
+  __syncwarp();
+}
+
+template <int BN, int A_MN, int B_MN, int COMM>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                              const GemmParams p) {
+                              const GemmParams p, const __grid_constant__ TpExt tpx) {
   using Cfg = Gemm2Cfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int HALF = BN / 2;  // B rows (output columns) staged by each CTA
@@ -531,15 +610,26 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint32_t a_want = (COMM == 1) ? 128u * *tpx.pass : 0u;
       for (int work = pair; ok && work < total_work; work += num_pairs) {
         const int ks = work / tiles;
         const int t = work - ks * tiles;
-        const int nb = t / p.num_m_blocks;
-        const int mb = t - nb * p.num_m_blocks;
+        int mb, nb;
+        pair_decode_tile<COMM>(p, tpx, t, mb, nb);
         const int row0 = mb * 256 + (int)rank * 128;   // this CTA's rows of A
         const int col0 = nb * BN + (int)rank * HALF;   // this CTA's rows of B (output columns)
         const int kb0 = ks * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
+        if (COMM == 1 && row0 < p.M && row0 / tpx.rows_per_rank != tpx.rank) {
+          // rows pushed by their owner: wait until the whole 128-row block has landed, then make the peer's
+          // (generic-proxy) stores visible to the TMA reads that follow
+          if (!spin_until<true>(tpx.a_ready + (row0 >> 7), a_want)) {
+            raise_abort(p.status, abort_flag, ST_TIMEOUT_PEER);
+            ok = false;
+            break;
+          }
+          fence_proxy_async_all();
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_or_abort(&empty[stage], phase ^ 1, abort_flag)) {
             raise_abort(p.status, abort_flag, ST_TIMEOUT_PRODUCER);
@@ -626,26 +716,43 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t tempty_remote[2] = {mapa_shared(smem_u32(&tempty[0]), 0), mapa_shared(smem_u32(&tempty[1]), 0)};
-    for (int work = pair; work < total_work; work += num_pairs) {
+    bool unsignalled = false;  // COMM == 2: remote tiles stored but not yet published
+    int work = pair;
+    for (; work < total_work; work += num_pairs) {
       const int ks = work / tiles;
       const int t = work - ks * tiles;
-      const int nb = t / p.num_m_blocks;
-      const int mb = t - nb * p.num_m_blocks;
+      int mb, nb;
+      pair_decode_tile<COMM>(p, tpx, t, mb, nb);
+      const int row_cta = mb * 256 + (int)rank * 128;
+      EpiOut eo = {p.D, p.ldd, p.flags};
+      if (COMM == 2) {
+        const int owner = min(row_cta / tpx.rows_per_rank, tpx.tp - 1);
+        const bool remote = owner != tpx.rank;
+        if (!remote && unsignalled) {  // the last remote tile of this CTA is behind us
+          tp_signal_remote_tiles<BN>(p, tpx, pair, num_pairs, work, rank, half, lane);
+          unsignalled = false;
+        }
+        // block of the owning rank, addressed with the global row index
+        eo.D = reinterpret_cast<__nv_bfloat16*>(tpx.out[owner]) - (long long)owner * tpx.rows_per_rank * tpx.ldo;
+        eo.ldd = tpx.ldo;
+        if (remote) eo.flags = p.flags & ~EPI_BIAS;
+        unsignalled = unsignalled || (remote && row_cta < p.M);
+      }
       if (!wait_or_abort(&tfull[acc], acc_phase, abort_flag)) {
         if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
         break;
       }
       tc_fence_after();
       uint8_t* stage_tile = smem + STAGES * Cfg::STAGE_BYTES + 256 + (warp - 2) * 4096;
-      const int row_base = mb * 256 + (int)rank * 128 + q * 32;
+      const int row_base = row_cta + q * 32;
       if (BN == 384) {
         // warp half h owns output columns [h*192, h*192+192): 128 from the first product, 64 from the second
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-        epilogue_warp(p, t_lane + half * 128, 4, row_base, nb * BN + half * 192, lane, stage_tile);
-        epilogue_warp(p, t_lane + 256 + half * 64, 2, row_base, nb * BN + half * 192 + 128, lane, stage_tile);
+        epilogue_warp(p, eo, t_lane + half * 128, 4, row_base, nb * BN + half * 192, lane, stage_tile);
+        epilogue_warp(p, eo, t_lane + 256 + half * 64, 2, row_base, nb * BN + half * 192 + 128, lane, stage_tile);
       } else {
         const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + half * HALF;
-        epilogue_warp(p, t_addr, HALF / 32, row_base, nb * BN + half * HALF, lane, stage_tile);
+        epilogue_warp(p, eo, t_addr, HALF / 32, row_base, nb * BN + half * HALF, lane, stage_tile);
       }
       tc_fence_before();
       __syncwarp();
@@ -653,6 +760,8 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
       if (Cfg::ACCS == 2) acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    // also after an aborted loop: whatever was stored is published, the peers' counters stay consistent
+    if (COMM == 2 && unsignalled) tp_signal_remote_tiles<BN>(p, tpx, pair, num_pairs, work, rank, half, lane);
   }
 
   tc_fence_before();
@@ -753,16 +862,17 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
 
-template <int BN, int A_MN, int B_MN>
-static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
-  auto kern = gemm_bf16_tcgen05_pair_kernel<BN, A_MN, B_MN>;
+template <int BN, int A_MN, int B_MN, int COMM = 0>
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream,
+                            const TpExt& tpx = TpExt{}) {
+  auto kern = gemm_bf16_tcgen05_pair_kernel<BN, A_MN, B_MN, COMM>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg<BN>::SMEM_BYTES);
     if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
     attr_set = true;
   }
-  kern<<<grid, 320, Gemm2Cfg<BN>::SMEM_BYTES, stream>>>(ta, tb, p);  // cluster of two through __cluster_dims__
+  kern<<<grid, 320, Gemm2Cfg<BN>::SMEM_BYTES, stream>>>(ta, tb, p, tpx);  // cluster of two through __cluster_dims__
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
@@ -771,11 +881,11 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
 
 using namespace tnnb;
 
-extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int a_mn,
-                              int b_mn, long long lda, long long ldb, long long ldd,
-                              const void* bias, const void* aux_in, void* aux_out,
-                              long long ld_aux, const void* resid, long long ld_res, int flags,
-                              int split_k, int force_bn, int* status, void* stream_) {
+static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, int K, int a_mn,
+                         int b_mn, long long lda, long long ldb, long long ldd,
+                         const void* bias, const void* aux_in, void* aux_out,
+                         long long ld_aux, const void* resid, long long ld_res, int flags,
+                         int split_k, int force_bn, int* status, void* stream_, const TpExt* tpx) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0) return -2;
   if ((lda % 8) || (ldb % 8)) return -3;
@@ -788,6 +898,11 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
   p.M = M; p.N = N; p.K = K;
   // 256 x 256 tiles on CTA pairs whenever the problem has at least one such tile's worth of rows and
   // columns (force_bn: 512 forces the pair kernel, 128 / 256 force the single-CTA tile widths)
+  int pair_bn = 0;  // force_bn = 1024 + 256 / 384: the pair kernel with that tile width
+  if (force_bn >= 1024) {
+    pair_bn = force_bn - 1024;
+    force_bn = 512;
+  }
   const bool pair = (force_bn == 512) || (force_bn == 0 && M > 128 && N > 128);
   p.num_m_blocks = pair ? (M + 255) / 256 : (M + 127) / 128;
   p.num_k_blocks = (K + 63) / 64;
@@ -800,7 +915,8 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
     const long long sk = split_k > 0 ? split_k : 1;
     const long long w256 = ((long long)p.num_m_blocks * ((N + 255) / 256) * sk + units - 1) / units * 256;
     const long long w384 = ((long long)p.num_m_blocks * ((N + 383) / 384) * sk + units - 1) / units * 384;
-    bn = (force_bn == 0 && !(flags & EPI_ATOMIC) && w384 * 10 <= w256 * 8) ? 384 : 256;
+    bn = ((force_bn == 0 || tpx) && !(flags & EPI_ATOMIC) && w384 * 10 <= w256 * 8) ? 384 : 256;
+    if (pair_bn == 256 || pair_bn == 384) bn = pair_bn;
   } else if (bn != 128 && bn != 256) {
     const int t256 = p.num_m_blocks * ((N + 255) / 256);
     bn = (N > 128 && t256 * (split_k > 0 ? split_k : 1) >= sm_count()) ? 256 : 128;
@@ -858,6 +974,20 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
   }
   if (rc) return rc;
 
+  if (pair && tpx) {
+    // tensor-parallel variants: A is always K-major, no split-K
+    if (a_mn || p.split_k != 1) return -6;
+    const int grid2 = 2 * min(tiles, sm_count() / 2);
+#define TNNB_TP(BN_, BM_, CM) return launch_gemm_pair<BN_, 0, BM_, CM>(ta, tb, p, grid2, stream, *tpx)
+    if (tpx->mode == 1) {
+      if (bn == 256) { if (b_mn) TNNB_TP(256, 1, 1); TNNB_TP(256, 0, 1); }
+      if (b_mn) TNNB_TP(384, 1, 1); TNNB_TP(384, 0, 1);
+    } else {
+      if (bn == 256) { if (b_mn) TNNB_TP(256, 1, 2); TNNB_TP(256, 0, 2); }
+      if (b_mn) TNNB_TP(384, 1, 2); TNNB_TP(384, 0, 2);
+    }
+#undef TNNB_TP
+  }
   if (pair) {
     const int grid2 = 2 * min(tiles * p.split_k, sm_count() / 2);
 #define TNNB_PAIR(BN_, AM, BM_) return launch_gemm_pair<BN_, AM, BM_>(ta, tb, p, grid2, stream)
@@ -887,4 +1017,52 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
     TNNB_LAUNCH(128, 1, 1);
   }
 #undef TNNB_LAUNCH
+}
+
+extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int a_mn,
+                              int b_mn, long long lda, long long ldb, long long ldd,
+                              const void* bias, const void* aux_in, void* aux_out,
+                              long long ld_aux, const void* resid, long long ld_res, int flags,
+                              int split_k, int force_bn, int* status, void* stream_) {
+  return gemm_dispatch(A, B, D, M, N, K, a_mn, b_mn, lda, ldb, ldd, bias, aux_in, aux_out, ld_aux, resid, ld_res, flags,
+                       split_k, force_bn, status, stream_, nullptr);
+}
+
+// Tensor-parallel GEMMs on the CTA-pair kernel (protocol: tp_flags.cuh). A is [M, K] K-major.
+//   mode 1  Y[M, N] = A * op(B)^T where the rows of A owned by other ranks (row r belongs to rank
+//           r / rows_per_rank) are pushed into A by their owners; a_ready = this rank's counters [M / 128].
+//   mode 2  partial sums of the rows owned by rank o go to out[o] ([rows_per_rank, ldo], bf16): out[rank] is the
+//           local output (bias applied), out[o != rank] this rank's slot in o's inbox; arrived[o] = rank o's
+//           counters [rows_per_rank / 128]. D / ldd are ignored.
+// pass = device word holding the number of passes including this one. out / arrived are arrays of tp pointers.
+extern "C" int tnnb_gemm_tp(int mode, const void* A, const void* B, void* D, int M, int N, int K, int b_mn, long long lda,
+                            long long ldb, long long ldd, const void* bias, const void* aux_in, void* aux_out, long long ld_aux,
+                            int flags, int tp, int rank, int rows_per_rank, const void* pass, const void* a_ready, void** out,
+                            long long ldo, void** arrived, int force_bn, int* status, void* stream_) {
+  if (mode != 1 && mode != 2) return -2;
+  if (tp < 1 || tp > TP_MAX || rank < 0 || rank >= tp || !pass) return -2;
+  if (rows_per_rank <= 0 || rows_per_rank % 128 || (long long)rows_per_rank * tp != M) return -8;
+  if (flags & (EPI_ATOMIC | EPI_OUT_F32 | EPI_ACCUM | EPI_RESID)) return -6;
+  TpExt x{};
+  x.mode = mode; x.tp = tp; x.rank = rank; x.rows_per_rank = rows_per_rank;
+  x.pair_blocks_per_rank = (rows_per_rank % 256 == 0) ? rows_per_rank / 256 : 0;
+  x.pass = static_cast<const uint32_t*>(pass);
+  x.status = status;
+  if (mode == 1) {
+    if (!a_ready || !D) return -5;
+    x.a_ready = static_cast<const uint32_t*>(a_ready);
+  } else {
+    if (!out || !arrived || (ldo % 8)) return -5;
+    for (int o = 0; o < tp; ++o) {
+      if (!out[o] || (o != rank && !arrived[o])) return -5;
+      x.out[o] = out[o];
+      x.arrived[o] = static_cast<uint32_t*>(arrived[o]);
+    }
+    x.ldo = ldo;
+    D = out[rank];
+    ldd = ldo;
+  }
+  const int fb = (force_bn == 256 || force_bn == 384) ? force_bn + 1024 : 512;  // always the pair kernel
+  return gemm_dispatch(A, B, D, M, N, K, 0, b_mn, lda, ldb, ldd, bias, aux_in, aux_out, ld_aux, nullptr, 0, flags, 1, fb,
+                       status, stream_, &x);
 }

@@ -41,3 +41,11 @@ int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, i
                    long long ld_res, int flags, int split_k, int force_bn, int* status,
                    void* stream);
 }
+
+extern "C" {
+// Tensor-parallel GEMMs (all-gather -> GEMM, GEMM -> reduce-scatter); see gemm_tcgen05.cu and tp_flags.cuh.
+int tnnb_gemm_tp(int mode, const void* A, const void* B, void* D, int M, int N, int K, int b_mn, long long lda,
+                 long long ldb, long long ldd, const void* bias, const void* aux_in, void* aux_out, long long ld_aux,
+                 int flags, int tp, int rank, int rows_per_rank, const void* pass, const void* a_ready, void** out,
+                 long long ldo, void** arrived, int force_bn, int* status, void* stream);
+}

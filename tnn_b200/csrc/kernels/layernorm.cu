@@ -12,7 +12,17 @@
 // a one-thread-per-row fallback (cuda_engine.cu:962-1047) and launches the
 // residual add and dropout separately; semantics (biased variance, eps inside
 // the square root) follow src/nn/engines/cpu_engine.cpp:513-614.
+//
+// Tensor-parallel variants (template flag TP; protocol in tp_flags.cuh). With sequence parallelism every rank
+// normalises its own rows, and the kernels on both sides of a layer norm are the fused GEMMs of the tensor-parallel
+// transformer block, so the layer-norm kernels are where rows change hands:
+//   pull  the `delta` (forward) / `dh` (backward) operand is the sum of the local partial result and the partial
+//         results the peers' GEMM epilogues pushed into this rank's inbox; a warp polls the arrival counter of
+//         its row's 128-row block before it reads the inbox.
+//   push  `h` (forward) / `ddelta` (backward) is also stored into every peer's copy of the gather buffer, and the
+//         block adds the rows it delivered to the peers' row-block counters once it has finished.
 #include "ptx.cuh"
+#include "tp_flags.cuh"
 
 namespace tnnb {
 
@@ -27,13 +37,15 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-template <int MAXCH>
+template <int MAXCH, bool TP>
 __global__ void __launch_bounds__(256)
 ln_fwd_kernel(const bf16* __restrict__ x_in, const bf16* __restrict__ delta, bf16* __restrict__ x_out,
               bf16* __restrict__ h, const bf16* __restrict__ gamma, const bf16* __restrict__ beta,
               float* __restrict__ mean_o, float* __restrict__ rstd_o, long long rows, int C, float eps,
-              float p, unsigned long long seed, const unsigned long long* __restrict__ seed_off) {
+              float p, unsigned long long seed, const unsigned long long* __restrict__ seed_off,
+              const __grid_constant__ TpPull pull, const __grid_constant__ TpPush push) {
   seed = mix_seed(seed, seed_off);
+  const uint32_t pull_want = (TP && pull.n) ? pull.units * *pull.pass : 0u;
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int chunks = C >> 3;
@@ -42,6 +54,7 @@ ln_fwd_kernel(const bf16* __restrict__ x_in, const bf16* __restrict__ delta, bf1
   for (long long r = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += (long long)gridDim.x * wpb) {
     float v[MAXCH][8];
     float s = 0.f;
+    if (TP && pull.n) tp_pull_wait(pull, r, pull_want, lane);
 #pragma unroll
     for (int i = 0; i < MAXCH; ++i) {
       const int c = lane + i * 32;
@@ -51,10 +64,14 @@ ln_fwd_kernel(const bf16* __restrict__ x_in, const bf16* __restrict__ delta, bf1
         for (int k = 0; k < 8; ++k) v[i][k] = __bfloat162float(a.v[k]);
         if (delta) {
           LBf8 d = *reinterpret_cast<const LBf8*>(delta + r * C + c * 8);
+          float dsum[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) dsum[k] = __bfloat162float(d.v[k]);
+          if (TP && pull.n) tp_pull_add8(pull, r * C + c * 8, dsum);
           const uint32_t keep = p > 0.f ? dropout_keep8(seed, (uint64_t)(r * chunks + c), thr) : 0xffu;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
-            float dv = __bfloat162float(d.v[k]);
+            float dv = dsum[k];
             if (p > 0.f) dv = (keep >> k) & 1u ? dv * inv_keep : 0.f;
             // Round the residual stream to bf16 first so that the saved x_out and
             // the statistics below describe exactly the same numbers.
@@ -102,9 +119,13 @@ ln_fwd_kernel(const bf16* __restrict__ x_in, const bf16* __restrict__ delta, bf1
           for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16((v[i][k] - mean) * rstd);
         }
         *reinterpret_cast<LBf8*>(h + r * C + c * 8) = o;
+        if (TP) {
+          for (int t = 0; t < push.n; ++t) *reinterpret_cast<LBf8*>(push.dst[t] + r * C + c * 8) = o;
+        }
       }
     }
   }
+  if (TP && push.n) tp_push_signal(push, rows, wpb);
 }
 
 // Backward. One warp per row with the row held in registers as packed bf16; the dgamma / dbeta partial
@@ -124,14 +145,15 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int MAXCH>
+template <int MAXCH, bool TP>
 __global__ void __launch_bounds__(256, (MAXCH <= 3) ? 3 : 2)
 ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const float* __restrict__ mean_i,
               const float* __restrict__ rstd_i, const bf16* __restrict__ gamma, const bf16* __restrict__ dres,
               bf16* __restrict__ dx, bf16* __restrict__ ddelta, float* __restrict__ dgamma,
               float* __restrict__ dbeta, long long rows, int C, float p, unsigned long long seed,
-              const unsigned long long* __restrict__ seed_off) {
+              const unsigned long long* __restrict__ seed_off, const __grid_constant__ TpPull pull, const __grid_constant__ TpPush push) {
   seed = mix_seed(seed, seed_off);
+  const uint32_t pull_want = (TP && pull.n) ? pull.units * *pull.pass : 0u;
   extern __shared__ float sm[];  // [warps][2][C]
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -148,6 +170,7 @@ ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const flo
 
   for (long long r = (long long)blockIdx.x * wpb + warp; r < rows; r += (long long)gridDim.x * wpb) {
     uint4 xa[MAXCH], da[MAXCH], ra[MAXCH];
+    if (TP && pull.n) tp_pull_wait(pull, r, pull_want, lane);
 #pragma unroll
     for (int i = 0; i < MAXCH; ++i) {
       const int c = lane + i * 32;
@@ -155,6 +178,12 @@ ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const flo
       xa[i] = in ? *reinterpret_cast<const uint4*>(x + r * C + c * 8) : zero4;
       da[i] = in ? *reinterpret_cast<const uint4*>(dh + r * C + c * 8) : zero4;
       ra[i] = (in && dres) ? *reinterpret_cast<const uint4*>(dres + r * C + c * 8) : zero4;
+      if (TP && pull.n && in) {  // dh = local partial + the peers' partials, rounded to bf16 like a reduce-scatter result
+        float t[8];
+        unpack8(da[i], t);
+        tp_pull_add8(pull, r * C + c * 8, t);
+        da[i] = make_uint4(pack2(t[0], t[1]), pack2(t[2], t[3]), pack2(t[4], t[5]), pack2(t[6], t[7]));
+      }
     }
     const float mean = mean_i[r], rstd = rstd_i[r];
     float s1 = 0.f, s2 = 0.f;
@@ -211,12 +240,16 @@ ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const flo
 #pragma unroll
             for (int k = 0; k < 8; ++k) t[k] = (keep >> k) & 1u ? t[k] * inv_keep : 0.f;
           }
-          *reinterpret_cast<uint4*>(ddelta + r * C + c * 8) =
-              make_uint4(pack2(t[0], t[1]), pack2(t[2], t[3]), pack2(t[4], t[5]), pack2(t[6], t[7]));
+          const uint4 dd = make_uint4(pack2(t[0], t[1]), pack2(t[2], t[3]), pack2(t[4], t[5]), pack2(t[6], t[7]));
+          *reinterpret_cast<uint4*>(ddelta + r * C + c * 8) = dd;
+          if (TP) {
+            for (int u = 0; u < push.n; ++u) *reinterpret_cast<uint4*>(push.dst[u] + r * C + c * 8) = dd;
+          }
         }
       }
     }
   }
+  if (TP && push.n) tp_push_signal(push, rows, wpb);
   if (dgamma) {
     __syncthreads();
     for (int i = threadIdx.x; i < C; i += blockDim.x) {
@@ -241,13 +274,42 @@ static inline int pick_maxch(int C) {
   return per_lane <= 3 ? 3 : per_lane <= 5 ? 5 : per_lane <= 8 ? 8 : 0;
 }
 
-extern "C" {
+// Fill the parameter blocks of the tensor-parallel variants from flat C arguments (see tnnb_layernorm_fwd_tp).
+static int make_tp_blocks(TpPull& pull, TpPush& push, int n_pull, void** pull_src, const void* arrived, const void* pass,
+                          unsigned int units, int n_push, void** push_dst, void** push_ready, long long push_row0,
+                          int* status) {
+  if (n_pull < 0 || n_pull > TP_MAX - 1 || n_push < 0 || n_push > TP_MAX - 1) return -2;
+  pull = TpPull{};
+  push = TpPush{};
+  pull.n = n_pull;
+  if (n_pull) {
+    if (!pull_src || !arrived || !pass) return -5;
+    for (int i = 0; i < n_pull; ++i) {
+      if (!pull_src[i] || ((uintptr_t)pull_src[i] & 15)) return -4;
+      pull.src[i] = (const bf16*)pull_src[i];
+    }
+    pull.arrived = (const uint32_t*)arrived;
+    pull.pass = (const uint32_t*)pass;
+    pull.units = units;
+    pull.status = status;
+  }
+  push.n = n_push;
+  if (n_push) {
+    if (!push_dst || !push_ready || push_row0 < 0 || (push_row0 % 8)) return -5;
+    push.row0 = (int)push_row0;
+    for (int i = 0; i < n_push; ++i) {
+      if (!push_dst[i] || !push_ready[i] || ((uintptr_t)push_dst[i] & 15)) return -4;
+      push.dst[i] = (bf16*)push_dst[i];
+      push.ready[i] = (uint32_t*)push_ready[i];
+    }
+  }
+  return 0;
+}
 
-// rows x C, C % 8 == 0 and C <= 2048. delta/x_out may be null together
-// (plain layernorm of x_in); gamma/beta may be null together (no affine).
-int tnnb_layernorm_fwd(const void* x_in, const void* delta, void* x_out, void* h, const void* gamma,
-                       const void* beta, void* mean, void* rstd, long long rows, int C, float eps, float p,
-                       unsigned long long seed, const void* seed_off, void* stream) {
+static int layernorm_fwd_impl(const void* x_in, const void* delta, void* x_out, void* h, const void* gamma,
+                              const void* beta, void* mean, void* rstd, long long rows, int C, float eps, float p,
+                              unsigned long long seed, const void* seed_off, void* stream, const TpPull* pull,
+                              const TpPush* push) {
   if (C % 8 || rows <= 0) return -3;
   if ((delta == nullptr) != (x_out == nullptr)) return -5;
   const int mc = pick_maxch(C);
@@ -256,20 +318,54 @@ int tnnb_layernorm_fwd(const void* x_in, const void* delta, void* x_out, void* h
   long long g = (rows + wpb - 1) / wpb;
   int grid = (int)(g > 148 * 8 ? 148 * 8 : g);
   cudaStream_t st = (cudaStream_t)stream;
-#define LN_F(MC)                                                                                          \
-  ln_fwd_kernel<MC><<<grid, block, 0, st>>>((const bf16*)x_in, (const bf16*)delta, (bf16*)x_out, (bf16*)h, \
-                                            (const bf16*)gamma, (const bf16*)beta, (float*)mean,          \
-                                            (float*)rstd, rows, C, eps, p, seed, (const unsigned long long*)seed_off)
-  if (mc == 3) LN_F(3); else if (mc == 5) LN_F(5); else LN_F(8);
+#define LN_F(MC, TP_, PL, PS)                                                                                       \
+  ln_fwd_kernel<MC, TP_><<<grid, block, 0, st>>>((const bf16*)x_in, (const bf16*)delta, (bf16*)x_out, (bf16*)h,      \
+                                                 (const bf16*)gamma, (const bf16*)beta, (float*)mean, (float*)rstd, \
+                                                 rows, C, eps, p, seed, (const unsigned long long*)seed_off, PL, PS)
+  if (pull) {
+    if (mc == 3) LN_F(3, true, *pull, *push); else if (mc == 5) LN_F(5, true, *pull, *push); else LN_F(8, true, *pull, *push);
+  } else {
+    if (mc == 3) LN_F(3, false, TpPull{}, TpPush{}); else if (mc == 5) LN_F(5, false, TpPull{}, TpPush{}); else LN_F(8, false, TpPull{}, TpPush{});
+  }
 #undef LN_F
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
 }
 
-// dgamma/dbeta (fp32 [C]) are accumulated into; pass null to skip them.
-int tnnb_layernorm_bwd(const void* dh, const void* x, const void* mean, const void* rstd, const void* gamma,
-                       const void* dres, void* dx, void* ddelta, void* dgamma, void* dbeta, long long rows,
-                       int C, float p, unsigned long long seed, const void* seed_off, void* stream) {
+extern "C" {
+
+// rows x C, C % 8 == 0 and C <= 2048. delta/x_out may be null together
+// (plain layernorm of x_in); gamma/beta may be null together (no affine).
+int tnnb_layernorm_fwd(const void* x_in, const void* delta, void* x_out, void* h, const void* gamma,
+                       const void* beta, void* mean, void* rstd, long long rows, int C, float eps, float p,
+                       unsigned long long seed, const void* seed_off, void* stream) {
+  return layernorm_fwd_impl(x_in, delta, x_out, h, gamma, beta, mean, rstd, rows, C, eps, p, seed, seed_off, stream,
+                            nullptr, nullptr);
+}
+
+// Tensor-parallel form. pull: delta is the sum of `delta` and pull_src[0..n_pull) (each [rows, C], local memory)
+// once arrived[row / 128] has reached units x *pass. push: h is also stored to push_dst[i] (peer i's gather buffer,
+// already offset to this rank's first row) and the rows delivered are added to push_ready[i][(push_row0 + row) / 128].
+int tnnb_layernorm_fwd_tp(const void* x_in, const void* delta, void* x_out, void* h, const void* gamma,
+                          const void* beta, void* mean, void* rstd, long long rows, int C, float eps, float p,
+                          unsigned long long seed, const void* seed_off, int n_pull, void** pull_src,
+                          const void* arrived, const void* pass, unsigned int units, int n_push, void** push_dst,
+                          void** push_ready, long long push_row0, int* status, void* stream) {
+  TpPull pull;
+  TpPush push;
+  const int rc = make_tp_blocks(pull, push, n_pull, pull_src, arrived, pass, units, n_push, push_dst, push_ready, push_row0, status);
+  if (rc) return rc;
+  if (n_pull && !delta) return -5;
+  return layernorm_fwd_impl(x_in, delta, x_out, h, gamma, beta, mean, rstd, rows, C, eps, p, seed, seed_off, stream, &pull,
+                            &push);
+}
+
+}  // extern "C"
+
+static int layernorm_bwd_impl(const void* dh, const void* x, const void* mean, const void* rstd, const void* gamma,
+                              const void* dres, void* dx, void* ddelta, void* dgamma, void* dbeta, long long rows,
+                              int C, float p, unsigned long long seed, const void* seed_off, void* stream,
+                              const TpPull* pull, const TpPush* push) {
   if (C % 8 || rows <= 0) return -3;
   const int mc = pick_maxch(C);
   if (!mc) return -7;
@@ -280,21 +376,54 @@ int tnnb_layernorm_bwd(const void* dh, const void* x, const void* mean, const vo
   size_t smem = (size_t)wpb * 2 * C * sizeof(float);  // <= 128 KB at C = 2048
   static bool attr_done = false;
   if (!attr_done) {
-    cudaFuncSetAttribute(ln_bwd_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 768 * 4);
-    cudaFuncSetAttribute(ln_bwd_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 1280 * 4);
-    cudaFuncSetAttribute(ln_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 2048 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 768 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<5, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 1280 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 2048 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 768 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 1280 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 2048 * 4);
     attr_done = true;
   }
   cudaStream_t st = (cudaStream_t)stream;
-#define LN_B(MC)                                                                                              \
-  ln_bwd_kernel<MC><<<grid, block, smem, st>>>((const bf16*)dh, (const bf16*)x, (const float*)mean,           \
-                                               (const float*)rstd, (const bf16*)gamma, (const bf16*)dres,     \
-                                               (bf16*)dx, (bf16*)ddelta, (float*)dgamma, (float*)dbeta, rows, \
-                                               C, p, seed, (const unsigned long long*)seed_off)
-  if (mc == 3) LN_B(3); else if (mc == 5) LN_B(5); else LN_B(8);
+#define LN_B(MC, TP_, PL, PS)                                                                                          \
+  ln_bwd_kernel<MC, TP_><<<grid, block, smem, st>>>((const bf16*)dh, (const bf16*)x, (const float*)mean,               \
+                                                    (const float*)rstd, (const bf16*)gamma, (const bf16*)dres,         \
+                                                    (bf16*)dx, (bf16*)ddelta, (float*)dgamma, (float*)dbeta, rows, C, \
+                                                    p, seed, (const unsigned long long*)seed_off, PL, PS)
+  if (pull) {
+    if (mc == 3) LN_B(3, true, *pull, *push); else if (mc == 5) LN_B(5, true, *pull, *push); else LN_B(8, true, *pull, *push);
+  } else {
+    if (mc == 3) LN_B(3, false, TpPull{}, TpPush{}); else if (mc == 5) LN_B(5, false, TpPull{}, TpPush{}); else LN_B(8, false, TpPull{}, TpPush{});
+  }
 #undef LN_B
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
+}
+
+extern "C" {
+
+// dgamma/dbeta (fp32 [C]) are accumulated into; pass null to skip them.
+int tnnb_layernorm_bwd(const void* dh, const void* x, const void* mean, const void* rstd, const void* gamma,
+                       const void* dres, void* dx, void* ddelta, void* dgamma, void* dbeta, long long rows,
+                       int C, float p, unsigned long long seed, const void* seed_off, void* stream) {
+  return layernorm_bwd_impl(dh, x, mean, rstd, gamma, dres, dx, ddelta, dgamma, dbeta, rows, C, p, seed, seed_off, stream,
+                            nullptr, nullptr);
+}
+
+// Tensor-parallel form: dh is the sum of `dh` and the pulled partials; ddelta is also pushed (arguments as in
+// tnnb_layernorm_fwd_tp).
+int tnnb_layernorm_bwd_tp(const void* dh, const void* x, const void* mean, const void* rstd, const void* gamma,
+                          const void* dres, void* dx, void* ddelta, void* dgamma, void* dbeta, long long rows,
+                          int C, float p, unsigned long long seed, const void* seed_off, int n_pull, void** pull_src,
+                          const void* arrived, const void* pass, unsigned int units, int n_push, void** push_dst,
+                          void** push_ready, long long push_row0, int* status, void* stream) {
+  TpPull pull;
+  TpPush push;
+  const int rc = make_tp_blocks(pull, push, n_pull, pull_src, arrived, pass, units, n_push, push_dst, push_ready, push_row0, status);
+  if (rc) return rc;
+  if (n_push && !ddelta) return -5;
+  return layernorm_bwd_impl(dh, x, mean, rstd, gamma, dres, dx, ddelta, dgamma, dbeta, rows, C, p, seed, seed_off, stream,
+                            &pull, &push);
 }
 
 }  // extern "C"

@@ -231,12 +231,41 @@ def colsum_accum(dy: torch.Tensor, db: torch.Tensor) -> None:
 
 
 # ------------------------------------------------------------------------- layernorm
+def _tp_tail(tp_pull, tp_push, device):
+    """The trailing arguments of the tensor-parallel layer-norm entry points (csrc/kernels/layernorm.cu). ``tp_pull``
+    is a reduce-scatter site whose inbox is added to the operand, ``tp_push`` a gather site whose peers receive the
+    output (objects of tnn_b200.parallel.tp)."""
+    pl = (tp_pull.n_pull, tp_pull.pull_src, _lib.ptr(tp_pull.arrived), _lib.ptr(tp_pull.pass_ctr), tp_pull.units) \
+        if tp_pull is not None else (0, None, None, None, 0)
+    ps = (tp_push.n_push, tp_push.push_dst, tp_push.push_ready, tp_push.push_row0) if tp_push is not None else (0, None, None, 0)
+    return (*pl, *ps, _lib.ptr(_lib.status_word(device)), _lib.stream())
+
+
+_TP_DECLARED = False
+
+
+def _declare_tp(lib):
+    global _TP_DECLARED
+    if _TP_DECLARED:
+        return
+    import ctypes
+    vp, ll, i, u, f, ull = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_uint, ctypes.c_float, ctypes.c_ulonglong
+    tail = [i, vp, vp, vp, u, i, vp, vp, ll, vp, vp]
+    lib.tnnb_layernorm_fwd_tp.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ll, i, f, f, ull, vp] + tail
+    lib.tnnb_layernorm_fwd_tp.restype = i
+    lib.tnnb_layernorm_bwd_tp.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ll, i, f, ull, vp] + tail
+    lib.tnnb_layernorm_bwd_tp.restype = i
+    _TP_DECLARED = True
+
+
 def layernorm_fwd(x: torch.Tensor, delta: Optional[torch.Tensor], gamma: Optional[torch.Tensor],
                   beta: Optional[torch.Tensor], eps: float, p: float = 0.0, seed: int = 0,
-                  h_out: Optional[torch.Tensor] = None
+                  h_out: Optional[torch.Tensor] = None, tp_pull=None, tp_push=None
                   ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """``x_out = x + dropout(delta)``; ``h = LN(x_out)``. Returns (x_out, h, mean, rstd); x is 2-D [rows, C].
-    ``h_out`` (contiguous, same shape) receives ``h`` in place, e.g. rows of a symmetric gather buffer."""
+    ``h_out`` (contiguous, same shape) receives ``h`` in place, e.g. rows of a symmetric gather buffer.
+    Tensor parallelism (CUDA only): ``tp_pull`` adds the partial sums in a reduce-scatter site's inbox to ``delta``;
+    ``tp_push`` also delivers ``h`` to the peers of a gather site (``h_out`` must then be that site's own rows)."""
     rows, C = x.shape
     if x.is_cuda and x.dtype == torch.bfloat16:
         x = x.contiguous()
@@ -246,12 +275,20 @@ def layernorm_fwd(x: torch.Tensor, delta: Optional[torch.Tensor], gamma: Optiona
         rstd = torch.empty_like(mean)
         if delta is not None:
             delta = delta.contiguous()
-        rc = _lib.load().tnnb_layernorm_fwd(_lib.ptr(x), _lib.ptr(delta), _lib.ptr(x_out), _lib.ptr(h),
-                                            _lib.ptr(gamma), _lib.ptr(beta), _lib.ptr(mean), _lib.ptr(rstd), rows, C,
-                                            eps, p, seed & _M64, _seed_off_ptr(), _lib.stream())
+        lib = _lib.load()
+        if tp_pull is not None or tp_push is not None:
+            _declare_tp(lib)
+            rc = lib.tnnb_layernorm_fwd_tp(_lib.ptr(x), _lib.ptr(delta), _lib.ptr(x_out), _lib.ptr(h), _lib.ptr(gamma),
+                                           _lib.ptr(beta), _lib.ptr(mean), _lib.ptr(rstd), rows, C, eps, p, seed & _M64,
+                                           _seed_off_ptr(), *_tp_tail(tp_pull, tp_push, x.device))
+        else:
+            rc = lib.tnnb_layernorm_fwd(_lib.ptr(x), _lib.ptr(delta), _lib.ptr(x_out), _lib.ptr(h),
+                                        _lib.ptr(gamma), _lib.ptr(beta), _lib.ptr(mean), _lib.ptr(rstd), rows, C,
+                                        eps, p, seed & _M64, _seed_off_ptr(), _lib.stream())
         _lib.check_rc(rc, "layernorm_fwd")
         _count()
         return (x_out if delta is not None else x), h, mean, rstd
+    assert tp_pull is None and tp_push is None, "the tensor-parallel hand-offs exist on CUDA only"
     xf = x.float()
     if delta is not None:
         d = delta.float()
@@ -270,9 +307,11 @@ def layernorm_fwd(x: torch.Tensor, delta: Optional[torch.Tensor], gamma: Optiona
 def layernorm_bwd(dh: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: torch.Tensor,
                   gamma: Optional[torch.Tensor], dres: Optional[torch.Tensor], want_ddelta: bool, p: float,
                   seed: int, dgamma: Optional[torch.Tensor], dbeta: Optional[torch.Tensor],
-                  ddelta_out: Optional[torch.Tensor] = None
+                  ddelta_out: Optional[torch.Tensor] = None, tp_pull=None, tp_push=None
                   ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-    """Returns (dx, ddelta); accumulates into fp32 dgamma/dbeta. ``ddelta_out`` receives ddelta in place."""
+    """Returns (dx, ddelta); accumulates into fp32 dgamma/dbeta. ``ddelta_out`` receives ddelta in place.
+    ``tp_pull`` / ``tp_push`` as in :func:`layernorm_fwd`: the pulled partial sums are added to ``dh``, ``ddelta`` is
+    what gets pushed."""
     rows, C = x.shape
     if x.is_cuda and x.dtype == torch.bfloat16:
         dh = dh.contiguous()
@@ -280,12 +319,20 @@ def layernorm_bwd(dh: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: t
         dd = (ddelta_out if ddelta_out is not None else torch.empty_like(x)) if want_ddelta else None
         if dres is not None:
             dres = dres.contiguous()
-        rc = _lib.load().tnnb_layernorm_bwd(_lib.ptr(dh), _lib.ptr(x), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma),
-                                            _lib.ptr(dres), _lib.ptr(dx), _lib.ptr(dd), _lib.ptr(dgamma),
-                                            _lib.ptr(dbeta), rows, C, p, seed & _M64, _seed_off_ptr(), _lib.stream())
+        lib = _lib.load()
+        if tp_pull is not None or tp_push is not None:
+            _declare_tp(lib)
+            rc = lib.tnnb_layernorm_bwd_tp(_lib.ptr(dh), _lib.ptr(x), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma),
+                                           _lib.ptr(dres), _lib.ptr(dx), _lib.ptr(dd), _lib.ptr(dgamma), _lib.ptr(dbeta),
+                                           rows, C, p, seed & _M64, _seed_off_ptr(), *_tp_tail(tp_pull, tp_push, x.device))
+        else:
+            rc = lib.tnnb_layernorm_bwd(_lib.ptr(dh), _lib.ptr(x), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma),
+                                        _lib.ptr(dres), _lib.ptr(dx), _lib.ptr(dd), _lib.ptr(dgamma),
+                                        _lib.ptr(dbeta), rows, C, p, seed & _M64, _seed_off_ptr(), _lib.stream())
         _lib.check_rc(rc, "layernorm_bwd")
         _count()
         return dx, dd
+    assert tp_pull is None and tp_push is None, "the tensor-parallel hand-offs exist on CUDA only"
     xh = (x.float() - mean[:, None]) * rstd[:, None]
     g = dh.float()
     if dgamma is not None:

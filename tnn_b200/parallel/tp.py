@@ -3,10 +3,16 @@
 Inside a tensor-parallel group of ``tp`` ranks every rank keeps ``1/tp`` of the attention heads and
 of the MLP width, and - between those regions - ``1/tp`` of the rows (tokens) of the residual
 stream. The two places per block where the row shards have to be combined are fused with the
-GEMMs around them by the kernels of csrc/kernels/comm_fused.cu:
+kernels around them (csrc/kernels/tp_flags.cuh describes the protocol):
 
-* ``gemm_ag``  all-gather of the row shards -> GEMM   (QKV and fc1 forward; out-proj and fc2 dgrad)
-* ``gemm_rs``  GEMM -> reduce-scatter of the rows     (out-proj and fc2 forward; QKV and fc1 dgrad)
+* all-gather -> GEMM (QKV and fc1 forward; out-proj and fc2 dgrad): the layer-norm kernel that produces a
+  rank's rows stores them into every peer's gather buffer as well, and the GEMM (the tensor-parallel variant of
+  the CTA-pair tcgen05 kernel) starts with the local rows and polls a counter before it touches a peer's rows;
+* GEMM -> reduce-scatter (out-proj and fc2 forward; QKV and fc1 dgrad): the GEMM epilogue stores the partial
+  sums of a peer's rows into that peer's inbox, and the layer-norm kernel that consumes the result adds the
+  inbox to the local partial sum.
+
+No kernel waits for a peer to arrive at the same call: data only ever flows from kernels that ran earlier.
 
 With ``fused=False`` the same math runs through ``all_gather_into_tensor`` / ``reduce_scatter_tensor``
 around the plain GEMM - the NCCL baseline. The head and the embedding are not split by features:
@@ -85,9 +91,12 @@ def _declare(lib):
     if _DECLARED:
         return
     vp, ll, i, u = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_uint
-    lib.tnnb_gemm_comm.argtypes = [i, i, i, i, i, vp, ll, vp, ll, vp, ll, vp, i, i, i, u, vp, vp, vp, vp, vp, vp, vp, vp, vp, ll,
-                                   i, vp, vp, vp]
-    lib.tnnb_gemm_comm.restype = i
+    lib.tnnb_gemm_tp.argtypes = [i, vp, vp, vp, i, i, i, i, ll, ll, ll, vp, vp, vp, ll, i, i, i, i, vp, vp, vp, ll, vp, i, vp, vp]
+    lib.tnnb_gemm_tp.restype = i
+    lib.tnnb_tp_push.argtypes = [vp, vp, ll, i, i, vp, vp, ll, vp]
+    lib.tnnb_tp_push.restype = i
+    lib.tnnb_tp_resolve.argtypes = [vp, vp, ll, i, i, vp, vp, vp, u, vp, vp]
+    lib.tnnb_tp_resolve.restype = i
     _DECLARED = True
 
 
@@ -98,39 +107,68 @@ class CommContext:
         self.tp, self.idx, self.ranks, self.group = topo.tp, topo.tp_idx, topo.tp_ranks, topo.tp_group
         self.heap, self.fused, self.device = heap, fused and heap is not None, device
         self.lib = _lib.load() if self.fused else None
-        # call number of the current pass, read by the kernels from device memory so that a captured
-        # CUDA graph sees a new value on every replay
-        self.tick = torch.zeros(1, dtype=torch.int32, device=device)
         self.seq_len = 0  # set by the pipeline runtime: stages after the first cannot read it off their input
         if self.fused:
             _declare(self.lib)
 
+    def new_pass_counter(self) -> torch.Tensor:
+        """A device word that counts the passes through one set of sites (bumped once at the start of every
+        pass; the kernels read it, so a captured CUDA graph sees a new value on every replay)."""
+        return torch.zeros(1, dtype=torch.int32, device=self.device)
+
+
+# EPI_* bits of csrc/kernels/gemm_tcgen05.h
+_EPI_BIAS, _EPI_GELU, _EPI_DGELU = 1, 2, 4
+
 
 class GatherSite:
-    """A symmetric ``[M, K]`` buffer whose row block ``idx`` is written locally and whose other row
-    blocks are pulled from the peers by ``gemm_ag``. After the call the whole buffer is valid
-    locally (it is kept for the weight-gradient GEMM)."""
+    """A symmetric ``[M, K]`` buffer whose row block ``idx`` is produced locally and whose other row blocks are
+    PUSHED into it by the ranks that own them (csrc/kernels/tp_flags.cuh): the kernel that produces this rank's
+    rows - a layer norm, through :meth:`push_args`, or :meth:`push` - also stores them into every peer's buffer and
+    bumps the peers' row-block counters; :meth:`gemm` runs the tiles of the local rows first and polls the
+    counters of the other row blocks only when it reaches them. After the call the whole buffer is valid locally
+    (it is kept for the weight-gradient GEMM)."""
 
-    def __init__(self, cc: CommContext, M: int, K: int):
-        self.cc, self.M, self.K, self.epoch = cc, M, K, 0
+    def __init__(self, cc: CommContext, M: int, K: int, pass_ctr: Optional[torch.Tensor] = None):
+        self.cc, self.M, self.K = cc, M, K
         self.rows = M // cc.tp
+        self.pass_ctr = pass_ctr
         if cc.fused:
             self.buf = cc.heap.alloc((M, K), torch.bfloat16)
-            self.barrier = cc.heap.alloc((16,), torch.int32).zero_()
-            self.src = ptr_array(cc.heap.peer_ptrs(self.buf, cc.ranks))
-            self.bar = ptr_array(cc.heap.peer_ptrs(self.barrier, cc.ranks))
-            # 128 piece flags per row block, written by the ranks that push their rows into this rank's buffer
-            self.piece_flags = cc.heap.alloc(((M // 128 + 1) * 128,), torch.int32).zero_()
-            self.chunk_flags = ptr_array(cc.heap.peer_ptrs(self.piece_flags, cc.ranks))
-            self.go = torch.zeros(1, dtype=torch.int32, device=cc.device)
+            self.ready = cc.heap.alloc((M // 128 + 1,), torch.int32).zero_()
+            peers = [r for r in range(cc.tp) if r != cc.idx]
+            bufs, rdy = cc.heap.peer_ptrs(self.buf, cc.ranks), cc.heap.peer_ptrs(self.ready, cc.ranks)
+            self.n_push = len(peers)
+            self.push_row0 = cc.idx * self.rows
+            self.push_dst = ptr_array([bufs[r] + self.push_row0 * K * 2 for r in peers])
+            self.push_ready = ptr_array([rdy[r] for r in peers])
         else:
             self.buf = torch.empty(M, K, dtype=torch.bfloat16 if cc.device.type == "cuda" else torch.float32, device=cc.device)
 
     def mine(self) -> torch.Tensor:
         return self.buf[self.cc.idx * self.rows:(self.cc.idx + 1) * self.rows]
 
+    def push_args(self):
+        """Arguments that make a layer-norm kernel writing :meth:`mine` deliver the rows to the peers as well
+        (``None`` on the NCCL path)."""
+        return self if self.cc.fused else None
+
+    def push(self, src: Optional[torch.Tensor] = None) -> None:
+        """Stand-alone push: copy ``src`` (default: the rows already in :meth:`mine`) to the peers and publish."""
+        cc = self.cc
+        if not cc.fused:
+            if src is not None:
+                self.mine().copy_(src)
+            return
+        mine = self.mine()
+        s = mine if src is None else src.contiguous()
+        rc = cc.lib.tnnb_tp_push(_lib.ptr(s), _lib.ptr(mine) if src is not None else None, self.rows, self.K, self.n_push,
+                                 self.push_dst, self.push_ready, self.push_row0, _lib.stream())
+        _lib.check_rc(rc, "tnnb_tp_push")
+        LAUNCHES["count"] += 1
+
     def gemm(self, w: torch.Tensor, b_t: bool = False, bias=None, gelu_preact: Optional[torch.Tensor] = None,
-             dgelu_of: Optional[torch.Tensor] = None) -> torch.Tensor:
+             dgelu_of: Optional[torch.Tensor] = None, force_bn: int = 0) -> torch.Tensor:
         """``epilogue(AllGather(rows) @ op(w).T)`` -> ``[M, N]``."""
         cc = self.cc
         N = w.shape[1] if b_t else w.shape[0]
@@ -141,37 +179,45 @@ class GatherSite:
                 return gemm(self.buf, w, b_t=b_t, bias=bias, gelu=True, save_preact=gelu_preact)
             return gemm(self.buf, w, b_t=b_t, bias=bias, dgelu_of=dgelu_of)
         out = torch.empty(self.M, N, dtype=torch.bfloat16, device=cc.device)
-        pass  # the call number lives in cc.tick (device memory), bumped once per forward and backward pass
-        epi, aux = (1, gelu_preact) if gelu_preact is not None else (2, dgelu_of) if dgelu_of is not None else (0, None)
-        rc = cc.lib.tnnb_gemm_comm(1, self.M, N, self.K, int(b_t), _lib.ptr(self.buf), self.K, _lib.ptr(w), w.stride(0),
-                                   _lib.ptr(out), N, _lib.ptr(bias), cc.tp, cc.idx, self.rows, 0, _lib.ptr(cc.tick), self.bar, self.src,
-                                   self.chunk_flags, _lib.ptr(self.go), None, None, None, None, 0, epi,
-                                   _lib.ptr(aux), _lib.ptr(_lib.status_word(cc.device)), _lib.stream())
-        _lib.check_rc(rc, "tnnb_gemm_comm(all-gather)")
+        flags = (_EPI_BIAS if bias is not None else 0) | (_EPI_GELU if gelu_preact is not None else 0) | \
+                (_EPI_DGELU if dgelu_of is not None else 0)
+        aux = gelu_preact if gelu_preact is not None else dgelu_of
+        rc = cc.lib.tnnb_gemm_tp(1, _lib.ptr(self.buf), _lib.ptr(w), _lib.ptr(out), self.M, N, self.K, int(b_t), self.K,
+                                 w.stride(0), N, _lib.ptr(bias), _lib.ptr(dgelu_of), _lib.ptr(gelu_preact),
+                                 aux.stride(0) if aux is not None else 0, flags, cc.tp, cc.idx, self.rows,
+                                 _lib.ptr(self.pass_ctr), _lib.ptr(self.ready), None, 0, None, force_bn,
+                                 _lib.ptr(_lib.status_word(cc.device)), _lib.stream())
+        _lib.check_rc(rc, "tnnb_gemm_tp(all-gather)")
         LAUNCHES["count"] += 1
         return out
 
 
 class ScatterSite:
-    """Inbox and per-tile flags of one GEMM -> reduce-scatter call site (output ``[M/tp, N]``)."""
+    """Inbox and arrival counters of one GEMM -> reduce-scatter call site (output ``[M/tp, N]``).
 
-    def __init__(self, cc: CommContext, M: int, N: int):
-        self.cc, self.M, self.N, self.epoch = cc, M, N, 0
+    :meth:`gemm` computes this rank's partial sums of ALL rows: the rows it owns stay local (bias added), the
+    others go straight from the epilogue into their owner's inbox. The sum over ranks is formed by whoever reads
+    the result: a layer-norm kernel given :meth:`pull_args`, or :meth:`resolve`."""
+
+    def __init__(self, cc: CommContext, M: int, N: int, pass_ctr: Optional[torch.Tensor] = None):
+        self.cc, self.M, self.N = cc, M, N
         self.rows = M // cc.tp
+        self.pass_ctr = pass_ctr
         if cc.fused:
-            tiles = 8 * (self.rows // 128) * ((N + 127) // 128)  # one flag per (tile, 32-row quarter, column half)
-            self.inbox = cc.heap.alloc((cc.tp, self.rows, N), torch.bfloat16)
-            self.flags = cc.heap.alloc((cc.tp, tiles), torch.int32).zero_()
-            ib, fl = cc.heap.peer_ptrs(self.inbox, cc.ranks), cc.heap.peer_ptrs(self.flags, cc.ranks)
-            slot_b, slot_f = self.rows * N * 2, tiles * 4
-            # on owner o, the slot that belongs to me is slot index cc.idx
-            self.inbox_remote = ptr_array([ib[o] + cc.idx * slot_b for o in range(cc.tp)])
-            self.flag_remote = ptr_array([fl[o] + cc.idx * slot_f for o in range(cc.tp)])
-            self.inbox_local = ptr_array([ib[cc.idx] + s * slot_b for s in range(cc.tp)])
-            self.flag_local = ptr_array([fl[cc.idx] + s * slot_f for s in range(cc.tp)])
+            self.inbox = cc.heap.alloc((cc.tp, self.rows, N), torch.bfloat16)   # slot s: partial sums from rank s
+            self.arrived = cc.heap.alloc((self.rows // 128 + 1,), torch.int32).zero_()
+            ib, ar = cc.heap.peer_ptrs(self.inbox, cc.ranks), cc.heap.peer_ptrs(self.arrived, cc.ranks)
+            slot = self.rows * N * 2
+            self._remote_out = [ib[o] + cc.idx * slot for o in range(cc.tp)]  # my slot on owner o
+            self.arrived_ptrs = ptr_array(ar)
+            peers = [r for r in range(cc.tp) if r != cc.idx]
+            self.n_pull = len(peers)
+            self.pull_src = ptr_array([self.inbox[r].data_ptr() for r in peers])
+            self.units = 4 * ((N + 31) // 32) * self.n_pull   # what one pass adds to each 128-row counter
 
-    def gemm(self, a: torch.Tensor, w: torch.Tensor, b_t: bool = False, bias=None) -> torch.Tensor:
-        """``ReduceScatter_rows(a @ op(w).T) + bias`` -> ``[M/tp, N]`` (a holds this rank's K slice)."""
+    def gemm(self, a: torch.Tensor, w: torch.Tensor, b_t: bool = False, bias=None, force_bn: int = 0) -> torch.Tensor:
+        """This rank's rows of ``a @ op(w).T`` (+ bias) -> ``[M/tp, N]``: the complete reduce-scatter result on the
+        NCCL path, the local partial sum on the fused path (a holds this rank's K slice)."""
         cc = self.cc
         if not cc.fused:
             full = gemm(a, w, b_t=b_t)
@@ -188,13 +234,32 @@ class ScatterSite:
                 out = (out.float() + bias.float()).to(out.dtype)
             return out
         out = torch.empty(self.rows, self.N, dtype=torch.bfloat16, device=cc.device)
-        pass  # see GatherSite.gemm
         K = a.shape[1]
-        rc = cc.lib.tnnb_gemm_comm(2, self.M, self.N, K, int(b_t), _lib.ptr(a), a.stride(0), _lib.ptr(w), w.stride(0),
-                                   _lib.ptr(out), self.N, _lib.ptr(bias), cc.tp, cc.idx, self.rows, 0, _lib.ptr(cc.tick), None, None,
-                                   None, None, self.inbox_remote, self.inbox_local, self.flag_remote, self.flag_local,
-                                   self.N, 0, None, _lib.ptr(_lib.status_word(cc.device)), _lib.stream())
-        _lib.check_rc(rc, "tnnb_gemm_comm(reduce-scatter)")
+        outs = list(self._remote_out)
+        outs[cc.idx] = out.data_ptr()
+        rc = cc.lib.tnnb_gemm_tp(2, _lib.ptr(a), _lib.ptr(w), None, self.M, self.N, K, int(b_t), a.stride(0), w.stride(0), 0,
+                                 _lib.ptr(bias), None, None, 0, _EPI_BIAS if bias is not None else 0, cc.tp, cc.idx, self.rows,
+                                 _lib.ptr(self.pass_ctr), None, ptr_array(outs), self.N, self.arrived_ptrs, force_bn,
+                                 _lib.ptr(_lib.status_word(cc.device)), _lib.stream())
+        _lib.check_rc(rc, "tnnb_gemm_tp(reduce-scatter)")
+        LAUNCHES["count"] += 1
+        return out
+
+    def pull_args(self):
+        """Arguments that make a layer-norm kernel add the peers' partial sums to the local one (``None`` on the
+        NCCL path, where :meth:`gemm` already returned the sum)."""
+        return self if self.cc.fused else None
+
+    def resolve(self, partial: torch.Tensor) -> torch.Tensor:
+        """Stand-alone form of the sum: ``partial`` + the peers' partial sums."""
+        cc = self.cc
+        if not cc.fused:
+            return partial
+        out = torch.empty_like(partial)
+        rc = cc.lib.tnnb_tp_resolve(_lib.ptr(partial), _lib.ptr(out), self.rows, self.N, self.n_pull, self.pull_src,
+                                    _lib.ptr(self.arrived), _lib.ptr(self.pass_ctr), self.units,
+                                    _lib.ptr(_lib.status_word(cc.device)), _lib.stream())
+        _lib.check_rc(rc, "tnnb_tp_resolve")
         LAUNCHES["count"] += 1
         return out
 

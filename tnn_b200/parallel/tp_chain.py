@@ -3,7 +3,8 @@
 Rows of the residual stream are split over the tensor-parallel ranks (sequence parallelism): the
 layernorm / residual / dropout kernels work on ``M/tp`` rows, the attention and MLP GEMMs on all
 ``M`` rows but ``1/tp`` of the heads / hidden width. Per block and direction there are two
-all-gather->GEMM and two GEMM->reduce-scatter launches; no stand-alone collective is issued.
+all-gather->GEMM and two GEMM->reduce-scatter hand-offs; the rows travel inside the layer-norm kernels and the
+GEMM epilogues (pushed with peer stores), so no stand-alone collective or copy kernel is issued.
 """
 from __future__ import annotations
 
@@ -32,22 +33,28 @@ class _TPGPTChain(_Segment):
 
     def _make_sites(self, M: int, E: int):
         cc = self.cc
+        # pass counters of this set of sites: one per direction, bumped at the start of every pass
+        cf, cb = cc.new_pass_counter(), cc.new_pass_counter()
         sites = []
         for es in self.blocks:
             fc1 = es[5].layer
             F = fc1.output_features // cc.tp
             sites.append({
-                "g1": GatherSite(cc, M, E), "g2": GatherSite(cc, M, E),          # forward: LN1 / LN2 outputs
-                "gb1": GatherSite(cc, M, E), "gb2": GatherSite(cc, M, E),        # backward: dY of out-proj / fc2
-                "s_out": ScatterSite(cc, M, E), "s_fc2": ScatterSite(cc, M, E),  # forward reduce-scatters
-                "s_qkv": ScatterSite(cc, M, E), "s_fc1": ScatterSite(cc, M, E),  # backward reduce-scatters
-                "F": F,
+                "g1": GatherSite(cc, M, E, cf), "g2": GatherSite(cc, M, E, cf),          # forward: LN1 / LN2 outputs
+                "gb1": GatherSite(cc, M, E, cb), "gb2": GatherSite(cc, M, E, cb),        # backward: dY of out-proj / fc2
+                "s_out": ScatterSite(cc, M, E, cf), "s_fc2": ScatterSite(cc, M, E, cf),  # forward reduce-scatters
+                "s_qkv": ScatterSite(cc, M, E, cb), "s_fc1": ScatterSite(cc, M, E, cb),  # backward reduce-scatters
+                "F": F, "pass_f": cf, "pass_b": cb,
             })
         return sites
 
-    def _ln_into(self, site: GatherSite, x, pending, ln, p, seed):
+    def _ln_into(self, site: GatherSite, x, pending, pend_site, ln, p, seed):
+        """Layer norm of ``x + dropout(pending)`` straight into this rank's rows of a gather site; on the fused
+        path the kernel also adds the peers' share of ``pending`` and delivers the result to the peers."""
         tgt = site.mine()
-        xo, h, mean, rstd = raw.layernorm_fwd(x, pending, ln.params[0], ln.params[1], ln.epsilon, p, seed, h_out=tgt)
+        xo, h, mean, rstd = raw.layernorm_fwd(x, pending, ln.params[0], ln.params[1], ln.epsilon, p, seed, h_out=tgt,
+                                              tp_pull=pend_site.pull_args() if pend_site is not None else None,
+                                              tp_push=site.push_args())
         if h.data_ptr() != tgt.data_ptr():
             tgt.copy_(h)
         return xo, mean, rstd
@@ -67,14 +74,14 @@ class _TPGPTChain(_Segment):
             self.site_ring[slot] = (M, self._make_sites(M, E))
         sites = ctx["sites"] = self.site_ring[slot][1]
         Ms = M // cc.tp
-        cc.tick.add_(1)  # new call number for every fused GEMM of this pass
+        sites[0]["pass_f"].add_(1)  # new pass number for every hand-off of this pass
         x = _flat2d(x3).contiguous() if self.in_is_shard else _flat2d(x3)[cc.idx * Ms:(cc.idx + 1) * Ms].contiguous()
-        pending, p_pend, seed_pend = None, 0.0, 0
+        pending, pend_site, p_pend, seed_pend = None, None, 0.0, 0
         saved = []
         for es, st in zip(self.blocks, sites):
             ln1, attn, drop1, _, ln2, fc1, _, fc2, drop2, _ = (e.layer for e in es)
             s = {}
-            x, s["mean1"], s["rstd1"] = self._ln_into(st["g1"], x, pending, ln1, p_pend, seed_pend)
+            x, s["mean1"], s["rstd1"] = self._ln_into(st["g1"], x, pending, pend_site, ln1, p_pend, seed_pend)
             s["x"], s["p_in"], s["seed_in"], s["had_pending"] = x, p_pend, seed_pend, pending is not None
             wqkv, bqkv, wo, bo = attn.params
             qkv = st["g1"].gemm(wqkv, bias=bqkv)                                  # [M, 3E/tp]
@@ -83,22 +90,25 @@ class _TPGPTChain(_Segment):
             y1 = st["s_out"].gemm(a, wo, bias=bo)                                 # [Ms, E]
             p1 = drop1.dropout_rate if drop1.training else 0.0
             seed1 = drop1.step_seed(ctx)
-            x1, s["mean2"], s["rstd2"] = self._ln_into(st["g2"], x, y1, ln2, p1, seed1)
+            x1, s["mean2"], s["rstd2"] = self._ln_into(st["g2"], x, y1, st["s_out"], ln2, p1, seed1)
             z = torch.empty(M, st["F"], dtype=x.dtype, device=x.device)
             gact = st["g2"].gemm(fc1.params[0], bias=fc1.params[1], gelu_preact=z)  # [M, 4E/tp]
             y2 = st["s_fc2"].gemm(gact, fc2.params[0], bias=fc2.params[1])        # [Ms, E]
             s.update(qkv=qkv, a=a, lse=lse, x1=x1, z=z, g=gact, p1=p1, seed1=seed1, heads=heads)
             saved.append(s)
-            x, pending = x1, y2
+            x, pending, pend_site = x1, y2, st["s_fc2"]
             p_pend = drop2.dropout_rate if drop2.training else 0.0
             seed_pend = drop2.step_seed(ctx)
         ctx["saved"], ctx["dims"], ctx["tail"] = saved, (B, S, E), (p_pend, seed_pend)
         if self.final is not None:
             ln = self.final.layer
-            xf, hf, mean, rstd = raw.layernorm_fwd(x, pending, ln.params[0], ln.params[1], ln.epsilon, p_pend, seed_pend)
+            xf, hf, mean, rstd = raw.layernorm_fwd(x, pending, ln.params[0], ln.params[1], ln.epsilon, p_pend, seed_pend,
+                                                   tp_pull=pend_site.pull_args() if pend_site is not None else None)
             ctx["final"] = (xf, mean, rstd)
             out = hf
         else:
+            if pend_site is not None:
+                pending = pend_site.resolve(pending)
             out = raw.binary(x, raw.dropout(pending, p_pend, seed_pend), "add")
         # downstream layers (the vocabulary head) see only this rank's rows
         vals[id(self.out_node)] = out.reshape(1, Ms, E)
@@ -112,15 +122,16 @@ class _TPGPTChain(_Segment):
         M = B * S
         Ms = M // cc.tp
         g = _flat2d(g).contiguous()
-        cc.tick.add_(1)
         p_pend, seed_pend = ctx["tail"]
         sites = ctx["sites"]
+        sites[0]["pass_b"].add_(1)
         last = sites[-1]
         if self.final is not None:
             ln = self.final.layer
             xf, mean, rstd = ctx["final"]
             dres, dpend = raw.layernorm_bwd(g, xf, mean, rstd, ln.params[0], None, True, p_pend, seed_pend, ln.grads[0],
-                                            ln.grads[1], ddelta_out=last["gb2"].mine() if g.is_cuda else None)
+                                            ln.grads[1], ddelta_out=last["gb2"].mine() if g.is_cuda else None,
+                                            tp_push=last["gb2"].push_args() if g.is_cuda else None)
         else:
             dres, dpend = g, raw.dropout(g, p_pend, seed_pend)
         for bi in reversed(range(len(self.blocks))):
@@ -129,8 +140,8 @@ class _TPGPTChain(_Segment):
             wqkv, bqkv, wo, bo = attn.params
             # ---- fc2 (row parallel): gather dY, dgrad with GELU' ----
             tgt = st["gb2"].mine()
-            if dpend.data_ptr() != tgt.data_ptr():
-                tgt.copy_(dpend)
+            if dpend.data_ptr() != tgt.data_ptr():  # not written in place (and delivered) by a layer-norm backward
+                st["gb2"].push(dpend)
             raw.colsum_accum(tgt, fc2.grads[1])
             dz = st["gb2"].gemm(fc2.params[0], b_t=True, dgelu_of=s["z"])          # [M, 4E/tp]
             gemm(st["gb2"].buf, s["g"], a_t=True, b_t=True, out=fc2.grads[0], atomic=True)
@@ -140,10 +151,11 @@ class _TPGPTChain(_Segment):
             dh2 = st["s_fc1"].gemm(dz, fc1.params[0], b_t=True)                    # [Ms, E]
             # ---- LN2 + residual + dropout ----
             dx1, dy1 = raw.layernorm_bwd(dh2, s["x1"], s["mean2"], s["rstd2"], ln2.params[0], dres, True, s["p1"], s["seed1"],
-                                         ln2.grads[0], ln2.grads[1], ddelta_out=st["gb1"].mine() if dh2.is_cuda else None)
+                                         ln2.grads[0], ln2.grads[1], ddelta_out=st["gb1"].mine() if dh2.is_cuda else None,
+                                         tp_pull=st["s_fc1"].pull_args(), tp_push=st["gb1"].push_args() if dh2.is_cuda else None)
             tgt = st["gb1"].mine()
             if dy1.data_ptr() != tgt.data_ptr():
-                tgt.copy_(dy1)
+                st["gb1"].push(dy1)
             # ---- attention output projection (row parallel) ----
             raw.colsum_accum(tgt, attn.grads[3])
             da = st["gb1"].gemm(wo, b_t=True)                                      # [M, E/tp]
@@ -154,9 +166,11 @@ class _TPGPTChain(_Segment):
             raw.colsum_accum(dqkv, attn.grads[1])
             dh1 = st["s_qkv"].gemm(dqkv, wqkv, b_t=True)                           # [Ms, E]
             # ---- LN1 (+ the previous block's trailing residual add + dropout) ----
-            prev_tgt = sites[bi - 1]["gb2"].mine() if (bi > 0 and dh1.is_cuda) else None
+            prev = sites[bi - 1]["gb2"] if (bi > 0 and dh1.is_cuda and s["had_pending"]) else None
             dres, dpend = raw.layernorm_bwd(dh1, s["x"], s["mean1"], s["rstd1"], ln1.params[0], dx1, s["had_pending"],
-                                            s["p_in"], s["seed_in"], ln1.grads[0], ln1.grads[1], ddelta_out=prev_tgt)
+                                            s["p_in"], s["seed_in"], ln1.grads[0], ln1.grads[1],
+                                            ddelta_out=prev.mine() if prev is not None else None,
+                                            tp_pull=st["s_qkv"].pull_args(), tp_push=prev.push_args() if prev is not None else None)
         if self.in_is_shard:
             if id(self.in_node) not in no_grad_nodes:
                 _accum(gvals, self.in_node, dres.reshape(1, Ms, E))
