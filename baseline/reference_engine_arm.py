@@ -89,6 +89,8 @@ def run_engine(model: str, batch: int, warm: int, steps: int, dtype: str = "", t
                    model_path="")
         if dtype:
             cfg.update(io_dtype=dtype, param_dtype=dtype, compute_dtype=dtype)
+        if os.environ.get("TNNB_REF_MODEL"):  # e.g. gpt2_small: the reference's GPT-2 small without the cuDNN attention block
+            cfg.update(model_name=os.environ["TNNB_REF_MODEL"])
         t_short, _ = _run(trainer, root, cfg, warm, timeout)
         t_long, loss = _run(trainer, root, cfg, warm + steps, timeout)
     finally:
@@ -100,7 +102,7 @@ def run_engine(model: str, batch: int, warm: int, steps: int, dtype: str = "", t
         "value": round(value, 1), "ms_per_step": round(ms / steps, 3), "loss_last": loss,
         "dtype": "/".join(str(v) for v in used.values()) + " (io/param/compute of the reference's gpt2_config.json"
                  + (", overridden by TNNB_REF_DTYPE)" if dtype else ")"),
-        "path": "reference C++/cuDNN engine: examples/trainer.cpp --config configs/gpt2_config.json (model flash_gpt2_small), "
+        "path": f"reference C++/cuDNN engine: examples/trainer.cpp --config configs/gpt2_config.json (model {cfg['model_name']}), "
                 f"built by baseline/build_reference_engine.py{' --fix-block-engine (Block forwards engine and backend handle to its sub-layers; the unmodified build dereferences a null engine on the first step)' if fixed else ''}; wall clock of the step loop, ({warm + steps}-step run) - ({warm}-step run)",
         "h2d_bytes_per_step": batch * 1024 * (4 + 4), "d2h_bytes_per_step": 8,
         "run_ms": {"short": t_short, "long": t_long},

@@ -6,7 +6,7 @@ over ranks). Launch with one process per GPU:
 Shapes are those of GPT-2 small with 16 sequences of 1024 tokens per tensor-parallel pair. A hand-off is timed
 together with the layer norm it rides on, in three forms:
 
-    fused   layer norm that pushes its rows -> all-gather GEMM        |  GEMM that pushes partial sums -> layer norm that pulls
+    fused   layer norm, rows sent to the peers by copy engine -> all-gather GEMM  |  GEMM that pushes partial sums -> layer norm that pulls
     nccl    layer norm -> all_gather -> GEMM                           |  GEMM -> reduce_scatter -> layer norm
     local   layer norm -> GEMM on an already complete operand          |  GEMM -> layer norm (no communication at all)
 
@@ -27,7 +27,7 @@ tp = dist.get_world_size()
 topo = Topology(f"tp{tp}")
 dev = torch.device("cuda", local)
 heap = SymmetricHeap(2 << 30, None, dev)
-cc = CommContext(topo, heap, True, dev)
+cc = CommContext(topo, heap, True, dev)   # TNNB_TP_PUSH=ln selects the in-kernel push for comparison
 cn = CommContext(topo, None, False, dev)
 PEAK = 1393.6e12  # measured sustained cuBLAS bf16 rate of this pool (MEASURED_PEAKS.json); burst 1681.9e12
 LINK = 770e9      # measured peer-copy bandwidth per direction
@@ -58,7 +58,8 @@ t_ln = timeit(lambda: raw.layernorm_fwd(x, None, gamma, beta, 1e-5))
 for name, N in (("QKV", 3 * E // tp), ("fc1", 4 * E // tp)):
     ctr = cc.new_pass_counter(); site = GatherSite(cc, M, E, ctr); site_n = GatherSite(cn, M, E); w = bf(N, E)
     def fused():
-        ctr.add_(1); raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site.mine(), tp_push=site.push_args()); return site.gemm(w)
+        ctr.add_(1); raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site.mine(), tp_push=site.push_args()); site.after_produce()
+        y = site.gemm(w); cc.join(); return y
     def nccl():
         raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site_n.mine()); return site_n.gemm(w)
     full = bf(M, E)
@@ -84,7 +85,21 @@ for name, K in (("attention out", E // tp), ("fc2", 4 * E // tp)):
     roof = max(2.0 * M * E * K / PEAK, bytes_link / LINK) * 1e6
     out.append({"op": f"GEMM -> reduce-scatter ({name}) N={E} K={K}", "fused_us": tf, "nccl_us": tn, "local_us": tl, "gemm_us": tg, "ln_us": t_ln2,
                 "exposed_us": tf - tl, "roofline_us": roof, "frac": roof / max(tf - t_ln2, 1e-3), "speedup_vs_nccl": tn / tf})
+# the pieces on their own: what a push costs the kernel that carries it
+ctr = cc.new_pass_counter(); site = GatherSite(cc, M, E, ctr)
+def ln_push():
+    raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site.mine(), tp_push=site.push_args()); site.after_produce(); cc.join()
+def push_only():
+    site.push(x); cc.join()
+parts = {"push_mode": 0.0 if cc.push_mode == "ce" else 1.0, "ln_fwd_us": t_ln, "ln_fwd_then_push_us": timeit(ln_push),
+         "push_only_us": timeit(push_only)}
+for K in (E // tp, 4 * E // tp):
+    ctr2 = cc.new_pass_counter(); s2 = ScatterSite(cc, M, E, ctr2); a = bf(M, K); w = bf(E, K)
+    parts[f"gemm_rs_push_K{K}_us"] = timeit(lambda: s2.gemm(a, w))
+    parts[f"gemm_plain_K{K}_us"] = timeit(lambda: gemm(a, w))
+parts["bytes_pushed_MB"] = (tp - 1) * rows * E * 2 / 1e6
 if dist.get_rank() == 0:
+    print(json.dumps({k: round(v, 2) for k, v in parts.items()}), flush=True)
     for r in out:
         print(json.dumps({k: (round(v, 2) if isinstance(v, float) else v) for k, v in r.items()}), flush=True)
 torch.cuda.synchronize(); dist.barrier()

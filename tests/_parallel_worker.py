@@ -50,6 +50,11 @@ def main():
         t.close()
         dist.destroy_process_group()
         return
+    if mode == "tpeq":
+        # plain SGD: the update is proportional to the gradient, so rounding noise stays proportional too (the first
+        # Adam steps move every element by the full learning rate in the direction of a sign that noise can flip)
+        cfg = TrainingConfig.from_dict({"model_name": "tiny_gpt", "batch_size": 2, "device_type": "CUDA", "seed": 5,
+                                        "optimizer": {"type": "sgd", "learning_rate": 0.05, "momentum": 0.9}})
     layout = {"dp": f"dp{world}", "tp": f"tp2dp{world // 2}" if world > 2 else "tp2",
               "tpeq": f"tp2dp{world // 2}" if world > 2 else "tp2"}[mode]
     t = ParallelTrainer(cfg, layout=layout, fused=fused, log=False, heap_bytes=256 << 20)
@@ -66,11 +71,23 @@ def main():
     _lib.check_status()
     if mode == "tpeq":  # gather the shards into an unsharded model and hand its parameters back
         from tnn_b200.parallel.tp import gather_full_state
-        t._refresh_master()
+        g = t.graph
+        if hasattr(t.optimizer, "sites"):
+            # sharded optimizer: a rank holds fp32 master values only for the slices it updates. Collect the exact
+            # fp32 values of the replicated region from their owners (the sharded region is updated by this rank
+            # alone when dp = 1); the compute copy would only give them rounded to bf16.
+            mine = torch.zeros_like(g.trainable_mask)
+            for s in t.optimizer.sites:
+                mine[s["lo"]:s["hi"]] = True
+            b = g.shard_boundary
+            rep = torch.where(mine[:b], g.master_flat[:b], torch.zeros_like(g.master_flat[:b]))
+            dist.all_reduce(rep)
+            g.master_flat[:b].copy_(rep)
+            assert bool(mine[b:].all()) or world > 2
         full = zoo.create(cfg.model_name).compile(device="cpu", seed=cfg.seed)
         gather_full_state(t.graph, full, t.topo)
         if rank == 0:
-            torch.save({"params": full.params_flat.float().cpu(), "losses": losses}, sys.argv[3])
+            torch.save({"params": full.master_flat.float().cpu(), "losses": losses}, sys.argv[3])
             print("RESULT " + json.dumps({"losses": losses}), flush=True)
         t.close()
         dist.destroy_process_group()

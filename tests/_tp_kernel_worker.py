@@ -39,6 +39,8 @@ def main():
     topo = Topology(f"tp{tp}")
     heap = SymmetricHeap(512 << 20, None, dev)
     cc = CommContext(topo, heap, True, dev)
+    if len(sys.argv) > 1:
+        cc.push_mode = sys.argv[1]  # "split" (default), "gemm", "ce" or "ln": see CommContext.push_mode
     cn = CommContext(topo, None, False, dev)  # NCCL path of the same classes
     torch.manual_seed(1000 + rank)
     res = {}
@@ -60,7 +62,9 @@ def main():
             x = bf(rows, K)
             ctr.add_(1)
             raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site.mine(), tp_push=site.push_args())
+            site.after_produce()
             y = site.gemm(w, b_t=b_t, bias=bias)
+            cc.join()
             raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site_n.mine())
             y_n = site_n.gemm(w, b_t=b_t, bias=bias)
             xs = torch.cat(gather(x, tp)).float()
@@ -70,6 +74,10 @@ def main():
             for name, got, want in (("ag_vs_fp32", y, ref), ("ag_vs_nccl", y, y_n), ("ag_buf", site.buf, h)):
                 e, ok = err(got, want)
                 worst, all_ok = max(worst, e), all_ok and ok
+            # a site may be written again only after every rank has finished reading it; a training step has the
+            # dependencies between its kernels for that, this loop needs a barrier
+            torch.cuda.synchronize()
+            dist.barrier()
         _lib.check_status()
     res["ag_worst"] = worst
     res["ag_ok"] = all_ok
@@ -98,12 +106,17 @@ def main():
             for name, got, want in (("rs_vs_fp32", red, mine), ("rs_vs_nccl", red, full_n), ("rs_ln_x", xo, x.float() + mine)):
                 e, ok = err(got, want)
                 worst, all_ok = max(worst, e), all_ok and ok
+            torch.cuda.synchronize()
+            dist.barrier()
         _lib.check_status()
     res["rs_worst"] = worst
     res["rs_ok"] = all_ok
     flags = torch.tensor([int(res["ag_ok"]), int(res["rs_ok"])], device=dev)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     res["all_ranks_ok"] = bool(flags.min().item())
+    w = torch.tensor([res["ag_worst"], res["rs_worst"]], device=dev)
+    dist.all_reduce(w, op=dist.ReduceOp.MAX)
+    res["ag_worst"], res["rs_worst"] = float(w[0]), float(w[1])
     torch.cuda.synchronize()
     dist.barrier()
     if rank == 0:

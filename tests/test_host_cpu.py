@@ -66,6 +66,38 @@ def test_packets_have_36_byte_headers_and_reassemble_out_of_order():
     assert done is not None and done[0] == 42 and bytes(done[1]) == wire and agg.pending() == 0
 
 
+def _packet(packet_len, msg_len, msg_id, offset, total, payload):
+    return struct.pack("<BBBQQQIIB", 1, 0, 1, packet_len, msg_len, msg_id, offset, total, 0) + payload
+
+
+def test_aggregator_rejects_malformed_headers():
+    """Header fields arrive from the network: a fragment longer than its message, an offset that wraps, a message
+    or packet count beyond the receiver's limits must all be refused before anything is allocated or copied."""
+    import pytest
+    bad = [
+        _packet(4096, 8, 1, 1, 2, b"x" * 4096),                 # last fragment longer than the message (used to underflow)
+        _packet(8, 8, 2, 5, 2, b"x" * 8),                        # packet index >= packet count
+        _packet(8, 16, 3, 0, 0, b"x" * 8),                       # zero packets
+        _packet(4, 8, 4, 2, 4, b"x" * 4),                        # fragment 2 of 4 x 4 bytes lies beyond an 8-byte message
+        _packet(1, 1 << 40, 5, 0, 1 << 20, b"x"),                # announces a terabyte
+        _packet(1, 64, 6, 0, 100, b"x"),                         # more packets than bytes
+        _packet(2**63, 2**63 + 8, 7, 3, 4, b""),                 # offset arithmetic would wrap
+    ]
+    for pkt in bad:
+        agg = H.Aggregator(1 << 20, 1 << 10)
+        with pytest.raises(Exception):
+            agg.feed(pkt)
+    # limits are per receiver: the same well-formed message passes a roomy aggregator and is refused by a tight one
+    wire = bytes(300)
+    pk = H.slice_message(wire, 9, 100)
+    tight = H.Aggregator(256, 16)
+    with pytest.raises(Exception):
+        tight.feed(pk[0])
+    roomy = H.Aggregator(1 << 20, 16)
+    out = [roomy.feed(p) for p in pk]
+    assert out[-1] is not None and bytes(out[-1][1]) == wire
+
+
 def test_tconfig_type_tags_round_trip_and_profiler_merge():
     c = H.TConfig()
     c.name, c.type = "fc", "dense"

@@ -25,15 +25,15 @@ def launch(n, mode, kind, out):
     return json.loads(line[7:])
 
 
-def single_process_reference(global_batch_sets, tmp):
+def single_process_reference(global_batch_sets, tmp, optimizer=None):
     zoo.register_model("tiny_gpt", lambda: zoo.gpt2(128, 2, 2, "t", seq_len=128, vocab=203, drop=0.0))
     cfg = TrainingConfig.from_dict({"model_name": "tiny_gpt", "batch_size": 4, "device_type": "CUDA", "seed": 5,
-                                    "optimizer": {"type": "adamw", "learning_rate": 1e-2, "weight_decay": 0.01}})
+                                    "optimizer": optimizer or {"type": "adamw", "learning_rate": 1e-2, "weight_decay": 0.01}})
     t = Trainer(cfg, log=False)
     losses = []
     for seq in global_batch_sets:
         losses.append(float(t.train_step(seq[:, :-1].contiguous(), seq[:, 1:].contiguous()).item()))
-    p = t.graph.params_flat.float().cpu()
+    p = (t.graph.master_flat if optimizer is not None else t.graph.params_flat).float().cpu()  # fp32 master on request
     t.close()
     return losses, p
 
@@ -82,28 +82,57 @@ def test_tp2_trains(kind, tmp_path):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("kind", ["fused", "nccl"])
-def test_tp2_matches_single_process(kind, tmp_path):
-    """Tensor parallelism must not change the training run: same initial weights and batches as one process,
-    parameters compared after four AdamW steps (the two ranks see the same sequences, each half of the rows)."""
-    out = str(tmp_path / "tpeq.pt")
-    res = launch(2, "tpeq", kind, out)
+def test_tp2_matches_single_process(tmp_path):
+    """Tensor parallelism must not change the training run: same initial weights and batches as one process; what
+    four SGD steps changed in the parameters is compared (the two ranks see the same sequences, each half of the
+    rows). bf16 activations and fp32 atomics make even two single-process runs differ measurably on this tiny
+    model (gradients of the layer-norm gains are sums with heavy cancellation), so the yardstick is measured: the
+    same single-process run with the sequences of every batch in reverse order - the same mathematics in another
+    summation order. The fused kernels and the NCCL path must each stay within a small multiple of that."""
     g = torch.Generator().manual_seed(100)
     sets = [torch.randint(0, 203, (4, 129), generator=g) for _ in range(4)]
-    ref_losses, ref_params = single_process_reference(sets, tmp_path)
-    got = torch.load(out)
-    rel = (got["params"] - ref_params).norm() / ref_params.norm()
-    assert rel < 2e-2, float(rel)
-    assert res["losses"][-1] < res["losses"][0]
+    ref_losses, ref_params = single_process_reference(sets, tmp_path, {"type": "sgd", "learning_rate": 0.05, "momentum": 0.9})
+    start = zoo.create("tiny_gpt").compile(device="cpu", seed=5).master_flat.float()
+    d_ref = ref_params - start
+    assert float(d_ref.norm()) > 0   # the run did move the parameters
+    _, alt_params = single_process_reference([b.flip(0) for b in sets], tmp_path, {"type": "sgd", "learning_rate": 0.05, "momentum": 0.9})
+    floor = float((alt_params - ref_params).norm() / d_ref.norm())
+    deltas, rels, losses = {}, {}, {}
+    for kind in ("fused", "nccl"):
+        out = str(tmp_path / f"tpeq_{kind}.pt")
+        res = launch(2, "tpeq", kind, out)
+        deltas[kind] = torch.load(out)["params"] - start
+        rels[kind] = float((deltas[kind] - d_ref).norm() / d_ref.norm())
+        losses[kind] = res["losses"]
+    rels["between"] = float((deltas["fused"] - deltas["nccl"]).norm() / d_ref.norm())
+    # per-parameter breakdown for the failure message: where the fused run departs from the single-process one
+    full = zoo.create("tiny_gpt").compile(device="cpu", seed=5)
+    worst = []
+    for l in full.layers():
+        for (o, n, _, _), spec in zip(full.layer_slices[id(l)], l.param_specs()):
+            d = float(d_ref[o:o + n].norm())
+            if d > 0:  # share of the total squared error, relative errors of both paths, share of the update norm
+                ef = float((deltas["fused"][o:o + n] - d_ref[o:o + n]).norm())
+                en = float((deltas["nccl"][o:o + n] - d_ref[o:o + n]).norm())
+                worst.append((round(ef ** 2 / float((deltas["fused"] - d_ref).norm()) ** 2, 3), round(ef / d, 3), round(en / d, 3),
+                              round(d ** 2 / float(d_ref.norm()) ** 2, 3), l.name + "." + spec.name))
+    worst.sort(reverse=True)
+    info = (rels, floor, losses, ref_losses, worst[:12])
+    print("tp2 equivalence:", json.dumps(info))
+    bound = 2.0 * floor + 0.03   # fp32 master weights are compared, so what remains is the bf16 arithmetic of the step
+    assert rels["fused"] < bound and rels["nccl"] < bound and rels["between"] < bound, info
+    assert rels["fused"] < 1.5 * rels["nccl"] + 0.01, info
+    assert abs(losses["fused"][-1] - ref_losses[-1]) < 0.3 and abs(losses["fused"][-1] - losses["nccl"][-1]) < 0.05, info
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tp2_kernels_match_fp32_and_nccl():
+@pytest.mark.parametrize("push_mode", ["ln", "split", "gemm", "ce"])
+def test_tp2_kernels_match_fp32_and_nccl(push_mode):
     """The fused hand-offs across two real GPUs against fp32 on gathered operands and against the NCCL path,
-    ragged widths included, three calls per site in a row."""
+    ragged widths included, three calls per site in a row; rows pushed by copy engine or by the layer-norm kernel."""
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29617", os.path.join(HERE, "_tp_kernel_worker.py")]
+           "--master-port", "29617", os.path.join(HERE, "_tp_kernel_worker.py"), push_mode]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, "\n".join(l for l in r.stdout.splitlines() if "WORKER-ERROR" in l)[:3000] + r.stdout[-2000:] + r.stderr[-500:]
     res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])

@@ -47,12 +47,14 @@ class _HeapView:
         raise ValueError("not a heap tensor")
 
 
-def _contexts(tp, dev):
+def _contexts(tp, dev, push_mode="ln"):
     heap = _VirtualHeap(tp, dev)
     ccs = []
     for r in range(tp):
         topo = types.SimpleNamespace(tp=tp, tp_idx=r, tp_ranks=list(range(tp)), tp_group=None)
-        ccs.append(CommContext(topo, heap.view(r), True, dev))
+        cc = CommContext(topo, heap.view(r), True, dev)
+        cc.push_mode = push_mode
+        ccs.append(cc)
     return ccs
 
 
@@ -72,12 +74,15 @@ def _ln_ref(x, gamma, beta, eps=1e-5):
     return (x - m) * torch.rsqrt(v + eps) * gamma.float() + beta.float()
 
 
+@pytest.mark.parametrize("mode", ["ln", "ce"])  # "gemm" needs the ranks' kernels to run at the same time: 2-GPU tests
 @pytest.mark.parametrize("tp,M,K,N,b_t", [(2, 1024, 256, 320, False), (2, 256, 128, 72, False), (2, 1024, 256, 384, True),
                                            (4, 2048, 128, 256, False)])
-def test_layernorm_push_then_gather_gemm(tp, M, K, N, b_t):
+def test_layernorm_push_then_gather_gemm(tp, M, K, N, b_t, mode):
+    """``ln``: the layer-norm kernel stores its rows into the peers' buffers itself; ``ce``: they travel by
+    copy-engine transfers on a side stream, which is joined here before any consumer is launched."""
     torch.manual_seed(0)
     dev = torch.device("cuda")
-    ccs = _contexts(tp, dev)
+    ccs = _contexts(tp, dev, mode)
     ctrs = [cc.new_pass_counter() for cc in ccs]
     sites = [GatherSite(cc, M, K, c) for cc, c in zip(ccs, ctrs)]
     rows = M // tp
@@ -90,6 +95,9 @@ def test_layernorm_push_then_gather_gemm(tp, M, K, N, b_t):
             c.add_(1)
         for r in range(tp):
             raw.layernorm_fwd(xs[r], None, gamma, beta, 1e-5, h_out=sites[r].mine(), tp_push=sites[r].push_args())
+            sites[r].after_produce()
+        for cc in ccs:
+            cc.join()
         outs = [sites[r].gemm(w, b_t=b_t, bias=bias) for r in range(tp)]
         _lib.check_status()
         h = torch.cat([_ln_ref(x, gamma, beta) for x in xs]).bfloat16().float()

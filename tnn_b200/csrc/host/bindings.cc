@@ -252,7 +252,7 @@ PYBIND11_MODULE(_host, m) {
     return d;
   });
   py::class_<Aggregator>(m, "Aggregator")
-      .def(py::init<>())
+      .def(py::init<uint64_t, uint32_t>(), py::arg("max_message_bytes") = 16ull << 30, py::arg("max_packets") = 1u << 22)
       .def("feed", [](Aggregator& a, const std::string& pkt) -> py::object {
         std::string out;
         uint64_t id = 0;
@@ -274,6 +274,7 @@ PYBIND11_MODULE(_host, m) {
       .def(py::init<std::string, int, int, uint64_t>(), py::arg("host") = "127.0.0.1", py::arg("port") = 0,
            py::arg("sockets_per_endpoint") = 4, py::arg("max_packet_size") = 4ull << 20)
       .def("start", &TcpCommunicator::start, py::call_guard<py::gil_scoped_release>())
+      .def("set_max_message_bytes", &TcpCommunicator::set_max_message_bytes)
       .def("endpoint", &TcpCommunicator::endpoint)
       .def("connect", &TcpCommunicator::connect, py::arg("host"), py::arg("port"), py::arg("timeout_s") = 10.0,
            py::call_guard<py::gil_scoped_release>())

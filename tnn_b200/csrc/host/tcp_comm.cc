@@ -279,6 +279,7 @@ void TcpCommunicator::read_loop(std::shared_ptr<Conn> c) {
     try {
       h = read_packet_header(hdr, PacketHeader::kSize);
       if (h.packet_length > max_packet_ + (1ull << 20)) break;  // not a packet of this protocol
+      if (h.msg_length > max_message_) break;                    // larger than this endpoint agrees to buffer
       std::lock_guard<std::mutex> g(c->peer->mu);
       dst = c->peer->agg.reserve(h, &dup);
     } catch (const std::exception&) {

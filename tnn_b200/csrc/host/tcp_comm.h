@@ -48,6 +48,8 @@ class TcpCommunicator {
   void flush(double timeout_s = 30.0);                 // wait until every queued packet has been written
   void stop();
 
+  // Longest message (bytes) this endpoint lets a peer announce; default 16 GiB.
+  void set_max_message_bytes(uint64_t n) { max_message_ = n; }
   uint64_t bytes_sent() const { return bytes_sent_; }
   uint64_t bytes_received() const { return bytes_received_; }
   uint64_t messages_sent() const { return messages_sent_; }
@@ -91,6 +93,7 @@ class TcpCommunicator {
   int port_;
   int sockets_;
   uint64_t max_packet_;
+  std::atomic<uint64_t> max_message_{16ull << 30};  // a header that announces a longer message closes its connection
   int listen_fd_ = -1;
   std::thread acceptor_;
   std::atomic<bool> stopping_{false};

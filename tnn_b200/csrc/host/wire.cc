@@ -166,21 +166,32 @@ std::vector<std::string> slice_message(const std::string& msg, uint64_t msg_id, 
 }
 
 char* Aggregator::reserve(const PacketHeader& h, bool* duplicate) {
-  if (h.packet_offset >= h.total_packets) throw std::runtime_error("packet index out of range");
+  // Every field of the header comes from the peer: nothing is allocated or indexed before it has been checked
+  // against the limits of this aggregator and against the other fields.
+  if (h.total_packets == 0 || h.packet_offset >= h.total_packets) throw std::runtime_error("packet index out of range");
+  if (h.msg_length > max_message_bytes_) throw std::runtime_error("message longer than this receiver accepts");
+  if (h.total_packets > max_packets_) throw std::runtime_error("message split into more packets than this receiver accepts");
+  if (h.packet_length > h.msg_length) throw std::runtime_error("fragment longer than its message");
+  // a message of n bytes needs at most n packets (one byte each); an empty one exactly one
+  if (h.total_packets > std::max<uint64_t>(h.msg_length, 1)) throw std::runtime_error("more packets than message bytes");
+  // Every packet but the last carries the same payload size, so the byte
+  // offset of packet i is i * (size of a non-final packet).
+  uint64_t stride;
+  if (h.total_packets == 1) stride = 0;
+  else if (h.packet_offset + 1 < h.total_packets) stride = h.packet_length;
+  else stride = (h.msg_length - h.packet_length) / (h.total_packets - 1);  // packet_length <= msg_length: no wrap
+  // stride <= msg_length and packet_offset < total_packets <= msg_length <= max_message_bytes_ (< 2^63 / 2^32 is
+  // not guaranteed), so multiply in 128 bits and compare before narrowing
+  const unsigned __int128 off128 = static_cast<unsigned __int128>(stride) * h.packet_offset;
+  if (off128 > h.msg_length || h.packet_length > h.msg_length - static_cast<uint64_t>(off128))
+    throw std::runtime_error("fragment exceeds message length");
+  const uint64_t off = static_cast<uint64_t>(off128);
   Slot& s = slots_[h.msg_serial_id];
   if (s.seen.empty()) {
     s.buf.resize(h.msg_length);
     s.seen.assign(h.total_packets, 0);
   }
   if (s.seen.size() != h.total_packets || s.buf.size() != h.msg_length) throw std::runtime_error("inconsistent fragments for one message");
-  // Every packet but the last carries the same payload size, so the byte
-  // offset of packet i is i * (size of a non-final packet).
-  uint64_t stride;
-  if (h.total_packets == 1) stride = 0;
-  else if (h.packet_offset + 1 < h.total_packets) stride = h.packet_length;
-  else stride = (h.msg_length - h.packet_length) / (h.total_packets - 1);
-  const uint64_t off = stride * h.packet_offset;
-  if (off + h.packet_length > s.buf.size()) throw std::runtime_error("fragment exceeds message length");
   if (duplicate) *duplicate = s.seen[h.packet_offset] != 0;
   return s.buf.empty() ? nullptr : &s.buf[0] + off;
 }

@@ -93,6 +93,15 @@ std::vector<std::string> slice_message(const std::string& msg, uint64_t msg_id, 
 // fills `out`) when the message the packet belongs to is complete.
 class Aggregator {
  public:
+  // Limits on what a peer may make this receiver allocate: the longest message and the largest packet count it
+  // accepts (defaults: 16 GiB and 2^22 packets - a 16 GiB message in 4 KiB packets). Headers beyond them, or
+  // inconsistent with themselves, are rejected with an exception before any memory is touched.
+  explicit Aggregator(uint64_t max_message_bytes = 16ull << 30, uint32_t max_packets = 1u << 22)
+      : max_message_bytes_(max_message_bytes), max_packets_(max_packets) {}
+  void set_limits(uint64_t max_message_bytes, uint32_t max_packets) {
+    max_message_bytes_ = max_message_bytes;
+    max_packets_ = max_packets;
+  }
   bool feed(const char* packet, size_t n, std::string* out, uint64_t* msg_id = nullptr);
   // The two halves of feed() for a receiver that reads a payload straight from a socket into the message:
   // reserve() returns where the payload of the packet described by `h` belongs (`duplicate` tells whether that
@@ -111,6 +120,8 @@ class Aggregator {
     uint64_t packet_size = 0;
   };
   std::map<uint64_t, Slot> slots_;
+  uint64_t max_message_bytes_;
+  uint32_t max_packets_;
 };
 
 }  // namespace tnnb

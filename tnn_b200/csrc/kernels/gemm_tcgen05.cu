@@ -25,6 +25,7 @@
 // raises a CTA-wide abort flag and unwinds (TMEM is always released).
 #include "gemm_tcgen05.h"
 
+#include <cstdlib>
 #include <mutex>
 
 #include "ptx.cuh"
@@ -34,8 +35,12 @@ namespace tnnb {
 
 // Tensor-parallel extension of the CTA-pair kernel (tnnb_gemm_tp; protocol in tp_flags.cuh).
 //   mode 1  all-gather -> GEMM: rows of A that another rank owns are pushed into the local A buffer by
-//           that rank's producing kernel; the TMA producer polls the row block's counter before it loads
-//           a tile of such rows. Tiles of the locally owned rows run first.
+//           that rank; the TMA producer polls the row block's counter before it loads a tile of such rows.
+//           Tiles of the locally owned rows run first. The push itself is done by two extra warps of this very
+//           kernel (push_n > 0): while the tensor cores work on the local tiles they copy this rank's rows
+//           into every peer's buffer with plain 16-byte stores, piece by piece in row order, and bump the
+//           peer's row-block counter after each piece - the transfer hides behind the local half of the GEMM
+//           on both sides and blocks nobody but the two warps that issue it.
 //   mode 2  GEMM -> reduce-scatter: the epilogue stores the bf16 partial sums of rows another rank owns
 //           straight into that rank's inbox (peer stores) and the rows this rank owns into the local
 //           output (with the bias); remote tiles run first and their counters are bumped as soon as the
@@ -48,6 +53,12 @@ struct TpExt {
   int* status;
   // mode 1
   const uint32_t* a_ready;   // [M/128] cumulative rows landed per 128-row block of A (local memory)
+  int push_n;                // number of peers this rank's rows of A are sent to by this kernel (0: none)
+  int push_first_block;      // first 128-row block (inside this rank's rows) the kernel sends; earlier ones were sent by the producer
+  const __nv_bfloat16* push_src;        // this rank's A buffer (all M rows; only its own rows are read)
+  long long push_ld;                    // row pitch of A in elements (the same on every rank)
+  __nv_bfloat16* push_dst[TP_MAX - 1];  // peer i's A buffer
+  uint32_t* push_ready[TP_MAX - 1];     // peer i's counters [M/128]
   // mode 2
   void* out[TP_MAX];         // out[o]: [rows_per_rank, ldo] block that receives the rows owned by rank o
   long long ldo;
@@ -524,9 +535,15 @@ __device__ __forceinline__ void pair_decode_tile(const GemmParams& p, const TpEx
   const int per_group = bpr * p.num_n_blocks;
   const int g = t / per_group;
   const int u = t - g * per_group;
-  nb = u / bpr;
   const int owner = (x.rank + g + (COMM == 2 ? 1 : 0)) % x.tp;
-  mb = owner * bpr + (u - nb * bpr);
+  if (COMM == 1 && g > 0) {  // a peer's rows: row block by row block, the order they arrive in
+    const int j = u / p.num_n_blocks;
+    nb = u - j * p.num_n_blocks;
+    mb = owner * bpr + j;
+  } else {
+    nb = u / bpr;
+    mb = owner * bpr + (u - nb * bpr);
+  }
 }
 
 // Reduce-scatter side: publish the partial sums this warp stored for its remote tiles. `upto` = first work item
@@ -556,8 +573,59 @@ __device__ __forceinline__ void tp_signal_remote_tiles(const GemmParams& p, cons
   __syncwarp();
 }
 
+#ifndef TP_COPY_WARPS
+#define TP_COPY_WARPS 6
+#endif
+// Copy warps of mode 1 (the last TP_COPY_WARPS warps of every CTA): send this rank's rows of A to the peers. A piece
+// is a few whole rows inside one 128-row block (about 8 KB: one round of loads); pieces are dealt to the copy warps
+// of the grid in row order and each is published as soon as it is out, so the row blocks complete in the order in
+// which the peers' GEMMs ask for them.
+__device__ __forceinline__ void tp_push_rows(const GemmParams& p, const TpExt& x, int gw, int nw, int lane) {
+  constexpr int UNROLL = 16;            // 16-byte loads in flight per lane: 8 KB per warp and round
+  const int chunks_per_row = p.K >> 3;  // 16-byte chunks (K % 8 == 0 is checked on the host)
+  const int piece_rows = max(1, min(128, (UNROLL * 512) / (p.K * 2)));  // whole rows, about one round each
+  const int ppb = (128 + piece_rows - 1) / piece_rows;
+  const int total = (x.rows_per_rank / 128 - x.push_first_block) * ppb;
+  const int my0 = x.rank * x.rows_per_rank;
+  for (int piece = gw; piece < total; piece += nw) {
+    const int blk = x.push_first_block + piece / ppb, part = piece % ppb;
+    const int r0 = my0 + blk * 128 + part * piece_rows;
+    const int nrows = min(piece_rows, 128 - part * piece_rows);
+    const __nv_bfloat16* src = x.push_src + (long long)r0 * x.push_ld;
+    const int n16 = nrows * chunks_per_row;
+    for (int e0 = 0; e0 < n16; e0 += 32 * UNROLL) {
+      uint4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {  // independent loads in flight before the first store
+        const int e = e0 + u * 32 + lane;
+        if (e < n16) {
+          const int rr = e / chunks_per_row, cc = e - rr * chunks_per_row;
+          v[u] = *reinterpret_cast<const uint4*>(src + (long long)rr * x.push_ld + cc * 8);
+        }
+      }
+      for (int i = 0; i < x.push_n; ++i) {
+        __nv_bfloat16* dst = x.push_dst[i] + (long long)r0 * x.push_ld;
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int e = e0 + u * 32 + lane;
+          if (e < n16) {
+            const int rr = e / chunks_per_row, cc = e - rr * chunks_per_row;
+            *reinterpret_cast<uint4*>(dst + (long long)rr * x.push_ld + cc * 8) = v[u];
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_system();
+      for (int i = 0; i < x.push_n; ++i) red_add_sys(x.push_ready[i] + (r0 >> 7), (uint32_t)nrows);
+    }
+    __syncwarp();
+  }
+}
+
 template <int BN, int A_MN, int B_MN, int COMM>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(COMM == 1 ? 320 + 32 * TP_COPY_WARPS : 320, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                               const GemmParams p, const __grid_constant__ TpExt tpx) {
   using Cfg = Gemm2Cfg<BN>;
@@ -710,6 +778,9 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
         if (acc == 0) acc_phase ^= 1;
       }
     }
+  } else if (COMM == 1 && warp >= 10) {
+    if (tpx.push_n > 0)
+      tp_push_rows(p, tpx, (int)blockIdx.x * TP_COPY_WARPS + (warp - 10), (int)gridDim.x * TP_COPY_WARPS, lane);
   } else {
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
@@ -872,7 +943,7 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
     attr_set = true;
   }
-  kern<<<grid, 320, Gemm2Cfg<BN>::SMEM_BYTES, stream>>>(ta, tb, p, tpx);  // cluster of two through __cluster_dims__
+  kern<<<grid, COMM == 1 ? 320 + 32 * TP_COPY_WARPS : 320, Gemm2Cfg<BN>::SMEM_BYTES, stream>>>(ta, tb, p, tpx);  // cluster of two through __cluster_dims__
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
@@ -1034,11 +1105,15 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
 //   mode 2  partial sums of the rows owned by rank o go to out[o] ([rows_per_rank, ldo], bf16): out[rank] is the
 //           local output (bias applied), out[o != rank] this rank's slot in o's inbox; arrived[o] = rank o's
 //           counters [rows_per_rank / 128]. D / ldd are ignored.
+//           n_push > 0: the kernel also sends this rank's rows of A to n_push peers (push_dst[i] = base of peer i's
+//           A buffer, push_ready[i] = peer i's counters), starting at its 128-row block push_first_block - the
+//           blocks before it were delivered by the kernel that produced the rows; 0 when that kernel delivered all.
 // pass = device word holding the number of passes including this one. out / arrived are arrays of tp pointers.
 extern "C" int tnnb_gemm_tp(int mode, const void* A, const void* B, void* D, int M, int N, int K, int b_mn, long long lda,
                             long long ldb, long long ldd, const void* bias, const void* aux_in, void* aux_out, long long ld_aux,
                             int flags, int tp, int rank, int rows_per_rank, const void* pass, const void* a_ready, void** out,
-                            long long ldo, void** arrived, int force_bn, int* status, void* stream_) {
+                            long long ldo, void** arrived, int n_push, void** push_dst, void** push_ready, int push_first_block,
+                            int force_bn, int* status, void* stream_) {
   if (mode != 1 && mode != 2) return -2;
   if (tp < 1 || tp > TP_MAX || rank < 0 || rank >= tp || !pass) return -2;
   if (rows_per_rank <= 0 || rows_per_rank % 128 || (long long)rows_per_rank * tp != M) return -8;
@@ -1051,6 +1126,20 @@ extern "C" int tnnb_gemm_tp(int mode, const void* A, const void* B, void* D, int
   if (mode == 1) {
     if (!a_ready || !D) return -5;
     x.a_ready = static_cast<const uint32_t*>(a_ready);
+    if (n_push < 0 || n_push > TP_MAX - 1) return -2;
+    if (n_push > 0) {
+      if (!push_dst || !push_ready || (K % 8)) return -5;
+      if (push_first_block < 0 || push_first_block > rows_per_rank / 128) return -3;
+      x.push_n = n_push;
+      x.push_first_block = push_first_block;
+      x.push_src = static_cast<const __nv_bfloat16*>(A);
+      x.push_ld = lda;
+      for (int i = 0; i < n_push; ++i) {
+        if (!push_dst[i] || !push_ready[i] || (reinterpret_cast<uintptr_t>(push_dst[i]) & 15)) return -4;
+        x.push_dst[i] = static_cast<__nv_bfloat16*>(push_dst[i]);
+        x.push_ready[i] = static_cast<uint32_t*>(push_ready[i]);
+      }
+    }
   } else {
     if (!out || !arrived || (ldo % 8)) return -5;
     for (int o = 0; o < tp; ++o) {

@@ -47,5 +47,6 @@ extern "C" {
 int tnnb_gemm_tp(int mode, const void* A, const void* B, void* D, int M, int N, int K, int b_mn, long long lda,
                  long long ldb, long long ldd, const void* bias, const void* aux_in, void* aux_out, long long ld_aux,
                  int flags, int tp, int rank, int rows_per_rank, const void* pass, const void* a_ready, void** out,
-                 long long ldo, void** arrived, int force_bn, int* status, void* stream);
+                 long long ldo, void** arrived, int n_push, void** push_dst, void** push_ready, int push_first_block, int force_bn, int* status,
+                 void* stream);
 }

@@ -119,7 +119,7 @@ ln_fwd_kernel(const bf16* __restrict__ x_in, const bf16* __restrict__ delta, bf1
           for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16((v[i][k] - mean) * rstd);
         }
         *reinterpret_cast<LBf8*>(h + r * C + c * 8) = o;
-        if (TP) {
+        if (TP && r < push.rows) {
           for (int t = 0; t < push.n; ++t) *reinterpret_cast<LBf8*>(push.dst[t] + r * C + c * 8) = o;
         }
       }
@@ -242,7 +242,7 @@ ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const flo
           }
           const uint4 dd = make_uint4(pack2(t[0], t[1]), pack2(t[2], t[3]), pack2(t[4], t[5]), pack2(t[6], t[7]));
           *reinterpret_cast<uint4*>(ddelta + r * C + c * 8) = dd;
-          if (TP) {
+          if (TP && r < push.rows) {
             for (int u = 0; u < push.n; ++u) *reinterpret_cast<uint4*>(push.dst[u] + r * C + c * 8) = dd;
           }
         }
@@ -277,7 +277,7 @@ static inline int pick_maxch(int C) {
 // Fill the parameter blocks of the tensor-parallel variants from flat C arguments (see tnnb_layernorm_fwd_tp).
 static int make_tp_blocks(TpPull& pull, TpPush& push, int n_pull, void** pull_src, const void* arrived, const void* pass,
                           unsigned int units, int n_push, void** push_dst, void** push_ready, long long push_row0,
-                          int* status) {
+                          long long push_rows, int* status) {
   if (n_pull < 0 || n_pull > TP_MAX - 1 || n_push < 0 || n_push > TP_MAX - 1) return -2;
   pull = TpPull{};
   push = TpPush{};
@@ -295,8 +295,9 @@ static int make_tp_blocks(TpPull& pull, TpPush& push, int n_pull, void** pull_sr
   }
   push.n = n_push;
   if (n_push) {
-    if (!push_dst || !push_ready || push_row0 < 0 || (push_row0 % 8)) return -5;
+    if (!push_dst || !push_ready || push_row0 < 0 || (push_row0 % 8) || push_rows < 0 || (push_rows % 8)) return -5;
     push.row0 = (int)push_row0;
+    push.rows = push_rows;
     for (int i = 0; i < n_push; ++i) {
       if (!push_dst[i] || !push_ready[i] || ((uintptr_t)push_dst[i] & 15)) return -4;
       push.dst[i] = (bf16*)push_dst[i];
@@ -344,16 +345,18 @@ int tnnb_layernorm_fwd(const void* x_in, const void* delta, void* x_out, void* h
 }
 
 // Tensor-parallel form. pull: delta is the sum of `delta` and pull_src[0..n_pull) (each [rows, C], local memory)
-// once arrived[row / 128] has reached units x *pass. push: h is also stored to push_dst[i] (peer i's gather buffer,
-// already offset to this rank's first row) and the rows delivered are added to push_ready[i][(push_row0 + row) / 128].
+// once arrived[row / 128] has reached units x *pass. push: rows [0, push_rows) of h are also stored to push_dst[i]
+// (peer i's gather buffer, already offset to this rank's first row) and the rows delivered are added to
+// push_ready[i][(push_row0 + row) / 128]; the rest of the rows is sent by the GEMM that consumes the buffer.
 int tnnb_layernorm_fwd_tp(const void* x_in, const void* delta, void* x_out, void* h, const void* gamma,
                           const void* beta, void* mean, void* rstd, long long rows, int C, float eps, float p,
                           unsigned long long seed, const void* seed_off, int n_pull, void** pull_src,
                           const void* arrived, const void* pass, unsigned int units, int n_push, void** push_dst,
-                          void** push_ready, long long push_row0, int* status, void* stream) {
+                          void** push_ready, long long push_row0, long long push_rows, int* status, void* stream) {
   TpPull pull;
   TpPush push;
-  const int rc = make_tp_blocks(pull, push, n_pull, pull_src, arrived, pass, units, n_push, push_dst, push_ready, push_row0, status);
+  const int rc = make_tp_blocks(pull, push, n_pull, pull_src, arrived, pass, units, n_push, push_dst, push_ready, push_row0,
+                                push_rows, status);
   if (rc) return rc;
   if (n_pull && !delta) return -5;
   return layernorm_fwd_impl(x_in, delta, x_out, h, gamma, beta, mean, rstd, rows, C, eps, p, seed, seed_off, stream, &pull,
@@ -416,10 +419,11 @@ int tnnb_layernorm_bwd_tp(const void* dh, const void* x, const void* mean, const
                           const void* dres, void* dx, void* ddelta, void* dgamma, void* dbeta, long long rows,
                           int C, float p, unsigned long long seed, const void* seed_off, int n_pull, void** pull_src,
                           const void* arrived, const void* pass, unsigned int units, int n_push, void** push_dst,
-                          void** push_ready, long long push_row0, int* status, void* stream) {
+                          void** push_ready, long long push_row0, long long push_rows, int* status, void* stream) {
   TpPull pull;
   TpPush push;
-  const int rc = make_tp_blocks(pull, push, n_pull, pull_src, arrived, pass, units, n_push, push_dst, push_ready, push_row0, status);
+  const int rc = make_tp_blocks(pull, push, n_pull, pull_src, arrived, pass, units, n_push, push_dst, push_ready, push_row0,
+                                push_rows, status);
   if (rc) return rc;
   if (n_push && !ddelta) return -5;
   return layernorm_bwd_impl(dh, x, mean, rstd, gamma, dres, dx, ddelta, dgamma, dbeta, rows, C, p, seed, seed_off, stream,

@@ -64,6 +64,7 @@ __device__ __forceinline__ bool spin_until(const uint32_t* p, uint32_t want) {
 struct TpPush {
   int n;                    // number of peers (0: nothing to push)
   int row0;                 // global row of the kernel's row 0 (multiple of 8)
+  long long rows;           // only rows [0, rows) of the kernel are pushed (a multiple of 8; the consuming GEMM sends the rest)
   __nv_bfloat16* dst[TP_MAX - 1];
   uint32_t* ready[TP_MAX - 1];   // base of the peer's counter array ([M/128])
 };
@@ -96,12 +97,14 @@ __device__ __forceinline__ void tp_pull_wait(const TpPull& pull, long long r, ui
   bool ok = true;
   if (lane == 0) ok = spin_until<true>(pull.arrived + (r >> 7), want);
   ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  __syncwarp();  // orders the other lanes' reads of the inbox after lane 0's acquire
   if (!ok && lane == 0 && pull.status) atomicCAS(pull.status, 0, ST_TIMEOUT_PEER);
 }
 // End of a pushing kernel: publish the rows this block stored into the peers' buffers. Blocks own groups of
 // `wpb` consecutive rows (a multiple of 8 that divides 128), so a group never straddles a 128-row block.
 __device__ __forceinline__ void tp_push_signal(const TpPush& push, long long rows, int wpb) {
   __syncthreads();
+  rows = min(rows, push.rows);
   if (threadIdx.x == 0) {
     __threadfence_system();
     for (long long base = (long long)blockIdx.x * wpb; base < rows; base += (long long)gridDim.x * wpb) {

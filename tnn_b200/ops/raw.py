@@ -237,7 +237,8 @@ def _tp_tail(tp_pull, tp_push, device):
     output (objects of tnn_b200.parallel.tp)."""
     pl = (tp_pull.n_pull, tp_pull.pull_src, _lib.ptr(tp_pull.arrived), _lib.ptr(tp_pull.pass_ctr), tp_pull.units) \
         if tp_pull is not None else (0, None, None, None, 0)
-    ps = (tp_push.n_push, tp_push.push_dst, tp_push.push_ready, tp_push.push_row0) if tp_push is not None else (0, None, None, 0)
+    ps = (tp_push.n_push, tp_push.push_dst, tp_push.push_ready, tp_push.push_row0, tp_push.ln_rows) if tp_push is not None \
+        else (0, None, None, 0, 0)
     return (*pl, *ps, _lib.ptr(_lib.status_word(device)), _lib.stream())
 
 
@@ -250,7 +251,7 @@ def _declare_tp(lib):
         return
     import ctypes
     vp, ll, i, u, f, ull = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_uint, ctypes.c_float, ctypes.c_ulonglong
-    tail = [i, vp, vp, vp, u, i, vp, vp, ll, vp, vp]
+    tail = [i, vp, vp, vp, u, i, vp, vp, ll, ll, vp, vp]
     lib.tnnb_layernorm_fwd_tp.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ll, i, f, f, ull, vp] + tail
     lib.tnnb_layernorm_fwd_tp.restype = i
     lib.tnnb_layernorm_bwd_tp.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ll, i, f, ull, vp] + tail

@@ -23,6 +23,7 @@ The reference has no tensor parallelism (its only distributed mode is the pipeli
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional
 
 import torch
@@ -91,12 +92,16 @@ def _declare(lib):
     if _DECLARED:
         return
     vp, ll, i, u = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_uint
-    lib.tnnb_gemm_tp.argtypes = [i, vp, vp, vp, i, i, i, i, ll, ll, ll, vp, vp, vp, ll, i, i, i, i, vp, vp, vp, ll, vp, i, vp, vp]
+    lib.tnnb_gemm_tp.argtypes = [i, vp, vp, vp, i, i, i, i, ll, ll, ll, vp, vp, vp, ll, i, i, i, i, vp, vp, vp, ll, vp, i, vp, vp, i, i, vp, vp]
     lib.tnnb_gemm_tp.restype = i
     lib.tnnb_tp_push.argtypes = [vp, vp, ll, i, i, vp, vp, ll, vp]
     lib.tnnb_tp_push.restype = i
     lib.tnnb_tp_resolve.argtypes = [vp, vp, ll, i, i, vp, vp, vp, u, vp, vp]
     lib.tnnb_tp_resolve.restype = i
+    lib.tnnb_peer_copy.argtypes = [vp, vp, ctypes.c_ulonglong, vp]
+    lib.tnnb_peer_copy.restype = i
+    lib.tnnb_tp_signal.argtypes = [i, vp, i, i, u, vp]
+    lib.tnnb_tp_signal.restype = i
     _DECLARED = True
 
 
@@ -108,8 +113,32 @@ class CommContext:
         self.heap, self.fused, self.device = heap, fused and heap is not None, device
         self.lib = _lib.load() if self.fused else None
         self.seq_len = 0  # set by the pipeline runtime: stages after the first cannot read it off their input
+        # How the rows of a gather site reach the peers (TNNB_TP_PUSH selects one; measured on 2 B200 with the
+        # GPT-2 small shapes, 12.6 MB per hand-off, layer norm + all-gather GEMM for QKV; plain kernels: 8 + 29 us):
+        #   "ln"    the producing layer-norm kernel stores the rows into the peers' buffers itself (default): the
+        #           kernel takes 33 us instead of 8, the GEMM then finds every row in place: 66 us.
+        #   "gemm"  six extra warps of the consuming GEMM kernel send them while the tensor cores work on the local
+        #           tiles: 66 us as well - SM-issued stores move 12.6 MB in about 30 us whoever issues them, and the
+        #           GEMM's remote tiles cannot finish before the last rows have landed.
+        #   "split" the layer-norm kernel sends the first ``ln_share`` of the rows, the GEMM's copy warps the rest: 69 us.
+        #   "ce"    copy-engine transfers on a side stream in two halves, each followed by a one-warp kernel that
+        #           updates the counters: the copy itself is the fastest mover (21 us for 12.6 MB, no SM time), but
+        #           the four extra graph nodes and the cross-stream edges cost more than it saves: 77 us.
+        self.push_mode = os.environ.get("TNNB_TP_PUSH", "ln")
+        self.ln_share = float(os.environ.get("TNNB_TP_LN_SHARE", "0.5"))
+        self.side = None
+        self._forked = False
         if self.fused:
             _declare(self.lib)
+            if device.type == "cuda":
+                self.side = torch.cuda.Stream(device=device, priority=-1)
+
+    def join(self) -> None:
+        """Make the current stream wait for the side stream's transfers (end of a pass: the rows they read may be
+        overwritten afterwards, and a stream capture must end with every forked stream joined)."""
+        if self._forked:
+            torch.cuda.current_stream().wait_stream(self.side)
+            self._forked = False
 
     def new_pass_counter(self) -> torch.Tensor:
         """A device word that counts the passes through one set of sites (bumped once at the start of every
@@ -123,11 +152,11 @@ _EPI_BIAS, _EPI_GELU, _EPI_DGELU = 1, 2, 4
 
 class GatherSite:
     """A symmetric ``[M, K]`` buffer whose row block ``idx`` is produced locally and whose other row blocks are
-    PUSHED into it by the ranks that own them (csrc/kernels/tp_flags.cuh): the kernel that produces this rank's
-    rows - a layer norm, through :meth:`push_args`, or :meth:`push` - also stores them into every peer's buffer and
-    bumps the peers' row-block counters; :meth:`gemm` runs the tiles of the local rows first and polls the
-    counters of the other row blocks only when it reaches them. After the call the whole buffer is valid locally
-    (it is kept for the weight-gradient GEMM)."""
+    PUSHED into it by the ranks that own them (csrc/kernels/tp_flags.cuh), each push followed by an update of the
+    receiver's row-block counters. :meth:`gemm` runs the tiles of the local rows first and polls the counters of
+    the other row blocks only when it reaches them; by default it is also the kernel that sends this rank's rows
+    (two copy warps per CTA, see ``CommContext.push_mode`` for the alternatives). After the call the whole buffer
+    is valid locally (it is kept for the weight-gradient GEMM)."""
 
     def __init__(self, cc: CommContext, M: int, K: int, pass_ctr: Optional[torch.Tensor] = None):
         self.cc, self.M, self.K = cc, M, K
@@ -135,13 +164,21 @@ class GatherSite:
         self.pass_ctr = pass_ctr
         if cc.fused:
             self.buf = cc.heap.alloc((M, K), torch.bfloat16)
-            self.ready = cc.heap.alloc((M // 128 + 1,), torch.int32).zero_()
+            # counters start at zero because the heap does (it is cleared when created and never recycles a block);
+            # clearing them here would race with a peer that is already pushing rows
+            self.ready = cc.heap.alloc((M // 128 + 1,), torch.int32)
             peers = [r for r in range(cc.tp) if r != cc.idx]
             bufs, rdy = cc.heap.peer_ptrs(self.buf, cc.ranks), cc.heap.peer_ptrs(self.ready, cc.ranks)
             self.n_push = len(peers)
             self.push_row0 = cc.idx * self.rows
-            self.push_dst = ptr_array([bufs[r] + self.push_row0 * K * 2 for r in peers])
+            self.push_dst = ptr_array([bufs[r] + self.push_row0 * K * 2 for r in peers])  # peers' copies of my rows
+            self.push_base = ptr_array([bufs[r] for r in peers])                         # peers' whole buffers
             self.push_ready = ptr_array([rdy[r] for r in peers])
+            # rows [0, ln_rows) of this rank's shard travel with the producing kernel, the rest with the GEMM
+            blocks = self.rows // 128
+            share = {"ln": 1.0, "gemm": 0.0, "ce": 0.0}.get(cc.push_mode, cc.ln_share)
+            self.ln_blocks = min(blocks, max(0, int(round(blocks * share))))
+            self.ln_rows = self.ln_blocks * 128
         else:
             self.buf = torch.empty(M, K, dtype=torch.bfloat16 if cc.device.type == "cuda" else torch.float32, device=cc.device)
 
@@ -150,8 +187,32 @@ class GatherSite:
 
     def push_args(self):
         """Arguments that make a layer-norm kernel writing :meth:`mine` deliver the rows to the peers as well
-        (``None`` on the NCCL path)."""
-        return self if self.cc.fused else None
+        (``None`` on the NCCL path and when the rows travel by copy engine, see :meth:`after_produce`)."""
+        return self if (self.cc.fused and self.cc.push_mode in ("ln", "split") and self.ln_rows > 0) else None
+
+    def after_produce(self) -> None:
+        """Call once the kernel that writes :meth:`mine` has been launched on the current stream. In copy-engine
+        mode this starts the transfer of the rows to every peer on the side stream (two halves, each followed by
+        the counter update that lets the peer's GEMM use them); otherwise it does nothing."""
+        cc = self.cc
+        if not cc.fused or cc.push_mode != "ce" or self.n_push == 0:
+            return
+        main = torch.cuda.current_stream()
+        cc.side.wait_stream(main)
+        cc._forked = True
+        row_bytes = self.K * 2
+        blocks = self.rows // 128
+        halves = [(0, blocks)] if blocks < 2 else [(0, blocks // 2), (blocks // 2, blocks)]
+        src0 = self.mine().data_ptr()
+        side = ctypes.c_void_p(cc.side.cuda_stream)
+        for (b0, b1) in halves:
+            off, nbytes = b0 * 128 * row_bytes, (b1 - b0) * 128 * row_bytes
+            for i in range(self.n_push):
+                _lib.check_rc(cc.lib.tnnb_peer_copy(ctypes.c_void_p(self.push_dst[i] + off), ctypes.c_void_p(src0 + off), nbytes, side),
+                              "tnnb_peer_copy")
+            _lib.check_rc(cc.lib.tnnb_tp_signal(self.n_push, self.push_ready, self.push_row0 // 128 + b0, b1 - b0, 128, side),
+                          "tnnb_tp_signal")
+            LAUNCHES["count"] += 1
 
     def push(self, src: Optional[torch.Tensor] = None) -> None:
         """Stand-alone push: copy ``src`` (default: the rows already in :meth:`mine`) to the peers and publish."""
@@ -161,8 +222,15 @@ class GatherSite:
                 self.mine().copy_(src)
             return
         mine = self.mine()
+        if cc.push_mode not in ("ln", "split") or self.ln_rows == 0:
+            if src is not None:
+                mine.copy_(src)
+            self.after_produce()
+            return
+        if src is not None and self.ln_rows < self.rows:
+            mine[self.ln_rows:].copy_(src[self.ln_rows:])   # these rows are sent by the GEMM
         s = mine if src is None else src.contiguous()
-        rc = cc.lib.tnnb_tp_push(_lib.ptr(s), _lib.ptr(mine) if src is not None else None, self.rows, self.K, self.n_push,
+        rc = cc.lib.tnnb_tp_push(_lib.ptr(s), _lib.ptr(mine) if src is not None else None, self.ln_rows, self.K, self.n_push,
                                  self.push_dst, self.push_ready, self.push_row0, _lib.stream())
         _lib.check_rc(rc, "tnnb_tp_push")
         LAUNCHES["count"] += 1
@@ -185,7 +253,9 @@ class GatherSite:
         rc = cc.lib.tnnb_gemm_tp(1, _lib.ptr(self.buf), _lib.ptr(w), _lib.ptr(out), self.M, N, self.K, int(b_t), self.K,
                                  w.stride(0), N, _lib.ptr(bias), _lib.ptr(dgelu_of), _lib.ptr(gelu_preact),
                                  aux.stride(0) if aux is not None else 0, flags, cc.tp, cc.idx, self.rows,
-                                 _lib.ptr(self.pass_ctr), _lib.ptr(self.ready), None, 0, None, force_bn,
+                                 _lib.ptr(self.pass_ctr), _lib.ptr(self.ready), None, 0, None,
+                                 self.n_push if (cc.push_mode in ("gemm", "split") and self.ln_blocks < self.rows // 128) else 0,
+                                 self.push_base, self.push_ready, self.ln_blocks, force_bn,
                                  _lib.ptr(_lib.status_word(cc.device)), _lib.stream())
         _lib.check_rc(rc, "tnnb_gemm_tp(all-gather)")
         LAUNCHES["count"] += 1
@@ -205,7 +275,7 @@ class ScatterSite:
         self.pass_ctr = pass_ctr
         if cc.fused:
             self.inbox = cc.heap.alloc((cc.tp, self.rows, N), torch.bfloat16)   # slot s: partial sums from rank s
-            self.arrived = cc.heap.alloc((self.rows // 128 + 1,), torch.int32).zero_()
+            self.arrived = cc.heap.alloc((self.rows // 128 + 1,), torch.int32)   # zero from the heap, see GatherSite
             ib, ar = cc.heap.peer_ptrs(self.inbox, cc.ranks), cc.heap.peer_ptrs(self.arrived, cc.ranks)
             slot = self.rows * N * 2
             self._remote_out = [ib[o] + cc.idx * slot for o in range(cc.tp)]  # my slot on owner o
@@ -239,7 +309,7 @@ class ScatterSite:
         outs[cc.idx] = out.data_ptr()
         rc = cc.lib.tnnb_gemm_tp(2, _lib.ptr(a), _lib.ptr(w), None, self.M, self.N, K, int(b_t), a.stride(0), w.stride(0), 0,
                                  _lib.ptr(bias), None, None, 0, _EPI_BIAS if bias is not None else 0, cc.tp, cc.idx, self.rows,
-                                 _lib.ptr(self.pass_ctr), None, ptr_array(outs), self.N, self.arrived_ptrs, force_bn,
+                                 _lib.ptr(self.pass_ctr), None, ptr_array(outs), self.N, self.arrived_ptrs, 0, None, None, 0, force_bn,
                                  _lib.ptr(_lib.status_word(cc.device)), _lib.stream())
         _lib.check_rc(rc, "tnnb_gemm_tp(reduce-scatter)")
         LAUNCHES["count"] += 1

@@ -57,6 +57,7 @@ class _TPGPTChain(_Segment):
                                               tp_push=site.push_args())
         if h.data_ptr() != tgt.data_ptr():
             tgt.copy_(h)
+        site.after_produce()
         return xo, mean, rstd
 
     def forward(self, vals, ctx):
@@ -110,6 +111,7 @@ class _TPGPTChain(_Segment):
             if pend_site is not None:
                 pending = pend_site.resolve(pending)
             out = raw.binary(x, raw.dropout(pending, p_pend, seed_pend), "add")
+        cc.join()
         # downstream layers (the vocabulary head) see only this rank's rows
         vals[id(self.out_node)] = out.reshape(1, Ms, E)
 
@@ -132,6 +134,8 @@ class _TPGPTChain(_Segment):
             dres, dpend = raw.layernorm_bwd(g, xf, mean, rstd, ln.params[0], None, True, p_pend, seed_pend, ln.grads[0],
                                             ln.grads[1], ddelta_out=last["gb2"].mine() if g.is_cuda else None,
                                             tp_push=last["gb2"].push_args() if g.is_cuda else None)
+            if g.is_cuda:
+                last["gb2"].after_produce()
         else:
             dres, dpend = g, raw.dropout(g, p_pend, seed_pend)
         for bi in reversed(range(len(self.blocks))):
@@ -156,6 +160,8 @@ class _TPGPTChain(_Segment):
             tgt = st["gb1"].mine()
             if dy1.data_ptr() != tgt.data_ptr():
                 st["gb1"].push(dy1)
+            else:
+                st["gb1"].after_produce()
             # ---- attention output projection (row parallel) ----
             raw.colsum_accum(tgt, attn.grads[3])
             da = st["gb1"].gemm(wo, b_t=True)                                      # [M, E/tp]
@@ -171,6 +177,9 @@ class _TPGPTChain(_Segment):
                                             s["p_in"], s["seed_in"], ln1.grads[0], ln1.grads[1],
                                             ddelta_out=prev.mine() if prev is not None else None,
                                             tp_pull=st["s_qkv"].pull_args(), tp_push=prev.push_args() if prev is not None else None)
+            if prev is not None:
+                prev.after_produce()
+        cc.join()
         if self.in_is_shard:
             if id(self.in_node) not in no_grad_nodes:
                 _accum(gvals, self.in_node, dres.reshape(1, Ms, E))
