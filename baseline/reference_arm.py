@@ -40,6 +40,32 @@ def _unavailable(why: str):
 
 
 def run_reference(args):
+    """Print the reference arm's line for ``args.model``. For the default model (GPT-2 small) the line also carries a
+    ``resnet50`` sub-record - the other half of the headline metric - measured by a second run of this arm in a
+    child process (so that a failure or an over-long ``torch.compile`` of the CNN cannot lose the GPT-2 number);
+    ``TNNB_BENCH_RESNET=0`` leaves it out."""
+    line = _measure(args)
+    if line is None:
+        return
+    rank = int(os.environ.get("RANK", "0"))
+    if args.model == "gpt2_small" and rank == 0 and os.environ.get("TNNB_BENCH_RESNET", "1") != "0":
+        import subprocess
+        cmd = [sys.executable, os.path.join(os.path.dirname(HERE), "bench.py"), "--impl", "reference", "--model", "resnet50", "--gpus", "1",
+               "--steps", str(args.steps), "--warmup", str(args.warmup)]
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=float(os.environ.get("TNNB_REF_RESNET_TIMEOUT", "900")))
+            rows = [l for l in r.stdout.splitlines() if l.startswith("{")]
+            sub = json.loads(rows[-1]) if rows else {"unavailable": f"exit {r.returncode}: {r.stderr.strip()[-200:]}"}
+        except subprocess.TimeoutExpired:
+            sub = {"unavailable": "the reference ResNet-50 run did not finish within its time limit (torch.compile max-autotune)"}
+        except Exception as e:
+            sub = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+        keep = ("metric", "value", "unit", "ms_per_step", "steps", "warmup", "dtype", "config", "e2e", "loss_last", "unavailable")
+        line["resnet50"] = {k: sub[k] for k in keep if k in sub}
+    print(json.dumps(line), flush=True)
+
+
+def _measure(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if world > 1 or args.gpus > 1:
@@ -64,7 +90,7 @@ def run_reference(args):
             warm, steps = max(3, args.warmup), args.steps
             try:
                 r = eng.run_engine("gpt2_small", batch, warm, steps, dtype=os.environ.get("TNNB_REF_DTYPE", ""), fixed=fixed)
-                print(json.dumps({
+                return ({
                     "impl": "reference", "metric": "tokens_per_sec", "value": r["value"], "unit": "tokens/s", "n_gpus": 1,
                     "steps": steps, "warmup": warm, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
                     "vs_baseline": None, "dtype": r["dtype"], "data": "synthetic",
@@ -74,8 +100,7 @@ def run_reference(args):
                     "loss_last": r["loss_last"], "run_ms": r["run_ms"],
                     "note": "the timed loop is the reference trainer's own: it uploads each batch from host memory and reads the loss "
                             "back every step, so value and e2e are the same measurement",
-                }), flush=True)
-                return
+                })
             except Exception as e:  # fall through to the reference's PyTorch trainer, and say why
                 engine_error = f"{type(e).__name__}: {e}"[:500]
         else:
@@ -167,7 +192,7 @@ def run_reference(args):
     ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
     value = batch * items * steps / (ms / 1e3)
     x0, y0 = ds[0]
-    print(json.dumps({
+    return ({
         "impl": "reference", "metric": metric, "value": round(value, 1), "unit": unit, "n_gpus": 1, "steps": steps, "warmup": warm,
         "ms_per_step": round(ms / steps, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp32 (the reference trainer's stock precision; TF32 matmul via set_float32_matmul_precision('high'))",
@@ -178,4 +203,4 @@ def run_reference(args):
                 "d2h_bytes_per_step": 12},
         "loss_last": round(float(loss), 4), **({"engine_error": engine_error} if engine_error else {}),
         "note": "the timed loop is the reference's own train_epoch: it uploads each batch and reads loss/accuracy back every step",
-    }), flush=True)
+    })

@@ -9,7 +9,9 @@ The step is the full training step of the flagship configuration: GPT-2 small (1
 12 heads, context 1024, vocabulary 50257, tanh-GELU, pre-LN, dropout 0.1, untied biased head),
 bf16 compute with fp32 master weights, AdamW, 8 sequences of 1024 tokens per GPU (global batch 64
 at 8 GPUs, weak scaling), synthetic uniform token ids, random-init weights. With more than one
-GPU the layout is TP=2 x DP=N/2. ``--model resnet50`` runs the ResNet-50 images/s configuration.
+GPU the layout is TP=2 x DP=N/2. The same invocation then measures ResNet-50 images/s (256 images per GPU, data
+parallel) under the same rules and reports it as the ``resnet50`` sub-record of the line; ``--model resnet50`` runs
+that configuration alone.
 
 Two numbers are reported in one JSON line: ``value`` times K steps on the device (CUDA events,
 max over ranks) with the batch already resident, ``e2e`` times the same K steps through
@@ -121,18 +123,18 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     ms = model_setup(args)
-    cfg = TrainingConfig.from_dict({"model_name": ms["zoo"], "batch_size": ms["per_gpu_batch"], "device_type": "CUDA",
-                                    "optimizer": ms["optimizer"], "scheduler": {"type": "no_op"},
-                                    "loss": {"type": "logsoftmax_crossentropy"}, "seed": 0})
-    is_lm = ms["seq_len"] is not None
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def measure(layout, sample_clocks):
+    def measure(layout, sample_clocks, ms=ms):
         """Build the trainer for one layout, warm up, time K resident steps on the device and K end-to-end steps."""
+        cfg = TrainingConfig.from_dict({"model_name": ms["zoo"], "batch_size": ms["per_gpu_batch"], "device_type": "CUDA",
+                                        "optimizer": ms["optimizer"], "scheduler": {"type": "no_op"},
+                                        "loss": {"type": "logsoftmax_crossentropy"}, "seed": 0})
+        is_lm = ms["seq_len"] is not None
         if world > 1:
             from tnn_b200.parallel.runtime import ParallelTrainer
             trainer = ParallelTrainer(cfg, layout=layout, log=False)
@@ -321,6 +323,27 @@ def run_ours(args):
         args.no_graph = True
     else:
         r = measure(layout, True)
+    # The other half of the headline metric: ResNet-50 images/s (bottleneck blocks [3,4,6,3], 256 images of
+    # 224 x 224 x 3 per GPU, bf16, SGD momentum 0.9, data parallel with the fused reduce + update kernel), measured in
+    # the same invocation with the same rules. TNNB_BENCH_RESNET=0 leaves it out.
+    resnet = None
+    if args.model == "gpt2_small" and not args.parallelism and os.environ.get("TNNB_BENCH_RESNET", "1") != "0":
+        rargs = argparse.Namespace(**{**vars(args), "model": "resnet50", "per_gpu_batch": 0})
+        rms = model_setup(rargs)
+        rl = f"dp{world}" if world > 1 else "single"
+        try:
+            rr = measure(rl, True, rms)
+            resnet = {"metric": rms["metric"], "value": round(rr["value"], 1), "unit": rms["unit"], "ms_per_step": round(rr["dev_ms"] / args.steps, 3),
+                      "steps": args.steps, "warmup": max(3, args.warmup), "dtype": "bf16",
+                      "config": {"model": "resnet50", "global_batch": rr["global_batch"], "per_gpu_batch": rms["per_gpu_batch"],
+                                 "image": "224x224x3 NHWC, N(0,1) pixels, labels uniform in [0,1000)", "parallelism": rl,
+                                 "optimizer": "sgd momentum 0.9", "cuda_graph": not args.no_graph},
+                      "e2e": {"value": round(rr["e2e"], 1), "unit": rms["unit"], "ms_per_step": round(rr["e2e_ms"] / args.steps, 3),
+                              "h2d_bytes_per_step": rr["h2d"], "d2h_bytes_per_step": 4},
+                      "gpu_launches": rr["launches"], "clocks": rr["clocks"],
+                      "loss_first": round(rr["first_loss"], 4), "loss_last": round(rr["last_loss"], 4)}
+        except Exception as e:  # the headline line must still be printed
+            resnet = {"error": f"{type(e).__name__}: {e}"[:300]}
     alt = None
     dp_layout = default_layout(world, ms["zoo"])
     if world > 1 and not args.parallelism and layout != dp_layout and not layout.startswith("pp"):
@@ -343,6 +366,8 @@ def run_ours(args):
         out["checkpoint"] = r["checkpoint"]
         out["config"]["microbatches"] = r["microbatches"]
         out["config"]["schedule"] = "1F1B"
+    if resnet is not None:
+        out["resnet50"] = resnet
     if alt is not None:
         out["alt"] = {"parallelism": alt["layout"], "value": round(alt["value"], 1), "ms_per_step": round(alt["dev_ms"] / args.steps, 3),
                       "e2e_value": round(alt["e2e"], 1), "note": "same model, batch and steps as pure data parallelism (fused reduce + AdamW + broadcast kernel)"}

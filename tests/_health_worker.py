@@ -34,7 +34,7 @@ def main():
             seq = torch.randint(0, 31, (2, 17), generator=gen)
             runner.step(seq[:, :-1].contiguous(), seq[:, 1:].contiguous())
             result["steps"] = step + 1
-            if rank == 0 and step == 1:
+            if step == 1:  # collective: every rank takes part, the first one writes
                 result["snapshot"] = t.save_snapshot(os.path.join(out_dir, "ckpt_step2.tnng"), with_optimizer=True)
             time.sleep(0.6)  # a step every 0.6 s: the lost rank is noticed within a few steps
     except RankFailure as e:

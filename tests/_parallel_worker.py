@@ -50,6 +50,34 @@ def main():
         t.close()
         dist.destroy_process_group()
         return
+    if mode == "dpresume":
+        # fused (sharded) optimizer: snapshot with optimizer state after 3 steps, 2 more steps; a second trainer loads
+        # the snapshot and must reproduce those 2 steps
+        def seqs(t, first, n):
+            g = torch.Generator().manual_seed(100 + t.data_rank)
+            return [torch.randint(0, 203, (t.local_batch, 129), generator=g) for _ in range(first + n)][first:]
+        a = ParallelTrainer(cfg, layout=f"dp{world}", fused=fused, log=False, heap_bytes=256 << 20)
+        for sq in seqs(a, 0, 3):
+            a.train_step(sq[:, :-1].contiguous(), sq[:, 1:].contiguous())
+        snap = sys.argv[3] + ".snap.tnng"
+        a.save_snapshot(snap, with_optimizer=True)
+        for sq in seqs(a, 3, 2):
+            a.train_step(sq[:, :-1].contiguous(), sq[:, 1:].contiguous())
+        b = ParallelTrainer(cfg, layout=f"dp{world}", fused=fused, log=False, heap_bytes=256 << 20)
+        b.load_snapshot(snap)
+        steps = (a.optimizer.step_count - 2, b.optimizer.step_count)
+        for sq in seqs(b, 3, 2):
+            b.train_step(sq[:, :-1].contiguous(), sq[:, 1:].contiguous())
+        _lib.check_status()
+        pa, pb = a.graph.params_flat.float(), b.graph.params_flat.float()
+        out = {"steps": steps, "diff": float((pa - pb).abs().max()), "scale": float(pa.abs().max()),
+               "sidecar": os.path.exists(snap + ".opt")}
+        if rank == 0:
+            print("RESULT " + json.dumps(out), flush=True)
+        a.close()
+        b.close()
+        dist.destroy_process_group()
+        return
     if mode == "tpeq":
         # plain SGD: the update is proportional to the gradient, so rounding noise stays proportional too (the first
         # Adam steps move every element by the full learning rate in the direction of a sign that noise can flip)

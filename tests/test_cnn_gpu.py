@@ -19,6 +19,9 @@ def close(got, ref, tol=2e-2, what=""):
     err = (got - ref).abs().max().item()
     scale = ref.abs().max().item() + 1e-6
     assert err / scale < tol, f"{what} rel err {err / scale:.4g}"
+    # and element by element: 3 % of the element plus half of that tolerance times the largest value
+    bad = (got - ref).abs() > (3e-2 * ref.abs() + 0.5 * tol * scale)
+    assert not bool(bad.any()), f"{what}: {int(bad.sum())} of {bad.numel()} elements outside the per-element tolerance"
 
 
 @pytest.mark.parametrize("n,h,c,o,k,s,p", [(2, 16, 64, 64, 3, 1, 1), (2, 15, 32, 48, 3, 2, 1), (3, 14, 64, 128, 1, 1, 0),

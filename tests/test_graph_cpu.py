@@ -138,3 +138,34 @@ def test_memory_report_counts_params_and_saved_tensors():
     assert sum(r[1] for r in rows) >= g.num_parameters() * g.params_flat.element_size()
     assert sum(r[2] for r in rows) > 0
     assert "total" in g.format_memory_report()
+
+
+def test_batchnorm_without_affine_still_saves_four_tensors(tmp_path):
+    """The reference lists gamma, beta, running_mean, running_var for every batch norm, affine or not
+    (include/nn/layers_impl/batchnorm_layer.hpp:51-81): a file of an affine=false layer must carry all four and load
+    back, and the untrained gamma / beta must not influence the output."""
+    from tnn_b200.models import zoo
+    from tnn_b200.nn.layers import BatchNorm
+
+    def build():
+        b = zoo._start((1, 8, 8, 3))
+        b.conv(4, 3, 1, 1, False, "c1")
+        b.apply(BatchNorm(4, 1e-5, 0.1, False, False, name="bn_plain"))
+        return zoo._finish(b.flatten().dense(5, True, "fc"))
+
+    g = build().compile(device="cpu", seed=3)
+    bn = [l for l in g.layers() if l.name == "bn_plain"][0]
+    assert [s.name for s in bn.param_specs()] == ["gamma", "beta", "running_mean", "running_var"]
+    assert [s.trainable for s in bn.param_specs()] == [False, False, False, False]
+    x = torch.randn(6, 8, 8, 3)
+    g.set_training(True)
+    y = g.forward({"input": x})["output"]
+    bn.params[0].fill_(7.0)   # gamma of a non-affine layer is carried along, not used
+    y2 = g.forward({"input": x})["output"]
+    assert torch.allclose(y, y2)
+    path = str(tmp_path / "bn.tnng")
+    g.save_state(path)
+    g2 = Graph.load_state(path, device="cpu")
+    bn2 = [l for l in g2.layers() if l.name == "bn_plain"][0]
+    assert len(bn2.params) == 4 and not bn2.affine
+    assert torch.allclose(bn2.params[0], bn.params[0]) and torch.allclose(bn2.params[3], bn.params[3])

@@ -13,10 +13,14 @@ def rnd(*shape, scale=1.0):
 
 
 def close(got, ref, tol=2e-2, what=""):
+    """Largest error against the largest value, and every element on its own (3 % of the element plus half of the
+    first tolerance times the largest value): a kernel that drops its small elements does not pass."""
     got, ref = got.float().cpu(), ref.float().cpu()
     err = (got - ref).abs().max().item()
     scale = ref.abs().max().item() + 1e-6
     assert err / scale < tol, f"{what} rel err {err / scale:.4g} (abs {err:.4g})"
+    bad = (got - ref).abs() > (3e-2 * ref.abs() + 0.5 * tol * scale)
+    assert not bool(bad.any()), f"{what}: {int(bad.sum())} of {bad.numel()} elements outside the per-element tolerance"
 
 
 @pytest.mark.parametrize("kind,alpha", [("relu", 0), ("gelu", 0), ("elu", 1.0), ("leaky_relu", 0.01),

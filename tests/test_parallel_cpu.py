@@ -77,6 +77,24 @@ def test_tp2_equals_single_process(tmp_path):
     assert n_checked > 20
 
 
+def test_snapshot_with_optimizer_resumes_exactly(tmp_path):
+    """A data-parallel and a tensor-parallel job each write a snapshot with optimizer state after three steps; a
+    second trainer that loads it must reproduce the next two steps bit for bit (weights, AdamW moments, bias
+    correction step, scheduler position). The data-parallel job leaves the same ``.opt`` sidecar a single process
+    writes, the tensor-parallel one a sidecar per rank."""
+    for mode, port in (("resume_dp", 29624), ("resume_tp", 29625)):
+        res = launch(2, mode, str(tmp_path / f"{mode}.pt"), port)
+        for st in res:
+            assert st["step"][0] == st["step"][1] == 3 and st["global"][0] == st["global"][1], st
+            assert st["lr"][0] == st["lr"][1] and st["lr"][0] < 1e-2, st      # the scheduler had stepped twice
+            assert st["diff"] < 1e-7 and st["moved"] > 1e-3, st
+        names = res[0]["sidecars"]
+        if mode == "resume_dp":
+            assert any(n.endswith(".tnng.opt") for n in names), names
+        else:
+            assert sum(".opt.rank" in n for n in names) == 2, names
+
+
 def test_grad_hook_order_and_bucket_plan():
     """Backward reports final gradient ranges from the end of the flat buffer; the bucket plan follows that order."""
     import torch

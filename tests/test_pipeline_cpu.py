@@ -82,22 +82,23 @@ def test_block_aligned_ratios_cut_between_blocks():
     assert len(st[0].output_uids) == 1
 
 
-def launch(n, layout, out, port):
+def launch(n, layout, out, port, accum=1):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", str(port), os.path.join(HERE, "_cpu_pp_worker.py"), layout, out]
+           "--master-port", str(port), os.path.join(HERE, "_cpu_pp_worker.py"), layout, out, str(accum)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     return torch.load(out, weights_only=False)
 
 
-def reference():
+def reference(accum=1):
     zoo.register_model("tiny_gpt", lambda: zoo.gpt2(128, 2, 4, "t", seq_len=128, vocab=97, drop=0.0))
     cfg = TrainingConfig.from_dict({"model_name": "tiny_gpt", "batch_size": 4, "device_type": "CPU", "seed": 5,
+                                    "gradient_accumulation_steps": accum,
                                     "optimizer": {"type": "sgd", "learning_rate": 0.1, "momentum": 0.9}})
     t = Trainer(cfg, log=False)
     gen = torch.Generator().manual_seed(100)
     losses = []
-    for _ in range(3):
+    for _ in range(3 if accum == 1 else 2 * accum):
         seq = torch.randint(0, 97, (4, 129), generator=gen)
         losses.append(float(t.train_step(seq[:, :-1].contiguous(), seq[:, 1:].contiguous()).item()))
     return losses, {l.name: [p.clone() for p in l.params] for l in t.graph.layers()}
@@ -108,6 +109,19 @@ def test_pp2_matches_single_process(tmp_path):
     ref_losses, ref_params = reference()
     got_losses = res[1][0]
     assert all(abs(a - b) < 1e-3 for a, b in zip(got_losses, ref_losses)), (got_losses, ref_losses)
+    for losses, params, _, _ in res:
+        for name, ps in params.items():
+            for p, q in zip(ps, ref_params[name]):
+                assert torch.allclose(p, q, atol=2e-4), name
+
+
+def test_pp2_gradient_accumulation_matches_single_process(tmp_path):
+    """Two batches per update: the pipeline must add their (halved) gradients up and update every second batch,
+    exactly like the single-process trainer with the same setting."""
+    res = launch(2, "pp2", str(tmp_path / "ppacc.pt"), 29633, accum=2)
+    ref_losses, ref_params = reference(accum=2)
+    got_losses = res[1][0]
+    assert len(got_losses) == 4 and all(abs(a - b) < 1e-3 for a, b in zip(got_losses, ref_losses)), (got_losses, ref_losses)
     for losses, params, _, _ in res:
         for name, ps in params.items():
             for p, q in zip(ps, ref_params[name]):

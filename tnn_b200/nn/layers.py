@@ -619,19 +619,18 @@ class BatchNorm(Layer):
                 ("momentum", T_FLOAT, f32(self.momentum)), ("affine", T_BOOL, self.affine), ("use_relu", T_BOOL, self.use_relu)]
 
     def param_specs(self):
+        # Always four tensors, like the reference's param_descriptors: with affine = false, gamma = 1 and beta = 0
+        # are still saved and loaded (files are interchangeable in both directions) but never trained or read.
         c = (self.num_features,)
-        specs = []
-        if self.affine:
-            specs += [ParamSpec("gamma", c, True, ("ones", 0)), ParamSpec("beta", c, True, ("zeros", 0))]
-        specs += [ParamSpec("running_mean", c, False, ("zeros", 0)), ParamSpec("running_var", c, False, ("ones", 0))]
-        return specs
+        return [ParamSpec("gamma", c, self.affine, ("ones", 0)), ParamSpec("beta", c, self.affine, ("zeros", 0)),
+                ParamSpec("running_mean", c, False, ("zeros", 0)), ParamSpec("running_var", c, False, ("ones", 0))]
 
     def _split(self):
         # gamma / beta in the compute dtype, running statistics always from the fp32 master views
         stats = getattr(self, "masters", None) or self.params
         if self.affine:
             return self.params[0], self.params[1], stats[2], stats[3]
-        return None, None, stats[0], stats[1]
+        return None, None, stats[2], stats[3]
 
     def forward(self, inputs, ctx):
         x = inputs[0].contiguous()

@@ -54,11 +54,26 @@ class Optimizer:
         """Keep lr / bias corrections in device memory so a captured step sees new values."""
         dev = self.graph.master_flat.device
         self.hyper = torch.zeros(4, dtype=torch.float32, device=dev)
-        self._hyper_host = torch.zeros(4, dtype=torch.float32).pin_memory() if dev.type == "cuda" else torch.zeros(4)
+        # The upload is an asynchronous copy from pinned memory, and a replayed step is a single launch, so the host
+        # can run several steps ahead of the device: every step gets a staging buffer of its own out of a small ring,
+        # and a buffer is rewritten only after the copy that last read it has completed (its event).
+        cuda = dev.type == "cuda"
+        self._hyper_ring = [torch.zeros(4, dtype=torch.float32).pin_memory() if cuda else torch.zeros(4) for _ in range(8 if cuda else 1)]
+        self._hyper_events = [torch.cuda.Event() if cuda else None for _ in self._hyper_ring]
+        self._hyper_used = [False] * len(self._hyper_ring)
+        self._hyper_next = 0
 
     def _push_hyper(self, lr, bc1, bc2, gscale):
-        self._hyper_host[0], self._hyper_host[1], self._hyper_host[2], self._hyper_host[3] = lr, bc1, bc2, gscale
-        self.hyper.copy_(self._hyper_host, non_blocking=True)
+        k = self._hyper_next
+        self._hyper_next = (k + 1) % len(self._hyper_ring)
+        buf, ev = self._hyper_ring[k], self._hyper_events[k]
+        if ev is not None and self._hyper_used[k]:
+            ev.synchronize()
+        buf[0], buf[1], buf[2], buf[3] = lr, bc1, bc2, gscale
+        self.hyper.copy_(buf, non_blocking=True)
+        if ev is not None:
+            ev.record()
+            self._hyper_used[k] = True
 
     def prepare_step(self) -> None:
         """Host-side part of ``update`` (step count, hyper-parameter upload); call before a graph replay."""

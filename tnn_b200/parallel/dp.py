@@ -236,6 +236,46 @@ class FusedDPOptimizer:
             if s["v"] is not None:
                 s["v"].copy_(d[f"v{k}"])
 
+    # --- the unsharded form of the state: what a single-process optimizer of the same type saves and loads ---
+    def full_state(self, group=None) -> dict:
+        """Moments gathered to full-length flat vectors (``m``/``v`` for Adam, ``velocity`` for SGD) plus the
+        fp32 master values of every slice from the rank that owns them. Collective over ``group`` (the ranks that
+        share the slices); every rank gets the result. Only meaningful when one region covers the whole buffer."""
+        g = self.graph
+        n = g.total_elems
+        dev = g.master_flat.device
+        full_m = torch.zeros(n, dtype=torch.float32, device=dev)
+        full_v = torch.zeros(n, dtype=torch.float32, device=dev) if self.is_adam else None
+        master = torch.zeros(n, dtype=torch.float32, device=dev)
+        for s in self.sites:
+            lo, hi = s["lo"], s["hi"]
+            full_m[lo:hi] = s["m"][:hi - lo]
+            if full_v is not None:
+                full_v[lo:hi] = s["v"][:hi - lo]
+            master[lo:hi] = g.master_flat[lo:hi]
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            for t in (full_m, full_v, master):
+                if t is not None:
+                    dist.all_reduce(t, group=group)
+        d = {"step": torch.tensor(self.opt.step_count), "lr": torch.tensor(self.opt.lr), "master": master}
+        if self.is_adam:
+            d.update(m=full_m, v=full_v)
+        else:
+            d["velocity"] = full_m
+        return d
+
+    def load_full_state(self, d) -> None:
+        """Inverse of :meth:`full_state` for this rank's slices; ``d`` may come from a single-process optimizer."""
+        self.opt.step_count = int(d["step"])
+        self.opt.lr = float(d["lr"])
+        first = d.get("m", d.get("velocity"))
+        for s in self.sites:
+            lo, hi = s["lo"], s["hi"]
+            if first is not None:
+                s["m"][:hi - lo].copy_(first[lo:hi])
+            if s["v"] is not None and "v" in d:
+                s["v"][:hi - lo].copy_(d["v"][lo:hi])
+
 
 class NcclDPOptimizer:
     """Library-collective version: all-reduce (gloo/CPU) or reduce-scatter + all-gather (NCCL) around

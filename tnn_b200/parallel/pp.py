@@ -139,6 +139,24 @@ class PipelineTrainer:
             self.optimizer = opt.attach(self.stage)
         self.scheduler = create_scheduler(cfg.scheduler, self.optimizer)
         self.loss = create_loss(cfg.loss)
+        # Rendezvous of a tensor-parallel group (fused path): the fused kernels of a stage hand rows to each other with
+        # waits that are bounded at about two seconds, which is ample for ranks that run in step but not for a rank
+        # whose boundary tensor is still on its way through the pipeline (a neighbour stage that is late, a
+        # connection NCCL is still setting up, a checkpoint write). So the members of a group meet right after each
+        # of them has received a micro-batch's boundary tensor - a flag store into every partner's memory and a
+        # stream-ordered wait for theirs, with a limit of its own (ten seconds, reported separately) - and only then
+        # enter the stage's kernels together.
+        self._rv = None
+        if self.fused and topo.tp > 1:
+            import ctypes
+            from ..ops import _lib
+            lib = _lib.load()
+            lib.tnnb_flag_wait.argtypes = [ctypes.c_void_p, ctypes.c_uint, ctypes.c_ulonglong, ctypes.c_void_p, ctypes.c_void_p]
+            lib.tnnb_flag_set.argtypes = [ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p]
+            flags = self.heap.alloc((16,), torch.int32)
+            peers = self.heap.peer_ptrs(flags, topo.tp_ranks)
+            self._rv = {"lib": lib, "flags": flags, "mine": flags.data_ptr(), "epoch": 0,
+                        "others": [(t, peers[t]) for t in range(topo.tp) if t != topo.tp_idx]}
         self.prev = topo.pp_ranks[topo.pp_idx - 1] if not self.first else None
         self.next = topo.pp_ranks[topo.pp_idx + 1] if not self.last else None
         self.global_step = 0
@@ -205,6 +223,21 @@ class PipelineTrainer:
             r.wait()
         return out
 
+    def _tp_rendezvous(self) -> None:
+        """See the constructor: every member of the tensor-parallel group calls this at the same points of the schedule."""
+        rv = self._rv
+        if rv is None:
+            return
+        import ctypes
+        from ..ops import _lib
+        rv["epoch"] += 1
+        st, status = _lib.stream(), _lib.ptr(_lib.status_word(self.device))
+        for t, base in rv["others"]:   # my slot in the partner's flag array
+            _lib.check_rc(rv["lib"].tnnb_flag_set(ctypes.c_void_p(base + 4 * self.topo.tp_idx), rv["epoch"], st), "tnnb_flag_set")
+        for t, _ in rv["others"]:      # the partner's slot in mine
+            _lib.check_rc(rv["lib"].tnnb_flag_wait(ctypes.c_void_p(rv["mine"] + 4 * t), rv["epoch"], 10_000_000_000, status, st),
+                          "tnnb_flag_wait")
+
     def _send(self, tensors: Dict[str, torch.Tensor], uids: Sequence[str], dst: int) -> List:
         reqs = []
         grp = self._group(dst, forward=dst > self.topo.rank)
@@ -267,6 +300,7 @@ class PipelineTrainer:
                     inputs = {in_uid: x.to(st.io_dtype) if x.is_floating_point() else x}
                 else:
                     inputs = self._recv(self.recv_uids, self.prev, shapes)
+                    self._tp_rendezvous()
                 outs = st.forward(inputs, pid=m)
                 if self.last:
                     out = outs[out_uid]
@@ -286,14 +320,21 @@ class PipelineTrainer:
                     grads = self._last_grad.pop(m)
                 else:
                     grads = self._recv(self.send_uids, self.next, shapes)
+                    self._tp_rendezvous()
                 gin = st.backward(grads, pid=m)
                 if not self.first:
                     pending_sends += self._send(gin, self.recv_uids, self.prev)
         for r in pending_sends:
             r.wait()
-        self.optimizer.update()
-        st.zero_grads()
-        self.scheduler.step()
+        # gradients of `gradient_accumulation_steps` batches (each already scaled by 1 / that count) add up in the
+        # flat gradient buffer before one update - the reference divides the loss gradient by the count and updates
+        # every count-th batch (src/nn/train.cpp:284-294, include/distributed/train.hpp:76-91)
+        self._accum_count = getattr(self, "_accum_count", 0) + 1
+        if self._accum_count >= max(1, int(self.cfg.gradient_accumulation_steps)):
+            self._accum_count = 0
+            self.optimizer.update()
+            st.zero_grads()
+            self.scheduler.step()
         self.global_step += 1
         if self.last:
             return torch.stack([l.reshape(()) for l in losses]).mean().reshape(1)

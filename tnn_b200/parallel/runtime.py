@@ -161,26 +161,105 @@ class ParallelTrainer(Trainer):
                 mine[s["lo"]:s["hi"]] = True
             g.master_flat.copy_(torch.where(mine, g.master_flat, g.params_flat.float()))
 
+    def _train_state(self) -> dict:
+        return {"scheduler": self.scheduler.state_dict(), "global_step": self.global_step,
+                "step_counter": int(self.step_counter.item()), "rng": torch.get_rng_state(),
+                "layout": self.topo.describe(), "world": self.topo.world}
+
     def save_snapshot(self, path=None, with_optimizer: bool = False, gather_tp: bool = True) -> str:
         """Writes ONE TNNG file that any layout (or the reference) can read: tensor-parallel shards are gathered
         to full tensors first (collective over the tensor-parallel group), then the first rank writes.
-        ``gather_tp=False`` writes each shard as held, to ``<path>.tp<i>``."""
-        self._refresh_master()
+        ``gather_tp=False`` writes each shard as held, to ``<path>.tp<i>``.
+
+        ``with_optimizer=True`` also saves what an exact resume needs. Pure data parallelism: the moments and the
+        fp32 master values are collected from the ranks that own them and written as the same ``<path>.opt``
+        sidecar a single-process trainer writes, so the job can resume on any number of ranks. With tensor
+        parallelism the optimizer state follows the shard layout: every rank writes ``<path>.opt.rank<r>``
+        (moments, owned fp32 master slices, scheduler, step counters), which a job of the same layout reads back.
+        Collective: every rank must call it."""
+        topo = self.topo
         path = path or self.snapshot_path()
-        if self.topo.tp > 1 and gather_tp:
+        fused_opt = isinstance(self.optimizer, FusedDPOptimizer)
+        full = None
+        if with_optimizer and topo.tp == 1 and fused_opt:
+            full = self.optimizer.full_state(topo.dp_group)
+            self.graph.master_flat.copy_(full.pop("master"))    # exact fp32 values for every slice, not bf16 copies
+        else:
+            self._refresh_master()
+        if with_optimizer and topo.tp > 1:
+            st = self._train_state()
+            st["optimizer"] = {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in self.optimizer.state_dict().items()}
+            if fused_opt:
+                st["master"] = [(s["lo"], s["hi"], self.graph.master_flat[s["lo"]:s["hi"]].detach().cpu()) for s in self.optimizer.sites]
+            os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+            torch.save(st, f"{path}.opt.rank{topo.rank}")
+        if topo.tp > 1 and gather_tp:
             from ..models import zoo
             from .tp import gather_full_state
-            full = zoo.create(self.cfg.model_name).compile(device="cpu", seed=self.cfg.seed)
-            gather_full_state(self.graph, full, self.topo)
-            if self.topo.dp_idx == 0 and self.topo.tp_idx == 0:
+            fullg = zoo.create(self.cfg.model_name).compile(device="cpu", seed=self.cfg.seed)
+            gather_full_state(self.graph, fullg, topo)
+            if topo.dp_idx == 0 and topo.tp_idx == 0:
                 os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
-                full.save_state(path)
-            return path
-        if self.topo.tp > 1:
-            path = f"{path}.tp{self.topo.tp_idx}"
-        if self.topo.dp_idx == 0:
-            return super().save_snapshot(path, with_optimizer=False)
+                fullg.save_state(path)
+        elif topo.tp > 1:
+            if topo.dp_idx == 0:
+                super().save_snapshot(f"{path}.tp{topo.tp_idx}", with_optimizer=False)
+        elif topo.dp_idx == 0:
+            if full is not None:
+                super().save_snapshot(path, with_optimizer=False)
+                st = self._train_state()
+                st["optimizer"] = {k: v.detach().cpu() for k, v in full.items()}
+                torch.save(st, path + ".opt")
+            else:
+                super().save_snapshot(path, with_optimizer=with_optimizer)
+        if dist.is_initialized():
+            dist.barrier()
         return path
+
+    def load_snapshot(self, path: str) -> None:
+        """Weights from a TNNG file of the unsharded model (sharded again here when the job is tensor parallel),
+        then the optimizer / scheduler / step state: this rank's ``<path>.opt.rank<r>`` if the job that wrote it had
+        this layout, else the unsharded ``<path>.opt`` (written by a single process or by a data-parallel job)."""
+        from ..nn.graph import Graph
+        topo = self.topo
+        g2 = Graph.load_state(path, device="cpu")
+        if topo.tp > 1:
+            from .tp import copy_full_to_shards
+            copy_full_to_shards(self.graph, g2, topo)
+        else:
+            self.graph.master_flat.copy_(g2.master_flat.to(self.graph.master_flat.device))
+            self.graph.sync_params_from_master()
+        fused_opt = isinstance(self.optimizer, FusedDPOptimizer)
+        mine, plain = f"{path}.opt.rank{topo.rank}", path + ".opt"
+        st = None
+        if os.path.exists(mine):
+            st = torch.load(mine, map_location="cpu", weights_only=False)
+            if st.get("layout") != topo.describe() or st.get("world") != topo.world:
+                raise ValueError(f"{mine} was written by a {st.get('layout')} job of {st.get('world')} ranks; this job is "
+                                 f"{topo.describe()} on {topo.world}")
+            dev = self.graph.master_flat.device
+            self.optimizer.load_state_dict({k: (v.to(dev) if isinstance(v, torch.Tensor) and v.dim() > 0 else v)
+                                            for k, v in st["optimizer"].items()})
+            for lo, hi, vals in st.get("master", []):
+                self.graph.master_flat[lo:hi].copy_(vals.to(dev))
+        elif os.path.exists(plain):
+            if topo.tp > 1:
+                raise ValueError("an unsharded optimizer state cannot be loaded into a tensor-parallel job; resume with the "
+                                 "layout that wrote the snapshot")
+            st = torch.load(plain, map_location="cpu", weights_only=False)
+            dev = self.graph.master_flat.device
+            od = {k: (v.to(dev) if isinstance(v, torch.Tensor) and v.dim() > 0 else v) for k, v in st["optimizer"].items()}
+            if fused_opt:
+                self.optimizer.load_full_state(od)
+            else:
+                self.optimizer.load_state_dict(od)
+        if st is not None:
+            self.scheduler.load_state_dict(st["scheduler"])
+            self.global_step = int(st["global_step"])
+            self.step_counter.fill_(int(st["step_counter"]))
+            torch.set_rng_state(st["rng"])
+        if dist.is_initialized():
+            dist.barrier()
 
     def close(self):
         super().close()
