@@ -95,7 +95,7 @@ def model_setup(args):
     if args.model == "resnet50":
         per_gpu = args.per_gpu_batch or 256
         return {"zoo": "imagenet_resnet50", "per_gpu_batch": per_gpu, "seq_len": None, "unit": "images/s",
-                "metric": "images_per_sec", "items_per_sample": 1, "optimizer": {"type": "sgd", "learning_rate": 0.1, "momentum": 0.9}}
+                "metric": "images_per_sec", "items_per_sample": 1, "optimizer": {"type": "sgd", "learning_rate": 0.01, "momentum": 0.9}}
     per_gpu = args.per_gpu_batch or 128
     return {"zoo": "cifar100_wrn16_8", "per_gpu_batch": per_gpu, "seq_len": None, "unit": "images/s", "metric": "images_per_sec",
             "items_per_sample": 1, "optimizer": {"type": "sgd", "learning_rate": 0.1, "momentum": 0.9}}

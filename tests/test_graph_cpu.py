@@ -35,6 +35,21 @@ def test_fused_gpt_chain_equals_unfused():
     assert torch.allclose(ga, gb, atol=1e-4, rtol=1e-3)
 
 
+def test_recompute_qkv_gives_the_same_gradients():
+    """Dropping the saved q/k/v projection and computing it again in the backward pass (what the reference's
+    attention block always does) must not change loss or gradients, fused chain or layer by layer."""
+    torch.manual_seed(0)
+    ids = torch.randint(0, 50, (3, 16))
+    labels = torch.randint(0, 50, (3, 16))
+    for fuse in (True, False):
+        a = tiny_gpt().compile(seed=1, fuse=fuse)
+        b = tiny_gpt().compile(seed=1, fuse=fuse)
+        assert b.set_recompute_qkv(True) >= 1
+        la, ga = run(a, ids, labels)
+        lb, gb = run(b, ids, labels)
+        assert torch.allclose(la, lb, atol=1e-6) and torch.allclose(ga, gb, atol=1e-6)
+
+
 def test_gpt_matches_torch_autograd():
     torch.manual_seed(1)
     g = tiny_gpt().compile(seed=2)

@@ -172,3 +172,45 @@ def test_pp2_1f1b_trains_and_saves_stage(tmp_path):
 def test_pp2_tp2_fused_trains(tmp_path):
     res = launch_pp(4, "pp2tp2", "fused", str(tmp_path / "ckpt"))
     assert res["losses"][-1] < res["losses"][0] - 0.5
+
+
+# ------------------------------------------------------------------------------------- 8 GPUs
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+def test_dp8_matches_single_process(tmp_path):
+    """Eight data-parallel ranks with the fused reduce + AdamW + broadcast kernel (bucketed, overlapped with the
+    backward pass) against one process on the combined batch of sixteen sequences."""
+    out = str(tmp_path / "dp8.pt")
+    res = launch(8, "dp", "fused", out)
+    assert res["max_rank_diff"] == 0.0 and res["dp_overlap"], res
+    gens = [torch.Generator().manual_seed(100 + r) for r in range(8)]
+    sets = [torch.cat([torch.randint(0, 203, (2, 129), generator=g) for g in gens]) for _ in range(4)]
+    zoo.register_model("tiny_gpt", lambda: zoo.gpt2(128, 2, 2, "t", seq_len=128, vocab=203, drop=0.0))
+    cfg = TrainingConfig.from_dict({"model_name": "tiny_gpt", "batch_size": 16, "device_type": "CUDA", "seed": 5,
+                                    "optimizer": {"type": "adamw", "learning_rate": 1e-2, "weight_decay": 0.01}})
+    t = Trainer(cfg, log=False)
+    for seq in sets:
+        t.train_step(seq[:, :-1].contiguous(), seq[:, 1:].contiguous())
+    ref = t.graph.params_flat.float().cpu()
+    t.close()
+    got = torch.load(out)["params"]
+    rel = (got - ref).norm() / ref.norm()
+    assert rel < 2e-2, float(rel)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+def test_tp2dp4_fused_tracks_nccl(tmp_path):
+    """The benchmark's named layout on a tiny model: four data-parallel replicas of a tensor-parallel pair. The
+    fused kernels and the NCCL path start from the same shards and see the same batches; their losses must agree
+    step by step and fall."""
+    runs = {kind: launch(8, "tp", kind, str(tmp_path / f"tp2dp4_{kind}.pt")) for kind in ("fused", "nccl")}
+    lf, ln = runs["fused"]["losses"], runs["nccl"]["losses"]
+    assert lf[-1] < lf[0] and ln[-1] < ln[0], (lf, ln)
+    assert all(abs(a - b) < 0.05 for a, b in zip(lf, ln)), (lf, ln)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+def test_pp4_tp2_fused_trains(tmp_path):
+    """Four pipeline stages of one transformer block each, every stage a tensor-parallel pair with the fused
+    hand-offs, 1F1B with two micro-batches: the layout of the GPT-2 medium benchmark configuration."""
+    res = launch_pp(8, "pp4tp2", "fused", str(tmp_path / "ckpt"))
+    assert res["losses"][-1] < res["losses"][0] - 0.5, res

@@ -132,3 +132,25 @@ def test_prefetched_batches_give_the_same_training(graphed):
     a, b = run(True), run(False)
     assert len(a) == 8 and max(abs(x - y) for x, y in zip(a, b)) < 2e-2, (a, b)
     assert abs(a[0] - a[-1]) > 1e-3  # different batches and updates: the losses move
+
+
+def test_allocation_tracker_reports_peak_per_edge():
+    """The allocation hook brackets every edge's forward and backward pass with allocator readings: a training
+    forward keeps memory (what it saved), its backward gives it back, and every peak is at least what was kept."""
+    import torch
+    from tnn_b200.models import zoo
+    g = zoo.gpt2(128, 2, 2, "t", seq_len=128, vocab=203, drop=0.0).compile(device="cuda", seed=0)
+    g.set_training(True)
+    trk = g.track_memory(True)
+    ids = torch.randint(0, 203, (4, 128), device="cuda")
+    out = g.forward({"input": ids})["output"]
+    g.backward({"output": torch.randn_like(out)})
+    rows = trk.peak_per_edge()
+    assert len(rows) == len(g.segments)
+    kept = sum(d["forward_kept"] for d in rows.values())
+    freed = sum(d["backward_freed"] for d in rows.values())
+    assert kept > 4 * 128 * 128 * 2 * 4 and freed > 0
+    assert all(d["forward_peak"] >= d["forward_kept"] for d in rows.values())
+    assert "fwd peak MiB" in trk.format()
+    g.track_memory(False)
+    assert g.alloc_hook is None

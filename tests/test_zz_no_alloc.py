@@ -59,10 +59,15 @@ def test_noalloc_matches_regular_twice(shape, relu, affine):
         mean = torch.empty(C, dtype=torch.float32, device=dev)
         rstd = torch.empty_like(mean)
         gc.collect()  # garbage of earlier tests must not be freed between the two readings
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before, _ = torch.cuda.mem_get_info()   # what the driver has left: sees cudaMalloc calls of any origin
         rc = _call(lib, x, y, gamma, beta, mean, rstd, rm_b, rv_b, eps, mom, relu)
         assert rc == 0, lib.tnnb_noalloc_strerror(rc).decode()
         assert torch.cuda.memory_allocated() <= before  # the call took nothing from the tensor allocator
+        torch.cuda.synchronize()
+        if it > 0:  # the first call on a device may load the module that holds the scratch array (set-up)
+            assert torch.cuda.mem_get_info()[0] >= free_before, "device memory was allocated behind the allocator's back"
         torch.cuda.synchronize()
         # plain fp32 reference of the same op
         x2 = x.float().reshape(-1, C)

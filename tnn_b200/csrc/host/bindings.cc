@@ -305,6 +305,19 @@ PYBIND11_MODULE(_host, m) {
         if (!ok) return py::none();
         return py::make_tuple(ep, py::bytes(msg));
       }, py::arg("timeout_s") = -1.0)
+      .def("echo", [](TcpCommunicator& c, const std::string& stop) {
+        py::gil_scoped_release rel;
+        return c.echo(stop);
+      }, py::arg("stop_message"))
+      .def("ping_pong", [](TcpCommunicator& c, const std::string& ep, size_t bytes, double seconds) {
+        double dt = 0.0;
+        uint64_t n;
+        {
+          py::gil_scoped_release rel;
+          n = c.ping_pong(ep, bytes, seconds, &dt);
+        }
+        return py::make_tuple(n, dt);
+      }, py::arg("endpoint"), py::arg("message_bytes"), py::arg("seconds"))
       .def("flush", &TcpCommunicator::flush, py::arg("timeout_s") = 30.0, py::call_guard<py::gil_scoped_release>())
       .def("stop", &TcpCommunicator::stop, py::call_guard<py::gil_scoped_release>())
       .def("stats", [](const TcpCommunicator& c) {

@@ -306,6 +306,34 @@ void TcpCommunicator::read_loop(std::shared_ptr<Conn> c) {
   c->cv.notify_all();
 }
 
+uint64_t TcpCommunicator::echo(const std::string& stop_message) {
+  uint64_t n = 0;
+  std::string from, msg;
+  while (recv(-1.0, &from, &msg)) {
+    if (msg == stop_message) break;
+    send(from, std::move(msg));
+    msg.clear();
+    ++n;
+  }
+  return n;
+}
+
+uint64_t TcpCommunicator::ping_pong(const std::string& endpoint, size_t message_bytes, double seconds, double* elapsed_s) {
+  auto payload = std::make_shared<std::string>(message_bytes, '\0');
+  const auto t0 = std::chrono::steady_clock::now();
+  auto elapsed = [&] { return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count(); };
+  uint64_t n = 0;
+  std::string from, msg;
+  while (elapsed() < seconds) {
+    send_view(endpoint, payload->data(), payload->size(), payload);
+    if (!recv(60.0, &from, &msg)) throw std::runtime_error("the echo did not come back");
+    if (msg.size() != message_bytes) throw std::runtime_error("the echo has the wrong length");
+    ++n;
+  }
+  if (elapsed_s) *elapsed_s = elapsed();
+  return n;
+}
+
 void TcpCommunicator::deliver(const std::string& from, std::string&& msg) {
   {
     std::lock_guard<std::mutex> g(inbox_mu_);

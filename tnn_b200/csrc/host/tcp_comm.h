@@ -45,6 +45,15 @@ class TcpCommunicator {
   void send_view(const std::string& endpoint, const char* data, size_t n, std::shared_ptr<const void> keep);
   // Next complete message, oldest first. False when `timeout_s` ran out (negative = wait for ever) or after stop().
   bool recv(double timeout_s, std::string* endpoint, std::string* message);
+  // Benchmark loops that stay inside the communicator (the reference's tcp_communicator_benchmark.cpp bounces
+  // messages between two of its communicators without leaving C++ either):
+  //   echo()       send every received message back to its sender (the received buffer itself, no copy) until a
+  //                message equal to `stop_message` arrives or the endpoint stops; returns the number echoed.
+  //   ping_pong()  send one `message_bytes` message to `endpoint` and wait for the echo, again and again for
+  //                `seconds`; returns the number of round trips and stores the elapsed time. The same buffer is
+  //                sent every time, so no copy is made on this side either.
+  uint64_t echo(const std::string& stop_message);
+  uint64_t ping_pong(const std::string& endpoint, size_t message_bytes, double seconds, double* elapsed_s);
   void flush(double timeout_s = 30.0);                 // wait until every queued packet has been written
   void stop();
 

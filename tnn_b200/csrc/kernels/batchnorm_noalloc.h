@@ -21,6 +21,9 @@
 //  * There is one scratch array per device. Two calls that may overlap on the same device (different
 //    streams, or different host threads) race on it; serialise them on one stream or with events.
 //    The first call on a device is also not safe to make from two host threads at once.
+//  * The array's address is looked up once per device and remembered for the life of the process. A
+//    cudaDeviceReset() in the same process unloads the module and makes the remembered address stale:
+//    do not call this entry point again after a device reset (restart the process instead).
 //  * Returns TNNB_NOALLOC_OK (0) or a negative code; tnnb_noalloc_strerror gives the text.
 #pragma once
 

@@ -177,6 +177,11 @@ class FlashAttentionBlock(Layer):
     place; there are no transposes. The checkpoint still sees the reference's eight tensors
     (q.W, q.b, k.W, k.b, v.W, v.b, out.W, out.b) through :meth:`param_descriptors`.
     ``is_causal`` is not part of the saved config (a reloaded block is causal), as in the reference.
+
+    ``recompute_qkv`` (attribute, default off): do not keep the packed q/k/v projection for the backward pass but
+    compute it again from the saved input - the reference's backward always does this
+    (src/nn/blocks_impl/flash_attention_block.cpp:216-224); here it trades one extra GEMM per block for
+    ``3 * B * S * E`` elements of saved activations. ``Graph.set_recompute_qkv`` switches every block of a model.
     """
     TYPE_NAME = "flash_attention_block"
 
@@ -187,6 +192,7 @@ class FlashAttentionBlock(Layer):
             raise ValueError("embed_dim must be divisible by num_heads")
         self.head_dim = self.embed_dim // self.num_heads
         self.attn_scale = float(attn_scale)
+        self.recompute_qkv = False
 
     def config_items(self):
         return [("embed_dim", T_SIZE, self.embed_dim), ("num_heads", T_SIZE, self.num_heads)]
@@ -214,7 +220,7 @@ class FlashAttentionBlock(Layer):
         qkv = gemm(x2, w, bias=b, out_dtype=x.dtype)
         a, lse = raw.attn_fwd(qkv, B, S, self.num_heads, self.head_dim, self.is_causal, self.attn_scale)
         y = gemm(a, wo, bias=bo, out_dtype=x.dtype)
-        ctx.update(x=x2, qkv=qkv, a=a, lse=lse, dims=(B, S))
+        ctx.update(x=x2, qkv=None if self.recompute_qkv else qkv, a=a, lse=lse, dims=(B, S))
         return y.reshape(B, S, E)
 
     def backward(self, grad, ctx):
@@ -225,7 +231,8 @@ class FlashAttentionBlock(Layer):
             gemm(dy, ctx["a"], a_t=True, b_t=True, out=self.grads[2], atomic=True)
             raw.colsum_accum(dy, self.grads[3])
         da = gemm(dy, wo, b_t=True, out_dtype=dy.dtype)
-        dqkv = raw.attn_bwd(ctx["qkv"], ctx["a"], da, ctx["lse"], B, S, self.num_heads, self.head_dim, self.is_causal,
+        qkv = ctx["qkv"] if ctx["qkv"] is not None else gemm(ctx["x"], w, bias=b, out_dtype=dy.dtype)
+        dqkv = raw.attn_bwd(qkv, ctx["a"], da, ctx["lse"], B, S, self.num_heads, self.head_dim, self.is_causal,
                             self.attn_scale)
         if self.grads[0] is not None:
             gemm(dqkv, ctx["x"], a_t=True, b_t=True, out=self.grads[0], atomic=True)

@@ -88,6 +88,53 @@ def _layer_call(self: Layer, *nodes: Node) -> Node:
 Layer.__call__ = _layer_call
 
 
+class AllocationTracker:
+    """Per-segment readings of the device allocator (see ``Graph.track_memory``). ``rows`` holds
+    ``(segment, pass, bytes_live_after - bytes_live_before, peak_above_start)``; on the CPU, where there is no
+    allocator to ask, both figures are zero."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.rows: List[Tuple[str, str, int, int]] = []
+        self._start = 0
+
+    def enter(self) -> None:
+        if self.cuda:
+            torch.cuda.reset_peak_memory_stats(self.device)
+            self._start = torch.cuda.memory_allocated(self.device)
+
+    def leave(self, name: str, which: str) -> None:
+        if self.cuda:
+            now = torch.cuda.memory_allocated(self.device)
+            peak = torch.cuda.max_memory_allocated(self.device)
+            self.rows.append((name, which, now - self._start, max(0, peak - self._start)))
+        else:
+            self.rows.append((name, which, 0, 0))
+
+    def peak_per_edge(self) -> Dict[str, Dict[str, int]]:
+        """``{segment: {"forward_kept", "forward_peak", "backward_freed", "backward_peak"}}`` over everything seen."""
+        out: Dict[str, Dict[str, int]] = {}
+        for name, which, delta, peak in self.rows:
+            d = out.setdefault(name, {"forward_kept": 0, "forward_peak": 0, "backward_freed": 0, "backward_peak": 0})
+            if which == "forward":
+                d["forward_kept"] = max(d["forward_kept"], delta)
+                d["forward_peak"] = max(d["forward_peak"], peak)
+            else:
+                d["backward_freed"] = max(d["backward_freed"], -delta)
+                d["backward_peak"] = max(d["backward_peak"], peak)
+        return out
+
+    def format(self) -> str:
+        rows = self.peak_per_edge()
+        w = max([len(n) for n in rows] + [5])
+        mib = 2 ** 20
+        lines = [f"{'edge':<{w}}  {'fwd kept MiB':>12}  {'fwd peak MiB':>12}  {'bwd freed MiB':>13}  {'bwd peak MiB':>12}"]
+        lines += [f"{n:<{w}}  {d['forward_kept'] / mib:>12.2f}  {d['forward_peak'] / mib:>12.2f}  {d['backward_freed'] / mib:>13.2f}  "
+                  f"{d['backward_peak'] / mib:>12.2f}" for n, d in rows.items()]
+        return "\n".join(lines)
+
+
 class Graph:
     def __init__(self):
         self.nodes: List[Node] = []
@@ -102,6 +149,7 @@ class Graph:
         self.io_dtype = torch.float32
         self.params_flat: Optional[torch.Tensor] = None   # compute copy (bf16 or fp32)
         self.master_flat: Optional[torch.Tensor] = None   # fp32 master (aliases params_flat for fp32)
+        self.alloc_hook: Optional["AllocationTracker"] = None  # per-segment device-memory accounting (track_memory)
         self.grads_flat: Optional[torch.Tensor] = None    # fp32
         self.trainable_mask: Optional[torch.Tensor] = None
         self.layer_slices: Dict[int, List[Tuple[int, int, Tuple[int, ...], bool]]] = {}
@@ -299,6 +347,17 @@ class Graph:
         for l in self.layers():
             l.set_training(flag)
 
+    def set_recompute_qkv(self, flag: bool = True) -> int:
+        """Switch every attention block between keeping its packed q/k/v projection for the backward pass and
+        computing it again there (less saved activation memory, one more GEMM per block). Returns the number of
+        blocks switched."""
+        n = 0
+        for l in self.layers():
+            if hasattr(l, "recompute_qkv"):
+                l.recompute_qkv = bool(flag)
+                n += 1
+        return n
+
     def train(self):
         self.set_training(True)
 
@@ -389,13 +448,18 @@ class Graph:
                 t = t.to(self.io_dtype)
             vals[id(by_uid[uid])] = t
         prof = self.profiler
+        mem = self.alloc_hook
         for k, seg in enumerate(self.segments):
             sctx = st["seg"][k] = {"_step": self.step, "_pid": pid}
+            if mem is not None:
+                mem.enter()
             if prof is None:
                 seg.forward(vals, sctx)
             else:
                 with prof.span(self.segment_name(k), "forward"):
                     seg.forward(vals, sctx)
+            if mem is not None:
+                mem.leave(self.segment_name(k), "forward")
         out = {n._uid: vals[id(n)] for n in self.output_nodes}
         if not self.training:
             self._ctx.pop(pid, None)
@@ -415,12 +479,18 @@ class Graph:
         prof = self.profiler
         hook = self.grad_hook
         floors = self.segment_floors() if hook is not None else None
+        mem = self.alloc_hook
         for k in reversed(range(len(self.segments))):
+            if mem is not None:
+                mem.enter()
             if prof is None:
                 self.segments[k].backward(gvals, st["seg"][k], need_in)
             else:
                 with prof.span(self.segment_name(k), "backward"):
                     self.segments[k].backward(gvals, st["seg"][k], need_in)
+            st["seg"][k] = None  # what the segment saved for this pass is dead now
+            if mem is not None:
+                mem.leave(self.segment_name(k), "backward")
             if hook is not None and floors[k] is not None:
                 hook(floors[k])
         return {n._uid: gvals[id(n)] for n in self.input_nodes if id(n) in gvals and gvals[id(n)] is not None}
@@ -430,6 +500,15 @@ class Graph:
         seg = self.segments[k]
         names = [self.edges[i].layer.name for i in range(seg.start, seg.end)]
         return names[0] if len(names) == 1 else f"{names[0]}..{names[-1]}[{type(seg).__name__.lstrip('_')}]"
+
+    def track_memory(self, on: bool = True) -> Optional["AllocationTracker"]:
+        """Install (or remove) the allocation hook: while it is installed every executor segment's forward and
+        backward pass is bracketed by readings of the device allocator, which gives, per edge of the graph, how
+        much memory the pass left allocated and how far above its starting level it peaked (the reference gathers
+        the same figures through its allocator's hooks in ``Graph::forward``, src/nn/graph.cpp:206-233). Not for a
+        captured step: the readings synchronise nothing but they are host calls."""
+        self.alloc_hook = AllocationTracker(self.device) if on else None
+        return self.alloc_hook
 
     def memory_report(self, pid: int = 0) -> List[Tuple[str, int, int]]:
         """``(segment name, parameter bytes, bytes saved for backward)`` per executor segment.
@@ -798,7 +877,9 @@ class _GPTChain(_Segment):
             z = torch.empty(x.shape[0], fc1.output_features, dtype=x.dtype, device=x.device)
             gact = gemm(h2, fc1.params[0], bias=fc1.params[1], gelu=True, save_preact=z)
             y2 = gemm(gact, fc2.params[0], bias=fc2.params[1])
-            s.update(qkv=qkv, a=a, lse=lse, x1=x1, h2=h2, z=z, g=gact, p1=p1, seed1=seed1)
+            # recompute_qkv: the packed projection (3 x the residual stream per block) is not kept for the backward
+            # pass but computed again there from the saved layer-norm output
+            s.update(qkv=None if attn.recompute_qkv else qkv, a=a, lse=lse, x1=x1, h2=h2, z=z, g=gact, p1=p1, seed1=seed1)
             saved.append(s)
             x, pending = x1, y2
             p_pend = drop2.dropout_rate if drop2.training else 0.0
@@ -846,7 +927,8 @@ class _GPTChain(_Segment):
             gemm(dy1, s["a"], a_t=True, b_t=True, out=attn.grads[2], atomic=True)
             raw.colsum_accum(dy1, attn.grads[3])
             da = gemm(dy1, wo, b_t=True)
-            dqkv = raw.attn_bwd(s["qkv"], s["a"], da, s["lse"], B, S, attn.num_heads, attn.head_dim, attn.is_causal,
+            qkv = s["qkv"] if s["qkv"] is not None else gemm(s["h1"], wqkv, bias=bqkv)
+            dqkv = raw.attn_bwd(qkv, s["a"], da, s["lse"], B, S, attn.num_heads, attn.head_dim, attn.is_causal,
                                 attn.attn_scale)
             gemm(dqkv, s["h1"], a_t=True, b_t=True, out=attn.grads[0], atomic=True)
             raw.colsum_accum(dqkv, attn.grads[1])

@@ -95,7 +95,7 @@ class _TPGPTChain(_Segment):
             z = torch.empty(M, st["F"], dtype=x.dtype, device=x.device)
             gact = st["g2"].gemm(fc1.params[0], bias=fc1.params[1], gelu_preact=z)  # [M, 4E/tp]
             y2 = st["s_fc2"].gemm(gact, fc2.params[0], bias=fc2.params[1])        # [Ms, E]
-            s.update(qkv=qkv, a=a, lse=lse, x1=x1, z=z, g=gact, p1=p1, seed1=seed1, heads=heads)
+            s.update(qkv=None if attn.recompute_qkv else qkv, a=a, lse=lse, x1=x1, z=z, g=gact, p1=p1, seed1=seed1, heads=heads)
             saved.append(s)
             x, pending, pend_site = x1, y2, st["s_fc2"]
             p_pend = drop2.dropout_rate if drop2.training else 0.0
@@ -166,7 +166,9 @@ class _TPGPTChain(_Segment):
             raw.colsum_accum(tgt, attn.grads[3])
             da = st["gb1"].gemm(wo, b_t=True)                                      # [M, E/tp]
             gemm(st["gb1"].buf, s["a"], a_t=True, b_t=True, out=attn.grads[2], atomic=True)
-            dqkv = raw.attn_bwd(s["qkv"], s["a"], da, s["lse"], B, S, s["heads"], attn.head_dim, attn.is_causal, attn.attn_scale)
+            # recompute_qkv: the gathered layer-norm output is still complete in the site's buffer, a plain GEMM redoes it
+            qkv = s["qkv"] if s["qkv"] is not None else gemm(st["g1"].buf, wqkv, bias=bqkv)
+            dqkv = raw.attn_bwd(qkv, s["a"], da, s["lse"], B, S, s["heads"], attn.head_dim, attn.is_causal, attn.attn_scale)
             # ---- QKV projection (column parallel) ----
             gemm(dqkv, st["g1"].buf, a_t=True, b_t=True, out=attn.grads[0], atomic=True)
             raw.colsum_accum(dqkv, attn.grads[1])

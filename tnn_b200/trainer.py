@@ -117,9 +117,11 @@ class Trainer:
     def _fwd_bwd(self, d: torch.Tensor, l: torch.Tensor, scale: float):
         g = self.graph
         in_uid, out_uid = g.input_nodes[0].uid(), g.output_nodes[0].uid()
+        tracking = self._print_memory_once and g.alloc_hook is None
+        if tracking:
+            g.track_memory(True)   # allocator readings around every edge of this first step
         out = g.forward({in_uid: d})[out_uid]
         if self._print_memory_once:
-            self._print_memory_once = False
             print("per-layer memory after the first forward pass:\n" + g.format_memory_report(), flush=True)
         in_place = isinstance(self.loss, CrossEntropyLoss) and out.is_cuda
         if in_place:
@@ -127,6 +129,11 @@ class Trainer:
         else:
             loss, grad = self.loss.compute(out, l, scale, True)
         g.backward({out_uid: grad})
+        if self._print_memory_once:
+            self._print_memory_once = False
+            if tracking:
+                print("device memory per edge (allocator readings, first step):\n" + g.alloc_hook.format(), flush=True)
+                g.track_memory(False)
         return loss
 
     def train_step(self, data: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
