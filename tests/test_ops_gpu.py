@@ -96,6 +96,19 @@ def test_layernorm(rows, C, fused, p):
         close(dd, rdd, what="ddelta")
     close(dg, rdg, what="dgamma")
     close(dbt, rdb, what="dbeta")
+    if fused:
+        # the same pass with the column sums of ddelta (bias gradient of the dense layer in front of the norm),
+        # accumulated onto what the buffer already holds; reference: fp32 sum of the bf16 ddelta rows
+        dbias = torch.full((C,), 0.5, device="cuda")
+        dg2, dbt2 = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+        dx2, dd2 = raw.layernorm_bwd(dh.cuda(), xo, mean, rstd, g.cuda(), dres.cuda(), True, p, 99, dg2, dbt2, dbias=dbias)
+        assert torch.equal(dx2, dx) and torch.equal(dd2, dd)
+        close(dg2, rdg, what="dgamma with dbias")
+        ref = 0.5 + rdd.float().sum(0)
+        # the kernel sums the bf16 values it stored, in fp32: only the order of the additions differs
+        err = (dbias.cpu() - 0.5 - dd.cpu().float().sum(0)).abs()
+        assert bool((err <= 1e-5 * dd.cpu().float().abs().sum(0) + 1e-6).all()), err.max().item()
+        close(dbias, ref, what="dbias")
 
 
 @pytest.mark.parametrize("rows,V,ld", [(64, 1000, 1000), (33, 100, 104), (16, 50257, 50304), (8, 10, 10), (5, 3000, 3000)])
@@ -133,9 +146,11 @@ def test_attention_fwd_bwd(B, S, H, causal):
         close(dqkv[:, i * E:(i + 1) * E], rd[:, i * E:(i + 1) * E], tol=3e-2, what="d" + name)
 
 
-@pytest.mark.parametrize("B,S,H,D,causal", [(2, 128, 2, 96, True), (1, 200, 3, 32, False), (1, 256, 1, 128, True)])
+@pytest.mark.parametrize("B,S,H,D,causal", [(2, 128, 2, 96, True), (1, 200, 3, 32, False), (1, 256, 1, 128, True),
+                                             (3, 77, 2, 96, True), (2, 512, 8, 96, False), (1, 333, 2, 40, True)])
 def test_attention_other_head_sizes(B, S, H, D, causal):
-    """Head sizes other than 64 run head by head on the GEMM kernel (the reference's attention benchmark uses 96)."""
+    """Head sizes other than 64 run as batched GEMMs over all heads with a row-softmax kernel between them (the
+    reference's attention benchmark uses 96); sequence lengths that are no multiple of 8 or 128 included."""
     torch.manual_seed(14)
     qkv = rnd(B * S, 3 * H * D, scale=0.5)
     scale = D ** -0.5
@@ -149,6 +164,24 @@ def test_attention_other_head_sizes(B, S, H, D, causal):
     _lib.check_status()
     rd = raw.attn_bwd(qkv, rout, dout, rlse, B, S, H, D, causal, scale)
     close(dqkv, rd, tol=3e-2, what="dqkv")
+
+
+def test_batched_gemm_layouts():
+    """The batched tcgen05 GEMM in all four operand layouts, bf16 and fp32 output, padded output rows."""
+    from tnn_b200.ops.gemm import gemm_batched
+    torch.manual_seed(15)
+    G, M, N, K = 5, 200, 136, 72
+    for a_t in (False, True):
+        for b_t in (False, True):
+            a = rnd(G, K, M) if a_t else rnd(G, M, K)
+            b = rnd(G, K, N) if b_t else rnd(G, N, K)
+            ref = (a.transpose(1, 2) if a_t else a).float() @ (b if b_t else b.transpose(1, 2)).float()
+            close(gemm_batched(a.cuda(), b.cuda(), a_t=a_t, b_t=b_t), ref, what=f"bf16 {a_t} {b_t}")
+            buf = torch.zeros(G, M, 144, dtype=torch.float32, device="cuda")
+            gemm_batched(a.cuda(), b.cuda(), a_t=a_t, b_t=b_t, out=buf[:, :, :N])
+            close(buf[:, :, :N], ref, tol=1e-2, what=f"f32 {a_t} {b_t}")
+            assert float(buf[:, :, N:].abs().max()) == 0.0
+    _lib.check_status()
 
 
 def test_attention_scale_one_like_reference_block():

@@ -270,6 +270,53 @@ static inline int grid_for(long long n, int per_thread, int block) {
   return (int)(g < 1 ? 1 : (g > cap ? cap : g));
 }
 
+// ------------------------------------------------------------------ row softmax of attention scores
+// For head sizes the flash kernels do not cover, attention runs as batched GEMMs with the scores materialised
+// (ops/raw.py): these two kernels are the softmax between the products. One warp per score row.
+//   forward   x = s * scale (masked above the diagonal when causal);  P = softmax(x) as bf16;
+//             lse2 = log2 of the row's sum of exp(x)  (the unit the flash kernels use)
+//   backward  p = exp2(x * log2e - lse2);  P = p as bf16;  dS = p * (dP - delta) * scale as bf16
+__global__ void __launch_bounds__(256)
+attn_softmax_fwd_kernel(const float* __restrict__ S, bf16* __restrict__ P, float* __restrict__ lse2, long long rows, int Sq,
+                        int Sk, long long ld, float scale, int causal) {
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (long long r = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += (long long)gridDim.x * wpb) {
+    const int qi = (int)(r % Sq);
+    const int lim = causal ? min(Sk, qi + 1) : Sk;  // keys [0, lim) take part
+    const float* s = S + r * ld;
+    float m = -INFINITY;
+    for (int k = lane; k < lim; k += 32) m = fmaxf(m, s[k] * scale);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float sum = 0.f;
+    for (int k = lane; k < lim; k += 32) sum += __expf(s[k] * scale - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum;
+    bf16* p = P + r * ld;
+    for (int k = lane; k < Sk; k += 32) p[k] = __float2bfloat16(k < lim ? __expf(s[k] * scale - m) * inv : 0.f);
+    if (lane == 0) lse2[r] = (m + __logf(sum)) * 1.4426950408889634f;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+attn_softmax_bwd_kernel(const float* __restrict__ S, const float* __restrict__ dP, const float* __restrict__ lse2,
+                        const float* __restrict__ delta, bf16* __restrict__ P, bf16* __restrict__ dS, long long rows, int Sq,
+                        int Sk, long long ld, float scale, int causal) {
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (long long r = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += (long long)gridDim.x * wpb) {
+    const int qi = (int)(r % Sq);
+    const int lim = causal ? min(Sk, qi + 1) : Sk;
+    const float l2 = lse2[r], dl = delta[r];
+    const float c = scale * 1.4426950408889634f;
+    for (int k = lane; k < Sk; k += 32) {
+      const float pv = k < lim ? exp2f(S[r * ld + k] * c - l2) : 0.f;
+      P[r * ld + k] = __float2bfloat16(pv);
+      dS[r * ld + k] = __float2bfloat16(pv * (dP[r * ld + k] - dl) * scale);
+    }
+  }
+}
+
 }  // namespace tnnb
 
 using namespace tnnb;
@@ -333,6 +380,24 @@ int tnnb_colsum_accum(const void* dy, long long ld, void* db, long long M, int N
   rpb = (rpb + 127) / 128 * 128;
   const int gy = (int)((M + rpb - 1) / rpb);
   colsum_kernel<<<dim3(gx, gy), dim3(8, 32), 0, (cudaStream_t)stream>>>((const bf16*)dy, ld, (float*)db, M, N, (int)rpb);
+  LAUNCH_RC();
+}
+// Scores S and outputs P (and dS) are [rows, ld] with rows = batch * Sq consecutive query rows, Sk valid columns.
+int tnnb_attn_softmax_fwd(const void* S, void* P, void* lse2, long long rows, int Sq, int Sk, long long ld, float scale,
+                          int causal, void* stream) {
+  if (rows <= 0 || Sq <= 0 || Sk <= 0 || ld < Sk) return -3;
+  const long long g = (rows + 7) / 8;
+  attn_softmax_fwd_kernel<<<(int)(g > 148 * 16 ? 148 * 16 : g), 256, 0, (cudaStream_t)stream>>>(
+      (const float*)S, (bf16*)P, (float*)lse2, rows, Sq, Sk, ld, scale, causal);
+  LAUNCH_RC();
+}
+int tnnb_attn_softmax_bwd(const void* S, const void* dP, const void* lse2, const void* delta, void* P, void* dS, long long rows,
+                          int Sq, int Sk, long long ld, float scale, int causal, void* stream) {
+  if (rows <= 0 || Sq <= 0 || Sk <= 0 || ld < Sk) return -3;
+  const long long g = (rows + 7) / 8;
+  attn_softmax_bwd_kernel<<<(int)(g > 148 * 16 ? 148 * 16 : g), 256, 0, (cudaStream_t)stream>>>(
+      (const float*)S, (const float*)dP, (const float*)lse2, (const float*)delta, (bf16*)P, (bf16*)dS, rows, Sq, Sk, ld, scale,
+      causal);
   LAUNCH_RC();
 }
 int tnnb_cast_f32_bf16(const void* s, void* d, long long n, void* stream) {

@@ -79,6 +79,8 @@ struct GemmParams {
   long long ld_res;
   int flags;
   int* status;
+  int batch;                    // batched form (single-CTA kernel): number of independent products ...
+  long long batch_stride_d;     // ... and the distance between their outputs, in elements of D
 };
 
 template <int BN>
@@ -321,7 +323,9 @@ __device__ __forceinline__ void epilogue_warp(const GemmParams& p, const EpiOut&
   }
 }
 
-template <int BN, int A_MN, int B_MN>
+// BATCHED: the tensor maps have a third (batch) dimension and the work list runs over batch x tiles; used for the
+// per-head products of attention with head sizes the flash kernels do not cover.
+template <int BN, int A_MN, int B_MN, bool BATCHED = false>
 __global__ void __launch_bounds__(320, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -364,7 +368,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const uint32_t tmem_base = *tmem_slot;
 
   const int tiles = p.num_m_blocks * p.num_n_blocks;
-  const int total_work = tiles * p.split_k;
+  const int per_batch = tiles * p.split_k;
+  const int total_work = per_batch * (BATCHED ? p.batch : 1);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -374,8 +379,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t last_phase = 0;
       bool ok = true;
       for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
-        const int ks = work / tiles;
-        const int t = work - ks * tiles;
+        const int bi = BATCHED ? work / per_batch : 0;
+        const int w = work - bi * per_batch;
+        const int ks = w / tiles;
+        const int t = w - ks * tiles;
         const int nb = t / p.num_m_blocks;
         const int mb = t - nb * p.num_m_blocks;
         const int kb0 = ks * p.kb_per_split;
@@ -390,18 +397,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           uint8_t* a_dst = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* b_dst = a_dst + Cfg::A_BYTES;
           if (A_MN == 0) {
-            tma_load_2d(a_dst, &tmA, &full[stage], kb * 64, mb * 128);
+            if (BATCHED) tma_load_3d(a_dst, &tmA, &full[stage], kb * 64, mb * 128, bi);
+            else tma_load_2d(a_dst, &tmA, &full[stage], kb * 64, mb * 128);
           } else {
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
-              tma_load_2d(a_dst + i * 8192, &tmA, &full[stage], mb * 128 + i * 64, kb * 64);
+            for (int i = 0; i < 2; ++i) {
+              if (BATCHED) tma_load_3d(a_dst + i * 8192, &tmA, &full[stage], mb * 128 + i * 64, kb * 64, bi);
+              else tma_load_2d(a_dst + i * 8192, &tmA, &full[stage], mb * 128 + i * 64, kb * 64);
+            }
           }
           if (B_MN == 0) {
-            tma_load_2d(b_dst, &tmB, &full[stage], kb * 64, nb * BN);
+            if (BATCHED) tma_load_3d(b_dst, &tmB, &full[stage], kb * 64, nb * BN, bi);
+            else tma_load_2d(b_dst, &tmB, &full[stage], kb * 64, nb * BN);
           } else {
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i)
-              tma_load_2d(b_dst + i * 8192, &tmB, &full[stage], nb * BN + i * 64, kb * 64);
+            for (int i = 0; i < BN / 64; ++i) {
+              if (BATCHED) tma_load_3d(b_dst + i * 8192, &tmB, &full[stage], nb * BN + i * 64, kb * 64, bi);
+              else tma_load_2d(b_dst + i * 8192, &tmB, &full[stage], nb * BN + i * 64, kb * 64);
+            }
           }
           last_stage = stage;
           last_phase = phase;
@@ -428,7 +441,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
-        const int ks = work / tiles;
+        const int ks = (BATCHED ? work % per_batch : work) / tiles;
         const int kb0 = ks * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
         if (!wait_or_abort(&tempty[acc], acc_phase ^ 1, abort_flag)) {
@@ -472,8 +485,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
-      const int ks = work / tiles;
-      const int t = work - ks * tiles;
+      const int bi = BATCHED ? work / per_batch : 0;
+      const int w = work - bi * per_batch;
+      const int ks = w / tiles;
+      const int t = w - ks * tiles;
       const int nb = t / p.num_m_blocks;
       const int mb = t - nb * p.num_m_blocks;
       if (!wait_or_abort(&tfull[acc], acc_phase, abort_flag)) {
@@ -482,7 +497,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + half * (BN / 2);
-      const EpiOut eo = {p.D, p.ldd, p.flags};
+      const long long d_off = BATCHED ? (long long)bi * p.batch_stride_d * ((p.flags & (EPI_ATOMIC | EPI_OUT_F32)) ? 4 : 2) : 0;
+      const EpiOut eo = {static_cast<uint8_t*>(p.D) + d_off, p.ldd, p.flags};
       epilogue_warp(p, eo, t_addr, BN / 64, mb * 128 + q * 32, nb * BN + half * (BN / 2), lane,
                     smem + STAGES * Cfg::STAGE_BYTES + 256 + (warp - 2) * 4096);
       tc_fence_before();
@@ -917,10 +933,10 @@ int sm_count() {
   return n;
 }
 
-template <int BN, int A_MN, int B_MN>
+template <int BN, int A_MN, int B_MN, bool BATCHED = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
                        cudaStream_t stream) {
-  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN, BATCHED>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1017,6 +1033,8 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
   p.ld_res = ld_res;
   p.flags = flags;
   p.status = status;
+  p.batch = 1;
+  p.batch_stride_d = 0;
 
   CUtensorMap ta, tb;
   int rc;
@@ -1097,6 +1115,60 @@ extern "C" int tnnb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
                               int split_k, int force_bn, int* status, void* stream_) {
   return gemm_dispatch(A, B, D, M, N, K, a_mn, b_mn, lda, ldb, ldd, bias, aux_in, aux_out, ld_aux, resid, ld_res, flags,
                        split_k, force_bn, status, stream_, nullptr);
+}
+
+// `batch` independent products D[b] = op(A[b]) * op(B[b])^T on the single-CTA kernel: operand b starts stride_a /
+// stride_b elements after operand b - 1 (multiples of 8), output b stride_d elements of D's type after the previous
+// one. flags: 0 (bf16 output) or EPI_OUT_F32. Used for attention with head sizes other than 64: scores and
+// probabilities of all heads in one launch each.
+extern "C" int tnnb_gemm_bf16_batched(const void* A, const void* B, void* D, int M, int N, int K, int a_mn, int b_mn,
+                                      long long lda, long long ldb, long long ldd, int batch, long long stride_a,
+                                      long long stride_b, long long stride_d, int flags, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -2;
+  if ((lda % 8) || (ldb % 8) || (stride_a % 8) || (stride_b % 8)) return -3;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -4;
+  if (flags & ~EPI_OUT_F32) return -6;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.num_m_blocks = (M + 127) / 128;
+  p.num_k_blocks = (K + 63) / 64;
+  const int bn = (N > 128) ? 256 : 128;
+  p.num_n_blocks = (N + bn - 1) / bn;
+  p.split_k = 1;
+  p.kb_per_split = p.num_k_blocks;
+  p.D = D; p.ldd = ldd;
+  p.flags = flags;
+  p.status = status;
+  p.batch = batch;
+  p.batch_stride_d = stride_d;
+  CUtensorMap ta, tb;
+  int rc;
+  {
+    uint64_t dims[3] = {(uint64_t)(a_mn ? M : K), (uint64_t)(a_mn ? K : M), (uint64_t)batch};
+    uint64_t str[2] = {(uint64_t)lda * 2, (uint64_t)stride_a * 2};
+    uint32_t box[3] = {64, (uint32_t)(a_mn ? 64 : 128), 1};
+    if ((rc = encode_tmap_bf16(&ta, A, 3, dims, str, box, nullptr))) return rc;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)(b_mn ? N : K), (uint64_t)(b_mn ? K : N), (uint64_t)batch};
+    uint64_t str[2] = {(uint64_t)ldb * 2, (uint64_t)stride_b * 2};
+    uint32_t box[3] = {64, (uint32_t)(b_mn ? 64 : bn), 1};
+    if ((rc = encode_tmap_bf16(&tb, B, 3, dims, str, box, nullptr))) return rc;
+  }
+  const int grid = min(p.num_m_blocks * p.num_n_blocks * batch, sm_count());
+#define TNNB_B(BN_, AM, BM_) return launch_gemm<BN_, AM, BM_, true>(ta, tb, p, grid, stream)
+  if (bn == 256) {
+    if (!a_mn && !b_mn) TNNB_B(256, 0, 0);
+    if (!a_mn && b_mn) TNNB_B(256, 0, 1);
+    if (a_mn && !b_mn) TNNB_B(256, 1, 0);
+    TNNB_B(256, 1, 1);
+  }
+  if (!a_mn && !b_mn) TNNB_B(128, 0, 0);
+  if (!a_mn && b_mn) TNNB_B(128, 0, 1);
+  if (a_mn && !b_mn) TNNB_B(128, 1, 0);
+  TNNB_B(128, 1, 1);
+#undef TNNB_B
 }
 
 // Tensor-parallel GEMMs on the CTA-pair kernel (protocol: tp_flags.cuh). A is [M, K] K-major.

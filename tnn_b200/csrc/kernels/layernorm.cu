@@ -151,7 +151,11 @@ ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const flo
               const float* __restrict__ rstd_i, const bf16* __restrict__ gamma, const bf16* __restrict__ dres,
               bf16* __restrict__ dx, bf16* __restrict__ ddelta, float* __restrict__ dgamma,
               float* __restrict__ dbeta, long long rows, int C, float p, unsigned long long seed,
-              const unsigned long long* __restrict__ seed_off, const __grid_constant__ TpPull pull, const __grid_constant__ TpPush push) {
+              const unsigned long long* __restrict__ seed_off, const __grid_constant__ TpPull pull, const __grid_constant__ TpPush push,
+              float* __restrict__ dbias) {
+  // dbias (fp32 [C], optional): += column sums of ddelta - the bias gradient of the dense layer whose output was
+  // added to the residual stream in front of this layer norm (a third accumulator beside dgamma / dbeta instead of a
+  // separate pass over ddelta).
   seed = mix_seed(seed, seed_off);
   const uint32_t pull_want = (TP && pull.n) ? pull.units * *pull.pass : 0u;
   extern __shared__ float sm[];  // [warps][2][C]
@@ -161,9 +165,11 @@ ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const flo
   const int chunks = C >> 3;
   const float inv_keep = 1.f / (1.f - p);
   const uint32_t thr = dropout_threshold(p);
-  float* acc_g = sm + (size_t)warp * 2 * C;
+  const int nacc = dbias ? 3 : 2;
+  float* acc_g = sm + (size_t)warp * nacc * C;
   float* acc_b = acc_g + C;
-  for (int i = lane; i < 2 * C; i += 32) acc_g[i] = 0.f;
+  float* acc_d = acc_b + C;  // only when dbias
+  for (int i = lane; i < nacc * C; i += 32) acc_g[i] = 0.f;
   __syncwarp();
   const uint4 ones = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);  // bf16 1.0 x 8
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
@@ -242,6 +248,15 @@ ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const flo
           }
           const uint4 dd = make_uint4(pack2(t[0], t[1]), pack2(t[2], t[3]), pack2(t[4], t[5]), pack2(t[6], t[7]));
           *reinterpret_cast<uint4*>(ddelta + r * C + c * 8) = dd;
+          if (dbias) {
+            float4 d0 = *reinterpret_cast<float4*>(acc_d + c * 8), d1 = *reinterpret_cast<float4*>(acc_d + c * 8 + 4);
+            float td[8];
+            unpack8(dd, td);  // the values as stored
+            d0.x += td[0]; d0.y += td[1]; d0.z += td[2]; d0.w += td[3];
+            d1.x += td[4]; d1.y += td[5]; d1.z += td[6]; d1.w += td[7];
+            *reinterpret_cast<float4*>(acc_d + c * 8) = d0;
+            *reinterpret_cast<float4*>(acc_d + c * 8 + 4) = d1;
+          }
           if (TP && r < push.rows) {
             for (int u = 0; u < push.n; ++u) *reinterpret_cast<uint4*>(push.dst[u] + r * C + c * 8) = dd;
           }
@@ -250,16 +265,20 @@ ln_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ x, const flo
     }
   }
   if (TP && push.n) tp_push_signal(push, rows, wpb);
-  if (dgamma) {
+  if (dgamma || dbias) {
     __syncthreads();
     for (int i = threadIdx.x; i < C; i += blockDim.x) {
-      float g = 0.f, bb = 0.f;
+      float g = 0.f, bb = 0.f, dd = 0.f;
       for (int w = 0; w < wpb; ++w) {
-        g += sm[(size_t)w * 2 * C + i];
-        bb += sm[(size_t)w * 2 * C + C + i];
+        g += sm[(size_t)w * nacc * C + i];
+        bb += sm[(size_t)w * nacc * C + C + i];
+        if (dbias) dd += sm[(size_t)w * nacc * C + 2 * C + i];
       }
-      atomicAdd(dgamma + i, g);
-      atomicAdd(dbeta + i, bb);
+      if (dgamma) {
+        atomicAdd(dgamma + i, g);
+        atomicAdd(dbeta + i, bb);
+      }
+      if (dbias) atomicAdd(dbias + i, dd);
     }
   }
 }
@@ -368,23 +387,24 @@ int tnnb_layernorm_fwd_tp(const void* x_in, const void* delta, void* x_out, void
 static int layernorm_bwd_impl(const void* dh, const void* x, const void* mean, const void* rstd, const void* gamma,
                               const void* dres, void* dx, void* ddelta, void* dgamma, void* dbeta, long long rows,
                               int C, float p, unsigned long long seed, const void* seed_off, void* stream,
-                              const TpPull* pull, const TpPush* push) {
+                              const TpPull* pull, const TpPush* push, void* dbias = nullptr) {
   if (C % 8 || rows <= 0) return -3;
+  if (dbias && !ddelta) return -5;
   const int mc = pick_maxch(C);
   if (!mc) return -7;
   const int block = 256, wpb = 8;
   long long g = (rows + wpb - 1) / wpb;
   const int per_sm = (mc == 3) ? 3 : (mc == 5) ? 2 : 1;
   int grid = (int)(g > 148 * per_sm ? 148 * per_sm : g);
-  size_t smem = (size_t)wpb * 2 * C * sizeof(float);  // <= 128 KB at C = 2048
+  size_t smem = (size_t)wpb * (dbias ? 3 : 2) * C * sizeof(float);  // <= 192 KB at C = 2048
   static bool attr_done = false;
   if (!attr_done) {
-    cudaFuncSetAttribute(ln_bwd_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 768 * 4);
-    cudaFuncSetAttribute(ln_bwd_kernel<5, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 1280 * 4);
-    cudaFuncSetAttribute(ln_bwd_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 2048 * 4);
-    cudaFuncSetAttribute(ln_bwd_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 768 * 4);
-    cudaFuncSetAttribute(ln_bwd_kernel<5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 1280 * 4);
-    cudaFuncSetAttribute(ln_bwd_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 2048 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 768 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<5, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 1280 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 2048 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 768 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 1280 * 4);
+    cudaFuncSetAttribute(ln_bwd_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 2048 * 4);
     attr_done = true;
   }
   cudaStream_t st = (cudaStream_t)stream;
@@ -392,7 +412,7 @@ static int layernorm_bwd_impl(const void* dh, const void* x, const void* mean, c
   ln_bwd_kernel<MC, TP_><<<grid, block, smem, st>>>((const bf16*)dh, (const bf16*)x, (const float*)mean,               \
                                                     (const float*)rstd, (const bf16*)gamma, (const bf16*)dres,         \
                                                     (bf16*)dx, (bf16*)ddelta, (float*)dgamma, (float*)dbeta, rows, C, \
-                                                    p, seed, (const unsigned long long*)seed_off, PL, PS)
+                                                    p, seed, (const unsigned long long*)seed_off, PL, PS, (float*)dbias)
   if (pull) {
     if (mc == 3) LN_B(3, true, *pull, *push); else if (mc == 5) LN_B(5, true, *pull, *push); else LN_B(8, true, *pull, *push);
   } else {
@@ -413,6 +433,14 @@ int tnnb_layernorm_bwd(const void* dh, const void* x, const void* mean, const vo
                             nullptr, nullptr);
 }
 
+// The same with dbias (fp32 [C]) += column sums of ddelta: the bias gradient of the dense layer in front of the norm.
+int tnnb_layernorm_bwd_db(const void* dh, const void* x, const void* mean, const void* rstd, const void* gamma,
+                          const void* dres, void* dx, void* ddelta, void* dgamma, void* dbeta, void* dbias, long long rows,
+                          int C, float p, unsigned long long seed, const void* seed_off, void* stream) {
+  return layernorm_bwd_impl(dh, x, mean, rstd, gamma, dres, dx, ddelta, dgamma, dbeta, rows, C, p, seed, seed_off, stream,
+                            nullptr, nullptr, dbias);
+}
+
 // Tensor-parallel form: dh is the sum of `dh` and the pulled partials; ddelta is also pushed (arguments as in
 // tnnb_layernorm_fwd_tp).
 int tnnb_layernorm_bwd_tp(const void* dh, const void* x, const void* mean, const void* rstd, const void* gamma,
@@ -428,6 +456,22 @@ int tnnb_layernorm_bwd_tp(const void* dh, const void* x, const void* mean, const
   if (n_push && !ddelta) return -5;
   return layernorm_bwd_impl(dh, x, mean, rstd, gamma, dres, dx, ddelta, dgamma, dbeta, rows, C, p, seed, seed_off, stream,
                             &pull, &push);
+}
+
+// Tensor-parallel form with the bias gradient of tnnb_layernorm_bwd_db.
+int tnnb_layernorm_bwd_tp_db(const void* dh, const void* x, const void* mean, const void* rstd, const void* gamma,
+                             const void* dres, void* dx, void* ddelta, void* dgamma, void* dbeta, void* dbias, long long rows,
+                             int C, float p, unsigned long long seed, const void* seed_off, int n_pull, void** pull_src,
+                             const void* arrived, const void* pass, unsigned int units, int n_push, void** push_dst,
+                             void** push_ready, long long push_row0, long long push_rows, int* status, void* stream) {
+  TpPull pull;
+  TpPush push;
+  const int rc = make_tp_blocks(pull, push, n_pull, pull_src, arrived, pass, units, n_push, push_dst, push_ready, push_row0,
+                                push_rows, status);
+  if (rc) return rc;
+  if (n_push && !ddelta) return -5;
+  return layernorm_bwd_impl(dh, x, mean, rstd, gamma, dres, dx, ddelta, dgamma, dbeta, rows, C, p, seed, seed_off, stream,
+                            &pull, &push, dbias);
 }
 
 }  // extern "C"

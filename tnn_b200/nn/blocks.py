@@ -11,7 +11,7 @@ import torch
 
 from ..ops import raw
 from ..ops.gemm import gemm
-from .layers import (LAYER_REGISTRY, T_JSON, T_SIZE, T_STR, Layer, ParamSpec, _flat2d, register)
+from .layers import (LAYER_REGISTRY, T_JSON, T_SIZE, T_STR, Conv2D, Layer, ParamSpec, _flat2d, register)
 
 
 def layer_from_config(cfg: dict) -> Layer:
@@ -161,8 +161,13 @@ class ResidualBlock(_Composite):
             grad = raw.act_bwd(ctx["y"], grad, "relu")  # y > 0 <=> pre-activation > 0
         elif "z" in ctx:
             grad = raw.act_bwd(ctx["z"], grad, self.activation, 1.0 if self.activation == "elu" else 0.01)
-        gm = self.main.backward(grad, ctx["m"])[0]
         gs = self.shortcut.backward(grad, ctx["s"])[0] if self.shortcut is not None else grad
+        first = self.main.layers[0] if self.main.layers else None
+        if isinstance(first, Conv2D) and not ctx["m"][0].get("_skip_dgrad"):
+            # the main path's first convolution adds the shortcut's gradient while it writes its own input gradient
+            ctx["m"][0]["_add_to_dx"] = gs
+            return [self.main.backward(grad, ctx["m"])[0]]
+        gm = self.main.backward(grad, ctx["m"])[0]
         return [raw.binary(gm, gs, "add")]
 
 

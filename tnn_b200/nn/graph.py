@@ -905,15 +905,21 @@ class _GPTChain(_Segment):
         if self.final is not None:
             ln = self.final.layer
             xf, mean, rstd = ctx["final"]
+            # the layer-norm backward kernels also sum the columns of the ddelta they emit: that is the bias gradient
+            # of the dense layer in front of the norm (fc2 of the last block here)
             dres, dpend = raw.layernorm_bwd(g, xf, mean, rstd, ln.params[0], None, True, p_pend, seed_pend,
-                                            ln.grads[0], ln.grads[1])
+                                            ln.grads[0], ln.grads[1], dbias=self.blocks[-1][7].layer.grads[1])
+            bias_done = True
         else:
             dres, dpend = g, raw.dropout(g, p_pend, seed_pend)
-        for es, s in zip(reversed(self.blocks), reversed(ctx["saved"])):
+            bias_done = False
+        for bi in reversed(range(len(self.blocks))):
+            es, s = self.blocks[bi], ctx["saved"][bi]
             ln1, attn, _, _, ln2, fc1, _, fc2, _, _ = (e.layer for e in es)
             # fc2
             gemm(dpend, s["g"], a_t=True, b_t=True, out=fc2.grads[0], atomic=True)
-            raw.colsum_accum(dpend, fc2.grads[1])
+            if not bias_done:
+                raw.colsum_accum(dpend, fc2.grads[1])
             dz = gemm(dpend, fc2.params[0], b_t=True, dgelu_of=s["z"])
             # fc1
             gemm(dz, s["h2"], a_t=True, b_t=True, out=fc1.grads[0], atomic=True)
@@ -921,11 +927,10 @@ class _GPTChain(_Segment):
             dh2 = gemm(dz, fc1.params[0], b_t=True)
             # LN2 + residual + dropout
             dx1, dy1 = raw.layernorm_bwd(dh2, s["x1"], s["mean2"], s["rstd2"], ln2.params[0], dres, True, s["p1"],
-                                         s["seed1"], ln2.grads[0], ln2.grads[1])
+                                         s["seed1"], ln2.grads[0], ln2.grads[1], dbias=attn.grads[3])
             # attention
             wqkv, bqkv, wo, bo = attn.params
             gemm(dy1, s["a"], a_t=True, b_t=True, out=attn.grads[2], atomic=True)
-            raw.colsum_accum(dy1, attn.grads[3])
             da = gemm(dy1, wo, b_t=True)
             qkv = s["qkv"] if s["qkv"] is not None else gemm(s["h1"], wqkv, bias=bqkv)
             dqkv = raw.attn_bwd(qkv, s["a"], da, s["lse"], B, S, attn.num_heads, attn.head_dim, attn.is_causal,
@@ -934,8 +939,10 @@ class _GPTChain(_Segment):
             raw.colsum_accum(dqkv, attn.grads[1])
             dh1 = gemm(dqkv, wqkv, b_t=True)
             # LN1 (+ the previous block's trailing residual add + dropout)
+            bias_done = bool(s["had_pending"]) and bi > 0
             dres, dpend = raw.layernorm_bwd(dh1, s["x"], s["mean1"], s["rstd1"], ln1.params[0], dx1, s["had_pending"],
-                                            s["p_in"], s["seed_in"], ln1.grads[0], ln1.grads[1])
+                                            s["p_in"], s["seed_in"], ln1.grads[0], ln1.grads[1],
+                                            dbias=self.blocks[bi - 1][7].layer.grads[1] if bias_done else None)
             if self.g.grad_hook is not None:  # this block and everything after it in the flat buffer is final
                 self.g.grad_hook(self._block_floor(self.g, es))
         if id(self.in_node) not in no_grad_nodes:

@@ -590,7 +590,9 @@ class Conv2D(Layer):
                 raw.colsum_accum(_flat2d(grad), self.grads[1])
         if ctx.get("_skip_dgrad"):
             return [None]
-        dx = raw.conv2d_dgrad(grad, self.params[0], x.shape, (self.stride_h, self.stride_w), (self.pad_h, self.pad_w))
+        # "_add_to_dx": a residual block hands over the gradient of its shortcut branch; it is added here
+        dx = raw.conv2d_dgrad(grad, self.params[0], x.shape, (self.stride_h, self.stride_w), (self.pad_h, self.pad_w),
+                              add=ctx.pop("_add_to_dx", None))
         return [dx]
 
 

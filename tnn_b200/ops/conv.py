@@ -105,13 +105,22 @@ def conv2d_fwd(x, w, bias, stride, pad, relu=False, keep=None):
     return y.view(n, oh, ow, o)
 
 
-def conv2d_dgrad(dy, w, x_shape, stride, pad):
+def conv2d_dgrad(dy, w, x_shape, stride, pad, add=None):
+    """Gradient with respect to the input. ``add`` (same shape as the result): another contribution to the same
+    gradient - the shortcut branch of a residual block - which the 1 x 1 case adds in the GEMM epilogue instead of
+    leaving it to a separate three-tensor pass."""
     stride, pad = tuple(stride), tuple(pad)
     n, h, wd, c, o, kh, kw, oh, ow = _geom(x_shape, w.shape, stride, pad)
     dy2 = dy.reshape(-1, o)
     K = kh * kw * c
     if _is_pointwise(kh, kw, stride, pad) and c % 8 == 0:
-        return gemm(dy2, w.reshape(o, K), b_t=True).view(n, h, wd, c)
+        res = add.reshape(-1, c) if add is not None and add.is_contiguous() else None
+        dx = gemm(dy2, w.reshape(o, K), b_t=True, residual=res).view(n, h, wd, c)
+        if add is not None and res is None:
+            dx = raw_binary_add(dx, add)
+        return dx
+    if add is not None:
+        return raw_binary_add(conv2d_dgrad(dy, w, x_shape, stride, pad), add)
     if stride == (1, 1) and _implicit_ok(o, c) and dy.is_contiguous() and kh - 1 - pad[0] >= 0 and kw - 1 - pad[1] >= 0:
         # dx = conv(dy, filter rotated by 180 degrees with its channel axes swapped), padding k - 1 - p
         w_rot = w.flip(1, 2).permute(3, 1, 2, 0).contiguous()
@@ -125,6 +134,11 @@ def conv2d_dgrad(dy, w, x_shape, stride, pad):
     _lib.check_rc(rc, "col2im")
     LAUNCHES["count"] += 1
     return dx
+
+
+def raw_binary_add(a, b):
+    from . import raw
+    return raw.binary(a.contiguous(), b.contiguous(), "add")
 
 
 def conv2d_wgrad(x, dy, dw, stride, pad, cols=None):

@@ -123,3 +123,42 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     _lib.check_rc(rc, "tnnb_gemm_bf16")
     LAUNCHES["count"] += 1
     return out
+
+
+_BATCHED_DECLARED = False
+
+
+def gemm_batched(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
+                 out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[i] = op(a[i]) @ op(b[i]).T`` for every ``i`` of the leading dimension, in one launch of the batched
+    tcgen05 kernel. a: ``[G, M, K]`` (``[G, K, M]`` with ``a_t``), b: ``[G, N, K]`` (``[G, K, N]`` with ``b_t``); the
+    last dimension must be contiguous, the row pitch a multiple of 8 elements. ``out``: ``[G, M, N]`` bf16 or fp32,
+    possibly a view with a padded row pitch."""
+    G = a.shape[0]
+    M = a.shape[2] if a_t else a.shape[1]
+    K = a.shape[1] if a_t else a.shape[2]
+    N = b.shape[2] if b_t else b.shape[1]
+    assert b.shape[0] == G and (b.shape[1] if b_t else b.shape[2]) == K
+    if out is None:
+        out = torch.empty(G, M, N, dtype=out_dtype or a.dtype, device=a.device)
+    if not a.is_cuda:
+        A = (a.transpose(1, 2) if a_t else a).float()
+        B = (b.transpose(1, 2) if b_t else b).float()
+        out.copy_((A @ B.transpose(1, 2)).to(out.dtype))
+        return out
+    global _BATCHED_DECLARED
+    lib = _lib.load()
+    if not _BATCHED_DECLARED:
+        import ctypes
+        vp, ll, i = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
+        lib.tnnb_gemm_bf16_batched.argtypes = [vp, vp, vp, i, i, i, i, i, ll, ll, ll, i, ll, ll, ll, i, vp, vp]
+        lib.tnnb_gemm_bf16_batched.restype = i
+        _BATCHED_DECLARED = True
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.stride(2) == 1 and b.stride(2) == 1 and out.stride(2) == 1
+    assert out.dtype in (torch.bfloat16, torch.float32)
+    rc = lib.tnnb_gemm_bf16_batched(_lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, int(a_t), int(b_t), a.stride(1), b.stride(1),
+                                    out.stride(1), G, a.stride(0), b.stride(0), out.stride(0),
+                                    64 if out.dtype == torch.float32 else 0, _lib.ptr(_lib.status_word(a.device)), _lib.stream())
+    _lib.check_rc(rc, "tnnb_gemm_bf16_batched")
+    LAUNCHES["count"] += 1
+    return out

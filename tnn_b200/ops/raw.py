@@ -256,6 +256,10 @@ def _declare_tp(lib):
     lib.tnnb_layernorm_fwd_tp.restype = i
     lib.tnnb_layernorm_bwd_tp.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ll, i, f, ull, vp] + tail
     lib.tnnb_layernorm_bwd_tp.restype = i
+    lib.tnnb_layernorm_bwd_tp_db.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ll, i, f, ull, vp] + tail
+    lib.tnnb_layernorm_bwd_tp_db.restype = i
+    lib.tnnb_layernorm_bwd_db.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ll, i, f, ull, vp, vp]
+    lib.tnnb_layernorm_bwd_db.restype = i
     _TP_DECLARED = True
 
 
@@ -308,11 +312,13 @@ def layernorm_fwd(x: torch.Tensor, delta: Optional[torch.Tensor], gamma: Optiona
 def layernorm_bwd(dh: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: torch.Tensor,
                   gamma: Optional[torch.Tensor], dres: Optional[torch.Tensor], want_ddelta: bool, p: float,
                   seed: int, dgamma: Optional[torch.Tensor], dbeta: Optional[torch.Tensor],
-                  ddelta_out: Optional[torch.Tensor] = None, tp_pull=None, tp_push=None
+                  ddelta_out: Optional[torch.Tensor] = None, tp_pull=None, tp_push=None,
+                  dbias: Optional[torch.Tensor] = None
                   ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """Returns (dx, ddelta); accumulates into fp32 dgamma/dbeta. ``ddelta_out`` receives ddelta in place.
     ``tp_pull`` / ``tp_push`` as in :func:`layernorm_fwd`: the pulled partial sums are added to ``dh``, ``ddelta`` is
-    what gets pushed."""
+    what gets pushed. ``dbias`` (fp32 [C]) += column sums of ddelta: the bias gradient of the dense layer whose output
+    was added to the residual stream in front of this norm, computed in the same pass."""
     rows, C = x.shape
     if x.is_cuda and x.dtype == torch.bfloat16:
         dh = dh.contiguous()
@@ -321,11 +327,24 @@ def layernorm_bwd(dh: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: t
         if dres is not None:
             dres = dres.contiguous()
         lib = _lib.load()
+        if dbias is not None and not want_ddelta:
+            raise ValueError("dbias is the column sum of ddelta: want_ddelta must be set")
         if tp_pull is not None or tp_push is not None:
             _declare_tp(lib)
-            rc = lib.tnnb_layernorm_bwd_tp(_lib.ptr(dh), _lib.ptr(x), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma),
+            if dbias is not None:
+                rc = lib.tnnb_layernorm_bwd_tp_db(_lib.ptr(dh), _lib.ptr(x), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma),
+                                                  _lib.ptr(dres), _lib.ptr(dx), _lib.ptr(dd), _lib.ptr(dgamma), _lib.ptr(dbeta),
+                                                  _lib.ptr(dbias), rows, C, p, seed & _M64, _seed_off_ptr(),
+                                                  *_tp_tail(tp_pull, tp_push, x.device))
+            else:
+                rc = lib.tnnb_layernorm_bwd_tp(_lib.ptr(dh), _lib.ptr(x), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma),
+                                               _lib.ptr(dres), _lib.ptr(dx), _lib.ptr(dd), _lib.ptr(dgamma), _lib.ptr(dbeta),
+                                               rows, C, p, seed & _M64, _seed_off_ptr(), *_tp_tail(tp_pull, tp_push, x.device))
+        elif dbias is not None:
+            _declare_tp(lib)
+            rc = lib.tnnb_layernorm_bwd_db(_lib.ptr(dh), _lib.ptr(x), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma),
                                            _lib.ptr(dres), _lib.ptr(dx), _lib.ptr(dd), _lib.ptr(dgamma), _lib.ptr(dbeta),
-                                           rows, C, p, seed & _M64, _seed_off_ptr(), *_tp_tail(tp_pull, tp_push, x.device))
+                                           _lib.ptr(dbias), rows, C, p, seed & _M64, _seed_off_ptr(), _lib.stream())
         else:
             rc = lib.tnnb_layernorm_bwd(_lib.ptr(dh), _lib.ptr(x), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma),
                                         _lib.ptr(dres), _lib.ptr(dx), _lib.ptr(dd), _lib.ptr(dgamma),
@@ -352,6 +371,8 @@ def layernorm_bwd(dh: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: t
         if p > 0:
             dd = torch.where(dropout_mask(dd.shape, p, _eff_seed(seed),dd.device), dd / (1 - p), torch.zeros_like(dd))
         dd = dd.to(x.dtype)
+        if dbias is not None:
+            dbias.add_(dd.float().sum(0).to(dbias.dtype))
     return dx, dd
 
 
@@ -407,60 +428,90 @@ def softmax_ce(logits: torch.Tensor, labels: torch.Tensor, vocab: int, grad_scal
 
 # ------------------------------------------------------------------------- attention
 # Head sizes other than 64 on a GPU: the fused flash kernels are specialised for D = 64 (every zoo model); other sizes
-# (the reference's attention benchmark uses E 768 / 8 heads = 96, benchmarks/attention_benchmark.cpp:11-40) run head by
-# head on the tcgen05 GEMM - scores, probabilities and the five backward products - with the softmax as element-wise
-# tensor ops. Memory is one S x S tile at a time; D must be a multiple of 8 (16-byte rows for the TMA descriptors).
-def _head_views(qkv, b, h, S, D, E):
-    rows = qkv[b * S:(b + 1) * S]
-    return rows[:, h * D:(h + 1) * D], rows[:, E + h * D:E + (h + 1) * D], rows[:, 2 * E + h * D:2 * E + (h + 1) * D]
+# (the reference's attention benchmark uses E 768 / 8 heads = 96, benchmarks/attention_benchmark.cpp:11-40) run as
+# batched tcgen05 GEMMs over all heads of a group at once - scores, probabilities and the backward products - with the
+# row softmax between them as a kernel of its own (csrc/kernels/elementwise.cu). The scores are materialised in fp32,
+# so memory is O(S^2) per head; heads are processed in groups whose score buffers stay below about 1 GiB.
+# D must be a multiple of 8 (16-byte rows for the TMA descriptors); S is free (rows are padded to a multiple of 8).
+_ATTN_DECLARED = False
 
 
-def _scores(q, k, S, causal, scale):
-    from .gemm import gemm
-    s = gemm(q, k, out_dtype=torch.float32).mul_(scale)
-    if causal:
-        s.masked_fill_(torch.triu(torch.ones(S, S, dtype=torch.bool, device=s.device), 1), float("-inf"))
-    return s
+def _attn_lib():
+    global _ATTN_DECLARED
+    lib = _lib.load()
+    if not _ATTN_DECLARED:
+        import ctypes
+        vp, ll, i, f = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float
+        lib.tnnb_attn_softmax_fwd.argtypes = [vp, vp, vp, ll, i, i, ll, f, i, vp]
+        lib.tnnb_attn_softmax_fwd.restype = i
+        lib.tnnb_attn_softmax_bwd.argtypes = [vp, vp, vp, vp, vp, vp, ll, i, i, ll, f, i, vp]
+        lib.tnnb_attn_softmax_bwd.restype = i
+        _ATTN_DECLARED = True
+    return lib
+
+
+def _heads(x2d: torch.Tensor, B: int, S: int, H: int, D: int, part: int, parts: int) -> torch.Tensor:
+    """``[B*S, parts*H*D]`` -> contiguous ``[B*H, S, D]`` of part ``part`` (q, k or v of a packed projection)."""
+    return x2d.view(B, S, parts, H, D)[:, :, part].permute(0, 2, 1, 3).reshape(B * H, S, D).contiguous()
+
+
+def _group(BH: int, S: int) -> int:
+    per_head = max(1, S * ((S + 7) // 8 * 8) * 4)
+    return max(1, min(BH, (1 << 30) // per_head))
 
 
 def _attn_fwd_generic(qkv, B, S, H, D, causal, scale):
-    from .gemm import gemm
+    from .gemm import gemm_batched
     if D % 8:
         raise ValueError(f"attention on a GPU needs a head size that is a multiple of 8 (got {D})")
-    E = H * D
-    out = torch.empty(B * S, E, dtype=qkv.dtype, device=qkv.device)
-    lse = torch.empty(B, H, S, dtype=torch.float32, device=qkv.device)
-    for b in range(B):
-        for h in range(H):
-            q, k, v = _head_views(qkv, b, h, S, D, E)
-            s = _scores(q, k, S, causal, scale)
-            l = torch.logsumexp(s, -1)
-            p = torch.exp(s - l[:, None]).to(qkv.dtype)
-            gemm(p, v, b_t=True, out=out[b * S:(b + 1) * S, h * D:(h + 1) * D])
-            lse[b, h] = l * 1.4426950408889634
-    return out, lse
+    lib = _attn_lib()
+    E, BH, Sp = H * D, B * H, (S + 7) // 8 * 8
+    q, k, v = (_heads(qkv, B, S, H, D, i, 3) for i in range(3))
+    o = torch.empty(BH, S, D, dtype=qkv.dtype, device=qkv.device)
+    lse = torch.empty(BH, S, dtype=torch.float32, device=qkv.device)
+    G = _group(BH, S)
+    sc = torch.empty(G, S, Sp, dtype=torch.float32, device=qkv.device)
+    pr = torch.zeros(G, S, Sp, dtype=qkv.dtype, device=qkv.device)
+    for g0 in range(0, BH, G):
+        n = min(G, BH - g0)
+        gemm_batched(q[g0:g0 + n], k[g0:g0 + n], out=sc[:n, :, :S])                         # scores
+        rc = lib.tnnb_attn_softmax_fwd(_lib.ptr(sc), _lib.ptr(pr), _lib.ptr(lse[g0:g0 + n]), n * S, S, S, Sp, scale, int(causal),
+                                       _lib.stream())
+        _lib.check_rc(rc, "attn_softmax_fwd")
+        _count()
+        gemm_batched(pr[:n, :, :S], v[g0:g0 + n], b_t=True, out=o[g0:g0 + n])                # P V
+    out = o.view(B, H, S, D).permute(0, 2, 1, 3).reshape(B * S, E).contiguous()
+    return out, lse.view(B, H, S)
 
 
 def _attn_bwd_generic(qkv, out, dout, lse, B, S, H, D, causal, scale):
-    from .gemm import gemm
-    E = H * D
-    dqkv = torch.empty_like(qkv)
-    for b in range(B):
-        for h in range(H):
-            q, k, v = _head_views(qkv, b, h, S, D, E)
-            dq, dk, dv = _head_views(dqkv, b, h, S, D, E)
-            do = dout[b * S:(b + 1) * S, h * D:(h + 1) * D]
-            o = out[b * S:(b + 1) * S, h * D:(h + 1) * D]
-            s = _scores(q, k, S, causal, scale)
-            p = torch.exp2(s * 1.4426950408889634 - lse[b, h][:, None])
-            pb = p.to(qkv.dtype)
-            gemm(pb, do, a_t=True, b_t=True, out=dv)                      # dV = P^T dO
-            dp = gemm(do, v, out_dtype=torch.float32)                    # dP = dO V^T
-            delta = (do.float() * o.float()).sum(-1, keepdim=True)
-            ds = (p * (dp - delta) * scale).to(qkv.dtype)
-            gemm(ds, k, b_t=True, out=dq)                                # dQ = dS K
-            gemm(ds, q, a_t=True, b_t=True, out=dk)                      # dK = dS^T Q
-    return dqkv
+    from .gemm import gemm_batched
+    lib = _attn_lib()
+    E, BH, Sp = H * D, B * H, (S + 7) // 8 * 8
+    q, k, v = (_heads(qkv, B, S, H, D, i, 3) for i in range(3))
+    do, o = _heads(dout, B, S, H, D, 0, 1), _heads(out, B, S, H, D, 0, 1)
+    delta = (do.float() * o.float()).sum(-1)                                                 # [BH, S]
+    lse2 = lse.reshape(BH, S).contiguous()
+    dq, dk, dv = (torch.empty(BH, S, D, dtype=qkv.dtype, device=qkv.device) for _ in range(3))
+    G = _group(BH, S)
+    sc = torch.empty(G, S, Sp, dtype=torch.float32, device=qkv.device)
+    dp = torch.empty(G, S, Sp, dtype=torch.float32, device=qkv.device)
+    pr = torch.zeros(G, S, Sp, dtype=qkv.dtype, device=qkv.device)
+    ds = torch.zeros(G, S, Sp, dtype=qkv.dtype, device=qkv.device)
+    for g0 in range(0, BH, G):
+        n = min(G, BH - g0)
+        sl = slice(g0, g0 + n)
+        gemm_batched(q[sl], k[sl], out=sc[:n, :, :S])                                        # scores again
+        gemm_batched(do[sl], v[sl], out=dp[:n, :, :S])                                       # dP = dO V^T
+        rc = lib.tnnb_attn_softmax_bwd(_lib.ptr(sc), _lib.ptr(dp), _lib.ptr(lse2[sl]), _lib.ptr(delta[sl]), _lib.ptr(pr),
+                                       _lib.ptr(ds), n * S, S, S, Sp, scale, int(causal), _lib.stream())
+        _lib.check_rc(rc, "attn_softmax_bwd")
+        _count()
+        gemm_batched(pr[:n, :, :S], do[sl], a_t=True, b_t=True, out=dv[sl])                  # dV = P^T dO
+        gemm_batched(ds[:n, :, :S], k[sl], b_t=True, out=dq[sl])                             # dQ = dS K
+        gemm_batched(ds[:n, :, :S], q[sl], a_t=True, b_t=True, out=dk[sl])                   # dK = dS^T Q
+    pack = torch.stack([t.view(B, H, S, D).permute(0, 2, 1, 3).reshape(B * S, E) for t in (dq, dk, dv)], 1)
+    return pack.reshape(B * S, 3 * E).contiguous()
 
 
 def attn_fwd(qkv: torch.Tensor, B: int, S: int, H: int, D: int, causal: bool, scale: float
@@ -581,13 +632,17 @@ def conv2d_fwd(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], s
     return y.permute(0, 2, 3, 1).contiguous().to(x.dtype)
 
 
-def conv2d_dgrad(dy: torch.Tensor, w: torch.Tensor, x_shape, stride, pad) -> torch.Tensor:
+def conv2d_dgrad(dy: torch.Tensor, w: torch.Tensor, x_shape, stride, pad, add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Input gradient of a convolution; ``add`` is summed into it (fused into the GEMM epilogue for 1 x 1 filters)."""
     if dy.is_cuda and dy.dtype == torch.bfloat16:
         from . import conv
-        return conv.conv2d_dgrad(dy, w, x_shape, stride, pad)
+        return conv.conv2d_dgrad(dy, w, x_shape, stride, pad, add)
     n, h, wd, c = x_shape
     dx = torch.nn.grad.conv2d_input((n, c, h, wd), w.permute(0, 3, 1, 2).float(), _to_nchw(dy).float(), stride, pad)
-    return dx.permute(0, 2, 3, 1).contiguous().to(dy.dtype)
+    dx = dx.permute(0, 2, 3, 1)
+    if add is not None:
+        dx = dx + add.float()
+    return dx.contiguous().to(dy.dtype)
 
 
 def conv2d_wgrad(x: torch.Tensor, dy: torch.Tensor, dw: torch.Tensor, stride, pad, cols: Optional[torch.Tensor] = None) -> None:

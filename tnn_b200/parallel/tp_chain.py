@@ -133,11 +133,14 @@ class _TPGPTChain(_Segment):
             xf, mean, rstd = ctx["final"]
             dres, dpend = raw.layernorm_bwd(g, xf, mean, rstd, ln.params[0], None, True, p_pend, seed_pend, ln.grads[0],
                                             ln.grads[1], ddelta_out=last["gb2"].mine() if g.is_cuda else None,
-                                            tp_push=last["gb2"].push_args() if g.is_cuda else None)
+                                            tp_push=last["gb2"].push_args() if g.is_cuda else None,
+                                            dbias=self.blocks[-1][7].layer.grads[1])
+            bias_done = True   # the norm's backward kernel summed the columns of the ddelta it emitted
             if g.is_cuda:
                 last["gb2"].after_produce()
         else:
             dres, dpend = g, raw.dropout(g, p_pend, seed_pend)
+            bias_done = False
         for bi in reversed(range(len(self.blocks))):
             es, s, st = self.blocks[bi], ctx["saved"][bi], sites[bi]
             ln1, attn, _, _, ln2, fc1, _, fc2, _, _ = (e.layer for e in es)
@@ -146,7 +149,8 @@ class _TPGPTChain(_Segment):
             tgt = st["gb2"].mine()
             if dpend.data_ptr() != tgt.data_ptr():  # not written in place (and delivered) by a layer-norm backward
                 st["gb2"].push(dpend)
-            raw.colsum_accum(tgt, fc2.grads[1])
+            if not bias_done:
+                raw.colsum_accum(tgt, fc2.grads[1])
             dz = st["gb2"].gemm(fc2.params[0], b_t=True, dgelu_of=s["z"])          # [M, 4E/tp]
             gemm(st["gb2"].buf, s["g"], a_t=True, b_t=True, out=fc2.grads[0], atomic=True)
             # ---- fc1 (column parallel) ----
@@ -156,14 +160,14 @@ class _TPGPTChain(_Segment):
             # ---- LN2 + residual + dropout ----
             dx1, dy1 = raw.layernorm_bwd(dh2, s["x1"], s["mean2"], s["rstd2"], ln2.params[0], dres, True, s["p1"], s["seed1"],
                                          ln2.grads[0], ln2.grads[1], ddelta_out=st["gb1"].mine() if dh2.is_cuda else None,
-                                         tp_pull=st["s_fc1"].pull_args(), tp_push=st["gb1"].push_args() if dh2.is_cuda else None)
+                                         tp_pull=st["s_fc1"].pull_args(), tp_push=st["gb1"].push_args() if dh2.is_cuda else None,
+                                         dbias=attn.grads[3])
             tgt = st["gb1"].mine()
             if dy1.data_ptr() != tgt.data_ptr():
                 st["gb1"].push(dy1)
             else:
                 st["gb1"].after_produce()
             # ---- attention output projection (row parallel) ----
-            raw.colsum_accum(tgt, attn.grads[3])
             da = st["gb1"].gemm(wo, b_t=True)                                      # [M, E/tp]
             gemm(st["gb1"].buf, s["a"], a_t=True, b_t=True, out=attn.grads[2], atomic=True)
             # recompute_qkv: the gathered layer-norm output is still complete in the site's buffer, a plain GEMM redoes it
@@ -175,10 +179,12 @@ class _TPGPTChain(_Segment):
             dh1 = st["s_qkv"].gemm(dqkv, wqkv, b_t=True)                           # [Ms, E]
             # ---- LN1 (+ the previous block's trailing residual add + dropout) ----
             prev = sites[bi - 1]["gb2"] if (bi > 0 and dh1.is_cuda and s["had_pending"]) else None
+            bias_done = bool(s["had_pending"]) and bi > 0
             dres, dpend = raw.layernorm_bwd(dh1, s["x"], s["mean1"], s["rstd1"], ln1.params[0], dx1, s["had_pending"],
                                             s["p_in"], s["seed_in"], ln1.grads[0], ln1.grads[1],
                                             ddelta_out=prev.mine() if prev is not None else None,
-                                            tp_pull=st["s_qkv"].pull_args(), tp_push=prev.push_args() if prev is not None else None)
+                                            tp_pull=st["s_qkv"].pull_args(), tp_push=prev.push_args() if prev is not None else None,
+                                            dbias=self.blocks[bi - 1][7].layer.grads[1] if bias_done else None)
             if prev is not None:
                 prev.after_produce()
         cc.join()
