@@ -93,6 +93,15 @@ def push_only():
     site.push(x); cc.join()
 parts = {"push_mode": 0.0 if cc.push_mode == "ce" else 1.0, "ln_fwd_us": t_ln, "ln_fwd_then_push_us": timeit(ln_push),
          "push_only_us": timeit(push_only)}
+# the same rows sent by the bulk-copy unit (one thread per block, shared-memory staging), checked against NCCL once
+if cc.push_mode in ("ln", "split"):
+    site.buf.zero_(); torch.cuda.synchronize(); dist.barrier()
+    site.push(x, bulk_ctas=0); torch.cuda.synchronize(); dist.barrier()
+    ref = torch.empty(M, E, dtype=x.dtype, device=dev); dist.all_gather_into_tensor(ref, x)
+    parts["push_bulk_matches_nccl"] = float(torch.equal(site.buf, ref))
+    _lib.check_status()
+    for ctas in (148, 296, 592):
+        parts[f"push_bulk_{ctas}ctas_us"] = timeit(lambda: (site.push(x, bulk_ctas=ctas), cc.join()))
 for K in (E // tp, 4 * E // tp):
     ctr2 = cc.new_pass_counter(); s2 = ScatterSite(cc, M, E, ctr2); a = bf(M, K); w = bf(E, K)
     parts[f"gemm_rs_push_K{K}_us"] = timeit(lambda: s2.gemm(a, w))

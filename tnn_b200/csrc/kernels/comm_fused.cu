@@ -62,6 +62,57 @@ tp_push_kernel(const bf16* __restrict__ src, bf16* __restrict__ local_dst, long 
   if (push.n) tp_push_signal(push, rows, wpb);
 }
 
+// The same push done by the bulk-copy unit instead of SM stores: one thread per block streams 8-row pieces
+// local memory -> shared memory -> every peer's buffer (cp.async.bulk both ways, no multicast), PB_STAGES pieces
+// in flight per block, and publishes its pieces after its last store has completed. rows % 8 == 0.
+static constexpr int PB_STAGES = 4;
+__global__ void __launch_bounds__(32)
+tp_push_bulk_kernel(const bf16* __restrict__ src, bf16* __restrict__ local_dst, long long rows, int C,
+                    const __grid_constant__ TpPush push, int* __restrict__ status) {
+  extern __shared__ __align__(128) uint8_t pb_smem[];
+  __shared__ __align__(8) uint64_t full[PB_STAGES];
+  if (threadIdx.x != 0) return;
+  const uint32_t piece = (uint32_t)C * 16u;  // 8 rows of bf16
+  const long long pieces = rows >> 3;
+  const long long mine = pieces > blockIdx.x ? (pieces - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  for (int s = 0; s < PB_STAGES; ++s) mbar_init(&full[s], 1);
+  mbar_fence_init();
+  auto load = [&](long long k) {
+    const int s = (int)(k % PB_STAGES);
+    const long long pc = blockIdx.x + k * gridDim.x;
+    mbar_expect_tx(&full[s], piece);
+    bulk_load_g2s(pb_smem + (size_t)s * piece, src + pc * 8 * C, piece, &full[s]);
+  };
+  long long issued = 0, done = 0;
+  for (; issued < mine && issued < PB_STAGES; ++issued) load(issued);
+  for (long long k = 0; k < mine; ++k) {
+    const int s = (int)(k % PB_STAGES);
+    if (!mbar_wait(&full[s], (uint32_t)((k / PB_STAGES) & 1))) {
+      if (status) atomicOr(status, ST_TIMEOUT_PEER);
+      break;
+    }
+    const long long pc = blockIdx.x + k * gridDim.x;
+    for (int t = 0; t < push.n; ++t) bulk_store_s2g(push.dst[t] + pc * 8 * C, pb_smem + (size_t)s * piece, piece);
+    if (local_dst) bulk_store_s2g(local_dst + pc * 8 * C, pb_smem + (size_t)s * piece, piece);
+    bulk_commit_group();
+    done = k + 1;
+    if (k >= 1 && k - 1 + PB_STAGES < mine) {  // the stage of the piece before this one is free once it was read
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      load(issued++);
+    }
+  }
+  bulk_wait_group0();
+  // loads that were issued but never consumed (only after a timeout): let them land before the block exits
+  for (long long k = done; k < issued; ++k) mbar_wait(&full[k % PB_STAGES], (uint32_t)((k / PB_STAGES) & 1));
+  if (push.n && done) {
+    __threadfence_system();
+    for (long long k = 0; k < done; ++k) {
+      const long long r = (blockIdx.x + k * gridDim.x) * 8;
+      for (int i = 0; i < push.n; ++i) red_add_sys(push.ready[i] + ((push.row0 + r) >> 7), 8u);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 tp_resolve_kernel(const bf16* __restrict__ a, bf16* __restrict__ out, long long rows, int C,
                   const __grid_constant__ TpPull pull) {
@@ -277,6 +328,34 @@ int tnnb_tp_push(const void* src, void* local_dst, long long rows, int C, int n_
   const long long g = (rows + 7) / 8;
   const int grid = (int)(g > 148 * 8 ? 148 * 8 : g);
   tp_push_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)src, (bf16*)local_dst, rows, C, push);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e - 1000;
+}
+
+// The push through the bulk-copy unit (tp_push_bulk_kernel): rows % 8 == 0, C * 16 bytes per piece <= 48 KB.
+int tnnb_tp_push_bulk(const void* src, void* local_dst, long long rows, int C, int n_push, void** push_dst,
+                      void** push_ready, long long push_row0, int ctas, int* status, void* stream) {
+  if (C % 8 || rows <= 0 || (rows % 8) || n_push < 0 || n_push > TP_MAX - 1 || (push_row0 % 8) || push_row0 < 0) return -3;
+  if (((uintptr_t)src & 15) || ((uintptr_t)local_dst & 15) || (size_t)C * 16 > 48 * 1024) return -4;
+  TpPush push{};
+  push.n = n_push;
+  push.row0 = (int)push_row0;
+  push.rows = rows;
+  for (int i = 0; i < n_push; ++i) {
+    if (!push_dst[i] || !push_ready[i] || ((uintptr_t)push_dst[i] & 15)) return -4;
+    push.dst[i] = (bf16*)push_dst[i];
+    push.ready[i] = (uint32_t*)push_ready[i];
+  }
+  const size_t smem = (size_t)PB_STAGES * C * 16;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(tp_push_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 48 * 1024);
+    attr_done = true;
+  }
+  const long long pieces = rows / 8;
+  if (ctas <= 0) ctas = 148 * 2;
+  const int grid = (int)(pieces < ctas ? pieces : ctas);
+  tp_push_bulk_kernel<<<grid, 32, smem, (cudaStream_t)stream>>>((const bf16*)src, (bf16*)local_dst, rows, C, push, status);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
 }

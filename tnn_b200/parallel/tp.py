@@ -96,6 +96,8 @@ def _declare(lib):
     lib.tnnb_gemm_tp.restype = i
     lib.tnnb_tp_push.argtypes = [vp, vp, ll, i, i, vp, vp, ll, vp]
     lib.tnnb_tp_push.restype = i
+    lib.tnnb_tp_push_bulk.argtypes = [vp, vp, ll, i, i, vp, vp, ll, i, vp, vp]
+    lib.tnnb_tp_push_bulk.restype = i
     lib.tnnb_tp_resolve.argtypes = [vp, vp, ll, i, i, vp, vp, vp, u, vp, vp]
     lib.tnnb_tp_resolve.restype = i
     lib.tnnb_peer_copy.argtypes = [vp, vp, ctypes.c_ulonglong, vp]
@@ -214,8 +216,9 @@ class GatherSite:
                           "tnnb_tp_signal")
             LAUNCHES["count"] += 1
 
-    def push(self, src: Optional[torch.Tensor] = None) -> None:
-        """Stand-alone push: copy ``src`` (default: the rows already in :meth:`mine`) to the peers and publish."""
+    def push(self, src: Optional[torch.Tensor] = None, bulk_ctas: Optional[int] = None) -> None:
+        """Stand-alone push: copy ``src`` (default: the rows already in :meth:`mine`) to the peers and publish.
+        ``bulk_ctas``: use the bulk-copy kernel with that many blocks (0 = its default) instead of SM stores."""
         cc = self.cc
         if not cc.fused:
             if src is not None:
@@ -230,6 +233,13 @@ class GatherSite:
         if src is not None and self.ln_rows < self.rows:
             mine[self.ln_rows:].copy_(src[self.ln_rows:])   # these rows are sent by the GEMM
         s = mine if src is None else src.contiguous()
+        if bulk_ctas is not None:
+            rc = cc.lib.tnnb_tp_push_bulk(_lib.ptr(s), _lib.ptr(mine) if src is not None else None, self.ln_rows, self.K,
+                                          self.n_push, self.push_dst, self.push_ready, self.push_row0, int(bulk_ctas),
+                                          _lib.ptr(_lib.status_word(mine.device)), _lib.stream())
+            _lib.check_rc(rc, "tnnb_tp_push_bulk")
+            LAUNCHES["count"] += 1
+            return
         rc = cc.lib.tnnb_tp_push(_lib.ptr(s), _lib.ptr(mine) if src is not None else None, self.ln_rows, self.K, self.n_push,
                                  self.push_dst, self.push_ready, self.push_row0, _lib.stream())
         _lib.check_rc(rc, "tnnb_tp_push")
