@@ -102,6 +102,21 @@ if cc.push_mode in ("ln", "split"):
     _lib.check_status()
     for ctas in (148, 296, 592):
         parts[f"push_bulk_{ctas}ctas_us"] = timeit(lambda: (site.push(x, bulk_ctas=ctas), cc.join()))
+    # the layer-norm kernel sending its rows the same way (a staging row per warp, one bulk copy per row and peer)
+    os.environ["TNNB_TP_LN_BULK"] = "1"
+    site.buf.zero_(); torch.cuda.synchronize(); dist.barrier()
+    ln_push(); torch.cuda.synchronize(); dist.barrier()
+    mine_ref = raw.layernorm_fwd(x, None, gamma, beta, 1e-5)[1]
+    ref = torch.empty(M, E, dtype=x.dtype, device=dev); dist.all_gather_into_tensor(ref, mine_ref.contiguous())
+    parts["ln_bulk_matches_nccl"] = float(torch.equal(site.buf, ref))
+    parts["ln_fwd_then_bulk_push_us"] = timeit(ln_push)
+    ctrb = cc.new_pass_counter(); siteb = GatherSite(cc, M, E, ctrb); wq = bf(3 * E // tp, E)
+    def fused_bulk():
+        ctrb.add_(1); raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=siteb.mine(), tp_push=siteb.push_args()); siteb.after_produce()
+        y = siteb.gemm(wq); cc.join(); return y
+    parts["qkv_handoff_ln_bulk_us"] = timeit(fused_bulk); _lib.check_status()
+    os.environ["TNNB_TP_LN_BULK"] = "0"
+    parts["qkv_handoff_ln_stores_us"] = timeit(fused_bulk); _lib.check_status()
 for K in (E // tp, 4 * E // tp):
     ctr2 = cc.new_pass_counter(); s2 = ScatterSite(cc, M, E, ctr2); a = bf(M, K); w = bf(E, K)
     parts[f"gemm_rs_push_K{K}_us"] = timeit(lambda: s2.gemm(a, w))

@@ -186,3 +186,51 @@ def test_resnet9_step_matches_cpu():
     b = torch.cat([g.reshape(-1).float().cpu() for l in gg.layers() for g in l.grads if g is not None])
     cos = torch.nn.functional.cosine_similarity(a, b, dim=0)
     assert cos > 0.95, float(cos)  # bf16 batch-norm statistics over a batch of 4 are noisy
+
+
+def _bottleneck_graph():
+    from tnn_b200.models.zoo import _start, _finish, bottleneck_block
+    b = _start((1, 16, 16, 64))
+    b = bottleneck_block(b, 32, 128, 1, "b1")   # projection shortcut (channels change)
+    b = bottleneck_block(b, 32, 128, 1, "b2")   # identity shortcut
+    b = bottleneck_block(b, 64, 256, 2, "b3")   # strided projection shortcut
+    return _finish(b)
+
+
+def test_bottleneck_blocks_fused_add_paths():
+    """Graph-level fusions of a bottleneck stack: the block's closing add runs inside the last batch norm's pass
+    (y = relu(bn(x)) + shortcut) and the gradient of the block input is summed in the first convolution's data
+    gradient GEMM. Compared with the same graph run edge by edge on the GPU and with the fp32 CPU path."""
+    torch.manual_seed(5)
+    x = torch.randn(8, 16, 16, 64)
+    dy = torch.randn(8, 8, 8, 256) * 0.1
+    gf = _bottleneck_graph().compile(device="cuda", seed=4)
+    gu = _bottleneck_graph().compile(device="cuda", seed=4, fuse=False)
+    gc = _bottleneck_graph().compile(device="cpu", seed=4)
+    for g in (gf, gu, gc):
+        g.input_requires_grad = True
+    names = [type(s).__name__ for s in gf.segments]
+    assert names.count("_BnAddSegment") == 3 and "_BnAddSegment" not in [type(s).__name__ for s in gu.segments]
+    for lf, lu, lc in zip(gf.layers(), gu.layers(), gc.layers()):
+        for pf, pu, pc in zip(lf.params, lu.params, lc.params):
+            pu.copy_(pf)
+            pc.copy_(pf.float().cpu())
+    of = gf.forward({"input": x.cuda()})["output"]
+    ou = gu.forward({"input": x.cuda()})["output"]
+    oc = gc.forward({"input": x})["output"]
+    _lib.check_status()
+    # same kernels, same rounding points: the fused add sums the same two bf16 tensors
+    assert torch.equal(of, ou)
+    close(of, oc, tol=3e-2, what="bottleneck forward")
+    gin_f = gf.backward({"output": dy.cuda().bfloat16()})["input"]
+    gin_u = gu.backward({"output": dy.cuda().bfloat16()})["input"]
+    gin_c = gc.backward({"output": dy.bfloat16().float()})["input"]
+    _lib.check_status()
+    # the fused gradient sum rounds once (fp32 sum in the GEMM epilogue) where the separate add rounds twice
+    close(gin_f, gin_u, tol=2e-2, what="input gradient, fused vs edge by edge")
+    close(gin_f, gin_c, tol=6e-2, what="input gradient vs fp32")
+    a = torch.cat([g.reshape(-1).float().cpu() for l in gf.layers() for g in l.grads if g is not None])
+    b = torch.cat([g.reshape(-1).float().cpu() for l in gu.layers() for g in l.grads if g is not None])
+    c = torch.cat([g.reshape(-1).float() for l in gc.layers() for g in l.grads if g is not None])
+    assert torch.nn.functional.cosine_similarity(a, b, dim=0) > 0.999
+    assert torch.nn.functional.cosine_similarity(a, c, dim=0) > 0.98

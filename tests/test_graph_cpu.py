@@ -184,3 +184,39 @@ def test_batchnorm_without_affine_still_saves_four_tensors(tmp_path):
     bn2 = [l for l in g2.layers() if l.name == "bn_plain"][0]
     assert len(bn2.params) == 4 and not bn2.affine
     assert torch.allclose(bn2.params[0], bn.params[0]) and torch.allclose(bn2.params[3], bn.params[3])
+
+
+def test_bottleneck_add_fusions_match_edge_by_edge():
+    """The executor's two residual-block fusions (closing add inside the last batch norm's segment, gradient of the
+    block input summed by the first convolution's data-gradient pass) give what the plain edge-by-edge run gives."""
+    from tnn_b200.models.zoo import _start, _finish, bottleneck_block
+
+    def build():
+        b = _start((1, 8, 8, 16))
+        b = bottleneck_block(b, 8, 32, 1, "b1")
+        b = bottleneck_block(b, 8, 32, 1, "b2")
+        b = bottleneck_block(b, 16, 64, 2, "b3")
+        return _finish(b)
+
+    torch.manual_seed(0)
+    gf = build().compile(device="cpu", seed=4)
+    gu = build().compile(device="cpu", seed=4, fuse=False)
+    gf.input_requires_grad = gu.input_requires_grad = True
+    assert [type(s).__name__ for s in gf.segments].count("_BnAddSegment") == 3
+    assert all(type(s).__name__ == "_EdgeSegment" for s in gu.segments)
+    x, dy = torch.randn(4, 8, 8, 16), torch.randn(4, 4, 4, 64)
+    of, ou = gf.forward({"input": x})["output"], gu.forward({"input": x})["output"]
+    assert torch.allclose(of, ou, atol=1e-6)
+    gi, gj = gf.backward({"output": dy})["input"], gu.backward({"output": dy})["input"]
+    assert torch.allclose(gi, gj, rtol=1e-5, atol=1e-5 * float(gj.abs().max()))
+    a = torch.cat([g.reshape(-1) for l in gf.layers() for g in l.grads if g is not None])
+    b = torch.cat([g.reshape(-1) for l in gu.layers() for g in l.grads if g is not None])
+    assert torch.allclose(a, b, rtol=1e-5, atol=1e-5 * float(b.abs().max()))
+    # and against autograd on the same arithmetic: finite difference of sum(out * dy) along a random direction
+    d = torch.randn_like(x)
+    eps = 1e-3
+    fp = (gu.forward({"input": x + eps * d})["output"] * dy).sum()
+    fm = (gu.forward({"input": x - eps * d})["output"] * dy).sum()
+    fd = float((fp - fm) / (2 * eps))
+    an = float((gi * d).sum())
+    assert abs(fd - an) <= 6e-2 * max(abs(fd), abs(an)) + 1e-3, (fd, an)  # ReLU kinks inside the step

@@ -74,14 +74,17 @@ def _ln_ref(x, gamma, beta, eps=1e-5):
     return (x - m) * torch.rsqrt(v + eps) * gamma.float() + beta.float()
 
 
-@pytest.mark.parametrize("mode", ["ln", "ce"])  # "gemm" needs the ranks' kernels to run at the same time: 2-GPU tests
+@pytest.mark.parametrize("mode", ["ln", "lnbulk", "ce"])  # "gemm" needs the ranks' kernels to run at the same time: 2-GPU tests
 @pytest.mark.parametrize("tp,M,K,N,b_t", [(2, 1024, 256, 320, False), (2, 256, 128, 72, False), (2, 1024, 256, 384, True),
                                            (4, 2048, 128, 256, False)])
-def test_layernorm_push_then_gather_gemm(tp, M, K, N, b_t, mode):
-    """``ln``: the layer-norm kernel stores its rows into the peers' buffers itself; ``ce``: they travel by
-    copy-engine transfers on a side stream, which is joined here before any consumer is launched."""
+def test_layernorm_push_then_gather_gemm(tp, M, K, N, b_t, mode, monkeypatch):
+    """``ln``: the layer-norm kernel stores its rows into the peers' buffers itself (``lnbulk``: through shared
+    memory with bulk copies); ``ce``: they travel by copy-engine transfers on a side stream, which is joined here
+    before any consumer is launched."""
     torch.manual_seed(0)
     dev = torch.device("cuda")
+    monkeypatch.setenv("TNNB_TP_LN_BULK", "1" if mode == "lnbulk" else "0")
+    mode = "ln" if mode == "lnbulk" else mode
     ccs = _contexts(tp, dev, mode)
     ctrs = [cc.new_pass_counter() for cc in ccs]
     sites = [GatherSite(cc, M, K, c) for cc, c in zip(ccs, ctrs)]
@@ -106,6 +109,30 @@ def test_layernorm_push_then_gather_gemm(tp, M, K, N, b_t, mode):
             _close(sites[r].buf, h)      # every rank holds the full gathered operand afterwards
             _close(outs[r], ref)
     for r in range(tp):  # counters: two passes of 128 rows for every block a peer owns, nothing for the own blocks
+        cnt = sites[r].ready[:M // 128].view(tp, -1)
+        for o in range(tp):
+            assert int(cnt[o].min()) == int(cnt[o].max()) == (0 if o == r else 256), (r, o, cnt[o])
+
+
+@pytest.mark.parametrize("tp,M,K,ctas", [(2, 1024, 256, 0), (2, 2048, 768, 7), (4, 1024, 128, 0)])
+def test_bulk_push_delivers_rows_and_counts(tp, M, K, ctas):
+    """Stand-alone push through the bulk-copy unit: every rank's buffer ends up complete and every 128-row block a
+    peer owns has been counted once per row."""
+    torch.manual_seed(3)
+    dev = torch.device("cuda")
+    ccs = _contexts(tp, dev, "ln")
+    sites = [GatherSite(cc, M, K, cc.new_pass_counter()) for cc in ccs]
+    rows = M // tp
+    for it in range(2):
+        xs = [_bf(rows, K) for _ in range(tp)]
+        for r in range(tp):
+            sites[r].push(xs[r], bulk_ctas=ctas)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        full = torch.cat(xs)
+        for r in range(tp):
+            assert torch.equal(sites[r].buf, full)
+    for r in range(tp):
         cnt = sites[r].ready[:M // 128].view(tp, -1)
         for o in range(tp):
             assert int(cnt[o].min()) == int(cnt[o].max()) == (0 if o == r else 256), (r, o, cnt[o])

@@ -117,8 +117,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pair = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // the tile index is the slowest grid dimension and runs backwards: every head's heaviest (latest) causal
+  // tiles are handed out first and the lightest fill the tail of the last wave
+  const int pair = gridDim.z - 1 - blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int q0 = pair * 256;
   const int n_kv_all = (p.S + 127) / 128;
   // number of K/V tiles each Q tile needs (causal: up to and including its diagonal tile)
@@ -455,7 +457,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   float* stats = reinterpret_cast<float*>(smem + BwdSmem::STATS);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // slowest grid dimension = K/V tile: tile 0 (attended by every Q tile under a causal mask) goes out first
+  const int kt = blockIdx.z, h = blockIdx.x, b = blockIdx.y;
   const int kv0 = kt * 128;
   const int n_q_all = (p.S + 127) / 128;
   const int qt_begin = p.causal ? kt : 0;
@@ -818,7 +821,8 @@ int tnnb_attn_fwd(const void* qkv, void* out, void* lse, int B, int S, int H, in
     if ((rc = set_smem(attn_fwd_kernel, FwdSmem::TOTAL))) return rc;
     once = true;
   }
-  dim3 grid((S + 255) / 256, H, B);
+  if (B > 65535 || (S + 255) / 256 > 65535) return -3;  // grid y / z limits
+  dim3 grid(H, B, (S + 255) / 256);
   attn_fwd_kernel<<<grid, 320, FwdSmem::TOTAL, (cudaStream_t)stream>>>(tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
@@ -867,7 +871,8 @@ int tnnb_attn_bwd(const void* qkv, const void* out, const void* dout, const void
   const long long dw = (rows + 3) / 4;  // warps of work for the delta kernel, eight per block
   int g = (int)((dw + 7) / 8 > 148 * 8 ? 148 * 8 : (dw + 7) / 8);
   attn_delta_kernel<<<g, 256, 0, st>>>((const bf16*)out, (const bf16*)dout, (float*)delta, B, S, H);
-  dim3 grid((S + 127) / 128, H, B);
+  if (B > 65535 || (S + 127) / 128 > 65535) return -3;  // grid y / z limits
+  dim3 grid(H, B, (S + 127) / 128);
   attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, st>>>(tq, tk, tv, tdo, tdq, p);
   attn_dq_convert_kernel<<<148 * 4, 256, 0, st>>>((const float*)dq_acc, (bf16*)dqkv, (long long)B * S, (int)E);
   cudaError_t e = cudaGetLastError();

@@ -134,6 +134,8 @@ bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const 
 }
 
 // RES: y = relu?(bn(x) + resid) - the closing add (+ ReLU) of a residual block folded into the block's last batch norm.
+// `relu` bit 0 = ReLU; bit 1 (RES only) = the residual joins AFTER the activation: y = relu?(bn(x)) + resid, the
+// form of blocks whose last batch norm carries the ReLU and whose add is the block's output.
 template <bool RES>
 __global__ void __launch_bounds__(256)
 bn_fwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ resid, bf16* __restrict__ yout, const bf16* __restrict__ gamma,
@@ -193,8 +195,10 @@ bn_fwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ resid, 
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         float v = __bfloat162float(xv[k]) * sc[k] + sh[k];
-        if (RES) v = __bfloat162float(__float2bfloat16(v)) + __bfloat162float(rv[k]);  // the sum of two bf16 tensors, as a separate add would see it
-        o[k] = __float2bfloat16(relu ? fmaxf(v, 0.f) : v);
+        if (RES && !(relu & 2)) v = __bfloat162float(__float2bfloat16(v)) + __bfloat162float(rv[k]);  // the sum of two bf16 tensors, as a separate add would see it
+        if (relu & 1) v = fmaxf(v, 0.f);
+        if (RES && (relu & 2)) v = __bfloat162float(__float2bfloat16(v)) + __bfloat162float(rv[k]);
+        o[k] = __float2bfloat16(v);
       }
       if (ok[u]) *reinterpret_cast<uint4*>(yout + (r + (long long)u * nry) * C + c0) = *reinterpret_cast<uint4*>(o);
     }
@@ -319,7 +323,8 @@ int tnnb_batchnorm_fwd(const void* x, void* y, const void* gamma, const void* be
   return bn_fwd_impl(x, nullptr, y, gamma, beta, ws, mean, rstd, run_mean, run_var, M, C, eps, momentum, relu, training, stream);
 }
 
-// y = relu?(bn(x) + resid): resid has the shape of x (bf16, 16-byte aligned).
+// y = relu?(bn(x) + resid), or with relu bit 1 set y = relu?(bn(x)) + resid: resid has the shape of x (bf16,
+// 16-byte aligned).
 int tnnb_batchnorm_fwd_res(const void* x, const void* resid, void* y, const void* gamma, const void* beta, void* ws, void* mean,
                            void* rstd, void* run_mean, void* run_var, long long M, int C, float eps, float momentum, int relu,
                            int training, void* stream) {

@@ -526,15 +526,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 //   full[s]   lives in the even CTA; both CTAs' TMA loads count their bytes on it (no multicast of data)
 //   empty[s]  one per CTA, signalled by a multicast tcgen05.commit
 //   tfull[a]  one per CTA (multicast commit); tempty[a] in the even CTA, 8 local + 8 remote warp arrivals
-template <int BN>
+template <int BN, int COMM = 0>
 struct Gemm2Cfg {
   static constexpr int A_BYTES = 128 * 64 * 2;
   static constexpr int B_BYTES = (BN / 2) * 64 * 2;  // this CTA's half of the BN-row B tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 384) ? 4 : (BN == 256) ? 6 : 8;
+  // mode 1 (COMM == 1) gives one operand stage to the two 16 KB stages of its copy thread (the 384-wide tile has
+  // the room to spare)
+  static constexpr int COPY_BYTES = (COMM == 1) ? 2 * 16384 : 0;
+  static constexpr int STAGES = (BN == 384) ? 4 : (BN == 256) ? 6 - (COMM == 1 ? 1 : 0) : 8 - (COMM == 1 ? 2 : 0);
   static constexpr int ACCS = (BN == 384) ? 1 : 2;  // 384 columns leave no room for a second accumulator
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 8 * 4096;  // + per-warp epilogue staging
+  static constexpr int COPY_OFF = STAGES * STAGE_BYTES + 256 + 8 * 4096;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 8 * 4096 + COPY_BYTES;  // + per-warp epilogue staging
 };
+static_assert(Gemm2Cfg<256, 1>::SMEM_BYTES <= 227 * 1024 && Gemm2Cfg<384, 1>::SMEM_BYTES <= 227 * 1024 &&
+              Gemm2Cfg<128, 1>::SMEM_BYTES <= 227 * 1024, "mode-1 shared memory");
 
 // Tile order of the tensor-parallel variants: the 256-row blocks are grouped by the rank that owns their rows;
 // mode 1 runs the group of this rank first (its operand rows are already here), mode 2 runs it last (the partial
@@ -589,62 +595,65 @@ __device__ __forceinline__ void tp_signal_remote_tiles(const GemmParams& p, cons
   __syncwarp();
 }
 
-#ifndef TP_COPY_WARPS
-#define TP_COPY_WARPS 6
-#endif
-// Copy warps of mode 1 (the last TP_COPY_WARPS warps of every CTA): send this rank's rows of A to the peers. A piece
-// is a few whole rows inside one 128-row block (about 8 KB: one round of loads); pieces are dealt to the copy warps
-// of the grid in row order and each is published as soon as it is out, so the row blocks complete in the order in
-// which the peers' GEMMs ask for them.
-__device__ __forceinline__ void tp_push_rows(const GemmParams& p, const TpExt& x, int gw, int nw, int lane) {
-  constexpr int UNROLL = 16;            // 16-byte loads in flight per lane: 8 KB per warp and round
-  const int chunks_per_row = p.K >> 3;  // 16-byte chunks (K % 8 == 0 is checked on the host)
-  const int piece_rows = max(1, min(128, (UNROLL * 512) / (p.K * 2)));  // whole rows, about one round each
-  const int ppb = (128 + piece_rows - 1) / piece_rows;
-  const int total = (x.rows_per_rank / 128 - x.push_first_block) * ppb;
-  const int my0 = x.rank * x.rows_per_rank;
-  for (int piece = gw; piece < total; piece += nw) {
-    const int blk = x.push_first_block + piece / ppb, part = piece % ppb;
-    const int r0 = my0 + blk * 128 + part * piece_rows;
-    const int nrows = min(piece_rows, 128 - part * piece_rows);
-    const __nv_bfloat16* src = x.push_src + (long long)r0 * x.push_ld;
-    const int n16 = nrows * chunks_per_row;
-    for (int e0 = 0; e0 < n16; e0 += 32 * UNROLL) {
-      uint4 v[UNROLL];
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {  // independent loads in flight before the first store
-        const int e = e0 + u * 32 + lane;
-        if (e < n16) {
-          const int rr = e / chunks_per_row, cc = e - rr * chunks_per_row;
-          v[u] = *reinterpret_cast<const uint4*>(src + (long long)rr * x.push_ld + cc * 8);
-        }
-      }
-      for (int i = 0; i < x.push_n; ++i) {
-        __nv_bfloat16* dst = x.push_dst[i] + (long long)r0 * x.push_ld;
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-          const int e = e0 + u * 32 + lane;
-          if (e < n16) {
-            const int rr = e / chunks_per_row, cc = e - rr * chunks_per_row;
-            *reinterpret_cast<uint4*>(dst + (long long)rr * x.push_ld + cc * 8) = v[u];
-          }
-        }
-      }
+// Copy warp of mode 1 (one extra warp per CTA, one working thread): send this rank's rows of A to the peers with the
+// bulk-copy unit while the tensor core works on the tiles of the rows that are already here. A piece is up to eight
+// whole rows inside one 128-row block (at most TP_COPY_STAGE bytes); it is loaded from this rank's buffer into a
+// shared-memory stage and stored from there into every peer's buffer (cp.async.bulk both ways, no multicast).
+// Pieces are dealt to the CTAs of the grid in row order and each is published as soon as its stores have
+// completed, so the row blocks fill up in the order in which the peers' GEMMs ask for them.
+#define TP_COPY_WARPS 1
+static constexpr int TP_COPY_STAGES = 2;
+static constexpr int TP_COPY_STAGE = 16384;
+__device__ __forceinline__ void tp_push_rows_bulk(const GemmParams& p, const TpExt& x, uint8_t* stage, uint64_t* bars,
+                                                  int cta, int nctas) {
+  const uint32_t row_bytes = (uint32_t)p.K * 2u;  // K % 8 == 0 and K * 2 <= TP_COPY_STAGE are checked on the host
+  int piece_rows = 8;
+  while (piece_rows > 1 && piece_rows * row_bytes > (uint32_t)TP_COPY_STAGE) piece_rows >>= 1;
+  if (x.push_ld != p.K) piece_rows = 1;  // padded rows: only one row is contiguous
+  const uint32_t bytes = piece_rows * row_bytes;
+  const int total = (x.rows_per_rank / 128 - x.push_first_block) * (128 / piece_rows);
+  const long long my0 = (long long)x.rank * x.rows_per_rank + (long long)x.push_first_block * 128;
+  const int mine = total > cta ? (total - cta + nctas - 1) / nctas : 0;
+  auto row_of = [&](int k) { return my0 + (long long)(cta + k * nctas) * piece_rows; };
+  auto load = [&](int k) {
+    const int s = k % TP_COPY_STAGES;
+    mbar_expect_tx(&bars[s], bytes);
+    bulk_load_g2s(stage + s * TP_COPY_STAGE, x.push_src + row_of(k) * x.push_ld, bytes, &bars[s]);
+  };
+  auto publish = [&](int k) {  // the stores of piece k have completed
+    __threadfence_system();
+    const long long r0 = row_of(k);
+    for (int i = 0; i < x.push_n; ++i) red_add_sys(x.push_ready[i] + (r0 >> 7), (uint32_t)piece_rows);
+  };
+  int issued = 0, done = 0;
+  for (; issued < mine && issued < TP_COPY_STAGES; ++issued) load(issued);
+  for (int k = 0; k < mine; ++k) {
+    const int s = k % TP_COPY_STAGES;
+    if (!mbar_wait(&bars[s], (uint32_t)((k / TP_COPY_STAGES) & 1))) {
+      if (p.status) atomicOr(p.status, ST_TIMEOUT_PRODUCER);
+      break;
     }
-    __syncwarp();
-    if (lane == 0) {
-      __threadfence_system();
-      for (int i = 0; i < x.push_n; ++i) red_add_sys(x.push_ready[i] + (r0 >> 7), (uint32_t)nrows);
+    const long long r0 = row_of(k);
+    for (int i = 0; i < x.push_n; ++i) bulk_store_s2g(x.push_dst[i] + r0 * x.push_ld, stage + s * TP_COPY_STAGE, bytes);
+    bulk_commit_group();
+    done = k + 1;
+    if (k >= 1) {
+      asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");  // piece k - 1 has arrived: its stage is free as well
+      publish(k - 1);
+      if (issued < mine) load(issued++);
     }
-    __syncwarp();
   }
+  bulk_wait_group0();
+  if (done) publish(done - 1);
+  // loads issued but not consumed (only after a time-out): let them land before the block's shared memory goes away
+  for (int k = done; k < issued; ++k) mbar_wait(&bars[k % TP_COPY_STAGES], (uint32_t)((k / TP_COPY_STAGES) & 1));
 }
 
 template <int BN, int A_MN, int B_MN, int COMM>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(COMM == 1 ? 320 + 32 * TP_COPY_WARPS : 320, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                               const GemmParams p, const __grid_constant__ TpExt tpx) {
-  using Cfg = Gemm2Cfg<BN>;
+  using Cfg = Gemm2Cfg<BN, COMM>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int HALF = BN / 2;  // B rows (output columns) staged by each CTA
   extern __shared__ uint8_t smem_raw[];
@@ -671,6 +680,8 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
       mbar_init(&tfull[a], 1);
       mbar_init(&tempty[a], 16);
     }
+    if (COMM == 1)
+      for (int s = 0; s < TP_COPY_STAGES; ++s) mbar_init(&full[24 + s], 1);  // copy thread's stages (byte 192 of the barrier block)
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -796,7 +807,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
     }
   } else if (COMM == 1 && warp >= 10) {
     if (tpx.push_n > 0)
-      tp_push_rows(p, tpx, (int)blockIdx.x * TP_COPY_WARPS + (warp - 10), (int)gridDim.x * TP_COPY_WARPS, lane);
+      if (lane == 0) tp_push_rows_bulk(p, tpx, smem + Cfg::COPY_OFF, &full[24], (int)blockIdx.x, (int)gridDim.x);
   } else {
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
@@ -955,11 +966,11 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
   auto kern = gemm_bf16_tcgen05_pair_kernel<BN, A_MN, B_MN, COMM>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg<BN>::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg<BN, COMM>::SMEM_BYTES);
     if (e != cudaSuccess) return -static_cast<int>(e) - 1000;
     attr_set = true;
   }
-  kern<<<grid, COMM == 1 ? 320 + 32 * TP_COPY_WARPS : 320, Gemm2Cfg<BN>::SMEM_BYTES, stream>>>(ta, tb, p, tpx);  // cluster of two through __cluster_dims__
+  kern<<<grid, COMM == 1 ? 320 + 32 * TP_COPY_WARPS : 320, Gemm2Cfg<BN, COMM>::SMEM_BYTES, stream>>>(ta, tb, p, tpx);  // cluster of two through __cluster_dims__
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 1000;
 }
@@ -1201,6 +1212,7 @@ extern "C" int tnnb_gemm_tp(int mode, const void* A, const void* B, void* D, int
     if (n_push < 0 || n_push > TP_MAX - 1) return -2;
     if (n_push > 0) {
       if (!push_dst || !push_ready || (K % 8)) return -5;
+      if ((long long)K * 2 > TP_COPY_STAGE) return -3;  // a row must fit one stage of the copy thread
       if (push_first_block < 0 || push_first_block > rows_per_rank / 128) return -3;
       x.push_n = n_push;
       x.push_first_block = push_first_block;

@@ -21,6 +21,8 @@
 //         its row's 128-row block before it reads the inbox.
 //   push  `h` (forward) / `ddelta` (backward) is also stored into every peer's copy of the gather buffer, and the
 //         block adds the rows it delivered to the peers' row-block counters once it has finished.
+#include <cstdlib>
+
 #include "ptx.cuh"
 #include "tp_flags.cuh"
 
@@ -51,10 +53,22 @@ ln_fwd_kernel(const bf16* __restrict__ x_in, const bf16* __restrict__ delta, bf1
   const int chunks = C >> 3;
   const float inv_keep = 1.f / (1.f - p);
   const uint32_t thr = dropout_threshold(p);
+  // bulk push: every warp owns two row-sized staging buffers; lane 0 sends a finished row to each peer with one
+  // bulk copy and reuses a buffer once the copy that last read it is done with shared memory
+  extern __shared__ __align__(128) uint8_t ln_stage[];
+  const bool bulk = TP && push.n && push.bulk;
+  bf16* my_stage = reinterpret_cast<bf16*>(ln_stage) + (size_t)(threadIdx.x >> 5) * 2 * C;
+  int sent = 0;
   for (long long r = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += (long long)gridDim.x * wpb) {
     float v[MAXCH][8];
     float s = 0.f;
     if (TP && pull.n) tp_pull_wait(pull, r, pull_want, lane);
+    const bool send = bulk && r < push.rows;
+    bf16* stage = my_stage + (sent & 1) * C;
+    if (send && sent >= 2) {
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      __syncwarp();
+    }
 #pragma unroll
     for (int i = 0; i < MAXCH; ++i) {
       const int c = lane + i * 32;
@@ -119,12 +133,24 @@ ln_fwd_kernel(const bf16* __restrict__ x_in, const bf16* __restrict__ delta, bf1
           for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16((v[i][k] - mean) * rstd);
         }
         *reinterpret_cast<LBf8*>(h + r * C + c * 8) = o;
-        if (TP && r < push.rows) {
+        if (send) {
+          *reinterpret_cast<LBf8*>(stage + c * 8) = o;
+        } else if (TP && r < push.rows) {
           for (int t = 0; t < push.n; ++t) *reinterpret_cast<LBf8*>(push.dst[t] + r * C + c * 8) = o;
         }
       }
     }
+    if (send) {
+      fence_proxy_async_smem();  // the lanes' stores to the staging row, before the bulk copy reads it
+      __syncwarp();
+      if (lane == 0) {
+        for (int t = 0; t < push.n; ++t) bulk_store_s2g(push.dst[t] + r * C, stage, (uint32_t)C * 2u);
+        bulk_commit_group();
+      }
+      ++sent;
+    }
   }
+  if (bulk && lane == 0) bulk_wait_group0();  // the rows have left before they are published
   if (TP && push.n) tp_push_signal(push, rows, wpb);
 }
 
@@ -313,6 +339,8 @@ static int make_tp_blocks(TpPull& pull, TpPush& push, int n_pull, void** pull_sr
     pull.status = status;
   }
   push.n = n_push;
+  const char* ln_bulk = getenv("TNNB_TP_LN_BULK");  // read per call: a test or benchmark may switch it
+  push.bulk = ln_bulk ? atoi(ln_bulk) : 0;
   if (n_push) {
     if (!push_dst || !push_ready || push_row0 < 0 || (push_row0 % 8) || push_rows < 0 || (push_rows % 8)) return -5;
     push.row0 = (int)push_row0;
@@ -338,8 +366,15 @@ static int layernorm_fwd_impl(const void* x_in, const void* delta, void* x_out, 
   long long g = (rows + wpb - 1) / wpb;
   int grid = (int)(g > 148 * 8 ? 148 * 8 : g);
   cudaStream_t st = (cudaStream_t)stream;
+  TpPush push_local;
+  if (push) {  // the staging rows of the bulk push must fit the default dynamic shared memory
+    push_local = *push;
+    if ((size_t)wpb * 2 * C * sizeof(bf16) > 48 * 1024) push_local.bulk = 0;
+    push = &push_local;
+  }
+  const size_t stage_bytes = (push && push->n && push->bulk) ? (size_t)wpb * 2 * C * sizeof(bf16) : 0;
 #define LN_F(MC, TP_, PL, PS)                                                                                       \
-  ln_fwd_kernel<MC, TP_><<<grid, block, 0, st>>>((const bf16*)x_in, (const bf16*)delta, (bf16*)x_out, (bf16*)h,      \
+  ln_fwd_kernel<MC, TP_><<<grid, block, stage_bytes, st>>>((const bf16*)x_in, (const bf16*)delta, (bf16*)x_out, (bf16*)h,      \
                                                  (const bf16*)gamma, (const bf16*)beta, (float*)mean, (float*)rstd, \
                                                  rows, C, eps, p, seed, (const unsigned long long*)seed_off, PL, PS)
   if (pull) {

@@ -67,6 +67,7 @@ struct TpPush {
   long long rows;           // only rows [0, rows) of the kernel are pushed (a multiple of 8; the consuming GEMM sends the rest)
   __nv_bfloat16* dst[TP_MAX - 1];
   uint32_t* ready[TP_MAX - 1];   // base of the peer's counter array ([M/128])
+  int bulk;                 // 1: rows go out through shared memory with the bulk-copy unit instead of SM stores
 };
 
 // Partial sums the other ranks pushed for rows this rank owns (the reduce-scatter direction): the

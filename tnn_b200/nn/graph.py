@@ -33,8 +33,8 @@ import torch
 from ..ops import raw
 from ..ops.gemm import gemm
 from .blocks import FlashAttentionBlock, layer_from_config
-from .layers import (Add, Dense, Div, Dropout, Embedding, GELU, Layer, LayerNorm, Mul, PositionalEmbedding, Sub,
-                     _flat2d)
+from .layers import (Add, BatchNorm, Conv2D, Dense, Div, Dropout, Embedding, GELU, Layer, LayerNorm, Mul,
+                     PositionalEmbedding, Sub, _flat2d)
 
 ALIGN_BYTES = 256
 
@@ -380,7 +380,8 @@ class Graph:
         while i < n_e:
             seg = None
             if self.fuse:
-                seg = _GPTChain.match(self, i, consumers_of, outs) or _EmbedSegment.match(self, i, consumers_of, outs)
+                seg = (_GPTChain.match(self, i, consumers_of, outs) or _EmbedSegment.match(self, i, consumers_of, outs)
+                       or _BnAddSegment.match(self, i, consumers_of, outs))
             if seg is None:
                 seg = _EdgeSegment(self, i)
             segs.append(seg)
@@ -714,6 +715,7 @@ class _EdgeSegment(_Segment):
     def __init__(self, g: Graph, i: int):
         self.start, self.end = i, i + 1
         self.edge = g.edges[i]
+        self.absorb = bool(g.fuse)
 
     def forward(self, vals, ctx):
         e = self.edge
@@ -727,10 +729,79 @@ class _EdgeSegment(_Segment):
             return
         if all(id(p) in no_grad_nodes for p in e.producers):
             ctx["_skip_dgrad"] = True
+        # Fan-out into a convolution (a residual block's input feeds the main path's first convolution and the
+        # shortcut): when the other branch's gradient is already there, the convolution adds it while it writes its
+        # own input gradient (GEMM epilogue for 1 x 1 filters) instead of a separate three-tensor add afterwards.
+        absorbed = False
+        if self.absorb and type(e.layer) is Conv2D and "_skip_dgrad" not in ctx:
+            prev = gvals.get(id(e.producers[0]))
+            if prev is not None and prev.dtype == g.dtype and tuple(prev.shape) == tuple(ctx["x"].shape):
+                ctx["_add_to_dx"] = gvals.pop(id(e.producers[0]))
+                absorbed = True
         gin = e.layer.backward(g, ctx)
+        if absorbed:
+            gvals[id(e.producers[0])] = gin[0]
+            return
         for p, gi in zip(e.producers, gin):
             if id(p) not in no_grad_nodes:
                 _accum(gvals, p, gi)
+
+
+class _BnAddSegment(_Segment):
+    """batch norm -> add in one pass: ``y = relu?(bn(x)) + other``, where the add consumes the norm's output and the
+    value of another branch (the closing add of a bottleneck block, whose last norm carries the ReLU -
+    src/nn/example_graphs.cpp:176-196). The norm's apply pass reads ``other`` and writes the sum, which replaces a
+    separate kernel that reads two tensors and writes a third. Backward: the add hands its gradient to both
+    operands unchanged and the norm's ReLU mask depends on ``bn(x)`` alone, so the layers' own backward passes run
+    as they are. Off the GPU (fp32 reference path) the two layers run one after the other."""
+
+    def __init__(self, g: Graph, i: int):
+        self.start, self.end = i, i + 2
+        self.bn_edge, self.add_edge = g.edges[i], g.edges[i + 1]
+        self.bn: BatchNorm = self.bn_edge.layer
+        mid = self.bn_edge.consumers[0]
+        self.other = [p for p in self.add_edge.producers if p is not mid][0]
+        self.bn_first = self.add_edge.producers[0] is mid
+
+    @staticmethod
+    def match(g: Graph, i: int, cons, outs):
+        E = g.edges
+        if i + 2 > len(E):
+            return None
+        a, b = E[i], E[i + 1]
+        if not (isinstance(a.layer, BatchNorm) and type(b.layer) is Add and len(b.producers) == 2):
+            return None
+        if a.layer.use_relu and not a.layer.affine:  # the backward could not recompute the mask from x
+            return None
+        mid = a.consumers[0]
+        if sum(p is mid for p in b.producers) != 1 or cons.get(id(mid), []) != [i + 1] or id(mid) in outs:
+            return None
+        return _BnAddSegment(g, i)
+
+    def forward(self, vals, ctx):
+        x = vals[id(self.bn_edge.producers[0])]
+        other = vals[id(self.other)]
+        bctx = ctx["bn"] = {"_step": ctx.get("_step"), "_pid": ctx.get("_pid")}
+        fused = x.is_cuda and x.dtype == torch.bfloat16 and other.shape == x.shape and other.dtype == x.dtype
+        if fused:
+            bctx["_post_add"] = other
+            out = self.bn.forward([x], bctx)
+        else:
+            y = self.bn.forward([x], bctx)
+            out = self.add_edge.layer.forward([y, other] if self.bn_first else [other, y], ctx.setdefault("add", {}))
+        vals[id(self.add_edge.consumers[0])] = out
+
+    def backward(self, gvals, ctx, no_grad_nodes):
+        g = gvals.pop(id(self.add_edge.consumers[0]), None)
+        if g is None:
+            return
+        if id(self.other) not in no_grad_nodes:
+            _accum(gvals, self.other, g)
+        src = self.bn_edge.producers[0]
+        if id(src) not in no_grad_nodes or self.bn.grads[0] is not None:
+            gin = self.bn.backward(g, ctx["bn"])
+            if id(src) not in no_grad_nodes:
+                _accum(gvals, src, gin[0])
 
 
 class _EmbedSegment(_Segment):

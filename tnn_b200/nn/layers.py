@@ -641,12 +641,21 @@ class BatchNorm(Layer):
         # add + ReLU then happens in this layer's normalisation pass (one read of the shortcut instead of a separate
         # three-tensor kernel). The ReLU belongs to the block, whose backward masks the gradient before it gets here.
         res = ctx.pop("_add_relu", None)
+        # "_post_add": the graph executor hands over the other operand of the add that consumes this layer's output
+        # (y = relu?(bn(x)) + other): same pass, and the backward is unchanged because the mask depends on bn(x) only
+        post = ctx.pop("_post_add", None)
         relu = self.use_relu or res is not None
+        if post is not None:
+            res = post
         if self.training:
-            y, mean, rstd = raw.batchnorm_fwd_train(x, g, b, rm, rv, self.epsilon, self.momentum, relu, resid=res)
-            ctx["x"], ctx["y"], ctx["mean"], ctx["rstd"] = x, (y if self.use_relu else None), mean, rstd
+            y, mean, rstd = raw.batchnorm_fwd_train(x, g, b, rm, rv, self.epsilon, self.momentum, relu, resid=res,
+                                                    post_add=post is not None)
+            # the saved output is only read as a ReLU mask, and only where the kernels cannot recompute the mask from
+            # x (no beta, or the CPU path): the executor does not hand over "_post_add" in those cases
+            y_mask = y if (self.use_relu and post is None) else None
+            ctx["x"], ctx["y"], ctx["mean"], ctx["rstd"] = x, y_mask, mean, rstd
             return y
-        return raw.batchnorm_infer(x, g, b, rm, rv, self.epsilon, relu, resid=res)
+        return raw.batchnorm_infer(x, g, b, rm, rv, self.epsilon, relu, resid=res, post_add=post is not None)
 
     def backward(self, grad, ctx):
         g, b, _, _ = self._split()

@@ -40,7 +40,7 @@ def _fwd(x, resid, *rest):
     return _l().tnnb_batchnorm_fwd_res(_lib.ptr(x), _lib.ptr(resid.contiguous()), *rest)
 
 
-def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps, momentum, relu, resid=None):
+def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps, momentum, relu, resid=None, post_add=False):
     C = x.shape[-1]
     M = x.numel() // C
     y = torch.empty_like(x)
@@ -49,18 +49,19 @@ def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps, momentum, relu, 
     ws = torch.empty(2 * C, dtype=torch.float64, device=x.device)
     rc = _fwd(x, resid, _lib.ptr(y), _lib.ptr(gamma), _lib.ptr(beta), _lib.ptr(ws), _lib.ptr(mean),
               _lib.ptr(rstd), _lib.ptr(_f32(run_mean)), _lib.ptr(_f32(run_var)), M, C, eps, momentum,
-              int(relu), 1, _lib.stream())
+              int(relu) | (2 if (post_add and resid is not None) else 0), 1, _lib.stream())
     _lib.check_rc(rc, "batchnorm_fwd")
     LAUNCHES["count"] += 2
     return y, mean, rstd
 
 
-def batchnorm_infer(x, gamma, beta, run_mean, run_var, eps, relu, resid=None):
+def batchnorm_infer(x, gamma, beta, run_mean, run_var, eps, relu, resid=None, post_add=False):
     C = x.shape[-1]
     M = x.numel() // C
     y = torch.empty_like(x)
     rc = _fwd(x, resid, _lib.ptr(y), _lib.ptr(gamma), _lib.ptr(beta), None, None, None,
-              _lib.ptr(_f32(run_mean)), _lib.ptr(_f32(run_var)), M, C, eps, 0.0, int(relu), 0, _lib.stream())
+              _lib.ptr(_f32(run_mean)), _lib.ptr(_f32(run_var)), M, C, eps, 0.0,
+              int(relu) | (2 if (post_add and resid is not None) else 0), 0, _lib.stream())
     _lib.check_rc(rc, "batchnorm_infer")
     LAUNCHES["count"] += 1
     return y

@@ -656,14 +656,16 @@ def conv2d_wgrad(x: torch.Tensor, dy: torch.Tensor, dw: torch.Tensor, stride, pa
 
 
 # ------------------------------------------------------------------------- batchnorm
-def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps: float, momentum: float, relu: bool, resid=None):
+def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps: float, momentum: float, relu: bool, resid=None,
+                        post_add: bool = False):
     """Training-mode batch norm over all dims but the last; updates the running stats in place.
     Returns (y, mean, rstd) with fp32 statistics. With ``resid`` (shape of x) the result is ``relu?(bn(x) + resid)``:
-    the closing add of a residual block done in the same pass."""
+    the closing add of a residual block done in the same pass; with ``post_add`` it is ``relu?(bn(x)) + resid`` (the
+    add comes after the activation)."""
     C = x.shape[-1]
     if x.is_cuda and x.dtype == torch.bfloat16:
         from . import norm
-        return norm.batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps, momentum, relu, resid)
+        return norm.batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps, momentum, relu, resid, post_add)
     x2 = x.reshape(-1, C).float()
     M = x2.shape[0]
     mean = x2.mean(0)
@@ -672,31 +674,35 @@ def batchnorm_fwd_train(x, gamma, beta, run_mean, run_var, eps: float, momentum:
     y = (x2 - mean) * rstd
     if gamma is not None:
         y = y * gamma.float() + beta.float()
-    if resid is not None:
+    if resid is not None and not post_add:
         y = y.to(x.dtype).float() + resid.reshape(-1, C).float()
     if relu:
         y = torch.relu(y)
+    if resid is not None and post_add:
+        y = y.to(x.dtype).float() + resid.reshape(-1, C).float()
     unb = var * (M / max(M - 1, 1))
     run_mean.copy_(((1 - momentum) * run_mean.float() + momentum * mean).to(run_mean.dtype))
     run_var.copy_(((1 - momentum) * run_var.float() + momentum * unb).to(run_var.dtype))
     return y.reshape(x.shape).to(x.dtype), mean, rstd
 
 
-def batchnorm_infer(x, gamma, beta, run_mean, run_var, eps: float, relu: bool, resid=None):
+def batchnorm_infer(x, gamma, beta, run_mean, run_var, eps: float, relu: bool, resid=None, post_add: bool = False):
     C = x.shape[-1]
     if x.is_cuda and x.dtype == torch.bfloat16:
         from . import norm
-        return norm.batchnorm_infer(x, gamma, beta, run_mean, run_var, eps, relu, resid)
+        return norm.batchnorm_infer(x, gamma, beta, run_mean, run_var, eps, relu, resid, post_add)
     scale = torch.rsqrt(run_var.float() + eps)
     shift = -run_mean.float() * scale
     if gamma is not None:
         scale = scale * gamma.float()
         shift = beta.float() - run_mean.float() * scale
     y = x.reshape(-1, C).float() * scale + shift
-    if resid is not None:
+    if resid is not None and not post_add:
         y = y.to(x.dtype).float() + resid.reshape(-1, C).float()
     if relu:
         y = torch.relu(y)
+    if resid is not None and post_add:
+        y = y.to(x.dtype).float() + resid.reshape(-1, C).float()
     return y.reshape(x.shape).to(x.dtype)
 
 

@@ -119,10 +119,11 @@ class CommContext:
         # GPT-2 small shapes, 12.6 MB per hand-off, layer norm + all-gather GEMM for QKV; plain kernels: 8 + 29 us):
         #   "ln"    the producing layer-norm kernel stores the rows into the peers' buffers itself (default): the
         #           kernel takes 33 us instead of 8, the GEMM then finds every row in place: 66 us.
-        #   "gemm"  six extra warps of the consuming GEMM kernel send them while the tensor cores work on the local
-        #           tiles: 66 us as well - SM-issued stores move 12.6 MB in about 30 us whoever issues them, and the
-        #           GEMM's remote tiles cannot finish before the last rows have landed.
-        #   "split" the layer-norm kernel sends the first ``ln_share`` of the rows, the GEMM's copy warps the rest: 69 us.
+        #   "gemm"  one extra warp of the consuming GEMM kernel sends them through the bulk-copy unit (local memory ->
+        #           shared memory -> peer) while the tensor cores work on the local tiles: 68 - 72 us (66 us with six
+        #           warps of plain stores before) - the copy shares the unit with the GEMM's own operand loads, and
+        #           the GEMM's remote tiles cannot finish before the last rows have landed.
+        #   "split" the layer-norm kernel sends the first ``ln_share`` of the rows, the GEMM's copy warp the rest: 69 us.
         #   "ce"    copy-engine transfers on a side stream in two halves, each followed by a one-warp kernel that
         #           updates the counters: the copy itself is the fastest mover (21 us for 12.6 MB, no SM time), but
         #           the four extra graph nodes and the cross-stream edges cost more than it saves: 77 us.
@@ -156,9 +157,9 @@ class GatherSite:
     """A symmetric ``[M, K]`` buffer whose row block ``idx`` is produced locally and whose other row blocks are
     PUSHED into it by the ranks that own them (csrc/kernels/tp_flags.cuh), each push followed by an update of the
     receiver's row-block counters. :meth:`gemm` runs the tiles of the local rows first and polls the counters of
-    the other row blocks only when it reaches them; by default it is also the kernel that sends this rank's rows
-    (two copy warps per CTA, see ``CommContext.push_mode`` for the alternatives). After the call the whole buffer
-    is valid locally (it is kept for the weight-gradient GEMM)."""
+    the other row blocks only when it reaches them. By default the kernel that produces this rank's rows (a layer
+    norm) also sends them; ``CommContext.push_mode`` lists the alternatives. After the call the whole buffer is
+    valid locally (it is kept for the weight-gradient GEMM)."""
 
     def __init__(self, cc: CommContext, M: int, K: int, pass_ctr: Optional[torch.Tensor] = None):
         self.cc, self.M, self.K = cc, M, K
