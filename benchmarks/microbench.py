@@ -28,7 +28,9 @@ _FLUSH = None
 def flush_l2():
     global _FLUSH
     if _FLUSH is None:
-        _FLUSH = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+        # larger than the 126 MB L2, and long enough to write (about 0.2 ms) that the host-side work of the timed
+        # call - argument checks, tensor maps, the launch itself - is over before the GPU gets to the start event
+        _FLUSH = torch.empty(1024 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     _FLUSH.zero_()
 
 
@@ -83,7 +85,30 @@ def cmd_attention(a):
     fl = 4.0 * B * H * S * S * D / 2
     f = timeit(lambda: raw.attn_fwd(qkv, B, S, H, D, True, 0.125), a.iters)
     b = timeit(lambda: raw.attn_bwd(qkv, out, do, lse, B, S, H, D, True, 0.125), a.iters)
-    return {"fwd_ms": f, "fwd_tflops": round(fl / f / 1e9, 1), "bwd_ms": b, "bwd_tflops": round(2.5 * fl / b / 1e9, 1)}
+    res = {"fwd_ms": f, "fwd_tflops": round(fl / f / 1e9, 1), "bwd_ms": b, "bwd_tflops": round(2.5 * fl / b / 1e9, 1)}
+    if a.library:
+        res.update(_sdpa_library(qkv, do, B, S, H, D, a.iters))
+    return res
+
+
+def _sdpa_library(qkv, do, B, S, H, D, iters):
+    """The same attention through torch.nn.functional.scaled_dot_product_attention restricted to the cuDNN backend
+    (the library call of the reference's engine, src/nn/engines/cudnn_engine.cu:1479-1621), else the flash backend."""
+    import torch.nn.functional as F
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+    q, k, v = (t.permute(0, 2, 1, 3) for t in qkv.view(B, S, 3, H, D).unbind(2))  # [B, H, S, D] views, no copies
+    q, k, v = (t.detach().requires_grad_(True) for t in (q, k, v))
+    g = do.view(B, S, H, D).permute(0, 2, 1, 3)
+    for name, be in (("cudnn", SDPBackend.CUDNN_ATTENTION), ("flash", SDPBackend.FLASH_ATTENTION)):
+        try:
+            with sdpa_kernel([be]):
+                o = F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=0.125)
+                f = timeit(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=0.125), iters)
+                b = timeit(lambda: torch.autograd.grad(o, (q, k, v), g, retain_graph=True), iters)
+            return {"library": "torch sdpa / " + name, "lib_fwd_ms": f, "lib_bwd_ms": b}
+        except Exception as e:  # backend not available for this shape / build
+            last = f"{name}: {type(e).__name__}"
+    return {"library": "unavailable (" + last + ")"}
 
 
 def cmd_layernorm(a):
@@ -133,8 +158,52 @@ def cmd_conv2d(a):
     f = timeit(lambda: raw.conv2d_fwd(x, w, None, st, pd), a.iters)
     d = timeit(lambda: raw.conv2d_dgrad(dy, w, x.shape, st, pd), a.iters)
     g = timeit(lambda: raw.conv2d_wgrad(x, dy, dw, st, pd), a.iters)
-    return {"fwd_ms": f, "fwd_tflops": round(fl / f / 1e9, 1), "dgrad_ms": d, "dgrad_tflops": round(fl / d / 1e9, 1),
-            "wgrad_ms": g, "wgrad_tflops": round(fl / g / 1e9, 1)}
+    res = {"fwd_ms": f, "fwd_tflops": round(fl / f / 1e9, 1), "dgrad_ms": d, "dgrad_tflops": round(fl / d / 1e9, 1),
+           "wgrad_ms": g, "wgrad_tflops": round(fl / g / 1e9, 1)}
+    if a.library:
+        try:
+            res.update(_conv_library(x, w, dy, st, pd, a.iters))
+        except Exception as e:  # keep this package's figures if the library path refuses the shape
+            res["library_error"] = f"{type(e).__name__}: {str(e)[:120]}"
+    return res
+
+
+def _conv_library(x, w, dy, st, pd, iters):
+    """The same three passes through cuDNN as torch dispatches them (bf16, channels-last views of the NHWC tensors,
+    autotuned): the library the reference's engine builds its convolution graphs on
+    (src/nn/engines/cudnn_engine.cu:328-578)."""
+    torch.backends.cudnn.benchmark = True
+    xt, wt, gt = x.permute(0, 3, 1, 2), w.permute(0, 3, 1, 2), dy.permute(0, 3, 1, 2)
+    conv = torch.ops.aten.convolution_backward
+    args = (list(st), list(pd), [1, 1], False, [0, 0], 1)
+    f = timeit(lambda: torch.nn.functional.conv2d(xt, wt, None, st, pd), iters)
+    d = timeit(lambda: conv(gt, xt, wt, None, *args, [True, False, False]), iters)
+    g = timeit(lambda: conv(gt, xt, wt, None, *args, [False, True, False]), iters)
+    return {"lib_fwd_ms": f, "lib_dgrad_ms": d, "lib_wgrad_ms": g}
+
+
+# every distinct convolution of ResNet-50 at 224 x 224: (input size, C, O, filter, stride)
+_RESNET50_CONVS = [(224, 3, 64, 7, 2),
+                   (56, 64, 64, 1, 1), (56, 64, 64, 3, 1), (56, 64, 256, 1, 1), (56, 256, 64, 1, 1),
+                   (56, 256, 128, 1, 1), (56, 128, 128, 3, 2), (28, 128, 512, 1, 1), (56, 256, 512, 1, 2), (28, 512, 128, 1, 1),
+                   (28, 128, 128, 3, 1),
+                   (28, 512, 256, 1, 1), (28, 256, 256, 3, 2), (14, 256, 1024, 1, 1), (28, 512, 1024, 1, 2), (14, 1024, 256, 1, 1),
+                   (14, 256, 256, 3, 1),
+                   (14, 1024, 512, 1, 1), (14, 512, 512, 3, 2), (7, 512, 2048, 1, 1), (14, 1024, 2048, 1, 2), (7, 2048, 512, 1, 1),
+                   (7, 512, 512, 3, 1)]
+
+
+def cmd_conv_table(a):
+    """One line per distinct ResNet-50 convolution: this package's kernels beside cuDNN (through torch)."""
+    rows = []
+    for size, cin, cout, k, stride in _RESNET50_CONVS:
+        ns = argparse.Namespace(batch=a.batch, size=size, cin=cin, cout=cout, ksize=k, stride=stride, iters=a.iters, library=True)
+        r = cmd_conv2d(ns)
+        row = {"shape": f"{size}x{size}x{cin}->{cout} k{k} s{stride}", **{key: round(v, 4) for key, v in r.items()}}
+        print(json.dumps(row), flush=True)
+        rows.append(row)
+    tot = {key: round(sum(r.get(key, 0.0) for r in rows), 3) for key in ("fwd_ms", "dgrad_ms", "wgrad_ms", "lib_fwd_ms", "lib_dgrad_ms", "lib_wgrad_ms")}
+    return {"layers": len(rows), **tot}
 
 
 def cmd_batchnorm(a):
@@ -209,14 +278,15 @@ def main():
     p = sub.add_parser("gemm"); p.add_argument("--m", type=int, default=8192); p.add_argument("--n", type=int, default=3072)
     p.add_argument("--k", type=int, default=768); p.add_argument("--bn", type=int, default=0); p.add_argument("--all", action="store_true")
     p = sub.add_parser("attention"); p.add_argument("--batch", type=int, default=8); p.add_argument("--heads", type=int, default=12)
-    p.add_argument("--seq", type=int, default=1024)
+    p.add_argument("--seq", type=int, default=1024); p.add_argument("--library", action="store_true")
     p = sub.add_parser("layernorm"); p.add_argument("--rows", type=int, default=65536); p.add_argument("--cols", type=int, default=768)
     p = sub.add_parser("softmax_ce"); p.add_argument("--rows", type=int, default=8192); p.add_argument("--vocab", type=int, default=50257)
     p = sub.add_parser("colsum"); p.add_argument("--rows", type=int, default=8192); p.add_argument("--cols", type=int, default=3072)
     p = sub.add_parser("adam"); p.add_argument("--n", type=int, default=163_000_000)
     p = sub.add_parser("conv2d"); p.add_argument("--batch", type=int, default=128); p.add_argument("--size", type=int, default=56)
     p.add_argument("--cin", type=int, default=64); p.add_argument("--cout", type=int, default=64); p.add_argument("--ksize", type=int, default=3)
-    p.add_argument("--stride", type=int, default=1)
+    p.add_argument("--stride", type=int, default=1); p.add_argument("--library", action="store_true")
+    p = sub.add_parser("conv_table"); p.add_argument("--batch", type=int, default=256)
     p = sub.add_parser("attention_block"); p.add_argument("--batch", type=int, default=16); p.add_argument("--seq", type=int, default=512)
     p.add_argument("--embed", type=int, default=768); p.add_argument("--heads", type=int, default=8)
     p = sub.add_parser("conv_bn_pool"); p.add_argument("--batch", type=int, default=128); p.add_argument("--size", type=int, default=224)

@@ -30,6 +30,10 @@ def close(got, ref, tol=2e-2, what=""):
                                            # implicit-GEMM routes (channel counts multiple of 64): odd batch and spatial sizes,
                                            # strided 3x3, 7x7 maps, more than one column block
                                            (3, 28, 64, 64, 3, 1, 1), (4, 14, 128, 256, 3, 2, 1), (3, 7, 256, 64, 3, 1, 1),
+                                           # strided layers, odd sizes: the data gradient runs as one launch per parity class
+                                           (3, 15, 64, 128, 3, 2, 1), (2, 13, 128, 64, 1, 2, 0), (2, 18, 64, 64, 5, 3, 2),
+                                           # 64 -> 64 channels, stride 1: the kernels that load one input window per tile
+                                           (2, 20, 64, 64, 3, 1, 0), (2, 17, 64, 64, 2, 1, 0), (5, 56, 64, 64, 3, 1, 1),
                                            (5, 9, 64, 320, 3, 1, 1), (2, 12, 192, 128, 5, 1, 2)])
 def test_conv2d(n, h, c, o, k, s, p):
     torch.manual_seed(0)

@@ -32,7 +32,8 @@ struct ConvParams {
   int TN, TH, TW, lgTH, lgTW;   // pixel box of a tile (TH, TW powers of two)
   int tiles_n, tiles_h, tiles_w;
   int num_m_tiles, num_n_blocks, num_k_blocks;
-  bf16* Y;                      // [N, OH, OW, O]
+  bf16* Y;                      // [N, YH, YW, O]: output position (oh, ow) is pixel (oh * ys + yo, ow * xs + xo)
+  int YH, YW, ys, xs, yo, xo;   // plain convolution: YH = OH, YW = OW, ys = xs = 1, yo = xo = 0
   const bf16* bias;
   int relu;
   int* status;
@@ -58,7 +59,7 @@ __device__ __forceinline__ long long conv_out_row(const ConvParams& p, int ni, i
   const int tn = r >> (p.lgTW + p.lgTH);
   const int n = ni * p.TN + tn, oh = hi * p.TH + th, ow = wi * p.TW + tw;
   if (n >= p.N || oh >= p.OH || ow >= p.OW) return -1;
-  return ((long long)n * p.OH + oh) * p.OW + ow;
+  return ((long long)n * p.YH + (oh * p.ys + p.yo)) * p.YW + (ow * p.xs + p.xo);
 }
 
 template <int BN>
@@ -242,6 +243,199 @@ conv_fwd_implicit_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_c
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ----------------------------------------------------- forward, 64 channels: input tile with halo loaded once
+// For C = 64 the k-blocks of the kernel above are the filter taps, and each of them fetches the same 128 pixels
+// again, shifted by one: nine 16 KB loads per tile, which makes 64-channel 3 x 3 layers L2-bandwidth bound. Here a
+// tile is 16 x 8 output pixels of one image and ONE TMA box brings its input window with the halo,
+// (16 + KH - 1) rows of 16 pixels (the row pitch is 16 so that every 8-pixel row of the tile starts a whole
+// number of 1024-byte swizzle repeats after the one above it). The A operand of tap (kh, kw) is that same
+// shared-memory tile read through a descriptor whose start is moved by kh rows and kw pixels and whose 8-row groups
+// are one pitch (2048 bytes) apart. The 64-row filter matrix of all taps stays in shared memory for the CTA's
+// lifetime. Stride 1, KH <= 3, KW <= 9, C == 64, O == 64.
+struct HaloCfg {
+  static constexpr int PITCH = 16, TH = 16, TW = 8, MAXROWS = TH + 2;
+  static constexpr int HALO_BYTES = MAXROWS * PITCH * 128;  // 36 KB
+  static constexpr int STAGES = 3;
+  static constexpr int MAXTAPS = 9;
+  static constexpr int W_BYTES = MAXTAPS * 64 * 128;         // 72 KB
+  static constexpr int HALO0 = W_BYTES;
+  static constexpr int BARS = HALO0 + STAGES * HALO_BYTES;
+  static constexpr int STAGING = BARS + 256;
+  static constexpr int SMEM_BYTES = STAGING + 4 * 4096 + 1024;
+};
+static_assert(HaloCfg::SMEM_BYTES <= 227 * 1024, "halo kernel shared memory");
+
+__global__ void __launch_bounds__(192, 1)
+conv_fwd_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const ConvParams p) {
+  // tmX: box {64, 16, TH + KH - 1, 1}
+  using Cfg = HaloCfg;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::BARS);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint64_t* wfull = tempty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(wfull + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int taps = p.KH * p.KW;
+  const uint32_t halo_bytes = (uint32_t)(Cfg::TH + p.KH - 1) * Cfg::PITCH * 128u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    mbar_init(wfull, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmX);
+    tma_prefetch_desc(&tmW);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 128);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int tiles = p.num_m_tiles;
+  const int per_img = p.tiles_h * p.tiles_w;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(wfull, (uint32_t)taps * 64u * 128u);
+      for (int t = 0; t < taps; ++t) tma_load_2d(smem + t * 8192, &tmW, wfull, t * 64, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int ni = t / per_img, rem = t - ni * per_img;
+        const int hi = rem / p.tiles_w, wi = rem - hi * p.tiles_w;
+        if (!wait_or_abort(&empty[stage], phase ^ 1, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_PRODUCER);
+          break;
+        }
+        mbar_expect_tx(&full[stage], halo_bytes);
+        tma_load_4d(smem + Cfg::HALO0 + stage * Cfg::HALO_BYTES, &tmX, &full[stage], 0, wi * Cfg::TW - p.PW, hi * Cfg::TH - p.PH, ni);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, 64, 0, 0);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = wait_or_abort(wfull, 0, abort_flag);
+      if (!ok) raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+      const uint32_t w_addr = smem_u32(smem);
+      for (int t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
+        if (!wait_or_abort(&tempty[acc], acc_phase ^ 1, abort_flag) || !wait_or_abort(&full[stage], phase, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * 64;
+        const uint32_t h_addr = smem_u32(smem + Cfg::HALO0 + stage * Cfg::HALO_BYTES);
+        for (int tap = 0; tap < taps; ++tap) {
+          const int kh = tap / p.KW, kw = tap - kh * p.KW;
+          const uint32_t b_addr = w_addr + (uint32_t)tap * 8192u;
+          // The window of tap (kh, kw) starts kh rows and kw pixels into the tile. Its start is no longer a
+          // multiple of 1024 bytes, which is fine: the tensor core applies the 128-byte swizzle to the absolute
+          // shared-memory address of every row, exactly as TMA did when it wrote the tile (the descriptor's base
+          // offset field stays 0 - setting it to the start row gave wrong sums on B200).
+          const uint32_t a_addr = h_addr + (uint32_t)(kh * Cfg::PITCH + kw) * 128u;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_ss(d_tmem, make_smem_desc(a_addr + k * 32, 16, Cfg::PITCH * 128), make_smem_desc(b_addr + k * 32, 16, 1024), idesc,
+                      (tap > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(&empty[stage]);
+        tc_commit(&tfull[acc]);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    const int q = warp & 3;  // warps 2..5: TMEM lane quarter
+    uint8_t* stage_tile = smem + Cfg::STAGING + (warp - 2) * 4096;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+      const int ni = t / per_img, rem = t - ni * per_img;
+      const int hi = rem / p.tiles_w, wi = rem - hi * p.tiles_w;
+      if (!wait_or_abort(&tfull[acc], acc_phase, abort_flag)) {
+        if (lane == 0) raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + acc * 64 + (static_cast<uint32_t>(q * 32) << 16);
+      long long orow[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) orow[i] = conv_out_row(p, ni, hi, wi, q * 32 + i * 4 + (lane >> 3));
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + h * 32, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += __bfloat162float(p.bias[h * 32 + j]);
+        }
+        if (p.relu) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * k + 2 * j], v[8 * k + 2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t*>(&h2);
+          }
+          *reinterpret_cast<uint4*>(stage_tile + vstage_off(lane, h * 4 + k)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);  // the accumulator is in registers / shared memory now
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + (lane >> 3), c16 = lane & 7;
+        if (orow[i] >= 0)
+          *reinterpret_cast<uint4*>(p.Y + orow[i] * p.O + c16 * 8) = *reinterpret_cast<const uint4*>(stage_tile + vstage_off(rr, c16));
+      }
+      __syncwarp();
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 128);
   }
 }
 
@@ -446,6 +640,158 @@ conv_wgrad_implicit_kernel(const __grid_constant__ CUtensorMap tmDY, const __gri
   }
 }
 
+// ------------------------------------------- weight gradient, 64 channels: one input window for all filter taps
+// dW[o, kh, kw, c] = sum over pixels of dy[pixel, o] * x[pixel + (kh, kw) - pad, c]. The general kernel below
+// fetches x once per tap and fills half of every 128 x 128 tile with zeros when C = O = 64. Here a CTA walks over
+// 16 x 8 pixel tiles; per tile ONE box brings the x window with its halo (as in conv_fwd_halo_kernel: row pitch 16,
+// taps addressed by moving the descriptor start) and one box the dy tile, and all taps are accumulated at once:
+// the A operand (MN-major, rows = pixels, 64 channels per row) of one MMA covers TWO taps - its second 64-channel
+// block is the same window one pixel (or one row) further on, which the leading-dimension offset of the
+// descriptor expresses - so nine taps take five 128 x 64 accumulators [(tap, c), o]. They stay in tensor memory
+// for all tiles of the CTA and are added to dW once at the end. Stride 1, KH <= 3, KW <= 3, C == O == 64.
+struct WgradHaloCfg {
+  static constexpr int PITCH = 16, TH = 16, TW = 8;
+  static constexpr int X_BYTES = (TH + 2) * PITCH * 128;  // 36 KB
+  static constexpr int DY_BYTES = TH * TW * 128;          // 16 KB
+  static constexpr int STAGE_BYTES = X_BYTES + DY_BYTES;
+  static constexpr int STAGES = 4;
+  static constexpr int BARS = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = BARS + 256 + 1024;
+};
+static_assert(WgradHaloCfg::SMEM_BYTES <= 227 * 1024, "wgrad halo kernel shared memory");
+
+__global__ void __launch_bounds__(192, 1)
+conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap tmDY, const __grid_constant__ CUtensorMap tmX, const WgradParams p) {
+  using Cfg = WgradHaloCfg;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::BARS);
+  uint64_t* empty = full + STAGES;
+  uint64_t* done = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int taps = p.KH * p.KW;
+  const int groups = (taps + 1) / 2;
+  const uint32_t x_bytes = (uint32_t)(Cfg::TH + p.KH - 1) * Cfg::PITCH * 128u;
+  // tap t -> byte shift of its window inside the halo tile; pairs are taken in this order
+  auto shift = [&](int t) { return (uint32_t)((t / p.KW) * Cfg::PITCH + (t % p.KW)) * 128u; };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmDY);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int tiles = p.pix_blocks;
+  const int per_img = p.tiles_h * p.tiles_w;
+  const bool any = (int)blockIdx.x < tiles;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int ni = t / per_img, rem = t - ni * per_img;
+        const int hi = rem / p.tiles_w, wi = rem - hi * p.tiles_w;
+        if (!wait_or_abort(&empty[stage], phase ^ 1, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_PRODUCER);
+          break;
+        }
+        mbar_expect_tx(&full[stage], x_bytes + Cfg::DY_BYTES);
+        uint8_t* dst = smem + stage * Cfg::STAGE_BYTES;
+        tma_load_4d(dst, &tmX, &full[stage], 0, wi * Cfg::TW - p.PW, hi * Cfg::TH - p.PH, ni);
+        tma_load_4d(dst + Cfg::X_BYTES, &tmDY, &full[stage], 0, wi * Cfg::TW, hi * Cfg::TH, ni);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && any) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, 64, 1, 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true, first = true;
+      for (int t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
+        if (!wait_or_abort(&full[stage], phase, abort_flag)) {
+          raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t x_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+        const uint32_t dy_addr = x_addr + Cfg::X_BYTES;
+        for (int g = 0; g < groups; ++g) {
+          const int t0 = 2 * g, t1 = min(2 * g + 1, taps - 1);
+          const uint32_t a0 = x_addr + shift(t0);
+          const uint32_t lbo = (t1 > t0) ? shift(t1) - shift(t0) : 128u;  // odd tap count: the second half is never read back
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {  // 16 pixels (two tile rows) per instruction
+            const uint64_t ad = make_smem_desc(a0 + k * 2 * Cfg::PITCH * 128, lbo, Cfg::PITCH * 128);
+            const uint64_t bd = make_smem_desc(dy_addr + k * 2048, 8192, 1024);
+            tc_mma_ss(tmem_base + g * 64, ad, bd, idesc, (first && k == 0) ? 0u : 1u);
+          }
+        }
+        first = false;
+        tc_commit(&empty[stage]);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) tc_commit(done);
+    }
+  } else if (any) {
+    // warps 2..5: add the accumulators to dW. Lane = row (tap, c) of the group, register j = output channel o;
+    // for a fixed o the 32 lanes of a warp hit 32 consecutive floats.
+    const int q = warp & 3;
+    if (wait_or_abort(done, 0, abort_flag)) {
+      tc_fence_after();
+      const long long ldw = (long long)taps * 64;
+      for (int g = 0; g < groups; ++g) {
+        const int row = q * 32 + lane;
+        const int tap = 2 * g + (row >> 6), c = row & 63;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + g * 64 + h * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
+          tmem_ld_wait();
+          if (tap < taps) {
+            float* d = p.dW + (long long)tap * 64 + c;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) atomicAdd(d + (long long)(h * 32 + j) * ldw, __uint_as_float(r[j]));
+          }
+        }
+      }
+    } else if (lane == 0) {
+      raise_abort(p.status, abort_flag, ST_TIMEOUT_EPILOGUE);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ------------------------------------------------------------------------------------------ host
 static int ilog2(int v) {
   int l = 0;
@@ -489,18 +835,22 @@ static int set_smem_attr(K kern, int bytes) {
 
 using namespace tnnb;
 
-extern "C" {
-
-// x [N,H,W,C] bf16, w [O,KH,KW,C] bf16, y [N,OH,OW,O] bf16. C % 64 == 0, O % 64 == 0. bias may be null.
-int tnnb_conv2d_fwd_implicit(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int C, int O, int KH,
-                             int KW, int SH, int SW, int PH, int PW, int relu, int* status, void* stream) {
+// x [N,H,W,C] bf16, w [O,KH,KW,C] bf16, C % 64 == 0, O % 64 == 0, bias may be null. OH x OW output positions per
+// image are computed (position (oh, ow) reads input rows oh * SH - PH + kh, columns ow * SW - PW + kw; outside the
+// image reads zero; PH / PW may be negative) and written to pixel (oh * ys + yo, ow * xs + xo) of y [N,YH,YW,O]:
+// with ys / xs > 1 one call fills one parity class of a larger image (data gradient of a strided convolution).
+static int conv_fwd_implicit_impl(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int C, int O,
+                                  int KH, int KW, int SH, int SW, int PH, int PW, int OH, int OW, int YH, int YW, int ys,
+                                  int xs, int yo, int xo, int relu, int* status, void* stream) {
   if (C % 64 || O % 64 || C <= 0 || O <= 0) return -3;
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return -4;
+  if (ys < 1 || xs < 1 || yo < 0 || xo < 0 || OH <= 0 || OW <= 0) return -2;
+  if ((long long)(OH - 1) * ys + yo >= YH || (long long)(OW - 1) * xs + xo >= YW) return -2;  // every write inside y
   ConvParams p{};
   p.N = N; p.O = O;
-  p.OH = (H + 2 * PH - KH) / SH + 1;
-  p.OW = (W + 2 * PW - KW) / SW + 1;
-  if (p.OH <= 0 || p.OW <= 0) return -2;
+  p.OH = OH;
+  p.OW = OW;
+  p.YH = YH; p.YW = YW; p.ys = ys; p.xs = xs; p.yo = yo; p.xo = xo;
   p.KH = KH; p.KW = KW; p.SH = SH; p.SW = SW; p.PH = PH; p.PW = PW;
   p.cblocks = C / 64;
   pick_box(128, N, p.OH, p.OW, p.TN, p.TH, p.TW);
@@ -531,6 +881,88 @@ int tnnb_conv2d_fwd_implicit(const void* x, const void* w, const void* bias, voi
     if (!once) { if ((rc = set_smem_attr(conv_fwd_implicit_kernel<128>, ConvCfg<128>::SMEM_BYTES))) return rc; once = true; }
     conv_fwd_implicit_kernel<128><<<grid, 320, ConvCfg<128>::SMEM_BYTES, st>>>(tx, tw, p);
   }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e - 1000;
+}
+
+extern "C" {
+
+// The plain convolution: y [N,OH,OW,O] with OH = (H + 2 PH - KH) / SH + 1.
+int tnnb_conv2d_fwd_implicit(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int C, int O, int KH,
+                             int KW, int SH, int SW, int PH, int PW, int relu, int* status, void* stream) {
+  const int OH = (H + 2 * PH - KH) / SH + 1, OW = (W + 2 * PW - KW) / SW + 1;
+  return conv_fwd_implicit_impl(x, w, bias, y, N, H, W, C, O, KH, KW, SH, SW, PH, PW, OH, OW, OH, OW, 1, 1, 0, 0, relu, status,
+                                stream);
+}
+
+// 64 -> 64 channels, stride 1, KH <= 3, KW <= 9 (conv_fwd_halo_kernel): y [N,OH,OW,64] with OH = H + 2 PH - KH + 1.
+int tnnb_conv2d_fwd_halo(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int C, int O, int KH, int KW,
+                         int PH, int PW, int relu, int* status, void* stream) {
+  if (C != 64 || O != 64 || KH < 1 || KH > 3 || KW < 1 || KW > 9 || PH < 0 || PW < 0) return -3;
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return -4;
+  ConvParams p{};
+  p.N = N; p.O = O;
+  p.OH = H + 2 * PH - KH + 1;
+  p.OW = W + 2 * PW - KW + 1;
+  if (p.OH <= 0 || p.OW <= 0) return -2;
+  p.YH = p.OH; p.YW = p.OW; p.ys = p.xs = 1; p.yo = p.xo = 0;
+  p.KH = KH; p.KW = KW; p.SH = p.SW = 1; p.PH = PH; p.PW = PW;
+  p.cblocks = 1;
+  p.TN = 1; p.TH = HaloCfg::TH; p.TW = HaloCfg::TW;
+  p.lgTH = ilog2(p.TH); p.lgTW = ilog2(p.TW);
+  p.tiles_n = N; p.tiles_h = (p.OH + p.TH - 1) / p.TH; p.tiles_w = (p.OW + p.TW - 1) / p.TW;
+  p.num_m_tiles = p.tiles_n * p.tiles_h * p.tiles_w;
+  p.num_n_blocks = 1;
+  p.num_k_blocks = KH * KW;
+  p.Y = (bf16*)y; p.bias = (const bf16*)bias; p.relu = relu; p.status = status;
+  CUtensorMap tx, tw;
+  int rc;
+  if ((rc = map_nhwc(&tx, x, N, H, W, C, 64, HaloCfg::PITCH, HaloCfg::TH + KH - 1, 1, 1, 1))) return rc;
+  {
+    uint64_t dims[2] = {(uint64_t)KH * KW * C, (uint64_t)O};
+    uint64_t str[1] = {(uint64_t)KH * KW * C * 2};
+    uint32_t box[2] = {64, 64};
+    if ((rc = encode_tmap_bf16(&tw, w, 2, dims, str, box, nullptr))) return rc;
+  }
+  static bool once = false;
+  if (!once) { if ((rc = set_smem_attr(conv_fwd_halo_kernel, HaloCfg::SMEM_BYTES))) return rc; once = true; }
+  const int grid = min(p.num_m_tiles, sm_count());
+  conv_fwd_halo_kernel<<<grid, 192, HaloCfg::SMEM_BYTES, (cudaStream_t)stream>>>(tx, tw, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e - 1000;
+}
+
+// One parity class of a larger output (see conv_fwd_implicit_impl).
+int tnnb_conv2d_fwd_implicit_strided(const void* x, const void* w, void* y, int N, int H, int W, int C, int O, int KH, int KW,
+                                     int PH, int PW, int OH, int OW, int YH, int YW, int ys, int xs, int yo, int xo, int* status,
+                                     void* stream) {
+  return conv_fwd_implicit_impl(x, w, nullptr, y, N, H, W, C, O, KH, KW, 1, 1, PH, PW, OH, OW, YH, YW, ys, xs, yo, xo, 0, status,
+                                stream);
+}
+
+// C == O == 64, stride 1, KH <= 3, KW <= 3 (conv_wgrad_halo_kernel): dw [64,KH,KW,64] fp32 += the weight gradient.
+int tnnb_conv2d_wgrad_halo(const void* x, const void* dy, void* dw, int N, int H, int W, int C, int O, int KH, int KW, int PH,
+                           int PW, int* status, void* stream) {
+  if (C != 64 || O != 64 || KH < 1 || KH > 3 || KW < 1 || KW > 3 || PH < 0 || PW < 0) return -3;
+  if (((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dw) & 15) return -4;
+  WgradParams p{};
+  p.N = N; p.O = O; p.C = C;
+  p.OH = H + 2 * PH - KH + 1;
+  p.OW = W + 2 * PW - KW + 1;
+  if (p.OH <= 0 || p.OW <= 0) return -2;
+  p.KH = KH; p.KW = KW; p.SH = p.SW = 1; p.PH = PH; p.PW = PW;
+  p.TN = 1; p.TH = WgradHaloCfg::TH; p.TW = WgradHaloCfg::TW;
+  p.tiles_n = N; p.tiles_h = (p.OH + p.TH - 1) / p.TH; p.tiles_w = (p.OW + p.TW - 1) / p.TW;
+  p.pix_blocks = p.tiles_n * p.tiles_h * p.tiles_w;
+  p.dW = (float*)dw; p.status = status;
+  CUtensorMap tdy, tx;
+  int rc;
+  if ((rc = map_nhwc(&tx, x, N, H, W, C, 64, WgradHaloCfg::PITCH, WgradHaloCfg::TH + KH - 1, 1, 1, 1))) return rc;
+  if ((rc = map_nhwc(&tdy, dy, N, p.OH, p.OW, O, 64, WgradHaloCfg::TW, WgradHaloCfg::TH, 1, 1, 1))) return rc;
+  static bool once = false;
+  if (!once) { if ((rc = set_smem_attr(conv_wgrad_halo_kernel, WgradHaloCfg::SMEM_BYTES))) return rc; once = true; }
+  const int grid = min(p.pix_blocks, sm_count());
+  conv_wgrad_halo_kernel<<<grid, 192, WgradHaloCfg::SMEM_BYTES, (cudaStream_t)stream>>>(tdy, tx, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
 }

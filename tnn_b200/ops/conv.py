@@ -2,14 +2,21 @@
 
 * 1x1, stride 1: a plain GEMM over the activations;
 * channel counts that are multiples of 64: the implicit-GEMM kernels of ``csrc/kernels/conv_implicit.cu`` - TMA fetches
-  shifted spatial boxes of the input straight into operand tiles, no patch matrix exists (forward, weight gradient,
-  and the data gradient of stride-1 layers, which is the forward kernel run on ``dy`` with the rotated filter);
-* everything else (the 3-channel stem, data gradients of strided layers): im2col / col2im kernels around the GEMM.
+  shifted spatial boxes of the input straight into operand tiles, no patch matrix exists: forward, weight gradient,
+  the data gradient of stride-1 layers (the forward kernel run on ``dy`` with the rotated filter) and the data
+  gradient of strided layers (one launch of the forward kernel per parity class of input pixels, each a stride-1
+  correlation of ``dy`` with the sub-filter of the taps that reach that class);
+* 64 -> 64 channels, stride 1, filters up to 3 x 3 (ResNet-50's first stage): forward / data gradient and weight
+  gradient kernels that load ONE input window with its halo per 16 x 8 pixel tile and address every filter tap
+  inside it by moving the operand descriptor;
+* everything else (the 3-channel stem, channel counts that are not multiples of 64): im2col / col2im kernels around
+  the GEMM.
 
 Reference semantics: src/nn/engines/cpu_engine.cpp:617-734; the reference itself calls cuDNN conv graphs."""
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -30,6 +37,12 @@ def _lib_conv():
             getattr(lib, name).restype = i
         lib.tnnb_conv2d_fwd_implicit.argtypes = [vp, vp, vp, vp] + [i] * 12 + [vp, vp]
         lib.tnnb_conv2d_fwd_implicit.restype = i
+        lib.tnnb_conv2d_fwd_implicit_strided.argtypes = [vp, vp, vp] + [i] * 17 + [vp, vp]
+        lib.tnnb_conv2d_fwd_implicit_strided.restype = i
+        lib.tnnb_conv2d_fwd_halo.argtypes = [vp, vp, vp, vp] + [i] * 10 + [vp, vp]
+        lib.tnnb_conv2d_fwd_halo.restype = i
+        lib.tnnb_conv2d_wgrad_halo.argtypes = [vp, vp, vp] + [i] * 9 + [vp, vp]
+        lib.tnnb_conv2d_wgrad_halo.restype = i
         lib.tnnb_conv2d_wgrad_implicit.argtypes = [vp, vp, vp] + [i] * 11 + [vp, vp]
         lib.tnnb_conv2d_wgrad_implicit.restype = i
         _DECL = True
@@ -46,6 +59,14 @@ def _fwd_implicit(x, w, bias, stride, pad, relu):
     oh = (h + 2 * pad[0] - kh) // stride[0] + 1
     ow = (wd + 2 * pad[1] - kw) // stride[1] + 1
     y = torch.empty(n, oh, ow, o, dtype=x.dtype, device=x.device)
+    if (c == 64 and o == 64 and tuple(stride) == (1, 1) and kh <= 3 and kw <= 3 and kh * kw > 1 and pad[0] >= 0 and pad[1] >= 0
+            and os.environ.get("TNNB_CONV_HALO", "1") != "0"):
+        # 64-channel layers: the input tile is loaded once with its halo instead of once per filter tap
+        rc = _lib_conv().tnnb_conv2d_fwd_halo(_lib.ptr(x), _lib.ptr(w), _lib.ptr(bias), _lib.ptr(y), n, h, wd, c, o, kh, kw, pad[0],
+                                              pad[1], int(relu), _lib.ptr(_lib.status_word(x.device)), _lib.stream())
+        _lib.check_rc(rc, "conv2d_fwd_halo")
+        LAUNCHES["count"] += 1
+        return y
     rc = _lib_conv().tnnb_conv2d_fwd_implicit(_lib.ptr(x), _lib.ptr(w), _lib.ptr(bias), _lib.ptr(y), n, h, wd, c, o, kh, kw, stride[0],
                                               stride[1], pad[0], pad[1], int(relu), _lib.ptr(_lib.status_word(x.device)), _lib.stream())
     _lib.check_rc(rc, "conv2d_fwd_implicit")
@@ -125,6 +146,8 @@ def conv2d_dgrad(dy, w, x_shape, stride, pad, add=None):
         # dx = conv(dy, filter rotated by 180 degrees with its channel axes swapped), padding k - 1 - p
         w_rot = w.flip(1, 2).permute(3, 1, 2, 0).contiguous()
         return _fwd_implicit(dy, w_rot, None, (1, 1), (kh - 1 - pad[0], kw - 1 - pad[1]), False)
+    if (stride[0] > 1 or stride[1] > 1) and _implicit_ok(o, c) and dy.is_contiguous():
+        return _dgrad_strided_implicit(dy, w, x_shape, stride, pad)
     kld = (K + 7) // 8 * 8
     dcols = torch.empty(dy2.shape[0], kld, dtype=dy.dtype, device=dy.device)
     gemm(dy2, _w2d(w, K), b_t=True, out=dcols[:, :K])
@@ -133,6 +156,48 @@ def conv2d_dgrad(dy, w, x_shape, stride, pad, add=None):
                                  _lib.stream())
     _lib.check_rc(rc, "col2im")
     LAUNCHES["count"] += 1
+    return dx
+
+
+def _parity_classes(size: int, k: int, s: int, p: int):
+    """Input positions ``s * i + a`` (a = 0 .. s-1) of a strided convolution receive gradient only through the filter
+    taps ``kh = r + s * m`` with ``r = (a + p) % s``, from output position ``i + q - m`` (``q = (a + p - r) / s``).
+    Per class: (a, number of positions, taps in the order of ascending output position, padding of the equivalent
+    stride-1 correlation over the output gradient)."""
+    out = []
+    for a in range(s):
+        r = (a + p) % s
+        nt = 0 if r >= k else (k - r + s - 1) // s
+        q = (a + p - r) // s
+        taps = [r + s * (nt - 1 - u) for u in range(nt)]  # = reversed(range(r, k, s))
+        out.append((a, (size - a + s - 1) // s, taps, (nt - 1) - q))
+    return out
+
+
+def _dgrad_strided_implicit(dy, w, x_shape, stride, pad):
+    """Data gradient of a strided convolution without a patch matrix: the input pixels fall into
+    ``stride_h * stride_w`` parity classes, and each class is a stride-1 correlation of ``dy`` with the sub-filter of
+    the taps that reach it - one launch of the implicit-GEMM forward kernel per class, writing every
+    ``stride``-th pixel of ``dx``. Classes no tap reaches (1 x 1 filters) stay zero."""
+    n, h, wd, c = x_shape
+    o, kh, kw, _ = w.shape
+    oh, ow = dy.shape[1], dy.shape[2]
+    ch, cw = _parity_classes(h, kh, stride[0], pad[0]), _parity_classes(wd, kw, stride[1], pad[1])
+    full = all(t for _, _, t, _ in ch) and all(t for _, _, t, _ in cw)
+    dx = (torch.empty if full else torch.zeros)(n, h, wd, c, dtype=dy.dtype, device=dy.device)
+    lib = _lib_conv()
+    for a, hc, khs, phc in ch:
+        for b, wc, kws, pwc in cw:
+            if not khs or not kws or hc <= 0 or wc <= 0:
+                continue
+            # filter of the equivalent correlation: [C, taps_h, taps_w, O]
+            # taps descend by the stride: a strided slice, flipped (no index tensors: this runs inside captured steps)
+            w_sub = w[:, khs[-1]::stride[0], kws[-1]::stride[1]].flip(1, 2).permute(3, 1, 2, 0).contiguous()
+            rc = lib.tnnb_conv2d_fwd_implicit_strided(_lib.ptr(dy), _lib.ptr(w_sub), _lib.ptr(dx), n, oh, ow, o, c, len(khs),
+                                                      len(kws), phc, pwc, hc, wc, h, wd, stride[0], stride[1], a, b,
+                                                      _lib.ptr(_lib.status_word(dy.device)), _lib.stream())
+            _lib.check_rc(rc, "conv2d_fwd_implicit_strided")
+            LAUNCHES["count"] += 1
     return dx
 
 
@@ -150,6 +215,14 @@ def conv2d_wgrad(x, dy, dw, stride, pad, cols=None):
         a = x.reshape(-1, c)
     elif cols is None and _implicit_ok(c, o) and dw.dtype == torch.float32 and dw.is_contiguous() and x.is_contiguous() \
             and dy.is_contiguous():
+        if (c == 64 and o == 64 and stride == (1, 1) and kh <= 3 and kw <= 3 and kh * kw > 1 and pad[0] >= 0 and pad[1] >= 0
+                and os.environ.get("TNNB_CONV_HALO", "1") != "0"):
+            # 64-channel layers: one input window per pixel tile serves every filter tap
+            rc = _lib_conv().tnnb_conv2d_wgrad_halo(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), n, h, wd, c, o, kh, kw, pad[0], pad[1],
+                                                    _lib.ptr(_lib.status_word(x.device)), _lib.stream())
+            _lib.check_rc(rc, "conv2d_wgrad_halo")
+            LAUNCHES["count"] += 1
+            return
         rc = _lib_conv().tnnb_conv2d_wgrad_implicit(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), n, h, wd, c, o, kh, kw, stride[0], stride[1],
                                                     pad[0], pad[1], _lib.ptr(_lib.status_word(x.device)), _lib.stream())
         _lib.check_rc(rc, "conv2d_wgrad_implicit")
