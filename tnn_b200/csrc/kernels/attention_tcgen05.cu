@@ -174,21 +174,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, 0, 1);
       const uint32_t q_addr = smem_u32(smem + FwdSmem::Q);
       const uint32_t p_addr = smem_u32(smem + FwdSmem::P);
+      // This one thread issues 24 MMAs per K/V step. Everything about their descriptors that does not change is
+      // built once: the address field of a descriptor counts 16-byte units, so a k-step or a stage is an add.
+      constexpr uint32_t T16 = TILE_BYTES / 16;
+      const uint64_t q_desc = make_smem_desc(q_addr, 16, 1024);                                       // + x * T16
+      const uint64_t p_desc = make_smem_desc(p_addr, 16, 1024);                                       // + x * 2 * T16
+      const uint64_t k_desc = make_smem_desc(smem_u32(smem + FwdSmem::K0), 16, 1024);                 // + stage * 2 * T16
+      const uint64_t v_desc = make_smem_desc(smem_u32(smem + FwdSmem::K0 + TILE_BYTES), 8192, 1024);  // + stage * 2 * T16
       auto issue_qk = [&](int x, int j) {
-        const uint32_t k_addr = smem_u32(smem + FwdSmem::K0 + (j & 1) * 2 * TILE_BYTES);
+        const uint64_t qd = q_desc + x * T16, kd = k_desc + (j & 1) * 2 * T16;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ss(tmem_base + x * 128, make_smem_desc(q_addr + x * TILE_BYTES + k * 32, 16, 1024),
-                    make_smem_desc(k_addr + k * 32, 16, 1024), idesc_s, k > 0);
+        for (int k = 0; k < 4; ++k) tc_mma_ss(tmem_base + x * 128, qd + k * 2, kd + k * 2, idesc_s, k > 0);
         tc_commit(&s_full[x]);
       };
       auto issue_pv = [&](int x, int j) {
-        const uint32_t v_addr = smem_u32(smem + FwdSmem::K0 + (j & 1) * 2 * TILE_BYTES + TILE_BYTES);
-        const uint32_t pa = p_addr + x * 2 * TILE_BYTES;
+        const uint64_t pd = p_desc + x * 2 * T16, vd = v_desc + (j & 1) * 2 * T16;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          tc_mma_ss(tmem_base + 256 + x * 64, make_smem_desc(pa + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
-                    make_smem_desc(v_addr + k * 2048, 8192, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+          tc_mma_ss(tmem_base + 256 + x * 64, pd + (k >> 2) * T16 + (k & 3) * 2, vd + k * 128, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         tc_commit(&o_full[x]);
       };
       bool ok = wait_or_abort(q_full, 0, abort_flag) && wait_or_abort(&kv_full[0], 0, abort_flag);
@@ -516,17 +519,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_q = make_idesc_bf16(128, 64, 1, 1);
       const uint32_t k_addr = smem_u32(smem + BwdSmem::K), v_addr = smem_u32(smem + BwdSmem::V);
       const uint32_t pt_addr = smem_u32(smem + BwdSmem::PT), dst_addr = smem_u32(smem + BwdSmem::DST);
+      // 32 MMAs per step from this one thread: descriptors are built once and moved by adds (address field in
+      // 16-byte units)
+      constexpr uint32_t T16 = TILE_BYTES / 16;
+      const uint64_t k_km = make_smem_desc(k_addr, 16, 1024), k_mn = make_smem_desc(k_addr, 8192, 1024);
+      const uint64_t v_km = make_smem_desc(v_addr, 16, 1024);
+      const uint64_t pt_km = make_smem_desc(pt_addr, 16, 1024), dst_km = make_smem_desc(dst_addr, 16, 1024);
+      const uint64_t dst_mn = make_smem_desc(dst_addr, TILE_BYTES, 1024);
+      const uint64_t q0_km = make_smem_desc(smem_u32(smem + BwdSmem::Q0), 16, 1024);    // stage s: + s * 2 * T16; dO: + T16
+      const uint64_t q0_mn = make_smem_desc(smem_u32(smem + BwdSmem::Q0), 8192, 1024);
       auto issue_scores = [&](int it) {
-        const uint32_t q_addr = smem_u32(smem + BwdSmem::Q0 + (it % QS) * 2 * TILE_BYTES);
-        const uint32_t do_addr = q_addr + TILE_BYTES;
+        const uint64_t qd = q0_km + (it % QS) * 2 * T16, dod = qd + T16;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ss(tm_ST, make_smem_desc(k_addr + k * 32, 16, 1024), make_smem_desc(q_addr + k * 32, 16, 1024),
-                    idesc_s, k > 0);
+        for (int k = 0; k < 4; ++k) tc_mma_ss(tm_ST, k_km + k * 2, qd + k * 2, idesc_s, k > 0);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ss(tm_DPT, make_smem_desc(v_addr + k * 32, 16, 1024), make_smem_desc(do_addr + k * 32, 16, 1024),
-                    idesc_s, k > 0);
+        for (int k = 0; k < 4; ++k) tc_mma_ss(tm_DPT, v_km + k * 2, dod + k * 2, idesc_s, k > 0);
         tc_commit(s_full);
       };
       bool ok = n_steps > 0 && wait_or_abort(kv_full, 0, abort_flag) && wait_or_abort(&q_full[0], 0, abort_flag);
@@ -549,22 +556,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!ok) break;
         tc_fence_after();
         TRACE(1, it * 8 + 2);
-        const uint32_t q_addr = smem_u32(smem + BwdSmem::Q0 + s * 2 * TILE_BYTES);
-        const uint32_t do_addr = q_addr + TILE_BYTES;
+        const uint64_t q_mn = q0_mn + s * 2 * T16, do_mn = q_mn + T16;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          tc_mma_ss(tm_dV, make_smem_desc(pt_addr + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
-                    make_smem_desc(do_addr + k * 2048, 8192, 1024), idesc_g, (it > 0 || k > 0));
+          tc_mma_ss(tm_dV, pt_km + (k >> 2) * T16 + (k & 3) * 2, do_mn + k * 128, idesc_g, (it > 0 || k > 0));
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          tc_mma_ss(tm_dK, make_smem_desc(dst_addr + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
-                    make_smem_desc(q_addr + k * 2048, 8192, 1024), idesc_g, (it > 0 || k > 0));
+          tc_mma_ss(tm_dK, dst_km + (k >> 2) * T16 + (k & 3) * 2, q_mn + k * 128, idesc_g, (it > 0 || k > 0));
         tc_commit(&q_empty[s]);
         // dQ_i[q, d] = sum_kv dS^T[kv, q] K[kv, d]: both operands MN-major, 16 kv rows per instruction
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          tc_mma_ss(tm_dQ, make_smem_desc(dst_addr + k * 2048, TILE_BYTES, 1024),
-                    make_smem_desc(k_addr + k * 2048, 8192, 1024), idesc_q, k > 0);
+        for (int k = 0; k < 8; ++k) tc_mma_ss(tm_dQ, dst_mn + k * 128, k_mn + k * 128, idesc_q, k > 0);
         tc_commit(acc_done);
         TRACE(1, it * 8 + 3);
       }

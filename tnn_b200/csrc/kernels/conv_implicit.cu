@@ -153,10 +153,10 @@ conv_fwd_implicit_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_c
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
           const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+          // the address field of a descriptor counts 16-byte units: a k-step is an add
+          const uint64_t a_desc0 = make_smem_desc(a_addr, 16, 1024), b_desc0 = make_smem_desc(b_addr, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc_mma_ss(d_tmem, make_smem_desc(a_addr + k * 32, 16, 1024), make_smem_desc(b_addr + k * 32, 16, 1024), idesc,
-                      (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) tc_mma_ss(d_tmem, a_desc0 + k * 2, b_desc0 + k * 2, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           tc_commit(&empty[stage]);
           if (++stage == STAGES) {
             stage = 0;
@@ -254,7 +254,7 @@ conv_fwd_implicit_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_c
 // number of 1024-byte swizzle repeats after the one above it). The A operand of tap (kh, kw) is that same
 // shared-memory tile read through a descriptor whose start is moved by kh rows and kw pixels and whose 8-row groups
 // are one pitch (2048 bytes) apart. The 64-row filter matrix of all taps stays in shared memory for the CTA's
-// lifetime. Stride 1, KH <= 3, KW <= 9, C == 64, O == 64.
+// lifetime. Stride 1, KH <= 3, KW <= 3, C == 64, O == 64.
 struct HaloCfg {
   static constexpr int PITCH = 16, TH = 16, TW = 8, MAXROWS = TH + 2;
   static constexpr int HALO_BYTES = MAXROWS * PITCH * 128;  // 36 KB
@@ -340,7 +340,13 @@ conv_fwd_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       uint32_t phase = 0, acc_phase = 0;
       bool ok = wait_or_abort(wfull, 0, abort_flag);
       if (!ok) raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
-      const uint32_t w_addr = smem_u32(smem);
+      // One thread issues 36 short MMAs (128 x 64 x 16) per tile: what it spends per instruction on building
+      // descriptors bounds the kernel, so everything that does not depend on the tile is worked out here. A
+      // descriptor's low bits are the shared-memory address in 16-byte units, so windows and k-steps are plain adds.
+      const uint64_t b_desc0 = make_smem_desc(smem_u32(smem), 16, 1024);
+      uint32_t tap_off[Cfg::MAXTAPS];  // start of tap (kh, kw) inside the halo tile, in 16-byte units
+#pragma unroll
+      for (int tap = 0; tap < Cfg::MAXTAPS; ++tap) tap_off[tap] = (uint32_t)((tap / p.KW) * Cfg::PITCH + (tap % p.KW)) * 8u;
       for (int t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
         if (!wait_or_abort(&tempty[acc], acc_phase ^ 1, abort_flag) || !wait_or_abort(&full[stage], phase, abort_flag)) {
           raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
@@ -348,19 +354,18 @@ conv_fwd_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * 64;
-        const uint32_t h_addr = smem_u32(smem + Cfg::HALO0 + stage * Cfg::HALO_BYTES);
-        for (int tap = 0; tap < taps; ++tap) {
-          const int kh = tap / p.KW, kw = tap - kh * p.KW;
-          const uint32_t b_addr = w_addr + (uint32_t)tap * 8192u;
-          // The window of tap (kh, kw) starts kh rows and kw pixels into the tile. Its start is no longer a
-          // multiple of 1024 bytes, which is fine: the tensor core applies the 128-byte swizzle to the absolute
-          // shared-memory address of every row, exactly as TMA did when it wrote the tile (the descriptor's base
-          // offset field stays 0 - setting it to the start row gave wrong sums on B200).
-          const uint32_t a_addr = h_addr + (uint32_t)(kh * Cfg::PITCH + kw) * 128u;
+        // The window of tap (kh, kw) starts kh rows and kw pixels into the tile. Its start is no longer a multiple
+        // of 1024 bytes, which is fine: the tensor core applies the 128-byte swizzle to the absolute shared-memory
+        // address of every row, exactly as TMA did when it wrote the tile (the descriptor's base offset field stays
+        // 0 - setting it to the start row gave wrong sums on B200).
+        const uint64_t a_desc0 = make_smem_desc(smem_u32(smem + Cfg::HALO0 + stage * Cfg::HALO_BYTES), 16, Cfg::PITCH * 128);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc_mma_ss(d_tmem, make_smem_desc(a_addr + k * 32, 16, Cfg::PITCH * 128), make_smem_desc(b_addr + k * 32, 16, 1024), idesc,
-                      (tap > 0 || k > 0) ? 1u : 0u);
+        for (int tap = 0; tap < Cfg::MAXTAPS; ++tap) {
+          if (tap < taps) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              tc_mma_ss(d_tmem, a_desc0 + tap_off[tap] + k * 2, b_desc0 + tap * 512 + k * 2, idesc, (tap > 0 || k > 0) ? 1u : 0u);
+          }
         }
         tc_commit(&empty[stage]);
         tc_commit(&tfull[acc]);
@@ -568,10 +573,10 @@ conv_wgrad_implicit_kernel(const __grid_constant__ CUtensorMap tmDY, const __gri
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
           const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+          const uint64_t a_desc0 = make_smem_desc(a_addr, 8192, 1024), b_desc0 = make_smem_desc(b_addr, 8192, 1024);
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // 16 pixels per instruction; both operands MN-major
-            tc_mma_ss(d_tmem, make_smem_desc(a_addr + k * 2048, 8192, 1024), make_smem_desc(b_addr + k * 2048, 8192, 1024), idesc,
-                      (pb > pb0 || k > 0) ? 1u : 0u);
+            tc_mma_ss(d_tmem, a_desc0 + k * 128, b_desc0 + k * 128, idesc, (pb > pb0 || k > 0) ? 1u : 0u);
           tc_commit(&empty[stage]);
           if (++stage == STAGES) {
             stage = 0;
@@ -728,6 +733,16 @@ conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap tmDY, const __grid_co
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true, first = true;
+      // per group of two taps: the A descriptor without the tile's base address (window start of the first tap,
+      // distance to the second tap's window as leading-dimension offset) - 40 MMAs per tile then cost two adds each
+      constexpr int MAXG = 5;
+      uint64_t g_desc[MAXG];
+#pragma unroll
+      for (int g = 0; g < MAXG; ++g) {
+        const int t0 = min(2 * g, taps - 1), t1 = min(2 * g + 1, taps - 1);
+        const uint32_t lbo = (t1 > t0) ? shift(t1) - shift(t0) : 128u;  // odd tap count: the second half is never read back
+        g_desc[g] = make_smem_desc(shift(t0), lbo, Cfg::PITCH * 128);
+      }
       for (int t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
         if (!wait_or_abort(&full[stage], phase, abort_flag)) {
           raise_abort(p.status, abort_flag, ST_TIMEOUT_MMA);
@@ -736,16 +751,15 @@ conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap tmDY, const __grid_co
         }
         tc_fence_after();
         const uint32_t x_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
-        const uint32_t dy_addr = x_addr + Cfg::X_BYTES;
-        for (int g = 0; g < groups; ++g) {
-          const int t0 = 2 * g, t1 = min(2 * g + 1, taps - 1);
-          const uint32_t a0 = x_addr + shift(t0);
-          const uint32_t lbo = (t1 > t0) ? shift(t1) - shift(t0) : 128u;  // odd tap count: the second half is never read back
+        const uint64_t dy_desc0 = make_smem_desc(x_addr + Cfg::X_BYTES, 8192, 1024);
+        const uint32_t x16 = x_addr >> 4;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {  // 16 pixels (two tile rows) per instruction
-            const uint64_t ad = make_smem_desc(a0 + k * 2 * Cfg::PITCH * 128, lbo, Cfg::PITCH * 128);
-            const uint64_t bd = make_smem_desc(dy_addr + k * 2048, 8192, 1024);
-            tc_mma_ss(tmem_base + g * 64, ad, bd, idesc, (first && k == 0) ? 0u : 1u);
+        for (int g = 0; g < MAXG; ++g) {
+          if (g < groups) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)  // 16 pixels (two tile rows) per instruction
+              tc_mma_ss(tmem_base + g * 64, g_desc[g] + x16 + k * (2 * Cfg::PITCH * 128 / 16), dy_desc0 + k * 128, idesc,
+                        (first && k == 0) ? 0u : 1u);
           }
         }
         first = false;
@@ -895,10 +909,10 @@ int tnnb_conv2d_fwd_implicit(const void* x, const void* w, const void* bias, voi
                                 stream);
 }
 
-// 64 -> 64 channels, stride 1, KH <= 3, KW <= 9 (conv_fwd_halo_kernel): y [N,OH,OW,64] with OH = H + 2 PH - KH + 1.
+// 64 -> 64 channels, stride 1, KH <= 3, KW <= 3 (conv_fwd_halo_kernel): y [N,OH,OW,64] with OH = H + 2 PH - KH + 1.
 int tnnb_conv2d_fwd_halo(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int C, int O, int KH, int KW,
                          int PH, int PW, int relu, int* status, void* stream) {
-  if (C != 64 || O != 64 || KH < 1 || KH > 3 || KW < 1 || KW > 9 || PH < 0 || PW < 0) return -3;
+  if (C != 64 || O != 64 || KH < 1 || KH > 3 || KW < 1 || KW > 3 || PH < 0 || PW < 0) return -3;
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return -4;
   ConvParams p{};
   p.N = N; p.O = O;

@@ -459,14 +459,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
           const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+          // one descriptor per operand and k-block; its address field counts 16-byte units, so a k-step is an add
+          const uint64_t ad0 = A_MN ? make_smem_desc(a_addr, 8192, 1024) : make_smem_desc(a_addr, 16, 1024);
+          const uint64_t bd0 = B_MN ? make_smem_desc(b_addr, 8192, 1024) : make_smem_desc(b_addr, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t ad = A_MN ? make_smem_desc(a_addr + k * 2048, 8192, 1024)
-                                     : make_smem_desc(a_addr + k * 32, 16, 1024);
-            const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024)
-                                     : make_smem_desc(b_addr + k * 32, 16, 1024);
-            tc_mma_ss(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < 4; ++k)
+            tc_mma_ss(d_tmem, ad0 + k * (A_MN ? 128 : 2), bd0 + k * (B_MN ? 128 : 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           tc_commit(&empty[stage]);
           if (++stage == STAGES) {
             stage = 0;
@@ -782,16 +780,15 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __g
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
           const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+          const uint64_t ad0 = A_MN ? make_smem_desc(a_addr, 8192, 1024) : make_smem_desc(a_addr, 16, 1024);
+          const uint64_t bd0 = B_MN ? make_smem_desc(b_addr, 8192, 1024) : make_smem_desc(b_addr, 16, 1024);
+          // this CTA's B rows 128..191 (BN == 384 only): two 64-row boxes further when MN-major
+          const uint64_t bt0 = B_MN ? make_smem_desc(b_addr + 2 * 8192, 8192, 1024) : make_smem_desc(b_addr + 128 * 128, 16, 1024);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint64_t ad = A_MN ? make_smem_desc(a_addr + k * 2048, 8192, 1024) : make_smem_desc(a_addr + k * 32, 16, 1024);
-            const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024) : make_smem_desc(b_addr + k * 32, 16, 1024);
-            tc_mma_ss_pair(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-            if (BN == 384) {  // this CTA's B rows 128..191 (two 64-row boxes further when MN-major)
-              const uint64_t bt = B_MN ? make_smem_desc(b_addr + 2 * 8192 + k * 2048, 8192, 1024)
-                                       : make_smem_desc(b_addr + 128 * 128 + k * 32, 16, 1024);
-              tc_mma_ss_pair(d_tmem + 256, ad, bt, idesc_tail, (kb > kb0 || k > 0) ? 1u : 0u);
-            }
+            const uint64_t ad = ad0 + k * (A_MN ? 128 : 2);
+            tc_mma_ss_pair(d_tmem, ad, bd0 + k * (B_MN ? 128 : 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (BN == 384) tc_mma_ss_pair(d_tmem + 256, ad, bt0 + k * (B_MN ? 128 : 2), idesc_tail, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tc_commit_pair(&empty[stage], 3);
           if (++stage == STAGES) {
