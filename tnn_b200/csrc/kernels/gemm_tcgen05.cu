@@ -108,9 +108,19 @@ __device__ __forceinline__ void epilogue_math(const GemmParams& p, const EpiOut&
   const bool full = (col0 + 32 <= p.N);
 
   if (flags & EPI_BIAS) {
+    if (full && ((reinterpret_cast<uintptr_t>(p.bias + col0) & 15) == 0)) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (full || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+      for (int j = 0; j < 32; j += 8) {  // the same address in every lane: a broadcast
+        const uint4 raw = *reinterpret_cast<const uint4*>(p.bias + col0 + j);
+        const __nv_bfloat16* t = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[j + k] += __bfloat162float(t[k]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (full || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+    }
   }
   if (flags & EPI_GELU) {
     if (p.aux_out) {
@@ -287,17 +297,20 @@ __device__ __forceinline__ void epilogue_warp(const GemmParams& p, const EpiOut&
       continue;
     }
     const bool pair_staged = staged_ok && (col0 + 64 <= p.N) && (c + 1 < nchunks);
+    // both chunks of the pair are requested from tensor memory before the single wait: the epilogue is bound by the
+    // latency of its dependent chain (two warps per scheduler), not by issue slots
+    uint32_t rr[2][32];
+    tmem_ld_32x32(t_addr + c * 32, rr[0]);  // warp-collective: never under a per-lane condition
+    if (c + 1 < nchunks) tmem_ld_32x32(t_addr + (c + 1) * 32, rr[1]);
+    tmem_ld_wait();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       if (c + h >= nchunks) break;
-      uint32_t r[32];
-      tmem_ld_32x32(t_addr + (c + h) * 32, r);  // warp-collective: never under a per-lane condition
-      tmem_ld_wait();
       const int cc = col0 + h * 32;
       if (cc >= p.N) continue;
       float v[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[h][j]);
       if (row < p.M) epilogue_math(p, eo, v, row, cc);
       if (!pair_staged) {
         if (row < p.M) epilogue_store_rowwise(p, eo, v, row, cc);
