@@ -193,15 +193,16 @@ conv_fwd_implicit_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_c
       for (int c = 0; c < BN / 64; c += 2) {
         const int col0 = col_base + c * 32;
         if (col0 >= p.O) continue;   // O % 64 == 0: a pair of chunks is entirely inside or outside
+        uint32_t rr[2][32];  // both chunks requested before the one wait
+        tmem_ld_32x32(t_addr + c * 32, rr[0]);
+        tmem_ld_32x32(t_addr + (c + 1) * 32, rr[1]);
+        tmem_ld_wait();
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_addr + (c + h) * 32, r);
-          tmem_ld_wait();
           const int cc = col0 + h * 32;
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[h][j]);
           if (p.bias) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] += __bfloat162float(p.bias[cc + j]);  // same address in every lane: a broadcast
@@ -394,14 +395,15 @@ conv_fwd_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       long long orow[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) orow[i] = conv_out_row(p, ni, hi, wi, q * 32 + i * 4 + (lane >> 3));
+      uint32_t rr[2][32];  // both chunks requested before the one wait
+      tmem_ld_32x32(t_addr, rr[0]);
+      tmem_ld_32x32(t_addr + 32, rr[1]);
+      tmem_ld_wait();
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_addr + h * 32, r);
-        tmem_ld_wait();
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[h][j]);
         if (p.bias) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] += __bfloat162float(p.bias[h * 32 + j]);
