@@ -6,7 +6,7 @@ over ranks). Launch with one process per GPU:
 Shapes are those of GPT-2 small with 16 sequences of 1024 tokens per tensor-parallel pair. A hand-off is timed
 together with the layer norm it rides on, in three forms:
 
-    fused   layer norm, rows sent to the peers by copy engine -> all-gather GEMM  |  GEMM that pushes partial sums -> layer norm that pulls
+    fused   layer norm that also sends its rows to the peers -> all-gather GEMM   |  GEMM that pushes partial sums -> layer norm that pulls
     nccl    layer norm -> all_gather -> GEMM                           |  GEMM -> reduce_scatter -> layer norm
     local   layer norm -> GEMM on an already complete operand          |  GEMM -> layer norm (no communication at all)
 
@@ -27,7 +27,7 @@ tp = dist.get_world_size()
 topo = Topology(f"tp{tp}")
 dev = torch.device("cuda", local)
 heap = SymmetricHeap(2 << 30, None, dev)
-cc = CommContext(topo, heap, True, dev)   # TNNB_TP_PUSH=ln selects the in-kernel push for comparison
+cc = CommContext(topo, heap, True, dev)   # TNNB_TP_PUSH selects who sends the rows (ln, gemm, split)
 cn = CommContext(topo, None, False, dev)
 PEAK = 1393.6e12  # measured sustained cuBLAS bf16 rate of this pool (MEASURED_PEAKS.json); burst 1681.9e12
 LINK = 770e9      # measured peer-copy bandwidth per direction
@@ -58,8 +58,8 @@ t_ln = timeit(lambda: raw.layernorm_fwd(x, None, gamma, beta, 1e-5))
 for name, N in (("QKV", 3 * E // tp), ("fc1", 4 * E // tp)):
     ctr = cc.new_pass_counter(); site = GatherSite(cc, M, E, ctr); site_n = GatherSite(cn, M, E); w = bf(N, E)
     def fused():
-        ctr.add_(1); raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site.mine(), tp_push=site.push_args()); site.after_produce()
-        y = site.gemm(w); cc.join(); return y
+        ctr.add_(1); raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site.mine(), tp_push=site.push_args())
+        y = site.gemm(w); return y
     def nccl():
         raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site_n.mine()); return site_n.gemm(w)
     full = bf(M, E)
@@ -88,10 +88,10 @@ for name, K in (("attention out", E // tp), ("fc2", 4 * E // tp)):
 # the pieces on their own: what a push costs the kernel that carries it
 ctr = cc.new_pass_counter(); site = GatherSite(cc, M, E, ctr)
 def ln_push():
-    raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site.mine(), tp_push=site.push_args()); site.after_produce(); cc.join()
+    raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site.mine(), tp_push=site.push_args())
 def push_only():
-    site.push(x); cc.join()
-parts = {"push_mode": 0.0 if cc.push_mode == "ce" else 1.0, "ln_fwd_us": t_ln, "ln_fwd_then_push_us": timeit(ln_push),
+    site.push(x)
+parts = {"ln_fwd_us": t_ln, "ln_fwd_then_push_us": timeit(ln_push),
          "push_only_us": timeit(push_only)}
 # the same rows sent by the bulk-copy unit (one thread per block, shared-memory staging), checked against NCCL once
 if cc.push_mode in ("ln", "split"):
@@ -101,7 +101,7 @@ if cc.push_mode in ("ln", "split"):
     parts["push_bulk_matches_nccl"] = float(torch.equal(site.buf, ref))
     _lib.check_status()
     for ctas in (148, 296, 592):
-        parts[f"push_bulk_{ctas}ctas_us"] = timeit(lambda: (site.push(x, bulk_ctas=ctas), cc.join()))
+        parts[f"push_bulk_{ctas}ctas_us"] = timeit(lambda: (site.push(x, bulk_ctas=ctas)))
     # the layer-norm kernel sending its rows the same way (a staging row per warp, one bulk copy per row and peer)
     os.environ["TNNB_TP_LN_BULK"] = "1"
     site.buf.zero_(); torch.cuda.synchronize(); dist.barrier()
@@ -112,8 +112,8 @@ if cc.push_mode in ("ln", "split"):
     parts["ln_fwd_then_bulk_push_us"] = timeit(ln_push)
     ctrb = cc.new_pass_counter(); siteb = GatherSite(cc, M, E, ctrb); wq = bf(3 * E // tp, E)
     def fused_bulk():
-        ctrb.add_(1); raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=siteb.mine(), tp_push=siteb.push_args()); siteb.after_produce()
-        y = siteb.gemm(wq); cc.join(); return y
+        ctrb.add_(1); raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=siteb.mine(), tp_push=siteb.push_args())
+        y = siteb.gemm(wq); return y
     parts["qkv_handoff_ln_bulk_us"] = timeit(fused_bulk); _lib.check_status()
     os.environ["TNNB_TP_LN_BULK"] = "0"
     parts["qkv_handoff_ln_stores_us"] = timeit(fused_bulk); _lib.check_status()

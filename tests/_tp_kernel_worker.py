@@ -40,7 +40,7 @@ def main():
     heap = SymmetricHeap(512 << 20, None, dev)
     cc = CommContext(topo, heap, True, dev)
     if len(sys.argv) > 1:
-        cc.push_mode = sys.argv[1]  # "split" (default), "gemm", "ce" or "ln": see CommContext.push_mode
+        cc.push_mode = sys.argv[1]  # "ln" (default), "split" or "gemm": see CommContext.push_mode
     cn = CommContext(topo, None, False, dev)  # NCCL path of the same classes
     torch.manual_seed(1000 + rank)
     res = {}
@@ -62,9 +62,7 @@ def main():
             x = bf(rows, K)
             ctr.add_(1)
             raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site.mine(), tp_push=site.push_args())
-            site.after_produce()
             y = site.gemm(w, b_t=b_t, bias=bias)
-            cc.join()
             raw.layernorm_fwd(x, None, gamma, beta, 1e-5, h_out=site_n.mine())
             y_n = site_n.gemm(w, b_t=b_t, bias=bias)
             xs = torch.cat(gather(x, tp)).float()

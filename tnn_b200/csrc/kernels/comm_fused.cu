@@ -142,15 +142,6 @@ tp_resolve_kernel(const bf16* __restrict__ a, bf16* __restrict__ out, long long 
   }
 }
 
-// Publish rows that a copy-engine transfer earlier in the stream has delivered: add `amount` to `n_blocks`
-// consecutive row-block counters, starting at `first_block`, on every peer. One warp; the fence orders the adds
-// behind whatever this stream wrote before.
-__global__ void tp_signal_kernel(const __grid_constant__ TpPush push, int first_block, int n_blocks, uint32_t amount) {
-  __threadfence_system();
-  for (int b = threadIdx.x; b < n_blocks; b += blockDim.x)
-    for (int i = 0; i < push.n; ++i) red_add_sys(push.ready[i] + first_block + b, amount);
-}
-
 // ===================================================== DP: reduce + optimizer + broadcast
 struct DpParams {
   PeerFlags peers;
@@ -356,29 +347,6 @@ int tnnb_tp_push_bulk(const void* src, void* local_dst, long long rows, int C, i
   if (ctas <= 0) ctas = 148 * 2;
   const int grid = (int)(pieces < ctas ? pieces : ctas);
   tp_push_bulk_kernel<<<grid, 32, smem, (cudaStream_t)stream>>>((const bf16*)src, (bf16*)local_dst, rows, C, push, status);
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : -(int)e - 1000;
-}
-
-// Copy-engine form of the push, for a side stream: `bytes` from src to dst (a peer's memory) with cudaMemcpyAsync,
-// which the driver runs on a copy engine over NVLink without occupying an SM.
-int tnnb_peer_copy(void* dst, const void* src, unsigned long long bytes, void* stream) {
-  cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
-  return e == cudaSuccess ? 0 : -(int)e - 1000;
-}
-
-// After such copies: add `amount` to counters [first_block, first_block + n_blocks) of every peer (ready[i] =
-// base of peer i's counter array).
-int tnnb_tp_signal(int n_push, void** push_ready, int first_block, int n_blocks, unsigned int amount, void* stream) {
-  if (n_push < 0 || n_push > TP_MAX - 1 || first_block < 0 || n_blocks < 0) return -3;
-  if (n_push == 0 || n_blocks == 0) return 0;
-  TpPush push{};
-  push.n = n_push;
-  for (int i = 0; i < n_push; ++i) {
-    if (!push_ready[i]) return -4;
-    push.ready[i] = (uint32_t*)push_ready[i];
-  }
-  tp_signal_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(push, first_block, n_blocks, amount);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e - 1000;
 }

@@ -100,10 +100,6 @@ def _declare(lib):
     lib.tnnb_tp_push_bulk.restype = i
     lib.tnnb_tp_resolve.argtypes = [vp, vp, ll, i, i, vp, vp, vp, u, vp, vp]
     lib.tnnb_tp_resolve.restype = i
-    lib.tnnb_peer_copy.argtypes = [vp, vp, ctypes.c_ulonglong, vp]
-    lib.tnnb_peer_copy.restype = i
-    lib.tnnb_tp_signal.argtypes = [i, vp, i, i, u, vp]
-    lib.tnnb_tp_signal.restype = i
     _DECLARED = True
 
 
@@ -124,24 +120,13 @@ class CommContext:
         #           warps of plain stores before) - the copy shares the unit with the GEMM's own operand loads, and
         #           the GEMM's remote tiles cannot finish before the last rows have landed.
         #   "split" the layer-norm kernel sends the first ``ln_share`` of the rows, the GEMM's copy warp the rest: 69 us.
-        #   "ce"    copy-engine transfers on a side stream in two halves, each followed by a one-warp kernel that
-        #           updates the counters: the copy itself is the fastest mover (21 us for 12.6 MB, no SM time), but
-        #           the four extra graph nodes and the cross-stream edges cost more than it saves: 77 us.
+        # A copy-engine form (cudaMemcpyAsync on a side stream followed by a one-warp kernel that updates the counters)
+        # was measured at 77 us and then removed: that kernel has to run beside the GEMM of its own GPU, which is
+        # waiting for the other rank's counter update - two separate launches that depend on running at the same time.
         self.push_mode = os.environ.get("TNNB_TP_PUSH", "ln")
         self.ln_share = float(os.environ.get("TNNB_TP_LN_SHARE", "0.5"))
-        self.side = None
-        self._forked = False
         if self.fused:
             _declare(self.lib)
-            if device.type == "cuda":
-                self.side = torch.cuda.Stream(device=device, priority=-1)
-
-    def join(self) -> None:
-        """Make the current stream wait for the side stream's transfers (end of a pass: the rows they read may be
-        overwritten afterwards, and a stream capture must end with every forked stream joined)."""
-        if self._forked:
-            torch.cuda.current_stream().wait_stream(self.side)
-            self._forked = False
 
     def new_pass_counter(self) -> torch.Tensor:
         """A device word that counts the passes through one set of sites (bumped once at the start of every
@@ -179,7 +164,7 @@ class GatherSite:
             self.push_ready = ptr_array([rdy[r] for r in peers])
             # rows [0, ln_rows) of this rank's shard travel with the producing kernel, the rest with the GEMM
             blocks = self.rows // 128
-            share = {"ln": 1.0, "gemm": 0.0, "ce": 0.0}.get(cc.push_mode, cc.ln_share)
+            share = {"ln": 1.0, "gemm": 0.0}.get(cc.push_mode, cc.ln_share)
             self.ln_blocks = min(blocks, max(0, int(round(blocks * share))))
             self.ln_rows = self.ln_blocks * 128
         else:
@@ -190,32 +175,8 @@ class GatherSite:
 
     def push_args(self):
         """Arguments that make a layer-norm kernel writing :meth:`mine` deliver the rows to the peers as well
-        (``None`` on the NCCL path and when the rows travel by copy engine, see :meth:`after_produce`)."""
+        (``None`` on the NCCL path and when the consuming GEMM sends all of them)."""
         return self if (self.cc.fused and self.cc.push_mode in ("ln", "split") and self.ln_rows > 0) else None
-
-    def after_produce(self) -> None:
-        """Call once the kernel that writes :meth:`mine` has been launched on the current stream. In copy-engine
-        mode this starts the transfer of the rows to every peer on the side stream (two halves, each followed by
-        the counter update that lets the peer's GEMM use them); otherwise it does nothing."""
-        cc = self.cc
-        if not cc.fused or cc.push_mode != "ce" or self.n_push == 0:
-            return
-        main = torch.cuda.current_stream()
-        cc.side.wait_stream(main)
-        cc._forked = True
-        row_bytes = self.K * 2
-        blocks = self.rows // 128
-        halves = [(0, blocks)] if blocks < 2 else [(0, blocks // 2), (blocks // 2, blocks)]
-        src0 = self.mine().data_ptr()
-        side = ctypes.c_void_p(cc.side.cuda_stream)
-        for (b0, b1) in halves:
-            off, nbytes = b0 * 128 * row_bytes, (b1 - b0) * 128 * row_bytes
-            for i in range(self.n_push):
-                _lib.check_rc(cc.lib.tnnb_peer_copy(ctypes.c_void_p(self.push_dst[i] + off), ctypes.c_void_p(src0 + off), nbytes, side),
-                              "tnnb_peer_copy")
-            _lib.check_rc(cc.lib.tnnb_tp_signal(self.n_push, self.push_ready, self.push_row0 // 128 + b0, b1 - b0, 128, side),
-                          "tnnb_tp_signal")
-            LAUNCHES["count"] += 1
 
     def push(self, src: Optional[torch.Tensor] = None, bulk_ctas: Optional[int] = None) -> None:
         """Stand-alone push: copy ``src`` (default: the rows already in :meth:`mine`) to the peers and publish.
@@ -229,7 +190,6 @@ class GatherSite:
         if cc.push_mode not in ("ln", "split") or self.ln_rows == 0:
             if src is not None:
                 mine.copy_(src)
-            self.after_produce()
             return
         if src is not None and self.ln_rows < self.rows:
             mine[self.ln_rows:].copy_(src[self.ln_rows:])   # these rows are sent by the GEMM

@@ -57,7 +57,6 @@ class _TPGPTChain(_Segment):
                                               tp_push=site.push_args())
         if h.data_ptr() != tgt.data_ptr():
             tgt.copy_(h)
-        site.after_produce()
         return xo, mean, rstd
 
     def forward(self, vals, ctx):
@@ -111,7 +110,6 @@ class _TPGPTChain(_Segment):
             if pend_site is not None:
                 pending = pend_site.resolve(pending)
             out = raw.binary(x, raw.dropout(pending, p_pend, seed_pend), "add")
-        cc.join()
         # downstream layers (the vocabulary head) see only this rank's rows
         vals[id(self.out_node)] = out.reshape(1, Ms, E)
 
@@ -136,8 +134,6 @@ class _TPGPTChain(_Segment):
                                             tp_push=last["gb2"].push_args() if g.is_cuda else None,
                                             dbias=self.blocks[-1][7].layer.grads[1])
             bias_done = True   # the norm's backward kernel summed the columns of the ddelta it emitted
-            if g.is_cuda:
-                last["gb2"].after_produce()
         else:
             dres, dpend = g, raw.dropout(g, p_pend, seed_pend)
             bias_done = False
@@ -165,8 +161,6 @@ class _TPGPTChain(_Segment):
             tgt = st["gb1"].mine()
             if dy1.data_ptr() != tgt.data_ptr():
                 st["gb1"].push(dy1)
-            else:
-                st["gb1"].after_produce()
             # ---- attention output projection (row parallel) ----
             da = st["gb1"].gemm(wo, b_t=True)                                      # [M, E/tp]
             gemm(st["gb1"].buf, s["a"], a_t=True, b_t=True, out=attn.grads[2], atomic=True)
@@ -185,9 +179,6 @@ class _TPGPTChain(_Segment):
                                             ddelta_out=prev.mine() if prev is not None else None,
                                             tp_pull=st["s_qkv"].pull_args(), tp_push=prev.push_args() if prev is not None else None,
                                             dbias=self.blocks[bi - 1][7].layer.grads[1] if bias_done else None)
-            if prev is not None:
-                prev.after_produce()
-        cc.join()
         if self.in_is_shard:
             if id(self.in_node) not in no_grad_nodes:
                 _accum(gvals, self.in_node, dres.reshape(1, Ms, E))
