@@ -1,4 +1,5 @@
 """The fp32 torch restatements in ops.raw (used as references for the kernels) against autograd."""
+import pytest
 import torch
 
 from tnn_b200.ops import raw
@@ -150,3 +151,32 @@ def test_example_torch_module_on_functional_ops_trains():
     spec.loader.exec_module(mod)
     first, last = mod.main("cpu", 25)
     assert last < 0.6 * first
+
+
+@pytest.mark.parametrize("h,wd,c,o,k,s,p", [(16, 16, 4, 6, 3, 2, 1), (15, 17, 4, 6, 3, 2, 1), (16, 16, 4, 6, 1, 2, 0),
+                                            (14, 14, 3, 5, 7, 2, 3), (12, 12, 2, 3, 5, 3, 2), (9, 9, 2, 3, 3, 2, 0)])
+def test_strided_dgrad_parity_classes(h, wd, c, o, k, s, p):
+    """The decomposition the GPU path uses for the data gradient of a strided convolution: every parity class of input
+    pixels is a stride-1 correlation of ``dy`` with the sub-filter ``_parity_classes`` names. Restated here with
+    plain torch convolutions (same taps, same padding) and compared with ``conv2d_input``."""
+    import torch.nn.functional as F
+    from tnn_b200.ops.conv import _parity_classes
+    torch.manual_seed(0)
+    oh, ow = (h + 2 * p - k) // s + 1, (wd + 2 * p - k) // s + 1
+    dy, w = torch.randn(2, oh, ow, o), torch.randn(o, k, k, c)
+    ref = torch.nn.grad.conv2d_input((2, c, h, wd), w.permute(0, 3, 1, 2), dy.permute(0, 3, 1, 2), s, p).permute(0, 2, 3, 1)
+    dx = torch.zeros(2, h, wd, c)
+    for a, hc, khs, phc in _parity_classes(h, k, s, p):
+        for b, wc, kws, pwc in _parity_classes(wd, k, s, p):
+            if not khs or not kws or hc <= 0 or wc <= 0:
+                continue
+            # the same strided slice + flip the GPU path takes (no index tensors)
+            w_sub = w[:, khs[-1]::s, kws[-1]::s].flip(1, 2)
+            assert torch.equal(w_sub, w[:, khs][:, :, kws])
+            pt, pl = max(phc, 0), max(pwc, 0)
+            pb = max(0, hc - 1 + len(khs) - 1 - phc - (oh - 1))
+            pr = max(0, wc - 1 + len(kws) - 1 - pwc - (ow - 1))
+            d = F.pad(dy.permute(0, 3, 1, 2), (pl, pr, pt, pb))[:, :, pt - phc:, pl - pwc:]
+            y = F.conv2d(d, w_sub.permute(3, 0, 1, 2))[:, :, :hc, :wc]   # filter [C, O, th, tw]
+            dx[:, a::s, b::s, :] = y.permute(0, 2, 3, 1)
+    assert torch.allclose(dx, ref, atol=1e-4, rtol=1e-4)
