@@ -3,7 +3,7 @@ run): the two ranks of a pair are emulated as two sets of buffers on the same de
 the other on one stream, every producer before its consumer, so no kernel waits for a launch that has not happened.
 
     python benchmarks/tp_handoff_single_gpu.py [--rows 8192] [--iters 3]
-    ncu --set full --clock-control none -k regex:gemm_bf16_tcgen05_pair_kernel -s 8 -c 4 -o gpurun_out/tp_gemm \\
+    ncu --set full --clock-control none -k regex:gemm_bf16_tcgen05_pair_kernel -s 8 -c 4 -o tp_gemm \\
         python benchmarks/tp_handoff_single_gpu.py --iters 2
 
 Per iteration and rank: layer norm that stores its rows into the other rank's gather buffer, all-gather GEMM (QKV shape
